@@ -1,0 +1,169 @@
+/*
+ * lum_b200.h — C ABI of the B200 execution runtime for Luminal-style compiled decoder graphs.
+ *
+ * This is the boundary a host-language binding (the Rust `impl luminal::op::Runtime`, a ctypes
+ * wrapper, a C++ class) links against.  It replaces what `crates/luminal_cuda` provides behind
+ * `trait Runtime` (src/op.rs:10-30) plus the inherent methods user code calls on the runtime
+ * (`set_data`, `get_f32`, `load_safetensors`; crates/luminal_cuda/src/runtime.rs:133-236).
+ *
+ * Conventions
+ *   - every function returns an int32 status: 0 = ok, negative = error (LUM_E_*); nothing aborts,
+ *     the context stays usable after an error (the reference's search relies on `catch_unwind`
+ *     around a failing candidate, src/graph.rs:419-447);
+ *   - `lum_last_error(rt)` gives the message of the last failure on that runtime (or, with NULL,
+ *     of the last failed lum_create on this thread);
+ *   - plain pointers and sizes only; host pointers unless the name says `device`;
+ *   - one runtime = one device = one stream, single-threaded use (as the reference:
+ *     crates/luminal_cuda/src/runtime.rs:123-130).
+ *   - there is no CPU fallback: without a usable CUDA device lum_create fails.
+ */
+#ifndef LUM_B200_H
+#define LUM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "lum_llir.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct lum_rt lum_rt;
+
+enum {
+    LUM_OK = 0,
+    LUM_E_INVALID = -1,   /* bad argument / shape / state */
+    LUM_E_CUDA = -2,      /* a CUDA call failed; message has the CUDA error string */
+    LUM_E_UNSUPPORTED = -3,
+    LUM_E_DEVICE = -4,    /* a kernel reported a device-side status (bounded wait ran out, bad token, ...) */
+    LUM_E_NOMEM = -5
+};
+
+/* Replaces `CudaRuntime::initialize(stream)` (crates/luminal_cuda/src/runtime.rs:118-131): the
+ * reference hard-codes device 0 and takes a cudarc stream; here the device is a parameter. */
+typedef struct lum_config {
+    int32_t device;       /* CUDA device ordinal */
+    int32_t use_graph;    /* 1: replay one captured CUDA graph per token (default); 0: plain launches */
+    int32_t use_pdl;      /* 1: programmatic dependent launch between kernels (default); 0: off */
+    int32_t attn_splits;  /* CTAs per KV head in decode attention; 0 = choose from the SM count */
+} lum_config;
+
+void lum_config_default(lum_config* cfg);
+int32_t lum_create(const lum_config* cfg, lum_rt** out);
+void lum_destroy(lum_rt* rt);
+const char* lum_last_error(const lum_rt* rt);
+/* Library / device facts: SM count, bytes of device memory, compute capability major*10+minor. */
+int32_t lum_device_info(const lum_rt* rt, int32_t* sm_count, uint64_t* mem_bytes, int32_t* cc);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decoder plan.  The reference builds the model as a graph (`Llama::init/forward`,
+ * examples/llama/src/model.rs:29-114) and the search lowers it to block ops; the weights enter
+ * as named Input tensors.  This entry describes the same computation by its hyper-parameters so
+ * the runtime can lay out weights, KV cache and the per-token kernel schedule directly.
+ * Tensor slots name the reference's safetensors labels:
+ *   EMBED "model.embed_tokens.weight", ATTN_NORM "…input_layernorm.weight", Q/K/V/O
+ *   "…self_attn.{q,k,v,o}_proj.weight", MLP_NORM "…post_attention_layernorm.weight",
+ *   GATE/UP/DOWN "…mlp.{gate,up,down}_proj.weight", FINAL_NORM "model.norm.weight",
+ *   LM_HEAD "lm_head.weight", Q_NORM/K_NORM Qwen's per-head gains (examples/qwen/src/model.rs:217-251).
+ */
+typedef enum lum_slot {
+    LUM_S_EMBED = 0, LUM_S_ATTN_NORM, LUM_S_Q, LUM_S_K, LUM_S_V, LUM_S_O, LUM_S_MLP_NORM,
+    LUM_S_GATE, LUM_S_UP, LUM_S_DOWN, LUM_S_FINAL_NORM, LUM_S_LM_HEAD, LUM_S_Q_NORM, LUM_S_K_NORM
+} lum_slot;
+
+typedef struct lum_model_desc {
+    int32_t n_layers, hidden, n_q_heads, n_kv_heads, head_dim, ffn, vocab;
+    int32_t max_seq;        /* KV-cache capacity in positions (reference: main.rs:19,48) */
+    float rms_eps;          /* the graph constant, e.g. 1e-5; used after its 6-decimal text round trip */
+    float rope_theta;
+    int32_t rope_style;     /* 0: adjacent pairs as the Llama graph (model.rs:146-157); 1: split halves (qwen) */
+    uint32_t weight_dtype;  /* LUM_F32 or LUM_Q8_0: all linear weights */
+    uint32_t embed_dtype;   /* LUM_F32 or LUM_BF16: embedding table and norm gains */
+    uint32_t kv_dtype;      /* LUM_F32 (reference: model.rs:200-215) or LUM_BF16 */
+    int32_t qk_norm;        /* per-head RMSNorm on q and k (Qwen3) */
+    int32_t tied_head;      /* lm_head = embedding table (examples/qwen/src/model.rs:127) */
+    int32_t max_new_tokens; /* capacity of the on-device token log of lum_decode_greedy */
+    /* tensor parallel: this rank's shard.  1/0 = whole model.  Heads and FFN columns are split
+     * evenly; o/down hold a K-slice and their outputs are summed over ranks by the caller's
+     * collective (see lum_tp_*). */
+    int32_t tp_size, tp_rank;
+} lum_model_desc;
+
+int32_t lum_model_init(lum_rt* rt, const lum_model_desc* desc);
+/* Replaces `set_data(id, data)` / `load_safetensors` for weight tensors
+ * (crates/luminal_cuda/src/runtime.rs:133-165).  `dtype` = LUM_F32, LUM_BF16 or LUM_Q8_0 (wire
+ * blocks of lum_llir.h); `bytes` must match the slot's full (unsharded) shape. */
+int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void* host, size_t bytes, uint32_t dtype);
+/* Fill every tensor from the counter-based generator (documented in csrc/lum_synth.cu). */
+int32_t lum_model_synth(lum_rt* rt, uint64_t seed);
+/* Read `n` elements of a (possibly quantised) tensor back as f32, starting at element `offset`
+ * of this rank's shard.  For Q8_0: float(quant) * float(scale). */
+int32_t lum_model_get_weight_f32(lum_rt* rt, int32_t slot, int32_t layer, size_t offset, size_t n, float* host_out);
+/* Bytes of weights a decode step streams from HBM (all linear planes + gains + one embedding row). */
+int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes);
+
+/* KV cache: owned by the runtime (the reference has caller-owned buffers whose raw addresses are
+ * baked into op payloads, examples/llama/src/model.rs:194-223).  reset = `KVCache::reset`. */
+int32_t lum_kv_reset(lum_rt* rt);
+/* Copy rows [0, rows) of one layer's K (kind 0) or V (kind 1) cache to host as f32. */
+int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float* host_out);
+
+/* ---------------------------------------------------------------------------------------------
+ * Execution, at the level of the reference's decode loop (examples/llama/src/main.rs:82-118):
+ *   set_dim('s', n); set_dim('p', prev); set_data(input, ids); execute(); get_f32(logits); sample.
+ */
+/* `Graph::set_dim` (src/graph.rs:63-65): 's' = tokens this call, 'p' = tokens already cached. */
+int32_t lum_set_dim(lum_rt* rt, char dim, uint64_t value);
+/* `set_data(input.id, token ids)`: n must equal the current 's'. */
+int32_t lum_set_tokens(lum_rt* rt, const int32_t* ids, size_t n);
+/* `Runtime::execute(&dyn_map)` (src/op.rs:17): runs the s tokens at positions p..p+s-1, appends
+ * their K/V to the cache, leaves the logits of the LAST row and its greedy token on the device.
+ * (The reference graph computes logits for all s rows; only the last row is ever sampled,
+ * main.rs:109-113.)  Asynchronous; lum_get_* synchronise. */
+int32_t lum_execute(lum_rt* rt);
+/* `get_f32(logits.id)` for the last row: n = vocab (or this rank's vocab shard under TP). */
+int32_t lum_get_logits(lum_rt* rt, float* host_out, size_t n);
+/* The greedy sample of the last executed row — `sample()` of main.rs:137-148 (last maximum wins). */
+int32_t lum_get_token(lum_rt* rt, int32_t* token);
+
+/* Device-resident greedy loop: feeds each sampled token back as the next input, `n_steps` times,
+ * starting from the token/position state the last lum_execute (or lum_decode_greedy) left.
+ * No host transfer or synchronisation happens inside.  Tokens accumulate in a device log. */
+int32_t lum_decode_greedy(lum_rt* rt, int32_t n_steps);
+/* Copy the first `n` tokens of the log written since the last lum_decode_reset. Synchronises. */
+int32_t lum_get_decoded(lum_rt* rt, int32_t* host_out, size_t n);
+int32_t lum_decode_reset(lum_rt* rt);
+/* Block until all submitted work is done and report device-side status (LUM_E_DEVICE if a kernel flagged one). */
+int32_t lum_synchronize(lum_rt* rt);
+
+/* `Runtime::profile` (src/op.rs:18-23): time `trials` decode steps with CUDA events on the
+ * runtime's stream (state is restored afterwards); returns mean microseconds per step and a
+ * display string such as "1.30 ms/token". */
+int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec_per_step, char* display, size_t display_len);
+/* Number of kernel launches one decode step issues (graph nodes when captured). */
+int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n);
+/* CUDA stream the runtime launches on (a cudaStream_t), for callers that time with their own events. */
+void* lum_stream(lum_rt* rt);
+
+/* ---------------------------------------------------------------------------------------------
+ * Stand-alone operators (one launch each; device pointers).  These are the block ops of
+ * crates/luminal_cuda/src/block/ops.rs as single calls, for operator-level tests and for hosts
+ * that schedule ops themselves.  `stream` is a cudaStream_t (NULL = default stream).
+ */
+/* y[N] = W[N,K] x[K]; W in Q8_0 device planes (quants int8 [N,K], scales f16 [N,K/32]).
+ * `TileMatmulFullSplit` M==1 path (ops.rs:1588-1651) for a Q8_0 right-hand side. */
+int32_t lum_op_gemv_q8_0(const int8_t* quants_dev, const void* scales_dev, int32_t n, int32_t k,
+                         const float* x_dev, float* y_dev, int32_t force_direct, void* stream);
+int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev, void* stream);
+/* Q8_0 wire blocks (host layout, on device) -> planes; planes -> f32. */
+int32_t lum_op_q8_0_unpack(const uint8_t* blocks_dev, size_t n_blocks, int8_t* quants_dev, void* scales_dev, void* stream);
+int32_t lum_op_q8_0_dequant(const int8_t* quants_dev, const void* scales_dev, size_t n_elems, float* out_dev, void* stream);
+/* Synthetic tensors on the device (generator of csrc/lum_synth.cu). */
+int32_t lum_op_synth_q8_0(uint64_t seed, uint64_t tensor_id, size_t n_elems, int8_t* quants_dev, void* scales_dev, void* stream);
+int32_t lum_op_synth_normal(uint64_t seed, uint64_t tensor_id, uint32_t dtype, size_t n, int32_t ones, void* out_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUM_B200_H */

@@ -1,0 +1,116 @@
+// Argument blocks and launch entry points shared by the kernel files and the runtime.
+#pragma once
+#include "lum_common.cuh"
+
+namespace lum {
+
+// Weight element kinds (values follow lum_dtype in include/lum_llir.h).
+enum : int { WK_F32 = 0, WK_BF16 = 2, WK_Q8 = 7 };
+
+// What a matrix-vector kernel does with each finished row sum.
+enum : int {
+    EPI_STORE = 0,    // y[row] = acc
+    EPI_RESID = 1,    // y[row] = resid[row] + acc          (residual add, RowAdd in the reference)
+    EPI_SWIGLU = 2,   // y[row] = silu(acc_gate) * acc_up   (two segments walked in step)
+    EPI_ARGMAX = 3,   // y[row] = acc, then greedy sample over all rows (last maximum wins)
+};
+
+// Device-resident decode-loop state: one graph replay per token needs no host traffic.
+struct DecodeState {
+    int pos;        // cached tokens so far == position of the token being processed
+    int tok;        // token being processed
+    int step;       // tokens logged so far (index into tokens_out)
+    int max_steps;  // capacity of tokens_out
+    int vocab;
+    int max_seq;
+    int log;        // 1: the sampler appends to tokens_out
+    int last_tok;   // most recent greedy sample
+};
+
+struct GemvSeg {
+    const void* w;      // quants (int8 [rows, K]) for Q8_0, else the f32 / bf16 matrix [rows, K]
+    const __half* s;    // Q8_0 scales [rows, K/32], else null
+    int rows;
+};
+
+struct GemvArgs {
+    GemvSeg seg[3];
+    int nseg;
+    int K;
+    int wkind;
+    int epi;
+    const float* x;        // [K] activations
+    const float* x_add;    // optional: the kernel works on x + x_add (a reduced partial sum joining the residual stream)
+    float* x_out;          // optional: CTA 0 stores x + x_add here (must not alias x: other CTAs still read x)
+    const void* gain;      // RMSNorm gains [K] (null: no norm prologue)
+    int gain_kind;         // WK_F32 or WK_BF16
+    float eps;
+    float* y;
+    const float* resid;
+    // greedy-sample epilogue
+    float* part_val;       // [grid]
+    int* part_idx;         // [grid]
+    unsigned int* counter; // arrival ticket, left at 0
+    DecodeState* state;
+    int* tokens_out;
+    int advance;           // 1: the sampler also advances pos/step and feeds the token back
+    uint32_t* status;
+    // geometry of the streaming kernel
+    int KC;                // K-chunk per stage (power of two, divides K, 512..4096)
+    int stages;
+    int max_units;         // most stage-units any CTA owns (sizes the reduction scratch)
+    int use_pdl;
+    int force_direct;      // 1: never take the streaming kernel (operator tests compare the two)
+};
+
+struct AttnArgs {
+    const float* q;        // [n_q * hd] this step's queries (before RoPE)
+    const float* k_new;    // [n_kv * hd] this step's keys (before RoPE)
+    const float* v_new;    // [n_kv * hd]
+    void* k_cache;         // [max_seq, n_kv * hd] bf16 or f32
+    void* v_cache;
+    float* out;            // [n_q * hd]
+    float* part;           // [n_kv, n_splits, G, hd + 2] scratch: unnormalised partial outputs + (max, sum)
+    unsigned int* counters;// [n_kv] arrival tickets, left at 0
+    const DecodeState* state;
+    const void* q_gain;    // per-head RMSNorm gains [hd] or null
+    const void* k_gain;
+    int gain_kind;
+    float qk_eps;
+    int n_q, n_kv, hd, n_splits;
+    int kv_bf16;
+    int rope_style;        // 0 adjacent pairs (graph constants), 1 split halves (powf)
+    float c_inv_d, c_ln_theta, c_log2e, c_half_pi;   // the graph's 6-decimal constants
+    float theta;
+    int window;            // 0: full causal; else attend to the last `window` positions
+    int max_seq;
+    uint32_t* status;
+    int use_pdl;
+};
+
+struct EmbedArgs {
+    const void* table;     // [vocab, H] f32 or bf16
+    int kind;
+    int H;
+    float* x;
+    const DecodeState* state;
+    uint32_t* status;
+    int use_pdl;
+};
+
+// launchers (each returns the CUDA error of the launch)
+cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
+bool gemv_stream_supported(const GemvArgs& a);
+cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t st);
+cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
+
+// synthetic tensors + format conversion
+cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,
+                            size_t full_cols, cudaStream_t st);
+cudaError_t launch_synth_normal(uint64_t seed, uint64_t tid, void* out, int kind, size_t rows, size_t cols, size_t row0, size_t col0,
+                                size_t full_cols, int ones, cudaStream_t st);
+cudaError_t launch_q8_unpack_wire(const uint8_t* blocks, int8_t* q, __half* s, size_t n_blocks, cudaStream_t st);
+cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size_t n_elems, cudaStream_t st);
+cudaError_t launch_to_f32(const void* in, int kind, float* out, size_t n, cudaStream_t st);
+
+}  // namespace lum

@@ -1,0 +1,766 @@
+// Host side of the runtime behind include/lum_b200.h: device buffers, the decoder plan, the
+// per-token kernel schedule (captured once into a CUDA graph and replayed), and the C ABI.
+//
+// What it replaces in the reference: `CudaRuntime` (crates/luminal_cuda/src/runtime.rs:87-116),
+// its `execute` (runtime.rs:681-796: per-step memset of every intermediate, a synchronize after
+// every host op, re-upload of the task queue and pointer table, cuGraphExecKernelNodeSetParams
+// per node) and `CudaGraphOp` (crates/luminal_cuda/src/kernel/to_host.rs:154-436).  Here the only
+// thing that changes between decode steps is a 32-byte state block that lives on the device
+// (position, current token, log cursor), so one instantiated graph is replayed unchanged: no
+// per-step uploads, memsets, parameter updates or host synchronisation.
+//
+// Per token the schedule is: embed -> per layer { [RMSNorm + q,k,v projections] -> [RoPE + cache
+// append + attention] -> [o projection + residual] -> [RMSNorm + gate,up projections + SwiGLU] ->
+// [down projection + residual] } -> [RMSNorm + lm_head + greedy sample + state advance]:
+// 5 launches per layer, each bracket one kernel.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/lum_b200.h"
+#include "lum_kernels.cuh"
+
+using namespace lum;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+struct Tensor {
+    void* w = nullptr;       // quants / f32 / bf16
+    __half* s = nullptr;     // Q8_0 scales
+    int kind = WK_F32;
+    size_t rows = 0, cols = 0;          // this rank's shard
+    size_t row0 = 0, col0 = 0;          // shard origin in the full tensor
+    size_t full_rows = 0, full_cols = 0;
+    size_t bytes() const {
+        const size_t n = rows * cols;
+        return kind == WK_Q8 ? n + n / 16 : kind == WK_BF16 ? n * 2 : n * 4;
+    }
+};
+
+struct LayerW {
+    Tensor q, k, v, o, gate, up, down, attn_norm, mlp_norm, q_norm, k_norm;
+    void* kc = nullptr;
+    void* vc = nullptr;
+};
+
+}  // namespace
+
+struct lum_rt {
+    lum_config cfg{};
+    int sm_count = 0;
+    int cc = 0;
+    size_t mem_bytes = 0;
+    cudaStream_t stream = nullptr;
+    std::string err;
+
+    bool has_model = false;
+    lum_model_desc d{};
+    int nq_l = 0, nkv_l = 0, ffn_l = 0, vocab_l = 0;   // this rank's shard sizes
+    Tensor embed, final_norm, lm_head;
+    std::vector<LayerW> L;
+    std::vector<void*> allocs;
+
+    float *x = nullptr, *qkv = nullptr, *attn = nullptr, *h = nullptr, *logits = nullptr;
+    DecodeState* state = nullptr;
+    int* tokens_out = nullptr;
+    float* attn_part = nullptr;
+    unsigned int* attn_cnt = nullptr;
+    float* am_val = nullptr;
+    int* am_idx = nullptr;
+    unsigned int* am_cnt = nullptr;
+    uint32_t* status = nullptr;
+    int n_splits = 1;
+    float eps6 = 0.0f;
+    float c_inv_d = 0, c_ln_theta = 0, c_log2e = 0, c_half_pi = 0;
+
+    cudaGraphExec_t g_full = nullptr, g_body = nullptr;   // whole step / step without the head
+    int launches_full = 0;
+    bool graph_pdl = false;
+
+    uint64_t dim_s = 1, dim_p = 0;
+    std::vector<int32_t> tokens_in;
+};
+
+namespace {
+
+int fail(lum_rt* rt, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (rt) rt->err = buf; else g_create_error = buf;
+    return code;
+}
+#define CU(rt, call)                                                                                       \
+    do {                                                                                                   \
+        cudaError_t e_ = (call);                                                                           \
+        if (e_ != cudaSuccess) return fail(rt, LUM_E_CUDA, "%s: %s", #call, cudaGetErrorString(e_));      \
+    } while (0)
+
+// "{:.6}" text round trip every f32 graph constant takes in the reference (src/hlir.rs:215-219)
+float round6(double v) {
+    char tmp[64];
+    snprintf(tmp, sizeof tmp, "%.6f", (double)(float)v);
+    return strtof(tmp, nullptr);
+}
+
+int kind_of(uint32_t dt) { return dt == LUM_Q8_0 ? WK_Q8 : dt == LUM_BF16 ? WK_BF16 : WK_F32; }
+
+int dev_alloc(lum_rt* rt, void** p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "cudaMalloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
+    rt->allocs.push_back(*p);
+    return 0;
+}
+
+int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_cols, size_t rows, size_t cols, size_t row0, size_t col0) {
+    t.kind = kind; t.rows = rows; t.cols = cols; t.row0 = row0; t.col0 = col0; t.full_rows = full_rows; t.full_cols = full_cols;
+    const size_t n = rows * cols;
+    if (kind == WK_Q8) {
+        if (cols % 32 || full_cols % 32 || col0 % 32) return fail(rt, LUM_E_INVALID, "Q8_0 tensors need K %% 32 == 0 (K = %zu)", cols);
+        // +64: the streaming kernel's last scale copy may be rounded up to 16 bytes
+        if (int r = dev_alloc(rt, &t.w, n + 64)) return r;
+        if (int r = dev_alloc(rt, (void**)&t.s, n / 16 + 64)) return r;
+    } else {
+        if (int r = dev_alloc(rt, &t.w, n * (kind == WK_BF16 ? 2 : 4) + 64)) return r;
+    }
+    return 0;
+}
+
+void free_model(lum_rt* rt) {
+    if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
+    if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
+    rt->g_full = rt->g_body = nullptr;
+    for (void* p : rt->allocs) cudaFree(p);
+    rt->allocs.clear();
+    rt->L.clear();
+    rt->has_model = false;
+}
+
+// slot -> tensor of this runtime (null if the slot does not exist for this model)
+Tensor* slot_tensor(lum_rt* rt, int slot, int layer) {
+    switch (slot) {
+        case LUM_S_EMBED: return &rt->embed;
+        case LUM_S_FINAL_NORM: return &rt->final_norm;
+        case LUM_S_LM_HEAD: return rt->d.tied_head ? nullptr : &rt->lm_head;
+        default: break;
+    }
+    if (layer < 0 || layer >= rt->d.n_layers) return nullptr;
+    LayerW& l = rt->L[(size_t)layer];
+    switch (slot) {
+        case LUM_S_ATTN_NORM: return &l.attn_norm;
+        case LUM_S_Q: return &l.q;
+        case LUM_S_K: return &l.k;
+        case LUM_S_V: return &l.v;
+        case LUM_S_O: return &l.o;
+        case LUM_S_MLP_NORM: return &l.mlp_norm;
+        case LUM_S_GATE: return &l.gate;
+        case LUM_S_UP: return &l.up;
+        case LUM_S_DOWN: return &l.down;
+        case LUM_S_Q_NORM: return rt->d.qk_norm ? &l.q_norm : nullptr;
+        case LUM_S_K_NORM: return rt->d.qk_norm ? &l.k_norm : nullptr;
+        default: return nullptr;
+    }
+}
+// generator id of a slot: shared with the CPU oracle's own statement of the generator
+uint64_t tensor_id(int slot, int layer) { return (uint64_t)layer * 16u + (uint64_t)slot; }
+int slot_layer_for_id(const lum_rt* rt, int slot, int layer) {
+    return (slot == LUM_S_EMBED || slot == LUM_S_FINAL_NORM || slot == LUM_S_LM_HEAD) ? rt->d.n_layers : layer;
+}
+
+__global__ void set_state_kernel(DecodeState* st, int pos, int tok, int log, int set_pos_tok, int reset_step) {
+    if (set_pos_tok) { st->pos = pos; st->tok = tok; }
+    if (log >= 0) st->log = log;
+    if (reset_step) st->step = 0;
+}
+
+int check_status(lum_rt* rt) {
+    uint32_t st = 0;
+    CU(rt, cudaMemcpy(&st, rt->status, sizeof st, cudaMemcpyDeviceToHost));
+    if (st) {
+        cudaMemset(rt->status, 0, sizeof st);
+        return fail(rt, LUM_E_DEVICE, "device status 0x%x (%s%s%s%s%s)", st, (st & LUM_ST_WAIT_FULL) ? "stage wait timed out; " : "",
+                    (st & LUM_ST_WAIT_EMPTY) ? "producer wait timed out; " : "", (st & LUM_ST_WAIT_DRAIN) ? "drain wait timed out; " : "",
+                    (st & LUM_ST_BAD_TOKEN) ? "token id out of range; " : "", (st & LUM_ST_BAD_POS) ? "position out of range; " : "");
+    }
+    return 0;
+}
+
+// ---- the per-token schedule ---------------------------------------------------------------------
+// Issues the kernels of one token on rt->stream.  with_head: include final norm + lm_head + sampler.
+int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
+    const lum_model_desc& d = rt->d;
+    const int H = d.hidden, hd = d.head_dim;
+    const int gk = kind_of(d.embed_dtype);
+    int n = 0;
+    cudaStream_t st = rt->stream;
+
+    EmbedArgs e{};
+    e.table = rt->embed.w; e.kind = rt->embed.kind; e.H = H; e.x = rt->x; e.state = rt->state; e.status = rt->status;
+    e.use_pdl = 0;   // first kernel of the step: ordinary stream order behind the previous step
+    CU(rt, launch_embed(e, st)); n++;
+
+    for (int l = 0; l < d.n_layers; l++) {
+        LayerW& w = rt->L[(size_t)l];
+        GemvArgs a{};
+        a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = w.q.kind;
+        // RMSNorm + q,k,v
+        a.nseg = 3;
+        a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows};
+        a.seg[1] = {w.k.w, w.k.s, (int)w.k.rows};
+        a.seg[2] = {w.v.w, w.v.s, (int)w.v.rows};
+        a.K = H; a.epi = EPI_STORE; a.x = rt->x; a.gain = w.attn_norm.w; a.y = rt->qkv;
+        CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
+
+        AttnArgs t{};
+        t.q = rt->qkv; t.k_new = rt->qkv + (size_t)rt->nq_l * hd; t.v_new = t.k_new + (size_t)rt->nkv_l * hd;
+        t.k_cache = w.kc; t.v_cache = w.vc; t.out = rt->attn; t.part = rt->attn_part; t.counters = rt->attn_cnt;
+        t.state = rt->state; t.q_gain = d.qk_norm ? w.q_norm.w : nullptr; t.k_gain = d.qk_norm ? w.k_norm.w : nullptr;
+        t.gain_kind = gk; t.qk_eps = d.rms_eps; t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits;
+        t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
+        t.c_inv_d = rt->c_inv_d; t.c_ln_theta = rt->c_ln_theta; t.c_log2e = rt->c_log2e; t.c_half_pi = rt->c_half_pi;
+        t.theta = d.rope_theta; t.window = 0; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
+        CU(rt, launch_attn_decode(t, st)); n++;
+
+        // o projection + residual
+        GemvArgs o{};
+        o.status = rt->status; o.use_pdl = pdl; o.wkind = w.o.kind;
+        o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows};
+        o.K = (int)w.o.cols; o.epi = EPI_RESID; o.x = rt->attn; o.y = rt->x; o.resid = rt->x;
+        CU(rt, launch_gemv(o, rt->sm_count, st)); n++;
+
+        // RMSNorm + gate, up + SwiGLU
+        GemvArgs g{};
+        g.status = rt->status; g.use_pdl = pdl; g.gain_kind = gk; g.eps = rt->eps6; g.wkind = w.gate.kind;
+        g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows};
+        g.K = H; g.epi = EPI_SWIGLU; g.x = rt->x; g.gain = w.mlp_norm.w; g.y = rt->h;
+        CU(rt, launch_gemv(g, rt->sm_count, st)); n++;
+
+        // down projection + residual
+        GemvArgs dn{};
+        dn.status = rt->status; dn.use_pdl = pdl; dn.wkind = w.down.kind;
+        dn.nseg = 1; dn.seg[0] = {w.down.w, w.down.s, (int)w.down.rows};
+        dn.K = (int)w.down.cols; dn.epi = EPI_RESID; dn.x = rt->h; dn.y = rt->x; dn.resid = rt->x;
+        CU(rt, launch_gemv(dn, rt->sm_count, st)); n++;
+    }
+    if (with_head) {
+        const Tensor& hw = d.tied_head ? rt->embed : rt->lm_head;
+        GemvArgs a{};
+        a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = hw.kind;
+        a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows};
+        a.K = H; a.epi = EPI_ARGMAX; a.x = rt->x; a.gain = rt->final_norm.w; a.y = rt->logits;
+        a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
+        a.advance = 1;
+        CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
+    }
+    if (n_launch) *n_launch = n;
+    return 0;
+}
+
+int capture_graph(lum_rt* rt, bool with_head, bool pdl, cudaGraphExec_t* out, int* n_launch) {
+    cudaGraph_t g = nullptr;
+    CU(rt, cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeThreadLocal));
+    int r = issue_step(rt, with_head, pdl, n_launch);
+    cudaError_t e = cudaStreamEndCapture(rt->stream, &g);
+    if (r) { if (g) cudaGraphDestroy(g); return r; }
+    if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) { *out = nullptr; return fail(rt, LUM_E_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+    return 0;
+}
+
+int ensure_graphs(lum_rt* rt) {
+    if (!rt->cfg.use_graph || rt->g_full) return 0;
+    bool pdl = rt->cfg.use_pdl != 0;
+    int r = capture_graph(rt, true, pdl, &rt->g_full, &rt->launches_full);
+    if (r && pdl) {
+        // Programmatic edges could not be captured: fall back to ordinary dependencies.
+        cudaGetLastError();
+        pdl = false;
+        r = capture_graph(rt, true, pdl, &rt->g_full, &rt->launches_full);
+    }
+    if (r) return r;
+    rt->graph_pdl = pdl;
+    return capture_graph(rt, false, pdl, &rt->g_body, nullptr);
+}
+
+int run_step(lum_rt* rt, bool with_head) {
+    if (rt->cfg.use_graph) {
+        if (int r = ensure_graphs(rt)) return r;
+        CU(rt, cudaGraphLaunch(with_head ? rt->g_full : rt->g_body, rt->stream));
+        return 0;
+    }
+    return issue_step(rt, with_head, rt->cfg.use_pdl != 0, &rt->launches_full);
+}
+
+}  // namespace
+
+// =================================================================================== C ABI
+
+extern "C" {
+
+void lum_config_default(lum_config* c) {
+    if (!c) return;
+    c->device = 0; c->use_graph = 1; c->use_pdl = 1; c->attn_splits = 0;
+    if (const char* e = getenv("LUM_GRAPH")) c->use_graph = atoi(e);
+    if (const char* e = getenv("LUM_PDL")) c->use_pdl = atoi(e);
+    if (const char* e = getenv("LUM_ATTN_SPLITS")) c->attn_splits = atoi(e);
+}
+
+int32_t lum_create(const lum_config* cfg, lum_rt** out) {
+    if (!out) return fail(nullptr, LUM_E_INVALID, "lum_create: null output pointer");
+    *out = nullptr;
+    lum_config c;
+    if (cfg) c = *cfg; else lum_config_default(&c);
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev <= 0)
+        return fail(nullptr, LUM_E_CUDA, "no usable CUDA device (%s); this runtime has no CPU fallback", cudaGetErrorString(e));
+    if (c.device < 0 || c.device >= ndev) return fail(nullptr, LUM_E_INVALID, "device %d out of range (have %d)", c.device, ndev);
+    CU(nullptr, cudaSetDevice(c.device));
+    cudaDeviceProp p;
+    CU(nullptr, cudaGetDeviceProperties(&p, c.device));
+    if (p.major < 10) return fail(nullptr, LUM_E_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only", p.major, p.minor);
+    lum_rt* rt = new lum_rt();
+    rt->cfg = c; rt->sm_count = p.multiProcessorCount; rt->cc = p.major * 10 + p.minor; rt->mem_bytes = p.totalGlobalMem;
+    e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete rt; return fail(nullptr, LUM_E_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    *out = rt;
+    return 0;
+}
+
+void lum_destroy(lum_rt* rt) {
+    if (!rt) return;
+    cudaSetDevice(rt->cfg.device);
+    cudaStreamSynchronize(rt->stream);
+    free_model(rt);
+    cudaStreamDestroy(rt->stream);
+    delete rt;
+}
+
+const char* lum_last_error(const lum_rt* rt) { return rt ? rt->err.c_str() : g_create_error.c_str(); }
+
+int32_t lum_device_info(const lum_rt* rt, int32_t* sm_count, uint64_t* mem_bytes, int32_t* cc) {
+    if (!rt) return LUM_E_INVALID;
+    if (sm_count) *sm_count = rt->sm_count;
+    if (mem_bytes) *mem_bytes = rt->mem_bytes;
+    if (cc) *cc = rt->cc;
+    return 0;
+}
+
+void* lum_stream(lum_rt* rt) { return rt ? (void*)rt->stream : nullptr; }
+
+int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
+    if (!rt || !dp) return LUM_E_INVALID;
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    cudaStreamSynchronize(rt->stream);
+    free_model(rt);
+    lum_model_desc d = *dp;
+    if (d.tp_size <= 0) { d.tp_size = 1; d.tp_rank = 0; }
+    if (d.max_new_tokens <= 0) d.max_new_tokens = 4096;
+    const int tp = d.tp_size;
+    if (d.n_layers <= 0 || d.hidden <= 0 || d.n_q_heads <= 0 || d.n_kv_heads <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.max_seq <= 0)
+        return fail(rt, LUM_E_INVALID, "model dimensions must be positive");
+    if (d.head_dim != 64 && d.head_dim != 128) return fail(rt, LUM_E_UNSUPPORTED, "head_dim %d (supported: 64, 128)", d.head_dim);
+    if (d.n_q_heads % d.n_kv_heads || d.n_q_heads / d.n_kv_heads > 8) return fail(rt, LUM_E_UNSUPPORTED, "q/kv head ratio must be an integer <= 8");
+    if (d.tp_rank < 0 || d.tp_rank >= tp) return fail(rt, LUM_E_INVALID, "tp_rank %d outside tp_size %d", d.tp_rank, tp);
+    if (d.n_kv_heads % tp || d.ffn % tp || d.vocab % tp) return fail(rt, LUM_E_INVALID, "kv heads, ffn and vocab must divide by tp_size");
+    if (d.weight_dtype != LUM_F32 && d.weight_dtype != LUM_Q8_0) return fail(rt, LUM_E_UNSUPPORTED, "weight dtype must be F32 or Q8_0");
+    if (d.embed_dtype != LUM_F32 && d.embed_dtype != LUM_BF16) return fail(rt, LUM_E_UNSUPPORTED, "embedding dtype must be F32 or BF16");
+    if (d.kv_dtype != LUM_F32 && d.kv_dtype != LUM_BF16) return fail(rt, LUM_E_UNSUPPORTED, "KV dtype must be F32 or BF16");
+    if (d.tied_head && tp > 1) return fail(rt, LUM_E_UNSUPPORTED, "tied head under tensor parallelism");
+    if (tp > 1) return fail(rt, LUM_E_UNSUPPORTED, "tensor-parallel execution is not wired in this build");
+    rt->d = d;
+    rt->nq_l = d.n_q_heads / tp; rt->nkv_l = d.n_kv_heads / tp; rt->ffn_l = d.ffn / tp; rt->vocab_l = d.vocab / tp;
+    const int H = d.hidden, hd = d.head_dim, r = d.tp_rank;
+    const int wk = kind_of(d.weight_dtype), ek = kind_of(d.embed_dtype);
+    const size_t qd = (size_t)d.n_q_heads * hd, kvd = (size_t)d.n_kv_heads * hd;
+    const size_t qd_l = (size_t)rt->nq_l * hd, kvd_l = (size_t)rt->nkv_l * hd;
+
+#define TRY(x) do { if (int r_ = (x)) { free_model(rt); return r_; } } while (0)
+    TRY(alloc_tensor(rt, rt->embed, ek, d.vocab, H, d.vocab, H, 0, 0));
+    TRY(alloc_tensor(rt, rt->final_norm, ek, 1, H, 1, H, 0, 0));
+    if (!d.tied_head) TRY(alloc_tensor(rt, rt->lm_head, wk, d.vocab, H, rt->vocab_l, H, (size_t)r * rt->vocab_l, 0));
+    rt->L.resize((size_t)d.n_layers);
+    const size_t kv_elem = d.kv_dtype == LUM_BF16 ? 2 : 4;
+    for (int l = 0; l < d.n_layers; l++) {
+        LayerW& w = rt->L[(size_t)l];
+        TRY(alloc_tensor(rt, w.attn_norm, ek, 1, H, 1, H, 0, 0));
+        TRY(alloc_tensor(rt, w.mlp_norm, ek, 1, H, 1, H, 0, 0));
+        TRY(alloc_tensor(rt, w.q, wk, qd, H, qd_l, H, r * qd_l, 0));
+        TRY(alloc_tensor(rt, w.k, wk, kvd, H, kvd_l, H, r * kvd_l, 0));
+        TRY(alloc_tensor(rt, w.v, wk, kvd, H, kvd_l, H, r * kvd_l, 0));
+        TRY(alloc_tensor(rt, w.o, wk, H, qd, H, qd_l, 0, r * qd_l));
+        TRY(alloc_tensor(rt, w.gate, wk, d.ffn, H, rt->ffn_l, H, (size_t)r * rt->ffn_l, 0));
+        TRY(alloc_tensor(rt, w.up, wk, d.ffn, H, rt->ffn_l, H, (size_t)r * rt->ffn_l, 0));
+        TRY(alloc_tensor(rt, w.down, wk, H, d.ffn, H, rt->ffn_l, 0, (size_t)r * rt->ffn_l));
+        if (d.qk_norm) {
+            TRY(alloc_tensor(rt, w.q_norm, ek, 1, hd, 1, hd, 0, 0));
+            TRY(alloc_tensor(rt, w.k_norm, ek, 1, hd, 1, hd, 0, 0));
+        }
+        const size_t cache_bytes = (size_t)d.max_seq * kvd_l * kv_elem;
+        TRY(dev_alloc(rt, &w.kc, cache_bytes));
+        TRY(dev_alloc(rt, &w.vc, cache_bytes));
+        cudaMemsetAsync(w.kc, 0, cache_bytes, rt->stream);
+        cudaMemsetAsync(w.vc, 0, cache_bytes, rt->stream);
+    }
+    int splits = rt->cfg.attn_splits;
+    if (splits <= 0) { splits = rt->sm_count / (rt->nkv_l > 0 ? rt->nkv_l : 1); if (splits < 1) splits = 1; if (splits > 32) splits = 32; }
+    rt->n_splits = splits;
+    const int G = d.n_q_heads / d.n_kv_heads;
+    TRY(dev_alloc(rt, (void**)&rt->x, (size_t)H * 4));
+    TRY(dev_alloc(rt, (void**)&rt->qkv, (qd_l + 2 * kvd_l) * 4));
+    TRY(dev_alloc(rt, (void**)&rt->attn, qd_l * 4));
+    TRY(dev_alloc(rt, (void**)&rt->h, (size_t)rt->ffn_l * 4));
+    TRY(dev_alloc(rt, (void**)&rt->logits, (size_t)rt->vocab_l * 4));
+    TRY(dev_alloc(rt, (void**)&rt->state, sizeof(DecodeState)));
+    TRY(dev_alloc(rt, (void**)&rt->tokens_out, (size_t)d.max_new_tokens * 4));
+    TRY(dev_alloc(rt, (void**)&rt->attn_part, (size_t)rt->nkv_l * splits * G * (hd + 2) * 4));
+    TRY(dev_alloc(rt, (void**)&rt->attn_cnt, (size_t)rt->nkv_l * 4));
+    TRY(dev_alloc(rt, (void**)&rt->am_val, 1024 * 4));
+    TRY(dev_alloc(rt, (void**)&rt->am_idx, 1024 * 4));
+    TRY(dev_alloc(rt, (void**)&rt->am_cnt, 4));
+    TRY(dev_alloc(rt, (void**)&rt->status, 4));
+#undef TRY
+    cudaMemsetAsync(rt->attn_cnt, 0, (size_t)rt->nkv_l * 4, rt->stream);
+    cudaMemsetAsync(rt->am_cnt, 0, 4, rt->stream);
+    cudaMemsetAsync(rt->status, 0, 4, rt->stream);
+    cudaMemsetAsync(rt->tokens_out, 0, (size_t)d.max_new_tokens * 4, rt->stream);
+    DecodeState s0{};
+    s0.pos = 0; s0.tok = 0; s0.step = 0; s0.max_steps = d.max_new_tokens; s0.vocab = d.vocab; s0.max_seq = d.max_seq; s0.log = 0; s0.last_tok = 0;
+    CU(rt, cudaMemcpyAsync(rt->state, &s0, sizeof s0, cudaMemcpyHostToDevice, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+
+    rt->eps6 = round6(d.rms_eps);
+    rt->c_inv_d = round6(1.0 / (double)hd);
+    rt->c_ln_theta = round6(std::log((double)d.rope_theta));
+    rt->c_log2e = round6(1.0 / std::log(2.0));
+    rt->c_half_pi = round6(1.5707963267948966);
+    rt->dim_s = 1; rt->dim_p = 0;
+    rt->has_model = true;
+    return 0;
+}
+
+int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void* host, size_t bytes, uint32_t dtype) {
+    if (!rt || !rt->has_model || !host) return fail(rt, LUM_E_INVALID, "set_weight: no model or null data");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    Tensor* t = slot_tensor(rt, slot, layer);
+    if (!t) return fail(rt, LUM_E_INVALID, "set_weight: slot %d / layer %d does not exist in this model", slot, layer);
+    if (kind_of(dtype) != t->kind || (dtype != LUM_F32 && dtype != LUM_BF16 && dtype != LUM_Q8_0))
+        return fail(rt, LUM_E_INVALID, "set_weight: slot %d expects dtype kind %d, got %u", slot, t->kind, dtype);
+    const size_t full = t->full_rows * t->full_cols;
+    const size_t want = dtype == LUM_Q8_0 ? full / 32 * 34 : full * (dtype == LUM_BF16 ? 2 : 4);
+    if (bytes != want) return fail(rt, LUM_E_INVALID, "set_weight: slot %d needs %zu bytes, got %zu", slot, want, bytes);
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    // bytes per element-run in the wire format, so a shard is a 2-D slice of the host tensor
+    const size_t esz_num = dtype == LUM_Q8_0 ? 34 : (dtype == LUM_BF16 ? 2 : 4), esz_den = dtype == LUM_Q8_0 ? 32 : 1;
+    const size_t src_pitch = t->full_cols * esz_num / esz_den, row_bytes = t->cols * esz_num / esz_den;
+    const uint8_t* src = (const uint8_t*)host + t->row0 * src_pitch + t->col0 * esz_num / esz_den;
+    if (dtype == LUM_Q8_0) {
+        void* tmp = nullptr;
+        cudaError_t e = cudaMalloc(&tmp, t->rows * row_bytes);
+        if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "set_weight: staging buffer: %s", cudaGetErrorString(e));
+        e = cudaMemcpy2D(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)t->w, t->s, t->rows * t->cols / 32, rt->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+        cudaFree(tmp);
+        if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "set_weight: %s", cudaGetErrorString(e));
+    } else {
+        CU(rt, cudaMemcpy2D(t->w, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice));
+    }
+    return 0;
+}
+
+int32_t lum_model_synth(lum_rt* rt, uint64_t seed) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "synth: no model");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const lum_model_desc& d = rt->d;
+    auto fill = [&](int slot, int layer, int ones) -> int {
+        Tensor* t = slot_tensor(rt, slot, layer);
+        if (!t) return 0;
+        const uint64_t tid = tensor_id(slot, slot_layer_for_id(rt, slot, layer));
+        cudaError_t e;
+        if (t->kind == WK_Q8) e = launch_synth_q8(seed, tid, (int8_t*)t->w, t->s, t->rows, t->cols, t->row0, t->col0, t->full_cols, rt->stream);
+        else e = launch_synth_normal(seed, tid, t->w, t->kind, t->rows, t->cols, t->row0, t->col0, t->full_cols, ones, rt->stream);
+        if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "synth slot %d layer %d: %s", slot, layer, cudaGetErrorString(e));
+        return 0;
+    };
+    if (int r = fill(LUM_S_EMBED, 0, 0)) return r;
+    if (int r = fill(LUM_S_FINAL_NORM, 0, 1)) return r;
+    if (int r = fill(LUM_S_LM_HEAD, 0, 0)) return r;
+    for (int l = 0; l < d.n_layers; l++) {
+        const int lin[] = {LUM_S_Q, LUM_S_K, LUM_S_V, LUM_S_O, LUM_S_GATE, LUM_S_UP, LUM_S_DOWN};
+        for (int s : lin) if (int r = fill(s, l, 0)) return r;
+        const int nrm[] = {LUM_S_ATTN_NORM, LUM_S_MLP_NORM, LUM_S_Q_NORM, LUM_S_K_NORM};
+        for (int s : nrm) if (int r = fill(s, l, 1)) return r;
+    }
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
+int32_t lum_model_get_weight_f32(lum_rt* rt, int32_t slot, int32_t layer, size_t offset, size_t n, float* host_out) {
+    if (!rt || !rt->has_model || !host_out) return fail(rt, LUM_E_INVALID, "get_weight: no model or null output");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    Tensor* t = slot_tensor(rt, slot, layer);
+    if (!t) return fail(rt, LUM_E_INVALID, "get_weight: slot %d / layer %d does not exist", slot, layer);
+    if (offset + n > t->rows * t->cols) return fail(rt, LUM_E_INVALID, "get_weight: range outside the tensor");
+    if (t->kind == WK_Q8 && (offset % 32)) return fail(rt, LUM_E_INVALID, "get_weight: Q8_0 offset must be a multiple of 32");
+    float* tmp = nullptr;
+    cudaError_t e = cudaMalloc((void**)&tmp, n * 4 + 16);
+    if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "get_weight: %s", cudaGetErrorString(e));
+    if (t->kind == WK_Q8) e = launch_q8_dequant((const int8_t*)t->w + offset, t->s + offset / 32, tmp, n, rt->stream);
+    else e = launch_to_f32((const uint8_t*)t->w + offset * (t->kind == WK_BF16 ? 2 : 4), t->kind, tmp, n, rt->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+    cudaFree(tmp);
+    if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "get_weight: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes) {
+    if (!rt || !rt->has_model || !bytes) return LUM_E_INVALID;
+    uint64_t b = 0;
+    for (const LayerW& w : rt->L) {
+        b += w.q.bytes() + w.k.bytes() + w.v.bytes() + w.o.bytes() + w.gate.bytes() + w.up.bytes() + w.down.bytes();
+        b += w.attn_norm.bytes() + w.mlp_norm.bytes();
+        if (rt->d.qk_norm) b += w.q_norm.bytes() + w.k_norm.bytes();
+    }
+    b += rt->final_norm.bytes();
+    b += rt->d.tied_head ? rt->embed.bytes() : rt->lm_head.bytes();
+    b += (uint64_t)rt->d.hidden * (rt->embed.kind == WK_BF16 ? 2 : 4);   // one embedding row
+    *bytes = b;
+    return 0;
+}
+
+int32_t lum_kv_reset(lum_rt* rt) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "kv_reset: no model");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const size_t bytes = (size_t)rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+    for (LayerW& w : rt->L) {
+        CU(rt, cudaMemsetAsync(w.kc, 0, bytes, rt->stream));
+        CU(rt, cudaMemsetAsync(w.vc, 0, bytes, rt->stream));
+    }
+    rt->dim_p = 0;
+    return 0;
+}
+
+int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float* host_out) {
+    if (!rt || !rt->has_model || !host_out) return fail(rt, LUM_E_INVALID, "kv_read: no model or null output");
+    if (layer < 0 || layer >= rt->d.n_layers || rows < 0 || rows > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "kv_read: bad layer/rows");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const size_t n = (size_t)rows * rt->nkv_l * rt->d.head_dim;
+    if (!n) return 0;
+    float* tmp = nullptr;
+    cudaError_t e = cudaMalloc((void**)&tmp, n * 4);
+    if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "kv_read: %s", cudaGetErrorString(e));
+    const void* src = kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc;
+    e = launch_to_f32(src, rt->d.kv_dtype == LUM_BF16 ? WK_BF16 : WK_F32, tmp, n, rt->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+    cudaFree(tmp);
+    if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "kv_read: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int32_t lum_set_dim(lum_rt* rt, char dim, uint64_t value) {
+    if (!rt) return LUM_E_INVALID;
+    if (dim == 's') rt->dim_s = value;
+    else if (dim == 'p') rt->dim_p = value;
+    else return fail(rt, LUM_E_INVALID, "set_dim: unknown dynamic dimension '%c' (this plan has 's' and 'p')", dim);
+    return 0;
+}
+
+int32_t lum_set_tokens(lum_rt* rt, const int32_t* ids, size_t n) {
+    if (!rt || !ids) return fail(rt, LUM_E_INVALID, "set_tokens: null");
+    rt->tokens_in.assign(ids, ids + n);
+    return 0;
+}
+
+int32_t lum_execute(lum_rt* rt) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "execute: no model loaded");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const uint64_t s = rt->dim_s, p = rt->dim_p;
+    if (s == 0) return fail(rt, LUM_E_INVALID, "execute: 's' is 0");
+    if (rt->tokens_in.size() != s) return fail(rt, LUM_E_INVALID, "execute: 's' = %llu but %zu token ids were set", (unsigned long long)s, rt->tokens_in.size());
+    if (p + s > (uint64_t)rt->d.max_seq) return fail(rt, LUM_E_INVALID, "execute: p + s = %llu exceeds the cache capacity %d", (unsigned long long)(p + s), rt->d.max_seq);
+    for (uint64_t i = 0; i < s; i++) {
+        const int tok = rt->tokens_in[(size_t)i];
+        if (tok < 0 || tok >= rt->d.vocab) return fail(rt, LUM_E_INVALID, "execute: token id %d outside the vocabulary", tok);
+    }
+    for (uint64_t i = 0; i < s; i++) {
+        set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, (int)(p + i), rt->tokens_in[(size_t)i], 0, 1, 0);
+        CU(rt, cudaGetLastError());
+        if (int r = run_step(rt, i + 1 == s)) return r;
+    }
+    return 0;
+}
+
+int32_t lum_get_logits(lum_rt* rt, float* host_out, size_t n) {
+    if (!rt || !rt->has_model || !host_out) return fail(rt, LUM_E_INVALID, "get_logits: no model or null output");
+    if (n != (size_t)rt->vocab_l) return fail(rt, LUM_E_INVALID, "get_logits: expected %d elements, got %zu", rt->vocab_l, n);
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaMemcpyAsync(host_out, rt->logits, n * 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return check_status(rt);
+}
+
+int32_t lum_get_token(lum_rt* rt, int32_t* token) {
+    if (!rt || !rt->has_model || !token) return fail(rt, LUM_E_INVALID, "get_token: no model or null output");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaMemcpyAsync(token, &rt->state->last_tok, 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return check_status(rt);
+}
+
+int32_t lum_decode_reset(lum_rt* rt) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "decode_reset: no model");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, 0, 0, -1, 0, 1);
+    CU(rt, cudaGetLastError());
+    return 0;
+}
+
+int32_t lum_decode_greedy(lum_rt* rt, int32_t n_steps) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "decode: no model loaded");
+    if (n_steps < 0) return fail(rt, LUM_E_INVALID, "decode: negative step count");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, 0, 0, 1, 0, 0);
+    CU(rt, cudaGetLastError());
+    for (int i = 0; i < n_steps; i++)
+        if (int r = run_step(rt, true)) return r;
+    rt->dim_p += (uint64_t)n_steps;
+    return 0;
+}
+
+int32_t lum_get_decoded(lum_rt* rt, int32_t* host_out, size_t n) {
+    if (!rt || !rt->has_model || !host_out) return fail(rt, LUM_E_INVALID, "get_decoded: no model or null output");
+    if (n > (size_t)rt->d.max_new_tokens) return fail(rt, LUM_E_INVALID, "get_decoded: log holds at most %d tokens", rt->d.max_new_tokens);
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaMemcpyAsync(host_out, rt->tokens_out, n * 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return check_status(rt);
+}
+
+int32_t lum_synchronize(lum_rt* rt) {
+    if (!rt) return LUM_E_INVALID;
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    if (!rt->has_model) return 0;
+    return check_status(rt);
+}
+
+int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, size_t display_len) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "profile: no model loaded");
+    if (trials <= 0) trials = 1;
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    DecodeState saved;
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    CU(rt, cudaMemcpy(&saved, rt->state, sizeof saved, cudaMemcpyDeviceToHost));
+    if (saved.pos + trials + 1 > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "profile: not enough cache capacity left for %d trial steps", trials);
+    cudaEvent_t e0, e1;
+    CU(rt, cudaEventCreate(&e0));
+    CU(rt, cudaEventCreate(&e1));
+    int r = run_step(rt, true);   // warm-up, also builds the graphs
+    if (!r) {
+        cudaEventRecord(e0, rt->stream);
+        for (int i = 0; i < trials && !r; i++) r = run_step(rt, true);
+        cudaEventRecord(e1, rt->stream);
+    }
+    cudaStreamSynchronize(rt->stream);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    saved.log = 0;
+    cudaMemcpy(rt->state, &saved, sizeof saved, cudaMemcpyHostToDevice);
+    if (r) return r;
+    if (int s = check_status(rt)) return s;
+    const double us = (double)ms * 1000.0 / trials;
+    if (usec) *usec = us;
+    if (display && display_len) snprintf(display, display_len, "%.3f ms/token", us / 1000.0);
+    return 0;
+}
+
+int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n) {
+    if (!rt || !rt->has_model || !n) return LUM_E_INVALID;
+    *n = 1 + 5 * rt->d.n_layers + 1;
+    return 0;
+}
+
+// ---- stand-alone operators ------------------------------------------------------------------------
+
+static int op_fail(const char* what, cudaError_t e) {
+    g_create_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return LUM_E_CUDA;
+}
+static int cur_sm_count() {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 1;
+}
+static uint32_t* op_status_word() {
+    // one status word per device for the stand-alone operators
+    static uint32_t* words[64] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        if (cudaMalloc((void**)&words[dev], 4) != cudaSuccess) return nullptr;
+        cudaMemset(words[dev], 0, 4);
+    }
+    return words[dev];
+}
+
+int32_t lum_op_gemv_q8_0(const int8_t* q, const void* s, int32_t n, int32_t k, const float* x, float* y, int32_t force_direct, void* stream) {
+    if (!q || !s || !x || !y || n <= 0 || k <= 0 || (k % 32)) { g_create_error = "gemv_q8_0: bad arguments (K must be a multiple of 32)"; return LUM_E_INVALID; }
+    GemvArgs a{};
+    a.nseg = 1; a.seg[0] = {q, (const __half*)s, n}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_STORE; a.x = x; a.y = y;
+    a.status = op_status_word();
+    if (!a.status) return op_fail("gemv_q8_0 status word", cudaErrorMemoryAllocation);
+    a.force_direct = force_direct;
+    const cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("gemv_q8_0", e);
+}
+
+int32_t lum_op_gemv_f32(const float* w, int32_t n, int32_t k, const float* x, float* y, void* stream) {
+    if (!w || !x || !y || n <= 0 || k <= 0) { g_create_error = "gemv_f32: bad arguments"; return LUM_E_INVALID; }
+    GemvArgs a{};
+    a.nseg = 1; a.seg[0] = {w, nullptr, n}; a.K = k; a.wkind = WK_F32; a.epi = EPI_STORE; a.x = x; a.y = y;
+    a.status = op_status_word();
+    if (!a.status) return op_fail("gemv_f32 status word", cudaErrorMemoryAllocation);
+    cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("gemv_f32", e);
+}
+
+int32_t lum_op_q8_0_unpack(const uint8_t* blocks, size_t nb, int8_t* q, void* s, void* stream) {
+    if (!blocks || !q || !s) { g_create_error = "q8_0_unpack: null pointer"; return LUM_E_INVALID; }
+    cudaError_t e = launch_q8_unpack_wire(blocks, q, (__half*)s, nb, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("q8_0_unpack", e);
+}
+int32_t lum_op_q8_0_dequant(const int8_t* q, const void* s, size_t n, float* out, void* stream) {
+    if (!q || !s || !out || (n % 32)) { g_create_error = "q8_0_dequant: bad arguments"; return LUM_E_INVALID; }
+    cudaError_t e = launch_q8_dequant(q, (const __half*)s, out, n, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("q8_0_dequant", e);
+}
+int32_t lum_op_synth_q8_0(uint64_t seed, uint64_t tid, size_t n, int8_t* q, void* s, void* stream) {
+    if (!q || !s || (n % 32)) { g_create_error = "synth_q8_0: bad arguments"; return LUM_E_INVALID; }
+    // a flat tensor: one row of n columns would overflow nothing but keeps indices identical
+    cudaError_t e = launch_synth_q8(seed, tid, q, (__half*)s, 1, n, 0, 0, n, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("synth_q8_0", e);
+}
+int32_t lum_op_synth_normal(uint64_t seed, uint64_t tid, uint32_t dtype, size_t n, int32_t ones, void* out, void* stream) {
+    if (!out || (dtype != LUM_F32 && dtype != LUM_BF16)) { g_create_error = "synth_normal: bad arguments"; return LUM_E_INVALID; }
+    cudaError_t e = launch_synth_normal(seed, tid, out, kind_of(dtype), 1, n, 0, 0, n, ones, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("synth_normal", e);
+}
+
+}  // extern "C"

@@ -1,0 +1,130 @@
+// Weight-side helpers: the counter-based synthetic-tensor generator (there are no checkpoints to
+// load in a benchmark environment; the reference downloads them, examples/llama/src/hf.rs:26-50),
+// the Q8_0 wire <-> device-layout conversion, and dequantisation for inspection.
+//
+// Device layout of a Q8_0 matrix [N, K]: a plane of int8 quants [N, K] followed by a separate
+// plane of binary16 scales [N, K/32].  Same bytes as the 34-byte wire blocks (34/32 B per weight)
+// but every row of either plane starts 16-byte aligned, which bulk copies and 128-bit loads need.
+//
+// Generator (all integer arithmetic except the normal draw, which is binary64 Box-Muller):
+//   key(seed, tid)    = mix(seed + G * (tid + 1)),  G = 0x9E3779B97F4A7C15, mix = SplitMix64 finaliser
+//   r(key, idx, lane) = mix(key + G * (2 * idx + lane))
+//   quant             = ((r(.., 0) >> 32) * 255 >> 32) - 127
+//   normal z          = sqrt(-2 ln u1) cos(2 pi u2), u1 = ((r(..,0) >> 11) + 1) 2^-53, u2 = (r(..,1) >> 11) 2^-53
+//   scale             = f16((float)(|0.02 z| / 127)),   drawn from key(seed, tid + 4096)
+#include "lum_kernels.cuh"
+
+namespace lum {
+
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+static constexpr uint64_t kG = 0x9E3779B97F4A7C15ull;
+__host__ __device__ __forceinline__ uint64_t rng_key(uint64_t seed, uint64_t tid) { return mix64(seed + kG * (tid + 1)); }
+__host__ __device__ __forceinline__ uint64_t rng_draw(uint64_t key, uint64_t idx, uint64_t lane) { return mix64(key + kG * (2 * idx + lane)); }
+
+__device__ __forceinline__ double rng_normal(uint64_t key, uint64_t idx) {
+    const double u1 = (double)((rng_draw(key, idx, 0) >> 11) + 1) * 0x1.0p-53;
+    const double u2 = (double)(rng_draw(key, idx, 1) >> 11) * 0x1.0p-53;
+    return sqrt(-2.0 * log(u1)) * cos(6.283185307179586476925 * u2);
+}
+
+// A shard [rows, cols] of a full tensor with `full_cols` columns, starting at (row0, col0): element
+// (r, c) draws with the index it has in the full tensor, so every tensor-parallel rank regenerates
+// exactly its slice.
+struct Shard { size_t rows, cols, row0, col0, full_cols; };
+
+__global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh) {
+    // 16 quants per thread, one 128-bit store (cols is a multiple of 32)
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+    if (i >= sh.rows * sh.cols) return;
+    const size_t r = i / sh.cols, c = i - r * sh.cols;
+    const size_t gi = (sh.row0 + r) * sh.full_cols + sh.col0 + c;
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const uint64_t rr = rng_draw(key, gi + j * 4 + b, 0) >> 32;
+            const int qv = (int)((rr * 255ull) >> 32) - 127;
+            v |= (uint32_t)(uint8_t)(int8_t)qv << (8 * b);
+        }
+        w[j] = v;
+    }
+    *(uint4*)(q + i) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__global__ void synth_q8_scales(uint64_t skey, __half* s, Shard sh) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t bpr = sh.cols / 32;
+    if (b >= sh.rows * bpr) return;
+    const size_t r = b / bpr, cb = b - r * bpr;
+    const size_t gb = ((sh.row0 + r) * sh.full_cols + sh.col0) / 32 + cb;
+    s[b] = __float2half_rn((float)(fabs(0.02 * rng_normal(skey, gb)) / 127.0));
+}
+__global__ void synth_normal(uint64_t key, void* out, int kind, Shard sh, int ones) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= sh.rows * sh.cols) return;
+    const size_t r = i / sh.cols, c = i - r * sh.cols;
+    const size_t gi = (sh.row0 + r) * sh.full_cols + sh.col0 + c;
+    const float v = ones ? 1.0f : (float)(0.02 * rng_normal(key, gi));
+    if (kind == WK_BF16) ((__nv_bfloat16*)out)[i] = __float2bfloat16_rn(v);
+    else ((float*)out)[i] = v;
+}
+
+cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,
+                            size_t full_cols, cudaStream_t st) {
+    if (cols % 32 || col0 % 32 || full_cols % 32) return cudaErrorInvalidValue;
+    const Shard sh{rows, cols, row0, col0, full_cols};
+    const size_t t16 = rows * cols / 16;
+    synth_q8_quants<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(rng_key(seed, tid), q, sh);
+    const size_t nb = rows * cols / 32;
+    synth_q8_scales<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(rng_key(seed, tid + 4096), s, sh);
+    return cudaGetLastError();
+}
+cudaError_t launch_synth_normal(uint64_t seed, uint64_t tid, void* out, int kind, size_t rows, size_t cols, size_t row0, size_t col0,
+                                size_t full_cols, int ones, cudaStream_t st) {
+    const Shard sh{rows, cols, row0, col0, full_cols};
+    synth_normal<<<(unsigned)((rows * cols + 255) / 256), 256, 0, st>>>(rng_key(seed, tid), out, kind, sh, ones);
+    return cudaGetLastError();
+}
+
+// wire blocks {f16 scale, 32 x int8} -> planes
+__global__ void q8_unpack_wire(const uint8_t* blocks, int8_t* q, __half* s, size_t nb) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nb) return;
+    const uint8_t* src = blocks + b * 34;
+    const uint16_t sc = (uint16_t)src[0] | ((uint16_t)src[1] << 8);
+    s[b] = __ushort_as_half(sc);
+#pragma unroll
+    for (int j = 0; j < 32; j++) q[b * 32 + j] = (int8_t)src[2 + j];
+}
+cudaError_t launch_q8_unpack_wire(const uint8_t* blocks, int8_t* q, __half* s, size_t nb, cudaStream_t st) {
+    q8_unpack_wire<<<(unsigned)((nb + 127) / 128), 128, 0, st>>>(blocks, q, s, nb);
+    return cudaGetLastError();
+}
+
+// w = float(quant) * float(scale): one exact f32 product
+__global__ void q8_dequant(const int8_t* q, const __half* s, float* out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    out[i] = __fmul_rn((float)q[i], __half2float(s[i >> 5]));
+}
+cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size_t n, cudaStream_t st) {
+    q8_dequant<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(q, s, out, n);
+    return cudaGetLastError();
+}
+
+__global__ void to_f32(const void* in, int kind, float* out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    out[i] = kind == WK_BF16 ? bf16_bits_to_f32(((const uint16_t*)in)[i]) : ((const float*)in)[i];
+}
+cudaError_t launch_to_f32(const void* in, int kind, float* out, size_t n, cudaStream_t st) {
+    to_f32<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, kind, out, n);
+    return cudaGetLastError();
+}
+
+}  // namespace lum

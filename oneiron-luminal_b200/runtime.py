@@ -1,0 +1,319 @@
+"""ctypes host for ``liblum_b200.so`` — mirrors the reference's runtime surface.
+
+Reference interface -> method here
+  ``Runtime::initialize(arg)``          src/op.rs:15                 -> ``B200Runtime.initialize(device=…)``
+  ``Runtime::execute(&dyn_map)``        src/op.rs:17                 -> ``execute({'s': n, 'p': prev})``
+  ``Runtime::profile(..)``              src/op.rs:18-23              -> ``profile(trials)``
+  ``CudaRuntime::set_data(id, data)``   luminal_cuda runtime.rs:160  -> ``set_data(token_ids)`` / ``set_weight(..)``
+  ``CudaRuntime::get_f32(id)``          luminal_cuda runtime.rs:168  -> ``get_f32()`` (logits of the last row)
+  ``KVCache::reset``                    examples/llama/src/model.rs:217 -> ``kv_reset()``
+  ``sample``                            examples/llama/src/main.rs:137  -> ``get_token()`` (device-side greedy)
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Iterable, Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_NAME = "liblum_b200.so"
+
+
+class LumError(RuntimeError):
+    """A C-ABI call returned a non-zero status; ``code`` is the LUM_E_* value."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[lum {code}] {msg}")
+        self.code = code
+
+
+DTYPE = {"f32": 0, "f16": 1, "bf16": 2, "int": 3, "bool": 4, "nvfp4": 5, "mxfp4": 6, "q8_0": 7}
+SLOT = {
+    "embed": 0, "attn_norm": 1, "q": 2, "k": 3, "v": 4, "o": 5, "mlp_norm": 6,
+    "gate": 7, "up": 8, "down": 9, "final_norm": 10, "lm_head": 11, "q_norm": 12, "k_norm": 13,
+}
+
+
+class Config(C.Structure):
+    _fields_ = [("device", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32), ("attn_splits", C.c_int32)]
+
+
+class ModelDesc(C.Structure):
+    """Mirror of ``lum_model_desc`` (include/lum_b200.h)."""
+
+    _fields_ = [
+        ("n_layers", C.c_int32), ("hidden", C.c_int32), ("n_q_heads", C.c_int32), ("n_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32), ("max_seq", C.c_int32),
+        ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("rope_style", C.c_int32),
+        ("weight_dtype", C.c_uint32), ("embed_dtype", C.c_uint32), ("kv_dtype", C.c_uint32),
+        ("qk_norm", C.c_int32), ("tied_head", C.c_int32), ("max_new_tokens", C.c_int32),
+        ("tp_size", C.c_int32), ("tp_rank", C.c_int32),
+    ]
+
+    def copy(self, **kw) -> "ModelDesc":
+        d = ModelDesc()
+        C.memmove(C.byref(d), C.byref(self), C.sizeof(ModelDesc))
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+
+def _desc(**kw) -> ModelDesc:
+    d = ModelDesc()
+    base = dict(max_seq=4096, rms_eps=1e-5, rope_style=0, qk_norm=0, tied_head=0, max_new_tokens=4096, tp_size=1, tp_rank=0)
+    base.update(kw)
+    for k, v in base.items():
+        setattr(d, k, v)
+    return d
+
+
+# The workloads this runtime is measured and tested on (shapes only; weights are synthetic).
+CONFIGS: Dict[str, ModelDesc] = {
+    # tiny all-f32 decoder, CPU-runnable by the reference's interpreter
+    "tiny_f32": _desc(n_layers=2, hidden=256, n_q_heads=4, n_kv_heads=2, head_dim=64, ffn=688, vocab=1024, max_seq=64,
+                      rope_theta=10000.0, weight_dtype=DTYPE["f32"], embed_dtype=DTYPE["f32"], kv_dtype=DTYPE["f32"]),
+    # Llama-3-8B shape, Q8_0 linears, bf16 embedding / gains / KV cache
+    "llama3_8b_q8": _desc(n_layers=32, hidden=4096, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=128256,
+                          max_seq=4096, rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"],
+                          kv_dtype=DTYPE["bf16"]),
+    # a 2-layer cut of the same shape with a small vocabulary: same kernels and tile shapes, seconds on a CPU
+    "llama3_8b_q8_2layer": _desc(n_layers=2, hidden=4096, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=4096,
+                                 max_seq=256, rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"],
+                                 kv_dtype=DTYPE["bf16"]),
+    # small Q8_0 model for fast parity runs
+    "small_q8": _desc(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=1536, vocab=2048, max_seq=128,
+                      rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
+}
+
+
+def decode_bytes_per_token(d: ModelDesc, p: float) -> float:
+    """Algorithmic HBM bytes one decode step must move with ``p`` tokens already cached:
+    every linear weight once (Q8_0 = 34/32 B per weight), norm gains, one embedding row, the KV rows read and
+    the one row written.  Activations are excluded."""
+    wb = 34.0 / 32.0 if d.weight_dtype == DTYPE["q8_0"] else 4.0
+    eb = 2.0 if d.embed_dtype == DTYPE["bf16"] else 4.0
+    kb = 2.0 if d.kv_dtype == DTYPE["bf16"] else 4.0
+    qd, kvd = d.n_q_heads * d.head_dim, d.n_kv_heads * d.head_dim
+    per_layer = (qd * d.hidden + 2 * kvd * d.hidden + d.hidden * qd + 3 * d.ffn * d.hidden)
+    head = d.vocab * d.hidden
+    weights = d.n_layers * per_layer * wb + (head * eb if d.tied_head else head * wb)
+    gains = (2 * d.n_layers + 1) * d.hidden * eb
+    kv_row = d.n_layers * 2 * kvd * kb
+    return weights + gains + d.hidden * eb + kv_row * (p + 1)
+
+
+def library_path() -> str:
+    return os.path.join(_HERE, _LIB_NAME)
+
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """Load the built C-ABI library; raises (never falls back) when it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise LumError(-3, f"{path} is not built; run `make -C {os.path.join(_HERE, 'csrc')}` (needs nvcc) — there is no CPU fallback")
+    lib = C.CDLL(path)
+    i32, u32, u64, sz, vp = C.c_int32, C.c_uint32, C.c_uint64, C.c_size_t, C.c_void_p
+    P = C.POINTER
+    sig = {
+        "lum_config_default": (None, [P(Config)]),
+        "lum_create": (i32, [P(Config), P(vp)]),
+        "lum_destroy": (None, [vp]),
+        "lum_last_error": (C.c_char_p, [vp]),
+        "lum_device_info": (i32, [vp, P(i32), P(u64), P(i32)]),
+        "lum_model_init": (i32, [vp, P(ModelDesc)]),
+        "lum_model_set_weight": (i32, [vp, i32, i32, vp, sz, u32]),
+        "lum_model_synth": (i32, [vp, u64]),
+        "lum_model_get_weight_f32": (i32, [vp, i32, i32, sz, sz, P(C.c_float)]),
+        "lum_model_weight_bytes": (i32, [vp, P(u64)]),
+        "lum_kv_reset": (i32, [vp]),
+        "lum_kv_read": (i32, [vp, i32, i32, i32, P(C.c_float)]),
+        "lum_set_dim": (i32, [vp, C.c_char, u64]),
+        "lum_set_tokens": (i32, [vp, P(i32), sz]),
+        "lum_execute": (i32, [vp]),
+        "lum_get_logits": (i32, [vp, P(C.c_float), sz]),
+        "lum_get_token": (i32, [vp, P(i32)]),
+        "lum_decode_greedy": (i32, [vp, i32]),
+        "lum_get_decoded": (i32, [vp, P(i32), sz]),
+        "lum_decode_reset": (i32, [vp]),
+        "lum_synchronize": (i32, [vp]),
+        "lum_profile": (i32, [vp, i32, P(C.c_double), C.c_char_p, sz]),
+        "lum_launches_per_step": (i32, [vp, P(i32)]),
+        "lum_stream": (vp, [vp]),
+        "lum_op_gemv_q8_0": (i32, [vp, vp, i32, i32, vp, vp, i32, vp]),
+        "lum_op_gemv_f32": (i32, [vp, i32, i32, vp, vp, vp]),
+        "lum_op_q8_0_unpack": (i32, [vp, sz, vp, vp, vp]),
+        "lum_op_q8_0_dequant": (i32, [vp, vp, sz, vp, vp]),
+        "lum_op_synth_q8_0": (i32, [u64, u64, sz, vp, vp, vp]),
+        "lum_op_synth_normal": (i32, [u64, u64, u32, sz, i32, vp, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)   # AttributeError here = header and library disagree: fail loudly
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+EXPORTED_SYMBOLS = None  # filled lazily by tests from include/lum_b200.h
+
+
+class B200Runtime:
+    """One runtime = one B200 = one stream (as `CudaRuntime`, crates/luminal_cuda/src/runtime.rs:87-131)."""
+
+    def __init__(self, handle: int, lib: C.CDLL):
+        self._h = C.c_void_p(handle)
+        self._lib = lib
+        self.desc: Optional[ModelDesc] = None
+
+    # ---- lifecycle -------------------------------------------------------------------------------
+    @classmethod
+    def initialize(cls, device: int = 0, use_graph: Optional[bool] = None, use_pdl: Optional[bool] = None,
+                   attn_splits: Optional[int] = None) -> "B200Runtime":
+        lib = load_library()
+        cfg = Config()
+        lib.lum_config_default(C.byref(cfg))
+        cfg.device = device
+        if use_graph is not None:
+            cfg.use_graph = int(use_graph)
+        if use_pdl is not None:
+            cfg.use_pdl = int(use_pdl)
+        if attn_splits is not None:
+            cfg.attn_splits = int(attn_splits)
+        h = C.c_void_p()
+        rc = lib.lum_create(C.byref(cfg), C.byref(h))
+        if rc != 0:
+            raise LumError(rc, (lib.lum_last_error(None) or b"").decode())
+        return cls(h.value, lib)
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.lum_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, rc: int) -> None:
+        if rc != 0:
+            raise LumError(rc, (self._lib.lum_last_error(self._h) or b"").decode())
+
+    def device_info(self):
+        sm, mem, cc = C.c_int32(), C.c_uint64(), C.c_int32()
+        self._ck(self._lib.lum_device_info(self._h, C.byref(sm), C.byref(mem), C.byref(cc)))
+        return {"sm_count": sm.value, "mem_bytes": mem.value, "cc": cc.value}
+
+    # ---- model -----------------------------------------------------------------------------------
+    def load_model(self, desc: ModelDesc) -> None:
+        self._ck(self._lib.lum_model_init(self._h, C.byref(desc)))
+        self.desc = desc.copy()
+
+    def set_weight(self, slot: str, layer: int, data, dtype: str) -> None:
+        """``data``: a C-contiguous numpy array holding f32 values, bf16 bit patterns (uint16) or Q8_0 wire blocks (uint8)."""
+        self._ck(self._lib.lum_model_set_weight(self._h, SLOT[slot], layer, data.ctypes.data_as(C.c_void_p), data.nbytes, DTYPE[dtype]))
+
+    def synth(self, seed: int) -> None:
+        self._ck(self._lib.lum_model_synth(self._h, C.c_uint64(seed)))
+
+    def get_weight_f32(self, slot: str, layer: int, offset: int, n: int):
+        import numpy as np
+        out = np.empty(n, dtype=np.float32)
+        self._ck(self._lib.lum_model_get_weight_f32(self._h, SLOT[slot], layer, offset, n, out.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
+
+    def weight_bytes(self) -> int:
+        b = C.c_uint64()
+        self._ck(self._lib.lum_model_weight_bytes(self._h, C.byref(b)))
+        return b.value
+
+    def kv_reset(self) -> None:
+        self._ck(self._lib.lum_kv_reset(self._h))
+
+    def kv_read(self, layer: int, kind: str, rows: int):
+        import numpy as np
+        d = self.desc
+        out = np.empty((rows, (d.n_kv_heads // max(1, d.tp_size)) * d.head_dim), dtype=np.float32)
+        self._ck(self._lib.lum_kv_read(self._h, layer, 0 if kind == "k" else 1, rows, out.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
+
+    # ---- the reference's decode-loop surface -------------------------------------------------------
+    def set_dim(self, dim: str, value: int) -> None:
+        self._ck(self._lib.lum_set_dim(self._h, dim.encode()[0:1], value))
+
+    def set_data(self, token_ids: Sequence[int]) -> None:
+        arr = (C.c_int32 * len(token_ids))(*[int(t) for t in token_ids])
+        self._ck(self._lib.lum_set_tokens(self._h, arr, len(token_ids)))
+
+    def execute(self, dyn_map: Optional[Dict[str, int]] = None) -> None:
+        for k, v in (dyn_map or {}).items():
+            self.set_dim(k, v)
+        self._ck(self._lib.lum_execute(self._h))
+
+    def get_f32(self):
+        """Logits of the last executed row (``get_f32(logits.id)`` then taking the last row in the reference)."""
+        import numpy as np
+        n = self.desc.vocab // max(1, self.desc.tp_size)
+        out = np.empty(n, dtype=np.float32)
+        self._ck(self._lib.lum_get_logits(self._h, out.ctypes.data_as(C.POINTER(C.c_float)), n))
+        return out
+
+    def get_token(self) -> int:
+        t = C.c_int32()
+        self._ck(self._lib.lum_get_token(self._h, C.byref(t)))
+        return t.value
+
+    def decode_greedy(self, n_steps: int) -> None:
+        self._ck(self._lib.lum_decode_greedy(self._h, n_steps))
+
+    def decode_reset(self) -> None:
+        self._ck(self._lib.lum_decode_reset(self._h))
+
+    def get_decoded(self, n: int):
+        import numpy as np
+        out = np.empty(n, dtype=np.int32)
+        self._ck(self._lib.lum_get_decoded(self._h, out.ctypes.data_as(C.POINTER(C.c_int32)), n))
+        return out
+
+    def synchronize(self) -> None:
+        self._ck(self._lib.lum_synchronize(self._h))
+
+    def profile(self, trials: int = 16):
+        us = C.c_double()
+        buf = C.create_string_buffer(128)
+        self._ck(self._lib.lum_profile(self._h, trials, C.byref(us), buf, 128))
+        return us.value, buf.value.decode()
+
+    def launches_per_step(self) -> int:
+        n = C.c_int32()
+        self._ck(self._lib.lum_launches_per_step(self._h, C.byref(n)))
+        return n.value
+
+    def stream(self) -> int:
+        return self._lib.lum_stream(self._h) or 0
+
+    # convenience: the reference's whole loop (examples/llama/src/main.rs:82-118), greedy
+    def generate(self, prompt: Iterable[int], n_new: int):
+        prompt = list(prompt)
+        self.kv_reset()
+        self.decode_reset()
+        self.set_data(prompt)
+        self.execute({"s": len(prompt), "p": 0})
+        first = self.get_token()
+        if n_new <= 1:
+            return [first][:n_new]
+        self.decode_greedy(n_new - 1)
+        rest = self.get_decoded(n_new - 1)
+        return [first] + [int(t) for t in rest]

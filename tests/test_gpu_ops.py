@@ -1,0 +1,216 @@
+"""GPU parity tests of the stand-alone operators, through the C ABI, against the CPU oracle.
+
+Shapes follow the reference's quantised known-answer tests (crates/luminal_cuda/src/tests/mxfp4.rs:124-264,
+nvfp4.rs:154-311): a minimal all-ones case, exact-integer weights, random weights, the M = 1 decode path,
+and sizes that are not a multiple of the kernel's tile.
+Tolerance for f32 dot products: the reference's rtol = eps * sqrt(k), atol = 5 * eps
+(crates/luminal_cuda/src/tests/op_functional_tests.rs:53-120), relative to the row's |w|.|x| magnitude.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from oracle import load, _fp  # noqa: E402
+
+EPS = np.finfo(np.float32).eps
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.cuda.set_device(0)
+    return torch
+
+
+@pytest.fixture(scope="module")
+def lib(pkg):
+    return pkg.load_library()
+
+
+def ck(lib, rc):
+    assert rc == 0, (lib.lum_last_error(None) or b"").decode()
+
+
+def make_wire(rng, n, k, mode):
+    """Q8_0 wire blocks [n*k/32, 34] uint8 for the three KAT flavours."""
+    nb = n * k // 32
+    blocks = np.zeros((nb, 34), dtype=np.uint8)
+    if mode == "ones":
+        scale = np.full(nb, 1.0, dtype=np.float16)
+        q = np.ones((nb, 32), dtype=np.int8)
+    elif mode == "integers":
+        scale = rng.choice(np.array([0.5, 1.0, 2.0, 0.25], dtype=np.float16), nb)
+        q = rng.integers(-8, 9, (nb, 32)).astype(np.int8)
+    else:
+        scale = (np.abs(rng.normal(0, 0.02, nb)) / 127).astype(np.float16)
+        q = rng.integers(-127, 128, (nb, 32)).astype(np.int8)
+    blocks[:, :2] = scale.view(np.uint8).reshape(nb, 2)
+    blocks[:, 2:] = q.view(np.uint8)
+    return blocks
+
+
+def upload_q8(torch, lib, blocks, n, k):
+    dev_blocks = torch.from_numpy(blocks.reshape(-1)).cuda()
+    q = torch.empty(n * k, dtype=torch.int8, device="cuda")
+    s = torch.empty(n * k // 32, dtype=torch.float16, device="cuda")
+    ck(lib, lib.lum_op_q8_0_unpack(dev_blocks.data_ptr(), n * k // 32, q.data_ptr(), s.data_ptr(), None))
+    torch.cuda.synchronize()
+    return q, s
+
+
+def oracle_matvec_q8(blocks, n, k, x):
+    y = np.empty(n, dtype=np.float32)
+    load().orc_matvec_q8_0(blocks.ctypes.data_as(C.c_void_p), n, k, _fp(x), _fp(y))
+    return y
+
+
+def check_close(got, want, wabs_dot_xabs, k):
+    tol = EPS * np.sqrt(k) * wabs_dot_xabs + 5 * EPS
+    bad = np.abs(got - want) > tol
+    assert not bad.any(), f"{bad.sum()} rows off; worst {np.max(np.abs(got - want) / tol):.2f}x tolerance"
+
+
+def test_q8_unpack_and_dequant_bit_exact(torch_cuda, lib):
+    torch = torch_cuda
+    rng = np.random.default_rng(1)
+    n, k = 64, 512
+    blocks = make_wire(rng, n, k, "random")
+    q, s = upload_q8(torch, lib, blocks, n, k)
+    assert (q.cpu().numpy().reshape(-1, 32) == blocks[:, 2:].view(np.int8)).all()
+    assert (s.cpu().numpy().view(np.uint16) == blocks[:, :2].copy().view(np.uint16).ravel()).all()
+    out = torch.empty(n * k, dtype=torch.float32, device="cuda")
+    ck(lib, lib.lum_op_q8_0_dequant(q.data_ptr(), s.data_ptr(), n * k, out.data_ptr(), None))
+    want = np.empty(n * k, dtype=np.float32)
+    load().orc_q8_0_dequant(blocks.ctypes.data_as(C.c_void_p), n * k // 32, _fp(want))
+    assert (out.cpu().numpy().view(np.uint32) == want.view(np.uint32)).all()
+
+
+def test_synthetic_generator_bit_exact(torch_cuda, lib):
+    """Both sides regenerate tensors from (seed, id, index); dequantised weights must agree bit for bit."""
+    torch = torch_cuda
+    orc = load()
+    seed, tid, n = 77, 21, 1 << 20
+    q = torch.empty(n, dtype=torch.int8, device="cuda")
+    s = torch.empty(n // 32, dtype=torch.float16, device="cuda")
+    ck(lib, lib.lum_op_synth_q8_0(seed, tid, n, q.data_ptr(), s.data_ptr(), None))
+    out = torch.empty(n, dtype=torch.float32, device="cuda")
+    ck(lib, lib.lum_op_q8_0_dequant(q.data_ptr(), s.data_ptr(), n, out.data_ptr(), None))
+    blocks = np.empty(n // 32 * 34, dtype=np.uint8)
+    assert orc.orc_synth(seed, tid, 7, n, 0, blocks.ctypes.data_as(C.c_void_p)) == 0
+    want = np.empty(n, dtype=np.float32)
+    orc.orc_q8_0_dequant(blocks.ctypes.data_as(C.c_void_p), n // 32, _fp(want))
+    got = out.cpu().numpy()
+    assert (got.view(np.uint32) == want.view(np.uint32)).all()
+    qs = q.cpu().numpy()
+    assert qs.min() == -127 and qs.max() == 127 and abs(float(qs.mean())) < 0.5
+    for dt, npdt in ((0, np.float32), (2, np.uint16)):
+        m = 1 << 16
+        buf = torch.empty(m, dtype=torch.float32 if dt == 0 else torch.bfloat16, device="cuda")
+        ck(lib, lib.lum_op_synth_normal(seed, tid + 1, dt, m, 0, buf.data_ptr(), None))
+        ref = np.empty(m, dtype=npdt)
+        assert orc.orc_synth(seed, tid + 1, dt, m, 0, ref.ctypes.data_as(C.c_void_p)) == 0
+        g = buf.cpu().view(torch.int16 if dt == 2 else torch.int32).numpy()
+        assert (g.view(npdt if dt == 2 else np.uint32) == (ref if dt == 2 else ref.view(np.uint32))).all()
+
+
+KAT = [
+    # (n, k, mode, path)  path: 0 = let the library choose (streaming kernel where it applies), 1 = direct kernel
+    (1, 32, "ones", 0),            # minimal: one block of ones against ones -> 32.0
+    (4, 512, "ones", 0),
+    (8, 4096, "integers", 0),      # exact-integer weights and activations: exact result
+    (8, 4096, "integers", 1),
+    (64, 4096, "random", 0),
+    (64, 4096, "random", 1),
+    (148 * 4 + 12, 4096, "random", 0),   # rows not a multiple of (CTAs x tile)
+    (24, 14336, "random", 0),      # down-projection K: seven 2048-wide chunks per row
+    (24, 14336, "random", 1),
+    (40, 1024, "random", 0),
+    (36, 2560, "random", 0),       # K = 5 x 512
+    (7, 96, "random", 0),          # K below any tile: direct kernel
+    (6152, 4096, "random", 0),     # q,k,v-sized: more units than CTAs, uneven split
+]
+
+
+@pytest.mark.parametrize("n,k,mode,path", KAT)
+def test_gemv_q8_known_answers(torch_cuda, lib, n, k, mode, path):
+    torch = torch_cuda
+    rng = np.random.default_rng(n * 131 + k)
+    blocks = make_wire(rng, n, k, mode)
+    if mode == "ones":
+        x = np.ones(k, dtype=np.float32)
+    elif mode == "integers":
+        x = rng.integers(-4, 5, k).astype(np.float32)
+    else:
+        x = rng.normal(0, 1, k).astype(np.float32)
+    q, s = upload_q8(torch, lib, blocks, n, k)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+    ck(lib, lib.lum_op_gemv_q8_0(q.data_ptr(), s.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), path, None))
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    want = oracle_matvec_q8(blocks, n, k, x)
+    if mode == "ones":
+        assert (got == float(k)).all() and (want == float(k)).all()
+    elif mode == "integers":
+        assert (got == want).all()           # every partial sum is a small integer multiple of 1/4: exact in any order
+    else:
+        wf = np.empty(n * k, dtype=np.float32)
+        load().orc_q8_0_dequant(blocks.ctypes.data_as(C.c_void_p), n * k // 32, _fp(wf))
+        mag = np.abs(wf.reshape(n, k)).astype(np.float64) @ np.abs(x).astype(np.float64)
+        check_close(got.astype(np.float64), want.astype(np.float64), mag, k)
+
+
+def test_gemv_q8_streaming_equals_direct_on_lm_head_rows(torch_cuda, lib):
+    """Vocabulary-sized GEMV (N = 128256, K = 4096) on generated weights: the two kernels agree, the result is
+    linear in x, and sampled rows match the oracle."""
+    torch = torch_cuda
+    orc = load()
+    n, k, seed, tid = 128256, 4096, 5, 3
+    q = torch.empty(n * k, dtype=torch.int8, device="cuda")
+    s = torch.empty(n * k // 32, dtype=torch.float16, device="cuda")
+    ck(lib, lib.lum_op_synth_q8_0(seed, tid, n * k, q.data_ptr(), s.data_ptr(), None))
+    rng = np.random.default_rng(0)
+    x1 = rng.normal(0, 1, k).astype(np.float32)
+    x2 = rng.normal(0, 1, k).astype(np.float32)
+    ys = []
+    for xv, path in ((x1, 0), (x1, 1), (x2, 0), (x1 + x2, 0)):
+        xd = torch.from_numpy(xv).cuda()
+        y = torch.empty(n, dtype=torch.float32, device="cuda")
+        ck(lib, lib.lum_op_gemv_q8_0(q.data_ptr(), s.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), path, None))
+        torch.cuda.synchronize()
+        ys.append(y.cpu().numpy().astype(np.float64))
+    scale = np.abs(ys[0]).max()
+    assert np.max(np.abs(ys[0] - ys[1])) <= 1e-5 * scale          # streaming vs direct
+    assert np.max(np.abs(ys[0] + ys[2] - ys[3])) <= 1e-4 * scale  # linearity
+    rows = rng.choice(n, 64, replace=False)
+    for r in rows:
+        blk = np.empty(k // 32 * 34, dtype=np.uint8)
+        assert orc.orc_synth_range(seed, tid, 7, int(r) * k, k, blk.ctypes.data_as(C.c_void_p)) == 0
+        want = oracle_matvec_q8(blk, 1, k, x1)[0]
+        assert abs(ys[0][r] - want) <= 1e-5 * scale
+
+
+@pytest.mark.parametrize("n,k", [(1, 1), (5, 3), (33, 257), (1024, 256), (688, 256), (256, 688)])
+def test_gemv_f32(torch_cuda, lib, n, k):
+    torch = torch_cuda
+    rng = np.random.default_rng(n + 7 * k)
+    w = rng.uniform(-0.5, 0.5, (n, k)).astype(np.float32)
+    x = rng.uniform(-0.5, 0.5, k).astype(np.float32)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    y = torch.empty(n, dtype=torch.float32, device="cuda")
+    ck(lib, lib.lum_op_gemv_f32(wd.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), None))
+    torch.cuda.synchronize()
+    want = np.empty(n, dtype=np.float32)
+    load().orc_matvec_f32(_fp(w), n, k, _fp(x), _fp(want))
+    mag = np.abs(w).astype(np.float64) @ np.abs(x).astype(np.float64)
+    check_close(y.cpu().numpy().astype(np.float64), want.astype(np.float64), mag, k)
+
+
+def test_bad_arguments_return_errors(lib):
+    assert lib.lum_op_gemv_q8_0(None, None, 4, 32, None, None, 0, None) < 0
+    assert b"bad arguments" in lib.lum_last_error(None)
+    assert lib.lum_op_q8_0_dequant(None, None, 31, None, None) < 0
