@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark: Q8_0 Llama-3-8B-shape model, batch 1, greedy.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (seeded synthetic weights of the named shape; there are no checkpoints here): 512-token prompt, then
+K timed "steps" of TOKENS_PER_STEP greedy tokens each (default 4 x 64 = the 256 decoded tokens of the named
+configuration).  `value` is decode tokens/s with everything resident in HBM, timed with CUDA events on the
+runtime's stream; `e2e` is the same loop driven token by token through the public API with the token id going
+host -> device and the sampled token coming device -> host every token.  Weights (8 GB) are far larger than L2
+(126 MB), so every step streams them from HBM.
+
+`--impl reference` times the CPU restatement of the reference's interpreter semantics (oracle/, the reference
+itself is Rust and cannot be built here) on the host cores, on a bounded sample of the same workload.
+Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOKENS_PER_STEP = 64
+PROMPT_LEN = 512
+SEED = 20240607
+METRIC = "q8_llama3_8b_bs1_decode_tokens_per_s"
+UNIT = "tokens/s"
+WORKLOAD = "llama3_8b_q8"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.05)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ---------------------------------------------------------------------------------------------- CPU arm
+
+def cpu_port_tokens_per_s(pkg, steps: int, warmup: int):
+    """Times the oracle (a C++ restatement of the reference's CPU interpreter semantics, all host threads) on a
+    bounded sample: 2 of the 32 layers plus the full lm_head of the same shapes, one token at a short context,
+    and scales to the whole model: t_token = 16 x t(2 layers) + t(head)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import numpy as np
+    from oracle import OracleModel, load
+    full = pkg.CONFIGS[WORKLOAD]
+    cut_layers = 2
+    d_body = full.copy(n_layers=cut_layers, vocab=32, max_seq=64)       # layers only (tiny head)
+    d_head = full.copy(n_layers=0 + 1, vocab=full.vocab, max_seq=8, ffn=32, n_q_heads=8, n_kv_heads=8)  # head dominates
+    lib = load()
+    threads = lib.orc_threads()
+    body = OracleModel(d_body)
+    body.synth(SEED)
+    head = OracleModel(d_head)
+    head.synth(SEED)
+    toks = [1, 2, 3, 4, 5, 6, 7, 8]
+    body.forward(toks, 0)
+    head.forward([1], 0)
+
+    def one(m, p):
+        t0 = time.perf_counter()
+        m.forward([3], p)
+        return time.perf_counter() - t0
+
+    # the head model still runs one thin layer; measure that layer alone and subtract it
+    d_thin = d_head.copy(vocab=32)
+    thin = OracleModel(d_thin)
+    thin.synth(SEED)
+    thin.forward([1], 0)
+    for _ in range(warmup):
+        one(body, 8); one(head, 1); one(thin, 1)
+    t_body = min(one(body, 8 + i) for i in range(max(1, steps)))
+    t_head = min(one(head, 1 + i) for i in range(max(1, steps))) - min(one(thin, 1 + i) for i in range(max(1, steps)))
+    t_token = t_body * (full.n_layers / cut_layers) + max(t_head, 0.0)
+    sample = (f"{cut_layers} of {full.n_layers} layers (hidden {full.hidden}, ffn {full.ffn}, Q8_0) at context 8 plus the full "
+              f"{full.vocab}-row lm_head, best of {max(1, steps)}; scaled x{full.n_layers // cut_layers} + head")
+    return 1.0 / t_token, threads, sample, np.__version__
+
+
+def run_reference_arm(args, pkg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    v, threads, sample, _ = cpu_port_tokens_per_s(pkg, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 * TOKENS_PER_STEP / v, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch": 1, "prompt_len": PROMPT_LEN, "tokens_per_step": TOKENS_PER_STEP,
+                   "note": "CPU restatement of the reference's NativeRuntime semantics; the reference (Rust) cannot be built here"},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------- GPU arm
+
+def kernel_roofline(pkg, torch, peaks, peak_kind):
+    """The dominant kernel (q8_gemv_stream) timed alone on the gate+up-sized shape: N = 28672 rows, K = 4096."""
+    lib = pkg.load_library()
+    n, k, nbuf = 28672, 4096, 8                       # 8 x 125 MB of distinct weights: far larger than L2
+    q = [torch.empty(n * k, dtype=torch.int8, device="cuda") for _ in range(nbuf)]
+    s = [torch.empty(n * k // 32, dtype=torch.float16, device="cuda") for _ in range(nbuf)]
+    for i in range(nbuf):
+        assert lib.lum_op_synth_q8_0(SEED, 900 + i, n * k, q[i].data_ptr(), s[i].data_ptr(), None) == 0
+    x = torch.randn(k, dtype=torch.float32, device="cuda")
+    y = torch.empty(n, dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    for i in range(4):
+        assert lib.lum_op_gemv_q8_0(q[i % nbuf].data_ptr(), s[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st) == 0
+    launches = 40
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(launches):
+        lib.lum_op_gemv_q8_0(q[i % nbuf].data_ptr(), s[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / launches
+    bytes_per_launch = n * k * 34 // 32 + k * 4 + n * 4
+    achieved = bytes_per_launch / (ms * 1e-3) / 1e9
+    del q, s
+    torch.cuda.empty_cache()
+    return {"bound": "hbm", "kernel": "q8_gemv_stream", "shape": f"N={n} K={k} (gate+up sized), alone, back to back",
+            "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+            "peak_kind": f"of {peak_kind} (burst copy)", "us_per_launch": ms * 1000.0, "bytes_per_launch": bytes_per_launch,
+            "traffic": None}, launches + 4
+
+
+def run_ours(args, pkg):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this runtime has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks, peak_kind = measured_peaks()
+
+    desc = pkg.CONFIGS[WORKLOAD]
+    rt = pkg.B200Runtime.initialize(device=local)
+    rt.load_model(desc)
+    rt.synth(SEED)
+    # prompt: 512 seeded ids (same generator as the oracle's: tensor id 2^20, uniform over the vocabulary)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    prompt = _prompt_tokens(desc.vocab, PROMPT_LEN)
+    rt.kv_reset()
+    rt.decode_reset()
+    rt.set_data(prompt)
+    rt.execute({"s": len(prompt), "p": 0})
+    rt.synchronize()
+
+    ext = torch.cuda.ExternalStream(rt.stream(), device=torch.device("cuda", local))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        rt.decode_greedy(TOKENS_PER_STEP)
+    rt.synchronize()
+    p_start = PROMPT_LEN + args.warmup * TOKENS_PER_STEP
+
+    sampler = ClockSampler(physical_gpu_index(local))
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ext)
+    for _ in range(args.steps):
+        rt.decode_greedy(TOKENS_PER_STEP)
+    e1.record(ext)
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    n_tok = args.steps * TOKENS_PER_STEP
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tok_s_rank = n_tok / (ms * 1e-3)
+    value = tok_s_rank * world            # independent replicas: every rank decodes its own sequence
+    p_mean = p_start + n_tok / 2.0
+    bytes_tok = pkg.decode_bytes_per_token(desc, p_mean)
+
+    # end-to-end through the public API, one token at a time, host <-> device every token
+    tok = rt.get_token()
+    p = p_start + n_tok
+    e2e_tokens = min(n_tok, 128)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_tokens):
+        rt.set_data([tok])
+        rt.execute({"s": 1, "p": p})
+        tok = rt.get_token()
+        p += 1
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = e2e_tokens / e2e_s * world
+
+    launches_step = rt.launches_per_step()
+    line = None
+    if rank == 0:
+        roof, extra_launches = kernel_roofline(pkg, torch, peaks, peak_kind)
+        step_ach = bytes_tok * tok_s_rank / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 accumulate over Q8_0 (int8 x f16-scale) weights", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch": 1, "prompt_len": PROMPT_LEN, "tokens_per_step": TOKENS_PER_STEP,
+                       "context_at_start": p_start, "l2": "weights 8.0 GB >> 126 MB L2; every token re-streams them",
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)",
+                       "seed": SEED},
+            "roofline": roof,
+            "step_roofline": {"bound": "hbm", "what": "whole decode step (one graph replay, all kernels)", "bytes_per_token": bytes_tok,
+                              "achieved": step_ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": step_ach / peaks["hbm_gbs"],
+                              "frac_of_8tbs_nominal": step_ach / 8000.0, "peak_kind": f"of {peak_kind}"},
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": 8 * TOKENS_PER_STEP, "d2h_bytes_per_step": 4 * TOKENS_PER_STEP,
+                    "note": "per token: token id + position host->device, sampled token device->host, synchronous"},
+            "gpu_launches": launches_step * n_tok,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            try:
+                v, threads, sample, _ = cpu_port_tokens_per_s(pkg, 2, 1)
+                line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+            except Exception as exc:  # the GPU number stands on its own
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+    rt.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line))
+
+
+def _prompt_tokens(vocab: int, n: int):
+    """The seeded prompt, generated without the oracle: SplitMix64 counter generator, tensor id 2^20."""
+    mask = (1 << 64) - 1
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        return z ^ (z >> 31)
+
+    g = 0x9E3779B97F4A7C15
+    key = mix((SEED + g * ((1 << 20) + 1)) & mask)
+    return [((mix((key + g * (2 * i)) & mask) >> 32) * vocab) >> 32 for i in range(n)]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if args.impl == "reference":
+        run_reference_arm(args, pkg)
+    else:
+        run_ours(args, pkg)
+
+
+if __name__ == "__main__":
+    main()
