@@ -326,15 +326,27 @@ def _prompt_tokens(vocab: int, n: int):
 
 
 def main():
+    global PROMPT_LEN, TOKENS_PER_STEP
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
+    ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
+    ap.add_argument("--only", default="all", choices=["all", "kernel"], help="kernel: time only the dominant kernel alone (small, for ncu captures)")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
+    PROMPT_LEN, TOKENS_PER_STEP = args.prompt_len, args.tokens_per_step
+    if args.only == "kernel":
+        import torch
+        torch.cuda.set_device(0)
+        peaks, kind = measured_peaks()
+        roof, _ = kernel_roofline(pkg, torch, peaks, kind)
+        print(json.dumps({"roofline": roof}))
+        return
     if args.impl == "reference":
         run_reference_arm(args, pkg)
     else:

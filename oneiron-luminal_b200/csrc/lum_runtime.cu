@@ -183,9 +183,10 @@ __global__ void set_state_kernel(DecodeState* st, int pos, int tok, int log, int
 
 int check_status(lum_rt* rt) {
     uint32_t st = 0;
-    CU(rt, cudaMemcpy(&st, rt->status, sizeof st, cudaMemcpyDeviceToHost));
+    CU(rt, cudaMemcpyAsync(&st, rt->status, sizeof st, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
     if (st) {
-        cudaMemset(rt->status, 0, sizeof st);
+        cudaMemsetAsync(rt->status, 0, sizeof st, rt->stream);
         return fail(rt, LUM_E_DEVICE, "device status 0x%x (%s%s%s%s%s)", st, (st & LUM_ST_WAIT_FULL) ? "stage wait timed out; " : "",
                     (st & LUM_ST_WAIT_EMPTY) ? "producer wait timed out; " : "", (st & LUM_ST_WAIT_DRAIN) ? "drain wait timed out; " : "",
                     (st & LUM_ST_BAD_TOKEN) ? "token id out of range; " : "", (st & LUM_ST_BAD_POS) ? "position out of range; " : "");
@@ -468,13 +469,16 @@ int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void
         void* tmp = nullptr;
         cudaError_t e = cudaMalloc(&tmp, t->rows * row_bytes);
         if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "set_weight: staging buffer: %s", cudaGetErrorString(e));
-        e = cudaMemcpy2D(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice);
+        // copies go on the runtime's own (non-blocking) stream: a legacy-stream copy from pageable memory may return
+        // before its DMA has landed and would not be ordered against kernels on this stream
+        e = cudaMemcpy2DAsync(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice, rt->stream);
         if (e == cudaSuccess) e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)t->w, t->s, t->rows * t->cols / 32, rt->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
         cudaFree(tmp);
         if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "set_weight: %s", cudaGetErrorString(e));
     } else {
-        CU(rt, cudaMemcpy2D(t->w, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice));
+        CU(rt, cudaMemcpy2DAsync(t->w, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice, rt->stream));
+        CU(rt, cudaStreamSynchronize(rt->stream));
     }
     return 0;
 }
@@ -663,7 +667,8 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     CU(rt, cudaSetDevice(rt->cfg.device));
     DecodeState saved;
     CU(rt, cudaStreamSynchronize(rt->stream));
-    CU(rt, cudaMemcpy(&saved, rt->state, sizeof saved, cudaMemcpyDeviceToHost));
+    CU(rt, cudaMemcpyAsync(&saved, rt->state, sizeof saved, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
     if (saved.pos + trials + 1 > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "profile: not enough cache capacity left for %d trial steps", trials);
     cudaEvent_t e0, e1;
     CU(rt, cudaEventCreate(&e0));
@@ -680,7 +685,8 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     saved.log = 0;
-    cudaMemcpy(rt->state, &saved, sizeof saved, cudaMemcpyHostToDevice);
+    cudaMemcpyAsync(rt->state, &saved, sizeof saved, cudaMemcpyHostToDevice, rt->stream);
+    cudaStreamSynchronize(rt->stream);
     if (r) return r;
     if (int s = check_status(rt)) return s;
     const double us = (double)ms * 1000.0 / trials;

@@ -1,0 +1,92 @@
+// C++ host over the C ABI of include/lum_b200.h, shaped like the reference's runtime interface so
+// that code written against `luminal::op::Runtime` (src/op.rs:10-30) and `CudaRuntime`'s inherent
+// methods (crates/luminal_cuda/src/runtime.rs:133-236) reads the same:
+//
+//   auto rt = lum::B200Runtime::initialize(0);         // Runtime::initialize(arg)
+//   rt.load_model(desc);                               // Runtime::load_llir(&graph) for a decoder plan
+//   rt.set_data(ids);                                  // set_data(input.id, ids)
+//   rt.execute({{'s', n}, {'p', prev}});               // Runtime::execute(&dyn_map)
+//   std::vector<float> logits = rt.get_f32();          // get_f32(logits.id), last row
+//   auto [usec, text] = rt.profile(16);                // Runtime::profile -> (metric, display)
+//
+// Errors surface as lum::Error (the reference panics; `Graph::search` catches panics around a
+// failing candidate, src/graph.rs:419-447 — an exception plays that role here).  Header-only.
+#pragma once
+#include <map>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/lum_b200.h"
+
+namespace lum {
+
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string& m) : std::runtime_error("[lum " + std::to_string(c) + "] " + m), code(c) {}
+};
+
+class B200Runtime {
+public:
+    using CompileArg = int;          // device ordinal
+    using ProfileMetric = double;    // microseconds per decode step
+
+    static B200Runtime initialize(CompileArg device) {
+        lum_config cfg;
+        lum_config_default(&cfg);
+        cfg.device = device;
+        return B200Runtime(cfg);
+    }
+    explicit B200Runtime(const lum_config& cfg) {
+        if (int rc = lum_create(&cfg, &h_)) throw Error(rc, lum_last_error(nullptr));
+    }
+    B200Runtime(B200Runtime&& o) noexcept : h_(o.h_), desc_(o.desc_) { o.h_ = nullptr; }
+    B200Runtime& operator=(B200Runtime&& o) noexcept {
+        if (this != &o) { if (h_) lum_destroy(h_); h_ = o.h_; desc_ = o.desc_; o.h_ = nullptr; }
+        return *this;
+    }
+    B200Runtime(const B200Runtime&) = delete;
+    B200Runtime& operator=(const B200Runtime&) = delete;
+    ~B200Runtime() { if (h_) lum_destroy(h_); }
+
+    void load_model(const lum_model_desc& d) { ck(lum_model_init(h_, &d)); desc_ = d; }
+    void set_weight(lum_slot slot, int layer, const void* host, size_t bytes, lum_dtype dt) { ck(lum_model_set_weight(h_, slot, layer, host, bytes, dt)); }
+    void synth(uint64_t seed) { ck(lum_model_synth(h_, seed)); }
+    void kv_reset() { ck(lum_kv_reset(h_)); }
+
+    void set_dim(char dim, uint64_t v) { ck(lum_set_dim(h_, dim, v)); }
+    void set_data(const std::vector<int32_t>& ids) { ck(lum_set_tokens(h_, ids.data(), ids.size())); }
+    void execute(const std::map<char, size_t>& dyn_map) {
+        for (const auto& kv : dyn_map) set_dim(kv.first, kv.second);
+        ck(lum_execute(h_));
+    }
+    std::vector<float> get_f32() {
+        std::vector<float> out((size_t)(desc_.vocab / (desc_.tp_size > 0 ? desc_.tp_size : 1)));
+        ck(lum_get_logits(h_, out.data(), out.size()));
+        return out;
+    }
+    int32_t get_token() { int32_t t = 0; ck(lum_get_token(h_, &t)); return t; }
+    void decode_greedy(int n) { ck(lum_decode_greedy(h_, n)); }
+    std::vector<int32_t> get_decoded(size_t n) { std::vector<int32_t> v(n); ck(lum_get_decoded(h_, v.data(), n)); return v; }
+    void decode_reset() { ck(lum_decode_reset(h_)); }
+    void synchronize() { ck(lum_synchronize(h_)); }
+    std::pair<ProfileMetric, std::string> profile(int trials) {
+        double us = 0; char buf[128] = {0};
+        ck(lum_profile(h_, trials, &us, buf, sizeof buf));
+        return {us, buf};
+    }
+    // allocate_dummy_input / clear_intermediate_buffers (src/op.rs:24-29) have nothing to do here:
+    // the plan owns fixed activation buffers and no intermediate is ever re-zeroed.
+    void allocate_dummy_input(size_t, size_t) {}
+    void clear_intermediate_buffers() {}
+
+    lum_rt* raw() const { return h_; }
+
+private:
+    void ck(int rc) { if (rc) throw Error(rc, lum_last_error(h_)); }
+    lum_rt* h_ = nullptr;
+    lum_model_desc desc_{};
+};
+
+}  // namespace lum
