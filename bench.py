@@ -166,28 +166,27 @@ def kernel_roofline(pkg, torch, peaks, peak_kind):
     """The dominant kernel (q8_gemv_stream) timed alone on the gate+up-sized shape: N = 28672 rows, K = 4096."""
     lib = pkg.load_library()
     n, k, nbuf = 28672, 4096, 8                       # 8 x 125 MB of distinct weights: far larger than L2
-    q = [torch.empty(n * k, dtype=torch.int8, device="cuda") for _ in range(nbuf)]
-    s = [torch.empty(n * k // 32, dtype=torch.float16, device="cuda") for _ in range(nbuf)]
+    w = [torch.empty(lib.lum_q8_0_packed_bytes(n, k), dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
     for i in range(nbuf):
-        assert lib.lum_op_synth_q8_0(SEED, 900 + i, n * k, q[i].data_ptr(), s[i].data_ptr(), None) == 0
+        assert lib.lum_op_synth_q8_0_packed(SEED, 900 + i, n, k, w[i].data_ptr(), None) == 0
     x = torch.randn(k, dtype=torch.float32, device="cuda")
     y = torch.empty(n, dtype=torch.float32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
     torch.cuda.synchronize()
     for i in range(4):
-        assert lib.lum_op_gemv_q8_0(q[i % nbuf].data_ptr(), s[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st) == 0
+        assert lib.lum_op_gemv_q8_0_packed(w[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st) == 0
     launches = 40
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
     for i in range(launches):
-        lib.lum_op_gemv_q8_0(q[i % nbuf].data_ptr(), s[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st)
+        lib.lum_op_gemv_q8_0_packed(w[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / launches
     bytes_per_launch = n * k * 34 // 32 + k * 4 + n * 4
     achieved = bytes_per_launch / (ms * 1e-3) / 1e9
-    del q, s
+    del w
     torch.cuda.empty_cache()
     return {"bound": "hbm", "kernel": "q8_gemv_stream", "shape": f"N={n} K={k} (gate+up sized), alone, back to back",
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],

@@ -151,10 +151,21 @@ void* lum_stream(lum_rt* rt);
  * crates/luminal_cuda/src/block/ops.rs as single calls, for operator-level tests and for hosts
  * that schedule ops themselves.  `stream` is a cudaStream_t (NULL = default stream).
  */
-/* y[N] = W[N,K] x[K]; W in Q8_0 device planes (quants int8 [N,K], scales f16 [N,K/32]).
- * `TileMatmulFullSplit` M==1 path (ops.rs:1588-1651) for a Q8_0 right-hand side. */
+/* y[N] = W[N,K] x[K]; W in Q8_0 device planes (quants int8 [N,K], scales f16 [N,K/32]); any K % 32 == 0.
+ * `TileMatmulFullSplit` M==1 path (ops.rs:1588-1651) for a Q8_0 right-hand side.  Plane-layout weights
+ * always run the plain-load kernel; `force_direct` is accepted for symmetry with the packed entry. */
 int32_t lum_op_gemv_q8_0(const int8_t* quants_dev, const void* scales_dev, int32_t n, int32_t k,
                          const float* x_dev, float* y_dev, int32_t force_direct, void* stream);
+/* The streaming layout: stage-units of R rows x KC columns (R * KC = 16384), each 16 KiB of quants followed
+ * by 1 KiB of scales, ordered by row group then K-chunk (documented in csrc/lum_synth.cu).  Same 34/32 bytes
+ * per weight.  lum_q8_0_packed_bytes returns 0 when [n, k] cannot be packed (needs K % 512 == 0,
+ * K <= 16384, N % (16384 / KC) == 0). */
+size_t lum_q8_0_packed_bytes(int32_t n, int32_t k);
+int32_t lum_op_q8_0_pack(const int8_t* quants_dev, const void* scales_dev, int32_t n, int32_t k, void* packed_dev, void* stream);
+/* Same product on packed weights: the bulk-copy streaming kernel (force_direct = 1: the plain-load kernel). */
+int32_t lum_op_gemv_q8_0_packed(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev,
+                                int32_t force_direct, void* stream);
+int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tensor_id, int32_t n, int32_t k, void* packed_dev, void* stream);
 int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev, void* stream);
 /* Q8_0 wire blocks (host layout, on device) -> planes; planes -> f32. */
 int32_t lum_op_q8_0_unpack(const uint8_t* blocks_dev, size_t n_blocks, int8_t* quants_dev, void* scales_dev, void* stream);

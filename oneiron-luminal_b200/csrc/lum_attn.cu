@@ -47,7 +47,7 @@ __device__ __forceinline__ float gain_at(const void* g, int kind, int i) {
 }
 
 // cos/sin of the rotation for pair index i at position pos.
-__device__ __noinline__ void rope_cs(const AttnArgs& a, int i, int pos, float* cs, float* sn) {
+__device__ __forceinline__ void rope_cs(const AttnArgs& a, int i, int pos, float* cs, float* sn) {
     if (a.rope_style == 0) {
         // the graph's chain, constant by constant: f = 2i * (1/d); inv = 1/exp2((f * ln theta) * log2 e);
         // emb = pos * inv; sin(emb); cos as sin(-emb + pi/2)
@@ -64,66 +64,20 @@ __device__ __noinline__ void rope_cs(const AttnArgs& a, int i, int pos, float* c
     }
 }
 
-// Load this lane's 16 dims [d0, d0+16) of one head vector from f32 memory, optionally RMS-normalise
-// the head (needs the other lanes of the head group: LPP lanes hold one head), rotate, return in v.
-template <int HD>
-__device__ __forceinline__ void load_rotated(const AttnArgs& a, const float* head, const void* gain, int d0, const float* rc, const float* rs, float* v, uint32_t gmask) {
-    constexpr int LPP = HD / 16;
-    if (a.rope_style == 0) {
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = head[d0 + i];
-    }
-    float other[16];
-    if (a.rope_style != 0) {
-        const int half = HD / 2;
-        const int o0 = d0 < half ? d0 + half : d0 - half;
-#pragma unroll
-        for (int i = 0; i < 16; i++) { v[i] = head[d0 + i]; other[i] = head[o0 + i]; }
-    }
-    if (gain) {
-        // per-head RMSNorm: x * rsqrt(mean(x^2) + eps) * g
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; i++) ss = fmaf(v[i], v[i], ss);
-#pragma unroll
-        for (int o = LPP / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(gmask, ss, o);
-        const float inv = 1.0f / sqrtf(ss * (1.0f / (float)HD) + a.qk_eps);
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = (inv * v[i]) * gain_at(gain, a.gain_kind, d0 + i);
-        if (a.rope_style != 0) {
-            const int half = HD / 2;
-            const int o0 = d0 < half ? d0 + half : d0 - half;
-#pragma unroll
-            for (int i = 0; i < 16; i++) other[i] = (inv * other[i]) * gain_at(gain, a.gain_kind, o0 + i);
-        }
-    }
-    if (a.rope_style == 0) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float cs = rc[j], sn = rs[j];
-            const float x0 = v[2 * j], x1 = v[2 * j + 1];
-            // separately rounded products and sums, as the graph's Mul/Add nodes produce them
-            v[2 * j] = __fadd_rn(__fmul_rn(x0, cs), __fmul_rn(__fmul_rn(x1, sn), -1.0f));
-            v[2 * j + 1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
-        }
-    } else {
-        const int half = HD / 2;
-        const bool lo = d0 < half;
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const float cs = rc[i], sn = rs[i];
-            // lower half: x0*c - x1*s with x1 = partner; upper half: x1*c + x0*s with x0 = partner
-            v[i] = lo ? __fsub_rn(__fmul_rn(v[i], cs), __fmul_rn(other[i], sn)) : __fadd_rn(__fmul_rn(v[i], cs), __fmul_rn(other[i], sn));
-        }
-    }
-}
-
 // One (kv head, split) per CTA.  G query heads per KV head (G <= 8; processed in tiles of GT).
+//
+// Phase A (whole CTA): this step's q heads of the group — and, in the CTA that owns the last split, the
+// step's own k and v — are staged in shared memory, RMS-normalised per head if the model asks for it,
+// rotated, and (k, v) rounded to the cache type and appended to the cache.
+// Phase B: each group of LPP lanes walks cached rows with a running (max, sum, weighted V) per q head.
+// Loops over heads stay rolled where they can: the kernel runs once per CTA, so every instruction
+// cache line it touches is a cold miss and straight-line code size is latency.
 template <int HD, int GT, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a) {
     constexpr int LPP = HD / 16;            // lanes per cached position
     constexpr int PPW = 32 / LPP;           // positions per warp per trip
     constexpr int NW = kAttnThreads / 32;
+    constexpr int kMaxG = 8;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.x, split = blockIdx.y;
     const int G = a.n_q / a.n_kv;
@@ -132,8 +86,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     const uint32_t gmask = (LPP == 32 ? 0xffffffffu : ((1u << LPP) - 1u)) << (sub * LPP);   // the lanes sharing one position
     const size_t row_elems = (size_t)a.n_kv * HD;
 
+    __shared__ __align__(16) float s_q[kMaxG + 1][HD];   // rotated q heads; row G = this step's k
+    __shared__ __align__(16) float s_v[HD];
     __shared__ float s_m[NW][GT], s_l[NW][GT];
-    __shared__ float s_o[NW][GT][HD];
+    __shared__ __align__(16) float s_o[NW][GT][HD];
     __shared__ int s_last;
 
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
@@ -149,52 +105,82 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     const int per = (n_cached + a.n_splits - 1) / a.n_splits;
     const int r0 = lo + split * per;
     const int r1 = min(p, r0 + per);
+    const int nc = max(0, r1 - r0);                    // cached rows of this CTA
     const bool owns_new = split == a.n_splits - 1;
+    const int n_rows = nc + (owns_new ? 1 : 0);
     const float scale = 1.0f / sqrtf((float)HD);
 
-    // rotation factors for this lane's dims: pair (d0/2 + j) for adjacent pairs, pair (d0 mod d/2) + i for split halves
-    float rc[16], rs[16];
-    {
-        const int npair = a.rope_style == 0 ? 8 : 16;
-        const int first = a.rope_style == 0 ? (d0 >> 1) : (d0 < HD / 2 ? d0 : d0 - HD / 2);
-#pragma unroll 1
-        for (int j = 0; j < npair; j++) rope_cs(a, first + j, p, &rc[j], &rs[j]);
+    // ---- phase A
+    const int nheads = G + (owns_new ? 1 : 0);
+    for (int idx = tid; idx < nheads * HD; idx += kAttnThreads) {
+        const int h = idx / HD, e = idx - h * HD;
+        s_q[h][e] = h < G ? a.q[((size_t)kvh * G + h) * HD + e] : a.k_new[(size_t)kvh * HD + e];
     }
-
-    // this step's K/V row for the KV head: rotate, round to the cache type, store (one sub-group of warp 0)
-    float knew[16], vnew[16];
-    if (owns_new && warp == 0 && sub == 0) {
-        load_rotated<HD>(a, a.k_new + (size_t)kvh * HD, a.k_gain, d0, rc, rs, knew, gmask);
-#pragma unroll
-        for (int i = 0; i < 16; i++) vnew[i] = a.v_new[(size_t)kvh * HD + d0 + i];
-        const size_t off = (size_t)p * row_elems + (size_t)kvh * HD + d0;
-        if (BF16) {
-            __nv_bfloat16* kc = (__nv_bfloat16*)a.k_cache + off;
-            __nv_bfloat16* vc = (__nv_bfloat16*)a.v_cache + off;
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const __nv_bfloat16 kb = __float2bfloat16_rn(knew[i]), vb = __float2bfloat16_rn(vnew[i]);
-                kc[i] = kb; vc[i] = vb;
-                knew[i] = __bfloat162float(kb); vnew[i] = __bfloat162float(vb);
-            }
+    if (owns_new)
+        for (int e = tid; e < HD; e += kAttnThreads) s_v[e] = a.v_new[(size_t)kvh * HD + e];
+    __syncthreads();
+    if (a.q_gain || a.k_gain) {
+        // per-head RMSNorm: x * 1/sqrt(mean(x^2) + eps) * g   (one warp per head)
+#pragma unroll 1
+        for (int h = warp; h < nheads; h += NW) {
+            const void* gain = h < G ? a.q_gain : a.k_gain;
+            if (!gain) continue;
+            float ss = 0.0f;
+            for (int e = lane; e < HD; e += 32) ss = fmaf(s_q[h][e], s_q[h][e], ss);
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss * (1.0f / (float)HD) + a.qk_eps);
+            for (int e = lane; e < HD; e += 32) s_q[h][e] = (inv * s_q[h][e]) * gain_at(gain, a.gain_kind, e);
+        }
+        __syncthreads();
+    }
+#pragma unroll 1
+    for (int idx = tid; idx < nheads * (HD / 2); idx += kAttnThreads) {
+        const int h = idx / (HD / 2), i = idx - h * (HD / 2);
+        float cs, sn;
+        rope_cs(a, i, p, &cs, &sn);
+        const int e0 = a.rope_style == 0 ? 2 * i : i, e1 = a.rope_style == 0 ? 2 * i + 1 : i + HD / 2;
+        const float x0 = s_q[h][e0], x1 = s_q[h][e1];
+        // separately rounded products and sums, as the graph's Mul / Add nodes produce them
+        if (a.rope_style == 0) {
+            s_q[h][e0] = __fadd_rn(__fmul_rn(x0, cs), __fmul_rn(__fmul_rn(x1, sn), -1.0f));
+            s_q[h][e1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
         } else {
-            float* kc = (float*)a.k_cache + off;
-            float* vc = (float*)a.v_cache + off;
-#pragma unroll
-            for (int i = 0; i < 16; i++) { kc[i] = knew[i]; vc[i] = vnew[i]; }
+            s_q[h][e0] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+            s_q[h][e1] = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(x0, sn));
         }
     }
+    __syncthreads();
+    if (owns_new) {
+        // append this step's row to the cache; keep the rounded values for our own use
+        const size_t off = (size_t)p * row_elems + (size_t)kvh * HD;
+        for (int e = tid; e < HD; e += kAttnThreads) {
+            if (BF16) {
+                const __nv_bfloat16 kb = __float2bfloat16_rn(s_q[G][e]), vb = __float2bfloat16_rn(s_v[e]);
+                ((__nv_bfloat16*)a.k_cache)[off + e] = kb;
+                ((__nv_bfloat16*)a.v_cache)[off + e] = vb;
+                s_q[G][e] = __bfloat162float(kb);
+                s_v[e] = __bfloat162float(vb);
+            } else {
+                ((float*)a.k_cache)[off + e] = s_q[G][e];
+                ((float*)a.v_cache)[off + e] = s_v[e];
+            }
+        }
+        __syncthreads();
+    }
 
+    // ---- phase B
+#pragma unroll 1
     for (int g0 = 0; g0 < G; g0 += GT) {
         const int gn = min(GT, G - g0);
-        // rotated queries of this head tile, this lane's 16 dims
         float q[GT][16];
 #pragma unroll
         for (int g = 0; g < GT; g++) {
-            if (g < gn) load_rotated<HD>(a, a.q + ((size_t)kvh * G + g0 + g) * HD, a.q_gain, d0, rc, rs, q[g], gmask);
-            else {
+            const float4* p4 = (const float4*)&s_q[min(g0 + g, G - 1)][d0];
 #pragma unroll
-                for (int i = 0; i < 16; i++) q[g][i] = 0.0f;
+            for (int i = 0; i < 4; i++) {
+                const float4 t = p4[i];
+                const float keep = g < gn ? 1.0f : 0.0f;
+                q[g][4 * i] = t.x * keep; q[g][4 * i + 1] = t.y * keep; q[g][4 * i + 2] = t.z * keep; q[g][4 * i + 3] = t.w * keep;
             }
         }
         float m[GT], l[GT], o[GT][16];
@@ -205,43 +191,43 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
             for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
         }
 
-        auto absorb = [&](const float* kr, const float* vr) {
-#pragma unroll
-            for (int g = 0; g < GT; g++) {
-                float d = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 16; i++) d = fmaf(q[g][i], kr[i], d);
-#pragma unroll
-                for (int s = LPP / 2; s > 0; s >>= 1) d += __shfl_xor_sync(gmask, d, s);
-                const float logit = d * scale;
-                const float mn = fmaxf(m[g], logit);
-                const float corr = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - mn);
-                const float w = expf(logit - mn);
-                l[g] = l[g] * corr + w;
-#pragma unroll
-                for (int i = 0; i < 16; i++) o[g][i] = fmaf(w, vr[i], o[g][i] * corr);
-                m[g] = mn;
-            }
-        };
-
-        // cached rows of this split: warp w, sub-group s takes rows r0 + (trip*NW + w)*PPW + s
-        for (int base = r0 + warp * PPW; base < r1; base += NW * PPW) {
-            const int r = base + sub;
-            // a sub-group (the LPP lanes of one position) is active or idle as a whole, and the
-            // shuffles inside absorb() name only that sub-group
-            if (r < r1) {
+        // rows of this CTA: cached rows r0 .. r1-1, then (last split only) the step's own row from shared memory.
+        // A sub-group (the LPP lanes of one position) is active or idle as a whole; its shuffles name only itself.
+#pragma unroll 1
+        for (int base = warp * PPW; base < n_rows; base += NW * PPW) {
+            const int j = base + sub;
+            if (j < n_rows) {
                 float kr[16], vr[16];
-                const size_t off = (size_t)r * row_elems + (size_t)kvh * HD + d0;
-                load16<BF16>(a.k_cache, off, kr);
-                load16<BF16>(a.v_cache, off, vr);
-                absorb(kr, vr);
+                if (j < nc) {
+                    const size_t off = (size_t)(r0 + j) * row_elems + (size_t)kvh * HD + d0;
+                    load16<BF16>(a.k_cache, off, kr);
+                    load16<BF16>(a.v_cache, off, vr);
+                } else {
+                    load16<false>(&s_q[G][0], (size_t)d0, kr);
+                    load16<false>(&s_v[0], (size_t)d0, vr);
+                }
+#pragma unroll
+                for (int g = 0; g < GT; g++) {
+                    float d = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) d = fmaf(q[g][i], kr[i], d);
+#pragma unroll
+                    for (int s = LPP / 2; s > 0; s >>= 1) d += __shfl_xor_sync(gmask, d, s);
+                    const float logit = d * scale;
+                    const float mn = fmaxf(m[g], logit);
+                    const float corr = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - mn);
+                    const float w = expf(logit - mn);
+                    l[g] = l[g] * corr + w;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) o[g][i] = fmaf(w, vr[i], o[g][i] * corr);
+                    m[g] = mn;
+                }
             }
         }
-        if (owns_new && warp == 0 && sub == 0) absorb(knew, vnew);
         __syncwarp();
 
         // merge the PPW sub-groups of the warp
-#pragma unroll
+#pragma unroll 1
         for (int s = LPP; s < 32; s <<= 1) {
 #pragma unroll
             for (int g = 0; g < GT; g++) {
@@ -298,18 +284,41 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // The partials were written by other CTAs: read them through L2 (ld.cg), in batches of independent
+    // loads so the round trips overlap instead of queueing behind one another.
+    constexpr int kBatch = 8;
+#pragma unroll 1
     for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, e = idx - g * HD;
-        const volatile float* src = a.part + ((size_t)kvh * a.n_splits * G + g) * (HD + 2);
+        const float* src = a.part + ((size_t)kvh * a.n_splits * G + g) * (HD + 2);
         const size_t sstride = (size_t)G * (HD + 2);
         float M = -INFINITY;
-        for (int s = 0; s < a.n_splits; s++) M = fmaxf(M, src[s * sstride + HD]);
+#pragma unroll 1
+        for (int s0 = 0; s0 < a.n_splits; s0 += kBatch) {
+            float mv[kBatch];
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) mv[j] = (s0 + j < a.n_splits) ? __ldcg(src + (size_t)(s0 + j) * sstride + HD) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) M = fmaxf(M, mv[j]);
+        }
         float L = 0.0f, O = 0.0f;
-        for (int s = 0; s < a.n_splits; s++) {
-            const float ms = src[s * sstride + HD];
-            const float c = (ms == -INFINITY) ? 0.0f : expf(ms - M);
-            L = fmaf(src[s * sstride + HD + 1], c, L);
-            O = fmaf(src[s * sstride + e], c, O);
+#pragma unroll 1
+        for (int s0 = 0; s0 < a.n_splits; s0 += kBatch) {
+            float mv[kBatch], lv[kBatch], ov[kBatch];
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) {
+                const bool in = s0 + j < a.n_splits;
+                const float* q = src + (size_t)(in ? s0 + j : 0) * sstride;
+                mv[j] = in ? __ldcg(q + HD) : -INFINITY;
+                lv[j] = __ldcg(q + HD + 1);
+                ov[j] = __ldcg(q + e);
+            }
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) {
+                const float c = (mv[j] == -INFINITY) ? 0.0f : expf(mv[j] - M);
+                L = fmaf(lv[j], c, L);
+                O = fmaf(ov[j], c, O);
+            }
         }
         a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);
     }

@@ -21,9 +21,11 @@ enum : uint32_t {
     LUM_ST_BAD_POS = 1u << 4,     // position outside the cache capacity
 };
 
-// Wall-clock budget for any single wait, in nanoseconds of %globaltimer.
-#ifndef LUM_WAIT_BUDGET_NS
-#define LUM_WAIT_BUDGET_NS 2000000000ull
+// Budget for any single wait, in SM clock cycles (about two seconds at 2 GHz).  The SM-local cycle
+// counter is used because reading %globaltimer costs on the order of a microsecond per read, which
+// would sit on the critical path of every stage hand-over.
+#ifndef LUM_WAIT_BUDGET_CYCLES
+#define LUM_WAIT_BUDGET_CYCLES 4000000000ll
 #endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -58,15 +60,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false once LUM_WAIT_BUDGET_NS has passed without the phase completing.
+// Bounded wait: false once LUM_WAIT_BUDGET_CYCLES have passed without the phase completing.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    for (int i = 0; i < 32; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; i++)
+        for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > LUM_WAIT_BUDGET_NS) return false;
+        if (clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) return false;
     }
 }
 

@@ -28,9 +28,10 @@ struct DecodeState {
 };
 
 struct GemvSeg {
-    const void* w;      // quants (int8 [rows, K]) for Q8_0, else the f32 / bf16 matrix [rows, K]
-    const __half* s;    // Q8_0 scales [rows, K/32], else null
+    const void* w;      // Q8_0: quants plane (int8 [rows, K]) or the packed stage-unit stream; else the f32 / bf16 matrix [rows, K]
+    const __half* s;    // Q8_0 planes: scales [rows, K/32]; otherwise null
     int rows;
+    int kc;             // Q8_0: 0 = planes; > 0 = packed stage-units with this K-chunk (see lum_synth.cu)
 };
 
 struct GemvArgs {
@@ -61,6 +62,7 @@ struct GemvArgs {
     int max_units;         // most stage-units any CTA owns (sizes the reduction scratch)
     int use_pdl;
     int force_direct;      // 1: never take the streaming kernel (operator tests compare the two)
+    int debug;             // tuning probes of the streaming kernel (0 in normal use)
 };
 
 struct AttnArgs {
@@ -106,11 +108,16 @@ cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
 
 // synthetic tensors + format conversion
 cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,
-                            size_t full_cols, cudaStream_t st);
+                            size_t full_cols, int kc, cudaStream_t st);
 cudaError_t launch_synth_normal(uint64_t seed, uint64_t tid, void* out, int kind, size_t rows, size_t cols, size_t row0, size_t col0,
                                 size_t full_cols, int ones, cudaStream_t st);
+// Packed Q8_0 layout: the K-chunk a [rows, K] matrix packs with (0 = not packable) and its size in bytes.
+int q8_pack_kc(int rows, int K);
+size_t q8_packed_bytes(int rows, int K);
+cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st);
 cudaError_t launch_q8_unpack_wire(const uint8_t* blocks, int8_t* q, __half* s, size_t n_blocks, cudaStream_t st);
 cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size_t n_elems, cudaStream_t st);
+cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st);
 cudaError_t launch_to_f32(const void* in, int kind, float* out, size_t n, cudaStream_t st);
 
 }  // namespace lum

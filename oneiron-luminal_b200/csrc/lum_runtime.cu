@@ -34,6 +34,7 @@ struct Tensor {
     void* w = nullptr;       // quants / f32 / bf16
     __half* s = nullptr;     // Q8_0 scales
     int kind = WK_F32;
+    int kc = 0;              // Q8_0: 0 = planes, > 0 = packed stage-units with this K-chunk
     size_t rows = 0, cols = 0;          // this rank's shard
     size_t row0 = 0, col0 = 0;          // shard origin in the full tensor
     size_t full_rows = 0, full_cols = 0;
@@ -125,9 +126,14 @@ int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_
     const size_t n = rows * cols;
     if (kind == WK_Q8) {
         if (cols % 32 || full_cols % 32 || col0 % 32) return fail(rt, LUM_E_INVALID, "Q8_0 tensors need K %% 32 == 0 (K = %zu)", cols);
-        // +64: the streaming kernel's last scale copy may be rounded up to 16 bytes
-        if (int r = dev_alloc(rt, &t.w, n + 64)) return r;
-        if (int r = dev_alloc(rt, (void**)&t.s, n / 16 + 64)) return r;
+        t.kc = q8_pack_kc((int)rows, (int)cols);
+        if (t.kc) {
+            if (int r = dev_alloc(rt, &t.w, q8_packed_bytes((int)rows, (int)cols) + 64)) return r;
+            t.s = nullptr;
+        } else {
+            if (int r = dev_alloc(rt, &t.w, n + 64)) return r;
+            if (int r = dev_alloc(rt, (void**)&t.s, n / 16 + 64)) return r;
+        }
     } else {
         if (int r = dev_alloc(rt, &t.w, n * (kind == WK_BF16 ? 2 : 4) + 64)) return r;
     }
@@ -214,9 +220,9 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = w.q.kind;
         // RMSNorm + q,k,v
         a.nseg = 3;
-        a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows};
-        a.seg[1] = {w.k.w, w.k.s, (int)w.k.rows};
-        a.seg[2] = {w.v.w, w.v.s, (int)w.v.rows};
+        a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows, w.q.kc};
+        a.seg[1] = {w.k.w, w.k.s, (int)w.k.rows, w.k.kc};
+        a.seg[2] = {w.v.w, w.v.s, (int)w.v.rows, w.v.kc};
         a.K = H; a.epi = EPI_STORE; a.x = rt->x; a.gain = w.attn_norm.w; a.y = rt->qkv;
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
 
@@ -233,21 +239,21 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         // o projection + residual
         GemvArgs o{};
         o.status = rt->status; o.use_pdl = pdl; o.wkind = w.o.kind;
-        o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows};
+        o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows, w.o.kc};
         o.K = (int)w.o.cols; o.epi = EPI_RESID; o.x = rt->attn; o.y = rt->x; o.resid = rt->x;
         CU(rt, launch_gemv(o, rt->sm_count, st)); n++;
 
         // RMSNorm + gate, up + SwiGLU
         GemvArgs g{};
         g.status = rt->status; g.use_pdl = pdl; g.gain_kind = gk; g.eps = rt->eps6; g.wkind = w.gate.kind;
-        g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows};
+        g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows, w.gate.kc}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows, w.up.kc};
         g.K = H; g.epi = EPI_SWIGLU; g.x = rt->x; g.gain = w.mlp_norm.w; g.y = rt->h;
         CU(rt, launch_gemv(g, rt->sm_count, st)); n++;
 
         // down projection + residual
         GemvArgs dn{};
         dn.status = rt->status; dn.use_pdl = pdl; dn.wkind = w.down.kind;
-        dn.nseg = 1; dn.seg[0] = {w.down.w, w.down.s, (int)w.down.rows};
+        dn.nseg = 1; dn.seg[0] = {w.down.w, w.down.s, (int)w.down.rows, w.down.kc};
         dn.K = (int)w.down.cols; dn.epi = EPI_RESID; dn.x = rt->h; dn.y = rt->x; dn.resid = rt->x;
         CU(rt, launch_gemv(dn, rt->sm_count, st)); n++;
     }
@@ -255,7 +261,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         const Tensor& hw = d.tied_head ? rt->embed : rt->lm_head;
         GemvArgs a{};
         a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = hw.kind;
-        a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows};
+        a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows, hw.kc};
         a.K = H; a.epi = EPI_ARGMAX; a.x = rt->x; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
@@ -472,8 +478,23 @@ int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void
         // copies go on the runtime's own (non-blocking) stream: a legacy-stream copy from pageable memory may return
         // before its DMA has landed and would not be ordered against kernels on this stream
         e = cudaMemcpy2DAsync(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice, rt->stream);
-        if (e == cudaSuccess) e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)t->w, t->s, t->rows * t->cols / 32, rt->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+        if (t->kc) {
+            // wire blocks -> temporary planes -> packed stage-units
+            void* planes = nullptr;
+            const size_t n = t->rows * t->cols;
+            if (e == cudaSuccess) e = cudaMalloc(&planes, n + n / 16 + 64);
+            if (e == cudaSuccess) {
+                __half* ps = (__half*)((char*)planes + n);
+                e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)planes, ps, n / 32, rt->stream);
+                if (e == cudaSuccess) e = launch_q8_pack_units((const int8_t*)planes, ps, (int)t->rows, (int)t->cols, t->kc, (unsigned char*)t->w, rt->stream);
+            }
+            if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+            else cudaStreamSynchronize(rt->stream);
+            if (planes) cudaFree(planes);
+        } else {
+            if (e == cudaSuccess) e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)t->w, t->s, t->rows * t->cols / 32, rt->stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+        }
         cudaFree(tmp);
         if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "set_weight: %s", cudaGetErrorString(e));
     } else {
@@ -492,7 +513,7 @@ int32_t lum_model_synth(lum_rt* rt, uint64_t seed) {
         if (!t) return 0;
         const uint64_t tid = tensor_id(slot, slot_layer_for_id(rt, slot, layer));
         cudaError_t e;
-        if (t->kind == WK_Q8) e = launch_synth_q8(seed, tid, (int8_t*)t->w, t->s, t->rows, t->cols, t->row0, t->col0, t->full_cols, rt->stream);
+        if (t->kind == WK_Q8) e = launch_synth_q8(seed, tid, (int8_t*)t->w, t->s, t->rows, t->cols, t->row0, t->col0, t->full_cols, t->kc, rt->stream);
         else e = launch_synth_normal(seed, tid, t->w, t->kind, t->rows, t->cols, t->row0, t->col0, t->full_cols, ones, rt->stream);
         if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "synth slot %d layer %d: %s", slot, layer, cudaGetErrorString(e));
         return 0;
@@ -516,11 +537,11 @@ int32_t lum_model_get_weight_f32(lum_rt* rt, int32_t slot, int32_t layer, size_t
     Tensor* t = slot_tensor(rt, slot, layer);
     if (!t) return fail(rt, LUM_E_INVALID, "get_weight: slot %d / layer %d does not exist", slot, layer);
     if (offset + n > t->rows * t->cols) return fail(rt, LUM_E_INVALID, "get_weight: range outside the tensor");
-    if (t->kind == WK_Q8 && (offset % 32)) return fail(rt, LUM_E_INVALID, "get_weight: Q8_0 offset must be a multiple of 32");
+    if (t->kind == WK_Q8 && (offset % t->cols || n % t->cols)) return fail(rt, LUM_E_INVALID, "get_weight: Q8_0 ranges must cover whole rows");
     float* tmp = nullptr;
     cudaError_t e = cudaMalloc((void**)&tmp, n * 4 + 16);
     if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "get_weight: %s", cudaGetErrorString(e));
-    if (t->kind == WK_Q8) e = launch_q8_dequant((const int8_t*)t->w + offset, t->s + offset / 32, tmp, n, rt->stream);
+    if (t->kind == WK_Q8) e = launch_q8_dequant_rows(t->w, t->s, (int)t->cols, t->kc, offset / t->cols, n / t->cols, tmp, rt->stream);
     else e = launch_to_f32((const uint8_t*)t->w + offset * (t->kind == WK_BF16 ? 2 : 4), t->kind, tmp, n, rt->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
@@ -729,18 +750,46 @@ static uint32_t* op_status_word() {
 int32_t lum_op_gemv_q8_0(const int8_t* q, const void* s, int32_t n, int32_t k, const float* x, float* y, int32_t force_direct, void* stream) {
     if (!q || !s || !x || !y || n <= 0 || k <= 0 || (k % 32)) { g_create_error = "gemv_q8_0: bad arguments (K must be a multiple of 32)"; return LUM_E_INVALID; }
     GemvArgs a{};
-    a.nseg = 1; a.seg[0] = {q, (const __half*)s, n}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_STORE; a.x = x; a.y = y;
+    a.nseg = 1; a.seg[0] = {q, (const __half*)s, n, 0}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_STORE; a.x = x; a.y = y;
     a.status = op_status_word();
     if (!a.status) return op_fail("gemv_q8_0 status word", cudaErrorMemoryAllocation);
-    a.force_direct = force_direct;
+    (void)force_direct;   // plane-layout weights always take the direct kernel
     const cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : op_fail("gemv_q8_0", e);
+}
+
+size_t lum_q8_0_packed_bytes(int32_t n, int32_t k) { return q8_packed_bytes(n, k); }
+
+int32_t lum_op_q8_0_pack(const int8_t* q, const void* s, int32_t n, int32_t k, void* packed, void* stream) {
+    const int kc = q8_pack_kc(n, k);
+    if (!q || !s || !packed || !kc) { g_create_error = "q8_0_pack: shape cannot be packed (needs K % 512 == 0, K <= 16384, N % (16384 / KC) == 0)"; return LUM_E_INVALID; }
+    cudaError_t e = launch_q8_pack_units(q, (const __half*)s, n, k, kc, (unsigned char*)packed, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("q8_0_pack", e);
+}
+
+int32_t lum_op_gemv_q8_0_packed(const void* packed, int32_t n, int32_t k, const float* x, float* y, int32_t force_direct, void* stream) {
+    const int kc = q8_pack_kc(n, k);
+    if (!packed || !x || !y || !kc) { g_create_error = "gemv_q8_0_packed: bad arguments or shape cannot be packed"; return LUM_E_INVALID; }
+    GemvArgs a{};
+    a.nseg = 1; a.seg[0] = {packed, nullptr, n, kc}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_STORE; a.x = x; a.y = y;
+    a.status = op_status_word();
+    if (!a.status) return op_fail("gemv_q8_0_packed status word", cudaErrorMemoryAllocation);
+    a.force_direct = force_direct;
+    const cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("gemv_q8_0_packed", e);
+}
+
+int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tid, int32_t n, int32_t k, void* packed, void* stream) {
+    const int kc = q8_pack_kc(n, k);
+    if (!packed || !kc) { g_create_error = "synth_q8_0_packed: shape cannot be packed"; return LUM_E_INVALID; }
+    cudaError_t e = launch_synth_q8(seed, tid, (int8_t*)packed, nullptr, (size_t)n, (size_t)k, 0, 0, (size_t)k, kc, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("synth_q8_0_packed", e);
 }
 
 int32_t lum_op_gemv_f32(const float* w, int32_t n, int32_t k, const float* x, float* y, void* stream) {
     if (!w || !x || !y || n <= 0 || k <= 0) { g_create_error = "gemv_f32: bad arguments"; return LUM_E_INVALID; }
     GemvArgs a{};
-    a.nseg = 1; a.seg[0] = {w, nullptr, n}; a.K = k; a.wkind = WK_F32; a.epi = EPI_STORE; a.x = x; a.y = y;
+    a.nseg = 1; a.seg[0] = {w, nullptr, n, 0}; a.K = k; a.wkind = WK_F32; a.epi = EPI_STORE; a.x = x; a.y = y;
     a.status = op_status_word();
     if (!a.status) return op_fail("gemv_f32 status word", cudaErrorMemoryAllocation);
     cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
@@ -760,7 +809,7 @@ int32_t lum_op_q8_0_dequant(const int8_t* q, const void* s, size_t n, float* out
 int32_t lum_op_synth_q8_0(uint64_t seed, uint64_t tid, size_t n, int8_t* q, void* s, void* stream) {
     if (!q || !s || (n % 32)) { g_create_error = "synth_q8_0: bad arguments"; return LUM_E_INVALID; }
     // a flat tensor: one row of n columns would overflow nothing but keeps indices identical
-    cudaError_t e = launch_synth_q8(seed, tid, q, (__half*)s, 1, n, 0, 0, n, (cudaStream_t)stream);
+    cudaError_t e = launch_synth_q8(seed, tid, q, (__half*)s, 1, n, 0, 0, n, 0, (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : op_fail("synth_q8_0", e);
 }
 int32_t lum_op_synth_normal(uint64_t seed, uint64_t tid, uint32_t dtype, size_t n, int32_t ones, void* out, void* stream) {

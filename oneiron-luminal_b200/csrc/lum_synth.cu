@@ -2,9 +2,13 @@
 // load in a benchmark environment; the reference downloads them, examples/llama/src/hf.rs:26-50),
 // the Q8_0 wire <-> device-layout conversion, and dequantisation for inspection.
 //
-// Device layout of a Q8_0 matrix [N, K]: a plane of int8 quants [N, K] followed by a separate
-// plane of binary16 scales [N, K/32].  Same bytes as the 34-byte wire blocks (34/32 B per weight)
-// but every row of either plane starts 16-byte aligned, which bulk copies and 128-bit loads need.
+// Device layouts of a Q8_0 matrix [N, K] (both hold exactly the wire format's 34/32 bytes per weight):
+//  * planes — int8 quants [N, K] and, separately, binary16 scales [N, K/32]; every row 16-byte aligned.
+//  * packed — the layout the streaming GEMV reads.  The matrix is cut into stage-units of R rows x KC
+//    columns with R * KC = 16384 (KC the largest power of two in 512..4096 dividing K).  A unit is
+//    17408 contiguous bytes: its quants row-major [R, KC], then its scales [R, KC/32].  Units are
+//    ordered by row group, then K-chunk, so that one bulk copy fetches one pipeline stage and the
+//    chunks of a row group are consecutive.  Used whenever K % 512 == 0, K <= 16384 and N % R == 0.
 //
 // Generator (all integer arithmetic except the normal draw, which is binary64 Box-Muller):
 //   key(seed, tid)    = mix(seed + G * (tid + 1)),  G = 0x9E3779B97F4A7C15, mix = SplitMix64 finaliser
@@ -36,11 +40,27 @@ __device__ __forceinline__ double rng_normal(uint64_t key, uint64_t idx) {
 // exactly its slice.
 struct Shard { size_t rows, cols, row0, col0, full_cols; };
 
-__global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh) {
+constexpr size_t kUnitQ = 16384, kUnitBytes = 17408;
+
+// packed position -> (row, col) of the shard.  i = index of a quant inside the packed quant areas
+// laid end to end (unit after unit), kc = K-chunk, cols = K.
+__device__ __forceinline__ void packed_to_rc(size_t i, int kc, size_t cols, size_t* r, size_t* c, size_t* byte_off) {
+    const size_t u = i / kUnitQ, within = i - u * kUnitQ;
+    const size_t nch = cols / kc, R = kUnitQ / kc;
+    const size_t g = u / nch, ch = u - g * nch;
+    const size_t rr = within / kc, kk = within - rr * kc;
+    *r = g * R + rr;
+    *c = ch * kc + kk;
+    *byte_off = u * kUnitBytes + within;
+}
+
+__global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh, int kc) {
     // 16 quants per thread, one 128-bit store (cols is a multiple of 32)
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
     if (i >= sh.rows * sh.cols) return;
-    const size_t r = i / sh.cols, c = i - r * sh.cols;
+    size_t r, c, off;
+    if (kc) packed_to_rc(i, kc, sh.cols, &r, &c, &off);
+    else { r = i / sh.cols; c = i - r * sh.cols; off = i; }
     const size_t gi = (sh.row0 + r) * sh.full_cols + sh.col0 + c;
     uint32_t w[4];
 #pragma unroll
@@ -54,15 +74,41 @@ __global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh) {
         }
         w[j] = v;
     }
-    *(uint4*)(q + i) = make_uint4(w[0], w[1], w[2], w[3]);
+    *(uint4*)(q + off) = make_uint4(w[0], w[1], w[2], w[3]);
 }
-__global__ void synth_q8_scales(uint64_t skey, __half* s, Shard sh) {
+__global__ void synth_q8_scales(uint64_t skey, __half* s, unsigned char* packed, Shard sh, int kc) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t bpr = sh.cols / 32;
     if (b >= sh.rows * bpr) return;
-    const size_t r = b / bpr, cb = b - r * bpr;
-    const size_t gb = ((sh.row0 + r) * sh.full_cols + sh.col0) / 32 + cb;
-    s[b] = __float2half_rn((float)(fabs(0.02 * rng_normal(skey, gb)) / 127.0));
+    size_t r, c, off;
+    if (kc) packed_to_rc(b * 32, kc, sh.cols, &r, &c, &off);
+    else { r = b / bpr; c = (b - r * bpr) * 32; }
+    const size_t gb = ((sh.row0 + r) * sh.full_cols + sh.col0 + c) / 32;
+    const __half v = __float2half_rn((float)(fabs(0.02 * rng_normal(skey, gb)) / 127.0));
+    if (kc) {
+        const size_t u = (b * 32) / kUnitQ, within_blocks = b - u * (kUnitQ / 32);
+        *(__half*)(packed + u * kUnitBytes + kUnitQ + within_blocks * 2) = v;
+    } else {
+        s[b] = v;
+    }
+}
+// planes -> packed
+__global__ void q8_pack_units(const int8_t* q, const __half* s, size_t rows, size_t cols, int kc, unsigned char* out) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+    if (i >= rows * cols) return;
+    size_t r, c, off;
+    packed_to_rc(i, kc, cols, &r, &c, &off);
+    *(uint4*)(out + off) = *(const uint4*)(q + r * cols + c);
+    if ((i & 31) == 0) {
+        const size_t b = i / 32, u = i / kUnitQ, within_blocks = b - u * (kUnitQ / 32);
+        *(__half*)(out + u * kUnitBytes + kUnitQ + within_blocks * 2) = s[r * (cols / 32) + c / 32];
+    }
+}
+cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st) {
+    if (kc <= 0 || K % kc || ((size_t)rows * K) % kUnitQ) return cudaErrorInvalidValue;
+    const size_t t16 = (size_t)rows * K / 16;
+    q8_pack_units<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(q, s, (size_t)rows, (size_t)K, kc, out);
+    return cudaGetLastError();
 }
 __global__ void synth_normal(uint64_t key, void* out, int kind, Shard sh, int ones) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -74,14 +120,15 @@ __global__ void synth_normal(uint64_t key, void* out, int kind, Shard sh, int on
     else ((float*)out)[i] = v;
 }
 
+// kc == 0: planes (q, s).  kc > 0: packed stream written at q (s unused).
 cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,
-                            size_t full_cols, cudaStream_t st) {
+                            size_t full_cols, int kc, cudaStream_t st) {
     if (cols % 32 || col0 % 32 || full_cols % 32) return cudaErrorInvalidValue;
     const Shard sh{rows, cols, row0, col0, full_cols};
     const size_t t16 = rows * cols / 16;
-    synth_q8_quants<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(rng_key(seed, tid), q, sh);
+    synth_q8_quants<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(rng_key(seed, tid), q, sh, kc);
     const size_t nb = rows * cols / 32;
-    synth_q8_scales<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(rng_key(seed, tid + 4096), s, sh);
+    synth_q8_scales<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(rng_key(seed, tid + 4096), s, (unsigned char*)q, sh, kc);
     return cudaGetLastError();
 }
 cudaError_t launch_synth_normal(uint64_t seed, uint64_t tid, void* out, int kind, size_t rows, size_t cols, size_t row0, size_t col0,
@@ -114,6 +161,26 @@ __global__ void q8_dequant(const int8_t* q, const __half* s, float* out, size_t 
 }
 cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size_t n, cudaStream_t st) {
     q8_dequant<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(q, s, out, n);
+    return cudaGetLastError();
+}
+
+// logical rows [row0, row0 + n_rows) of a Q8_0 matrix in either layout -> f32 row-major
+__global__ void q8_dequant_rows(const void* w, const __half* s, size_t K, int kc, size_t row0, size_t n, float* out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t r = row0 + i / K, c = i % K;
+    if (kc) {
+        const size_t R = kUnitQ / kc, nch = K / kc;
+        const size_t u = (r / R) * nch + c / kc, rr = r % R, kk = c % kc;
+        const unsigned char* ub = (const unsigned char*)w + u * kUnitBytes;
+        out[i] = __fmul_rn((float)((const int8_t*)ub)[rr * kc + kk], __half2float(((const __half*)(ub + kUnitQ))[rr * (kc / 32) + kk / 32]));
+    } else {
+        out[i] = __fmul_rn((float)((const int8_t*)w)[r * K + c], __half2float(s[(r * K + c) >> 5]));
+    }
+}
+cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st) {
+    const size_t n = n_rows * (size_t)K;
+    q8_dequant_rows<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w, s, (size_t)K, kc, row0, n, out);
     return cudaGetLastError();
 }
 

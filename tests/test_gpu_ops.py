@@ -117,19 +117,38 @@ def test_synthetic_generator_bit_exact(torch_cuda, lib):
         assert (g.view(npdt if dt == 2 else np.uint32) == (ref if dt == 2 else ref.view(np.uint32))).all()
 
 
+def gemv_q8(torch, lib, q, s, n, k, xd, path):
+    """path 0: packed layout + streaming kernel where the shape packs (else planes); 1: planes + plain-load kernel;
+    2: packed layout read by the plain-load kernel."""
+    y = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+    nbytes = lib.lum_q8_0_packed_bytes(n, k)
+    if path != 1 and nbytes:
+        packed = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        ck(lib, lib.lum_op_q8_0_pack(q.data_ptr(), s.data_ptr(), n, k, packed.data_ptr(), None))
+        ck(lib, lib.lum_op_gemv_q8_0_packed(packed.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), 1 if path == 2 else 0, None))
+    else:
+        ck(lib, lib.lum_op_gemv_q8_0(q.data_ptr(), s.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), 0, None))
+    torch.cuda.synchronize()
+    return y
+
+
 KAT = [
-    # (n, k, mode, path)  path: 0 = let the library choose (streaming kernel where it applies), 1 = direct kernel
+    # (n, k, mode, path)
     (1, 32, "ones", 0),            # minimal: one block of ones against ones -> 32.0
     (4, 512, "ones", 0),
     (8, 4096, "integers", 0),      # exact-integer weights and activations: exact result
     (8, 4096, "integers", 1),
     (64, 4096, "random", 0),
     (64, 4096, "random", 1),
+    (64, 4096, "random", 2),
     (148 * 4 + 12, 4096, "random", 0),   # rows not a multiple of (CTAs x tile)
     (24, 14336, "random", 0),      # down-projection K: seven 2048-wide chunks per row
     (24, 14336, "random", 1),
-    (40, 1024, "random", 0),
-    (36, 2560, "random", 0),       # K = 5 x 512
+    (24, 14336, "random", 2),
+    (64, 512, "random", 0),        # KC = 512: 32 rows per stage-unit, half-warp rows
+    (48, 1024, "random", 0),
+    (40, 1024, "random", 0),       # rows not a multiple of the unit: planes + plain-load kernel
+    (64, 2560, "random", 0),       # K = 5 x 512
     (7, 96, "random", 0),          # K below any tile: direct kernel
     (6152, 4096, "random", 0),     # q,k,v-sized: more units than CTAs, uneven split
 ]
@@ -148,10 +167,7 @@ def test_gemv_q8_known_answers(torch_cuda, lib, n, k, mode, path):
         x = rng.normal(0, 1, k).astype(np.float32)
     q, s = upload_q8(torch, lib, blocks, n, k)
     xd = torch.from_numpy(x).cuda()
-    y = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
-    ck(lib, lib.lum_op_gemv_q8_0(q.data_ptr(), s.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), path, None))
-    torch.cuda.synchronize()
-    got = y.cpu().numpy()
+    got = gemv_q8(torch, lib, q, s, n, k, xd, path).cpu().numpy()
     want = oracle_matvec_q8(blocks, n, k, x)
     if mode == "ones":
         assert (got == float(k)).all() and (want == float(k)).all()
@@ -170,17 +186,16 @@ def test_gemv_q8_streaming_equals_direct_on_lm_head_rows(torch_cuda, lib):
     torch = torch_cuda
     orc = load()
     n, k, seed, tid = 128256, 4096, 5, 3
-    q = torch.empty(n * k, dtype=torch.int8, device="cuda")
-    s = torch.empty(n * k // 32, dtype=torch.float16, device="cuda")
-    ck(lib, lib.lum_op_synth_q8_0(seed, tid, n * k, q.data_ptr(), s.data_ptr(), None))
+    packed = torch.empty(lib.lum_q8_0_packed_bytes(n, k), dtype=torch.uint8, device="cuda")
+    ck(lib, lib.lum_op_synth_q8_0_packed(seed, tid, n, k, packed.data_ptr(), None))
     rng = np.random.default_rng(0)
     x1 = rng.normal(0, 1, k).astype(np.float32)
     x2 = rng.normal(0, 1, k).astype(np.float32)
     ys = []
-    for xv, path in ((x1, 0), (x1, 1), (x2, 0), (x1 + x2, 0)):
+    for xv, direct in ((x1, 0), (x1, 1), (x2, 0), (x1 + x2, 0)):
         xd = torch.from_numpy(xv).cuda()
         y = torch.empty(n, dtype=torch.float32, device="cuda")
-        ck(lib, lib.lum_op_gemv_q8_0(q.data_ptr(), s.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), path, None))
+        ck(lib, lib.lum_op_gemv_q8_0_packed(packed.data_ptr(), n, k, xd.data_ptr(), y.data_ptr(), direct, None))
         torch.cuda.synchronize()
         ys.append(y.cpu().numpy().astype(np.float64))
     scale = np.abs(ys[0]).max()
@@ -214,3 +229,5 @@ def test_bad_arguments_return_errors(lib):
     assert lib.lum_op_gemv_q8_0(None, None, 4, 32, None, None, 0, None) < 0
     assert b"bad arguments" in lib.lum_last_error(None)
     assert lib.lum_op_q8_0_dequant(None, None, 31, None, None) < 0
+    assert lib.lum_q8_0_packed_bytes(40, 1024) == 0 and lib.lum_q8_0_packed_bytes(48, 1024) == 48 * 1024 * 34 // 32
+    assert lib.lum_q8_0_packed_bytes(8, 96) == 0
