@@ -47,6 +47,8 @@ typedef struct lum_config {
     int32_t use_graph;    /* 1: replay one captured CUDA graph per token (default); 0: plain launches */
     int32_t use_pdl;      /* 1: programmatic dependent launch between kernels (default); 0: off */
     int32_t attn_splits;  /* CTAs per KV head in decode attention; 0 = choose from the SM count */
+    int32_t use_mega;     /* 1: run whole tokens in one persistent cooperative kernel when the model allows (default);
+                             0: one kernel per operation (CUDA graph / plain launches as chosen above) */
 } lum_config;
 
 void lum_config_default(lum_config* cfg);
@@ -141,7 +143,8 @@ int32_t lum_synchronize(lum_rt* rt);
  * runtime's stream (state is restored afterwards); returns mean microseconds per step and a
  * display string such as "1.30 ms/token". */
 int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec_per_step, char* display, size_t display_len);
-/* Number of kernel launches one decode step issues (graph nodes when captured). */
+/* Number of kernel launches one decode step issues (graph nodes when captured; 1 for the persistent kernel,
+ * which also takes any number of steps in that one launch). */
 int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n);
 /* CUDA stream the runtime launches on (a cudaStream_t), for callers that time with their own events. */
 void* lum_stream(lum_rt* rt);

@@ -1,0 +1,302 @@
+// Device-side body of single-token attention, shared by the one-op kernel (lum_attn.cu) and the whole-token
+// persistent kernel (lum_mega.cu).  See lum_attn.cu for what it computes and which reference code it follows.
+#pragma once
+#include "lum_kernels.cuh"
+
+namespace lum {
+
+
+
+template <bool BF16>
+__device__ __forceinline__ void load16(const void* base, size_t elem_off, float* out) {
+    if (BF16) {
+        const uint4* p = (const uint4*)((const uint16_t*)base + elem_off);
+        const uint4 a = p[0], b = p[1];
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else {
+        const float4* p = (const float4*)((const float*)base + elem_off);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 v = p[i];
+            out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+        }
+    }
+}
+
+__device__ __forceinline__ float gain_at(const void* g, int kind, int i) {
+    return kind == WK_BF16 ? bf16_bits_to_f32(((const uint16_t*)g)[i]) : ((const float*)g)[i];
+}
+
+// cos/sin of the rotation for pair index i at position pos.
+__device__ __forceinline__ void rope_cs(const AttnArgs& a, int i, int pos, float* cs, float* sn) {
+    if (a.rope_style == 0) {
+        // the graph's chain, constant by constant: f = 2i * (1/d); inv = 1/exp2((f * ln theta) * log2 e);
+        // emb = pos * inv; sin(emb); cos as sin(-emb + pi/2)
+        const float f = (float)(2 * i) * a.c_inv_d;
+        const float inv = 1.0f / exp2f((f * a.c_ln_theta) * a.c_log2e);
+        const float emb = (float)pos * inv;
+        *sn = sinf(emb);
+        *cs = sinf(emb * -1.0f + a.c_half_pi);
+    } else {
+        const float freq = powf(a.theta, -((float)(2 * i)) / (float)a.hd);
+        const float ang = (float)pos * freq;
+        *sn = sinf(ang);
+        *cs = cosf(ang);
+    }
+}
+
+// One (kv head, split) of cached rows per CTA; all G <= GM query heads that share the KV head together.
+//
+// Phase A (whole CTA): this step's q heads of the group — and, in the CTA that owns the last split, the
+// step's own k and v — are staged in shared memory, RMS-normalised per head if the model asks for it,
+// rotated, and (k, v) rounded to the cache type and appended to the cache.
+// Phase B: one warp per cached row and trip; lane i holds dims [i*DPL, (i+1)*DPL) of every head's q and
+// running output, so a thread needs only 2 * G * DPL registers for them and the kernel fits beside the
+// streaming GEMV's register budget in the persistent kernel.
+// Loops stay rolled where they can: the code runs once per CTA, so its size in instruction-cache lines is latency.
+constexpr int kAttnThreads = 512;
+constexpr int kAttnWarps = kAttnThreads / 32;
+
+// bytes of shared memory the body needs for G query heads per KV head
+__host__ __device__ inline size_t attn_smem_bytes(int HD, int G) {
+    return (size_t)(9 * HD + HD + 2 * kAttnWarps * 8 + 4) * 4 + (size_t)kAttnWarps * G * HD * 4;
+}
+
+template <bool BF16, int DPL>
+__device__ __forceinline__ void load_dpl(const void* base, size_t elem_off, float* out) {
+    if (BF16) {
+        if (DPL == 4) {
+            const uint2 r = *(const uint2*)((const uint16_t*)base + elem_off);
+            out[0] = __uint_as_float(r.x << 16); out[1] = __uint_as_float(r.x & 0xffff0000u);
+            out[2] = __uint_as_float(r.y << 16); out[3] = __uint_as_float(r.y & 0xffff0000u);
+        } else {
+            const uint32_t r = *(const uint32_t*)((const uint16_t*)base + elem_off);
+            out[0] = __uint_as_float(r << 16); out[1] = __uint_as_float(r & 0xffff0000u);
+        }
+    } else {
+        if (DPL == 4) {
+            const float4 r = *(const float4*)((const float*)base + elem_off);
+            out[0] = r.x; out[1] = r.y; out[2] = r.z; out[3] = r.w;
+        } else {
+            const float2 r = *(const float2*)((const float*)base + elem_off);
+            out[0] = r.x; out[1] = r.y;
+        }
+    }
+}
+
+// Runs on exactly kAttnThreads threads (tid 0..511) that synchronise on named barrier `bar_id`.
+// p = position of the token being processed (rows [.., p) are cached, row p is this step's own).
+// smem: attn_smem_bytes(HD, G) bytes, 16-byte aligned.
+template <int HD, int GM, bool BF16>
+__device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned char* smem, int kvh, int split, int p, int tid, int bar_id) {
+    constexpr int DPL = HD / 32;            // dims per lane
+    constexpr int NW = kAttnWarps;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int G = a.n_q / a.n_kv;
+    auto sync = [bar_id] { named_sync(bar_id, kAttnThreads); };
+    float (*s_q)[HD] = (float (*)[HD])smem;                 // [9][HD]: rotated q heads; row G = this step's k
+    float* s_v = (float*)smem + 9 * HD;                     // [HD]
+    float (*s_m)[8] = (float (*)[8])(s_v + HD);             // [NW][8]
+    float (*s_l)[8] = (float (*)[8])(s_v + HD + NW * 8);    // [NW][8]
+    int& s_last = *(int*)(s_v + HD + 2 * NW * 8);
+    float* s_o = s_v + HD + 2 * NW * 8 + 4;                 // [NW][G][HD]
+    const int d0 = lane * DPL;
+    const size_t row_elems = (size_t)a.n_kv * HD;
+
+    // rows [lo, p) come from the cache; row p is this step's own
+    const int lo = (a.window > 0 && p + 1 > a.window) ? p + 1 - a.window : 0;
+    const int n_cached = p - lo;
+    const int per = (n_cached + a.n_splits - 1) / a.n_splits;
+    const int r0 = lo + split * per;
+    const int r1 = min(p, r0 + per);
+    const int nc = max(0, r1 - r0);                    // cached rows of this CTA
+    const bool owns_new = split == a.n_splits - 1;
+    const int n_rows = nc + (owns_new ? 1 : 0);
+    const float scale = 1.0f / sqrtf((float)HD);
+
+    // ---- phase A
+    const int nheads = G + (owns_new ? 1 : 0);
+    for (int idx = tid; idx < nheads * HD; idx += kAttnThreads) {
+        const int h = idx / HD, e = idx - h * HD;
+        s_q[h][e] = h < G ? a.q[((size_t)kvh * G + h) * HD + e] : a.k_new[(size_t)kvh * HD + e];
+    }
+    if (owns_new)
+        for (int e = tid; e < HD; e += kAttnThreads) s_v[e] = a.v_new[(size_t)kvh * HD + e];
+    sync();
+    if (a.q_gain || a.k_gain) {
+        // per-head RMSNorm: x * 1/sqrt(mean(x^2) + eps) * g   (one warp per head)
+#pragma unroll 1
+        for (int h = warp; h < nheads; h += NW) {
+            const void* gain = h < G ? a.q_gain : a.k_gain;
+            if (!gain) continue;
+            float ss = 0.0f;
+            for (int e = lane; e < HD; e += 32) ss = fmaf(s_q[h][e], s_q[h][e], ss);
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss * (1.0f / (float)HD) + a.qk_eps);
+            for (int e = lane; e < HD; e += 32) s_q[h][e] = (inv * s_q[h][e]) * gain_at(gain, a.gain_kind, e);
+        }
+        sync();
+    }
+#pragma unroll 1
+    for (int idx = tid; idx < nheads * (HD / 2); idx += kAttnThreads) {
+        const int h = idx / (HD / 2), i = idx - h * (HD / 2);
+        float cs, sn;
+        rope_cs(a, i, p, &cs, &sn);
+        const int e0 = a.rope_style == 0 ? 2 * i : i, e1 = a.rope_style == 0 ? 2 * i + 1 : i + HD / 2;
+        const float x0 = s_q[h][e0], x1 = s_q[h][e1];
+        // separately rounded products and sums, as the graph's Mul / Add nodes produce them
+        if (a.rope_style == 0) {
+            s_q[h][e0] = __fadd_rn(__fmul_rn(x0, cs), __fmul_rn(__fmul_rn(x1, sn), -1.0f));
+            s_q[h][e1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+        } else {
+            s_q[h][e0] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+            s_q[h][e1] = __fadd_rn(__fmul_rn(x1, cs), __fmul_rn(x0, sn));
+        }
+    }
+    sync();
+    if (owns_new) {
+        // append this step's row to the cache; keep the rounded values for our own use
+        const size_t off = (size_t)p * row_elems + (size_t)kvh * HD;
+        for (int e = tid; e < HD; e += kAttnThreads) {
+            if (BF16) {
+                const __nv_bfloat16 kb = __float2bfloat16_rn(s_q[G][e]), vb = __float2bfloat16_rn(s_v[e]);
+                ((__nv_bfloat16*)a.k_cache)[off + e] = kb;
+                ((__nv_bfloat16*)a.v_cache)[off + e] = vb;
+                s_q[G][e] = __bfloat162float(kb);
+                s_v[e] = __bfloat162float(vb);
+            } else {
+                ((float*)a.k_cache)[off + e] = s_q[G][e];
+                ((float*)a.v_cache)[off + e] = s_v[e];
+            }
+        }
+        sync();
+    }
+
+    // ---- phase B
+    float q[GM][DPL], o[GM][DPL], m[GM], l[GM];
+#pragma unroll
+    for (int g = 0; g < GM; g++) {
+        m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) { q[g][i] = g < G ? s_q[g][d0 + i] : 0.0f; o[g][i] = 0.0f; }
+    }
+    // rows of this CTA: cached rows r0 .. r1-1, then (last split only) the step's own row from shared memory
+#pragma unroll 1
+    for (int j = warp; j < n_rows; j += NW) {
+        float kr[DPL], vr[DPL];
+        if (j < nc) {
+            const size_t off = (size_t)(r0 + j) * row_elems + (size_t)kvh * HD + d0;
+            load_dpl<BF16, DPL>(a.k_cache, off, kr);
+            load_dpl<BF16, DPL>(a.v_cache, off, vr);
+        } else {
+#pragma unroll
+            for (int i = 0; i < DPL; i++) { kr[i] = s_q[G][d0 + i]; vr[i] = s_v[d0 + i]; }
+        }
+#pragma unroll
+        for (int g = 0; g < GM; g++) {
+            if (g < G) {
+                float d = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) d = fmaf(q[g][i], kr[i], d);
+                d = warp_sum(d);
+                const float logit = d * scale;
+                const float mn = fmaxf(m[g], logit);
+                const float corr = (m[g] == -INFINITY) ? 0.0f : expf(m[g] - mn);
+                const float w = expf(logit - mn);
+                l[g] = l[g] * corr + w;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) o[g][i] = fmaf(w, vr[i], o[g][i] * corr);
+                m[g] = mn;
+            }
+        }
+    }
+    // every warp publishes its running state; then the CTA merges them
+#pragma unroll
+    for (int g = 0; g < GM; g++) {
+        if (g < G) {
+            if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+#pragma unroll
+            for (int i = 0; i < DPL; i++) s_o[((size_t)warp * G + g) * HD + d0 + i] = o[g][i];
+        }
+    }
+    sync();
+#pragma unroll 1
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, e = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; w++) M = fmaxf(M, s_m[w][g]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) {
+            const float c = (s_m[w][g] == -INFINITY) ? 0.0f : expf(s_m[w][g] - M);
+            L = fmaf(s_l[w][g], c, L);
+            O = fmaf(s_o[((size_t)w * G + g) * HD + e], c, O);
+        }
+        if (a.n_splits == 1) {
+            a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);      // no other split to merge with
+        } else {
+            float* dst = a.part + (((size_t)kvh * a.n_splits + split) * G + g) * (HD + 2);
+            dst[e] = O;
+            if (e == 0) { dst[HD] = M; dst[HD + 1] = L; }
+        }
+    }
+    if (a.n_splits == 1) return;
+
+    // last CTA of this KV head merges the splits
+    __threadfence();
+    sync();
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(&a.counters[kvh], 1u);
+        s_last = (t == (unsigned int)a.n_splits - 1u) ? 1 : 0;
+    }
+    sync();
+    if (!s_last) return;
+    __threadfence();
+    // The partials were written by other CTAs: read them through L2 (ld.cg), in batches of independent
+    // loads so the round trips overlap instead of queueing behind one another.
+    constexpr int kBatch = 8;
+#pragma unroll 1
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, e = idx - g * HD;
+        const float* src = a.part + ((size_t)kvh * a.n_splits * G + g) * (HD + 2);
+        const size_t sstride = (size_t)G * (HD + 2);
+        float M = -INFINITY;
+#pragma unroll 1
+        for (int s0 = 0; s0 < a.n_splits; s0 += kBatch) {
+            float mv[kBatch];
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) mv[j] = (s0 + j < a.n_splits) ? __ldcg(src + (size_t)(s0 + j) * sstride + HD) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) M = fmaxf(M, mv[j]);
+        }
+        float L = 0.0f, O = 0.0f;
+#pragma unroll 1
+        for (int s0 = 0; s0 < a.n_splits; s0 += kBatch) {
+            float mv[kBatch], lv[kBatch], ov[kBatch];
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) {
+                const bool in = s0 + j < a.n_splits;
+                const float* q2 = src + (size_t)(in ? s0 + j : 0) * sstride;
+                mv[j] = in ? __ldcg(q2 + HD) : -INFINITY;
+                lv[j] = __ldcg(q2 + HD + 1);
+                ov[j] = __ldcg(q2 + e);
+            }
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) {
+                const float c = (mv[j] == -INFINITY) ? 0.0f : expf(mv[j] - M);
+                L = fmaf(lv[j], c, L);
+                O = fmaf(ov[j], c, O);
+            }
+        }
+        a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);
+    }
+    if (tid == 0) a.counters[kvh] = 0u;
+}
+
+}  // namespace lum

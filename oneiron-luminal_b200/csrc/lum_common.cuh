@@ -19,6 +19,7 @@ enum : uint32_t {
     LUM_ST_WAIT_DRAIN = 1u << 2,  // exit path gave up waiting for copies in flight
     LUM_ST_BAD_TOKEN = 1u << 3,   // token id outside the vocabulary
     LUM_ST_BAD_POS = 1u << 4,     // position outside the cache capacity
+    LUM_ST_WAIT_GRID = 1u << 5,   // a grid-wide barrier of the persistent kernel was not reached by every CTA in time
 };
 
 // Budget for any single wait, in SM clock cycles (about two seconds at 2 GHz).  The SM-local cycle
@@ -71,6 +72,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) return false;
+    }
+}
+
+// Same, but gives up at once when *abort becomes non-zero (another thread of the CTA already failed).
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile int* abort) {
+#pragma unroll 1
+    for (int i = 0; i < 32; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort || clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) return false;
     }
 }
 

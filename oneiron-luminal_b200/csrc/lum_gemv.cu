@@ -36,123 +36,41 @@
 // differ by f32 rounding only.)
 #include <cstdlib>
 
-#include "lum_kernels.cuh"
+#include "lum_gemv_dev.cuh"
 
 namespace lum {
 
-constexpr int kConsumers = 512;          // 16 consumer warps: enough independent warps to cover dp4a / shuffle / LDS latency
-constexpr int kGemvThreads = 544;        // + 1 producer warp
-constexpr int kUnitBytes = 16384;        // int8 bytes per stage-unit
-constexpr int kStageBytes = kUnitBytes + kUnitBytes / 16;   // + binary16 scales (2 B per 32 quants)
-constexpr int kBarBytes = 512;           // 2 x 12 mbarriers, then 64 words of reduction scratch
-
-#ifdef LUM_PROBE
-// Build-time probe (never in the shipped library): %globaltimer stamps of a few points in CTA 0.
-__device__ unsigned long long g_probe[32];
-#define PROBE(i) do { if (blockIdx.x == 0) g_probe[i] = globaltimer_ns(); } while (0)
-extern "C" int lum_probe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_probe, sizeof(g_probe)); }
-#else
-#define PROBE(i) do { } while (0)
-#endif
-
-// ------------------------------------------------------------------------------ shared pieces
-
-__device__ __forceinline__ float load_gain(const void* g, int kind, int i) {
-    return kind == WK_BF16 ? bf16_bits_to_f32(((const uint16_t*)g)[i]) : ((const float*)g)[i];
-}
-
-// Sum of squares over the block's `nthreads` threads (a multiple of 32, <= 256); result in all threads.
-__device__ __forceinline__ float block_sum(float v, float* scratch, int tid, int nthreads, int bar_id) {
-    v = warp_sum(v);
-    if ((tid & 31) == 0) scratch[tid >> 5] = v;
+// The greedy sampler's last step, run by the last CTA to arrive (one-op kernels) : fold the per-CTA
+// maxima, log the token and advance the decode state.
+__device__ __forceinline__ void argmax_finish(const GemvArgs& a, ArgBest mine, int tid, int nthreads, int bar_id) {
+    __shared__ int s_last;
+    if (tid == 0) {
+        a.part_val[blockIdx.x] = mine.v;
+        a.part_idx[blockIdx.x] = mine.i;
+        __threadfence();
+        const unsigned int ticket = atomicAdd(a.counter, 1u);
+        s_last = (ticket == gridDim.x - 1) ? 1 : 0;
+    }
     named_sync(bar_id, nthreads);
-    float t = 0.0f;
-    const int nw = nthreads >> 5;
-    for (int w = 0; w < nw; w++) t += scratch[w];
-    named_sync(bar_id, nthreads);
-    return t;
-}
-
-// SiLU gate as the graph spells it: g * 1/(exp2(-g * 1.442695) + 1), times u.
-__device__ __forceinline__ float swiglu(float g, float u) {
-    const float sig = 1.0f / (exp2f((g * -1.0f) * 1.442695f) + 1.0f);
-    return (g * sig) * u;
-}
-
-// Epilogue over the CTA's finished rows.  vals[i] is logical row row0 + i (for SwiGLU, gate sums in
-// vals[0..n) and up sums in vals[n..2n)).  Runs on `nthreads` threads with thread id `tid`.
-__device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, const float* vals, int row0, int n, int tid, int nthreads, float* scratch,
-                              int bar_id) {
-    if (a.epi == EPI_STORE) {
-        for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = vals[i];
-    } else if (a.epi == EPI_RESID) {
-        for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = a.resid[row0 + i] + vals[i];
-    } else if (a.epi == EPI_SWIGLU) {
-        for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = swiglu(vals[i], vals[n + i]);
-    } else {  // EPI_ARGMAX
-        float best = -INFINITY;
-        int bi = -1;
-        for (int i = tid; i < n; i += nthreads) {
-            const float v = vals[i];
-            a.y[row0 + i] = v;
-            if (bi < 0 || v > best || (v == best && row0 + i > bi)) { best = v; bi = row0 + i; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) { best = ov; bi = oi; }
-        }
-        int* iscratch = (int*)(scratch + 32);
-        if ((tid & 31) == 0) { scratch[tid >> 5] = best; iscratch[tid >> 5] = bi; }
-        named_sync(bar_id, nthreads);
-        __shared__ int s_last;
+    if (s_last && tid < 32) {
+        __threadfence();
+        const int fi = argmax_final(a.part_val, a.part_idx, (int)gridDim.x, tid);
         if (tid == 0) {
-            for (int w = 1; w < (nthreads >> 5); w++) {
-                const float ov = scratch[w];
-                const int oi = iscratch[w];
-                if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) { best = ov; bi = oi; }
+            DecodeState* st = a.state;
+            if (st) {
+                const int step = st->step;
+                st->last_tok = fi;
+                if (st->log && a.tokens_out && step < st->max_steps) { a.tokens_out[step] = fi; st->step = step + 1; }
+                if (a.advance) { st->tok = fi; st->pos = st->pos + 1; }
             }
-            a.part_val[blockIdx.x] = best;
-            a.part_idx[blockIdx.x] = bi;
-            __threadfence();
-            const unsigned int ticket = atomicAdd(a.counter, 1u);
-            s_last = (ticket == gridDim.x - 1) ? 1 : 0;
-        }
-        named_sync(bar_id, nthreads);
-        if (s_last && tid < 32) {
-            __threadfence();
-            float fb = -INFINITY;
-            int fi = -1;
-            for (int c = tid; c < (int)gridDim.x; c += 32) {
-                const float ov = ((volatile float*)a.part_val)[c];
-                const int oi = ((volatile int*)a.part_idx)[c];
-                if (oi >= 0 && (fi < 0 || ov > fb || (ov == fb && oi > fi))) { fb = ov; fi = oi; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, fb, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, fi, o);
-                if (oi >= 0 && (fi < 0 || ov > fb || (ov == fb && oi > fi))) { fb = ov; fi = oi; }
-            }
-            if (tid == 0) {
-                DecodeState* st = a.state;
-                if (st) {
-                    const int step = st->step;
-                    st->last_tok = fi;
-                    if (st->log && a.tokens_out && step < st->max_steps) { a.tokens_out[step] = fi; st->step = step + 1; }
-                    if (a.advance) { st->tok = fi; st->pos = st->pos + 1; }
-                }
-                *a.counter = 0u;
-            }
+            *a.counter = 0u;
         }
     }
 }
 
-// Prologue: bring x into shared memory (optionally RMS-normalised and scaled by the gains).
-// `permute`: store float4 j of 16-element slot t at float4 index j * (K/16) + t, so that threads
-// with consecutive slots read consecutive 16-byte words (no bank conflicts in the streaming kernel).
-__device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, bool permute, int tid, int nthreads, float* scratch, int bar_id) {
+// Prologue of the plain-load kernel: bring x into shared memory as f32 (optionally RMS-normalised and
+// scaled by the gains).
+__device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, int tid, int nthreads, float* scratch, int bar_id) {
     const int K = a.K;
     float inv = 1.0f;
     if (a.gain) {
@@ -162,7 +80,6 @@ __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, bool p
         const float mean = ss * (1.0f / (float)K);
         inv = 1.0f / sqrtf(mean + a.eps);
     }
-    const int slots = K >> 4;
     for (int k = tid; k < K; k += nthreads) {
         float v = a.x[k];
         if (a.x_add) {
@@ -170,12 +87,7 @@ __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, bool p
             if (a.x_out && blockIdx.x == 0) a.x_out[k] = v;
         }
         if (a.gain) v = (inv * v) * load_gain(a.gain, a.gain_kind, k);
-        int dst = k;
-        if (permute) {
-            const int t = k >> 4, j = (k >> 2) & 3, e = k & 3;
-            dst = ((j * slots + t) << 2) + e;
-        }
-        xs[dst] = v;
+        xs[k] = v;
     }
     named_sync(bar_id, nthreads);
 }
@@ -188,275 +100,34 @@ __device__ __forceinline__ float dot4_s8(uint32_t w, float4 x, float acc) {
     return acc;
 }
 
-// Prologue of the streaming kernel: x (optionally x + x_add, RMS-normalised, times the gains) is split
-// per 32-block into three int8 levels and one f32 scale (see the header comment).  One pass over
-// global memory; runs on the 256 consumer threads.  8 consecutive threads own one block.
-__device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, int8_t* xq, float* xsc, int tid, float* scratch) {
-    // Code size matters here: a kernel whose straight-line code runs once per CTA pays for every
-    // instruction-cache line it touches, so the loops below stay rolled.
-    const int K = a.K, n4 = K >> 2;
-    const float4* x4 = (const float4*)a.x;
-    const float4* xa4 = (const float4*)a.x_add;
-    float inv = 1.0f;
-    if (a.gain) {
-        float ss = 0.0f;
-#pragma unroll 4
-        for (int f4 = tid; f4 < n4; f4 += kConsumers) {
-            float4 t = x4[f4];
-            if (xa4) { const float4 u = xa4[f4]; t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
-            ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
-        }
-        ss = block_sum(ss, scratch, tid, kConsumers, 1);
-        const float mean = ss * (1.0f / (float)K);
-        inv = 1.0f / sqrtf(mean + a.eps);
-    }
-    // second pass re-reads x (an L1/L2 hit); all 256 threads run the same trip count so the 8-lane
-    // shuffles below always have their partners (K is a multiple of 32: a block never straddles the end)
-    const int trips = (n4 + kConsumers - 1) / kConsumers;
-#pragma unroll 1
-    for (int it = 0; it < trips; it++) {
-        const int f4 = it * kConsumers + tid;
-        const bool in = f4 < n4;
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (in) {
-            t = x4[f4];
-            if (xa4) {
-                const float4 u = xa4[f4];
-                t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
-                if (a.x_out && blockIdx.x == 0) ((float4*)a.x_out)[f4] = t;
-            }
-        }
-        float e[4] = {t.x, t.y, t.z, t.w};
-        if (a.gain && in) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) e[j] = (inv * e[j]) * load_gain(a.gain, a.gain_kind, f4 * 4 + j);
-        }
-        float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const float s1 = amax * (1.0f / 127.0f);
-        const float i1 = amax > 0.0f ? 127.0f / amax : 0.0f;
-        const float s2 = s1 * (1.0f / 254.0f), i2 = i1 * 254.0f;
-        const float i3 = i1 * 64516.0f;
-        uint32_t p1 = 0, p2 = 0, p3 = 0;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float q1 = fminf(fmaxf(rintf(e[j] * i1), -127.0f), 127.0f);
-            const float r1 = fmaf(-s1, q1, e[j]);
-            const float q2 = fminf(fmaxf(rintf(r1 * i2), -127.0f), 127.0f);
-            const float r2 = fmaf(-s2, q2, r1);
-            const float q3 = fminf(fmaxf(rintf(r2 * i3), -127.0f), 127.0f);
-            p1 |= ((uint32_t)(int)q1 & 0xffu) << (8 * j);
-            p2 |= ((uint32_t)(int)q2 & 0xffu) << (8 * j);
-            p3 |= ((uint32_t)(int)q3 & 0xffu) << (8 * j);
-        }
-        if (in) {
-            ((uint32_t*)xq)[f4] = p1;
-            ((uint32_t*)(xq + (size_t)K))[f4] = p2;
-            ((uint32_t*)(xq + 2 * (size_t)K))[f4] = p3;
-            if ((tid & 7) == 0) xsc[f4 >> 3] = s1;
-        }
-    }
-    named_sync(1, kConsumers);
-}
-
-// ------------------------------------------------------------------------------ streaming kernel
-
-// logical unit -> first stage-unit of its row group in the packed weight stream.  `which`: 0 or 1
-// picks gate/up in SwiGLU mode.  Units of one row group (its K-chunks) are consecutive.
-__device__ __forceinline__ const unsigned char* unit_base(const GemvArgs& a, int lu, int which, int R, int nch) {
-    int row = lu * R;
-    int sg = 0;
-    if (a.epi == EPI_SWIGLU) {
-        sg = which;
-    } else {
-        while (sg < a.nseg - 1 && row >= a.seg[sg].rows) { row -= a.seg[sg].rows; sg++; }
-    }
-    return (const unsigned char*)a.seg[sg].w + (size_t)(row / R) * nch * kStageBytes;
-}
+// ------------------------------------------------------------------------------ streaming kernel (one op)
 
 __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_abort;
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int K = a.K, KC = a.KC, nch = K / KC, stages = a.stages;
-    const int R = kUnitBytes / KC;                 // rows per stage-unit
-    const bool paired = a.epi == EPI_SWIGLU;
-    const int sub = paired ? 2 : 1;                // stage-units per logical unit
-
-    int rows_total = 0;
-    if (paired) rows_total = a.seg[0].rows;
-    else for (int s = 0; s < a.nseg; s++) rows_total += a.seg[s].rows;
-    const int LU = rows_total / R;
-    const int lu0 = (int)((long long)blockIdx.x * LU / gridDim.x);
-    const int lu1 = (int)((long long)(blockIdx.x + 1) * LU / gridDim.x);
-    const int n_lu = lu1 - lu0;
-
-    // shared memory map
-    uint64_t* bars = (uint64_t*)smem;                              // full[stages], empty[stages]
-    float* scratch = (float*)(smem + 256);                          // 64 words of reduction scratch
-    int8_t* xq = (int8_t*)(smem + kBarBytes);                       // 3 planes of K int8: the three levels of x
-    float* xsc = (float*)(xq + 3 * (size_t)K);                      // K/32 block scales of x
-    float* red = xsc + (K >> 5);                                    // max_units * 32 floats
-    float* vals = red + (size_t)a.max_units * 32;                   // max_units * R floats
-    unsigned char* stage0 = (unsigned char*)(((uintptr_t)(vals + (size_t)a.max_units * R) + 127) & ~(uintptr_t)127);
-    __shared__ int s_abort;
-
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8u * stages;
+    GemvSmem g;
+    gemv_carve(smem, a.K, a.stages, &s_abort, &g);
     if (tid == 0) {
-        PROBE(0);
-        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, kConsumers / 32); }
         s_abort = 0;
-        mbar_fence_init();
+        gemv_init_barriers(g);
     }
     __syncthreads();
     if (a.use_pdl) pdl_launch_dependents();
+    const GemvShare sh = gemv_share(a, (int)blockIdx.x, (int)gridDim.x);
 
     if (warp == kConsumers / 32) {
-        // ------------------------------------------------ producer warp: stream the weights
-        int stage = 0;
-        uint32_t phase = 0;
-        int issued = 0;
-        bool ok = true;
-        for (int lu = lu0; lu < lu1 && ok; lu++) {
-            for (int w = 0; w < sub && ok; w++) {
-                const unsigned char* ub = unit_base(a, lu, w, R, nch);
-                for (int c = 0; c < nch; c++) {
-                    if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u) || *(volatile int*)&s_abort) {
-                        if (lane == 0) { atomicOr(a.status, LUM_ST_WAIT_EMPTY); s_abort = 1; }
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t fb = full0 + 8u * stage;
-                    // one stage = one contiguous 17 KiB piece of the packed stream = one bulk copy
-                    if (lane == 0) {
-                        mbar_arrive_expect_tx(fb, (uint32_t)kStageBytes);
-                        bulk_g2s(smem_u32(stage0 + (size_t)stage * kStageBytes), ub + (size_t)c * kStageBytes, (uint32_t)kStageBytes, fb);
-                    }
-                    issued++;
-                    if (++stage == stages) { stage = 0; phase ^= 1u; }
-                }
-            }
-        }
-        if (lane == 0) PROBE(5);
-        // Exit path: never leave the CTA while a copy into its shared memory may still be in flight.
-        // Every fill that was armed completes its `full` phase; wait (bounded) for the newest ones.
-        if (!ok) {
-            int back = issued < stages ? issued : stages;
-            int s = stage;
-            uint32_t ph = phase;
-            for (int i = 0; i < back; i++) {
-                if (s == 0) { s = stages; ph ^= 1u; }
-                s--;
-                if (!mbar_wait(full0 + 8u * s, ph)) { if (lane == 0) atomicOr(a.status, LUM_ST_WAIT_DRAIN); break; }
-            }
-        }
+        // producer warp: the weight stream does not depend on the previous kernel, so it starts at once
+        if (!gemv_produce(a, sh, g, 0, lane, a.status)) gemv_producer_drain(g, sh.fills, lane, a.status);
         return;
     }
-
-    // ---------------------------------------------------- consumer warps
     if (a.use_pdl) pdl_grid_wait();
-    if (tid == 0) PROBE(1);
-    gemv_quantize_x(a, xq, xsc, tid, scratch);
-    if (tid == 0) PROBE(2);
-
-    const int TPB = KC >> 5;                   // threads across one row chunk: one 32-block each
-    const int row = tid / TPB;                 // this thread's row of the unit (512 threads = R rows x TPB blocks)
-    const int ks = tid - row * TPB;            // block slot inside the chunk
-    const int WPS = TPB >= 32 ? (TPB >> 5) : 1;
-    uint4 xa[3][2];
-    float sx = 0.0f;
-    auto load_xblock = [&](int c) {
-        const int blk = c * TPB + ks;
-#pragma unroll
-        for (int l = 0; l < 3; l++) {
-            const uint4* p = (const uint4*)(xq + (size_t)l * K + ((size_t)blk << 5));
-            xa[l][0] = p[0];
-            xa[l][1] = p[1];
-        }
-        sx = xsc[blk];
-    };
-    if (nch == 1) load_xblock(0);
-
-    int stage = 0;
-    uint32_t phase = 0;
-    const int n_units = n_lu * sub;            // stage-units of this CTA, in the producer's order
-    // Units are finished four at a time so that one transposed butterfly (6 shuffles) reduces four row sums.
-#pragma unroll 1
-    for (int u0 = 0; u0 < n_units; u0 += 4) {
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int uu = 0; uu < 4; uu++) {
-            if (u0 + uu < n_units) {
-#pragma unroll 1
-                for (int c = 0; c < nch; c++) {
-                    if (nch != 1) load_xblock(c);
-                    if (!*(volatile int*)&s_abort && !mbar_wait(full0 + 8u * stage, phase)) {
-                        atomicOr(a.status, LUM_ST_WAIT_FULL);
-                        s_abort = 1;
-                    }
-                    const unsigned char* sq = stage0 + (size_t)stage * kStageBytes;
-                    const uint4* wp = (const uint4*)(sq + (size_t)row * KC + ((size_t)ks << 5));
-                    const uint4 w0 = wp[0], w1 = wp[1];
-                    const float dw = __half2float(((const __half*)(sq + kUnitBytes))[row * TPB + ks]);
-                    int i1 = 0, i2 = 0, i3 = 0;
-#define LUM_DP(wv, j, f)                                   \
-    i1 = __dp4a((int)(wv), (int)xa[0][j].f, i1);           \
-    i2 = __dp4a((int)(wv), (int)xa[1][j].f, i2);           \
-    i3 = __dp4a((int)(wv), (int)xa[2][j].f, i3);
-                    LUM_DP(w0.x, 0, x) LUM_DP(w0.y, 0, y) LUM_DP(w0.z, 0, z) LUM_DP(w0.w, 0, w)
-                    LUM_DP(w1.x, 1, x) LUM_DP(w1.y, 1, y) LUM_DP(w1.z, 1, z) LUM_DP(w1.w, 1, w)
-#undef LUM_DP
-                    const float t = fmaf((float)i3, 1.0f / 64516.0f, fmaf((float)i2, 1.0f / 254.0f, (float)i1));
-                    acc[uu] = fmaf(t, sx * dw, acc[uu]);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(empty0 + 8u * stage);
-                    if (++stage == stages) { stage = 0; phase ^= 1u; }
-                }
-            }
-        }
-        // transposed butterfly over the lanes that share a row: afterwards one lane per unit holds its sum
-        int uidx;
-        float v;
-        if (TPB >= 32) {
-            const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
-            const float s0 = __shfl_xor_sync(0xffffffffu, h16 ? acc[0] : acc[2], 16);
-            const float s1 = __shfl_xor_sync(0xffffffffu, h16 ? acc[1] : acc[3], 16);
-            const float a0 = (h16 ? acc[2] : acc[0]) + s0, a1 = (h16 ? acc[3] : acc[1]) + s1;
-            v = (h8 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h8 ? a0 : a1, 8);
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            uidx = (h16 ? 2 : 0) + (h8 ? 1 : 0);
-            if ((lane & 7) == 0 && u0 + uidx < n_units) red[(size_t)(u0 + uidx) * 32 + row * WPS + (ks >> 5)] = v;
-        } else {
-            // 16 lanes per row (KC = 512): each half-warp is one row
-            const bool h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
-            const float s0 = __shfl_xor_sync(0xffffffffu, h8 ? acc[0] : acc[2], 8);
-            const float s1 = __shfl_xor_sync(0xffffffffu, h8 ? acc[1] : acc[3], 8);
-            const float a0 = (h8 ? acc[2] : acc[0]) + s0, a1 = (h8 ? acc[3] : acc[1]) + s1;
-            v = (h4 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h4 ? a0 : a1, 4);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            uidx = (h8 ? 2 : 0) + (h4 ? 1 : 0);
-            if ((lane & 3) == 0 && u0 + uidx < n_units) red[(size_t)(u0 + uidx) * 32 + row] = v;
-        }
-    }
-    if (tid == 0) PROBE(3);
-    named_sync(1, kConsumers);
-    // fixed-order sum of the per-warp partials -> vals
-    for (int i = tid; i < n_units * R; i += kConsumers) {
-        const int u = i / R, row = i - u * R;
-        float t = 0.0f;
-        for (int wi = 0; wi < WPS; wi++) t += red[(size_t)u * 32 + row * WPS + wi];
-        // unit u = logical unit u / sub, half u % sub; SwiGLU wants [gate rows..., up rows...]
-        const int l = u / sub, h = u - l * sub;
-        vals[(size_t)h * n_lu * R + (size_t)l * R + row] = t;
-    }
-    named_sync(1, kConsumers);
-    gemv_epilogue(a, vals, lu0 * R, n_lu * R, tid, kConsumers, scratch, 1);
-    if (tid == 0) PROBE(4);
+    XSource xs{};
+    xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
+    ArgBest best{-INFINITY, -1};
+    gemv_consume(a, xs, blockIdx.x == 0, sh, g, 0, tid, a.status, &best);
+    if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 1);
 }
 
 // ------------------------------------------------------------------------------ direct kernel
@@ -527,7 +198,7 @@ __global__ void __launch_bounds__(256) gemv_direct(const GemvArgs a) {
     float* vals = xs + ((a.K + 3) & ~3);       // 2 * max rows per CTA
 
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
-    gemv_load_x(a, xs, false, tid, 256, scratch, 1);
+    gemv_load_x(a, xs, tid, 256, scratch, 1);
 
     const int sub = paired ? 2 : 1;
     for (int i = warp; i < n * sub; i += 8) {
@@ -539,7 +210,9 @@ __global__ void __launch_bounds__(256) gemv_direct(const GemvArgs a) {
         if (lane == 0) vals[i] = v;
     }
     named_sync(1, 256);
-    gemv_epilogue(a, vals, row0, n, tid, 256, scratch, 1);
+    ArgBest best{-INFINITY, -1};
+    gemv_epilogue_rows(a, vals, row0, n, tid, 256, scratch, 1, &best);
+    if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, 256, 1);
 }
 
 // ------------------------------------------------------------------------------ host side
@@ -597,16 +270,16 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
         a.KC = pick_kc(a.K);
         const int R = kUnitBytes / a.KC;
         const int LU = rows_total / R;
-        const int sub = a.epi == EPI_SWIGLU ? 2 : 1;
         int grid = sm_count < LU ? sm_count : LU;
-        a.max_units = ((LU + grid - 1) / grid) * sub;
-        const size_t fixed = kBarBytes + (size_t)a.K * 3 + (size_t)(a.K / 32) * 4 + (size_t)a.max_units * 32 * 4 + (size_t)a.max_units * R * 4 + 128;
-        // Keep two kernels co-resident per SM (so the next one can prefetch): stay under ~110 KiB.
-        int stages = (int)((112 * 1024 - (long)fixed) / kStageBytes);
-        if (stages > 6) stages = 6;
+        const size_t fixed = gemv_fixed_smem(a.K);
+        // Two kernels co-resident per SM (so the next one can prefetch under programmatic dependent launch):
+        // stay under ~113 KiB each.  LUM_GEMV_STAGES overrides (deeper ring, no co-residency).
+        int stages = (int)((113 * 1024 - (long)fixed) / kStageBytes);
         static const int env_stages = [] { const char* e = getenv("LUM_GEMV_STAGES"); return e ? atoi(e) : 0; }();
-        if (env_stages > 0) stages = env_stages;     // tuning override: deeper ring, at the price of co-residency
-        if (stages > 12) stages = 12;
+        if (env_stages > 0) stages = env_stages;
+        const int fit = (int)((226 * 1024 - (long)fixed) / kStageBytes);
+        if (stages > fit) stages = fit;
+        if (stages > kMaxStages) stages = kMaxStages;
         if (stages < 2) stages = 2;
         a.stages = stages;
         const size_t smem = fixed + (size_t)stages * kStageBytes;

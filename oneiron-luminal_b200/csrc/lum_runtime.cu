@@ -23,6 +23,7 @@
 
 #include "../../include/lum_b200.h"
 #include "lum_kernels.cuh"
+#include "lum_mega.cuh"
 
 using namespace lum;
 
@@ -86,6 +87,16 @@ struct lum_rt {
 
     uint64_t dim_s = 1, dim_p = 0;
     std::vector<int32_t> tokens_in;
+
+    // whole-token persistent kernel
+    bool mega_ok = false;
+    MegaArgs mega{};
+    MegaLayer* mega_layers = nullptr;
+    int* forced_dev = nullptr;
+    unsigned long long* gbar = nullptr;
+    int* abort_flag = nullptr;
+    unsigned long long gbar_base = 0;
+    int use_mega = 1;
 };
 
 namespace {
@@ -144,6 +155,7 @@ void free_model(lum_rt* rt) {
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
+    rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
     rt->allocs.clear();
     rt->L.clear();
@@ -193,7 +205,13 @@ int check_status(lum_rt* rt) {
     CU(rt, cudaStreamSynchronize(rt->stream));
     if (st) {
         cudaMemsetAsync(rt->status, 0, sizeof st, rt->stream);
-        return fail(rt, LUM_E_DEVICE, "device status 0x%x (%s%s%s%s%s)", st, (st & LUM_ST_WAIT_FULL) ? "stage wait timed out; " : "",
+        if (rt->gbar) {   // an aborted persistent launch leaves its barrier count short: start over
+            cudaMemsetAsync(rt->gbar, 0, sizeof(unsigned long long), rt->stream);
+            cudaMemsetAsync(rt->abort_flag, 0, sizeof(int), rt->stream);
+            rt->gbar_base = 0;
+        }
+        return fail(rt, LUM_E_DEVICE, "device status 0x%x (%s%s%s%s%s%s)", st, (st & LUM_ST_WAIT_GRID) ? "grid barrier timed out; " : "",
+                    (st & LUM_ST_WAIT_FULL) ? "stage wait timed out; " : "",
                     (st & LUM_ST_WAIT_EMPTY) ? "producer wait timed out; " : "", (st & LUM_ST_WAIT_DRAIN) ? "drain wait timed out; " : "",
                     (st & LUM_ST_BAD_TOKEN) ? "token id out of range; " : "", (st & LUM_ST_BAD_POS) ? "position out of range; " : "");
     }
@@ -308,6 +326,90 @@ int run_step(lum_rt* rt, bool with_head) {
     return issue_step(rt, with_head, rt->cfg.use_pdl != 0, &rt->launches_full);
 }
 
+// n tokens in one go.  forced: host token ids (prompt processing: sample only after the last) or null (feed
+// every sample back in).  The persistent kernel takes them all in one launch; otherwise one step per token.
+int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
+    if (n <= 0) return 0;
+    if (rt->mega_ok && rt->use_mega) {
+        MegaArgs a = rt->mega;
+        a.n_tokens = n;
+        a.head_every_token = forced ? 0 : 1;
+        a.forced = nullptr;
+        if (forced) {
+            CU(rt, cudaMemcpyAsync(rt->forced_dev, forced, (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice, rt->stream));
+            a.forced = rt->forced_dev;
+            set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, pos0, forced[0], 0, 1, 0);
+            CU(rt, cudaGetLastError());
+        }
+        a.gbar_base = rt->gbar_base;
+        CU(rt, launch_mega(a, rt->sm_count, rt->stream));
+        rt->gbar_base += mega_barriers(a);
+        return 0;
+    }
+    for (int i = 0; i < n; i++) {
+        if (forced) {
+            set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, pos0 + i, forced[i], 0, 1, 0);
+            CU(rt, cudaGetLastError());
+        }
+        if (int r = run_step(rt, !forced || i + 1 == n)) return r;
+    }
+    return 0;
+}
+
+// Describe the loaded model to the persistent kernel; mega_ok says whether it can run it.
+int setup_mega(lum_rt* rt) {
+    rt->mega_ok = false;
+    const lum_model_desc& d = rt->d;
+    if (d.weight_dtype != LUM_Q8_0 || d.tied_head) return 0;
+    std::vector<MegaLayer> hl((size_t)d.n_layers);
+    bool packed = rt->lm_head.kc > 0;
+    for (int l = 0; l < d.n_layers && packed; l++) {
+        LayerW& w = rt->L[(size_t)l];
+        const Tensor* ts[] = {&w.q, &w.k, &w.v, &w.o, &w.gate, &w.up, &w.down};
+        for (const Tensor* t : ts) packed = packed && t->kc > 0;
+        packed = packed && w.q.kc == w.k.kc && w.q.kc == w.v.kc && w.q.kc == w.gate.kc && w.q.kc == w.up.kc && w.q.kc == rt->lm_head.kc;
+        MegaLayer& m = hl[(size_t)l];
+        m.wq = (const unsigned char*)w.q.w; m.wk = (const unsigned char*)w.k.w; m.wv = (const unsigned char*)w.v.w;
+        m.wo = (const unsigned char*)w.o.w; m.wg = (const unsigned char*)w.gate.w; m.wu = (const unsigned char*)w.up.w;
+        m.wd = (const unsigned char*)w.down.w;
+        m.attn_norm = w.attn_norm.w; m.mlp_norm = w.mlp_norm.w;
+        m.q_norm = d.qk_norm ? w.q_norm.w : nullptr; m.k_norm = d.qk_norm ? w.k_norm.w : nullptr;
+        m.kc = w.kc; m.vc = w.vc;
+    }
+    if (!packed) return 0;
+    MegaArgs a{};
+    a.n_layers = d.n_layers; a.hidden = d.hidden; a.n_q = rt->nq_l; a.n_kv = rt->nkv_l; a.hd = d.head_dim; a.ffn = rt->ffn_l; a.vocab = rt->vocab_l;
+    a.max_seq = d.max_seq;
+    a.kc_h = rt->L[0].q.kc; a.kc_o = rt->L[0].o.kc; a.kc_f = rt->L[0].down.kc;
+    a.k_max = d.hidden;
+    if (rt->nq_l * d.head_dim > a.k_max) a.k_max = rt->nq_l * d.head_dim;
+    if (rt->ffn_l > a.k_max) a.k_max = rt->ffn_l;
+    a.gain_kind = kind_of(d.embed_dtype); a.embed_kind = rt->embed.kind; a.kv_bf16 = d.kv_dtype == LUM_BF16; a.rope_style = d.rope_style;
+    a.eps = rt->eps6; a.qk_eps = d.rms_eps; a.theta = d.rope_theta;
+    a.c_inv_d = rt->c_inv_d; a.c_ln_theta = rt->c_ln_theta; a.c_log2e = rt->c_log2e; a.c_half_pi = rt->c_half_pi;
+    a.embed = rt->embed.w; a.final_norm = rt->final_norm.w; a.lm_head = (const unsigned char*)rt->lm_head.w;
+    a.x = rt->x; a.qkv = rt->qkv; a.attn = rt->attn; a.h = rt->h; a.logits = rt->logits;
+    a.attn_part = rt->attn_part; a.attn_cnt = rt->attn_cnt; a.part_val = rt->am_val; a.part_idx = rt->am_idx;
+    a.state = rt->state; a.tokens_out = rt->tokens_out;
+    a.n_splits = rt->n_splits;
+    a.stages = mega_pick_stages(a.k_max);
+    a.status = rt->status;
+    if (a.n_kv * a.n_splits > rt->sm_count || !mega_supported(a)) return 0;
+    if (int r = dev_alloc(rt, (void**)&rt->mega_layers, hl.size() * sizeof(MegaLayer))) return r;
+    if (int r = dev_alloc(rt, (void**)&rt->forced_dev, (size_t)d.max_seq * sizeof(int))) return r;
+    if (int r = dev_alloc(rt, (void**)&rt->gbar, sizeof(unsigned long long))) return r;
+    if (int r = dev_alloc(rt, (void**)&rt->abort_flag, sizeof(int))) return r;
+    CU(rt, cudaMemcpyAsync(rt->mega_layers, hl.data(), hl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->gbar, 0, sizeof(unsigned long long), rt->stream));
+    CU(rt, cudaMemsetAsync(rt->abort_flag, 0, sizeof(int), rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    a.layers = rt->mega_layers; a.gbar = rt->gbar; a.abort_flag = rt->abort_flag;
+    rt->mega = a;
+    rt->gbar_base = 0;
+    rt->mega_ok = true;
+    return 0;
+}
+
 }  // namespace
 
 // =================================================================================== C ABI
@@ -316,10 +418,12 @@ extern "C" {
 
 void lum_config_default(lum_config* c) {
     if (!c) return;
-    c->device = 0; c->use_graph = 1; c->use_pdl = 1; c->attn_splits = 0;
+    c->device = 0; c->use_graph = 1; c->use_pdl = 1; c->attn_splits = 0; c->use_mega = 1;
     if (const char* e = getenv("LUM_GRAPH")) c->use_graph = atoi(e);
     if (const char* e = getenv("LUM_PDL")) c->use_pdl = atoi(e);
     if (const char* e = getenv("LUM_ATTN_SPLITS")) c->attn_splits = atoi(e);
+    c->use_mega = 1;
+    if (const char* e = getenv("LUM_MEGA")) c->use_mega = atoi(e);
 }
 
 int32_t lum_create(const lum_config* cfg, lum_rt** out) {
@@ -453,6 +557,8 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     rt->c_half_pi = round6(1.5707963267948966);
     rt->dim_s = 1; rt->dim_p = 0;
     rt->has_model = true;
+    rt->use_mega = rt->cfg.use_mega;
+    if (int r = setup_mega(rt)) { free_model(rt); return r; }
     return 0;
 }
 
@@ -620,12 +726,7 @@ int32_t lum_execute(lum_rt* rt) {
         const int tok = rt->tokens_in[(size_t)i];
         if (tok < 0 || tok >= rt->d.vocab) return fail(rt, LUM_E_INVALID, "execute: token id %d outside the vocabulary", tok);
     }
-    for (uint64_t i = 0; i < s; i++) {
-        set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, (int)(p + i), rt->tokens_in[(size_t)i], 0, 1, 0);
-        CU(rt, cudaGetLastError());
-        if (int r = run_step(rt, i + 1 == s)) return r;
-    }
-    return 0;
+    return run_tokens(rt, (int)s, rt->tokens_in.data(), (int)p);
 }
 
 int32_t lum_get_logits(lum_rt* rt, float* host_out, size_t n) {
@@ -659,8 +760,7 @@ int32_t lum_decode_greedy(lum_rt* rt, int32_t n_steps) {
     CU(rt, cudaSetDevice(rt->cfg.device));
     set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, 0, 0, 1, 0, 0);
     CU(rt, cudaGetLastError());
-    for (int i = 0; i < n_steps; i++)
-        if (int r = run_step(rt, true)) return r;
+    if (int r = run_tokens(rt, n_steps, nullptr, 0)) return r;
     rt->dim_p += (uint64_t)n_steps;
     return 0;
 }
@@ -694,10 +794,10 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     cudaEvent_t e0, e1;
     CU(rt, cudaEventCreate(&e0));
     CU(rt, cudaEventCreate(&e1));
-    int r = run_step(rt, true);   // warm-up, also builds the graphs
+    int r = run_tokens(rt, 1, nullptr, 0);   // warm-up, also builds the graphs
     if (!r) {
         cudaEventRecord(e0, rt->stream);
-        for (int i = 0; i < trials && !r; i++) r = run_step(rt, true);
+        r = run_tokens(rt, trials, nullptr, 0);
         cudaEventRecord(e1, rt->stream);
     }
     cudaStreamSynchronize(rt->stream);
@@ -718,7 +818,7 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
 
 int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n) {
     if (!rt || !rt->has_model || !n) return LUM_E_INVALID;
-    *n = 1 + 5 * rt->d.n_layers + 1;
+    *n = (rt->mega_ok && rt->use_mega) ? 1 : 1 + 5 * rt->d.n_layers + 1;
     return 0;
 }
 

@@ -35,7 +35,8 @@ SLOT = {
 
 
 class Config(C.Structure):
-    _fields_ = [("device", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32), ("attn_splits", C.c_int32)]
+    _fields_ = [("device", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32), ("attn_splits", C.c_int32),
+                ("use_mega", C.c_int32)]
 
 
 class ModelDesc(C.Structure):
@@ -177,7 +178,7 @@ class B200Runtime:
     # ---- lifecycle -------------------------------------------------------------------------------
     @classmethod
     def initialize(cls, device: int = 0, use_graph: Optional[bool] = None, use_pdl: Optional[bool] = None,
-                   attn_splits: Optional[int] = None) -> "B200Runtime":
+                   attn_splits: Optional[int] = None, use_mega: Optional[bool] = None) -> "B200Runtime":
         lib = load_library()
         cfg = Config()
         lib.lum_config_default(C.byref(cfg))
@@ -188,6 +189,8 @@ class B200Runtime:
             cfg.use_pdl = int(use_pdl)
         if attn_splits is not None:
             cfg.attn_splits = int(attn_splits)
+        if use_mega is not None:
+            cfg.use_mega = int(use_mega)
         h = C.c_void_p()
         rc = lib.lum_create(C.byref(cfg), C.byref(h))
         if rc != 0:

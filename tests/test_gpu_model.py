@@ -160,16 +160,17 @@ def test_llama_shape_two_layers_32_steps(pkg, rt):
     assert rel_err(lg, lo) <= LOGIT_TOL
 
 
-@pytest.mark.parametrize("graph,pdl", [(0, 0), (1, 0), (0, 1)])
+@pytest.mark.parametrize("graph,pdl", [(0, 0), (1, 0), (0, 1), (1, 1)])
 def test_launch_modes_agree(pkg, rt, graph, pdl):
-    """Plain launches, captured graph, and programmatic dependent launch all compute the same thing, bit for bit."""
+    """The persistent whole-token kernel (the default where the model allows it), plain launches, a captured graph,
+    and programmatic dependent launch all compute the same thing, bit for bit."""
     desc = pkg.CONFIGS["small_q8"]
     prompt = [5, 17, 1000, 2, 2, 77]
     rt.load_model(desc)
     rt.synth(3)
     base = rt.generate(prompt, 12)
     lb = rt.get_f32()
-    other = pkg.B200Runtime.initialize(device=0, use_graph=bool(graph), use_pdl=bool(pdl))
+    other = pkg.B200Runtime.initialize(device=0, use_graph=bool(graph), use_pdl=bool(pdl), use_mega=False)
     try:
         other.load_model(desc)
         other.synth(3)
@@ -254,4 +255,4 @@ def test_profile_restores_state(pkg, rt):
     assert us > 0 and "ms/token" in text
     rt.decode_greedy(9)
     assert [first] + [int(t) for t in rt.get_decoded(9)] == base
-    assert rt.launches_per_step() == 2 + 5 * desc.n_layers
+    assert rt.launches_per_step() in (1, 2 + 5 * desc.n_layers)
