@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     GemvSmem g;
     gemv_carve(smem, a.K, a.stages, &s_abort, &g);
     if (tid == 0) {
+        GPROBE(0);
         s_abort = 0;
         gemv_init_barriers(g);
     }
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     if (warp == kConsumers / 32) {
         // producer warp: the weight stream does not depend on the previous kernel, so it starts at once
         if (!gemv_produce(a, sh, g, 0, lane, a.status)) gemv_producer_drain(g, sh.fills, lane, a.status);
+        GPROBE(5);
         return;
     }
     if (a.use_pdl) pdl_grid_wait();
@@ -128,7 +130,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     ArgBest best{-INFINITY, -1};
     gemv_consume(a, xs, blockIdx.x == 0, sh, g, 0, tid, a.status, &best);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 1);
+    GPROBE(4);
 }
+#ifdef LUM_PROBE
+extern "C" int lum_probe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_probe, sizeof(g_probe)); }
+#endif
 
 // ------------------------------------------------------------------------------ direct kernel
 
@@ -274,15 +280,15 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
         const size_t fixed = gemv_fixed_smem(a.K);
         // Two kernels co-resident per SM (so the next one can prefetch under programmatic dependent launch):
         // stay under ~113 KiB each.  LUM_GEMV_STAGES overrides (deeper ring, no co-residency).
-        int stages = (int)((113 * 1024 - (long)fixed) / kStageBytes);
+        int stages = (int)((113 * 1024 - (long)fixed) / kFillBytes);
         static const int env_stages = [] { const char* e = getenv("LUM_GEMV_STAGES"); return e ? atoi(e) : 0; }();
         if (env_stages > 0) stages = env_stages;
-        const int fit = (int)((226 * 1024 - (long)fixed) / kStageBytes);
+        const int fit = (int)((226 * 1024 - (long)fixed) / kFillBytes);
         if (stages > fit) stages = fit;
         if (stages > kMaxStages) stages = kMaxStages;
         if (stages < 2) stages = 2;
         a.stages = stages;
-        const size_t smem = fixed + (size_t)stages * kStageBytes;
+        const size_t smem = fixed + (size_t)stages * kFillBytes;
         static size_t attr_set = 0;
         if (smem > attr_set) {
             cudaError_t e = cudaFuncSetAttribute(q8_gemv_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));

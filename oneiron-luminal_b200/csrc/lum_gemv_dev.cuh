@@ -17,10 +17,19 @@
 
 namespace lum {
 
+#ifdef LUM_PROBE
+// Build-time probe (never in the shipped library): %globaltimer stamps of a few points in CTA 0 (one copy per translation unit).
+static __device__ unsigned long long g_probe[32];
+#define GPROBE(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || (i) == 5)) g_probe[i] = globaltimer_ns(); } while (0)
+#else
+#define GPROBE(i) do { } while (0)
+#endif
+
 constexpr int kConsumers = 512;          // 16 consumer warps: enough independent warps to cover dp4a / shuffle / LDS latency
 constexpr int kGemvThreads = 544;        // + 1 producer warp
 constexpr int kUnitBytes = 16384;        // int8 bytes per stage-unit
-constexpr int kStageBytes = kUnitBytes + kUnitBytes / 16;   // + binary16 scales (2 B per 32 quants)
+constexpr int kStageBytes = kUnitBytes + kUnitBytes / 16;   // one packed stage-unit: + binary16 scales (2 B per 32 quants)
+constexpr int kFillBytes = 2 * kStageBytes;                 // one ring stage holds up to two stage-units
 constexpr int kBarBytes = 512;           // 2 x 16 mbarriers (256 B), then 64 words of reduction scratch
 constexpr int kMaxStages = 16;
 constexpr int kChunkUnits = 64;          // stage-units whose row sums are held before an epilogue pass
@@ -35,7 +44,7 @@ struct GemvSmem {
     float* xsc;                  // K / 32 block scales of x
     float* red;                  // kRedFloats
     float* vals;                 // kValsFloats
-    unsigned char* stage0;       // ring of `stages` x kStageBytes, 128-byte aligned
+    unsigned char* stage0;       // ring of `stages` x kFillBytes, 128-byte aligned
     int stages;
     volatile int* abort;         // CTA-wide: a wait ran out of budget; stop waiting, finish fast
 };
@@ -207,17 +216,21 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         const float i1 = amax > 0.0f ? 127.0f / amax : 0.0f;
         const float s2 = s1 * (1.0f / 254.0f), i2 = i1 * 254.0f;
         const float i3 = i1 * 64516.0f;
+        // Round to nearest by adding 1.5 * 2^23: the sum's low mantissa bits are the integer in two's complement,
+        // so its low byte is the int8 value — no float->int conversion or rint (both quarter-rate instructions).
+        // |e * i1| <= 127 and every residual is at most half a step of the level before, so no clamping is needed.
+        constexpr float kMagic = 12582912.0f;
         uint32_t p1 = 0, p2 = 0, p3 = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float q1 = fminf(fmaxf(rintf(e[j] * i1), -127.0f), 127.0f);
-            const float r1 = fmaf(-s1, q1, e[j]);
-            const float q2 = fminf(fmaxf(rintf(r1 * i2), -127.0f), 127.0f);
-            const float r2 = fmaf(-s2, q2, r1);
-            const float q3 = fminf(fmaxf(rintf(r2 * i3), -127.0f), 127.0f);
-            p1 |= ((uint32_t)(int)q1 & 0xffu) << (8 * j);
-            p2 |= ((uint32_t)(int)q2 & 0xffu) << (8 * j);
-            p3 |= ((uint32_t)(int)q3 & 0xffu) << (8 * j);
+            const float t1 = fmaf(e[j], i1, kMagic);
+            const float r1 = fmaf(-s1, t1 - kMagic, e[j]);
+            const float t2 = fmaf(r1, i2, kMagic);
+            const float r2 = fmaf(-s2, t2 - kMagic, r1);
+            const float t3 = fmaf(r2, i3, kMagic);
+            p1 |= (__float_as_uint(t1) & 0xffu) << (8 * j);
+            p2 |= (__float_as_uint(t2) & 0xffu) << (8 * j);
+            p3 |= (__float_as_uint(t3) & 0xffu) << (8 * j);
         }
         if (in) {
             ((uint32_t*)g.xq)[f4] = p1;
@@ -230,7 +243,9 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
 }
 
 // This CTA's share of a phase: logical units [lu0, lu1) of R rows each.
-struct GemvShare { int R, nch, sub, lu0, n_lu, fills; };
+// A fill (one ring stage, one barrier hand-over) carries two stage-units: with a single K-chunk per row group
+// (nch == 1) two consecutive units of the CTA, otherwise two consecutive K-chunks of one unit (fpu fills per unit).
+struct GemvShare { int R, nch, sub, lu0, n_lu, fpu, fills; };
 __device__ __forceinline__ GemvShare gemv_share(const GemvArgs& a, int cta, int n_cta) {
     GemvShare s;
     s.R = kUnitBytes / a.KC;
@@ -242,7 +257,9 @@ __device__ __forceinline__ GemvShare gemv_share(const GemvArgs& a, int cta, int 
     const int LU = rows_total / s.R;
     s.lu0 = (int)((long long)cta * LU / n_cta);
     s.n_lu = (int)((long long)(cta + 1) * LU / n_cta) - s.lu0;
-    s.fills = s.n_lu * s.sub * s.nch;
+    const int n_units = s.n_lu * s.sub;
+    s.fpu = (s.nch + 1) / 2;
+    s.fills = s.nch == 1 ? (n_units + 1) / 2 : n_units * s.fpu;
     return s;
 }
 
@@ -268,7 +285,8 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvShare&
     if (lane >= g.stages) return true;
     const int S = g.stages;
     const uint32_t fb = g.full0 + 8u * lane, eb = g.empty0 + 8u * lane;
-    const uint32_t dst = smem_u32(g.stage0 + (size_t)lane * kStageBytes);
+    const uint32_t dst = smem_u32(g.stage0 + (size_t)lane * kFillBytes);
+    const int n_units = sh.n_lu * sh.sub;
     int first = (int)((lane - fill_base % S + S) % S);          // first fill of this phase that lands in my stage
 #pragma unroll 1
     for (int n = first; n < sh.fills; n += S) {
@@ -279,12 +297,22 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvShare&
             if (!*g.abort) { atomicOr(status, LUM_ST_WAIT_EMPTY); *g.abort = 1; }
             return false;
         }
-        const int u = n / sh.nch, c = n - u * sh.nch;             // stage-unit of this CTA, K-chunk
-        const int l = u / sh.sub, w = u - l * sh.sub;
-        const unsigned char* src = unit_base(a, sh.lu0 + l, w, sh.R, sh.nch) + (size_t)c * kStageBytes;
-        // one stage = one contiguous 17 KiB piece of the packed stream = one bulk copy
-        mbar_arrive_expect_tx(fb, (uint32_t)kStageBytes);
-        bulk_g2s(dst, src, (uint32_t)kStageBytes, fb);
+        if (sh.nch == 1) {
+            // units 2n and 2n + 1 of this CTA: two copies (they may sit in different matrices)
+            const int ua = 2 * n, ub = ua + 1;
+            const bool two = ub < n_units;
+            mbar_arrive_expect_tx(fb, (uint32_t)(two ? kFillBytes : kStageBytes));
+            bulk_g2s(dst, unit_base(a, sh.lu0 + ua / sh.sub, ua % sh.sub, sh.R, 1), (uint32_t)kStageBytes, fb);
+            if (two) bulk_g2s(dst + kStageBytes, unit_base(a, sh.lu0 + ub / sh.sub, ub % sh.sub, sh.R, 1), (uint32_t)kStageBytes, fb);
+        } else {
+            // K-chunks 2g and 2g + 1 of one unit: contiguous in the packed stream, one copy
+            const int u = n / sh.fpu, gq = n - u * sh.fpu;
+            const int c = 2 * gq;
+            const uint32_t bytes = (uint32_t)(c + 1 < sh.nch ? kFillBytes : kStageBytes);
+            const unsigned char* src = unit_base(a, sh.lu0 + u / sh.sub, u % sh.sub, sh.R, sh.nch) + (size_t)c * kStageBytes;
+            mbar_arrive_expect_tx(fb, bytes);
+            bulk_g2s(dst, src, bytes, fb);
+        }
     }
     return true;
 }
@@ -307,7 +335,12 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
                                              long long fill_base, int tid, uint32_t* status, ArgBest* best) {
     const int lane = tid & 31;
     const int K = a.K, KC = a.KC, nch = sh.nch, R = sh.R, S = g.stages;
+    GPROBE(1);
     gemv_quantize_x(a, xs, is_writer, g, tid);
+    GPROBE(2);
+#ifdef LUM_PROBE
+    if (blockIdx.x == 0 && tid == 0) { g_probe[8] = 0; g_probe[9] = 0; g_probe[10] = (unsigned long long)clock64(); }
+#endif
 
     const int TPB = KC >> 5;                   // threads across one row chunk: one 32-block each
     const int row = tid / TPB;                 // this thread's row of the unit (512 threads = R rows x TPB blocks)
@@ -330,6 +363,36 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
     int stage = (int)(fill_base % S);
     uint32_t phase = (uint32_t)((fill_base / S) & 1);
     const int n_units = sh.n_lu * sh.sub;      // stage-units of this CTA, in the producer's order
+
+    // wait for the ring stage, and afterwards hand it back
+    auto wait_full = [&]() {
+        if (!*g.abort && !mbar_wait_abortable(g.full0 + 8u * stage, phase, g.abort)) {
+            if (!*g.abort) { atomicOr(status, LUM_ST_WAIT_FULL); *g.abort = 1; }
+        }
+    };
+    auto release = [&]() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(g.empty0 + 8u * stage);
+        if (++stage == S) { stage = 0; phase ^= 1u; }
+    };
+    // one stage-unit held at `sq`: this thread's 32 weights of its row against its x block
+    auto unit_dot = [&](const unsigned char* sq) -> float {
+        const uint4* wp = (const uint4*)(sq + (size_t)row * KC + ((size_t)ks << 5));
+        const uint4 w0 = wp[0], w1 = wp[1];
+        const float dw = __half2float(((const __half*)(sq + kUnitBytes))[row * TPB + ks]);
+        int i1 = 0, i2 = 0, i3 = 0;
+#define LUM_DP(wv, j, f)                                   \
+    i1 = __dp4a((int)(wv), (int)xa[0][j].f, i1);           \
+    i2 = __dp4a((int)(wv), (int)xa[1][j].f, i2);           \
+    i3 = __dp4a((int)(wv), (int)xa[2][j].f, i3);
+        LUM_DP(w0.x, 0, x) LUM_DP(w0.y, 0, y) LUM_DP(w0.z, 0, z) LUM_DP(w0.w, 0, w)
+        LUM_DP(w1.x, 1, x) LUM_DP(w1.y, 1, y) LUM_DP(w1.z, 1, z) LUM_DP(w1.w, 1, w)
+#undef LUM_DP
+        // i1 * 254 + i2 fits an int32 (|i1| <= 32 * 127 * 127): one conversion fewer
+        const float t = fmaf((float)i3, 1.0f / 64516.0f, (float)(i1 * 254 + i2) * (1.0f / 254.0f));
+        return t * (sx * dw);
+    };
+
 #pragma unroll 1
     for (int c0 = 0; c0 < n_units; c0 += kChunkUnits) {
         const int c1 = min(n_units, c0 + kChunkUnits);
@@ -337,32 +400,38 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
 #pragma unroll 1
         for (int u0 = c0; u0 < c1; u0 += 4) {
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (nch == 1) {
+                // a fill = two units (two row groups, same x): both dot products run side by side
 #pragma unroll
-            for (int uu = 0; uu < 4; uu++) {
-                if (u0 + uu < c1) {
+                for (int j = 0; j < 2; j++) {
+                    if (u0 + 2 * j < c1) {
+                        wait_full();
+                        const unsigned char* sq = g.stage0 + (size_t)stage * kFillBytes;
+                        const bool two = u0 + 2 * j + 1 < c1;
+                        const float va = unit_dot(sq);
+                        const float vb = two ? unit_dot(sq + kStageBytes) : 0.0f;
+                        acc[2 * j] = va;
+                        acc[2 * j + 1] = vb;
+                        release();
+                    }
+                }
+            } else {
+                // a fill = two K-chunks of one unit
+#pragma unroll
+                for (int uu = 0; uu < 4; uu++) {
+                    if (u0 + uu < c1) {
 #pragma unroll 1
-                    for (int c = 0; c < nch; c++) {
-                        if (nch != 1) load_xblock(c);
-                        if (!*g.abort && !mbar_wait_abortable(g.full0 + 8u * stage, phase, g.abort)) {
-                            if (!*g.abort) { atomicOr(status, LUM_ST_WAIT_FULL); *g.abort = 1; }
+                        for (int c = 0; c < nch; c += 2) {
+                            wait_full();
+                            const unsigned char* sq = g.stage0 + (size_t)stage * kFillBytes;
+                            load_xblock(c);
+                            acc[uu] += unit_dot(sq);
+                            if (c + 1 < nch) {
+                                load_xblock(c + 1);
+                                acc[uu] += unit_dot(sq + kStageBytes);
+                            }
+                            release();
                         }
-                        const unsigned char* sq = g.stage0 + (size_t)stage * kStageBytes;
-                        const uint4* wp = (const uint4*)(sq + (size_t)row * KC + ((size_t)ks << 5));
-                        const uint4 w0 = wp[0], w1 = wp[1];
-                        const float dw = __half2float(((const __half*)(sq + kUnitBytes))[row * TPB + ks]);
-                        int i1 = 0, i2 = 0, i3 = 0;
-#define LUM_DP(wv, j, f)                                   \
-    i1 = __dp4a((int)(wv), (int)xa[0][j].f, i1);           \
-    i2 = __dp4a((int)(wv), (int)xa[1][j].f, i2);           \
-    i3 = __dp4a((int)(wv), (int)xa[2][j].f, i3);
-                        LUM_DP(w0.x, 0, x) LUM_DP(w0.y, 0, y) LUM_DP(w0.z, 0, z) LUM_DP(w0.w, 0, w)
-                        LUM_DP(w1.x, 1, x) LUM_DP(w1.y, 1, y) LUM_DP(w1.z, 1, z) LUM_DP(w1.w, 1, w)
-#undef LUM_DP
-                        const float t = fmaf((float)i3, 1.0f / 64516.0f, fmaf((float)i2, 1.0f / 254.0f, (float)i1));
-                        acc[uu] = fmaf(t, sx * dw, acc[uu]);
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(g.empty0 + 8u * stage);
-                        if (++stage == S) { stage = 0; phase ^= 1u; }
                     }
                 }
             }
@@ -392,6 +461,10 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
                 if ((lane & 3) == 0 && u0 + uidx < c1) g.red[(size_t)(ub + uidx) * 32 + row] = v;
             }
         }
+        GPROBE(3);
+#ifdef LUM_PROBE
+        if (blockIdx.x == 0 && tid == 0) g_probe[11] = (unsigned long long)clock64();
+#endif
         named_sync(1, kConsumers);
         // fixed-order sum of the per-warp partials -> vals, then the epilogue for this chunk's rows
         const int cu = c1 - c0;                // units in this chunk (even in SwiGLU mode: kChunkUnits is even)

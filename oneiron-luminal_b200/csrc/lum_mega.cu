@@ -24,6 +24,15 @@
 
 namespace lum {
 
+#ifdef LUM_PROBE
+// Build-time probe (never in the shipped library): %globaltimer stamps of CTA 0's phase boundaries.
+__device__ unsigned long long g_mprobe[1024];
+#define MPROBE(i) do { if (blockIdx.x == 0 && tid == 0 && (i) < 1024) g_mprobe[i] = globaltimer_ns(); } while (0)
+extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_mprobe, sizeof(g_mprobe)); }
+#else
+#define MPROBE(i) do { } while (0)
+#endif
+
 // ---- grid-wide barrier ----------------------------------------------------------------------------
 // Arrival counter in global memory, only ever incremented; barrier number b (0-based since the counter
 // was last zeroed by the host) is passed when the counter reaches (b + 1) * gridDim.x.  Called by all
@@ -157,16 +166,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                 if (streams) gemv_produce(ga, sh, g, fill, lane, a.status);
             } else if (!streams) {
                 // RoPE + cache append + attention
+                if (t == 1) MPROBE(ph * 3);
                 if (!s_abort) attn_phase<HD, GM, BF16>(a, L, (unsigned char*)g.xq, pos, tid);
+                if (t == 1) MPROBE(ph * 3 + 1);
                 grid_barrier(a, seq, &s_abort, tid);
+                if (t == 1) MPROBE(ph * 3 + 2);
             } else {
                 XSource xs{};
                 if (ph == 0) { xs.table = a.embed; xs.table_kind = a.embed_kind; xs.token = tok; xs.x_out = a.x; }   // the embedding row is x
                 else xs.x = p == 2 ? a.attn : p == 4 ? a.h : a.x;
                 ArgBest best{-INFINITY, -1};
+                if (t == 1) MPROBE(ph * 3);
                 if (!s_abort) gemv_consume(ga, xs, cta == 0, sh, g, fill, tid, a.status, &best);
+                if (t == 1) MPROBE(ph * 3 + 1);
                 if (p == 5 && tid == 0) { a.part_val[cta] = best.v; a.part_idx[cta] = best.i; }
                 grid_barrier(a, seq, &s_abort, tid);
+                if (t == 1) MPROBE(ph * 3 + 2);
                 if (p == 5) {
                     // every CTA folds the per-CTA maxima itself: all of them need the token for the next embedding row
                     if (warp == 0) {
@@ -204,10 +219,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
 
 // ------------------------------------------------------------------------------------------- host side
 
-size_t mega_smem_bytes(int k_max, int stages) { return gemv_fixed_smem(k_max) + (size_t)stages * kStageBytes; }
+size_t mega_smem_bytes(int k_max, int stages) { return gemv_fixed_smem(k_max) + (size_t)stages * kFillBytes; }
 
 int mega_pick_stages(int k_max) {
-    int stages = (int)((226 * 1024 - (long)gemv_fixed_smem(k_max)) / kStageBytes);
+    int stages = (int)((226 * 1024 - (long)gemv_fixed_smem(k_max)) / kFillBytes);
     if (stages > kMaxStages) stages = kMaxStages;
     static const int env_stages = [] { const char* e = getenv("LUM_MEGA_STAGES"); return e ? atoi(e) : 0; }();
     if (env_stages > 0 && env_stages < stages) stages = env_stages;
@@ -222,7 +237,7 @@ bool mega_supported(const MegaArgs& a) {
     const size_t alias = (size_t)3 * a.k_max + (size_t)a.k_max / 8 + (size_t)(kRedFloats + kValsFloats) * 4;
     if (a.n_kv <= 0 || a.n_q % a.n_kv || a.n_q / a.n_kv > 8 || a.n_splits < 1) return false;
     if (attn_smem_bytes(a.hd, a.n_q / a.n_kv) > alias) return false;
-    return mega_pick_stages(a.k_max) >= 3;
+    return mega_pick_stages(a.k_max) >= 2;
 }
 
 cudaError_t launch_mega(const MegaArgs& a_in, int sm_count, cudaStream_t st) {
