@@ -47,8 +47,8 @@ typedef struct lum_config {
     int32_t use_graph;    /* 1: replay one captured CUDA graph per token (default); 0: plain launches */
     int32_t use_pdl;      /* 1: programmatic dependent launch between kernels (default); 0: off */
     int32_t attn_splits;  /* CTAs per KV head in decode attention; 0 = choose from the SM count */
-    int32_t use_mega;     /* 1: run whole tokens in one persistent cooperative kernel when the model allows (default);
-                             0: one kernel per operation (CUDA graph / plain launches as chosen above) */
+    int32_t use_mega;     /* 1: run whole tokens in one persistent cooperative kernel when the model allows;
+                             0 (default): one kernel per operation (CUDA graph / plain launches as chosen above) */
 } lum_config;
 
 void lum_config_default(lum_config* cfg);

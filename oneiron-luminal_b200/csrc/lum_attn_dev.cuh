@@ -258,24 +258,15 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
     sync();
     if (!s_last) return;
     __threadfence();
-    // The partials were written by other CTAs: read them through L2 (ld.cg), in batches of independent
-    // loads so the round trips overlap instead of queueing behind one another.
+    // The partials were written by other CTAs: read them through L2 (ld.cg).  All loads of a batch of 8 splits
+    // are issued before any is used, so a batch costs one round trip; batches fold into a running (max, sum, out).
     constexpr int kBatch = 8;
 #pragma unroll 1
     for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, e = idx - g * HD;
         const float* src = a.part + ((size_t)kvh * a.n_splits * G + g) * (HD + 2);
         const size_t sstride = (size_t)G * (HD + 2);
-        float M = -INFINITY;
-#pragma unroll 1
-        for (int s0 = 0; s0 < a.n_splits; s0 += kBatch) {
-            float mv[kBatch];
-#pragma unroll
-            for (int j = 0; j < kBatch; j++) mv[j] = (s0 + j < a.n_splits) ? __ldcg(src + (size_t)(s0 + j) * sstride + HD) : -INFINITY;
-#pragma unroll
-            for (int j = 0; j < kBatch; j++) M = fmaxf(M, mv[j]);
-        }
-        float L = 0.0f, O = 0.0f;
+        float M = -INFINITY, L = 0.0f, O = 0.0f;
 #pragma unroll 1
         for (int s0 = 0; s0 < a.n_splits; s0 += kBatch) {
             float mv[kBatch], lv[kBatch], ov[kBatch];
@@ -287,12 +278,18 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
                 lv[j] = __ldcg(q2 + HD + 1);
                 ov[j] = __ldcg(q2 + e);
             }
+            float Mb = M;
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) Mb = fmaxf(Mb, mv[j]);
+            const float c0 = (M == -INFINITY) ? 0.0f : expf(M - Mb);
+            L *= c0; O *= c0;
 #pragma unroll
             for (int j = 0; j < kBatch; j++) {
-                const float c = (mv[j] == -INFINITY) ? 0.0f : expf(mv[j] - M);
+                const float c = (mv[j] == -INFINITY) ? 0.0f : expf(mv[j] - Mb);
                 L = fmaf(lv[j], c, L);
                 O = fmaf(ov[j], c, O);
             }
+            M = Mb;
         }
         a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);
     }

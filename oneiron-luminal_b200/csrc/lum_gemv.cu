@@ -116,19 +116,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     }
     __syncthreads();
     if (a.use_pdl) pdl_launch_dependents();
-    const GemvShare sh = gemv_share(a, (int)blockIdx.x, (int)gridDim.x);
+    const GemvPlan plan = gemv_plan(a, (int)gridDim.x, a.job_ctr != nullptr);
 
     if (warp == kConsumers / 32) {
-        // producer warp: the weight stream does not depend on the previous kernel, so it starts at once
-        if (!gemv_produce(a, sh, g, 0, lane, a.status)) gemv_producer_drain(g, sh.fills, lane, a.status);
-        GPROBE(5);
+        // producer: the weight stream does not depend on the previous kernel, so it starts at once
+        if (lane == 0) {
+            ProducerRing pr{0, 0u, 0};
+            if (!gemv_produce(a, plan, g, pr, (int)blockIdx.x, (int)gridDim.x, a.job_ctr, a.status)) gemv_producer_drain(g, pr, a.status);
+            GPROBE(5);
+        }
         return;
     }
     if (a.use_pdl) pdl_grid_wait();
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
     ArgBest best{-INFINITY, -1};
-    gemv_consume(a, xs, blockIdx.x == 0, sh, g, 0, tid, a.status, &best);
+    ConsumerRing cr{0, 0u};
+    gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, a.status, &best);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 1);
     GPROBE(4);
 }

@@ -9,9 +9,15 @@
 //                                     row sums are reduced in a fixed order and passed to the
 //                                     epilogue (store / residual add / SwiGLU / greedy sample).
 //
-// Ring stages are numbered by a fill counter that keeps running across phases, so in the
-// persistent kernel the producer streams the next operation's weights while the consumers are
-// still finishing (or waiting for the grid-wide dependency of) the current one.
+// The ring keeps running across phases, so in the persistent kernel the producer streams the next
+// operation's weights while the consumers are still finishing (or waiting for the grid-wide
+// dependency of) the current one.
+//
+// Work is handed out in jobs (two stage-units, or one row group with all its K-chunks).  Each CTA
+// owns a static run of jobs; the rest sit in a pool that producers claim from with an atomic
+// counter, so SMs that happen to get more HBM bandwidth take more of the matrix (equal static
+// shares finished up to 30 % apart on B200).  Every ring stage carries the id of the unit it
+// holds, and the producer ends a phase with an END marker stage.
 #pragma once
 #include "lum_kernels.cuh"
 
@@ -35,6 +41,7 @@ constexpr int kMaxStages = 16;
 constexpr int kChunkUnits = 64;          // stage-units whose row sums are held before an epilogue pass
 constexpr int kRedFloats = kChunkUnits * 32;
 constexpr int kValsFloats = kChunkUnits * 32;
+constexpr int kMetaEnd = -1;
 
 // Shared-memory carve-up used by a streaming phase.
 struct GemvSmem {
@@ -44,6 +51,8 @@ struct GemvSmem {
     float* xsc;                  // K / 32 block scales of x
     float* red;                  // kRedFloats
     float* vals;                 // kValsFloats
+    int* unit_of;                // kChunkUnits: global stage-unit id held in each local slot of the current chunk
+    int* meta;                   // kMaxStages: first stage-unit id of the fill in each ring stage, or kMetaEnd
     unsigned char* stage0;       // ring of `stages` x kFillBytes, 128-byte aligned
     int stages;
     volatile int* abort;         // CTA-wide: a wait ran out of budget; stop waiting, finish fast
@@ -51,7 +60,8 @@ struct GemvSmem {
 
 // bytes of dynamic shared memory before the ring, for activations of length K
 __host__ __device__ inline size_t gemv_fixed_smem(int K) {
-    return (size_t)kBarBytes + (size_t)K * 3 + (size_t)(K / 32) * 4 + (size_t)kRedFloats * 4 + (size_t)kValsFloats * 4 + 256;
+    return (size_t)kBarBytes + (size_t)K * 3 + (size_t)(K / 32) * 4 + (size_t)kRedFloats * 4 + (size_t)kValsFloats * 4 +
+           (size_t)(kChunkUnits + kMaxStages) * 4 + 256;
 }
 
 __device__ __forceinline__ void gemv_carve(unsigned char* smem, int K, int stages, volatile int* abort, GemvSmem* g) {
@@ -62,7 +72,9 @@ __device__ __forceinline__ void gemv_carve(unsigned char* smem, int K, int stage
     g->xsc = (float*)(g->xq + 3 * (size_t)K);
     g->red = g->xsc + (K >> 5);
     g->vals = g->red + kRedFloats;
-    g->stage0 = (unsigned char*)(((uintptr_t)(g->vals + kValsFloats) + 127) & ~(uintptr_t)127);
+    g->unit_of = (int*)(g->vals + kValsFloats);
+    g->meta = g->unit_of + kChunkUnits;
+    g->stage0 = (unsigned char*)(((uintptr_t)(g->meta + kMaxStages) + 127) & ~(uintptr_t)127);
     g->stages = stages;
     g->abort = abort;
 }
@@ -100,9 +112,51 @@ __device__ __forceinline__ void argbest_take(ArgBest& b, float ov, int oi) {
     if (oi >= 0 && (b.i < 0 || ov > b.v || (ov == b.v && oi > b.i))) { b.v = ov; b.i = oi; }
 }
 
-// Epilogue over `n` finished rows starting at logical row `row0`: vals[i] is row row0 + i (SwiGLU: gate
-// sums in vals[0..n), up sums in vals[n..2n)).  For EPI_ARGMAX the rows are stored and thread 0 folds
-// the chunk's best into *best.
+// Epilogue over the finished units of a chunk: slot s holds stage-unit unit_of[s], R row sums at vals[s*R ..].
+// A stage-unit id maps to logical rows: plain phases unit u = rows [u*R, (u+1)*R) of the concatenated segments;
+// SwiGLU phases unit 2l = gate rows of logical unit l, unit 2l+1 = its up rows, and the two sit in adjacent slots.
+// For EPI_ARGMAX the rows are stored and thread 0 folds the chunk's best into *best.
+__device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const float* vals, const int* unit_of, int n_slots, int R, int tid,
+                                                    int nthreads, float* scratch, int bar_id, ArgBest* best) {
+    const int n = n_slots * R;
+    if (a.epi == EPI_SWIGLU) {
+        for (int i = tid; i < (n_slots >> 1) * R; i += nthreads) {
+            const int p = i / R, r = i - p * R;
+            const int row = (unit_of[2 * p] >> 1) * R + r;
+            a.y[row] = swiglu(vals[(2 * p) * R + r], vals[(2 * p + 1) * R + r]);
+        }
+    } else if (a.epi == EPI_STORE) {
+        for (int i = tid; i < n; i += nthreads) { const int sl = i / R; a.y[unit_of[sl] * R + (i - sl * R)] = vals[i]; }
+    } else if (a.epi == EPI_RESID) {
+        for (int i = tid; i < n; i += nthreads) { const int sl = i / R; const int row = unit_of[sl] * R + (i - sl * R); a.y[row] = a.resid[row] + vals[i]; }
+    } else {  // EPI_ARGMAX
+        ArgBest b{-INFINITY, -1};
+        for (int i = tid; i < n; i += nthreads) {
+            const int sl = i / R;
+            const int row = unit_of[sl] * R + (i - sl * R);
+            const float v = vals[i];
+            a.y[row] = v;
+            argbest_take(b, v, row);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, b.v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, b.i, o);
+            argbest_take(b, ov, oi);
+        }
+        int* iscratch = (int*)(scratch + 32);
+        if ((tid & 31) == 0) { scratch[tid >> 5] = b.v; iscratch[tid >> 5] = b.i; }
+        named_sync(bar_id, nthreads);
+        if (tid == 0) {
+            for (int w = 1; w < (nthreads >> 5); w++) argbest_take(b, scratch[w], iscratch[w]);
+            argbest_take(*best, b.v, b.i);
+        }
+        named_sync(bar_id, nthreads);
+    }
+}
+
+// Same for a contiguous run of rows (the plain-load kernel): vals[i] is logical row row0 + i (SwiGLU: gate sums in
+// vals[0..n), up sums in vals[n..2n)).
 __device__ __forceinline__ void gemv_epilogue_rows(const GemvArgs& a, const float* vals, int row0, int n, int tid, int nthreads,
                                                    float* scratch, int bar_id, ArgBest* best) {
     if (a.epi == EPI_STORE) {
@@ -242,105 +296,155 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
     named_sync(1, kConsumers);
 }
 
-// This CTA's share of a phase: logical units [lu0, lu1) of R rows each.
-// A fill (one ring stage, one barrier hand-over) carries two stage-units: with a single K-chunk per row group
-// (nch == 1) two consecutive units of the CTA, otherwise two consecutive K-chunks of one unit (fpu fills per unit).
-struct GemvShare { int R, nch, sub, lu0, n_lu, fpu, fills; };
-__device__ __forceinline__ GemvShare gemv_share(const GemvArgs& a, int cta, int n_cta) {
-    GemvShare s;
-    s.R = kUnitBytes / a.KC;
-    s.nch = a.K / a.KC;
-    s.sub = a.epi == EPI_SWIGLU ? 2 : 1;
+// How a phase's matrix is cut into jobs.
+//   stage-unit u (global id): plain phases = R rows [u*R, ..) of the concatenated segments; SwiGLU phases 2l = gate rows of
+//   logical unit l, 2l+1 = up rows.  A fill (one ring stage, one barrier hand-over) carries two stage-units: with one
+//   K-chunk per row group (nch == 1) units 2j and 2j+1, otherwise two consecutive K-chunks of one unit.
+//   A job is what one CTA must do as a whole: nch == 1: one fill (units 2j, 2j+1);  nch > 1: upj units (2 for SwiGLU so
+//   gate and up of a logical unit stay together, else 1) with fpu fills each.
+struct GemvPlan {
+    int R, nch, sub, fpu, upj;
+    int U;            // stage-units in the phase
+    int J;            // jobs in the phase
+    int js;           // jobs statically owned by every CTA: CTA c has [c*js, (c+1)*js)
+    int pool0;        // first pooled job: [pool0, J) are claimed dynamically (or, without a counter, split statically)
+};
+// pooled_permille: share of the jobs left to the pool (0 = all static).
+__device__ __forceinline__ GemvPlan gemv_plan(const GemvArgs& a, int n_cta, bool dynamic) {
+    GemvPlan p;
+    p.R = kUnitBytes / a.KC;
+    p.nch = a.K / a.KC;
+    p.sub = a.epi == EPI_SWIGLU ? 2 : 1;
     int rows_total = 0;
     if (a.epi == EPI_SWIGLU) rows_total = a.seg[0].rows;
     else for (int i = 0; i < a.nseg; i++) rows_total += a.seg[i].rows;
-    const int LU = rows_total / s.R;
-    s.lu0 = (int)((long long)cta * LU / n_cta);
-    s.n_lu = (int)((long long)(cta + 1) * LU / n_cta) - s.lu0;
-    const int n_units = s.n_lu * s.sub;
-    s.fpu = (s.nch + 1) / 2;
-    s.fills = s.nch == 1 ? (n_units + 1) / 2 : n_units * s.fpu;
-    return s;
-}
-
-// logical unit -> first stage-unit of its row group in the packed weight stream.  `which`: 0 or 1
-// picks gate/up in SwiGLU mode.  Units of one row group (its K-chunks) are consecutive.
-__device__ __forceinline__ const unsigned char* unit_base(const GemvArgs& a, int lu, int which, int R, int nch) {
-    int row = lu * R;
-    int sg = 0;
-    if (a.epi == EPI_SWIGLU) {
-        sg = which;
+    p.U = rows_total / p.R * p.sub;
+    p.fpu = (p.nch + 1) / 2;
+    p.upj = p.nch == 1 ? 2 : p.sub;
+    p.J = (p.U + p.upj - 1) / p.upj;
+    if (dynamic) {
+        p.js = (int)((long long)p.J * 3 / 4 / n_cta);       // three quarters static, the rest to whoever is ahead
+        p.pool0 = p.js * n_cta;
     } else {
-        while (sg < a.nseg - 1 && row >= a.seg[sg].rows) { row -= a.seg[sg].rows; sg++; }
+        p.js = 0;                                            // everything in the "pool", split evenly by CTA index
+        p.pool0 = 0;
     }
-    return (const unsigned char*)a.seg[sg].w + (size_t)(row / R) * nch * kStageBytes;
+    return p;
 }
 
-// Producer side of one phase.  Called by every lane of the producer warp; lane i owns ring stage i and
-// issues the fills n (global numbering, starting at fill_base) with n % stages == i.  The lanes run their
-// wait -> arm -> issue sequences side by side, so the latency of those barrier operations is paid once per
-// `stages` fills instead of once per fill.  Returns false if a wait ran out of budget.
-__device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvShare& sh, const GemvSmem& g, long long fill_base, int lane,
-                                             uint32_t* status) {
-    if (lane >= g.stages) return true;
+// stage-unit id -> its first packed unit (K-chunk 0) in the weight stream
+__device__ __forceinline__ const unsigned char* unit_ptr(const GemvArgs& a, const GemvPlan& p, int u) {
+    int sg = 0;
+    int rg;                                  // row group inside the segment
+    if (a.epi == EPI_SWIGLU) {
+        sg = u & 1;
+        rg = u >> 1;
+    } else {
+        int row = u * p.R;
+        while (sg < a.nseg - 1 && row >= a.seg[sg].rows) { row -= a.seg[sg].rows; sg++; }
+        rg = row / p.R;
+    }
+    return (const unsigned char*)a.seg[sg].w + (size_t)rg * p.nch * kStageBytes;
+}
+
+// Producer ring position, carried across phases.
+struct ProducerRing { int stage; uint32_t par; long long armed; };
+struct ConsumerRing { int stage; uint32_t par; };
+
+// Producer side of one phase: ONE lane (lane 0 of the producer warp) walks this CTA's static jobs, then claims pooled
+// jobs with atomicAdd on *job_ctr (the next claim is always in flight while the current job is being issued), and
+// closes the phase with an END marker stage.  With job_ctr == null the pool is split evenly by CTA index instead.
+// Returns false if a wait ran out of budget (or the CTA is already aborting).
+__device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvPlan& p, const GemvSmem& g, ProducerRing& r, int cta, int n_cta,
+                                             unsigned int* job_ctr, uint32_t* status) {
     const int S = g.stages;
-    const uint32_t fb = g.full0 + 8u * lane, eb = g.empty0 + 8u * lane;
-    const uint32_t dst = smem_u32(g.stage0 + (size_t)lane * kFillBytes);
-    const int n_units = sh.n_lu * sh.sub;
-    int first = (int)((lane - fill_base % S + S) % S);          // first fill of this phase that lands in my stage
-#pragma unroll 1
-    for (int n = first; n < sh.fills; n += S) {
-        const long long gn = fill_base + n;
-        const uint32_t par = (uint32_t)((gn / S) & 1);
+    auto next_stage = [&]() -> bool {        // wait until the ring position is free
         if (*g.abort) return false;
-        if (!mbar_wait_abortable(eb, par ^ 1u, g.abort)) {
+        if (!mbar_wait_abortable(g.empty0 + 8u * r.stage, r.par ^ 1u, g.abort)) {
             if (!*g.abort) { atomicOr(status, LUM_ST_WAIT_EMPTY); *g.abort = 1; }
             return false;
         }
-        if (sh.nch == 1) {
-            // units 2n and 2n + 1 of this CTA: two copies (they may sit in different matrices)
-            const int ua = 2 * n, ub = ua + 1;
-            const bool two = ub < n_units;
+        return true;
+    };
+    auto advance = [&]() { r.armed++; if (++r.stage == S) { r.stage = 0; r.par ^= 1u; } };
+    auto issue_job = [&](int j) -> bool {
+        if (p.nch == 1) {
+            const int ua = 2 * j, ub = ua + 1;
+            const bool two = ub < p.U;
+            if (!next_stage()) return false;
+            const uint32_t fb = g.full0 + 8u * r.stage;
+            const uint32_t dst = smem_u32(g.stage0 + (size_t)r.stage * kFillBytes);
+            g.meta[r.stage] = ua;
             mbar_arrive_expect_tx(fb, (uint32_t)(two ? kFillBytes : kStageBytes));
-            bulk_g2s(dst, unit_base(a, sh.lu0 + ua / sh.sub, ua % sh.sub, sh.R, 1), (uint32_t)kStageBytes, fb);
-            if (two) bulk_g2s(dst + kStageBytes, unit_base(a, sh.lu0 + ub / sh.sub, ub % sh.sub, sh.R, 1), (uint32_t)kStageBytes, fb);
+            bulk_g2s(dst, unit_ptr(a, p, ua), (uint32_t)kStageBytes, fb);
+            if (two) bulk_g2s(dst + kStageBytes, unit_ptr(a, p, ub), (uint32_t)kStageBytes, fb);
+            advance();
         } else {
-            // K-chunks 2g and 2g + 1 of one unit: contiguous in the packed stream, one copy
-            const int u = n / sh.fpu, gq = n - u * sh.fpu;
-            const int c = 2 * gq;
-            const uint32_t bytes = (uint32_t)(c + 1 < sh.nch ? kFillBytes : kStageBytes);
-            const unsigned char* src = unit_base(a, sh.lu0 + u / sh.sub, u % sh.sub, sh.R, sh.nch) + (size_t)c * kStageBytes;
-            mbar_arrive_expect_tx(fb, bytes);
-            bulk_g2s(dst, src, bytes, fb);
+            for (int k = 0; k < p.upj; k++) {
+                const int u = j * p.upj + k;
+                if (u >= p.U) break;
+                const unsigned char* base = unit_ptr(a, p, u);
+                for (int c = 0; c < p.nch; c += 2) {
+                    if (!next_stage()) return false;
+                    const uint32_t fb = g.full0 + 8u * r.stage;
+                    const uint32_t bytes = (uint32_t)(c + 1 < p.nch ? kFillBytes : kStageBytes);
+                    g.meta[r.stage] = u;
+                    mbar_arrive_expect_tx(fb, bytes);
+                    bulk_g2s(smem_u32(g.stage0 + (size_t)r.stage * kFillBytes), base + (size_t)c * kStageBytes, bytes, fb);
+                    advance();
+                }
+            }
         }
+        return true;
+    };
+
+    const int npool = p.J - p.pool0;
+    unsigned int claim = 0;
+    if (job_ctr && npool > 0) claim = atomicAdd(job_ctr, 1u);               // first claim travels while the static part is issued
+    for (int j = cta * p.js; j < (cta + 1) * p.js; j++)
+        if (!issue_job(j)) return false;
+    if (job_ctr) {
+        while ((int)claim < npool) {
+            const unsigned int nxt = atomicAdd(job_ctr, 1u);
+            if (!issue_job(p.pool0 + (int)claim)) return false;
+            claim = nxt;
+        }
+    } else {
+        const int j0 = p.pool0 + (int)((long long)cta * npool / n_cta), j1 = p.pool0 + (int)((long long)(cta + 1) * npool / n_cta);
+        for (int j = j0; j < j1; j++)
+            if (!issue_job(j)) return false;
     }
+    // END marker: a stage with no bytes
+    if (!next_stage()) return false;
+    g.meta[r.stage] = kMetaEnd;
+    mbar_arrive(g.full0 + 8u * r.stage);
+    advance();
     return true;
 }
 
 // After an aborted run: never leave the CTA while a copy into its shared memory may still be in flight.
-// Lane i waits (bounded) for the last fill it armed, if any, to land.
-__device__ __forceinline__ void gemv_producer_drain(const GemvSmem& g, long long fills_issued_total, int lane, uint32_t* status) {
-    if (lane >= g.stages) return;
+// Wait (bounded) for every fill armed in the last ring revolution to land.
+__device__ __forceinline__ void gemv_producer_drain(const GemvSmem& g, const ProducerRing& r, uint32_t* status) {
     const int S = g.stages;
-    // last global fill index <= fills_issued_total - 1 with n % S == lane
-    long long last = fills_issued_total - 1;
-    last -= ((last % S) - lane + S) % S;
-    if (last < 0) return;
-    if (!mbar_wait(g.full0 + 8u * lane, (uint32_t)((last / S) & 1))) atomicOr(status, LUM_ST_WAIT_DRAIN);
+    int st = r.stage;
+    uint32_t par = r.par;
+    const long long back = r.armed < S ? r.armed : S;
+    for (long long i = 0; i < back; i++) {
+        if (st == 0) { st = S; par ^= 1u; }
+        st--;
+        if (!mbar_wait(g.full0 + 8u * st, par)) { atomicOr(status, LUM_ST_WAIT_DRAIN); return; }
+    }
 }
 
-// Consumer side of one phase: quantise x, stream this CTA's units, reduce, run the epilogue chunk by chunk.
-// fill_base as on the producer side.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
-__device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvShare& sh, const GemvSmem& g,
-                                             long long fill_base, int tid, uint32_t* status, ArgBest* best) {
+// Consumer side of one phase: quantise x, then take fills off the ring until the END marker, reducing row sums in a
+// fixed order and running the epilogue chunk by chunk.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
+__device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvPlan& p, const GemvSmem& g,
+                                             ConsumerRing& cr, int tid, uint32_t* status, ArgBest* best) {
     const int lane = tid & 31;
-    const int K = a.K, KC = a.KC, nch = sh.nch, R = sh.R, S = g.stages;
+    const int K = a.K, KC = a.KC, nch = p.nch, R = p.R, S = g.stages;
     GPROBE(1);
     gemv_quantize_x(a, xs, is_writer, g, tid);
     GPROBE(2);
-#ifdef LUM_PROBE
-    if (blockIdx.x == 0 && tid == 0) { g_probe[8] = 0; g_probe[9] = 0; g_probe[10] = (unsigned long long)clock64(); }
-#endif
 
     const int TPB = KC >> 5;                   // threads across one row chunk: one 32-block each
     const int row = tid / TPB;                 // this thread's row of the unit (512 threads = R rows x TPB blocks)
@@ -352,28 +456,27 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
         const int blk = c * TPB + ks;
 #pragma unroll
         for (int l = 0; l < 3; l++) {
-            const uint4* p = (const uint4*)(g.xq + (size_t)l * K + ((size_t)blk << 5));
-            xa[l][0] = p[0];
-            xa[l][1] = p[1];
+            const uint4* q = (const uint4*)(g.xq + (size_t)l * K + ((size_t)blk << 5));
+            xa[l][0] = q[0];
+            xa[l][1] = q[1];
         }
         sx = g.xsc[blk];
     };
     if (nch == 1) load_xblock(0);
 
-    int stage = (int)(fill_base % S);
-    uint32_t phase = (uint32_t)((fill_base / S) & 1);
-    const int n_units = sh.n_lu * sh.sub;      // stage-units of this CTA, in the producer's order
-
-    // wait for the ring stage, and afterwards hand it back
-    auto wait_full = [&]() {
-        if (!*g.abort && !mbar_wait_abortable(g.full0 + 8u * stage, phase, g.abort)) {
+    // wait for the ring stage (returns its unit id, or kMetaEnd also when the CTA is aborting), and hand it back
+    auto wait_full = [&]() -> int {
+        if (*g.abort) return kMetaEnd;
+        if (!mbar_wait_abortable(g.full0 + 8u * cr.stage, cr.par, g.abort)) {
             if (!*g.abort) { atomicOr(status, LUM_ST_WAIT_FULL); *g.abort = 1; }
+            return kMetaEnd;
         }
+        return g.meta[cr.stage];
     };
     auto release = [&]() {
         __syncwarp();
-        if (lane == 0) mbar_arrive(g.empty0 + 8u * stage);
-        if (++stage == S) { stage = 0; phase ^= 1u; }
+        if (lane == 0) mbar_arrive(g.empty0 + 8u * cr.stage);
+        if (++cr.stage == S) { cr.stage = 0; cr.par ^= 1u; }
     };
     // one stage-unit held at `sq`: this thread's 32 weights of its row against its x block
     auto unit_dot = [&](const unsigned char* sq) -> float {
@@ -393,92 +496,101 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
         return t * (sx * dw);
     };
 
+    bool ended = false;
 #pragma unroll 1
-    for (int c0 = 0; c0 < n_units; c0 += kChunkUnits) {
-        const int c1 = min(n_units, c0 + kChunkUnits);
-        // Units are finished four at a time so that one transposed butterfly (6 shuffles) reduces four row sums.
+    while (!ended) {
+        int slot = 0;                          // local unit slots filled in this chunk
 #pragma unroll 1
-        for (int u0 = c0; u0 < c1; u0 += 4) {
+        while (slot < kChunkUnits && !ended) {
+            // Units are finished four at a time so that one transposed butterfly (6 shuffles) reduces four row sums.
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            int filled = 0;
             if (nch == 1) {
-                // a fill = two units (two row groups, same x): both dot products run side by side
+                // a fill = a job = two units (two row groups, same x): both dot products run side by side
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
-                    if (u0 + 2 * j < c1) {
-                        wait_full();
-                        const unsigned char* sq = g.stage0 + (size_t)stage * kFillBytes;
-                        const bool two = u0 + 2 * j + 1 < c1;
-                        const float va = unit_dot(sq);
-                        const float vb = two ? unit_dot(sq + kStageBytes) : 0.0f;
-                        acc[2 * j] = va;
-                        acc[2 * j + 1] = vb;
-                        release();
+                    if (!ended) {
+                        const int u = wait_full();
+                        if (u == kMetaEnd) {
+                            ended = true;
+                            if (!*g.abort) release();
+                        } else {
+                            const unsigned char* sq = g.stage0 + (size_t)cr.stage * kFillBytes;
+                            const bool two = u + 1 < p.U;
+                            acc[2 * j] = unit_dot(sq);
+                            acc[2 * j + 1] = two ? unit_dot(sq + kStageBytes) : 0.0f;
+                            if (tid == 0) { g.unit_of[slot + 2 * j] = u; g.unit_of[slot + 2 * j + 1] = u + 1; }
+                            filled = 2 * j + (two ? 2 : 1);
+                            release();
+                        }
                     }
                 }
             } else {
-                // a fill = two K-chunks of one unit
+                // a unit = fpu fills of two K-chunks each; they arrive back to back
 #pragma unroll
                 for (int uu = 0; uu < 4; uu++) {
-                    if (u0 + uu < c1) {
+                    if (!ended) {
 #pragma unroll 1
                         for (int c = 0; c < nch; c += 2) {
-                            wait_full();
-                            const unsigned char* sq = g.stage0 + (size_t)stage * kFillBytes;
+                            const int u = wait_full();
+                            if (u == kMetaEnd) {
+                                ended = true;
+                                if (!*g.abort) release();
+                                break;
+                            }
+                            const unsigned char* sq = g.stage0 + (size_t)cr.stage * kFillBytes;
                             load_xblock(c);
                             acc[uu] += unit_dot(sq);
                             if (c + 1 < nch) {
                                 load_xblock(c + 1);
                                 acc[uu] += unit_dot(sq + kStageBytes);
                             }
+                            if (c == 0 && tid == 0) g.unit_of[slot + uu] = u;
+                            if (c + 2 >= nch) filled = uu + 1;
                             release();
                         }
                     }
                 }
             }
-            // transposed butterfly over the lanes that share a row: afterwards one lane per unit holds its sum
-            const int ub = u0 - c0;            // unit index inside the chunk
-            if (TPB >= 32) {
-                const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
-                const float s0 = __shfl_xor_sync(0xffffffffu, h16 ? acc[0] : acc[2], 16);
-                const float s1 = __shfl_xor_sync(0xffffffffu, h16 ? acc[1] : acc[3], 16);
-                const float a0 = (h16 ? acc[2] : acc[0]) + s0, a1 = (h16 ? acc[3] : acc[1]) + s1;
-                float v = (h8 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h8 ? a0 : a1, 8);
-                v += __shfl_xor_sync(0xffffffffu, v, 4);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                const int uidx = (h16 ? 2 : 0) + (h8 ? 1 : 0);
-                if ((lane & 7) == 0 && u0 + uidx < c1) g.red[(size_t)(ub + uidx) * 32 + row * WPS + (ks >> 5)] = v;
-            } else {
-                // 16 lanes per row (KC = 512): each half-warp is one row
-                const bool h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
-                const float s0 = __shfl_xor_sync(0xffffffffu, h8 ? acc[0] : acc[2], 8);
-                const float s1 = __shfl_xor_sync(0xffffffffu, h8 ? acc[1] : acc[3], 8);
-                const float a0 = (h8 ? acc[2] : acc[0]) + s0, a1 = (h8 ? acc[3] : acc[1]) + s1;
-                float v = (h4 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h4 ? a0 : a1, 4);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                const int uidx = (h8 ? 2 : 0) + (h4 ? 1 : 0);
-                if ((lane & 3) == 0 && u0 + uidx < c1) g.red[(size_t)(ub + uidx) * 32 + row] = v;
+            if (filled > 0) {
+                // transposed butterfly over the lanes that share a row: afterwards one lane per unit holds its sum
+                if (TPB >= 32) {
+                    const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
+                    const float s0 = __shfl_xor_sync(0xffffffffu, h16 ? acc[0] : acc[2], 16);
+                    const float s1 = __shfl_xor_sync(0xffffffffu, h16 ? acc[1] : acc[3], 16);
+                    const float a0 = (h16 ? acc[2] : acc[0]) + s0, a1 = (h16 ? acc[3] : acc[1]) + s1;
+                    float v = (h8 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h8 ? a0 : a1, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    const int uidx = (h16 ? 2 : 0) + (h8 ? 1 : 0);
+                    if ((lane & 7) == 0 && uidx < filled) g.red[(size_t)(slot + uidx) * 32 + row * WPS + (ks >> 5)] = v;
+                } else {
+                    // 16 lanes per row (KC = 512): each half-warp is one row
+                    const bool h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
+                    const float s0 = __shfl_xor_sync(0xffffffffu, h8 ? acc[0] : acc[2], 8);
+                    const float s1 = __shfl_xor_sync(0xffffffffu, h8 ? acc[1] : acc[3], 8);
+                    const float a0 = (h8 ? acc[2] : acc[0]) + s0, a1 = (h8 ? acc[3] : acc[1]) + s1;
+                    float v = (h4 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h4 ? a0 : a1, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    const int uidx = (h8 ? 2 : 0) + (h4 ? 1 : 0);
+                    if ((lane & 3) == 0 && uidx < filled) g.red[(size_t)(slot + uidx) * 32 + row] = v;
+                }
+                slot += filled;
             }
         }
         GPROBE(3);
-#ifdef LUM_PROBE
-        if (blockIdx.x == 0 && tid == 0) g_probe[11] = (unsigned long long)clock64();
-#endif
         named_sync(1, kConsumers);
-        // fixed-order sum of the per-warp partials -> vals, then the epilogue for this chunk's rows
-        const int cu = c1 - c0;                // units in this chunk (even in SwiGLU mode: kChunkUnits is even)
-        const int nl = cu / sh.sub;            // logical units in this chunk
-        for (int i = tid; i < cu * R; i += kConsumers) {
+        // fixed-order sum of the per-warp partials -> vals, then the epilogue for this chunk's units
+        for (int i = tid; i < slot * R; i += kConsumers) {
             const int u = i / R, r = i - u * R;
             float t = 0.0f;
             for (int wi = 0; wi < WPS; wi++) t += g.red[(size_t)u * 32 + r * WPS + wi];
-            // unit u = logical unit u / sub, half u % sub; SwiGLU wants [gate rows..., up rows...]
-            const int l = u / sh.sub, h = u - l * sh.sub;
-            g.vals[(size_t)h * nl * R + (size_t)l * R + r] = t;
+            g.vals[i] = t;
         }
         named_sync(1, kConsumers);
-        gemv_epilogue_rows(a, g.vals, (sh.lu0 + c0 / sh.sub) * R, nl * R, tid, kConsumers, g.scratch, 1, best);
+        if (slot > 0) gemv_epilogue_units(a, g.vals, g.unit_of, slot, R, tid, kConsumers, g.scratch, 1, best);
         named_sync(1, kConsumers);
     }
 }

@@ -63,6 +63,7 @@ struct GemvArgs {
     int use_pdl;
     int force_direct;      // 1: never take the streaming kernel (operator tests compare the two)
     int debug;             // tuning probes of the streaming kernel (0 in normal use)
+    unsigned int* job_ctr; // streaming kernel: zeroed counter the producers claim pooled jobs from (null: static split)
 };
 
 struct AttnArgs {

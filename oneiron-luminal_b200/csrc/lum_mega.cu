@@ -27,6 +27,8 @@ namespace lum {
 #ifdef LUM_PROBE
 // Build-time probe (never in the shipped library): %globaltimer stamps of CTA 0's phase boundaries.
 __device__ unsigned long long g_mprobe[1024];
+__device__ unsigned long long g_arrive[64 * 160];
+extern "C" int lum_arrive_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_arrive, sizeof(g_arrive)); }
 #define MPROBE(i) do { if (blockIdx.x == 0 && tid == 0 && (i) < 1024) g_mprobe[i] = globaltimer_ns(); } while (0)
 extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_mprobe, sizeof(g_mprobe)); }
 #else
@@ -35,30 +37,38 @@ extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpy
 
 // ---- grid-wide barrier ----------------------------------------------------------------------------
 // Arrival counter in global memory, only ever incremented; barrier number b (0-based since the counter
-// was last zeroed by the host) is passed when the counter reaches (b + 1) * gridDim.x.  Called by all
-// consumer threads; thread 0 arrives and polls, the rest wait on the named barrier.  The wait is bounded
+// was last zeroed by the host) completes when the counter reaches (b + 1) * gridDim.x.  Called by all
+// consumer threads; thread 0 arrives and waits, the rest wait on the named barrier.  The wait is bounded
 // (LUM_WAIT_BUDGET_CYCLES); once it runs out the kernel-wide abort flag is raised and every later wait
 // in every CTA returns at once.
 __device__ __forceinline__ void grid_barrier(const MegaArgs& a, unsigned long long& seq, volatile int* cta_abort, int tid) {
     named_sync(1, kConsumers);                      // all of this CTA's writes of the phase are issued
     if (tid == 0) {
         __threadfence();
-        atomicAdd(a.gbar, 1ull);
-        const unsigned long long target = (seq + 1ull) * gridDim.x;
-        const long long t0 = clock64();
-        unsigned int spins = 0;
-        for (;;) {
-            unsigned long long v;
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(a.gbar) : "memory");
-            if (v >= target) break;
-            if ((++spins & 63u) == 0) {
-                if (*cta_abort) break;
-                if (*(volatile int*)a.abort_flag) { *cta_abort = 1; break; }
-                if (clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) {
-                    atomicOr(a.status, LUM_ST_WAIT_GRID);
-                    *(volatile int*)a.abort_flag = 1;
-                    *cta_abort = 1;
-                    break;
+#ifdef LUM_PROBE
+        if (seq - a.gbar_base < 64) g_arrive[(seq - a.gbar_base) * 160 + blockIdx.x] = globaltimer_ns();
+#endif
+        // gbar[0] counts arrivals; gbar[16] (its own 128-byte line, so polls do not queue behind the atomics) holds the
+        // number of barriers completed.  The last CTA to arrive publishes the new generation; the others poll it.
+        const unsigned long long old = atomicAdd(a.gbar, 1ull);
+        const unsigned long long gen = seq + 1ull;
+        volatile unsigned long long* gword = a.gbar + 16;
+        if (old + 1ull == gen * gridDim.x) {
+            *gword = gen;
+        } else {
+            const long long t0 = clock64();
+            unsigned int spins = 0;
+            while (*gword < gen) {
+                __nanosleep(20);
+                if ((++spins & 255u) == 0) {
+                    if (*cta_abort) break;
+                    if (*(volatile int*)a.abort_flag) { *cta_abort = 1; break; }
+                    if (clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) {
+                        atomicOr(a.status, LUM_ST_WAIT_GRID);
+                        *(volatile int*)a.abort_flag = 1;
+                        *cta_abort = 1;
+                        break;
+                    }
                 }
             }
         }
@@ -69,7 +79,7 @@ __device__ __forceinline__ void grid_barrier(const MegaArgs& a, unsigned long lo
 }
 
 template <int HD, int GM, bool BF16>
-__device__ __forceinline__ void attn_phase(const MegaArgs& a, const MegaLayer& L, unsigned char* scratch_smem, int pos, int tid) {
+__device__ __noinline__ void attn_phase(const MegaArgs& a, const MegaLayer& L, unsigned char* scratch_smem, int pos, int tid) {
     const int items = a.n_kv * a.n_splits;
     if ((int)blockIdx.x >= items) return;           // uniform per CTA: the whole CTA skips, barriers inside stay matched
     AttnArgs t{};
@@ -134,8 +144,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
     __syncthreads();
 
     const bool is_producer = warp == kConsumers / 32;
-    long long fill = 0;                               // fills of this CTA so far (same count on both sides)
+    ProducerRing pring{0, 0u, 0};
+    ConsumerRing cring{0, 0u};
     unsigned long long seq = a.gbar_base;             // grid barriers passed so far
+    unsigned long long pseq = a.gbar_base;            // running phase number: picks the job-claim counter of each phase
+    bool producing = true;
     int pos = 0, tok = 0;
     if (!is_producer) {
         pos = a.state->pos;
@@ -160,10 +173,24 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
             const MegaLayer& L = a.layers[l];
             GemvArgs ga;
             const bool streams = phase_gemv(a, L, p, &ga);
-            GemvShare sh{};
-            if (streams) sh = gemv_share(ga, cta, ncta);
+            GemvPlan plan{};
+            if (streams) plan = gemv_plan(ga, ncta, true);
+            unsigned int* ctr = a.job_ctr + (pseq % kJobCtrRing);
+            // Re-zero the claim counter that phase pseq + 32 will use: its last user was phase pseq - 32, and no CTA can
+            // be that far behind or ahead (a producer leads its consumers by at most one ring of stages, each phase
+            // taking at least one).  Every phase does this, whether or not it streams weights itself.
+            if (cta == 0 && tid == 0) a.job_ctr[(pseq + kJobCtrRing / 2) % kJobCtrRing] = 0u;
+            pseq++;
             if (is_producer) {
-                if (streams) gemv_produce(ga, sh, g, fill, lane, a.status);
+                if (streams && lane == 0 && producing) {
+#ifdef LUM_PROBE
+                    if (t == 1 && blockIdx.x == 0) g_mprobe[512 + ph * 2] = globaltimer_ns();
+#endif
+                    producing = gemv_produce(ga, plan, g, pring, cta, ncta, ctr, a.status);
+#ifdef LUM_PROBE
+                    if (t == 1 && blockIdx.x == 0) g_mprobe[512 + ph * 2 + 1] = globaltimer_ns();
+#endif
+                }
             } else if (!streams) {
                 // RoPE + cache append + attention
                 if (t == 1) MPROBE(ph * 3);
@@ -177,7 +204,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                 else xs.x = p == 2 ? a.attn : p == 4 ? a.h : a.x;
                 ArgBest best{-INFINITY, -1};
                 if (t == 1) MPROBE(ph * 3);
-                if (!s_abort) gemv_consume(ga, xs, cta == 0, sh, g, fill, tid, a.status, &best);
+                if (!s_abort) gemv_consume(ga, xs, cta == 0, plan, g, cring, tid, a.status, &best);
                 if (t == 1) MPROBE(ph * 3 + 1);
                 if (p == 5 && tid == 0) { a.part_val[cta] = best.v; a.part_idx[cta] = best.i; }
                 grid_barrier(a, seq, &s_abort, tid);
@@ -201,14 +228,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                     // be reading them
                 }
             }
-            fill += sh.fills;
         }
         if (!is_producer && a.forced && t + 1 < a.n_tokens) tok = a.forced[t + 1];
         pos++;
     }
 
     if (is_producer) {
-        if (s_abort) gemv_producer_drain(g, fill, lane, a.status);
+        if (lane == 0 && (s_abort || !producing)) gemv_producer_drain(g, pring, a.status);
         return;
     }
     if (cta == 0 && tid == 0 && !s_abort) {

@@ -11,6 +11,8 @@ struct MegaLayer {
     void *kc, *vc;
 };
 
+constexpr int kJobCtrRing = 64;   // claim counters in rotation: a phase's counter is re-zeroed 32 phases before its next use
+
 struct MegaArgs {
     int n_layers, hidden, n_q, n_kv, hd, ffn, vocab, max_seq;
     int kc_h, kc_o, kc_f;         // K-chunks of the matrices with K = hidden, K = n_q * hd, K = ffn
@@ -33,7 +35,8 @@ struct MegaArgs {
     int head_every_token;         // 1: sample after every token (decode); 0: only after the last (prompt processing)
     int n_splits;
     int stages;
-    unsigned long long* gbar;     // grid-barrier arrival counter
+    unsigned int* job_ctr;        // [kJobCtrRing] job-claim counters, one per phase in flight (zero before first use)
+    unsigned long long* gbar;     // grid-barrier arrival counter ([0]) and completed-barrier count ([16])
     unsigned long long gbar_base; // barriers passed since the counter was zeroed
     int* abort_flag;              // kernel-wide: some wait ran out of budget
     uint32_t* status;
@@ -45,7 +48,7 @@ size_t mega_smem_bytes(int k_max, int stages);
 // number of grid barriers one launch passes (the host advances gbar_base by it)
 inline unsigned long long mega_barriers(const MegaArgs& a) {
     const unsigned long long heads = a.head_every_token ? (unsigned long long)a.n_tokens : 1ull;
-    return (unsigned long long)a.n_tokens * a.n_layers * 5ull + heads;
+    return (unsigned long long)a.n_tokens * a.n_layers * 5ull + heads;   // every phase ends in one barrier, so this is also the phase count
 }
 cudaError_t launch_mega(const MegaArgs& a, int sm_count, cudaStream_t st);
 

@@ -95,6 +95,7 @@ struct lum_rt {
     int* forced_dev = nullptr;
     unsigned long long* gbar = nullptr;
     int* abort_flag = nullptr;
+    unsigned int* job_ctr = nullptr;
     unsigned long long gbar_base = 0;
     int use_mega = 1;
 };
@@ -155,7 +156,7 @@ void free_model(lum_rt* rt) {
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
-    rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr;
+    rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
     rt->allocs.clear();
     rt->L.clear();
@@ -206,8 +207,9 @@ int check_status(lum_rt* rt) {
     if (st) {
         cudaMemsetAsync(rt->status, 0, sizeof st, rt->stream);
         if (rt->gbar) {   // an aborted persistent launch leaves its barrier count short: start over
-            cudaMemsetAsync(rt->gbar, 0, sizeof(unsigned long long), rt->stream);
+            cudaMemsetAsync(rt->gbar, 0, 32 * sizeof(unsigned long long), rt->stream);
             cudaMemsetAsync(rt->abort_flag, 0, sizeof(int), rt->stream);
+            cudaMemsetAsync(rt->job_ctr, 0, kJobCtrRing * sizeof(unsigned int), rt->stream);
             rt->gbar_base = 0;
         }
         return fail(rt, LUM_E_DEVICE, "device status 0x%x (%s%s%s%s%s%s)", st, (st & LUM_ST_WAIT_GRID) ? "grid barrier timed out; " : "",
@@ -397,13 +399,15 @@ int setup_mega(lum_rt* rt) {
     if (a.n_kv * a.n_splits > rt->sm_count || !mega_supported(a)) return 0;
     if (int r = dev_alloc(rt, (void**)&rt->mega_layers, hl.size() * sizeof(MegaLayer))) return r;
     if (int r = dev_alloc(rt, (void**)&rt->forced_dev, (size_t)d.max_seq * sizeof(int))) return r;
-    if (int r = dev_alloc(rt, (void**)&rt->gbar, sizeof(unsigned long long))) return r;
+    if (int r = dev_alloc(rt, (void**)&rt->gbar, 32 * sizeof(unsigned long long))) return r;   // [0] arrivals, [16] generation
     if (int r = dev_alloc(rt, (void**)&rt->abort_flag, sizeof(int))) return r;
+    if (int r = dev_alloc(rt, (void**)&rt->job_ctr, kJobCtrRing * sizeof(unsigned int))) return r;
+    CU(rt, cudaMemsetAsync(rt->job_ctr, 0, kJobCtrRing * sizeof(unsigned int), rt->stream));
     CU(rt, cudaMemcpyAsync(rt->mega_layers, hl.data(), hl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, rt->stream));
-    CU(rt, cudaMemsetAsync(rt->gbar, 0, sizeof(unsigned long long), rt->stream));
+    CU(rt, cudaMemsetAsync(rt->gbar, 0, 32 * sizeof(unsigned long long), rt->stream));
     CU(rt, cudaMemsetAsync(rt->abort_flag, 0, sizeof(int), rt->stream));
     CU(rt, cudaStreamSynchronize(rt->stream));
-    a.layers = rt->mega_layers; a.gbar = rt->gbar; a.abort_flag = rt->abort_flag;
+    a.layers = rt->mega_layers; a.gbar = rt->gbar; a.abort_flag = rt->abort_flag; a.job_ctr = rt->job_ctr;
     rt->mega = a;
     rt->gbar_base = 0;
     rt->mega_ok = true;
@@ -418,11 +422,11 @@ extern "C" {
 
 void lum_config_default(lum_config* c) {
     if (!c) return;
-    c->device = 0; c->use_graph = 1; c->use_pdl = 1; c->attn_splits = 0; c->use_mega = 1;
+    c->device = 0; c->use_graph = 1; c->use_pdl = 1; c->attn_splits = 0; c->use_mega = 0;
     if (const char* e = getenv("LUM_GRAPH")) c->use_graph = atoi(e);
     if (const char* e = getenv("LUM_PDL")) c->use_pdl = atoi(e);
     if (const char* e = getenv("LUM_ATTN_SPLITS")) c->attn_splits = atoi(e);
-    c->use_mega = 1;
+    c->use_mega = 0;
     if (const char* e = getenv("LUM_MEGA")) c->use_mega = atoi(e);
 }
 

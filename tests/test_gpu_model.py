@@ -16,6 +16,9 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 LOGIT_TOL = 1e-2
 
 
+_LLAMA2L = None   # oracle results of the two-layer Llama-shape case, computed once
+
+
 def rel_err(a, b):
     return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))) / np.max(np.abs(b)))
 
@@ -143,34 +146,42 @@ def test_host_supplied_weights_equal_generated(pkg, rt):
         rt.set_weight("q", 0, np.zeros(qd * H, dtype=np.float32), "f32")
 
 
-def test_llama_shape_two_layers_32_steps(pkg, rt):
+@pytest.mark.parametrize("mega", [0, 1])
+def test_llama_shape_two_layers_32_steps(pkg, mega):
     """Real Llama-3-8B tile shapes (hidden 4096, ffn 14336, 32/8 heads of 128) cut to 2 layers and a 4096 vocabulary
     so the oracle finishes in seconds: 32 greedy steps identical, logits within tolerance at the end."""
     desc = pkg.CONFIGS["llama3_8b_q8_2layer"]
     seed = 2024
-    orc = OracleModel(desc)
-    orc.synth(seed)
-    prompt = orc.synth_tokens(seed, 24)
-    rt.load_model(desc)
-    rt.synth(seed)
-    got = rt.generate(prompt, 33)
-    lg = rt.get_f32()
-    want, lo, margins = orc.generate(prompt, 33, return_last_logits=True, return_margins=True)
+    global _LLAMA2L
+    if _LLAMA2L is None:
+        orc = OracleModel(desc)
+        orc.synth(seed)
+        prompt = orc.synth_tokens(seed, 24)
+        _LLAMA2L = (prompt,) + orc.generate(prompt, 33, return_last_logits=True, return_margins=True)
+    prompt, want, lo, margins = _LLAMA2L
+    rt = pkg.B200Runtime.initialize(device=0, use_mega=bool(mega))
+    try:
+        rt.load_model(desc)
+        rt.synth(seed)
+        got = rt.generate(prompt, 33)
+        lg = rt.get_f32()
+    finally:
+        rt.close()
     assert got == want, f"min oracle top-1/top-2 margin {min(margins):.3e}"
     assert rel_err(lg, lo) <= LOGIT_TOL
 
 
-@pytest.mark.parametrize("graph,pdl", [(0, 0), (1, 0), (0, 1), (1, 1)])
-def test_launch_modes_agree(pkg, rt, graph, pdl):
-    """The persistent whole-token kernel (the default where the model allows it), plain launches, a captured graph,
-    and programmatic dependent launch all compute the same thing, bit for bit."""
+@pytest.mark.parametrize("graph,pdl,mega", [(0, 0, 0), (1, 0, 0), (0, 1, 0), (1, 1, 1), (0, 0, 1)])
+def test_launch_modes_agree(pkg, rt, graph, pdl, mega):
+    """Plain launches, a captured graph, programmatic dependent launch and the persistent whole-token kernel all
+    compute the same thing, bit for bit."""
     desc = pkg.CONFIGS["small_q8"]
     prompt = [5, 17, 1000, 2, 2, 77]
     rt.load_model(desc)
     rt.synth(3)
     base = rt.generate(prompt, 12)
     lb = rt.get_f32()
-    other = pkg.B200Runtime.initialize(device=0, use_graph=bool(graph), use_pdl=bool(pdl), use_mega=False)
+    other = pkg.B200Runtime.initialize(device=0, use_graph=bool(graph), use_pdl=bool(pdl), use_mega=bool(mega))
     try:
         other.load_model(desc)
         other.synth(3)
