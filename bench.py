@@ -191,7 +191,9 @@ def kernel_roofline(pkg, torch, peaks, peak_kind):
     return {"bound": "hbm", "kernel": "q8_gemv_stream", "shape": f"N={n} K={k} (gate+up sized), alone, back to back",
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
             "peak_kind": f"of {peak_kind} (burst copy)", "us_per_launch": ms * 1000.0, "bytes_per_launch": bytes_per_launch,
-            "traffic": None}, launches + 4
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised in
+            # profiles/q8_gemv_stream_gateup_shape.md (124.87 MB read + 5.91 MB written)
+            "traffic": 130_772_736}, launches + 4
 
 
 def run_ours(args, pkg):
