@@ -87,8 +87,7 @@ typedef struct lum_model_desc {
     int32_t tied_head;      /* lm_head = embedding table (examples/qwen/src/model.rs:127) */
     int32_t max_new_tokens; /* capacity of the on-device token log of lum_decode_greedy */
     /* tensor parallel: this rank's shard.  1/0 = whole model.  Heads and FFN columns are split
-     * evenly; o/down hold a K-slice and their outputs are summed over ranks by the caller's
-     * collective (see lum_tp_*). */
+     * evenly; o/down hold a K-slice and their outputs are summed over the ranks (see lum_tp_init). */
     int32_t tp_size, tp_rank;
 } lum_model_desc;
 
@@ -148,6 +147,18 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec_per_step, char* dis
 int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n);
 /* CUDA stream the runtime launches on (a cudaStream_t), for callers that time with their own events. */
 void* lum_stream(lum_rt* rt);
+
+/* ---------------------------------------------------------------------------------------------
+ * Tensor parallelism over the GPUs of one node: one process and one runtime per GPU (the reference is single-GPU:
+ * crates/luminal_cuda/src/runtime.rs:123-130; nothing there to replace).  Rank 0 makes an id, the host ships its 128
+ * bytes to the other ranks by any means (the Python host uses torch.distributed), every rank joins, then loads the
+ * model with the same tp_size and its own tp_rank in lum_model_desc.  Attention heads and FFN columns are sharded;
+ * the partial sums of the o and down projections are all-reduced (NCCL, one per projection) and join the residual
+ * stream in the next projection's prologue; the vocabulary is sharded and the greedy sample is folded over the
+ * ranks' best rows, so every rank ends each step with the same token.  NCCL is loaded at run time by these calls only.
+ */
+int32_t lum_tp_unique_id(uint8_t* out128);
+int32_t lum_tp_init(lum_rt* rt, const uint8_t* id128, int32_t tp_size, int32_t tp_rank);
 
 /* ---------------------------------------------------------------------------------------------
  * Stand-alone operators (one launch each; device pointers).  These are the block ops of

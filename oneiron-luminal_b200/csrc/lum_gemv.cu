@@ -54,9 +54,14 @@ __device__ __forceinline__ void argmax_finish(const GemvArgs& a, ArgBest mine, i
     named_sync(bar_id, nthreads);
     if (s_last && tid < 32) {
         __threadfence();
-        const int fi = argmax_final(a.part_val, a.part_idx, (int)gridDim.x, tid);
+        const ArgBest fb = argmax_final(a.part_val, a.part_idx, (int)gridDim.x, tid);
+        const int fi = fb.i;
         if (tid == 0) {
-            DecodeState* st = a.state;
+            DecodeState* st = a.pair_out ? nullptr : a.state;
+            if (a.pair_out) {   // tensor parallel: publish this shard's best; the ranks' pairs are folded after an all-gather
+                a.pair_out[0] = __float_as_int(fb.v);
+                a.pair_out[1] = fi >= 0 ? fi + a.row_offset : -1;
+            }
             if (st) {
                 const int step = st->step;
                 st->last_tok = fi;

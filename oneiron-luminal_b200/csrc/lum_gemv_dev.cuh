@@ -191,7 +191,7 @@ __device__ __forceinline__ void gemv_epilogue_rows(const GemvArgs& a, const floa
 
 // Reduce the per-CTA partial maxima published in part_val / part_idx (one per CTA) to the sample.
 // Called by one warp; every lane returns the winner.  Reads go through L2 (written by other CTAs).
-__device__ __forceinline__ int argmax_final(const float* part_val, const int* part_idx, int n_cta, int lane) {
+__device__ __forceinline__ ArgBest argmax_final(const float* part_val, const int* part_idx, int n_cta, int lane) {
     ArgBest f{-INFINITY, -1};
     for (int c = lane; c < n_cta; c += 32) argbest_take(f, __ldcg(part_val + c), __ldcg(part_idx + c));
 #pragma unroll
@@ -200,7 +200,7 @@ __device__ __forceinline__ int argmax_final(const float* part_val, const int* pa
         const int oi = __shfl_xor_sync(0xffffffffu, f.i, o);
         argbest_take(f, ov, oi);
     }
-    return f.i;
+    return f;
 }
 
 // Where a phase's activations come from.

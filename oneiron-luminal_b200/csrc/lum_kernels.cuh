@@ -55,6 +55,9 @@ struct GemvArgs {
     DecodeState* state;
     int* tokens_out;
     int advance;           // 1: the sampler also advances pos/step and feeds the token back
+    int* pair_out;         // tensor parallel: instead of touching the state, store {bits of the best logit, its global row}
+                           // of this rank's vocabulary shard here (2 ints); rows are offset by row_offset
+    int row_offset;
     uint32_t* status;
     // geometry of the streaming kernel
     int KC;                // K-chunk per stage (power of two, divides K, 512..4096)
@@ -106,6 +109,8 @@ cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 bool gemv_stream_supported(const GemvArgs& a);
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t st);
 cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
+// tensor parallel: fold the ranks' {logit bits, row} pairs into the sample (last maximum wins) and advance the state
+cudaError_t launch_tp_pick(const int* pairs, int n_ranks, DecodeState* state, int* tokens_out, int advance, cudaStream_t st);
 
 // synthetic tensors + format conversion
 cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,

@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                 if (p == 5) {
                     // every CTA folds the per-CTA maxima itself: all of them need the token for the next embedding row
                     if (warp == 0) {
-                        const int fi = argmax_final(a.part_val, a.part_idx, ncta, lane);
+                        const int fi = argmax_final(a.part_val, a.part_idx, ncta, lane).i;
                         if (lane == 0) s_tok = fi;
                     }
                     named_sync(1, kConsumers);

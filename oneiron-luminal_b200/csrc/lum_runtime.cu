@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <dlfcn.h>
 #include <string>
 #include <vector>
 
@@ -30,6 +31,39 @@ using namespace lum;
 namespace {
 
 thread_local std::string g_create_error;
+
+// NCCL is resolved at run time (dlopen), so single-GPU users never load it and there is no link-time dependency.
+// Only the handful of entry points the tensor-parallel path needs; signatures as in nccl.h.
+struct NcclApi {
+    typedef struct { char internal[128]; } UniqueId;
+    int (*GetUniqueId)(UniqueId*) = nullptr;
+    int (*CommInitRank)(void**, int, UniqueId, int) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+    std::string why;
+};
+NcclApi& nccl() {
+    static NcclApi api = [] {
+        NcclApi a;
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) { a.why = std::string("cannot load libnccl.so.2: ") + dlerror(); return a; }
+        a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+        a.CommInitRank = (decltype(a.CommInitRank))dlsym(h, "ncclCommInitRank");
+        a.CommDestroy = (decltype(a.CommDestroy))dlsym(h, "ncclCommDestroy");
+        a.AllReduce = (decltype(a.AllReduce))dlsym(h, "ncclAllReduce");
+        a.AllGather = (decltype(a.AllGather))dlsym(h, "ncclAllGather");
+        a.GetErrorString = (decltype(a.GetErrorString))dlsym(h, "ncclGetErrorString");
+        a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.AllGather && a.GetErrorString;
+        if (!a.ok) a.why = "libnccl is missing an entry point";
+        return a;
+    }();
+    return api;
+}
+constexpr int kNcclFloat32 = 7, kNcclInt32 = 2, kNcclSum = 0;   // ncclDataType_t / ncclRedOp_t values of nccl.h
 
 struct Tensor {
     void* w = nullptr;       // quants / f32 / bf16
@@ -87,6 +121,13 @@ struct lum_rt {
 
     uint64_t dim_s = 1, dim_p = 0;
     std::vector<int32_t> tokens_in;
+
+    // tensor parallel
+    void* comm = nullptr;             // ncclComm_t
+    int tp_size = 1, tp_rank = 0;
+    float* x2 = nullptr;              // second residual buffer (the stream alternates between x and x2)
+    float* part = nullptr;            // this rank's partial o / down projection, all-reduced in place
+    int* tp_pairs = nullptr;          // [tp_size][2] sampling candidates after the all-gather; this rank's own pair at [tp_size]
 
     // whole-token persistent kernel
     bool mega_ok = false;
@@ -222,12 +263,31 @@ int check_status(lum_rt* rt) {
 
 // ---- the per-token schedule ---------------------------------------------------------------------
 // Issues the kernels of one token on rt->stream.  with_head: include final norm + lm_head + sampler.
+//
+// Tensor parallel (tp_size > 1): q/k/v/gate/up are row shards, o/down are K shards whose outputs are partial sums.
+// The partial goes to `part`, is all-reduced in place, and joins the residual stream in the prologue of the next
+// projection (x_new = x + part, also written to the other residual buffer), so the residual add costs no kernel.
 int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
     const lum_model_desc& d = rt->d;
     const int H = d.hidden, hd = d.head_dim;
     const int gk = kind_of(d.embed_dtype);
+    const bool tp = rt->tp_size > 1;
     int n = 0;
     cudaStream_t st = rt->stream;
+    float* cur = rt->x;                 // residual stream lives here ...
+    float* other = rt->x2;              // ... and moves here when a partial sum joins it
+    bool pending = false;               // `part` holds a reduced partial that has not joined the stream yet
+
+    auto all_reduce = [&]() -> int {
+        const int rc = nccl().AllReduce(rt->part, rt->part, (size_t)H, kNcclFloat32, kNcclSum, rt->comm, st);
+        if (rc) return fail(rt, LUM_E_CUDA, "ncclAllReduce: %s", nccl().GetErrorString(rc));
+        n++;
+        return 0;
+    };
+    auto take_partial = [&](GemvArgs& g) {   // the projection's prologue folds the reduced partial into the stream
+        g.x = cur;
+        if (pending) { g.x_add = rt->part; g.x_out = other; float* t = cur; cur = other; other = t; pending = false; }
+    };
 
     EmbedArgs e{};
     e.table = rt->embed.w; e.kind = rt->embed.kind; e.H = H; e.x = rt->x; e.state = rt->state; e.status = rt->status;
@@ -243,7 +303,8 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows, w.q.kc};
         a.seg[1] = {w.k.w, w.k.s, (int)w.k.rows, w.k.kc};
         a.seg[2] = {w.v.w, w.v.s, (int)w.v.rows, w.v.kc};
-        a.K = H; a.epi = EPI_STORE; a.x = rt->x; a.gain = w.attn_norm.w; a.y = rt->qkv;
+        a.K = H; a.epi = EPI_STORE; a.gain = w.attn_norm.w; a.y = rt->qkv;
+        take_partial(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
 
         AttnArgs t{};
@@ -256,36 +317,52 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         t.theta = d.rope_theta; t.window = 0; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
         CU(rt, launch_attn_decode(t, st)); n++;
 
-        // o projection + residual
+        // o projection (+ residual)
         GemvArgs o{};
         o.status = rt->status; o.use_pdl = pdl; o.wkind = w.o.kind;
         o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows, w.o.kc};
-        o.K = (int)w.o.cols; o.epi = EPI_RESID; o.x = rt->attn; o.y = rt->x; o.resid = rt->x;
+        o.K = (int)w.o.cols; o.x = rt->attn;
+        if (tp) { o.epi = EPI_STORE; o.y = rt->part; }
+        else { o.epi = EPI_RESID; o.y = cur; o.resid = cur; }
         CU(rt, launch_gemv(o, rt->sm_count, st)); n++;
+        if (tp) { if (int r = all_reduce()) return r; pending = true; }
 
         // RMSNorm + gate, up + SwiGLU
         GemvArgs g{};
         g.status = rt->status; g.use_pdl = pdl; g.gain_kind = gk; g.eps = rt->eps6; g.wkind = w.gate.kind;
         g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows, w.gate.kc}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows, w.up.kc};
-        g.K = H; g.epi = EPI_SWIGLU; g.x = rt->x; g.gain = w.mlp_norm.w; g.y = rt->h;
+        g.K = H; g.epi = EPI_SWIGLU; g.gain = w.mlp_norm.w; g.y = rt->h;
+        take_partial(g);
         CU(rt, launch_gemv(g, rt->sm_count, st)); n++;
 
-        // down projection + residual
+        // down projection (+ residual)
         GemvArgs dn{};
         dn.status = rt->status; dn.use_pdl = pdl; dn.wkind = w.down.kind;
         dn.nseg = 1; dn.seg[0] = {w.down.w, w.down.s, (int)w.down.rows, w.down.kc};
-        dn.K = (int)w.down.cols; dn.epi = EPI_RESID; dn.x = rt->h; dn.y = rt->x; dn.resid = rt->x;
+        dn.K = (int)w.down.cols; dn.x = rt->h;
+        if (tp) { dn.epi = EPI_STORE; dn.y = rt->part; }
+        else { dn.epi = EPI_RESID; dn.y = cur; dn.resid = cur; }
         CU(rt, launch_gemv(dn, rt->sm_count, st)); n++;
+        if (tp) { if (int r = all_reduce()) return r; pending = true; }
     }
     if (with_head) {
         const Tensor& hw = d.tied_head ? rt->embed : rt->lm_head;
         GemvArgs a{};
         a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = hw.kind;
         a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows, hw.kc};
-        a.K = H; a.epi = EPI_ARGMAX; a.x = rt->x; a.gain = rt->final_norm.w; a.y = rt->logits;
+        a.K = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
+        take_partial(a);
+        if (tp) { a.pair_out = rt->tp_pairs + 2 * rt->tp_size; a.row_offset = rt->tp_rank * rt->vocab_l; }
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
+        if (tp) {
+            // every rank needs every shard's best row: all-gather the pairs, then fold them the same way everywhere
+            const int rc = nccl().AllGather(rt->tp_pairs + 2 * rt->tp_size, rt->tp_pairs, 2, kNcclInt32, rt->comm, st);
+            if (rc) return fail(rt, LUM_E_CUDA, "ncclAllGather: %s", nccl().GetErrorString(rc));
+            CU(rt, launch_tp_pick(rt->tp_pairs, rt->tp_size, rt->state, rt->tokens_out, 1, st));
+            n += 2;
+        }
     }
     if (n_launch) *n_launch = n;
     return 0;
@@ -362,7 +439,7 @@ int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
 int setup_mega(lum_rt* rt) {
     rt->mega_ok = false;
     const lum_model_desc& d = rt->d;
-    if (d.weight_dtype != LUM_Q8_0 || d.tied_head) return 0;
+    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || rt->tp_size > 1) return 0;
     std::vector<MegaLayer> hl((size_t)d.n_layers);
     bool packed = rt->lm_head.kc > 0;
     for (int l = 0; l < d.n_layers && packed; l++) {
@@ -457,6 +534,7 @@ void lum_destroy(lum_rt* rt) {
     cudaSetDevice(rt->cfg.device);
     cudaStreamSynchronize(rt->stream);
     free_model(rt);
+    if (rt->comm) nccl().CommDestroy(rt->comm);
     cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -472,6 +550,32 @@ int32_t lum_device_info(const lum_rt* rt, int32_t* sm_count, uint64_t* mem_bytes
 }
 
 void* lum_stream(lum_rt* rt) { return rt ? (void*)rt->stream : nullptr; }
+
+int32_t lum_tp_unique_id(uint8_t* out128) {
+    if (!out128) return LUM_E_INVALID;
+    if (!nccl().ok) return fail(nullptr, LUM_E_UNSUPPORTED, "%s", nccl().why.c_str());
+    NcclApi::UniqueId id;
+    const int rc = nccl().GetUniqueId(&id);
+    if (rc) return fail(nullptr, LUM_E_CUDA, "ncclGetUniqueId: %s", nccl().GetErrorString(rc));
+    memcpy(out128, id.internal, 128);
+    return 0;
+}
+
+int32_t lum_tp_init(lum_rt* rt, const uint8_t* id128, int32_t tp_size, int32_t tp_rank) {
+    if (!rt || !id128) return LUM_E_INVALID;
+    if (tp_size < 1 || tp_size > 8 || tp_rank < 0 || tp_rank >= tp_size) return fail(rt, LUM_E_INVALID, "tp_init: rank %d of %d", tp_rank, tp_size);
+    if (rt->has_model) return fail(rt, LUM_E_INVALID, "tp_init: join the group before loading a model");
+    if (rt->comm) return fail(rt, LUM_E_INVALID, "tp_init: already in a group");
+    if (tp_size == 1) { rt->tp_size = 1; rt->tp_rank = 0; return 0; }
+    if (!nccl().ok) return fail(rt, LUM_E_UNSUPPORTED, "%s", nccl().why.c_str());
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    NcclApi::UniqueId id;
+    memcpy(id.internal, id128, 128);
+    const int rc = nccl().CommInitRank(&rt->comm, tp_size, id, tp_rank);
+    if (rc) { rt->comm = nullptr; return fail(rt, LUM_E_CUDA, "ncclCommInitRank: %s", nccl().GetErrorString(rc)); }
+    rt->tp_size = tp_size; rt->tp_rank = tp_rank;
+    return 0;
+}
 
 int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (!rt || !dp) return LUM_E_INVALID;
@@ -492,7 +596,10 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (d.embed_dtype != LUM_F32 && d.embed_dtype != LUM_BF16) return fail(rt, LUM_E_UNSUPPORTED, "embedding dtype must be F32 or BF16");
     if (d.kv_dtype != LUM_F32 && d.kv_dtype != LUM_BF16) return fail(rt, LUM_E_UNSUPPORTED, "KV dtype must be F32 or BF16");
     if (d.tied_head && tp > 1) return fail(rt, LUM_E_UNSUPPORTED, "tied head under tensor parallelism");
-    if (tp > 1) return fail(rt, LUM_E_UNSUPPORTED, "tensor-parallel execution is not wired in this build");
+    if (tp > 1 && (!rt->comm || rt->tp_size != tp || rt->tp_rank != d.tp_rank))
+        return fail(rt, LUM_E_INVALID, "tp_size %d / tp_rank %d need a matching lum_tp_init first", tp, d.tp_rank);
+    if (tp == 1 && rt->tp_size > 1) return fail(rt, LUM_E_INVALID, "this runtime joined a %d-rank group; the model must be sharded the same way", rt->tp_size);
+    if (d.n_q_heads % tp || (d.n_q_heads / tp) % (d.n_kv_heads / tp)) return fail(rt, LUM_E_INVALID, "query heads must divide by tp_size");
     rt->d = d;
     rt->nq_l = d.n_q_heads / tp; rt->nkv_l = d.n_kv_heads / tp; rt->ffn_l = d.ffn / tp; rt->vocab_l = d.vocab / tp;
     const int H = d.hidden, hd = d.head_dim, r = d.tp_rank;
@@ -532,6 +639,9 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     rt->n_splits = splits;
     const int G = d.n_q_heads / d.n_kv_heads;
     TRY(dev_alloc(rt, (void**)&rt->x, (size_t)H * 4));
+    TRY(dev_alloc(rt, (void**)&rt->x2, (size_t)H * 4));
+    TRY(dev_alloc(rt, (void**)&rt->part, (size_t)H * 4));
+    TRY(dev_alloc(rt, (void**)&rt->tp_pairs, (size_t)(2 * tp + 2) * 4));
     TRY(dev_alloc(rt, (void**)&rt->qkv, (qd_l + 2 * kvd_l) * 4));
     TRY(dev_alloc(rt, (void**)&rt->attn, qd_l * 4));
     TRY(dev_alloc(rt, (void**)&rt->h, (size_t)rt->ffn_l * 4));
@@ -822,7 +932,7 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
 
 int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n) {
     if (!rt || !rt->has_model || !n) return LUM_E_INVALID;
-    *n = (rt->mega_ok && rt->use_mega) ? 1 : 1 + 5 * rt->d.n_layers + 1;
+    *n = (rt->mega_ok && rt->use_mega) ? 1 : rt->tp_size > 1 ? 1 + 5 * rt->d.n_layers + 1 + 1 /* pick */ : 1 + 5 * rt->d.n_layers + 1;
     return 0;
 }
 

@@ -146,6 +146,8 @@ def load_library() -> C.CDLL:
         "lum_profile": (i32, [vp, i32, P(C.c_double), C.c_char_p, sz]),
         "lum_launches_per_step": (i32, [vp, P(i32)]),
         "lum_stream": (vp, [vp]),
+        "lum_tp_unique_id": (i32, [vp]),
+        "lum_tp_init": (i32, [vp, vp, i32, i32]),
         "lum_op_gemv_q8_0": (i32, [vp, vp, i32, i32, vp, vp, i32, vp]),
         "lum_q8_0_packed_bytes": (sz, [i32, i32]),
         "lum_op_q8_0_pack": (i32, [vp, vp, i32, i32, vp, vp]),
@@ -217,6 +219,20 @@ class B200Runtime:
     def _ck(self, rc: int) -> None:
         if rc != 0:
             raise LumError(rc, (self._lib.lum_last_error(self._h) or b"").decode())
+
+    # ---- tensor parallel ---------------------------------------------------------------------------
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        lib = load_library()
+        buf = (C.c_uint8 * 128)()
+        rc = lib.lum_tp_unique_id(buf)
+        if rc != 0:
+            raise LumError(rc, (lib.lum_last_error(None) or b"").decode())
+        return bytes(buf)
+
+    def tp_init(self, unique_id: bytes, tp_size: int, tp_rank: int) -> None:
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        self._ck(self._lib.lum_tp_init(self._h, buf, tp_size, tp_rank))
 
     def device_info(self):
         sm, mem, cc = C.c_int32(), C.c_uint64(), C.c_int32()

@@ -1,0 +1,29 @@
+"""Tensor-parallel parity on real GPUs: the model sharded over 2 (and, when present, 4) GPUs of one node produces
+the same greedy tokens as the unsharded model, every rank ends with the same tokens, and the gathered logits match.
+Runs one process per GPU under torchrun.  Skipped when fewer than 2 GPUs are visible."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gpus():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.mark.parametrize("world,cfg", [(2, "small_q8"), (2, "llama3_8b_q8_2layer"), (4, "llama3_8b_q8_2layer")])
+def test_tp_matches_single_gpu(world, cfg):
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+                        "--master-addr", "127.0.0.1", "--master-port", "29633", os.path.join(ROOT, "tests", "tp_worker.py"),
+                        cfg, "77", "20"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-4000:]
+    assert f"TP{world} OK" in r.stdout

@@ -1,0 +1,58 @@
+"""One rank of the tensor-parallel GPU test (launched under torchrun by tests/test_gpu_tp.py).  Every rank runs the
+sharded model; rank 0 also runs the same model unsharded on its GPU and compares tokens and logits."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from __graft_entry__ import load_package  # noqa: E402
+
+
+def main():
+    cfg_name, seed, n_new = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = load_package()
+    from oneiron_luminal_b200 import tp as T
+    desc = pkg.CONFIGS[cfg_name]
+    T.validate(desc, world)
+    uid = T.exchange_unique_id(dist, rank, pkg.B200Runtime.tp_unique_id, device=torch.device("cuda", local))
+    rt = pkg.B200Runtime.initialize(device=local)
+    rt.tp_init(uid, world, rank)
+    rt.load_model(desc.copy(tp_size=world, tp_rank=rank))
+    rt.synth(seed)
+    prompt = [(7 * i + 3) % desc.vocab for i in range(12)]
+    toks = rt.generate(prompt, n_new)
+    logits = rt.get_f32()                       # this rank's vocabulary shard
+    shard = desc.vocab // world
+    gathered = [torch.zeros(shard, device="cuda") for _ in range(world)]
+    dist.all_gather(gathered, torch.from_numpy(logits).cuda())
+    full = torch.cat(gathered).cpu().numpy()
+    tok_t = torch.tensor(toks, device="cuda")
+    all_toks = [torch.zeros_like(tok_t) for _ in range(world)]
+    dist.all_gather(all_toks, tok_t)
+    assert all((t == tok_t).all().item() for t in all_toks), "ranks disagree on the sampled tokens"
+    rt.close()
+    if rank == 0:
+        ref = pkg.B200Runtime.initialize(device=local)
+        ref.load_model(desc)
+        ref.synth(seed)
+        want = ref.generate(prompt, n_new)
+        want_logits = ref.get_f32()
+        ref.close()
+        err = float(np.max(np.abs(full - want_logits)) / np.max(np.abs(want_logits)))
+        assert toks == want, (toks, want)
+        assert err <= 1e-3, err
+        print(f"TP{world} OK tokens={toks[:6]}... logits_rel_err={err:.2e}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
