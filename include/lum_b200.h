@@ -180,6 +180,11 @@ int32_t lum_op_q8_0_pack(const int8_t* quants_dev, const void* scales_dev, int32
 int32_t lum_op_gemv_q8_0_packed(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev,
                                 int32_t force_direct, void* stream);
 int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tensor_id, int32_t n, int32_t k, void* packed_dev, void* stream);
+/* Vocabulary projection + greedy sample in one launch: logits[N] = W x, best_dev[0] = bit pattern of the largest logit,
+ * best_dev[1] = its row (the LAST row among equal maxima — `sample`, examples/llama/src/main.rs:137-148).  The per-CTA
+ * maxima and the arrival ticket live in a small per-device scratch buffer the library allocates on first use. */
+int32_t lum_op_sample_q8_0(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* logits_dev,
+                           int32_t* best_dev, void* stream);
 int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev, void* stream);
 /* Q8_0 wire blocks (host layout, on device) -> planes; planes -> f32. */
 int32_t lum_op_q8_0_unpack(const uint8_t* blocks_dev, size_t n_blocks, int8_t* quants_dev, void* scales_dev, void* stream);

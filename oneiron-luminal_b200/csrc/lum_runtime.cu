@@ -993,6 +993,36 @@ int32_t lum_op_gemv_q8_0_packed(const void* packed, int32_t n, int32_t k, const 
     return e == cudaSuccess ? 0 : op_fail("gemv_q8_0_packed", e);
 }
 
+// per-device scratch of lum_op_sample_q8_0: per-CTA maxima, arrival ticket, status word (allocated on first use)
+struct SampleScratch { float* val; int* idx; unsigned int* counter; uint32_t* status; };
+static SampleScratch* sample_scratch() {
+    static SampleScratch per_dev[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return nullptr;
+    SampleScratch& s = per_dev[dev];
+    if (!s.val) {
+        unsigned char* base = nullptr;
+        if (cudaMalloc((void**)&base, 4096) != cudaSuccess) return nullptr;
+        cudaMemset(base, 0, 4096);
+        s.val = (float*)base; s.idx = (int*)(base + 1024); s.counter = (unsigned int*)(base + 2048); s.status = (uint32_t*)(base + 2052);
+    }
+    return &s;
+}
+
+int32_t lum_op_sample_q8_0(const void* packed, int32_t n, int32_t k, const float* x, float* logits, int32_t* best, void* stream) {
+    const int kc = q8_pack_kc(n, k);
+    if (!packed || !x || !logits || !best || !kc) { g_create_error = "sample_q8_0: bad arguments or shape cannot be packed"; return LUM_E_INVALID; }
+    SampleScratch* sc = sample_scratch();
+    if (!sc) return op_fail("sample_q8_0 scratch", cudaErrorMemoryAllocation);
+    if (cur_sm_count() > 256) { g_create_error = "sample_q8_0: more than 256 SMs"; return LUM_E_UNSUPPORTED; }
+    GemvArgs a{};
+    a.nseg = 1; a.seg[0] = {packed, nullptr, n, kc}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_ARGMAX; a.x = x; a.y = logits;
+    a.part_val = sc->val; a.part_idx = sc->idx; a.counter = sc->counter; a.status = sc->status; a.pair_out = best; a.row_offset = 0;
+    const cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("sample_q8_0", e);
+}
+
 int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tid, int32_t n, int32_t k, void* packed, void* stream) {
     const int kc = q8_pack_kc(n, k);
     if (!packed || !kc) { g_create_error = "synth_q8_0_packed: shape cannot be packed"; return LUM_E_INVALID; }

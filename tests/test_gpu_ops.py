@@ -225,6 +225,32 @@ def test_gemv_f32(torch_cuda, lib, n, k):
     check_close(y.cpu().numpy().astype(np.float64), want.astype(np.float64), mag, k)
 
 
+def test_sample_q8_0_matches_gemv_then_argmax(torch_cuda, lib):
+    """lm_head-style projection + greedy sample in one launch; ties go to the last row."""
+    torch = torch_cuda
+    n, k = 8192, 4096
+    packed = torch.empty(lib.lum_q8_0_packed_bytes(n, k), dtype=torch.uint8, device="cuda")
+    ck(lib, lib.lum_op_synth_q8_0_packed(3, 5, n, k, packed.data_ptr(), None))
+    x = torch.randn(k, device="cuda")
+    y = torch.empty(n, device="cuda")
+    ck(lib, lib.lum_op_gemv_q8_0_packed(packed.data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, None))
+    logits = torch.full((n,), float("nan"), device="cuda")
+    best = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        ck(lib, lib.lum_op_sample_q8_0(packed.data_ptr(), n, k, x.data_ptr(), logits.data_ptr(), best.data_ptr(), None))
+        torch.cuda.synchronize()
+        assert torch.equal(logits, y)
+        b = best.cpu().numpy()
+        yv = y.cpu().numpy()
+        want = int(np.flatnonzero(yv == yv.max())[-1])
+        assert int(b[1]) == want and b[:1].view(np.float32)[0] == yv.max()
+    # all-equal logits: the last row wins
+    zero = torch.zeros(k, device="cuda")
+    ck(lib, lib.lum_op_sample_q8_0(packed.data_ptr(), n, k, zero.data_ptr(), logits.data_ptr(), best.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert int(best.cpu()[1]) == n - 1
+
+
 def test_bad_arguments_return_errors(lib):
     assert lib.lum_op_gemv_q8_0(None, None, 4, 32, None, None, 0, None) < 0
     assert b"bad arguments" in lib.lum_last_error(None)
