@@ -185,6 +185,16 @@ int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tensor_id, int32_t n, i
  * maxima and the arrival ticket live in a small per-device scratch buffer the library allocates on first use. */
 int32_t lum_op_sample_q8_0(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* logits_dev,
                            int32_t* best_dev, void* stream);
+/* Same computation and outputs as lum_op_sample_q8_0, but this entry never allocates (no counterpart in the
+ * reference).  It is for hosts that cannot call cudaMalloc when they run a step: a server that has handed all of
+ * HBM to its own weight / KV-cache arenas, or any latency-critical loop (cudaMalloc and cudaFree synchronise the
+ * device).  Its scratch is a fixed 4 KiB device array inside the library: at most 256 CTAs, i.e. devices with more
+ * than 256 SMs are refused with LUM_E_UNSUPPORTED.  All calls on a device share that array and it keeps the last
+ * call's contents (the entry clears the two words that must start at zero), so calls that could overlap on the GPU
+ * race — order them on one stream.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before starting a stream capture. */
+int32_t lum_op_sample_q8_0_static(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* logits_dev,
+                                  int32_t* best_dev, void* stream);
 int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev, void* stream);
 /* Q8_0 wire blocks (host layout, on device) -> planes; planes -> f32. */
 int32_t lum_op_q8_0_unpack(const uint8_t* blocks_dev, size_t n_blocks, int8_t* quants_dev, void* scales_dev, void* stream);

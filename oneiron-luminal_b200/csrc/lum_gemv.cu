@@ -325,3 +325,61 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
 }
 
 }  // namespace lum
+
+// ------------------------------------------------------------------------------ sampling without allocating
+//
+// lum_op_sample_q8_0_static: the vocabulary projection + greedy sample of lum_op_sample_q8_0, for hosts that must
+// not allocate device memory at call time.  That is the situation of a runtime embedded in a server that has
+// already given every byte of HBM to its own arenas (weights, KV cache), where a cudaMalloc would fail — and of
+// any caller on a latency-critical path, because cudaMalloc and cudaFree synchronise the whole device.
+//
+// The kernel's scratch (one best-logit / best-row pair per CTA, the arrival ticket, a status word) lives in the
+// fixed array below instead of an allocated buffer.  Consequences, all part of the contract:
+//   * capacity: 256 CTAs.  The kernel runs one CTA per SM, so a device with more than 256 SMs is refused.
+//   * every GPU that loads this library carries the 4 KiB array until the process exits;
+//   * every call on a device shares it, and it keeps the previous call's contents: the entry zeroes the ticket and the
+//     status word on the caller's stream before each launch, the rest is overwritten by the kernel before it is read;
+//   * two calls whose kernels could overlap on one GPU (different streams, no dependency) race on it — order them;
+//   * the array's name is only a host-side handle; its device address is looked up with cudaGetSymbolAddress the first
+//     time the entry is called on a device (with that device current).  That first call does this one-time set-up
+//     and should therefore be made before any stream capture begins.
+static __device__ __align__(256) unsigned char g_sample_static[4096];
+constexpr int kStaticMaxCtas = 256;     // 256 floats + 256 ints + ticket + status = 2056 bytes of the 4096
+
+extern "C" int32_t lum_op_sample_q8_0_static(const void* packed, int32_t n, int32_t k, const float* x, float* logits,
+                                            int32_t* best, void* stream) {
+    using namespace lum;
+    static unsigned char* dev_ptr[64] = {nullptr};      // device address of the array, per device ordinal
+    const int kc = q8_pack_kc(n, k);
+    if (!packed || !x || !logits || !best || !kc) {
+        set_op_error("sample_q8_0_static: bad arguments or shape cannot be packed (needs K % 512 == 0, K <= 16384, N % (16384 / KC) == 0)");
+        return -1;
+    }
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) { set_op_error("sample_q8_0_static: cannot query the current device"); return -2; }
+    if (sms > kStaticMaxCtas) {
+        set_op_error("sample_q8_0_static: this device has more than 256 SMs; the static scratch holds one slot per CTA for at most 256");
+        return -3;
+    }
+    if (!dev_ptr[dev]) {
+        // one-time set-up for this device: the symbol's device address (a kernel given the host-side name would fault)
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_sample_static);
+        if (e != cudaSuccess || !p) { set_op_error("sample_q8_0_static: cudaGetSymbolAddress failed"); return -2; }
+        dev_ptr[dev] = (unsigned char*)p;
+    }
+    unsigned char* base = dev_ptr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+    e = cudaMemsetAsync(base + 2048, 0, 8, st);         // arrival ticket and status word start at zero
+    if (e != cudaSuccess) { set_op_error("sample_q8_0_static: clearing the ticket failed"); return -2; }
+    GemvArgs a{};
+    a.nseg = 1; a.seg[0] = {packed, nullptr, n, kc}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_ARGMAX; a.x = x; a.y = logits;
+    a.part_val = (float*)base; a.part_idx = (int*)(base + 1024); a.counter = (unsigned int*)(base + 2048);
+    a.status = (uint32_t*)(base + 2052); a.pair_out = best; a.row_offset = 0;
+    e = launch_gemv(a, sms, st);
+    if (e != cudaSuccess) { set_op_error(cudaGetErrorString(e)); return -2; }
+    return 0;
+}
+

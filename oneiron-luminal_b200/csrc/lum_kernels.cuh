@@ -104,6 +104,9 @@ struct EmbedArgs {
     int use_pdl;
 };
 
+// message of the last failed stand-alone operator on this thread (read back through lum_last_error(NULL))
+void set_op_error(const char* msg);
+
 // launchers (each returns the CUDA error of the launch)
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 bool gemv_stream_supported(const GemvArgs& a);

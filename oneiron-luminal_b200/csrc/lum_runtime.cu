@@ -87,6 +87,8 @@ struct LayerW {
 
 }  // namespace
 
+void lum::set_op_error(const char* msg) { g_create_error = msg ? msg : ""; }
+
 struct lum_rt {
     lum_config cfg{};
     int sm_count = 0;
