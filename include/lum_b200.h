@@ -104,6 +104,22 @@ int32_t lum_model_get_weight_f32(lum_rt* rt, int32_t slot, int32_t layer, size_t
 /* Bytes of weights a decode step streams from HBM (all linear planes + gains + one embedding row). */
 int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes);
 
+/* `Runtime::load_llir(&LLIRGraph)` (src/op.rs:16; crates/luminal_cuda/src/runtime.rs:470-585) for graphs serialised as
+ * include/lum_llir.h describes.  The block ops are matched against the Llama-style decoder schedule this runtime
+ * implements (csrc/lum_llir.cu lists the pattern); the hyper-parameters and the Input-node -> weight-slot map come out
+ * of the graph, while cache capacity and cache dtype — caller-owned buffers in the reference (main.rs:19,48) — are
+ * arguments.  A graph of another shape is refused (LUM_E_INVALID, message names the node); there is no fallback.
+ * lum_llir_describe does the recognition alone and needs no GPU. */
+int32_t lum_llir_describe(const uint8_t* blob, size_t size, lum_model_desc* desc_out, int64_t* token_input, int64_t* pos_input,
+                          int64_t* logits_output, char* err, size_t err_len);
+int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_seq, uint32_t kv_dtype, int32_t max_new_tokens);
+/* `set_data(node_id, data)` keyed by the HLIR node id of an Input op, as in the reference
+ * (crates/luminal_cuda/src/runtime.rs:160-165; NativeRuntime::set_data src/hlir.rs:1517-1533): weights in their wire
+ * dtype, the token-id input as Int, the position-id input as Int (checked against 'p'). */
+int32_t lum_set_input(lum_rt* rt, int64_t hlir_node, const void* host, size_t bytes, uint32_t dtype);
+/* `get_f32(node_id)` for the graph's Output: the logits of the last row (n = vocab). */
+int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n);
+
 /* KV cache: owned by the runtime (the reference has caller-owned buffers whose raw addresses are
  * baked into op payloads, examples/llama/src/model.rs:194-223).  reset = `KVCache::reset`. */
 int32_t lum_kv_reset(lum_rt* rt);

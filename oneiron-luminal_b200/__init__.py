@@ -8,7 +8,7 @@ reference's runtime interface (``luminal::op::Runtime``, src/op.rs:10-30, and th
 There is no CPU path: importing works anywhere, but creating a runtime without the built
 library or without a CUDA device raises.
 """
-from . import tp  # noqa: F401
+from . import llir, tp  # noqa: F401
 from .runtime import (  # noqa: F401
     B200Runtime,
     LumError,
@@ -19,4 +19,5 @@ from .runtime import (  # noqa: F401
     load_library,
     library_path,
     decode_bytes_per_token,
+    describe_llir,
 )

@@ -28,6 +28,14 @@
 
 using namespace lum;
 
+// csrc/lum_llir.cu
+struct lum_llir_plan;
+int lum_llir_make_plan(const uint8_t* blob, size_t size, lum_llir_plan** out, std::string* err);
+void lum_llir_free_plan(lum_llir_plan* p);
+int lum_llir_lookup(const lum_llir_plan* p, int64_t hlir_node, int* slot, int* layer);
+const lum_model_desc* lum_llir_desc(const lum_llir_plan* p);
+void lum_llir_io(const lum_llir_plan* p, int64_t* tok, int64_t* pos, int64_t* out);
+
 namespace {
 
 thread_local std::string g_create_error;
@@ -123,6 +131,8 @@ struct lum_rt {
 
     uint64_t dim_s = 1, dim_p = 0;
     std::vector<int32_t> tokens_in;
+
+    lum_llir_plan* llir = nullptr;    // set by lum_load_llir: which Input node feeds which weight slot
 
     // tensor parallel
     void* comm = nullptr;             // ncclComm_t
@@ -537,6 +547,7 @@ void lum_destroy(lum_rt* rt) {
     cudaStreamSynchronize(rt->stream);
     free_model(rt);
     if (rt->comm) nccl().CommDestroy(rt->comm);
+    if (rt->llir) lum_llir_free_plan(rt->llir);
     cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -552,6 +563,51 @@ int32_t lum_device_info(const lum_rt* rt, int32_t* sm_count, uint64_t* mem_bytes
 }
 
 void* lum_stream(lum_rt* rt) { return rt ? (void*)rt->stream : nullptr; }
+
+int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_seq, uint32_t kv_dtype, int32_t max_new_tokens) {
+    if (!rt || !blob) return fail(rt, LUM_E_INVALID, "load_llir: null argument");
+    lum_llir_plan* plan = nullptr;
+    std::string err;
+    if (int r = lum_llir_make_plan(blob, size, &plan, &err)) return fail(rt, r, "load_llir: %s", err.c_str());
+    lum_model_desc d = *lum_llir_desc(plan);
+    d.max_seq = max_seq; d.kv_dtype = kv_dtype; d.max_new_tokens = max_new_tokens;
+    d.tp_size = rt->tp_size; d.tp_rank = rt->tp_rank;
+    const int r = lum_model_init(rt, &d);
+    if (r) { lum_llir_free_plan(plan); return r; }
+    if (rt->llir) lum_llir_free_plan(rt->llir);
+    rt->llir = plan;
+    return 0;
+}
+
+int32_t lum_set_input(lum_rt* rt, int64_t hlir_node, const void* host, size_t bytes, uint32_t dtype) {
+    if (!rt || !rt->llir || !rt->has_model) return fail(rt, LUM_E_INVALID, "set_input: no graph loaded (lum_load_llir)");
+    if (!host) return fail(rt, LUM_E_INVALID, "set_input: null data");
+    int64_t tok, pos, out;
+    lum_llir_io(rt->llir, &tok, &pos, &out);
+    if (hlir_node == tok) {
+        if (dtype != LUM_INT || bytes % 4) return fail(rt, LUM_E_INVALID, "set_input: token ids must be Int");
+        return lum_set_tokens(rt, (const int32_t*)host, bytes / 4);
+    }
+    if (hlir_node == pos) {
+        // positions are implied by 'p' (p .. p+s-1); accept the reference's set_data call and check it agrees
+        if (dtype != LUM_INT || bytes % 4) return fail(rt, LUM_E_INVALID, "set_input: position ids must be Int");
+        const int32_t* v = (const int32_t*)host;
+        for (size_t i = 0; i < bytes / 4; i++)
+            if ((uint64_t)v[i] != rt->dim_p + i) return fail(rt, LUM_E_INVALID, "set_input: position ids must be p, p+1, ... (set 'p' first)");
+        return 0;
+    }
+    int slot = 0, layer = 0;
+    if (!lum_llir_lookup(rt->llir, hlir_node, &slot, &layer)) return fail(rt, LUM_E_INVALID, "set_input: node %lld is not an Input of the loaded graph", (long long)hlir_node);
+    return lum_model_set_weight(rt, slot, layer, host, bytes, dtype);
+}
+
+int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n) {
+    if (!rt || !rt->llir) return fail(rt, LUM_E_INVALID, "get_output: no graph loaded (lum_load_llir)");
+    int64_t tok, pos, out;
+    lum_llir_io(rt->llir, &tok, &pos, &out);
+    if (hlir_node != out) return fail(rt, LUM_E_INVALID, "get_output: node %lld is not the graph's Output", (long long)hlir_node);
+    return lum_get_logits(rt, host_out, n);
+}
 
 int32_t lum_tp_unique_id(uint8_t* out128) {
     if (!out128) return LUM_E_INVALID;

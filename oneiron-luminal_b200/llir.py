@@ -142,3 +142,92 @@ def contiguous(shape: Sequence[int]) -> List[int]:
         st.append(acc)
         acc *= d if isinstance(d, int) else 1
     return list(reversed(st))
+
+
+# lum_dtype values (include/lum_llir.h)
+F32, F16, BF16, INT, BOOL, NVFP4, MXFP4, Q8_0 = range(8)
+
+
+def build_llama_llir(desc, shuffle_qkv: bool = False):
+    """The block-level LLIR a search produces for the Llama example (examples/llama/src/model.rs:40-215 lowered
+    through the block ops of crates/luminal_cuda/src/block/ops.rs), for the hyper-parameters in ``desc`` (anything
+    with the fields of ``ModelDesc``).
+
+    Returns ``(blob, ids)`` where ``ids`` maps a label to the HLIR node id the host passes to ``set_input`` /
+    ``get_output``: ``"tokens"``, ``"positions"``, ``"logits"``, ``"embed"``, ``"final_norm"``, ``"lm_head"`` and
+    ``(name, layer)`` for the per-layer tensors (labels follow the safetensors names of
+    examples/llama/src/model.rs:55-107).  ``shuffle_qkv`` emits the three projections in v, q, k order, to show
+    that recognition goes by data flow and not by position.
+    """
+    b = LLIRBuilder()
+    ids = {}
+    next_id = [0]
+
+    def new_input(key, label, dt):
+        hid = next_id[0]
+        next_id[0] += 7          # HLIR ids are sparse in practice: other ops sit between the Inputs
+        ids[key] = hid
+        return b.input(hid, label, dt)
+
+    H, HD, NQ, NKV, F, V = desc.hidden, desc.head_dim, desc.n_q_heads, desc.n_kv_heads, desc.ffn, desc.vocab
+    wdt, edt = desc.weight_dtype, desc.embed_dtype
+    sms = 148
+
+    def matmul(a, w, n, k):
+        if wdt == Q8_0:
+            return b.add("TileMatmulQ8", expr(sms), elist(["s", n]), expr(Expr.of("s").ceil_div(32)), expr((n + 31) // 32),
+                         expr(k), inp(a), expr(k), inp(w), expr(n), expr(1), flt(1.0))
+        return b.add("TileMatmulFullSplit", expr(sms), elist(["s", n]), expr(Expr.of("s").ceil_div(32)), expr((n + 31) // 32),
+                     expr(k), inp(a), elist([k, 1]), expr(k), expr(1), inp(w), elist([1, k]), expr(k), expr(1),
+                     elist([n, 1]), expr(n), expr(1))
+
+    def rmsnorm(x, g):
+        return b.add("RowRMSNorm", elist(["s"]), inp(x), elist([H]), expr(H), inp(g), flt(desc.rms_eps))
+
+    def rope(x, n, pos):
+        return b.add("RowRope", elist(["s"]), inp(x), elist([n]), expr(n), inp(pos), flt(desc.rope_theta), integer(desc.rope_style))
+
+    tok = new_input("tokens", "input", INT)
+    pos = new_input("positions", "token_ids", INT)
+    emb = new_input("embed", "model.embed_tokens.weight", edt)
+    x = b.add("RowEmbed", elist(["s"]), inp(tok), elist([1]), inp(emb), elist([H]), expr(H))
+    for l in range(desc.n_layers):
+        pre = f"model.layers.{l}."
+        g1 = new_input(("attn_norm", l), pre + "input_layernorm.weight", F32)
+        wq = new_input(("q", l), pre + "self_attn.q_proj.weight", wdt)
+        wk = new_input(("k", l), pre + "self_attn.k_proj.weight", wdt)
+        wv = new_input(("v", l), pre + "self_attn.v_proj.weight", wdt)
+        wo = new_input(("o", l), pre + "self_attn.o_proj.weight", wdt)
+        g2 = new_input(("mlp_norm", l), pre + "post_attention_layernorm.weight", F32)
+        wg = new_input(("gate", l), pre + "mlp.gate_proj.weight", wdt)
+        wu = new_input(("up", l), pre + "mlp.up_proj.weight", wdt)
+        wd = new_input(("down", l), pre + "mlp.down_proj.weight", wdt)
+        extra = []
+        if desc.qk_norm:
+            extra = [new_input(("q_norm", l), pre + "self_attn.q_norm.weight", F32),
+                     new_input(("k_norm", l), pre + "self_attn.k_norm.weight", F32)]
+        n1 = rmsnorm(x, g1)
+        if shuffle_qkv:
+            v = matmul(n1, wv, NKV * HD, H); q = matmul(n1, wq, NQ * HD, H); k = matmul(n1, wk, NKV * HD, H)
+        else:
+            q = matmul(n1, wq, NQ * HD, H); k = matmul(n1, wk, NKV * HD, H); v = matmul(n1, wv, NKV * HD, H)
+        qr, kr = rope(q, NQ * HD, pos), rope(k, NKV * HD, pos)
+        # the example's KV-cache attention custom op (examples/llama/src/model.rs:224-330): inputs, head_dim, kv_groups
+        att = b.add("KVAttention", ilist([qr, kr, v] + extra), expr(HD), expr(NQ // NKV), integer(l))
+        o = matmul(att, wo, H, NQ * HD)
+        x1 = b.add("RowAdd", elist(["s"]), inp(x), elist([H]), inp(o), elist([H]), elist([H]), expr(H))
+        n2 = rmsnorm(x1, g2)
+        gate, up = matmul(n2, wg, F, H), matmul(n2, wu, F, H)
+        sw = b.add("RowSwishMul", elist(["s"]), inp(gate), elist([F]), inp(up), elist([F]), expr(F), expr(F))
+        dn = matmul(sw, wd, H, F)
+        x = b.add("RowAdd", elist(["s"]), inp(x1), elist([H]), inp(dn), elist([H]), elist([H]), expr(H))
+    gf = new_input("final_norm", "model.norm.weight", F32)
+    nf = rmsnorm(x, gf)
+    if desc.tied_head:
+        head = emb
+    else:
+        head = new_input("lm_head", "lm_head.weight", wdt)
+    logits = matmul(nf, head, V, H)
+    ids["logits"] = next_id[0]
+    b.output(logits, ids["logits"])
+    return b.blob(), ids

@@ -132,6 +132,10 @@ def load_library() -> C.CDLL:
         "lum_model_synth": (i32, [vp, u64]),
         "lum_model_get_weight_f32": (i32, [vp, i32, i32, sz, sz, P(C.c_float)]),
         "lum_model_weight_bytes": (i32, [vp, P(u64)]),
+        "lum_llir_describe": (i32, [vp, sz, P(ModelDesc), P(C.c_int64), P(C.c_int64), P(C.c_int64), C.c_char_p, sz]),
+        "lum_load_llir": (i32, [vp, vp, sz, i32, u32, i32]),
+        "lum_set_input": (i32, [vp, C.c_int64, vp, sz, u32]),
+        "lum_get_output": (i32, [vp, C.c_int64, P(C.c_float), sz]),
         "lum_kv_reset": (i32, [vp]),
         "lum_kv_read": (i32, [vp, i32, i32, i32, P(C.c_float)]),
         "lum_set_dim": (i32, [vp, C.c_char, u64]),
@@ -169,6 +173,20 @@ def load_library() -> C.CDLL:
 
 
 EXPORTED_SYMBOLS = None  # filled lazily by tests from include/lum_b200.h
+
+
+def describe_llir(blob: bytes):
+    """Host-only: ``(ModelDesc, token_input, pos_input, logits_output)`` a serialised graph implies; raises
+    ``LumError`` naming the node where the graph stops looking like a Llama-style decoder."""
+    lib = load_library()
+    d = ModelDesc()
+    tok, pos, out = C.c_int64(-1), C.c_int64(-1), C.c_int64(-1)
+    err = C.create_string_buffer(256)
+    buf = C.create_string_buffer(blob, len(blob))
+    rc = lib.lum_llir_describe(buf, len(blob), C.byref(d), C.byref(tok), C.byref(pos), C.byref(out), err, 256)
+    if rc != 0:
+        raise LumError(rc, err.value.decode())
+    return d, tok.value, pos.value, out.value
 
 
 class B200Runtime:
@@ -245,6 +263,25 @@ class B200Runtime:
     def load_model(self, desc: ModelDesc) -> None:
         self._ck(self._lib.lum_model_init(self._h, C.byref(desc)))
         self.desc = desc.copy()
+
+    def load_llir(self, blob: bytes, max_seq: int = 4096, kv_dtype: str = "bf16", max_new_tokens: int = 4096) -> None:
+        """``Runtime::load_llir`` (src/op.rs:16): recognise the decoder a serialised graph describes and set it up."""
+        d, tok, pos, out = describe_llir(blob)
+        buf = C.create_string_buffer(blob, len(blob))
+        self._ck(self._lib.lum_load_llir(self._h, buf, len(blob), max_seq, DTYPE[kv_dtype], max_new_tokens))
+        self.desc = d.copy(max_seq=max_seq, kv_dtype=DTYPE[kv_dtype], max_new_tokens=max_new_tokens)
+        self.token_input, self.pos_input, self.logits_output = tok, pos, out
+
+    def set_input(self, hlir_node: int, data, dtype: str) -> None:
+        """``set_data(node_id, data)`` (crates/luminal_cuda/src/runtime.rs:160-165) by HLIR node id of an Input."""
+        self._ck(self._lib.lum_set_input(self._h, hlir_node, data.ctypes.data_as(C.c_void_p), data.nbytes, DTYPE[dtype]))
+
+    def get_output(self, hlir_node: int):
+        """``get_f32(node_id)`` (crates/luminal_cuda/src/runtime.rs:168-204) for the graph's Output: last-row logits."""
+        import numpy as np
+        out = np.empty(self.desc.vocab, dtype=np.float32)
+        self._ck(self._lib.lum_get_output(self._h, hlir_node, out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
 
     def set_weight(self, slot: str, layer: int, data, dtype: str) -> None:
         """``data``: a C-contiguous numpy array holding f32 values, bf16 bit patterns (uint16) or Q8_0 wire blocks (uint8)."""

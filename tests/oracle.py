@@ -163,3 +163,33 @@ class OracleModel:
         if return_margins:
             res.append(margins)
         return res[0] if len(res) == 1 else tuple(res)
+
+
+def host_tensors(lib, desc, seed: int):
+    """Every tensor of the synthetic model `seed` as a host would hold it before upload: ``key -> (uint8 array, dtype
+    name)``, keys as in ``llir.build_llama_llir`` ("embed", "final_norm", "lm_head", (name, layer)).  Tensor ids follow
+    the generator's convention: layer * 16 + slot, with the model-level tensors at layer == n_layers."""
+    names = {0: "f32", 2: "bf16", 7: "q8_0"}
+    slot = {"embed": 0, "attn_norm": 1, "q": 2, "k": 3, "v": 4, "o": 5, "mlp_norm": 6, "gate": 7, "up": 8, "down": 9,
+            "final_norm": 10, "lm_head": 11}
+    H, F, V, hd = desc.hidden, desc.ffn, desc.vocab, desc.head_dim
+    qd, kvd = desc.n_q_heads * hd, desc.n_kv_heads * hd
+    dims = {"q": (qd, H), "k": (kvd, H), "v": (kvd, H), "o": (H, qd), "gate": (F, H), "up": (F, H), "down": (H, F)}
+    wdt, edt = desc.weight_dtype, desc.embed_dtype
+
+    def synth(tid, dt, n, ones=0):
+        size = n // 32 * 34 if dt == 7 else n * (2 if dt == 2 else 4)
+        buf = np.empty(size, dtype=np.uint8)
+        assert lib.orc_synth(seed, tid, dt, n, ones, buf.ctypes.data_as(C.c_void_p)) == 0
+        return buf, names[dt]
+
+    L = desc.n_layers
+    out = {"embed": synth(L * 16 + 0, edt, V * H), "final_norm": synth(L * 16 + 10, edt, H, 1)}
+    if not desc.tied_head:
+        out["lm_head"] = synth(L * 16 + 11, wdt, V * H)
+    for l in range(L):
+        for name, (n, k) in dims.items():
+            out[(name, l)] = synth(l * 16 + slot[name], wdt, n * k)
+        out[("attn_norm", l)] = synth(l * 16 + 1, edt, H, 1)
+        out[("mlp_norm", l)] = synth(l * 16 + 6, edt, H, 1)
+    return out
