@@ -186,13 +186,13 @@ int32_t lum_tp_init(lum_rt* rt, const uint8_t* id128, int32_t tp_size, int32_t t
  * always run the plain-load kernel; `force_direct` is accepted for symmetry with the packed entry. */
 int32_t lum_op_gemv_q8_0(const int8_t* quants_dev, const void* scales_dev, int32_t n, int32_t k,
                          const float* x_dev, float* y_dev, int32_t force_direct, void* stream);
-/* The streaming layout: stage-units of R rows x KC columns (R * KC = 16384), each 16 KiB of quants followed
- * by 1 KiB of scales, ordered by row group then K-chunk (documented in csrc/lum_synth.cu).  Same 34/32 bytes
+/* The streaming layout: tiles of 8 rows x 512 columns, each 4096 quants in tensor-core operand order followed by
+ * their 128 scales, the tiles of a row group consecutive (documented in csrc/lum_synth.cu).  Same 34/32 bytes
  * per weight.  lum_q8_0_packed_bytes returns 0 when [n, k] cannot be packed (needs K % 512 == 0,
- * K <= 16384, N % (16384 / KC) == 0). */
+ * K <= 16384, N % 8 == 0). */
 size_t lum_q8_0_packed_bytes(int32_t n, int32_t k);
 int32_t lum_op_q8_0_pack(const int8_t* quants_dev, const void* scales_dev, int32_t n, int32_t k, void* packed_dev, void* stream);
-/* Same product on packed weights: the bulk-copy streaming kernel (force_direct = 1: the plain-load kernel). */
+/* Same product on packed weights: the bulk-copy + tcgen05 streaming kernel (force_direct = 1: the plain-load kernel). */
 int32_t lum_op_gemv_q8_0_packed(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev,
                                 int32_t force_direct, void* stream);
 int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tensor_id, int32_t n, int32_t k, void* packed_dev, void* stream);

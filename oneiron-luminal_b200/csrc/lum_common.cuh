@@ -20,6 +20,7 @@ enum : uint32_t {
     LUM_ST_BAD_TOKEN = 1u << 3,   // token id outside the vocabulary
     LUM_ST_BAD_POS = 1u << 4,     // position outside the cache capacity
     LUM_ST_WAIT_GRID = 1u << 5,   // a grid-wide barrier of the persistent kernel was not reached by every CTA in time
+    LUM_ST_WAIT_TMEM = 1u << 6,   // a wait on the tensor-core hand-over (accumulators ready / drained) ran out of budget
 };
 
 // Budget for any single wait, in SM clock cycles (about two seconds at 2 GHz).  The SM-local cycle
@@ -98,6 +99,66 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
                  : "memory");
 }
 
+// ---- 5th-generation tensor core (tcgen05) and tensor memory ----------------------------------------
+// Shared-memory operand descriptor for a K-major operand without swizzling: the operand is a grid of "core matrices"
+// of 8 rows x 16 bytes, each stored as 128 contiguous bytes (row stride 16 B).  `lbo` is the byte distance between the
+// two core matrices that cover K = 32 bytes of the same 8 rows, `sbo` the distance between consecutive groups of 8 rows.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) |
+           (1ull << 46);   // bits 46-47: descriptor version of sm_100
+}
+// Instruction descriptor of kind::i8: s32 accumulators, s8 x s8, both operands K-major, shape M x N (K = 32).
+__host__ __device__ constexpr uint32_t umma_idesc_s8(int M, int N) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// The two halves of such a descriptor, for callers that step through many operands: `lo` carries the start address and
+// lbo (advance it by bytes / 16 to move the operand), `hi` carries sbo and the version and stays fixed.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo) { return ((smem_addr >> 4) & 0x3fffu) | (((lbo >> 4) & 0x3fffu) << 16); }
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3fffu) | (1u << 14); }
+// D[tmem] = A[smem] * B[smem]^T (accumulators overwritten).  Issued by ONE thread.
+__device__ __forceinline__ void umma_s8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(0u)
+        : "memory");
+}
+// Same with the descriptors given as halves (both operands share `hi`).
+__device__ __forceinline__ void umma_s8_ss_split(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, %4;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc)
+        : "memory");
+}
+// `bar` receives one arrival when every tcgen05.mma this thread issued before has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Whole warp: allocate `cols` (power of two, >= 32) tensor-memory columns; the base address is written to *slot (shared).
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+// Whole warp: 16 consecutive 32-bit columns of this thread's lane (warp w of the CTA reads lanes 32 * (w % 4) ..).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// generic-proxy writes to shared memory (st.shared) -> visible to the async proxy (tensor core operand reads)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // ---- programmatic dependent launch ------------------------------------------------------------
 // launch_dependents: the next kernel in the stream may start its prologue (weight prefetch) now.
 // grid_wait: block until every kernel this one depends on has finished and its writes are visible.
@@ -114,5 +175,7 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) { return __uint_as
 
 // named barrier over `n` threads (n a multiple of 32); id 0 is __syncthreads' own
 __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+// arrive without waiting (the waiting side calls named_sync with the same id and total count)
+__device__ __forceinline__ void named_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
 }  // namespace lum

@@ -114,16 +114,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     const int warp = tid >> 5, lane = tid & 31;
     GemvSmem g;
     gemv_carve(smem, a.K, a.stages, &s_abort, &g);
-    if (tid == 0) {
-        GPROBE(0);
-        s_abort = 0;
-        gemv_init_barriers(g);
-    }
-    __syncthreads();
+    if (tid == 0) GPROBE(0);
+    const uint32_t tmem = gemv_cta_begin(g, tid, &s_abort);
     if (a.use_pdl) pdl_launch_dependents();
     const GemvPlan plan = gemv_plan(a, (int)gridDim.x, a.job_ctr != nullptr);
 
-    if (warp == kConsumers / 32) {
+    if (warp == kProducerWarp) {
         // producer: the weight stream does not depend on the previous kernel, so it starts at once
         if (lane == 0) {
             ProducerRing pr{0, 0u, 0};
@@ -132,17 +128,28 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
         }
         return;
     }
+    if (warp == kMmaWarp) {
+        if (lane == 0) {
+            MmaRing mr{0, 0u, 0u, 0u, 0u, 0};
+            gemv_mma_issue(a, plan, g, mr, tmem, a.status);
+        }
+        gemv_mma_end(g, tmem, lane, a.status);
+        return;
+    }
     if (a.use_pdl) pdl_grid_wait();
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
     ArgBest best{-INFINITY, -1};
-    ConsumerRing cr{0, 0u};
-    gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, a.status, &best);
-    if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 1);
+    ConsumerRing cr{0, 0u, 0u, 0u, 0};
+    gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best);
+    if (tid >= kConsumers) return;
+    gemv_consumers_done();
+    if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
     GPROBE(4);
 }
 #ifdef LUM_PROBE
 extern "C" int lum_probe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_probe, sizeof(g_probe)); }
+extern "C" int lum_tl_read(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl)); }
 #endif
 
 // ------------------------------------------------------------------------------ direct kernel
@@ -151,26 +158,28 @@ template <int WK>
 __device__ __forceinline__ float row_dot(const GemvSeg& sg, int row, int K, const float* xs, int lane) {
     float acc = 0.0f;
     if (WK == WK_Q8) {
-        // planes: quants [N,K] + scales [N,K/32].  packed (kc > 0): stage-units of R rows x kc columns,
-        // each 16 KiB of quants followed by 1 KiB of scales (the streaming kernel's layout).
-        const int kc = sg.kc, R = kc ? kUnitBytes / kc : 1, nch = kc ? K / kc : 1;
-        const unsigned char* ubase = kc ? (const unsigned char*)sg.w + (size_t)(row / R) * nch * kStageBytes : nullptr;
+        // planes: quants [N,K] + scales [N,K/32].  packed (kc > 0): the streaming kernel's tile stream — per row group of
+        // 8 rows K/512 tiles of 4352 bytes; inside a tile block b (0..15) of row r sits at b*256 + (byte/16)*128 + r*16 +
+        // byte%16 and its scale is entry b*8 + r of the 128 binary16 values after the 4096 quants.
+        const int kc = sg.kc;
+        const unsigned char* gbase = kc ? (const unsigned char*)sg.w + (size_t)(row >> 3) * (K / kTileK) * kTileBytes : nullptr;
         const int8_t* q = (const int8_t*)sg.w + (size_t)row * K;
         const __half* sc = sg.s + (size_t)row * (K >> 5);
         for (int b = lane; b < (K >> 5); b += 32) {        // one 32-block per lane per trip
-            const uint4* p;
+            uint4 w0, w1;
             float d;
             if (kc) {
-                const int c = (b << 5) / kc, kk = (b << 5) - c * kc, r = row % R;
-                const unsigned char* u = ubase + (size_t)c * kStageBytes;
-                p = (const uint4*)(u + (size_t)r * kc + kk);
-                d = __half2float(((const __half*)(u + kUnitBytes))[r * (kc >> 5) + (kk >> 5)]);
+                const unsigned char* t = gbase + (size_t)(b >> 4) * kTileBytes;
+                const unsigned char* cm = t + ((b & 15) << 8) + ((row & 7) << 4);
+                w0 = *(const uint4*)cm;
+                w1 = *(const uint4*)(cm + 128);
+                d = __half2float(((const __half*)(t + kTileQ))[((b & 15) << 3) + (row & 7)]);
             } else {
-                p = (const uint4*)(q + (size_t)b * 32);
+                const uint4* p = (const uint4*)(q + (size_t)b * 32);
+                w0 = p[0]; w1 = p[1];
                 d = __half2float(sc[b]);
             }
             const float4* x4 = (const float4*)(xs + (size_t)b * 32);
-            const uint4 w0 = p[0], w1 = p[1];
             float p0 = dot4_s8(w0.x, x4[0], 0.0f), p1 = dot4_s8(w0.y, x4[1], 0.0f);
             p0 = dot4_s8(w0.z, x4[2], p0); p1 = dot4_s8(w0.w, x4[3], p1);
             p0 = dot4_s8(w1.x, x4[4], p0); p1 = dot4_s8(w1.y, x4[5], p1);
@@ -232,29 +241,21 @@ __global__ void __launch_bounds__(256) gemv_direct(const GemvArgs a) {
 
 // ------------------------------------------------------------------------------ host side
 
-static int pick_kc(int K) {
-    for (int kc = 4096; kc >= 512; kc >>= 1)
-        if (K % kc == 0) return kc;
-    return 0;
-}
-
+// Packed layout: available when the matrix cuts into whole tiles (8 rows x 512 columns).  The "K-chunk" reported for a
+// packed matrix is the tile width; 0 means the matrix stays in planes and is read by the direct kernel.
 int q8_pack_kc(int rows, int K) {
-    const int kc = pick_kc(K);
-    if (!kc || K > 16384) return 0;
-    return (rows % (kUnitBytes / kc)) ? 0 : kc;
+    if (K <= 0 || K % kTileK || K > 16384 || rows <= 0 || rows % kTileRows) return 0;
+    return kTileK;
 }
 size_t q8_packed_bytes(int rows, int K) {
-    const int kc = q8_pack_kc(rows, K);
-    return kc ? (size_t)rows * K / kUnitBytes * kStageBytes : 0;
+    return q8_pack_kc(rows, K) ? (size_t)rows / kTileRows * (size_t)(K / kTileK) * kTileBytes : 0;
 }
 
 bool gemv_stream_supported(const GemvArgs& a) {
     if (a.wkind != WK_Q8 || a.force_direct) return false;
-    const int kc = pick_kc(a.K);
-    if (!kc || a.K > 16384 || ((uintptr_t)a.x & 15) || (a.x_add && ((uintptr_t)a.x_add & 15))) return false;
-    const int R = kUnitBytes / kc;
+    if (a.K % kTileK || a.K > 16384 || ((uintptr_t)a.x & 15) || (a.x_add && ((uintptr_t)a.x_add & 15))) return false;
     for (int s = 0; s < a.nseg; s++)
-        if (a.seg[s].rows % R || a.seg[s].kc != kc) return false;       // every segment must be in the packed layout
+        if (a.seg[s].rows % kTileRows || a.seg[s].kc != kTileK) return false;       // every segment must be in the packed layout
     if (a.epi == EPI_SWIGLU && (a.nseg != 2 || a.seg[0].rows != a.seg[1].rows)) return false;
     return true;
 }
@@ -282,14 +283,13 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
     if (rows_total <= 0 || a.K <= 0) return cudaErrorInvalidValue;
 
     if (gemv_stream_supported(a)) {
-        a.KC = pick_kc(a.K);
-        const int R = kUnitBytes / a.KC;
-        const int LU = rows_total / R;
-        int grid = sm_count < LU ? sm_count : LU;
+        a.KC = kTileK;
+        const int tpr = a.K / kTileK, gpf = tpr >= 5 ? 1 : kFillTiles / tpr;
+        const int jobs = (rows_total / kTileRows + gpf - 1) / gpf;
+        int grid = sm_count < jobs ? sm_count : jobs;
         const size_t fixed = gemv_fixed_smem(a.K);
-        // Two kernels co-resident per SM (so the next one can prefetch under programmatic dependent launch):
-        // stay under ~113 KiB each.  LUM_GEMV_STAGES overrides (deeper ring, no co-residency).
-        int stages = (int)((113 * 1024 - (long)fixed) / kFillBytes);
+        // One CTA per SM (576 threads): the ring takes what is left of shared memory.  LUM_GEMV_STAGES overrides.
+        int stages = (int)((226 * 1024 - (long)fixed) / kFillBytes);
         static const int env_stages = [] { const char* e = getenv("LUM_GEMV_STAGES"); return e ? atoi(e) : 0; }();
         if (env_stages > 0) stages = env_stages;
         const int fit = (int)((226 * 1024 - (long)fixed) / kFillBytes);
@@ -352,7 +352,7 @@ extern "C" int32_t lum_op_sample_q8_0_static(const void* packed, int32_t n, int3
     static unsigned char* dev_ptr[64] = {nullptr};      // device address of the array, per device ordinal
     const int kc = q8_pack_kc(n, k);
     if (!packed || !x || !logits || !best || !kc) {
-        set_op_error("sample_q8_0_static: bad arguments or shape cannot be packed (needs K % 512 == 0, K <= 16384, N % (16384 / KC) == 0)");
+        set_op_error("sample_q8_0_static: bad arguments or shape cannot be packed (needs K % 512 == 0, K <= 16384, N % 8 == 0)");
         return -1;
     }
     int dev = 0, sms = 0;

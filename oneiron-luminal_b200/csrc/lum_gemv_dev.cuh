@@ -1,22 +1,35 @@
 // Device-side building blocks of the streaming Q8_0 matrix-vector product, shared by the one-op
 // kernel (lum_gemv.cu) and the whole-token persistent kernel (lum_mega.cu).  A "phase" is one
-// y = W x over one CTA's share of the weight stream:
+// y = W x over one CTA's share of the weight stream.  Three kinds of warps cooperate through
+// mbarriers:
 //
-//   producer side   gemv_produce()  — the producer warp arms ring stages and issues one bulk copy
-//                                     (17 KiB, one packed stage-unit) per stage; lane i owns stage i.
-//   consumer side   gemv_consume()  — 16 warps: quantise x into three int8 levels, then per stage
-//                                     wait, multiply-accumulate with dp4a, hand the stage back;
-//                                     row sums are reduced in a fixed order and passed to the
-//                                     epilogue (store / residual add / SwiGLU / greedy sample).
+//   producer warp      gemv_produce()    one lane arms ring stages and issues one bulk copy (up to 8
+//                                        tiles, 34 KiB) per stage.
+//   tensor-core warp   gemv_mma_issue()  one lane waits for a stage to land and issues one tcgen05.mma
+//                                        (kind::i8, M = 128, N = 48, K = 32) per tile: the weights go from
+//                                        shared memory into the tensor core without passing through
+//                                        registers, the exact int32 dot products land in tensor memory.
+//   draining warps     gemv_consume()    all 16 worker warps quantise x into three int8 levels (the B
+//                                        operand); then 8 of them read the accumulators back (tcgen05.ld),
+//                                        apply the block scales in f32, reduce row sums in a fixed order
+//                                        and run the epilogue (store / residual add / SwiGLU / greedy sample).
+//
+// Why the tensor core for a matrix-vector product: Q8_0 has one scale per 32 weights, so the arithmetic
+// per weight outside the integer multiply-add is small, but the multiply-adds themselves (three per weight,
+// one per activation level) cost the CUDA cores about 0.75 half-rate dp4a issue slots per weight — roughly
+// the time HBM needs to deliver the weight.  One M128 N48 K32 instruction does the 12288 useful (and 184320
+// ignored) multiply-adds of a tile in a few dozen cycles; per weight the draining threads are left with
+// 1/32 of an int->float conversion and a handful of FMAs, so they catch up quickly after every stall (grid
+// barrier, attention, prologue) and the weight stream from HBM is the only thing that takes time.
 //
 // The ring keeps running across phases, so in the persistent kernel the producer streams the next
-// operation's weights while the consumers are still finishing (or waiting for the grid-wide
+// operation's weights while the other warps are still finishing (or waiting for the grid-wide
 // dependency of) the current one.
 //
-// Work is handed out in jobs (two stage-units, or one row group with all its K-chunks).  Each CTA
-// owns a static run of jobs; the rest sit in a pool that producers claim from with an atomic
-// counter, so SMs that happen to get more HBM bandwidth take more of the matrix (equal static
-// shares finished up to 30 % apart on B200).  Every ring stage carries the id of the unit it
+// Work is handed out in jobs (one row group of 8 rows with all its tiles; for narrow matrices several
+// row groups).  Each CTA owns a static run of jobs; the rest sit in a pool that producers claim from with an
+// atomic counter, so SMs that happen to get more HBM bandwidth take more of the matrix (equal static
+// shares finished up to 30 % apart on B200).  Every ring stage carries the id of the row group it
 // holds, and the producer ends a phase with an END marker stage.
 #pragma once
 #include "lum_kernels.cuh"
@@ -27,60 +40,105 @@ namespace lum {
 // Build-time probe (never in the shipped library): %globaltimer stamps of a few points in CTA 0 (one copy per translation unit).
 static __device__ unsigned long long g_probe[32];
 #define GPROBE(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || (i) == 5)) g_probe[i] = globaltimer_ns(); } while (0)
+// per-fill timeline of CTA 0 (SM clock): [fill][event]
+static __device__ long long g_tl[64][16];   // one copy per translation unit
+#ifndef LUM_TL_FIRST
+#define LUM_TL_FIRST 0
+#endif
+#define TPROBE(f, e) do { if (blockIdx.x == 0 && (f) >= LUM_TL_FIRST && (f) < LUM_TL_FIRST + 64) g_tl[(f) - LUM_TL_FIRST][e] = clock64(); } while (0)
 #else
 #define GPROBE(i) do { } while (0)
+#define TPROBE(f, e) do { } while (0)
 #endif
 
-constexpr int kConsumers = 512;          // 16 consumer warps: enough independent warps to cover dp4a / shuffle / LDS latency
-constexpr int kGemvThreads = 544;        // + 1 producer warp
-constexpr int kUnitBytes = 16384;        // int8 bytes per stage-unit
-constexpr int kStageBytes = kUnitBytes + kUnitBytes / 16;   // one packed stage-unit: + binary16 scales (2 B per 32 quants)
-constexpr int kFillBytes = 2 * kStageBytes;                 // one ring stage holds up to two stage-units
-constexpr int kBarBytes = 512;           // 2 x 16 mbarriers (256 B), then 64 words of reduction scratch
+constexpr int kWorkers = 512;            // 16 worker warps: activation prologue, attention (persistent kernel); warps 0-7 also drain the accumulators
+constexpr int kConsumers = 256;          // the first 8 worker warps = two warpgroups, each owning one tensor-memory slot
+constexpr int kProducerWarp = 16;        // issues the bulk copies
+constexpr int kMmaWarp = 17;             // owns tensor memory and issues the tensor-core instructions
+constexpr int kGemvThreads = 576;
+constexpr int kTileK = 512;              // columns of one tile = 16 blocks of 32
+constexpr int kTileRows = 8;             // weight rows of one tile (a "row group")
+constexpr int kTileQ = 4096;             // int8 bytes of one tile: 128 (block, row) pairs x 32 quants, in tensor-core operand order
+constexpr int kTileBytes = kTileQ + 256; // + the 128 binary16 scales of those pairs
+constexpr int kFillTiles = 8;            // tiles per ring stage
+constexpr int kFillBytes = kFillTiles * kTileBytes;
+constexpr int kBarBytes = 640;           // mbarriers (320 B), then 64 words of reduction scratch
 constexpr int kMaxStages = 16;
-constexpr int kChunkUnits = 64;          // stage-units whose row sums are held before an epilogue pass
-constexpr int kRedFloats = kChunkUnits * 32;
-constexpr int kValsFloats = kChunkUnits * 32;
+constexpr int kChunkRG = 16;             // row groups whose sums are held before an epilogue pass (>= 2 x 8: one SwiGLU job of one-tile rows)
+constexpr int kRedFloats = kChunkRG * 64;   // [slot][consumer warp][row]
+constexpr int kValsFloats = kChunkRG * 8;
 constexpr int kMetaEnd = -1;
+constexpr int kTmemCols = 512;           // all of an SM's tensor memory: 2 slots x 4 tiles x 64 columns (48 used per tile)
+constexpr int kMmaN = 48;                // accumulator columns per tile: 16 blocks x 3 activation levels
+constexpr int kXqTileBytes = 1536;       // activation bytes per tile: 48 operand rows x 32
+
+// fields of meta2[stage]
+constexpr uint32_t kM2JobEnd = 1u << 16, kM2Up = 1u << 17;
+__device__ __forceinline__ uint32_t m2_pack(int ntiles, int c0, int n_rg, bool job_end, int part) {
+    return (uint32_t)ntiles | ((uint32_t)c0 << 4) | ((uint32_t)n_rg << 12) | (job_end ? kM2JobEnd : 0u) | (part ? kM2Up : 0u);
+}
 
 // Shared-memory carve-up used by a streaming phase.
 struct GemvSmem {
-    uint32_t full0, empty0;      // mbarrier arrays (shared-space addresses)
+    uint32_t full0, empty0;      // per-stage mbarriers (shared-space addresses): bytes landed / stage released
+    uint32_t tfull0, tempty0;    // accumulators of a fill written (tcgen05.commit) / read back by all 8 draining warps
+    uint32_t xready, mdone, fin; // activations quantised (per phase) / (unused) / last instruction retired
+    uint32_t tmem_slot;          // where tcgen05.alloc leaves the base address
     float* scratch;              // 64 words
-    int8_t* xq;                  // 3 planes of K int8
+    int8_t* xq;                  // activations as a tensor-core operand: rows (block, level), 32 bytes each, core-matrix order
     float* xsc;                  // K / 32 block scales of x
     float* red;                  // kRedFloats
     float* vals;                 // kValsFloats
-    int* unit_of;                // kChunkUnits: global stage-unit id held in each local slot of the current chunk
-    int* meta;                   // kMaxStages: first stage-unit id of the fill in each ring stage, or kMetaEnd
+    int* unit_of;                // kChunkRG: global row-group id held in each local slot of the current chunk
+    int* pair_of;                // kChunkRG: SwiGLU: slot of the matching up rows (gate slots) or -1 (up slots)
+    int2* meta;                  // kMaxStages: x = first row-group id of the fill in each ring stage, or kMetaEnd;
+                                 //             y = tiles / first tile / row groups / flags of the fill (m2_pack)
     unsigned char* stage0;       // ring of `stages` x kFillBytes, 128-byte aligned
     int stages;
     volatile int* abort;         // CTA-wide: a wait ran out of budget; stop waiting, finish fast
 };
 
-// bytes of dynamic shared memory before the ring, for activations of length K
-__host__ __device__ inline size_t gemv_fixed_smem(int K) {
-    return (size_t)kBarBytes + (size_t)K * 3 + (size_t)(K / 32) * 4 + (size_t)kRedFloats * 4 + (size_t)kValsFloats * 4 +
-           (size_t)(kChunkUnits + kMaxStages) * 4 + 256;
+// bytes of dynamic shared memory before the ring, for activations of length K.  `scratch_bytes`: the area behind the
+// barriers (activation operand, scales, reduction scratch) is at least this large, for a caller that borrows it between
+// phases (the persistent kernel's attention).
+__host__ __device__ inline size_t gemv_fixed_smem(int K, size_t scratch_bytes = 0) {
+    const size_t area = (size_t)K * 3 + (size_t)(K / 32) * 4 + (size_t)kRedFloats * 4 + (size_t)kValsFloats * 4;
+    return (size_t)kBarBytes + (area > scratch_bytes ? area : scratch_bytes) + (size_t)(2 * kChunkRG + 2 * kMaxStages) * 4 + 256;
 }
 
-__device__ __forceinline__ void gemv_carve(unsigned char* smem, int K, int stages, volatile int* abort, GemvSmem* g) {
+__device__ __forceinline__ void gemv_carve(unsigned char* smem, int K, int stages, volatile int* abort, GemvSmem* g, size_t scratch_bytes = 0) {
     g->full0 = smem_u32(smem);
     g->empty0 = g->full0 + 8u * kMaxStages;
-    g->scratch = (float*)(smem + 256);
+    g->tfull0 = g->empty0 + 8u * kMaxStages;
+    g->tempty0 = g->tfull0 + 16u;
+    g->xready = g->tempty0 + 16u;
+    g->mdone = g->xready + 8u;
+    g->fin = g->mdone + 8u;
+    g->tmem_slot = g->fin + 8u;
+    g->scratch = (float*)(smem + 384);
     g->xq = (int8_t*)(smem + kBarBytes);
     g->xsc = (float*)(g->xq + 3 * (size_t)K);
     g->red = g->xsc + (K >> 5);
     g->vals = g->red + kRedFloats;
     g->unit_of = (int*)(g->vals + kValsFloats);
-    g->meta = g->unit_of + kChunkUnits;
+    if ((size_t)((unsigned char*)g->unit_of - (unsigned char*)g->xq) < scratch_bytes) g->unit_of = (int*)((unsigned char*)g->xq + ((scratch_bytes + 15) & ~(size_t)15));
+    g->pair_of = g->unit_of + kChunkRG;
+    g->meta = (int2*)(g->pair_of + kChunkRG);
     g->stage0 = (unsigned char*)(((uintptr_t)(g->meta + kMaxStages) + 127) & ~(uintptr_t)127);
     g->stages = stages;
     g->abort = abort;
 }
 
 __device__ __forceinline__ void gemv_init_barriers(const GemvSmem& g) {
-    for (int s = 0; s < g.stages; s++) { mbar_init(g.full0 + 8u * s, 1); mbar_init(g.empty0 + 8u * s, kConsumers / 32); }
+    for (int s = 0; s < g.stages; s++) {
+        mbar_init(g.full0 + 8u * s, 1);
+        mbar_init(g.empty0 + 8u * s, kConsumers / 32);       // the 8 draining warps (they arrive after the tensor core has retired the stage's instructions)
+    }
+    mbar_init(g.tfull0, 1);
+    mbar_init(g.tempty0, kConsumers / 32);
+    mbar_init(g.xready, kWorkers / 32);
+    mbar_init(g.mdone, 1);
+    mbar_init(g.fin, 1);
     mbar_fence_init();
 }
 
@@ -112,28 +170,26 @@ __device__ __forceinline__ void argbest_take(ArgBest& b, float ov, int oi) {
     if (oi >= 0 && (b.i < 0 || ov > b.v || (ov == b.v && oi > b.i))) { b.v = ov; b.i = oi; }
 }
 
-// Epilogue over the finished units of a chunk: slot s holds stage-unit unit_of[s], R row sums at vals[s*R ..].
-// A stage-unit id maps to logical rows: plain phases unit u = rows [u*R, (u+1)*R) of the concatenated segments;
-// SwiGLU phases unit 2l = gate rows of logical unit l, unit 2l+1 = its up rows, and the two sit in adjacent slots.
+// Epilogue over the finished row groups of a chunk: slot s holds row group unit_of[s] (rows unit_of[s] * 8 ..), its 8 row
+// sums at vals[s*8 ..].  Plain phases: row group ids count over the concatenated segments.  SwiGLU phases: gate slots carry
+// the slot of the matching up rows in pair_of[s] (up slots carry -1) and only they produce output.
 // For EPI_ARGMAX the rows are stored and thread 0 folds the chunk's best into *best.
-__device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const float* vals, const int* unit_of, int n_slots, int R, int tid,
-                                                    int nthreads, float* scratch, int bar_id, ArgBest* best) {
-    const int n = n_slots * R;
+__device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const float* vals, const int* unit_of, const int* pair_of, int n_slots,
+                                                    int tid, int nthreads, float* scratch, int bar_id, ArgBest* best) {
+    const int n = n_slots * kTileRows;
     if (a.epi == EPI_SWIGLU) {
-        for (int i = tid; i < (n_slots >> 1) * R; i += nthreads) {
-            const int p = i / R, r = i - p * R;
-            const int row = (unit_of[2 * p] >> 1) * R + r;
-            a.y[row] = swiglu(vals[(2 * p) * R + r], vals[(2 * p + 1) * R + r]);
+        for (int i = tid; i < n; i += nthreads) {
+            const int sl = i >> 3, r = i & 7, pr = pair_of[sl];
+            if (pr >= 0) a.y[unit_of[sl] * kTileRows + r] = swiglu(vals[i], vals[pr * kTileRows + r]);
         }
     } else if (a.epi == EPI_STORE) {
-        for (int i = tid; i < n; i += nthreads) { const int sl = i / R; a.y[unit_of[sl] * R + (i - sl * R)] = vals[i]; }
+        for (int i = tid; i < n; i += nthreads) a.y[unit_of[i >> 3] * kTileRows + (i & 7)] = vals[i];
     } else if (a.epi == EPI_RESID) {
-        for (int i = tid; i < n; i += nthreads) { const int sl = i / R; const int row = unit_of[sl] * R + (i - sl * R); a.y[row] = a.resid[row] + vals[i]; }
+        for (int i = tid; i < n; i += nthreads) { const int row = unit_of[i >> 3] * kTileRows + (i & 7); a.y[row] = a.resid[row] + vals[i]; }
     } else {  // EPI_ARGMAX
         ArgBest b{-INFINITY, -1};
         for (int i = tid; i < n; i += nthreads) {
-            const int sl = i / R;
-            const int row = unit_of[sl] * R + (i - sl * R);
+            const int row = unit_of[i >> 3] * kTileRows + (i & 7);
             const float v = vals[i];
             a.y[row] = v;
             argbest_take(b, v, row);
@@ -213,10 +269,12 @@ struct XSource {
     int token;
 };
 
-// Prologue: activations (optionally RMS-normalised, times the gains) -> three int8 levels + one f32
-// scale per 32-block (x ~= s * (a1 + a2/254 + a3/254^2)).  Runs on the kConsumers consumer threads;
-// 8 consecutive threads own one block.  Loops stay rolled: this code runs once per CTA per phase,
-// so its size in instruction-cache lines is latency.
+// Prologue: activations (optionally RMS-normalised, times the gains) -> three int8 levels + one f32 scale per 32-block
+// (x ~= s * (a1 + a2/254 + a3/254^2)), written as the B operand of the tensor-core instruction: operand row 3 * block + level
+// holds that level's 32 bytes, rows grouped by 8 into core matrices (two per group: bytes 0-15 and 16-31 of each row).
+// Runs on all kWorkers threads; 8 consecutive threads own one block.  Loops stay rolled: this code runs once per CTA per
+// phase, so its size in instruction-cache lines is latency.  Ends with the writes published to the tensor core (xready)
+// and to the other workers (named barrier 1).
 __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvSmem& g, int tid) {
     const int K = a.K, n4 = K >> 2;
     auto load4 = [&](int f4) -> float4 {
@@ -237,20 +295,20 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
     if (a.gain) {
         float ss = 0.0f;
 #pragma unroll 4
-        for (int f4 = tid; f4 < n4; f4 += kConsumers) {
+        for (int f4 = tid; f4 < n4; f4 += kWorkers) {
             const float4 t = load4(f4);
             ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
         }
-        ss = block_sum(ss, g.scratch, tid, kConsumers, 1);
+        ss = block_sum(ss, g.scratch, tid, kWorkers, 1);
         const float mean = ss * (1.0f / (float)K);
         inv = 1.0f / sqrtf(mean + a.eps);
     }
     // second pass re-reads x (an L1/L2 hit); all threads run the same trip count so the 8-lane shuffles
     // always have their partners (K is a multiple of 32: a block never straddles the end)
-    const int trips = (n4 + kConsumers - 1) / kConsumers;
+    const int trips = (n4 + kWorkers - 1) / kWorkers;
 #pragma unroll 1
     for (int it = 0; it < trips; it++) {
-        const int f4 = it * kConsumers + tid;
+        const int f4 = it * kWorkers + tid;
         const bool in = f4 < n4;
         float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         if (in) {
@@ -287,41 +345,52 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             p3 |= (__float_as_uint(t3) & 0xffu) << (8 * j);
         }
         if (in) {
-            ((uint32_t*)g.xq)[f4] = p1;
-            ((uint32_t*)(g.xq + (size_t)K))[f4] = p2;
-            ((uint32_t*)(g.xq + 2 * (size_t)K))[f4] = p3;
-            if ((tid & 7) == 0) g.xsc[f4 >> 3] = s1;
+            const int blk = f4 >> 3, j0 = (f4 & 7) << 2;                 // this thread's 4 bytes: columns j0..j0+3 of block blk
+            const int inner = ((j0 >> 4) << 7) + (j0 & 15);
+            const int n1 = 3 * blk, n2 = n1 + 1, n3 = n1 + 2;              // operand rows of the three levels
+            *(uint32_t*)(g.xq + ((n1 >> 3) << 8) + ((n1 & 7) << 4) + inner) = p1;
+            *(uint32_t*)(g.xq + ((n2 >> 3) << 8) + ((n2 & 7) << 4) + inner) = p2;
+            *(uint32_t*)(g.xq + ((n3 >> 3) << 8) + ((n3 & 7) << 4) + inner) = p3;
+            if ((tid & 7) == 0) g.xsc[blk] = s1;
         }
     }
-    named_sync(1, kConsumers);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(g.xready);
+    named_sync(1, kWorkers);
 }
 
-// How a phase's matrix is cut into jobs.
-//   stage-unit u (global id): plain phases = R rows [u*R, ..) of the concatenated segments; SwiGLU phases 2l = gate rows of
-//   logical unit l, 2l+1 = up rows.  A fill (one ring stage, one barrier hand-over) carries two stage-units: with one
-//   K-chunk per row group (nch == 1) units 2j and 2j+1, otherwise two consecutive K-chunks of one unit.
-//   A job is what one CTA must do as a whole: nch == 1: one fill (units 2j, 2j+1);  nch > 1: upj units (2 for SwiGLU so
-//   gate and up of a logical unit stay together, else 1) with fpu fills each.
+// How a phase's matrices are cut into jobs.
+//   A matrix [N, K] (K a multiple of 512, N of 8) is a stream of tiles: row group rg = rows [8 rg, 8 rg + 8), tile t of it =
+//   columns [512 t, 512 t + 512); tiles of a row group are consecutive, row groups follow each other.  tpr = K / 512.
+//   A fill (one ring stage, one bulk copy) is up to 8 consecutive tiles: with tpr >= 5 a slice of one row group, otherwise
+//   gpf = 8 / tpr whole row groups.  A job is what one CTA must do as a whole: the fills of one row group (gpf == 1) or one
+//   fill of gpf row groups; for SwiGLU the same for the gate matrix followed by the same for the up matrix.
 struct GemvPlan {
-    int R, nch, sub, fpu, upj;
-    int U;            // stage-units in the phase
+    int tpr, gpf, sub;
     int J;            // jobs in the phase
     int js;           // jobs statically owned by every CTA: CTA c has [c*js, (c+1)*js)
     int pool0;        // first pooled job: [pool0, J) are claimed dynamically (or, without a counter, split statically)
+    int seg_job0[4];  // first job of each segment (plain phases)
+    int seg_rg0[4];   // first global row-group id of each segment
+    int nrg[3];       // row groups per segment
 };
-// pooled_permille: share of the jobs left to the pool (0 = all static).
 __device__ __forceinline__ GemvPlan gemv_plan(const GemvArgs& a, int n_cta, bool dynamic) {
     GemvPlan p;
-    p.R = kUnitBytes / a.KC;
-    p.nch = a.K / a.KC;
+    p.tpr = a.K / kTileK;
+    p.gpf = p.tpr >= 5 ? 1 : kFillTiles / p.tpr;
     p.sub = a.epi == EPI_SWIGLU ? 2 : 1;
-    int rows_total = 0;
-    if (a.epi == EPI_SWIGLU) rows_total = a.seg[0].rows;
-    else for (int i = 0; i < a.nseg; i++) rows_total += a.seg[i].rows;
-    p.U = rows_total / p.R * p.sub;
-    p.fpu = (p.nch + 1) / 2;
-    p.upj = p.nch == 1 ? 2 : p.sub;
-    p.J = (p.U + p.upj - 1) / p.upj;
+    int jobs = 0, rgs = 0;
+    for (int i = 0; i < 3; i++) {
+        const int n = i < a.nseg ? a.seg[i].rows / kTileRows : 0;
+        p.nrg[i] = n;
+        p.seg_job0[i] = jobs;
+        p.seg_rg0[i] = rgs;
+        if (a.epi != EPI_SWIGLU || i == 0) { jobs += (n + p.gpf - 1) / p.gpf; rgs += n; }
+    }
+    p.seg_job0[3] = jobs;
+    p.seg_rg0[3] = rgs;
+    p.J = jobs;
     if (dynamic) {
         p.js = (int)((long long)p.J * 3 / 4 / n_cta);       // three quarters static, the rest to whoever is ahead
         p.pool0 = p.js * n_cta;
@@ -332,24 +401,10 @@ __device__ __forceinline__ GemvPlan gemv_plan(const GemvArgs& a, int n_cta, bool
     return p;
 }
 
-// stage-unit id -> its first packed unit (K-chunk 0) in the weight stream
-__device__ __forceinline__ const unsigned char* unit_ptr(const GemvArgs& a, const GemvPlan& p, int u) {
-    int sg = 0;
-    int rg;                                  // row group inside the segment
-    if (a.epi == EPI_SWIGLU) {
-        sg = u & 1;
-        rg = u >> 1;
-    } else {
-        int row = u * p.R;
-        while (sg < a.nseg - 1 && row >= a.seg[sg].rows) { row -= a.seg[sg].rows; sg++; }
-        rg = row / p.R;
-    }
-    return (const unsigned char*)a.seg[sg].w + (size_t)rg * p.nch * kStageBytes;
-}
-
-// Producer ring position, carried across phases.
+// Ring positions, carried across phases.
 struct ProducerRing { int stage; uint32_t par; long long armed; };
-struct ConsumerRing { int stage; uint32_t par; };
+struct ConsumerRing { int stage; uint32_t par; uint32_t tpar; uint32_t ppar; int pf; };          // tpar: accumulator hand-over parity; ppar: phase parity
+struct MmaRing { int stage; uint32_t par; uint32_t tpar; uint32_t busy; uint32_t xpar; int pf; };   // busy: accumulators issued and not yet known drained
 
 // Producer side of one phase: ONE lane (lane 0 of the producer warp) walks this CTA's static jobs, then claims pooled
 // jobs with atomicAdd on *job_ctr (the next claim is always in flight while the current job is being issued), and
@@ -367,31 +422,30 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvPlan& 
         return true;
     };
     auto advance = [&]() { r.armed++; if (++r.stage == S) { r.stage = 0; r.par ^= 1u; } };
+    auto emit = [&](const unsigned char* src, int ntiles, int c0, int n_rg, int rg_global, bool job_end, int part) -> bool {
+        if (!next_stage()) return false;
+        const uint32_t fb = g.full0 + 8u * r.stage;
+        const uint32_t bytes = (uint32_t)ntiles * kTileBytes;
+        g.meta[r.stage] = make_int2(rg_global, (int)m2_pack(ntiles, c0, n_rg, job_end, part));
+        mbar_arrive_expect_tx(fb, bytes);
+        bulk_g2s(smem_u32(g.stage0 + (size_t)r.stage * kFillBytes), src, bytes, fb);
+        advance();
+        return true;
+    };
     auto issue_job = [&](int j) -> bool {
-        if (p.nch == 1) {
-            const int ua = 2 * j, ub = ua + 1;
-            const bool two = ub < p.U;
-            if (!next_stage()) return false;
-            const uint32_t fb = g.full0 + 8u * r.stage;
-            const uint32_t dst = smem_u32(g.stage0 + (size_t)r.stage * kFillBytes);
-            g.meta[r.stage] = ua;
-            mbar_arrive_expect_tx(fb, (uint32_t)(two ? kFillBytes : kStageBytes));
-            bulk_g2s(dst, unit_ptr(a, p, ua), (uint32_t)kStageBytes, fb);
-            if (two) bulk_g2s(dst + kStageBytes, unit_ptr(a, p, ub), (uint32_t)kStageBytes, fb);
-            advance();
-        } else {
-            for (int k = 0; k < p.upj; k++) {
-                const int u = j * p.upj + k;
-                if (u >= p.U) break;
-                const unsigned char* base = unit_ptr(a, p, u);
-                for (int c = 0; c < p.nch; c += 2) {
-                    if (!next_stage()) return false;
-                    const uint32_t fb = g.full0 + 8u * r.stage;
-                    const uint32_t bytes = (uint32_t)(c + 1 < p.nch ? kFillBytes : kStageBytes);
-                    g.meta[r.stage] = u;
-                    mbar_arrive_expect_tx(fb, bytes);
-                    bulk_g2s(smem_u32(g.stage0 + (size_t)r.stage * kFillBytes), base + (size_t)c * kStageBytes, bytes, fb);
-                    advance();
+        int sg = 0;
+        if (a.epi != EPI_SWIGLU) while (sg < a.nseg - 1 && j >= p.seg_job0[sg + 1]) sg++;
+        const int rg = (j - p.seg_job0[sg]) * p.gpf;                      // first row group of the job, inside its segment
+        const int n_rg = min(p.gpf, p.nrg[sg] - rg);
+        for (int part = 0; part < p.sub; part++) {
+            const unsigned char* base = (const unsigned char*)a.seg[sg + part].w + (size_t)rg * p.tpr * kTileBytes;
+            const bool last_part = part == p.sub - 1;
+            if (p.tpr <= kFillTiles) {
+                if (!emit(base, n_rg * p.tpr, 0, n_rg, p.seg_rg0[sg] + rg, last_part, part)) return false;
+            } else {
+                for (int c = 0; c < p.tpr; c += kFillTiles) {
+                    const int nt = min(kFillTiles, p.tpr - c);
+                    if (!emit(base + (size_t)c * kTileBytes, nt, c, 1, p.seg_rg0[sg] + rg, last_part && c + kFillTiles >= p.tpr, part)) return false;
                 }
             }
         }
@@ -416,7 +470,7 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvPlan& 
     }
     // END marker: a stage with no bytes
     if (!next_stage()) return false;
-    g.meta[r.stage] = kMetaEnd;
+    g.meta[r.stage] = make_int2(kMetaEnd, 0);
     mbar_arrive(g.full0 + 8u * r.stage);
     advance();
     return true;
@@ -436,163 +490,267 @@ __device__ __forceinline__ void gemv_producer_drain(const GemvSmem& g, const Pro
     }
 }
 
-// Consumer side of one phase: quantise x, then take fills off the ring until the END marker, reducing row sums in a
-// fixed order and running the epilogue chunk by chunk.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
+// Tensor-core side of one phase, run by ONE thread (lane 0 of the tensor-core warp).  For every fill that lands it issues
+// one tcgen05.mma per tile — A = the tile's 128 (block, row) vectors of 32 int8 weights straight from the ring stage,
+// B = the 48 activation rows (16 blocks x 3 levels) of the tile's K range, D = 128 lanes x 48 int32 columns of tensor
+// memory (tile i of the fill at column 64 i), overwritten — and has "accumulators written" signalled when they retire.
+// Lane (8 b + r) of tile t, column 3 b + l is the exact integer dot product of row r's block b with level l of the
+// matching activation block; the other 45 columns of a lane pair the weights with other blocks' activations and are
+// never read.  Measured on B200: an instruction of this shape occupies the tensor pipe for about 73 cycles whatever
+// N is, and tcgen05.ld issued while instructions are in flight completes only after they retire — so the fill's
+// instructions are issued back to back and the read-back follows as one burst, the two strictly alternating.
+__device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan& p, const GemvSmem& g, MmaRing& r, uint32_t tmem, uint32_t* status) {
+    const int S = g.stages;
+    auto fail = [&](uint32_t code) { if (!*g.abort) { atomicOr(status, code); *g.abort = 1; } return false; };
+    if (*g.abort) return false;
+    if (!mbar_wait_abortable(g.xready, r.xpar, g.abort)) return fail(LUM_ST_WAIT_TMEM);
+    r.xpar ^= 1u;
+    tc_fence_after_sync();
+    // operand descriptors: start address and lbo (128 B) in the low word, sbo (256 B) and the version in the high word
+    const uint32_t xq_lo = umma_desc_lo(smem_u32(g.xq), 128u);
+    const uint32_t st_lo = umma_desc_lo(smem_u32(g.stage0), 128u);
+    constexpr uint32_t hi = umma_desc_hi(256u);
+    constexpr uint32_t idesc = umma_idesc_s8(128, kMmaN);
+    const int tpr = p.tpr;
+    const bool wrap = p.gpf > 1;
+#ifdef LUM_PROBE
+    int& pf = r.pf;
+#endif
+    for (;;) {
+        // the previous fill's accumulators must have been read back before they are overwritten; waiting for that first
+        // costs nothing while the next fill is still in flight
+        if (r.busy) {
+            if (!mbar_wait_abortable(g.tempty0, r.tpar, g.abort)) return fail(LUM_ST_WAIT_TMEM);
+            r.tpar ^= 1u;
+            r.busy = 0u;
+        }
+        TPROBE(pf, 1);
+        if (!mbar_wait_abortable(g.full0 + 8u * r.stage, r.par, g.abort)) return fail(LUM_ST_WAIT_FULL);
+        TPROBE(pf, 0);
+        const int2 mm = g.meta[r.stage];
+        const int u = mm.x;
+        if (u != kMetaEnd) {
+            const uint32_t m2 = (uint32_t)mm.y;
+            const int nt = (int)(m2 & 15u), c0 = (int)((m2 >> 4) & 255u);
+            uint32_t a_lo = st_lo + (uint32_t)r.stage * (kFillBytes >> 4);
+            uint32_t b_lo = xq_lo + (uint32_t)c0 * (kXqTileBytes >> 4);
+            tc_fence_after_sync();
+            TPROBE(pf, 3);
+            if (nt == kFillTiles && !wrap) {
+                // the common case, straight-line: the tensor pipe takes ~60 cycles per instruction and the issuing thread
+                // is held that long, so every other instruction in between adds to the burst
+#pragma unroll
+                for (int i = 0; i < kFillTiles; i++)
+                    umma_s8_ss_split(tmem + (uint32_t)(64 * i), a_lo + (uint32_t)i * (kTileBytes >> 4), b_lo + (uint32_t)i * (kXqTileBytes >> 4), hi, idesc);
+            } else {
+                uint32_t d = tmem;
+                int t = c0;                                  // the tile's position along K
+#pragma unroll 1
+                for (int i = 0; i < nt; i++) {
+                    umma_s8_ss_split(d, a_lo, b_lo, hi, idesc);
+                    d += 64u;
+                    a_lo += kTileBytes >> 4;
+                    b_lo += kXqTileBytes >> 4;
+                    if (wrap && ++t == tpr) { t = 0; b_lo = xq_lo; }
+                }
+            }
+            TPROBE(pf, 4);
+            umma_commit(g.tfull0);
+            TPROBE(pf, 2);
+        } else {
+            mbar_arrive(g.tfull0);                           // the END marker travels the same way, with nothing to read back
+        }
+        r.busy = 1u;                                         // every hand-over, END included, is answered on tempty
+#ifdef LUM_PROBE
+        pf++;
+#endif
+        if (++r.stage == S) { r.stage = 0; r.par ^= 1u; }
+        if (u == kMetaEnd) break;
+    }
+    return true;
+}
+
+// Consumer side of one phase, called by all kWorkers threads: quantise x (everyone), then the first kConsumers threads
+// take fills off the ring until the END marker.  Warpgroup w (4 warps = the 128 lanes of tensor memory) drains slot w:
+// thread (warp q, lane) owns lane 32 q + lane of every tile = block 4 q + lane / 8, row lane % 8, reads its three int32 dot
+// products, turns them into the block's f32 contribution and adds up its tiles; per fill and row group the 4 block-lanes
+// of a warp that share a row are folded with two shuffles and the 8 warps' partials are summed in a fixed order at the
+// end of a chunk, followed by the epilogue.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
 __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvPlan& p, const GemvSmem& g,
-                                             ConsumerRing& cr, int tid, uint32_t* status, ArgBest* best) {
-    const int lane = tid & 31;
-    const int K = a.K, KC = a.KC, nch = p.nch, R = p.R, S = g.stages;
+                                             ConsumerRing& cr, int tid, uint32_t tmem, uint32_t* status, ArgBest* best) {
     GPROBE(1);
     gemv_quantize_x(a, xs, is_writer, g, tid);
     GPROBE(2);
+    if (tid >= kConsumers) return;
+    const int lane = tid & 31, warp = tid >> 5, wg = warp >> 2, q = warp & 3;
+    const int S = g.stages, tpr = p.tpr;
+    const int kbl = (q << 2) + (lane >> 3);              // this thread's block inside a tile
+    const int m = (q << 5) + lane;                       // its tensor-memory lane = (block, row) index inside a tile
+    const uint32_t tlane = tmem + ((uint32_t)(q << 5) << 16) + (uint32_t)(256 * wg + 12 * q);
+    const int sel = lane >> 3;
 
-    const int TPB = KC >> 5;                   // threads across one row chunk: one 32-block each
-    const int row = tid / TPB;                 // this thread's row of the unit (512 threads = R rows x TPB blocks)
-    const int ks = tid - row * TPB;            // block slot inside the chunk
-    const int WPS = TPB >= 32 ? (TPB >> 5) : 1;
-    uint4 xa[3][2];
-    float sx = 0.0f;
-    auto load_xblock = [&](int c) {
-        const int blk = c * TPB + ks;
-#pragma unroll
-        for (int l = 0; l < 3; l++) {
-            const uint4* q = (const uint4*)(g.xq + (size_t)l * K + ((size_t)blk << 5));
-            xa[l][0] = q[0];
-            xa[l][1] = q[1];
-        }
-        sx = g.xsc[blk];
-    };
-    if (nch == 1) load_xblock(0);
-
-    // wait for the ring stage (returns its unit id, or kMetaEnd also when the CTA is aborting), and hand it back
-    auto wait_full = [&]() -> int {
-        if (*g.abort) return kMetaEnd;
-        if (!mbar_wait_abortable(g.full0 + 8u * cr.stage, cr.par, g.abort)) {
-            if (!*g.abort) { atomicOr(status, LUM_ST_WAIT_FULL); *g.abort = 1; }
-            return kMetaEnd;
-        }
-        return g.meta[cr.stage];
-    };
-    auto release = [&]() {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(g.empty0 + 8u * cr.stage);
-        if (++cr.stage == S) { cr.stage = 0; cr.par ^= 1u; }
-    };
-    // one stage-unit held at `sq`: this thread's 32 weights of its row against its x block
-    auto unit_dot = [&](const unsigned char* sq) -> float {
-        const uint4* wp = (const uint4*)(sq + (size_t)row * KC + ((size_t)ks << 5));
-        const uint4 w0 = wp[0], w1 = wp[1];
-        const float dw = __half2float(((const __half*)(sq + kUnitBytes))[row * TPB + ks]);
-        int i1 = 0, i2 = 0, i3 = 0;
-#define LUM_DP(wv, j, f)                                   \
-    i1 = __dp4a((int)(wv), (int)xa[0][j].f, i1);           \
-    i2 = __dp4a((int)(wv), (int)xa[1][j].f, i2);           \
-    i3 = __dp4a((int)(wv), (int)xa[2][j].f, i3);
-        LUM_DP(w0.x, 0, x) LUM_DP(w0.y, 0, y) LUM_DP(w0.z, 0, z) LUM_DP(w0.w, 0, w)
-        LUM_DP(w1.x, 1, x) LUM_DP(w1.y, 1, y) LUM_DP(w1.z, 1, z) LUM_DP(w1.w, 1, w)
-#undef LUM_DP
-        // i1 * 254 + i2 fits an int32 (|i1| <= 32 * 127 * 127): one conversion fewer
-        const float t = fmaf((float)i3, 1.0f / 64516.0f, (float)(i1 * 254 + i2) * (1.0f / 254.0f));
-        return t * (sx * dw);
-    };
-
+    auto fail = [&](uint32_t code) { if (!*g.abort) { atomicOr(status, code); *g.abort = 1; } };
+    int slot = 0, slot_base = 0;
     bool ended = false;
+#ifdef LUM_PROBE
+    int& pf = cr.pf;
+    const bool pl = lane == 0 && q == 0;
+#endif
 #pragma unroll 1
     while (!ended) {
-        int slot = 0;                          // local unit slots filled in this chunk
+        slot = 0;
 #pragma unroll 1
-        while (slot < kChunkUnits && !ended) {
-            // Units are finished four at a time so that one transposed butterfly (6 shuffles) reduces four row sums.
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            int filled = 0;
-            if (nch == 1) {
-                // a fill = a job = two units (two row groups, same x): both dot products run side by side
+        for (;;) {
+            // "accumulators written" is the wait that blocks.  The accumulators are read back first and the slot handed back at
+            // once — that hand-over paces the tensor core; everything else happens off that path.  All four tiles of the slot
+            // are read whether or not the fill has them (absent tiles leave stale integers that are never used; an END marker
+            // has nothing new at all), in four loads and one wait (65-100 cycles).
+            if (!mbar_wait_abortable(g.tfull0, cr.tpar, g.abort)) { fail(LUM_ST_WAIT_TMEM); ended = true; break; }
+            cr.tpar ^= 1u;
+            tc_fence_after_sync();
+            uint32_t va[16], vb[16], vc[16], vd[16];
+            tmem_ld16(tlane, va);
+            tmem_ld16(tlane + 64u, vb);
+            tmem_ld16(tlane + 128u, vc);
+            tmem_ld16(tlane + 192u, vd);
+            tmem_ld_wait();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(g.tempty0);
+#ifdef LUM_PROBE
+            if (pl) TPROBE(pf, 7 + 4 * wg);
+#endif
+            // The stage has landed (the tensor-core warp waited for it); observing its barrier here, complete at the first
+            // attempt, makes the bulk copy's bytes and the producer's meta word visible to this thread by the book.
+            if (!mbar_wait_abortable(g.full0 + 8u * cr.stage, cr.par, g.abort)) { fail(LUM_ST_WAIT_FULL); ended = true; break; }
+            const int2 mm = g.meta[cr.stage];
+            const int u = mm.x;
+            if (u == kMetaEnd) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(g.empty0 + 8u * cr.stage);
+                if (++cr.stage == S) { cr.stage = 0; cr.par ^= 1u; }
+#ifdef LUM_PROBE
+                pf++;
+#endif
+                ended = true;
+                break;
+            }
+            const uint32_t m2 = (uint32_t)mm.y;
+            const int nt = (int)(m2 & 15u), c0 = (int)((m2 >> 4) & 255u), n_rg = (int)((m2 >> 12) & 15u);
+            const unsigned char* st = g.stage0 + (size_t)cr.stage * kFillBytes;
+            if (c0 == 0) {
+                slot_base = slot;
+                slot += n_rg;
+                if (tid < n_rg) {
+                    g.unit_of[slot_base + tid] = u + tid;
+                    g.pair_of[slot_base + tid] = (m2 & kM2Up) ? -1 : slot_base + n_rg + tid;
+                }
+            }
+            // The only thing the draining warps need from the stage are their block scales: fetch them and release the stage
+            // (its quants were consumed by the tensor core before "accumulators written" was signalled).
+            float dw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            {
+                const __half* wsc = (const __half*)(st + (size_t)(4 * wg) * kTileBytes + kTileQ) + m;
 #pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    if (!ended) {
-                        const int u = wait_full();
-                        if (u == kMetaEnd) {
-                            ended = true;
-                            if (!*g.abort) release();
-                        } else {
-                            const unsigned char* sq = g.stage0 + (size_t)cr.stage * kFillBytes;
-                            const bool two = u + 1 < p.U;
-                            acc[2 * j] = unit_dot(sq);
-                            acc[2 * j + 1] = two ? unit_dot(sq + kStageBytes) : 0.0f;
-                            if (tid == 0) { g.unit_of[slot + 2 * j] = u; g.unit_of[slot + 2 * j + 1] = u + 1; }
-                            filled = 2 * j + (two ? 2 : 1);
-                            release();
-                        }
+                for (int j = 0; j < 4; j++)
+                    if (4 * wg + j < nt) dw[j] = __half2float(wsc[j * (kTileBytes / 2)]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(g.empty0 + 8u * cr.stage);
+#ifdef LUM_PROBE
+            if (pl) TPROBE(pf, 8 + 4 * wg);
+#endif
+            if (++cr.stage == S) { cr.stage = 0; cr.par ^= 1u; }
+            float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (4 * wg < nt) {
+#define LUM_SEL(v, o) (int)(sel == 0 ? v[o] : sel == 1 ? v[3 + o] : sel == 2 ? v[6 + o] : v[9 + o])
+                const int i1[4] = {LUM_SEL(va, 0), LUM_SEL(vb, 0), LUM_SEL(vc, 0), LUM_SEL(vd, 0)};
+                const int i2[4] = {LUM_SEL(va, 1), LUM_SEL(vb, 1), LUM_SEL(vc, 1), LUM_SEL(vd, 1)};
+                const int i3[4] = {LUM_SEL(va, 2), LUM_SEL(vb, 2), LUM_SEL(vc, 2), LUM_SEL(vd, 2)};
+#undef LUM_SEL
+                // the K position of this warpgroup's first tile (narrow matrices: tile index modulo tiles per row group)
+                int t = c0 + 4 * wg;
+                if (p.gpf > 1) t = t % tpr;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (4 * wg + j < nt) {
+                        const float sx = g.xsc[(t << 4) + kbl];
+                        t++;
+                        if (p.gpf > 1 && t == tpr) t = 0;
+                        // i1 * 254 + i2 fits an int32 (|i1| <= 32 * 127 * 127): one conversion fewer
+                        const float tt = fmaf((float)i3[j], 1.0f / 64516.0f, (float)(i1[j] * 254 + i2[j]) * (1.0f / 254.0f));
+                        val[j] = tt * (sx * dw[j]);
                     }
+                }
+            }
+            // fold this warp's tiles into the fill's row groups: lanes with equal (lane & 7) hold the same row
+            if (p.gpf == 1) {
+                float v = (val[0] + val[1]) + (val[2] + val[3]);
+                v += __shfl_xor_sync(0xffffffffu, v, 8);
+                v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if (lane < 8) {
+                    float* dst = g.red + (size_t)slot_base * 64 + warp * 8 + lane;
+                    *dst = c0 == 0 ? v : *dst + v;
                 }
             } else {
-                // a unit = fpu fills of two K-chunks each; they arrive back to back
-#pragma unroll
-                for (int uu = 0; uu < 4; uu++) {
-                    if (!ended) {
 #pragma unroll 1
-                        for (int c = 0; c < nch; c += 2) {
-                            const int u = wait_full();
-                            if (u == kMetaEnd) {
-                                ended = true;
-                                if (!*g.abort) release();
-                                break;
-                            }
-                            const unsigned char* sq = g.stage0 + (size_t)cr.stage * kFillBytes;
-                            load_xblock(c);
-                            acc[uu] += unit_dot(sq);
-                            if (c + 1 < nch) {
-                                load_xblock(c + 1);
-                                acc[uu] += unit_dot(sq + kStageBytes);
-                            }
-                            if (c == 0 && tid == 0) g.unit_of[slot + uu] = u;
-                            if (c + 2 >= nch) filled = uu + 1;
-                            release();
-                        }
-                    }
+                for (int rgl = 0; rgl < n_rg; rgl++) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) v += ((4 * wg + j) / tpr == rgl) ? val[j] : 0.0f;
+                    v += __shfl_xor_sync(0xffffffffu, v, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 16);
+                    if (lane < 8) g.red[(size_t)(slot_base + rgl) * 64 + warp * 8 + lane] = v;
                 }
             }
-            if (filled > 0) {
-                // transposed butterfly over the lanes that share a row: afterwards one lane per unit holds its sum
-                if (TPB >= 32) {
-                    const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0;
-                    const float s0 = __shfl_xor_sync(0xffffffffu, h16 ? acc[0] : acc[2], 16);
-                    const float s1 = __shfl_xor_sync(0xffffffffu, h16 ? acc[1] : acc[3], 16);
-                    const float a0 = (h16 ? acc[2] : acc[0]) + s0, a1 = (h16 ? acc[3] : acc[1]) + s1;
-                    float v = (h8 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h8 ? a0 : a1, 8);
-                    v += __shfl_xor_sync(0xffffffffu, v, 4);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    const int uidx = (h16 ? 2 : 0) + (h8 ? 1 : 0);
-                    if ((lane & 7) == 0 && uidx < filled) g.red[(size_t)(slot + uidx) * 32 + row * WPS + (ks >> 5)] = v;
-                } else {
-                    // 16 lanes per row (KC = 512): each half-warp is one row
-                    const bool h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
-                    const float s0 = __shfl_xor_sync(0xffffffffu, h8 ? acc[0] : acc[2], 8);
-                    const float s1 = __shfl_xor_sync(0xffffffffu, h8 ? acc[1] : acc[3], 8);
-                    const float a0 = (h8 ? acc[2] : acc[0]) + s0, a1 = (h8 ? acc[3] : acc[1]) + s1;
-                    float v = (h4 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, h4 ? a0 : a1, 4);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    const int uidx = (h8 ? 2 : 0) + (h4 ? 1 : 0);
-                    if ((lane & 3) == 0 && uidx < filled) g.red[(size_t)(slot + uidx) * 32 + row] = v;
-                }
-                slot += filled;
-            }
+#ifdef LUM_PROBE
+            pf++;
+#endif
+            if ((m2 & kM2JobEnd) && slot + p.sub * p.gpf > kChunkRG) break;
         }
         GPROBE(3);
-        named_sync(1, kConsumers);
-        // fixed-order sum of the per-warp partials -> vals, then the epilogue for this chunk's units
-        for (int i = tid; i < slot * R; i += kConsumers) {
-            const int u = i / R, r = i - u * R;
+        named_sync(2, kConsumers);
+        // fixed-order sum of the 8 warps' partials -> vals, then the epilogue for this chunk's row groups
+        for (int i = tid; i < slot * kTileRows; i += kConsumers) {
+            const float* rp = g.red + (size_t)(i >> 3) * 64 + (i & 7);
             float t = 0.0f;
-            for (int wi = 0; wi < WPS; wi++) t += g.red[(size_t)u * 32 + r * WPS + wi];
+#pragma unroll
+            for (int w = 0; w < 8; w++) t += rp[w * 8];
             g.vals[i] = t;
         }
-        named_sync(1, kConsumers);
-        if (slot > 0) gemv_epilogue_units(a, g.vals, g.unit_of, slot, R, tid, kConsumers, g.scratch, 1, best);
-        named_sync(1, kConsumers);
+        named_sync(2, kConsumers);
+        if (slot > 0) gemv_epilogue_units(a, g.vals, g.unit_of, g.pair_of, slot, tid, kConsumers, g.scratch, 2, best);
+        named_sync(2, kConsumers);
     }
+    // (The END marker reaches the draining warps through the tensor-core warp, so they cannot finish a phase before it has:
+    // the "activations quantised" barrier of the next phase never runs more than one phase ahead of its waiter.)
+}
+
+// Kernel start (all threads of the CTA): barriers, tensor memory.  Returns the tensor-memory base address.
+__device__ __forceinline__ uint32_t gemv_cta_begin(const GemvSmem& g, int tid, volatile int* abort_word) {
+    if (tid == 0) {
+        *abort_word = 0;
+        gemv_init_barriers(g);
+    }
+    if ((tid >> 5) == kMmaWarp) tmem_alloc(g.tmem_slot, kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    uint32_t base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(base) : "r"(g.tmem_slot));
+    return base;
+}
+// Kernel end.  The draining warps call gemv_consumers_done() after their last phase; the tensor-core warp calls
+// gemv_mma_end(), which waits (bounded) for the last instruction it issued, then for the draining warps, and frees tensor memory.
+__device__ __forceinline__ void gemv_consumers_done() { tc_fence_before_sync(); named_arrive(4, kConsumers + 32); }
+__device__ __forceinline__ void gemv_mma_end(const GemvSmem& g, uint32_t tmem, int lane, uint32_t* status) {
+    if (lane == 0) {
+        umma_commit(g.fin);
+        if (!mbar_wait(g.fin, 0u)) atomicOr(status, LUM_ST_WAIT_TMEM);
+    }
+    __syncwarp();
+    named_sync(4, kConsumers + 32);
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
 }
 
 }  // namespace lum

@@ -15,7 +15,10 @@
 // CTA's share of *all* weight matrices of the step in order and keeps a ring of shared-memory
 // stages full with bulk copies, regardless of where the consumer warps are.  While the consumers sit
 // in a grid barrier, run attention, or quantise the next activation vector, the producer is already
-// fetching the next operation's weights, so HBM never waits for a kernel boundary.
+// fetching the next operation's weights, so HBM never waits for a kernel boundary.  The multiply-adds
+// run on the tensor core (a third warp role, see lum_gemv_dev.cuh), which leaves the draining warps so
+// little to do per weight that they empty a full ring in a fraction of the time HBM took to fill it:
+// a stall is paid for only to the extent that it outlasts the ring.
 #include <cstdlib>
 
 #include "lum_attn_dev.cuh"
@@ -31,6 +34,7 @@ __device__ unsigned long long g_arrive[64 * 160];
 extern "C" int lum_arrive_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_arrive, sizeof(g_arrive)); }
 #define MPROBE(i) do { if (blockIdx.x == 0 && tid == 0 && (i) < 1024) g_mprobe[i] = globaltimer_ns(); } while (0)
 extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_mprobe, sizeof(g_mprobe)); }
+extern "C" int lum_mtl_read(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl)); }
 #else
 #define MPROBE(i) do { } while (0)
 #endif
@@ -42,7 +46,7 @@ extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpy
 // (LUM_WAIT_BUDGET_CYCLES); once it runs out the kernel-wide abort flag is raised and every later wait
 // in every CTA returns at once.
 __device__ __forceinline__ void grid_barrier(const MegaArgs& a, unsigned long long& seq, volatile int* cta_abort, int tid) {
-    named_sync(1, kConsumers);                      // all of this CTA's writes of the phase are issued
+    named_sync(1, kWorkers);                        // all of this CTA's writes of the phase are issued
     if (tid == 0) {
         __threadfence();
 #ifdef LUM_PROBE
@@ -75,7 +79,7 @@ __device__ __forceinline__ void grid_barrier(const MegaArgs& a, unsigned long lo
         __threadfence();
     }
     seq++;
-    named_sync(1, kConsumers);
+    named_sync(1, kWorkers);
 }
 
 template <int HD, int GM, bool BF16>
@@ -136,28 +140,27 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = (int)blockIdx.x, ncta = (int)gridDim.x;
     GemvSmem g;
-    gemv_carve(smem, a.k_max, a.stages, &s_abort, &g);
-    if (tid == 0) {
-        s_abort = 0;
-        gemv_init_barriers(g);
-    }
-    __syncthreads();
+    gemv_carve(smem, a.k_max, a.stages, &s_abort, &g, attn_smem_bytes(HD, GM));
+    const uint32_t tmem = gemv_cta_begin(g, tid, &s_abort);
 
-    const bool is_producer = warp == kConsumers / 32;
+    const bool is_producer = warp == kProducerWarp, is_mma = warp == kMmaWarp;
+    const bool is_worker = warp < kWorkers / 32;
     ProducerRing pring{0, 0u, 0};
-    ConsumerRing cring{0, 0u};
+    ConsumerRing cring{0, 0u, 0u, 0u, 0};
+    MmaRing mring{0, 0u, 0u, 0u, 0u, 0};
+    bool issuing = true;
     unsigned long long seq = a.gbar_base;             // grid barriers passed so far
     unsigned long long pseq = a.gbar_base;            // running phase number: picks the job-claim counter of each phase
     bool producing = true;
     int pos = 0, tok = 0;
-    if (!is_producer) {
+    if (is_worker) {
         pos = a.state->pos;
         tok = a.forced ? a.forced[0] : a.state->tok;
         if (pos < 0 || pos + a.n_tokens > a.max_seq || tok < 0 || tok >= a.vocab) {
             // Refuse the whole launch the same way in every CTA (all read the same state): nothing was written yet.
             if (cta == 0 && tid == 0) atomicOr(a.status, pos < 0 || pos + a.n_tokens > a.max_seq ? LUM_ST_BAD_POS : LUM_ST_BAD_TOKEN);
             if (tid == 0) s_abort = 1;
-            named_sync(1, kConsumers);
+            named_sync(1, kWorkers);
         }
     }
 
@@ -191,6 +194,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                     if (t == 1 && blockIdx.x == 0) g_mprobe[512 + ph * 2 + 1] = globaltimer_ns();
 #endif
                 }
+            } else if (is_mma) {
+                if (streams && lane == 0 && issuing) issuing = gemv_mma_issue(ga, plan, g, mring, tmem, a.status);
             } else if (!streams) {
                 // RoPE + cache append + attention
                 if (t == 1) MPROBE(ph * 3);
@@ -204,7 +209,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                 else xs.x = p == 2 ? a.attn : p == 4 ? a.h : a.x;
                 ArgBest best{-INFINITY, -1};
                 if (t == 1) MPROBE(ph * 3);
-                if (!s_abort) gemv_consume(ga, xs, cta == 0, plan, g, cring, tid, a.status, &best);
+                if (!s_abort) gemv_consume(ga, xs, cta == 0, plan, g, cring, tid, tmem, a.status, &best);
                 if (t == 1) MPROBE(ph * 3 + 1);
                 if (p == 5 && tid == 0) { a.part_val[cta] = best.v; a.part_idx[cta] = best.i; }
                 grid_barrier(a, seq, &s_abort, tid);
@@ -215,7 +220,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                         const int fi = argmax_final(a.part_val, a.part_idx, ncta, lane).i;
                         if (lane == 0) s_tok = fi;
                     }
-                    named_sync(1, kConsumers);
+                    named_sync(1, kWorkers);
                     const int sampled = s_abort ? 0 : max(0, s_tok);
                     if (cta == 0 && tid == 0 && !s_abort) {
                         DecodeState* st = a.state;
@@ -229,7 +234,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                 }
             }
         }
-        if (!is_producer && a.forced && t + 1 < a.n_tokens) tok = a.forced[t + 1];
+        if (is_worker && a.forced && t + 1 < a.n_tokens) tok = a.forced[t + 1];
         pos++;
     }
 
@@ -237,6 +242,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
         if (lane == 0 && (s_abort || !producing)) gemv_producer_drain(g, pring, a.status);
         return;
     }
+    if (is_mma) {
+        gemv_mma_end(g, tmem, lane, a.status);
+        return;
+    }
+    if (tid < kConsumers) gemv_consumers_done();
     if (cta == 0 && tid == 0 && !s_abort) {
         a.state->pos = pos;
         a.state->tok = tok;
@@ -245,10 +255,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
 
 // ------------------------------------------------------------------------------------------- host side
 
-size_t mega_smem_bytes(int k_max, int stages) { return gemv_fixed_smem(k_max) + (size_t)stages * kFillBytes; }
+// the attention phase borrows the activation / reduction area; it is sized for the larger of the two uses
+static size_t mega_scratch(int hd, int groups) { return attn_smem_bytes(hd, groups <= 4 ? 4 : 8); }
+size_t mega_smem_bytes(int k_max, int stages, int hd, int groups) { return gemv_fixed_smem(k_max, mega_scratch(hd, groups)) + (size_t)stages * kFillBytes; }
 
-int mega_pick_stages(int k_max) {
-    int stages = (int)((226 * 1024 - (long)gemv_fixed_smem(k_max)) / kFillBytes);
+int mega_pick_stages(int k_max, int hd, int groups) {
+    int stages = (int)((226 * 1024 - (long)gemv_fixed_smem(k_max, mega_scratch(hd, groups))) / kFillBytes);
     if (stages > kMaxStages) stages = kMaxStages;
     static const int env_stages = [] { const char* e = getenv("LUM_MEGA_STAGES"); return e ? atoi(e) : 0; }();
     if (env_stages > 0 && env_stages < stages) stages = env_stages;
@@ -259,11 +271,8 @@ bool mega_supported(const MegaArgs& a) {
     if (a.hd != 64 && a.hd != 128) return false;
     if (!a.kc_h || !a.kc_o || !a.kc_f) return false;
     if (a.k_max > 16384) return false;
-    // attention scratch aliases the activation planes and the reduction scratch behind them
-    const size_t alias = (size_t)3 * a.k_max + (size_t)a.k_max / 8 + (size_t)(kRedFloats + kValsFloats) * 4;
     if (a.n_kv <= 0 || a.n_q % a.n_kv || a.n_q / a.n_kv > 8 || a.n_splits < 1) return false;
-    if (attn_smem_bytes(a.hd, a.n_q / a.n_kv) > alias) return false;
-    return mega_pick_stages(a.k_max) >= 2;
+    return mega_pick_stages(a.k_max, a.hd, a.n_q / a.n_kv) >= 2;
 }
 
 cudaError_t launch_mega(const MegaArgs& a_in, int sm_count, cudaStream_t st) {
@@ -276,7 +285,7 @@ cudaError_t launch_mega(const MegaArgs& a_in, int sm_count, cudaStream_t st) {
                                  : (bf ? (const void*)decode_mega<64, 8, true> : (const void*)decode_mega<64, 8, false>);
     else return cudaErrorInvalidValue;
     if (a.n_kv * a.n_splits > sm_count) return cudaErrorInvalidValue;
-    const size_t smem = mega_smem_bytes(a.k_max, a.stages);
+    const size_t smem = mega_smem_bytes(a.k_max, a.stages, a.hd, a.n_q / a.n_kv);
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));
     if (e != cudaSuccess) return e;
     if (smem > 226 * 1024) return cudaErrorInvalidValue;

@@ -43,8 +43,8 @@ struct MegaArgs {
 };
 
 bool mega_supported(const MegaArgs& a);
-int mega_pick_stages(int k_max);
-size_t mega_smem_bytes(int k_max, int stages);
+int mega_pick_stages(int k_max, int hd, int groups);
+size_t mega_smem_bytes(int k_max, int stages, int hd, int groups);
 // number of grid barriers one launch passes (the host advances gbar_base by it)
 inline unsigned long long mega_barriers(const MegaArgs& a) {
     const unsigned long long heads = a.head_every_token ? (unsigned long long)a.n_tokens : 1ull;

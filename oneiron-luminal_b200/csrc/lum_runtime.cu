@@ -483,7 +483,7 @@ int setup_mega(lum_rt* rt) {
     a.attn_part = rt->attn_part; a.attn_cnt = rt->attn_cnt; a.part_val = rt->am_val; a.part_idx = rt->am_idx;
     a.state = rt->state; a.tokens_out = rt->tokens_out;
     a.n_splits = rt->n_splits;
-    a.stages = mega_pick_stages(a.k_max);
+    a.stages = mega_pick_stages(a.k_max, a.hd, a.n_q / a.n_kv);
     a.status = rt->status;
     if (a.n_kv * a.n_splits > rt->sm_count || !mega_supported(a)) return 0;
     if (int r = dev_alloc(rt, (void**)&rt->mega_layers, hl.size() * sizeof(MegaLayer))) return r;
@@ -1034,7 +1034,7 @@ size_t lum_q8_0_packed_bytes(int32_t n, int32_t k) { return q8_packed_bytes(n, k
 
 int32_t lum_op_q8_0_pack(const int8_t* q, const void* s, int32_t n, int32_t k, void* packed, void* stream) {
     const int kc = q8_pack_kc(n, k);
-    if (!q || !s || !packed || !kc) { g_create_error = "q8_0_pack: shape cannot be packed (needs K % 512 == 0, K <= 16384, N % (16384 / KC) == 0)"; return LUM_E_INVALID; }
+    if (!q || !s || !packed || !kc) { g_create_error = "q8_0_pack: shape cannot be packed (needs K % 512 == 0, K <= 16384, N % 8 == 0)"; return LUM_E_INVALID; }
     cudaError_t e = launch_q8_pack_units(q, (const __half*)s, n, k, kc, (unsigned char*)packed, (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : op_fail("q8_0_pack", e);
 }

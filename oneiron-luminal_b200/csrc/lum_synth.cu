@@ -4,11 +4,13 @@
 //
 // Device layouts of a Q8_0 matrix [N, K] (both hold exactly the wire format's 34/32 bytes per weight):
 //  * planes — int8 quants [N, K] and, separately, binary16 scales [N, K/32]; every row 16-byte aligned.
-//  * packed — the layout the streaming GEMV reads.  The matrix is cut into stage-units of R rows x KC
-//    columns with R * KC = 16384 (KC the largest power of two in 512..4096 dividing K).  A unit is
-//    17408 contiguous bytes: its quants row-major [R, KC], then its scales [R, KC/32].  Units are
-//    ordered by row group, then K-chunk, so that one bulk copy fetches one pipeline stage and the
-//    chunks of a row group are consecutive.  Used whenever K % 512 == 0, K <= 16384 and N % R == 0.
+//  * packed — the layout the streaming GEMV reads, available when K % 512 == 0 and N % 8 == 0.  The matrix is a stream
+//    of tiles of 8 rows x 512 columns: the tiles of row group g (rows 8g .. 8g+7) are consecutive, row groups follow each
+//    other, so a contiguous run of tiles is one bulk copy.  A tile is 4352 bytes: 4096 quants in the order the tensor
+//    core reads a K-major operand without swizzling — the 32 quants of block b (0..15) of row r form operand row
+//    b*8 + r, and operand rows are stored in groups of 8 as two 128-byte core matrices (bytes 0-15 of the 8 rows, then
+//    bytes 16-31), i.e. quant j of (b, r) sits at b*256 + (j/16)*128 + r*16 + j%16 — followed by the 128 binary16 scales,
+//    entry b*8 + r.
 //
 // Generator (all integer arithmetic except the normal draw, which is binary64 Box-Muller):
 //   key(seed, tid)    = mix(seed + G * (tid + 1)),  G = 0x9E3779B97F4A7C15, mix = SplitMix64 finaliser
@@ -40,18 +42,24 @@ __device__ __forceinline__ double rng_normal(uint64_t key, uint64_t idx) {
 // exactly its slice.
 struct Shard { size_t rows, cols, row0, col0, full_cols; };
 
-constexpr size_t kUnitQ = 16384, kUnitBytes = 17408;
+constexpr size_t kTileQ = 4096, kTileBytes = 4352, kTileK = 512, kTileRows = 8;
 
-// packed position -> (row, col) of the shard.  i = index of a quant inside the packed quant areas
-// laid end to end (unit after unit), kc = K-chunk, cols = K.
-__device__ __forceinline__ void packed_to_rc(size_t i, int kc, size_t cols, size_t* r, size_t* c, size_t* byte_off) {
-    const size_t u = i / kUnitQ, within = i - u * kUnitQ;
-    const size_t nch = cols / kc, R = kUnitQ / kc;
-    const size_t g = u / nch, ch = u - g * nch;
-    const size_t rr = within / kc, kk = within - rr * kc;
-    *r = g * R + rr;
-    *c = ch * kc + kk;
-    *byte_off = u * kUnitBytes + within;
+// packed position -> (row, col) of the shard.  i = index of a quant inside the packed quant areas laid end to end
+// (tile after tile), a multiple of 16: the 16 quants from i on are 16 consecutive columns of one row.  cols = K.
+__device__ __forceinline__ void packed_to_rc(size_t i, size_t cols, size_t* r, size_t* c, size_t* byte_off) {
+    const size_t T = i / kTileQ, within = i - T * kTileQ;
+    const size_t tpr = cols / kTileK;
+    const size_t g = T / tpr, t = T - g * tpr;
+    const size_t b = within >> 8, h = (within >> 7) & 1, rr = (within >> 4) & 7, j = within & 15;
+    *r = g * kTileRows + rr;
+    *c = t * kTileK + b * 32 + h * 16 + j;
+    *byte_off = T * kTileBytes + within;
+}
+// where the scale of block (row r, columns c .. c+31) lives in the packed stream
+__device__ __forceinline__ size_t packed_scale_off(size_t r, size_t c, size_t cols) {
+    const size_t tpr = cols / kTileK;
+    const size_t T = (r / kTileRows) * tpr + c / kTileK;
+    return T * kTileBytes + kTileQ + ((((c % kTileK) >> 5) << 3) + (r & 7)) * 2;
 }
 
 __global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh, int kc) {
@@ -59,7 +67,7 @@ __global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh, int kc) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
     if (i >= sh.rows * sh.cols) return;
     size_t r, c, off;
-    if (kc) packed_to_rc(i, kc, sh.cols, &r, &c, &off);
+    if (kc) packed_to_rc(i, sh.cols, &r, &c, &off);
     else { r = i / sh.cols; c = i - r * sh.cols; off = i; }
     const size_t gi = (sh.row0 + r) * sh.full_cols + sh.col0 + c;
     uint32_t w[4];
@@ -80,32 +88,23 @@ __global__ void synth_q8_scales(uint64_t skey, __half* s, unsigned char* packed,
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t bpr = sh.cols / 32;
     if (b >= sh.rows * bpr) return;
-    size_t r, c, off;
-    if (kc) packed_to_rc(b * 32, kc, sh.cols, &r, &c, &off);
-    else { r = b / bpr; c = (b - r * bpr) * 32; }
+    const size_t r = b / bpr, c = (b - r * bpr) * 32;
     const size_t gb = ((sh.row0 + r) * sh.full_cols + sh.col0 + c) / 32;
     const __half v = __float2half_rn((float)(fabs(0.02 * rng_normal(skey, gb)) / 127.0));
-    if (kc) {
-        const size_t u = (b * 32) / kUnitQ, within_blocks = b - u * (kUnitQ / 32);
-        *(__half*)(packed + u * kUnitBytes + kUnitQ + within_blocks * 2) = v;
-    } else {
-        s[b] = v;
-    }
+    if (kc) *(__half*)(packed + packed_scale_off(r, c, sh.cols)) = v;
+    else s[b] = v;
 }
 // planes -> packed
 __global__ void q8_pack_units(const int8_t* q, const __half* s, size_t rows, size_t cols, int kc, unsigned char* out) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
     if (i >= rows * cols) return;
     size_t r, c, off;
-    packed_to_rc(i, kc, cols, &r, &c, &off);
+    packed_to_rc(i, cols, &r, &c, &off);
     *(uint4*)(out + off) = *(const uint4*)(q + r * cols + c);
-    if ((i & 31) == 0) {
-        const size_t b = i / 32, u = i / kUnitQ, within_blocks = b - u * (kUnitQ / 32);
-        *(__half*)(out + u * kUnitBytes + kUnitQ + within_blocks * 2) = s[r * (cols / 32) + c / 32];
-    }
+    if ((c & 31) == 0) *(__half*)(out + packed_scale_off(r, c, cols)) = s[r * (cols / 32) + c / 32];
 }
 cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st) {
-    if (kc <= 0 || K % kc || ((size_t)rows * K) % kUnitQ) return cudaErrorInvalidValue;
+    if (kc != (int)kTileK || K % kTileK || rows % kTileRows) return cudaErrorInvalidValue;
     const size_t t16 = (size_t)rows * K / 16;
     q8_pack_units<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(q, s, (size_t)rows, (size_t)K, kc, out);
     return cudaGetLastError();
@@ -170,10 +169,10 @@ __global__ void q8_dequant_rows(const void* w, const __half* s, size_t K, int kc
     if (i >= n) return;
     const size_t r = row0 + i / K, c = i % K;
     if (kc) {
-        const size_t R = kUnitQ / kc, nch = K / kc;
-        const size_t u = (r / R) * nch + c / kc, rr = r % R, kk = c % kc;
-        const unsigned char* ub = (const unsigned char*)w + u * kUnitBytes;
-        out[i] = __fmul_rn((float)((const int8_t*)ub)[rr * kc + kk], __half2float(((const __half*)(ub + kUnitQ))[rr * (kc / 32) + kk / 32]));
+        const size_t T = (r / kTileRows) * (K / kTileK) + c / kTileK, ck = c % kTileK, j = ck & 31;
+        const unsigned char* tb = (const unsigned char*)w + T * kTileBytes;
+        const int8_t qv = ((const int8_t*)tb)[((ck >> 5) << 8) + ((j >> 4) << 7) + ((r & 7) << 4) + (j & 15)];
+        out[i] = __fmul_rn((float)qv, __half2float(*(const __half*)((const unsigned char*)w + packed_scale_off(r, c, K))));
     } else {
         out[i] = __fmul_rn((float)((const int8_t*)w)[r * K + c], __half2float(s[(r * K + c) >> 5]));
     }

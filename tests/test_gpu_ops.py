@@ -141,16 +141,26 @@ KAT = [
     (64, 4096, "random", 0),
     (64, 4096, "random", 1),
     (64, 4096, "random", 2),
-    (148 * 4 + 12, 4096, "random", 0),   # rows not a multiple of (CTAs x tile)
-    (24, 14336, "random", 0),      # down-projection K: seven 2048-wide chunks per row
+    (148 * 4 + 12, 4096, "random", 0),   # rows not a multiple of 8: planes + plain-load kernel
+    (148 * 4 + 16, 4096, "random", 0),   # row groups not a multiple of the CTA count
+    (24, 14336, "random", 0),      # down-projection K: 28 tiles per row group = fills of 8, 8, 8, 4
     (24, 14336, "random", 1),
     (24, 14336, "random", 2),
-    (64, 512, "random", 0),        # KC = 512: 32 rows per stage-unit, half-warp rows
-    (48, 1024, "random", 0),
-    (40, 1024, "random", 0),       # rows not a multiple of the unit: planes + plain-load kernel
-    (64, 2560, "random", 0),       # K = 5 x 512
+    (8, 512, "integers", 0),       # one tile
+    (64, 512, "random", 0),        # one tile per row group: a fill carries 8 row groups
+    (72, 512, "random", 0),        # ... and the last fill only one
+    (48, 1024, "random", 0),       # two tiles per row group: fills of 4 row groups, then 2
+    (40, 1024, "random", 2),
+    (44, 1024, "random", 0),       # rows not a multiple of 8: planes + plain-load kernel
+    (64, 1536, "random", 0),       # three tiles per row group: a fill = 2 row groups = 6 tiles split 4 + 2 between the warpgroups
+    (64, 2048, "random", 0),       # four tiles per row group: each warpgroup drains a whole row group
+    (64, 2560, "random", 0),       # K = 5 x 512: one fill of 5 tiles
+    (32, 3584, "random", 0),       # 7 tiles
+    (32, 6144, "random", 0),       # 12 tiles: fills of 8 and 4
+    (16, 16384, "random", 0),      # longest K: 32 tiles
     (7, 96, "random", 0),          # K below any tile: direct kernel
-    (6152, 4096, "random", 0),     # q,k,v-sized: more units than CTAs, uneven split
+    (6152, 4096, "random", 0),     # q,k,v-sized: more row groups than CTAs, uneven split
+    (76800, 512, "random", 0),     # 9600 row groups: more per CTA than one epilogue chunk (64) holds
 ]
 
 
@@ -255,5 +265,5 @@ def test_bad_arguments_return_errors(lib):
     assert lib.lum_op_gemv_q8_0(None, None, 4, 32, None, None, 0, None) < 0
     assert b"bad arguments" in lib.lum_last_error(None)
     assert lib.lum_op_q8_0_dequant(None, None, 31, None, None) < 0
-    assert lib.lum_q8_0_packed_bytes(40, 1024) == 0 and lib.lum_q8_0_packed_bytes(48, 1024) == 48 * 1024 * 34 // 32
+    assert lib.lum_q8_0_packed_bytes(44, 1024) == 0 and lib.lum_q8_0_packed_bytes(48, 1024) == 48 * 1024 * 34 // 32
     assert lib.lum_q8_0_packed_bytes(8, 96) == 0
