@@ -23,13 +23,18 @@ namespace lum {
 template <int HD, int GM, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char attn_smem[];
-    if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
+    if (a.use_pdl) pdl_launch_dependents();
+    // The position was settled by the previous step's sampler, several kernels back in stream order (the step's first
+    // kernel waits for that step in full), so the rotation table can be worked out while the projections still run.
     const int p = a.state->pos;
-    if (p < 0 || p >= a.max_seq) {
+    const bool ok = p >= 0 && p < a.max_seq;
+    if (ok) attn_fill_rope<HD>(a, attn_smem, p, (int)threadIdx.x);
+    if (a.use_pdl) pdl_grid_wait();
+    if (!ok) {
         if (threadIdx.x == 0) atomicOr(a.status, LUM_ST_BAD_POS);
         return;
     }
-    attn_decode_body<HD, GM, BF16>(a, attn_smem, (int)blockIdx.x, (int)blockIdx.y, p, (int)threadIdx.x, 2);
+    attn_decode_body<HD, GM, BF16>(a, attn_smem, (int)blockIdx.x, (int)blockIdx.y, p, (int)threadIdx.x, 2, true);
 }
 
 template <int HD, int GM>
@@ -38,7 +43,7 @@ static const void* attn_fn(bool bf16) { return bf16 ? (const void*)attn_decode<H
 cudaError_t launch_attn_decode(const AttnArgs& a_in, cudaStream_t st) {
     AttnArgs a = a_in;
     const int G = a.n_q / a.n_kv;
-    if (a.n_kv <= 0 || G < 1 || G > 8 || a.n_q != G * a.n_kv || a.n_splits < 1) return cudaErrorInvalidValue;
+    if (a.n_kv <= 0 || G < 1 || G > 8 || a.n_q != G * a.n_kv || a.n_splits < 1 || a.n_splits > kMaxSplits) return cudaErrorInvalidValue;
     const void* fn = nullptr;
     if (a.hd == 128) fn = G <= 4 ? attn_fn<128, 4>(a.kv_bf16 != 0) : attn_fn<128, 8>(a.kv_bf16 != 0);
     else if (a.hd == 64) fn = G <= 4 ? attn_fn<64, 4>(a.kv_bf16 != 0) : attn_fn<64, 8>(a.kv_bf16 != 0);

@@ -63,8 +63,22 @@ constexpr int kAttnThreads = 512;
 constexpr int kAttnWarps = kAttnThreads / 32;
 
 // bytes of shared memory the body needs for G query heads per KV head
+constexpr int kMaxSplits = 32;
 __host__ __device__ inline size_t attn_smem_bytes(int HD, int G) {
-    return (size_t)(9 * HD + HD + 2 * kAttnWarps * 8 + 4) * 4 + (size_t)kAttnWarps * G * HD * 4;
+    return (size_t)(9 * HD + HD + 2 * kAttnWarps * 8 + 4 + HD) * 4 + (size_t)kAttnWarps * G * HD * 4;
+}
+// where the rotation table (cos, sin per dimension pair) lives in the attention scratch
+__device__ __forceinline__ float* attn_rope_table(unsigned char* smem, int HD) { return (float*)smem + 9 * HD + HD + 2 * kAttnWarps * 8 + 4; }
+// The table depends only on the position: a kernel can fill it while it still waits for the projections (threads 0 .. HD/2-1).
+template <int HD>
+__device__ __forceinline__ void attn_fill_rope(const AttnArgs& a, unsigned char* smem, int p, int tid) {
+    float* tab = attn_rope_table(smem, HD);
+    if (tid < HD / 2) {
+        float cs, sn;
+        rope_cs(a, tid, p, &cs, &sn);
+        tab[2 * tid] = cs;
+        tab[2 * tid + 1] = sn;
+    }
 }
 
 template <bool BF16, int DPL>
@@ -93,7 +107,8 @@ __device__ __forceinline__ void load_dpl(const void* base, size_t elem_off, floa
 // p = position of the token being processed (rows [.., p) are cached, row p is this step's own).
 // smem: attn_smem_bytes(HD, G) bytes, 16-byte aligned.
 template <int HD, int GM, bool BF16>
-__device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned char* smem, int kvh, int split, int p, int tid, int bar_id) {
+__device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned char* smem, int kvh, int split, int p, int tid, int bar_id,
+                                                 bool rope_ready = false) {
     constexpr int DPL = HD / 32;            // dims per lane
     constexpr int NW = kAttnWarps;
     const int warp = tid >> 5, lane = tid & 31;
@@ -104,7 +119,8 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
     float (*s_m)[8] = (float (*)[8])(s_v + HD);             // [NW][8]
     float (*s_l)[8] = (float (*)[8])(s_v + HD + NW * 8);    // [NW][8]
     int& s_last = *(int*)(s_v + HD + 2 * NW * 8);
-    float* s_o = s_v + HD + 2 * NW * 8 + 4;                 // [NW][G][HD]
+    float* s_rope = s_v + HD + 2 * NW * 8 + 4;              // [HD/2][2]: cos, sin
+    float* s_o = s_rope + HD;                               // [NW][G][HD]
     const int d0 = lane * DPL;
     const size_t row_elems = (size_t)a.n_kv * HD;
 
@@ -127,6 +143,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
     }
     if (owns_new)
         for (int e = tid; e < HD; e += kAttnThreads) s_v[e] = a.v_new[(size_t)kvh * HD + e];
+    if (!rope_ready) attn_fill_rope<HD>(a, smem, p, tid);
     sync();
     if (a.q_gain || a.k_gain) {
         // per-head RMSNorm: x * 1/sqrt(mean(x^2) + eps) * g   (one warp per head)
@@ -145,8 +162,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
 #pragma unroll 1
     for (int idx = tid; idx < nheads * (HD / 2); idx += kAttnThreads) {
         const int h = idx / (HD / 2), i = idx - h * (HD / 2);
-        float cs, sn;
-        rope_cs(a, i, p, &cs, &sn);
+        const float cs = s_rope[2 * i], sn = s_rope[2 * i + 1];
         const int e0 = a.rope_style == 0 ? 2 * i : i, e1 = a.rope_style == 0 ? 2 * i + 1 : i + HD / 2;
         const float x0 = s_q[h][e0], x1 = s_q[h][e1];
         // separately rounded products and sums, as the graph's Mul / Add nodes produce them

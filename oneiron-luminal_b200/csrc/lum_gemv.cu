@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     GemvSmem g;
     gemv_carve(smem, a.K, a.stages, &s_abort, &g);
     if (tid == 0) GPROBE(0);
+    if (tid == 0 && blockIdx.x == 0 && a.job_ctr_zero) *a.job_ctr_zero = 0u;
     const uint32_t tmem = gemv_cta_begin(g, tid, &s_abort);
     if (a.use_pdl) pdl_launch_dependents();
     const GemvPlan plan = gemv_plan(a, (int)gridDim.x, a.job_ctr != nullptr);
@@ -136,12 +137,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
         gemv_mma_end(g, tmem, lane, a.status);
         return;
     }
+    GainRegs gr;
+    gemv_gain_preload(a, tid, gr);             // independent of the previous kernel: fetched while waiting for it
     if (a.use_pdl) pdl_grid_wait();
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
     ArgBest best{-INFINITY, -1};
     ConsumerRing cr{0, 0u, 0u, 0u, 0};
-    gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best);
+    gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
     if (tid >= kConsumers) return;
     gemv_consumers_done();
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
@@ -149,6 +152,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
 }
 #ifdef LUM_PROBE
 extern "C" int lum_probe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_probe, sizeof(g_probe)); }
+extern "C" int lum_gpprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_pprobe, sizeof(g_pprobe)); }
 extern "C" int lum_tl_read(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl)); }
 #endif
 
@@ -221,6 +225,7 @@ __global__ void __launch_bounds__(256) gemv_direct(const GemvArgs a) {
     float* xs = scratch + 64;                  // K floats (K rounded up to 4)
     float* vals = xs + ((a.K + 3) & ~3);       // 2 * max rows per CTA
 
+    if (tid == 0 && blockIdx.x == 0 && a.job_ctr_zero) *a.job_ctr_zero = 0u;   // this kernel claims nothing, but keeps the rotation going
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
     gemv_load_x(a, xs, tid, 256, scratch, 1);
 

@@ -39,7 +39,10 @@ namespace lum {
 #ifdef LUM_PROBE
 // Build-time probe (never in the shipped library): %globaltimer stamps of a few points in CTA 0 (one copy per translation unit).
 static __device__ unsigned long long g_probe[32];
-#define GPROBE(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || (i) == 5)) g_probe[i] = globaltimer_ns(); } while (0)
+static __device__ unsigned long long g_pprobe[64 * 8];   // per phase (in call order, wrapping): stamps 1..4 of thread 0
+static __device__ int g_pphase;
+#define GPROBE(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || (i) == 5)) { g_probe[i] = globaltimer_ns(); \
+    if (threadIdx.x == 0) { if ((i) == 1) g_pphase++; g_pprobe[(g_pphase & 63) * 8 + (i)] = g_probe[i]; } } } while (0)
 // per-fill timeline of CTA 0 (SM clock): [fill][event]
 static __device__ long long g_tl[64][16];   // one copy per translation unit
 #ifndef LUM_TL_FIRST
@@ -269,13 +272,28 @@ struct XSource {
     int token;
 };
 
+// The RMSNorm gains do not depend on the previous operation, so a kernel can fetch them while it still waits for its
+// grid dependency: thread tid keeps the gains of the elements it will quantise (trip it: float4 number it * kWorkers + tid).
+constexpr int kXTrips = 8;                  // K <= 16384: at most 8 float4 per worker thread
+struct GainRegs { uint2 b[kXTrips]; bool loaded; };
+__device__ __forceinline__ void gemv_gain_preload(const GemvArgs& a, int tid, GainRegs& gr) {
+    gr.loaded = a.gain != nullptr && a.gain_kind == WK_BF16;
+    if (!gr.loaded) return;
+    const int n4 = a.K >> 2;
+#pragma unroll
+    for (int it = 0; it < kXTrips; it++) {
+        const int f4 = it * kWorkers + tid;
+        gr.b[it] = f4 < n4 ? ((const uint2*)a.gain)[f4] : make_uint2(0u, 0u);
+    }
+}
+
 // Prologue: activations (optionally RMS-normalised, times the gains) -> three int8 levels + one f32 scale per 32-block
 // (x ~= s * (a1 + a2/254 + a3/254^2)), written as the B operand of the tensor-core instruction: operand row 3 * block + level
 // holds that level's 32 bytes, rows grouped by 8 into core matrices (two per group: bytes 0-15 and 16-31 of each row).
-// Runs on all kWorkers threads; 8 consecutive threads own one block.  Loops stay rolled: this code runs once per CTA per
-// phase, so its size in instruction-cache lines is latency.  Ends with the writes published to the tensor core (xready)
-// and to the other workers (named barrier 1).
-__device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvSmem& g, int tid) {
+// Runs on all kWorkers threads; 8 consecutive threads own one block.  Every thread first issues all of its loads (the
+// vector sits in L2, a microsecond away: one round trip, not one per trip), keeps them in registers for both passes, and
+// ends with the writes published to the tensor core (xready) and to the other workers (named barrier 1).
+__device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvSmem& g, int tid, const GainRegs& gr) {
     const int K = a.K, n4 = K >> 2;
     auto load4 = [&](int f4) -> float4 {
         float4 t;
@@ -288,70 +306,92 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         } else {
             t = ((const float4*)((const float*)xs.table + (size_t)xs.token * K))[f4];
         }
-        if (xs.x_add) { const float4 u = ((const float4*)xs.x_add)[f4]; t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
         return t;
     };
+    float4 xv[kXTrips];
+#pragma unroll
+    for (int it = 0; it < kXTrips; it++) {
+        const int f4 = it * kWorkers + tid;
+        xv[it] = f4 < n4 ? load4(f4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (xs.x_add) {
+#pragma unroll
+        for (int it = 0; it < kXTrips; it++) {
+            const int f4 = it * kWorkers + tid;
+            if (f4 < n4) { const float4 u = ((const float4*)xs.x_add)[f4]; xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+        }
+    }
+    if (xs.x_out && is_writer) {
+#pragma unroll
+        for (int it = 0; it < kXTrips; it++) {
+            const int f4 = it * kWorkers + tid;
+            if (f4 < n4) ((float4*)xs.x_out)[f4] = xv[it];
+        }
+    }
     float inv = 1.0f;
     if (a.gain) {
         float ss = 0.0f;
-#pragma unroll 4
-        for (int f4 = tid; f4 < n4; f4 += kWorkers) {
-            const float4 t = load4(f4);
+#pragma unroll
+        for (int it = 0; it < kXTrips; it++) {      // absent trips hold zeros
+            const float4 t = xv[it];
             ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
         }
         ss = block_sum(ss, g.scratch, tid, kWorkers, 1);
         const float mean = ss * (1.0f / (float)K);
         inv = 1.0f / sqrtf(mean + a.eps);
     }
-    // second pass re-reads x (an L1/L2 hit); all threads run the same trip count so the 8-lane shuffles
-    // always have their partners (K is a multiple of 32: a block never straddles the end)
+    // all threads run every trip so the 8-lane shuffles always have their partners (K is a multiple of 32: a block never
+    // straddles the end); trips past the end of the vector are skipped as a whole warp
     const int trips = (n4 + kWorkers - 1) / kWorkers;
-#pragma unroll 1
-    for (int it = 0; it < trips; it++) {
-        const int f4 = it * kWorkers + tid;
-        const bool in = f4 < n4;
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (in) {
-            t = load4(f4);
-            if (xs.x_out && is_writer) ((float4*)xs.x_out)[f4] = t;
-        }
-        float e[4] = {t.x, t.y, t.z, t.w};
-        if (a.gain && in) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) e[j] = (inv * e[j]) * load_gain(a.gain, a.gain_kind, f4 * 4 + j);
-        }
-        float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const float s1 = amax * (1.0f / 127.0f);
-        const float i1 = amax > 0.0f ? 127.0f / amax : 0.0f;
-        const float s2 = s1 * (1.0f / 254.0f), i2 = i1 * 254.0f;
-        const float i3 = i1 * 64516.0f;
-        // Round to nearest by adding 1.5 * 2^23: the sum's low mantissa bits are the integer in two's complement,
-        // so its low byte is the int8 value — no float->int conversion or rint (both quarter-rate instructions).
-        // |e * i1| <= 127 and every residual is at most half a step of the level before, so no clamping is needed.
-        constexpr float kMagic = 12582912.0f;
-        uint32_t p1 = 0, p2 = 0, p3 = 0;
+    for (int it = 0; it < kXTrips; it++) {
+        if (it < trips) {
+            const int f4 = it * kWorkers + tid;
+            const bool in = f4 < n4;
+            float e[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
+            if (a.gain && in) {
+                if (gr.loaded) {
+                    const uint2 gb = gr.b[it];
+                    e[0] = (inv * e[0]) * __uint_as_float(gb.x << 16); e[1] = (inv * e[1]) * __uint_as_float(gb.x & 0xffff0000u);
+                    e[2] = (inv * e[2]) * __uint_as_float(gb.y << 16); e[3] = (inv * e[3]) * __uint_as_float(gb.y & 0xffff0000u);
+                } else {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float t1 = fmaf(e[j], i1, kMagic);
-            const float r1 = fmaf(-s1, t1 - kMagic, e[j]);
-            const float t2 = fmaf(r1, i2, kMagic);
-            const float r2 = fmaf(-s2, t2 - kMagic, r1);
-            const float t3 = fmaf(r2, i3, kMagic);
-            p1 |= (__float_as_uint(t1) & 0xffu) << (8 * j);
-            p2 |= (__float_as_uint(t2) & 0xffu) << (8 * j);
-            p3 |= (__float_as_uint(t3) & 0xffu) << (8 * j);
-        }
-        if (in) {
-            const int blk = f4 >> 3, j0 = (f4 & 7) << 2;                 // this thread's 4 bytes: columns j0..j0+3 of block blk
-            const int inner = ((j0 >> 4) << 7) + (j0 & 15);
-            const int n1 = 3 * blk, n2 = n1 + 1, n3 = n1 + 2;              // operand rows of the three levels
-            *(uint32_t*)(g.xq + ((n1 >> 3) << 8) + ((n1 & 7) << 4) + inner) = p1;
-            *(uint32_t*)(g.xq + ((n2 >> 3) << 8) + ((n2 & 7) << 4) + inner) = p2;
-            *(uint32_t*)(g.xq + ((n3 >> 3) << 8) + ((n3 & 7) << 4) + inner) = p3;
-            if ((tid & 7) == 0) g.xsc[blk] = s1;
+                    for (int j = 0; j < 4; j++) e[j] = (inv * e[j]) * load_gain(a.gain, a.gain_kind, f4 * 4 + j);
+                }
+            }
+            float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float s1 = amax * (1.0f / 127.0f);
+            const float i1 = amax > 0.0f ? 127.0f / amax : 0.0f;
+            const float s2 = s1 * (1.0f / 254.0f), i2 = i1 * 254.0f;
+            const float i3 = i1 * 64516.0f;
+            // Round to nearest by adding 1.5 * 2^23: the sum's low mantissa bits are the integer in two's complement,
+            // so its low byte is the int8 value — no float->int conversion or rint (both quarter-rate instructions).
+            // |e * i1| <= 127 and every residual is at most half a step of the level before, so no clamping is needed.
+            constexpr float kMagic = 12582912.0f;
+            uint32_t p1 = 0, p2 = 0, p3 = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float t1 = fmaf(e[j], i1, kMagic);
+                const float r1 = fmaf(-s1, t1 - kMagic, e[j]);
+                const float t2 = fmaf(r1, i2, kMagic);
+                const float r2 = fmaf(-s2, t2 - kMagic, r1);
+                const float t3 = fmaf(r2, i3, kMagic);
+                p1 |= (__float_as_uint(t1) & 0xffu) << (8 * j);
+                p2 |= (__float_as_uint(t2) & 0xffu) << (8 * j);
+                p3 |= (__float_as_uint(t3) & 0xffu) << (8 * j);
+            }
+            if (in) {
+                const int blk = f4 >> 3, j0 = (f4 & 7) << 2;                 // this thread's 4 bytes: columns j0..j0+3 of block blk
+                const int inner = ((j0 >> 4) << 7) + (j0 & 15);
+                const int n1 = 3 * blk, n2 = n1 + 1, n3 = n1 + 2;              // operand rows of the three levels
+                *(uint32_t*)(g.xq + ((n1 >> 3) << 8) + ((n1 & 7) << 4) + inner) = p1;
+                *(uint32_t*)(g.xq + ((n2 >> 3) << 8) + ((n2 & 7) << 4) + inner) = p2;
+                *(uint32_t*)(g.xq + ((n3 >> 3) << 8) + ((n3 & 7) << 4) + inner) = p3;
+                if ((tid & 7) == 0) g.xsc[blk] = s1;
+            }
         }
     }
     fence_proxy_async_smem();
@@ -577,9 +617,9 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
 // of a warp that share a row are folded with two shuffles and the 8 warps' partials are summed in a fixed order at the
 // end of a chunk, followed by the epilogue.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
 __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvPlan& p, const GemvSmem& g,
-                                             ConsumerRing& cr, int tid, uint32_t tmem, uint32_t* status, ArgBest* best) {
+                                             ConsumerRing& cr, int tid, uint32_t tmem, uint32_t* status, ArgBest* best, const GainRegs& gr) {
     GPROBE(1);
-    gemv_quantize_x(a, xs, is_writer, g, tid);
+    gemv_quantize_x(a, xs, is_writer, g, tid, gr);
     GPROBE(2);
     if (tid >= kConsumers) return;
     const int lane = tid & 31, warp = tid >> 5, wg = warp >> 2, q = warp & 3;
@@ -721,6 +761,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
         if (slot > 0) gemv_epilogue_units(a, g.vals, g.unit_of, g.pair_of, slot, tid, kConsumers, g.scratch, 2, best);
         named_sync(2, kConsumers);
     }
+    GPROBE(7);
     // (The END marker reaches the draining warps through the tensor-core warp, so they cannot finish a phase before it has:
     // the "activations quantised" barrier of the next phase never runs more than one phase ahead of its waiter.)
 }

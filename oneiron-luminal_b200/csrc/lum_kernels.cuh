@@ -67,6 +67,7 @@ struct GemvArgs {
     int force_direct;      // 1: never take the streaming kernel (operator tests compare the two)
     int debug;             // tuning probes of the streaming kernel (0 in normal use)
     unsigned int* job_ctr; // streaming kernel: zeroed counter the producers claim pooled jobs from (null: static split)
+    unsigned int* job_ctr_zero;   // optional: a counter of a launch far enough away in stream order, zeroed by CTA 0 for its next use
 };
 
 struct AttnArgs {

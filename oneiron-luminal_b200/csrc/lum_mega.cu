@@ -34,6 +34,7 @@ __device__ unsigned long long g_arrive[64 * 160];
 extern "C" int lum_arrive_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_arrive, sizeof(g_arrive)); }
 #define MPROBE(i) do { if (blockIdx.x == 0 && tid == 0 && (i) < 1024) g_mprobe[i] = globaltimer_ns(); } while (0)
 extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_mprobe, sizeof(g_mprobe)); }
+extern "C" int lum_pprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_pprobe, sizeof(g_pprobe)); }
 extern "C" int lum_mtl_read(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl)); }
 #else
 #define MPROBE(i) do { } while (0)
@@ -209,7 +210,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
                 else xs.x = p == 2 ? a.attn : p == 4 ? a.h : a.x;
                 ArgBest best{-INFINITY, -1};
                 if (t == 1) MPROBE(ph * 3);
-                if (!s_abort) gemv_consume(ga, xs, cta == 0, plan, g, cring, tid, tmem, a.status, &best);
+                if (!s_abort) {
+                    GainRegs gr;
+                    gemv_gain_preload(ga, tid, gr);
+                    gemv_consume(ga, xs, cta == 0, plan, g, cring, tid, tmem, a.status, &best, gr);
+                }
                 if (t == 1) MPROBE(ph * 3 + 1);
                 if (p == 5 && tid == 0) { a.part_val[cta] = best.v; a.part_idx[cta] = best.i; }
                 grid_barrier(a, seq, &s_abort, tid);

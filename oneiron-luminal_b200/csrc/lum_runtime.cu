@@ -120,6 +120,7 @@ struct lum_rt {
     float* am_val = nullptr;
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
+    unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
     int n_splits = 1;
     float eps6 = 0.0f;
@@ -209,7 +210,7 @@ void free_model(lum_rt* rt) {
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
-    rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr;
+    rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr; rt->step_ctr = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
     rt->allocs.clear();
     rt->L.clear();
@@ -296,6 +297,16 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         n++;
         return 0;
     };
+    // Dynamic job claiming: projection number gi of the step claims from its own counter, and re-zeroes the counter of the
+    // projection half a step away in stream order — used (and quiescent) long before, next used long after — so that every
+    // counter is zero again when its projection comes round in the next step.  The two maps (with and without the
+    // vocabulary projection) are both bijections that zero a counter either before its use in the same step or after it.
+    const int n_proj = 4 * d.n_layers + (with_head ? 1 : 0);
+    int gi = 0;
+    auto claim_ctr = [&](GemvArgs& g) {
+        if (n_proj >= 8 && rt->step_ctr) { g.job_ctr = rt->step_ctr + gi; g.job_ctr_zero = rt->step_ctr + (gi + n_proj / 2) % n_proj; }
+        gi++;
+    };
     auto take_partial = [&](GemvArgs& g) {   // the projection's prologue folds the reduced partial into the stream
         g.x = cur;
         if (pending) { g.x_add = rt->part; g.x_out = other; float* t = cur; cur = other; other = t; pending = false; }
@@ -317,6 +328,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.seg[2] = {w.v.w, w.v.s, (int)w.v.rows, w.v.kc};
         a.K = H; a.epi = EPI_STORE; a.gain = w.attn_norm.w; a.y = rt->qkv;
         take_partial(a);
+        claim_ctr(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
 
         AttnArgs t{};
@@ -336,6 +348,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         o.K = (int)w.o.cols; o.x = rt->attn;
         if (tp) { o.epi = EPI_STORE; o.y = rt->part; }
         else { o.epi = EPI_RESID; o.y = cur; o.resid = cur; }
+        claim_ctr(o);
         CU(rt, launch_gemv(o, rt->sm_count, st)); n++;
         if (tp) { if (int r = all_reduce()) return r; pending = true; }
 
@@ -345,6 +358,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows, w.gate.kc}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows, w.up.kc};
         g.K = H; g.epi = EPI_SWIGLU; g.gain = w.mlp_norm.w; g.y = rt->h;
         take_partial(g);
+        claim_ctr(g);
         CU(rt, launch_gemv(g, rt->sm_count, st)); n++;
 
         // down projection (+ residual)
@@ -354,6 +368,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         dn.K = (int)w.down.cols; dn.x = rt->h;
         if (tp) { dn.epi = EPI_STORE; dn.y = rt->part; }
         else { dn.epi = EPI_RESID; dn.y = cur; dn.resid = cur; }
+        claim_ctr(dn);
         CU(rt, launch_gemv(dn, rt->sm_count, st)); n++;
         if (tp) { if (int r = all_reduce()) return r; pending = true; }
     }
@@ -367,6 +382,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.advance = 1;
         take_partial(a);
         if (tp) { a.pair_out = rt->tp_pairs + 2 * rt->tp_size; a.row_offset = rt->tp_rank * rt->vocab_l; }
+        claim_ctr(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
         if (tp) {
             // every rank needs every shard's best row: all-gather the pairs, then fold them the same way everywhere
@@ -694,6 +710,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     }
     int splits = rt->cfg.attn_splits;
     if (splits <= 0) { splits = rt->sm_count / (rt->nkv_l > 0 ? rt->nkv_l : 1); if (splits < 1) splits = 1; if (splits > 32) splits = 32; }
+    if (splits > 32) splits = 32;       // the merge holds one partial per split in registers
     rt->n_splits = splits;
     const int G = d.n_q_heads / d.n_kv_heads;
     TRY(dev_alloc(rt, (void**)&rt->x, (size_t)H * 4));
@@ -711,6 +728,8 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     TRY(dev_alloc(rt, (void**)&rt->am_val, 1024 * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_idx, 1024 * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_cnt, 4));
+    TRY(dev_alloc(rt, (void**)&rt->step_ctr, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int)));
+    cudaMemsetAsync(rt->step_ctr, 0, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int), rt->stream);
     TRY(dev_alloc(rt, (void**)&rt->status, 4));
 #undef TRY
     cudaMemsetAsync(rt->attn_cnt, 0, (size_t)rt->nkv_l * 4, rt->stream);
