@@ -220,6 +220,10 @@ def run_ours(args, pkg):
         rt.tp_init(uid, world, rank)
         desc = desc.copy(tp_size=world, tp_rank=rank)
     rt.load_model(desc)
+    fused = world > 1 and os.environ.get("LUM_TP_FUSED", "1") != "0"
+    if fused:
+        # partial sums of the K-sharded projections travel through peer memory inside the projection kernels
+        rt.tp_peer_import(T.exchange_peer_handles(dist, world, rt.tp_peer_export(), device=torch.device("cuda", local)))
     rt.synth(SEED)
     # prompt: 512 seeded ids (same generator as the oracle's: tensor id 2^20, uniform over the vocabulary)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -294,7 +298,7 @@ def run_ours(args, pkg):
             "dtype": "f32 accumulate over Q8_0 (int8 x f16-scale) weights", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch": 1, "prompt_len": PROMPT_LEN, "tokens_per_step": TOKENS_PER_STEP,
                        "context_at_start": p_start, "l2": "weights 8.0 GB >> 126 MB L2; every token re-streams them",
-                       "parallelism": "single GPU" if world == 1 else f"tp{world}: heads/FFN/vocab sharded, NCCL all-reduce per projection",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world}: heads/FFN/vocab sharded, " + ("partial sums exchanged through peer memory inside the projection kernels" if fused else "NCCL all-reduce per projection"),
                        "seed": SEED},
             "roofline": roof,
             "step_roofline": {"bound": "hbm", "what": "whole decode step, all kernels; bytes are the whole model's, peak is per GPU x n_gpus",

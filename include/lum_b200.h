@@ -175,6 +175,13 @@ void* lum_stream(lum_rt* rt);
  */
 int32_t lum_tp_unique_id(uint8_t* out128);
 int32_t lum_tp_init(lum_rt* rt, const uint8_t* id128, int32_t tp_size, int32_t tp_rank);
+/* Optional, after lum_model_init on every rank: exchange the K-sharded projections' partial sums through peer memory
+ * instead of NCCL all-reduce kernels.  Each rank exports a 64-byte CUDA IPC handle of its exchange buffer; the host
+ * gathers the handles of all ranks (rank order) and gives every rank the full list.  From then on the projection kernels
+ * store their partial rows into every rank's buffer over NVLink and the next projection's prologue adds them up — no
+ * collective kernel between them.  (No reference counterpart: the reference is single-GPU.) */
+int32_t lum_tp_peer_export(lum_rt* rt, uint8_t* handle64);
+int32_t lum_tp_peer_import(lum_rt* rt, const uint8_t* handles, int32_t n_ranks);
 
 /* ---------------------------------------------------------------------------------------------
  * Stand-alone operators (one launch each; device pointers).  These are the block ops of

@@ -71,6 +71,7 @@ cudaError_t launch_attn_decode(const AttnArgs& a_in, cudaStream_t st) {
 // `RowEmbed` (crates/luminal_cuda/src/block/ops.rs:1921-1944): x = table[token, :], widened to f32.
 __global__ void __launch_bounds__(256) embed_row(const EmbedArgs a) {
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
+    if (a.seq_inc && blockIdx.x == 0 && threadIdx.x == 0) *a.seq_inc += 1u;     // every kernel after this one sees the new value
     const int tok = a.state->tok;
     if (tok < 0 || tok >= a.state->vocab) {
         if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(a.status, LUM_ST_BAD_TOKEN);

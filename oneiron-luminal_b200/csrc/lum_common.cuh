@@ -21,6 +21,7 @@ enum : uint32_t {
     LUM_ST_BAD_POS = 1u << 4,     // position outside the cache capacity
     LUM_ST_WAIT_GRID = 1u << 5,   // a grid-wide barrier of the persistent kernel was not reached by every CTA in time
     LUM_ST_WAIT_TMEM = 1u << 6,   // a wait on the tensor-core hand-over (accumulators ready / drained) ran out of budget
+    LUM_ST_WAIT_PEER = 1u << 7,   // tensor parallel: another rank's partial vector did not arrive in time
 };
 
 // Budget for any single wait, in SM clock cycles (about two seconds at 2 GHz).  The SM-local cycle
@@ -158,6 +159,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // generic-proxy writes to shared memory (st.shared) -> visible to the async proxy (tensor core operand reads)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- words shared with other GPUs (peer memory over NVLink) ------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until *p has reached `want` (words only ever grow); false when the budget ran out.
+__device__ __forceinline__ bool wait_word_sys(const uint32_t* p, uint32_t want) {
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+        if (clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) return false;
+    }
+}
 
 // ---- programmatic dependent launch ------------------------------------------------------------
 // launch_dependents: the next kernel in the stream may start its prologue (weight prefetch) now.

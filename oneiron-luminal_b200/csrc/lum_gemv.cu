@@ -77,22 +77,22 @@ __device__ __forceinline__ void argmax_finish(const GemvArgs& a, ArgBest mine, i
 // scaled by the gains).
 __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, int tid, int nthreads, float* scratch, int bar_id) {
     const int K = a.K;
-    float inv = 1.0f;
-    if (a.gain) {
-        float ss = 0.0f;
-        for (int k = tid; k < K; k += nthreads) { const float v = a.x_add ? a.x[k] + a.x_add[k] : a.x[k]; ss = fmaf(v, v, ss); }
-        ss = block_sum(ss, scratch, tid, nthreads, bar_id);
-        const float mean = ss * (1.0f / (float)K);
-        inv = 1.0f / sqrtf(mean + a.eps);
-    }
+    if (a.n_parts > 0) peer_wait_parts(a.part_flags, a.n_parts, a.seq, a.parts_tag, a.status, tid, nthreads, bar_id);
+    // the raw activations first (x, plus a reduced partial or the ranks' partials in rank order), then the norm over them
+    float ss = 0.0f;
     for (int k = tid; k < K; k += nthreads) {
         float v = a.x[k];
-        if (a.x_add) {
-            v += a.x_add[k];
-            if (a.x_out && blockIdx.x == 0) a.x_out[k] = v;
-        }
-        if (a.gain) v = (inv * v) * load_gain(a.gain, a.gain_kind, k);
+        if (a.x_add) v += a.x_add[k];
+        for (int r = 0; r < a.n_parts; r++) v += __ldcg(a.parts + (size_t)r * a.part_stride + k);
+        if ((a.x_add || a.n_parts > 0) && a.x_out && blockIdx.x == 0) a.x_out[k] = v;
         xs[k] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (a.gain) {
+        ss = block_sum(ss, scratch, tid, nthreads, bar_id);
+        const float mean = ss * (1.0f / (float)K);
+        const float inv = 1.0f / sqrtf(mean + a.eps);
+        for (int k = tid; k < K; k += nthreads) xs[k] = (inv * xs[k]) * load_gain(a.gain, a.gain_kind, k);
     }
     named_sync(bar_id, nthreads);
 }
@@ -142,11 +142,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     if (a.use_pdl) pdl_grid_wait();
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
+    xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq;
     ArgBest best{-INFINITY, -1};
     ConsumerRing cr{0, 0u, 0u, 0u, 0};
     gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
     if (tid >= kConsumers) return;
     gemv_consumers_done();
+    if (a.epi == EPI_PEER) peer_publish(a, tid, kConsumers, 2);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
     GPROBE(4);
 }
@@ -242,6 +244,7 @@ __global__ void __launch_bounds__(256) gemv_direct(const GemvArgs a) {
     ArgBest best{-INFINITY, -1};
     gemv_epilogue_rows(a, vals, row0, n, tid, 256, scratch, 1, &best);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, 256, 1);
+    if (a.epi == EPI_PEER) peer_publish(a, tid, 256, 1);
 }
 
 // ------------------------------------------------------------------------------ host side

@@ -189,6 +189,14 @@ __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const flo
         for (int i = tid; i < n; i += nthreads) a.y[unit_of[i >> 3] * kTileRows + (i & 7)] = vals[i];
     } else if (a.epi == EPI_RESID) {
         for (int i = tid; i < n; i += nthreads) { const int row = unit_of[i >> 3] * kTileRows + (i & 7); a.y[row] = a.resid[row] + vals[i]; }
+    } else if (a.epi == EPI_PEER) {
+        for (int i = tid; i < n; i += nthreads) {
+            const int row = unit_of[i >> 3] * kTileRows + (i & 7);
+            const float v = vals[i];
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; r++)
+                if (r < a.n_peers) a.peer_out[r][row] = v;
+        }
     } else {  // EPI_ARGMAX
         ArgBest b{-INFINITY, -1};
         for (int i = tid; i < n; i += nthreads) {
@@ -224,6 +232,13 @@ __device__ __forceinline__ void gemv_epilogue_rows(const GemvArgs& a, const floa
         for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = a.resid[row0 + i] + vals[i];
     } else if (a.epi == EPI_SWIGLU) {
         for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = swiglu(vals[i], vals[n + i]);
+    } else if (a.epi == EPI_PEER) {
+        for (int i = tid; i < n; i += nthreads) {
+            const float v = vals[i];
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; r++)
+                if (r < a.n_peers) a.peer_out[r][row0 + i] = v;
+        }
     } else {  // EPI_ARGMAX
         ArgBest b{-INFINITY, -1};
         for (int i = tid; i < n; i += nthreads) {
@@ -262,6 +277,32 @@ __device__ __forceinline__ ArgBest argmax_final(const float* part_val, const int
     return f;
 }
 
+// Tensor parallel, producing side: called by all `nthreads` threads of every CTA after the kernel's last row has been
+// stored into the ranks' buffers.  The last CTA to arrive tells every rank that this rank's partial vector is complete.
+__device__ __forceinline__ void peer_publish(const GemvArgs& a, int tid, int nthreads, int bar_id) {
+    __threadfence_system();                 // this thread's stores to the other GPUs are ordered before the arrival below
+    named_sync(bar_id, nthreads);
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(a.peer_ticket, 1u);
+        if (t == gridDim.x - 1) {
+            *a.peer_ticket = 0u;
+            __threadfence_system();
+            const uint32_t word = peer_word(__ldcg(a.seq), a.peer_tag);
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; r++)
+                if (r < a.n_peers) st_release_sys(a.peer_flag[r], word);
+        }
+    }
+}
+// Consuming side: wait (bounded) until every rank's partial vector for this projection has landed in local memory.
+__device__ __forceinline__ void peer_wait_parts(const uint32_t* flags, int n_parts, const uint32_t* seq, uint32_t tag, uint32_t* status,
+                                                int tid, int nthreads, int bar_id) {
+    if (tid < n_parts) {
+        if (!wait_word_sys(flags + (size_t)tid * 32, peer_word(__ldcg(seq), tag))) atomicOr(status, LUM_ST_WAIT_PEER);
+    }
+    named_sync(bar_id, nthreads);
+}
+
 // Where a phase's activations come from.
 struct XSource {
     const float* x;        // f32 vector [K] (null when the row of an embedding table is used)
@@ -270,6 +311,12 @@ struct XSource {
     const void* table;     // embedding table [vocab, K] (f32 or bf16) when x == null
     int table_kind;
     int token;
+    // tensor parallel: partial vectors written by the ranks, added in rank order (see GemvArgs)
+    const float* parts;
+    const uint32_t* part_flags;
+    int n_parts, part_stride;
+    uint32_t parts_tag;
+    const uint32_t* seq;
 };
 
 // The RMSNorm gains do not depend on the previous operation, so a kernel can fetch them while it still waits for its
@@ -308,11 +355,24 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         return t;
     };
+    if (xs.n_parts > 0) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
     float4 xv[kXTrips];
 #pragma unroll
     for (int it = 0; it < kXTrips; it++) {
         const int f4 = it * kWorkers + tid;
         xv[it] = f4 < n4 ? load4(f4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (xs.n_parts > 0) {
+        // written by other GPUs into this GPU's memory: read around L1; rank order, so every rank forms the same sums
+#pragma unroll 1
+        for (int r = 0; r < xs.n_parts; r++) {
+            const float4* pr = (const float4*)(xs.parts + (size_t)r * xs.part_stride);
+#pragma unroll
+            for (int it = 0; it < kXTrips; it++) {
+                const int f4 = it * kWorkers + tid;
+                if (f4 < n4) { const float4 u = __ldcg(pr + f4); xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+            }
+        }
     }
     if (xs.x_add) {
 #pragma unroll

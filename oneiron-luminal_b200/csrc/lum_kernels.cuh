@@ -13,7 +13,11 @@ enum : int {
     EPI_RESID = 1,    // y[row] = resid[row] + acc          (residual add, RowAdd in the reference)
     EPI_SWIGLU = 2,   // y[row] = silu(acc_gate) * acc_up   (two segments walked in step)
     EPI_ARGMAX = 3,   // y[row] = acc, then greedy sample over all rows (last maximum wins)
+    EPI_PEER = 4,     // tensor parallel: acc is this rank's partial of row; stored into every rank's copy of this rank's partial vector
 };
+constexpr int kMaxPeers = 8;
+// word (seq, tag) a rank publishes when its partial vector of one projection is complete everywhere
+__host__ __device__ inline uint32_t peer_word(uint32_t seq, uint32_t tag) { return seq * 1024u + tag; }
 
 // Device-resident decode-loop state: one graph replay per token needs no host traffic.
 struct DecodeState {
@@ -68,6 +72,21 @@ struct GemvArgs {
     int debug;             // tuning probes of the streaming kernel (0 in normal use)
     unsigned int* job_ctr; // streaming kernel: zeroed counter the producers claim pooled jobs from (null: static split)
     unsigned int* job_ctr_zero;   // optional: a counter of a launch far enough away in stream order, zeroed by CTA 0 for its next use
+    // Tensor parallel without a collective kernel.  Producing side (EPI_PEER): peer_out[r] is rank r's buffer for THIS rank's
+    // partial vector (r == own rank included), peer_flag[r] the word in rank r's memory that says it is complete.
+    float* peer_out[kMaxPeers];
+    uint32_t* peer_flag[kMaxPeers];
+    int n_peers;
+    unsigned int* peer_ticket;    // local arrival counter of the producing kernel's CTAs, left at 0
+    const uint32_t* seq;          // device word advanced once per decode step (the same on every rank)
+    uint32_t peer_tag;            // which projection of the step this is
+    // Consuming side: the activations are x + parts[0] + ... + parts[n_parts-1] (vectors part_stride floats apart in local
+    // memory, written by the ranks), each usable once its flag word reads peer_word(*seq, parts_tag).
+    const float* parts;
+    const uint32_t* part_flags;   // n_parts words, 32 words (128 bytes) apart
+    int n_parts;
+    int part_stride;
+    uint32_t parts_tag;
 };
 
 struct AttnArgs {
@@ -96,6 +115,7 @@ struct AttnArgs {
 };
 
 struct EmbedArgs {
+    uint32_t* seq_inc;     // optional: step counter advanced by this kernel (first kernel of every decode step)
     const void* table;     // [vocab, H] f32 or bf16
     int kind;
     int H;

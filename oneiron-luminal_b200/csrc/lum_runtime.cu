@@ -141,6 +141,15 @@ struct lum_rt {
     float* x2 = nullptr;              // second residual buffer (the stream alternates between x and x2)
     float* part = nullptr;            // this rank's partial o / down projection, all-reduced in place
     int* tp_pairs = nullptr;          // [tp_size][2] sampling candidates after the all-gather; this rank's own pair at [tp_size]
+    // Exchange of partial sums through peer memory instead of all-reduce kernels.  `sym` is this rank's buffer:
+    // 4 KiB of flag words ([2 buffers][rank], 128 bytes apart), then [2 buffers][rank][hidden] floats; the other
+    // ranks map it through a CUDA IPC handle and write their partial vectors and "complete" words straight into it.
+    unsigned char* sym = nullptr;
+    size_t sym_bytes = 0;
+    unsigned char* peer_sym[kMaxPeers] = {nullptr};   // every rank's buffer as seen from this process ([tp_rank] == sym)
+    bool peers_open = false;
+    uint32_t* tp_seq = nullptr;       // device word: decode steps issued so far (the same on every rank)
+    unsigned int* peer_ticket = nullptr;
 
     // whole-token persistent kernel
     bool mega_ok = false;
@@ -206,7 +215,17 @@ int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_
     return 0;
 }
 
+void close_peers(lum_rt* rt) {
+    for (int r = 0; r < kMaxPeers; r++) {
+        if (rt->peer_sym[r] && r != rt->tp_rank) cudaIpcCloseMemHandle(rt->peer_sym[r]);
+        rt->peer_sym[r] = nullptr;
+    }
+    rt->peers_open = false;
+}
+
 void free_model(lum_rt* rt) {
+    close_peers(rt);
+    rt->sym = nullptr; rt->sym_bytes = 0; rt->tp_seq = nullptr; rt->peer_ticket = nullptr;
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
@@ -307,14 +326,38 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         if (n_proj >= 8 && rt->step_ctr) { g.job_ctr = rt->step_ctr + gi; g.job_ctr_zero = rt->step_ctr + (gi + n_proj / 2) % n_proj; }
         gi++;
     };
+    // Fused exchange (after lum_tp_peer_import): a K-sharded projection stores each finished row into every rank's buffer
+    // and publishes a word when the last CTA is done; the next projection's prologue waits for all ranks' words and adds
+    // the partial vectors in rank order.  Two buffers alternate (o projection: 0, down projection: 1): a rank can only
+    // overwrite buffer b after every rank has published the projection in between, which each does after reading b.
+    const bool fused = tp && rt->peers_open;
+    uint32_t pending_tag = 0;
+    int pending_buf = 0;
+    auto sym_flag = [&](unsigned char* base, int buf, int rank) { return (uint32_t*)(base + ((size_t)buf * kMaxPeers + rank) * 128); };
+    auto sym_part = [&](unsigned char* base, int buf, int rank) { return (float*)(base + 4096) + ((size_t)buf * rt->tp_size + rank) * H; };
+    auto publish_to_peers = [&](GemvArgs& g, int buf, uint32_t tag) {
+        g.epi = EPI_PEER; g.y = nullptr;
+        g.n_peers = rt->tp_size;
+        for (int r = 0; r < rt->tp_size; r++) { g.peer_out[r] = sym_part(rt->peer_sym[r], buf, rt->tp_rank); g.peer_flag[r] = sym_flag(rt->peer_sym[r], buf, rt->tp_rank); }
+        g.peer_ticket = rt->peer_ticket; g.seq = rt->tp_seq; g.peer_tag = tag;
+        pending = true; pending_tag = tag; pending_buf = buf;
+    };
     auto take_partial = [&](GemvArgs& g) {   // the projection's prologue folds the reduced partial into the stream
         g.x = cur;
-        if (pending) { g.x_add = rt->part; g.x_out = other; float* t = cur; cur = other; other = t; pending = false; }
+        if (!pending) return;
+        if (fused) {
+            g.parts = sym_part(rt->sym, pending_buf, 0); g.part_flags = sym_flag(rt->sym, pending_buf, 0);
+            g.n_parts = rt->tp_size; g.part_stride = H; g.parts_tag = pending_tag; g.seq = rt->tp_seq;
+        } else {
+            g.x_add = rt->part;
+        }
+        g.x_out = other; float* t = cur; cur = other; other = t; pending = false;
     };
 
     EmbedArgs e{};
     e.table = rt->embed.w; e.kind = rt->embed.kind; e.H = H; e.x = rt->x; e.state = rt->state; e.status = rt->status;
     e.use_pdl = 0;   // first kernel of the step: ordinary stream order behind the previous step
+    e.seq_inc = rt->tp_seq;
     CU(rt, launch_embed(e, st)); n++;
 
     for (int l = 0; l < d.n_layers; l++) {
@@ -346,11 +389,12 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         o.status = rt->status; o.use_pdl = pdl; o.wkind = w.o.kind;
         o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows, w.o.kc};
         o.K = (int)w.o.cols; o.x = rt->attn;
-        if (tp) { o.epi = EPI_STORE; o.y = rt->part; }
+        if (fused) publish_to_peers(o, 0, (uint32_t)(2 * l + 1));
+        else if (tp) { o.epi = EPI_STORE; o.y = rt->part; }
         else { o.epi = EPI_RESID; o.y = cur; o.resid = cur; }
         claim_ctr(o);
         CU(rt, launch_gemv(o, rt->sm_count, st)); n++;
-        if (tp) { if (int r = all_reduce()) return r; pending = true; }
+        if (tp && !fused) { if (int r = all_reduce()) return r; pending = true; }
 
         // RMSNorm + gate, up + SwiGLU
         GemvArgs g{};
@@ -366,11 +410,12 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         dn.status = rt->status; dn.use_pdl = pdl; dn.wkind = w.down.kind;
         dn.nseg = 1; dn.seg[0] = {w.down.w, w.down.s, (int)w.down.rows, w.down.kc};
         dn.K = (int)w.down.cols; dn.x = rt->h;
-        if (tp) { dn.epi = EPI_STORE; dn.y = rt->part; }
+        if (fused) publish_to_peers(dn, 1, (uint32_t)(2 * l + 2));
+        else if (tp) { dn.epi = EPI_STORE; dn.y = rt->part; }
         else { dn.epi = EPI_RESID; dn.y = cur; dn.resid = cur; }
         claim_ctr(dn);
         CU(rt, launch_gemv(dn, rt->sm_count, st)); n++;
-        if (tp) { if (int r = all_reduce()) return r; pending = true; }
+        if (tp && !fused) { if (int r = all_reduce()) return r; pending = true; }
     }
     if (with_head) {
         const Tensor& hw = d.tied_head ? rt->embed : rt->lm_head;
@@ -651,6 +696,40 @@ int32_t lum_tp_init(lum_rt* rt, const uint8_t* id128, int32_t tp_size, int32_t t
     return 0;
 }
 
+int32_t lum_tp_peer_export(lum_rt* rt, uint8_t* handle64) {
+    if (!rt || !handle64) return LUM_E_INVALID;
+    if (!rt->has_model || rt->tp_size < 2 || !rt->sym) return fail(rt, LUM_E_INVALID, "tp_peer_export: load a sharded model first");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaIpcGetMemHandle(&h, rt->sym));
+    memcpy(handle64, &h, 64);
+    return 0;
+}
+
+int32_t lum_tp_peer_import(lum_rt* rt, const uint8_t* handles, int32_t n) {
+    if (!rt || !handles) return LUM_E_INVALID;
+    if (!rt->has_model || rt->tp_size < 2 || !rt->sym) return fail(rt, LUM_E_INVALID, "tp_peer_import: load a sharded model first");
+    if (n != rt->tp_size) return fail(rt, LUM_E_INVALID, "tp_peer_import: %d handles for %d ranks", n, rt->tp_size);
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    close_peers(rt);
+    for (int r = 0; r < n; r++) {
+        if (r == rt->tp_rank) { rt->peer_sym[r] = rt->sym; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { close_peers(rt); return fail(rt, LUM_E_CUDA, "cudaIpcOpenMemHandle (rank %d): %s", r, cudaGetErrorString(e)); }
+        rt->peer_sym[r] = (unsigned char*)p;
+    }
+    rt->peers_open = true;
+    // graphs captured with the collective path are stale now
+    if (rt->g_full) { cudaGraphExecDestroy(rt->g_full); rt->g_full = nullptr; }
+    if (rt->g_body) { cudaGraphExecDestroy(rt->g_body); rt->g_body = nullptr; }
+    return 0;
+}
+
 int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (!rt || !dp) return LUM_E_INVALID;
     CU(rt, cudaSetDevice(rt->cfg.device));
@@ -717,6 +796,15 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     TRY(dev_alloc(rt, (void**)&rt->x2, (size_t)H * 4));
     TRY(dev_alloc(rt, (void**)&rt->part, (size_t)H * 4));
     TRY(dev_alloc(rt, (void**)&rt->tp_pairs, (size_t)(2 * tp + 2) * 4));
+    if (tp > 1) {
+        rt->sym_bytes = 4096 + (size_t)2 * tp * H * 4;
+        TRY(dev_alloc(rt, (void**)&rt->sym, rt->sym_bytes));
+        TRY(dev_alloc(rt, (void**)&rt->tp_seq, 4));
+        TRY(dev_alloc(rt, (void**)&rt->peer_ticket, 4));
+        cudaMemsetAsync(rt->sym, 0, rt->sym_bytes, rt->stream);
+        cudaMemsetAsync(rt->tp_seq, 0, 4, rt->stream);
+        cudaMemsetAsync(rt->peer_ticket, 0, 4, rt->stream);
+    }
     TRY(dev_alloc(rt, (void**)&rt->qkv, (qd_l + 2 * kvd_l) * 4));
     TRY(dev_alloc(rt, (void**)&rt->attn, qd_l * 4));
     TRY(dev_alloc(rt, (void**)&rt->h, (size_t)rt->ffn_l * 4));

@@ -152,6 +152,8 @@ def load_library() -> C.CDLL:
         "lum_stream": (vp, [vp]),
         "lum_tp_unique_id": (i32, [vp]),
         "lum_tp_init": (i32, [vp, vp, i32, i32]),
+        "lum_tp_peer_export": (i32, [vp, vp]),
+        "lum_tp_peer_import": (i32, [vp, vp, i32]),
         "lum_op_gemv_q8_0": (i32, [vp, vp, i32, i32, vp, vp, i32, vp]),
         "lum_q8_0_packed_bytes": (sz, [i32, i32]),
         "lum_op_q8_0_pack": (i32, [vp, vp, i32, i32, vp, vp]),
@@ -253,6 +255,18 @@ class B200Runtime:
     def tp_init(self, unique_id: bytes, tp_size: int, tp_rank: int) -> None:
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         self._ck(self._lib.lum_tp_init(self._h, buf, tp_size, tp_rank))
+
+    def tp_peer_export(self) -> bytes:
+        """This rank's 64-byte IPC handle of its partial-sum exchange buffer (after ``load_model``)."""
+        buf = (C.c_uint8 * 64)()
+        self._ck(self._lib.lum_tp_peer_export(self._h, buf))
+        return bytes(buf)
+
+    def tp_peer_import(self, handles: Sequence[bytes]) -> None:
+        """All ranks' handles in rank order: switches the K-sharded projections to the fused peer-memory exchange."""
+        raw = b"".join(handles)
+        buf = (C.c_uint8 * len(raw)).from_buffer_copy(raw)
+        self._ck(self._lib.lum_tp_peer_import(self._h, buf, len(handles)))
 
     def device_info(self):
         sm, mem, cc = C.c_int32(), C.c_uint64(), C.c_int32()

@@ -61,3 +61,12 @@ def exchange_unique_id(dist, rank: int, make_id: Callable[[], bytes], device=Non
         buf.copy_(torch.tensor(list(raw), dtype=torch.uint8))
     dist.broadcast(buf, src=0)
     return bytes(buf.cpu().tolist())
+
+
+def exchange_peer_handles(dist, world: int, handle: bytes, device=None):
+    """All-gather the ranks' 64-byte IPC handles (rank order) through `torch.distributed` (any backend)."""
+    import torch
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
+    out = [torch.zeros(64, dtype=torch.uint8, device=device) for _ in range(world)]
+    dist.all_gather(out, mine)
+    return [bytes(t.cpu().tolist()) for t in out]

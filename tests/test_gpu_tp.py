@@ -17,11 +17,13 @@ def _gpus():
     return torch.cuda.device_count()
 
 
+@pytest.mark.parametrize("fused", [1, 0])
 @pytest.mark.parametrize("world,cfg", [(2, "small_q8"), (2, "llama3_8b_q8_2layer"), (4, "llama3_8b_q8_2layer")])
-def test_tp_matches_single_gpu(world, cfg):
+def test_tp_matches_single_gpu(world, cfg, fused):
+    """fused = 1: partial sums through peer memory inside the projection kernels; 0: NCCL all-reduce between them."""
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", LUM_TP_FUSED=str(fused))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
                         "--master-addr", "127.0.0.1", "--master-port", "29633", os.path.join(ROOT, "tests", "tp_worker.py"),
                         cfg, "77", "20"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env, timeout=600)

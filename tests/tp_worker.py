@@ -26,6 +26,9 @@ def main():
     rt = pkg.B200Runtime.initialize(device=local)
     rt.tp_init(uid, world, rank)
     rt.load_model(desc.copy(tp_size=world, tp_rank=rank))
+    if os.environ.get("LUM_TP_FUSED", "1") != "0":
+        # exchange of partial sums through peer memory (no collective kernel between the projections)
+        rt.tp_peer_import(T.exchange_peer_handles(dist, world, rt.tp_peer_export(), device=torch.device("cuda", local)))
     rt.synth(seed)
     prompt = [(7 * i + 3) % desc.vocab for i in range(12)]
     toks = rt.generate(prompt, n_new)
