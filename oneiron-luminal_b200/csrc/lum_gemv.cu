@@ -6,14 +6,15 @@
 // Decode is bound by HBM bandwidth: every weight byte is read exactly once per token and nothing
 // else is large.  Two kernels:
 //
-//  * q8_gemv_stream — the hot path.  One CTA per SM.  A producer warp walks the CTA's share of the
-//    weight matrix in 16 KiB stage-units (R rows x KC columns of int8 plus their binary16 scales)
-//    and fetches each unit with bulk asynchronous copies (cp.async.bulk, completion counted on an
-//    mbarrier) into a ring of shared-memory stages; 8 consumer warps wait on the stage and
-//    accumulate integer dot products against the (int8-decomposed) activation vector held in shared memory.  The weight
-//    stream does not depend on the activations, so under programmatic dependent launch the
-//    producer starts filling the ring while the previous kernel is still running; only the
-//    consumers wait for the grid dependency.  HBM therefore stays busy across kernel boundaries.
+//  * q8_gemv_stream — the hot path.  One CTA per SM, three kinds of warps (lum_gemv_dev.cuh).  A producer warp
+//    walks the CTA's share of the weight matrix in tiles of 8 rows x 512 columns (4096 int8 in tensor-core
+//    operand order plus their 128 binary16 scales) and fetches up to 8 of them per ring stage with one bulk
+//    asynchronous copy (cp.async.bulk, completion counted on an mbarrier).  A tensor-core warp issues one
+//    tcgen05.mma (kind::i8, M128 N48 K32) per tile straight from the stage; the exact int32 dot products land in
+//    tensor memory, from where 8 draining warps read them back, apply the block scales and reduce the rows.
+//    The weight stream does not depend on the activations, so under programmatic dependent launch the producer
+//    starts filling the ring while the previous kernel is still running; only the other warps wait for the
+//    grid dependency.
 //  * gemv_direct — any K, f32 / bf16 / Q8_0 weights, one warp per row with plain vector loads.
 //    Used for the small all-f32 model and for shapes the streaming kernel does not take.
 //
@@ -30,10 +31,10 @@
 // (three successive int8 roundings of the residual; |error| <= max|x| * 2^-24 per element, the
 // same order as f32 rounding).  A weight block then contributes
 //     d * s * (q.a1 + (q.a2)/254 + (q.a3)/254^2),   d = the block's binary16 scale
-// with the three integer dot products exact (dp4a: 4 multiply-adds per instruction, 0.75
-// instructions per weight).  The direct kernel keeps the plain f32 form sum_i float(q_i) * x_i.
-// (The CPU restatement multiplies each weight by its scale first and sums sequentially; all three
-// differ by f32 rounding only.)
+// with the three integer dot products exact: they are three of the 48 accumulator columns one tensor-core
+// instruction produces for each of the tile's 128 (block, row) pairs.  The direct kernel keeps the plain
+// f32 form sum_i float(q_i) * x_i.  (The CPU restatement multiplies each weight by its scale first and sums
+// sequentially; all three differ by f32 rounding only.)
 #include <cstdlib>
 
 #include "lum_gemv_dev.cuh"

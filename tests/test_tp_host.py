@@ -61,6 +61,9 @@ def test_unique_id_exchange_two_gloo_ranks(tmp_path):
         got = T.exchange_unique_id(dist, rank, make)
         assert got == bytes((7 * i + 3) % 256 for i in range(128)), got[:8]
         assert len(calls) == (1 if rank == 0 else 0)          # only rank 0 makes the id
+        # the peer-memory handles travel the same way: every rank ends with all handles in rank order
+        hs = T.exchange_peer_handles(dist, dist.get_world_size(), bytes([rank + 1]) * 64)
+        assert hs == [bytes([1]) * 64, bytes([2]) * 64], [h[:2] for h in hs]
         d = pkg.CONFIGS["llama3_8b_q8"]
         s = T.shard_of(d, "down", dist.get_world_size(), rank)
         assert s["col0"] == rank * d.ffn // 2 and s["cols"] == d.ffn // 2
