@@ -24,6 +24,23 @@ template <int HD, int GM, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char attn_smem[];
     if (a.use_pdl) pdl_launch_dependents();
+    // L2 warm-up for the kernels that follow: this CTA's share of each range, in 16 KiB requests (one per thread)
+    {
+        const unsigned int cta = blockIdx.y * gridDim.x + blockIdx.x, n_cta = gridDim.x * gridDim.y;
+        constexpr unsigned long long kReq = 16384;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const unsigned long long total = a.l2_pf_bytes[i];
+            if (total) {
+                const unsigned long long n_req = (total + kReq - 1) / kReq;
+                for (unsigned long long r = (unsigned long long)threadIdx.x * n_cta + cta; r < n_req; r += (unsigned long long)n_cta * kAttnThreads) {
+                    const unsigned long long off = r * kReq;
+                    const unsigned long long len = total - off < kReq ? (total - off) & ~15ull : kReq;
+                    if (len) bulk_prefetch_l2((const unsigned char*)a.l2_pf_ptr[i] + off, (uint32_t)len);
+                }
+            }
+        }
+    }
     // The position was settled by the previous step's sampler, several kernels back in stream order (the step's first
     // kernel waits for that step in full), so the rotation table can be worked out while the projections still run.
     const int p = a.state->pos;

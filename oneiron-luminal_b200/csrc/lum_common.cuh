@@ -100,6 +100,11 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
                  : "memory");
 }
 
+// Ask for [p, p + bytes) to be brought into L2 (16-byte aligned address, size a multiple of 16).  Fire and forget.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // ---- 5th-generation tensor core (tcgen05) and tensor memory ----------------------------------------
 // Shared-memory operand descriptor for a K-major operand without swizzling: the operand is a grid of "core matrices"
 // of 8 rows x 16 bytes, each stored as 128 contiguous bytes (row stride 16 B).  `lbo` is the byte distance between the

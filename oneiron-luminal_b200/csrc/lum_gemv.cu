@@ -116,6 +116,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     GemvSmem g;
     gemv_carve(smem, a.K, a.stages, &s_abort, &g);
     if (tid == 0) GPROBE(0);
+#if defined(LUM_PROBE) && defined(LUM_TL_EPI)
+    if (tid == 0 && blockIdx.x == 0) g_tl_on = (a.epi == LUM_TL_EPI && a.K == LUM_TL_K) ? 1 : 0;   // timeline of one kind of launch only
+#endif
     if (tid == 0 && blockIdx.x == 0 && a.job_ctr_zero) *a.job_ctr_zero = 0u;
     const uint32_t tmem = gemv_cta_begin(g, tid, &s_abort);
     if (a.use_pdl) pdl_launch_dependents();

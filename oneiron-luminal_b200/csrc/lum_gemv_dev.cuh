@@ -48,7 +48,8 @@ static __device__ long long g_tl[64][16];   // one copy per translation unit
 #ifndef LUM_TL_FIRST
 #define LUM_TL_FIRST 0
 #endif
-#define TPROBE(f, e) do { if (blockIdx.x == 0 && (f) >= LUM_TL_FIRST && (f) < LUM_TL_FIRST + 64) g_tl[(f) - LUM_TL_FIRST][e] = clock64(); } while (0)
+static __device__ int g_tl_on = 1;         // a kernel may switch the timeline off for launches it is not interested in
+#define TPROBE(f, e) do { if (blockIdx.x == 0 && g_tl_on && (f) >= LUM_TL_FIRST && (f) < LUM_TL_FIRST + 64) g_tl[(f) - LUM_TL_FIRST][e] = clock64(); } while (0)
 #else
 #define GPROBE(i) do { } while (0)
 #define TPROBE(f, e) do { } while (0)

@@ -112,6 +112,10 @@ struct AttnArgs {
     int max_seq;
     uint32_t* status;
     int use_pdl;
+    // Optional: bytes the NEXT kernels will stream (weights of the o projection, ...).  Attention is latency-bound and leaves
+    // HBM idle, so its CTAs ask for these ranges to be brought into L2 meanwhile (a hint: nothing waits for it).
+    const void* l2_pf_ptr[2];
+    unsigned long long l2_pf_bytes[2];
 };
 
 struct EmbedArgs {

@@ -120,6 +120,7 @@ struct lum_rt {
     float* am_val = nullptr;
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
+    bool l2_prefetch = true;          // attention warms L2 with the o projection's weights (LUM_L2_PREFETCH=0 turns it off)
     unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
     int n_splits = 1;
@@ -382,6 +383,9 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
         t.c_inv_d = rt->c_inv_d; t.c_ln_theta = rt->c_ln_theta; t.c_log2e = rt->c_log2e; t.c_half_pi = rt->c_half_pi;
         t.theta = d.rope_theta; t.window = 0; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
+        if (rt->l2_prefetch && w.o.kc > 0) {
+            t.l2_pf_ptr[0] = w.o.w; t.l2_pf_bytes[0] = q8_packed_bytes((int)w.o.rows, (int)w.o.cols);
+        }
         CU(rt, launch_attn_decode(t, st)); n++;
 
         // o projection (+ residual)
@@ -837,6 +841,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     rt->dim_s = 1; rt->dim_p = 0;
     rt->has_model = true;
     rt->use_mega = rt->cfg.use_mega;
+    if (const char* e = getenv("LUM_L2_PREFETCH")) rt->l2_prefetch = atoi(e) != 0;
     if (int r = setup_mega(rt)) { free_model(rt); return r; }
     return 0;
 }

@@ -51,6 +51,25 @@ public:
     ~B200Runtime() { if (h_) lum_destroy(h_); }
 
     void load_model(const lum_model_desc& d) { ck(lum_model_init(h_, &d)); desc_ = d; }
+    // `Runtime::load_llir` (src/op.rs:16) for a graph serialised as include/lum_llir.h describes
+    void load_llir(const std::vector<uint8_t>& blob, int max_seq, lum_dtype kv, int max_new_tokens = 4096) {
+        ck(lum_load_llir(h_, blob.data(), blob.size(), max_seq, kv, max_new_tokens));
+        char err[8];
+        int64_t t = 0, p = 0, o = 0;
+        lum_llir_describe(blob.data(), blob.size(), &desc_, &t, &p, &o, err, sizeof err);
+        desc_.max_seq = max_seq; desc_.kv_dtype = kv; desc_.max_new_tokens = max_new_tokens;
+    }
+    // `set_data(node, data)` / `get_f32(node)` keyed by HLIR node id (crates/luminal_cuda/src/runtime.rs:160-204)
+    void set_input(int64_t node, const void* host, size_t bytes, lum_dtype dt) { ck(lum_set_input(h_, node, host, bytes, dt)); }
+    std::vector<float> get_output(int64_t node) {
+        std::vector<float> out((size_t)desc_.vocab);
+        ck(lum_get_output(h_, node, out.data(), out.size()));
+        return out;
+    }
+    // tensor parallel: join the group before loading the model; exchange the peer handles after it
+    void tp_init(const uint8_t id[128], int tp_size, int tp_rank) { ck(lum_tp_init(h_, id, tp_size, tp_rank)); }
+    void tp_peer_export(uint8_t handle[64]) { ck(lum_tp_peer_export(h_, handle)); }
+    void tp_peer_import(const std::vector<uint8_t>& handles, int n_ranks) { ck(lum_tp_peer_import(h_, handles.data(), n_ranks)); }
     void set_weight(lum_slot slot, int layer, const void* host, size_t bytes, lum_dtype dt) { ck(lum_model_set_weight(h_, slot, layer, host, bytes, dt)); }
     void synth(uint64_t seed) { ck(lum_model_synth(h_, seed)); }
     void kv_reset() { ck(lum_kv_reset(h_)); }

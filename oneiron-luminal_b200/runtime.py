@@ -81,6 +81,11 @@ CONFIGS: Dict[str, ModelDesc] = {
     "llama3_8b_q8_2layer": _desc(n_layers=2, hidden=4096, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=4096,
                                  max_seq=256, rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"],
                                  kv_dtype=DTYPE["bf16"]),
+    # Qwen3-4B layer shape (per-head q/k RMSNorm, split-half RoPE, theta 1e6, eps 1e-6, head tied to the embedding) cut to
+    # 2 layers and a small vocabulary: hidden 2560 = 5 tiles, ffn 9728 = 19 tiles per row group
+    "qwen3_4b_q8_2layer": _desc(n_layers=2, hidden=2560, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=9728, vocab=4096,
+                                max_seq=256, rms_eps=1e-6, rope_theta=1000000.0, rope_style=1, qk_norm=1, tied_head=1,
+                                weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
     # small Q8_0 model for fast parity runs
     "small_q8": _desc(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=1536, vocab=2048, max_seq=128,
                       rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),

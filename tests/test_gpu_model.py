@@ -171,6 +171,28 @@ def test_llama_shape_two_layers_32_steps(pkg, mega):
     assert rel_err(lg, lo) <= LOGIT_TOL
 
 
+def test_qwen_shape_two_layers_24_steps(pkg):
+    """Qwen3-4B layer shape: per-head RMSNorm on q and k, split-half RoPE (theta 1e6), eps 1e-6, vocabulary projection
+    tied to the bf16 embedding; hidden 2560 and ffn 9728 give 5 and 19 tiles per row group (one short fill; fills of 8, 8, 3).
+    24 greedy steps identical to the oracle, logits within tolerance at the end."""
+    desc = pkg.CONFIGS["qwen3_4b_q8_2layer"]
+    seed = 4
+    orc = OracleModel(desc)
+    orc.synth(seed)
+    prompt = orc.synth_tokens(seed, 20)
+    want, lo, margins = orc.generate(prompt, 24, return_last_logits=True, return_margins=True)
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc)
+        rt.synth(seed)
+        got = rt.generate(prompt, 24)
+        lg = rt.get_f32()
+    finally:
+        rt.close()
+    assert got == want, f"min oracle top-1/top-2 margin {min(margins):.3e}"
+    assert rel_err(lg, lo) <= LOGIT_TOL
+
+
 @pytest.mark.parametrize("graph,pdl,mega", [(0, 0, 0), (1, 0, 0), (0, 1, 0), (1, 1, 1), (0, 0, 1)])
 def test_launch_modes_agree(pkg, rt, graph, pdl, mega):
     """Plain launches, a captured graph, programmatic dependent launch and the persistent whole-token kernel all
