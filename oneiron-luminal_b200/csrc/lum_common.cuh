@@ -30,6 +30,9 @@ enum : uint32_t {
 #ifndef LUM_WAIT_BUDGET_CYCLES
 #define LUM_WAIT_BUDGET_CYCLES 4000000000ll
 #endif
+#ifndef LUM_POLL_SLEEP_NS
+#define LUM_POLL_SLEEP_NS 20
+#endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
@@ -80,13 +83,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 // Same, but gives up at once when *abort becomes non-zero (another thread of the CTA already failed).
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile int* abort) {
 #pragma unroll 1
-    for (int i = 0; i < 32; i++)
+    for (int i = 0; i < 8; i++)
         if (mbar_try_wait(bar, parity)) return true;
+    // a longer wait: poll less eagerly, so that the waiting warps leave the instruction fetch and issue slots of their
+    // scheduler to the warps that have work (two thirds of all executed instructions were polls before)
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 256; i++)
+        for (int i = 0; i < 256; i++) {
             if (mbar_try_wait(bar, parity)) return true;
+#ifndef LUM_NO_POLL_SLEEP
+            __nanosleep(LUM_POLL_SLEEP_NS);
+#endif
+        }
         if (*abort || clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) return false;
     }
 }

@@ -108,6 +108,17 @@ __device__ __forceinline__ float dot4_s8(uint32_t w, float4 x, float acc) {
 
 // ------------------------------------------------------------------------------ streaming kernel (one op)
 
+#ifdef LUM_PROBE
+// per-CTA stamps of the last launches, keyed by the projection kind (epilogue kind * 2 + (K > 4096)): when every CTA got past the
+// grid dependency and when it finished
+__device__ unsigned long long g_kstart[8 * 160], g_kend[8 * 160];
+__device__ __forceinline__ int g_klaunch_of(const GemvArgs& a) { return a.epi * 2 + (a.K > 4096 ? 1 : 0); }
+extern "C" int lum_kstamps_read(unsigned long long* s, unsigned long long* e) {
+    int r = (int)cudaMemcpyFromSymbol(s, g_kstart, sizeof(g_kstart));
+    return r ? r : (int)cudaMemcpyFromSymbol(e, g_kend, sizeof(g_kend));
+}
+#endif
+
 __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_abort;
@@ -144,6 +155,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     GainRegs gr;
     gemv_gain_preload(a, tid, gr);             // independent of the previous kernel: fetched while waiting for it
     if (a.use_pdl) pdl_grid_wait();
+#ifdef LUM_PROBE
+    if (tid == 0) g_kstart[(g_klaunch_of(a) & 7) * 160 + blockIdx.x] = globaltimer_ns();
+#endif
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
     xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq;
@@ -155,6 +169,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     if (a.epi == EPI_PEER) peer_publish(a, tid, kConsumers, 2);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
     GPROBE(4);
+#ifdef LUM_PROBE
+    if (tid == 0) g_kend[(g_klaunch_of(a) & 7) * 160 + blockIdx.x] = globaltimer_ns();
+#endif
 }
 #ifdef LUM_PROBE
 extern "C" int lum_probe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_probe, sizeof(g_probe)); }
@@ -295,6 +312,12 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
     if (rows_total <= 0 || a.K <= 0) return cudaErrorInvalidValue;
 
     if (gemv_stream_supported(a)) {
+        // Share of the jobs every CTA owns without claiming.  One kernel per operation: none (measured best: a CTA that starts
+        // late, because its SM was still busy with the previous kernel, then simply finds less left to claim).
+        static const int env_static = [] { const char* e = getenv("LUM_STATIC_PERMILLE"); return e ? atoi(e) + 1 : 1; }();
+        if (a.debug == 0) a.debug = env_static;
+        static const int env_slack = [] { const char* e = getenv("LUM_CLAIM_SLACK"); return e ? atoi(e) + 1 : 0; }();
+        if (a.max_units == 0) a.max_units = env_slack;
         a.KC = kTileK;
         const int tpr = a.K / kTileK, gpf = tpr >= 5 ? 1 : kFillTiles / tpr;
         const int jobs = (rows_total / kTileRows + gpf - 1) / gpf;

@@ -493,7 +493,8 @@ __device__ __forceinline__ GemvPlan gemv_plan(const GemvArgs& a, int n_cta, bool
     p.seg_rg0[3] = rgs;
     p.J = jobs;
     if (dynamic) {
-        p.js = (int)((long long)p.J * 3 / 4 / n_cta);       // three quarters static, the rest to whoever is ahead
+        const int permille = a.debug > 0 ? a.debug - 1 : 750;   // statically owned share (a.debug carries a tuning override)
+        p.js = (int)((long long)p.J * permille / 1000 / n_cta);
         p.pool0 = p.js * n_cta;
     } else {
         p.js = 0;                                            // everything in the "pool", split evenly by CTA index
@@ -559,9 +560,16 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvPlan& 
     for (int j = cta * p.js; j < (cta + 1) * p.js; j++)
         if (!issue_job(j)) return false;
     if (job_ctr) {
+        // A CTA that starts early (its SM was free while the previous kernel still ran elsewhere) could fill its whole ring
+        // with claims before the others have started, and then has to drain it alone after the grid dependency resolves:
+        // measured on the o projection, the last CTA finished 3-5 us after the median.  So a CTA takes at most its even
+        // share plus one; a claim is only made when it will be used.
+        const int cap = (p.J + n_cta - 1) / n_cta + (a.max_units > 0 ? a.max_units - 1 : 1) - p.js;   // a.max_units: tuning override of the slack
+        int taken = 0;
         while ((int)claim < npool) {
-            const unsigned int nxt = atomicAdd(job_ctr, 1u);
+            const unsigned int nxt = taken + 1 < cap ? atomicAdd(job_ctr, 1u) : (unsigned int)npool;
             if (!issue_job(p.pool0 + (int)claim)) return false;
+            taken++;
             claim = nxt;
         }
     } else {

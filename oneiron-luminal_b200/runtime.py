@@ -86,6 +86,10 @@ CONFIGS: Dict[str, ModelDesc] = {
     "qwen3_4b_q8_2layer": _desc(n_layers=2, hidden=2560, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=9728, vocab=4096,
                                 max_seq=256, rms_eps=1e-6, rope_theta=1000000.0, rope_style=1, qk_norm=1, tied_head=1,
                                 weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
+    # like small_q8, but with an FFN width whose half (1792 = 3.5 tiles) does not cut into tiles: sharded over two ranks, the
+    # down and o projections take the plain-load kernel — the shapes an 8-way split of the Llama-3-8B model produces
+    "small_q8_odd": _desc(n_layers=2, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=3584, vocab=2048, max_seq=128,
+                          rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
     # small Q8_0 model for fast parity runs
     "small_q8": _desc(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=1536, vocab=2048, max_seq=128,
                       rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
