@@ -117,15 +117,22 @@ cudaError_t launch_embed(const EmbedArgs& a_in, cudaStream_t st) {
     return cudaLaunchKernelExC(&cfg, (const void*)embed_row, params);
 }
 
-// Tensor parallel sampling: every rank holds {logit bits, global row} of all ranks' vocabulary shards (after an
-// all-gather); the greedy sample is the maximum, the last row winning ties, exactly as on one GPU.
-__global__ void tp_pick(const int* pairs, int n_ranks, DecodeState* st, int* tokens_out, int advance) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// Tensor parallel sampling: every rank holds {logit bits, global row} of all ranks' vocabulary shards — after an all-gather, or
+// written straight into this rank's memory by the other ranks' sampling kernels, in which case `flags` (one word per rank,
+// 32 words apart) say when each pair has landed.  The greedy sample is the maximum, the last row winning ties, as on one GPU.
+__global__ void tp_pick(const int* pairs, int pair_stride, const uint32_t* flags, const uint32_t* seq, uint32_t tag, uint32_t* status,
+                        int n_ranks, DecodeState* st, int* tokens_out, int advance) {
+    if (blockIdx.x != 0) return;
+    if (flags) {
+        if ((int)threadIdx.x < n_ranks && !wait_word_sys(flags + (size_t)threadIdx.x * 32, peer_word(__ldcg(seq), tag))) atomicOr(status, LUM_ST_WAIT_PEER);
+        __syncthreads();
+    }
+    if (threadIdx.x != 0) return;
     float best = -INFINITY;
     int bi = -1;
     for (int r = 0; r < n_ranks; r++) {
-        const float v = __int_as_float(pairs[2 * r]);
-        const int i = pairs[2 * r + 1];
+        const float v = __int_as_float(__ldcg(pairs + (size_t)r * pair_stride));
+        const int i = __ldcg(pairs + (size_t)r * pair_stride + 1);
         if (i >= 0 && (bi < 0 || v > best || (v == best && i > bi))) { best = v; bi = i; }
     }
     if (bi < 0) bi = 0;
@@ -134,8 +141,9 @@ __global__ void tp_pick(const int* pairs, int n_ranks, DecodeState* st, int* tok
     if (st->log && tokens_out && step < st->max_steps) { tokens_out[step] = bi; st->step = step + 1; }
     if (advance) { st->tok = bi; st->pos = st->pos + 1; }
 }
-cudaError_t launch_tp_pick(const int* pairs, int n_ranks, DecodeState* state, int* tokens_out, int advance, cudaStream_t st) {
-    tp_pick<<<1, 32, 0, st>>>(pairs, n_ranks, state, tokens_out, advance);
+cudaError_t launch_tp_pick(const int* pairs, int pair_stride, const uint32_t* flags, const uint32_t* seq, uint32_t tag, uint32_t* status,
+                           int n_ranks, DecodeState* state, int* tokens_out, int advance, cudaStream_t st) {
+    tp_pick<<<1, 32, 0, st>>>(pairs, pair_stride, flags, seq, tag, status, n_ranks, state, tokens_out, advance);
     return cudaGetLastError();
 }
 

@@ -59,9 +59,20 @@ __device__ __forceinline__ void argmax_finish(const GemvArgs& a, ArgBest mine, i
         const int fi = fb.i;
         if (tid == 0) {
             DecodeState* st = a.pair_out ? nullptr : a.state;
-            if (a.pair_out) {   // tensor parallel: publish this shard's best; the ranks' pairs are folded after an all-gather
-                a.pair_out[0] = __float_as_int(fb.v);
-                a.pair_out[1] = fi >= 0 ? fi + a.row_offset : -1;
+            if (a.pair_out) {   // tensor parallel: publish this shard's best; the ranks' pairs are folded after an all-gather ...
+                const int pv = __float_as_int(fb.v), pi = fi >= 0 ? fi + a.row_offset : -1;
+                a.pair_out[0] = pv;
+                a.pair_out[1] = pi;
+                if (a.n_peers > 0) {   // ... or are written into every rank's memory right here, followed by "landed" words
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; r++)
+                        if (r < a.n_peers) { int* dst = (int*)a.peer_out[r]; dst[0] = pv; dst[1] = pi; }
+                    __threadfence_system();
+                    const uint32_t word = peer_word(__ldcg(a.seq), a.peer_tag);
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; r++)
+                        if (r < a.n_peers) st_release_sys(a.peer_flag[r], word);
+                }
             }
             if (st) {
                 const int step = st->step;

@@ -138,7 +138,8 @@ bool gemv_stream_supported(const GemvArgs& a);
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t st);
 cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
 // tensor parallel: fold the ranks' {logit bits, row} pairs into the sample (last maximum wins) and advance the state
-cudaError_t launch_tp_pick(const int* pairs, int n_ranks, DecodeState* state, int* tokens_out, int advance, cudaStream_t st);
+cudaError_t launch_tp_pick(const int* pairs, int pair_stride, const uint32_t* flags, const uint32_t* seq, uint32_t tag, uint32_t* status,
+                           int n_ranks, DecodeState* state, int* tokens_out, int advance, cudaStream_t st);
 
 // synthetic tensors + format conversion
 cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,

@@ -430,14 +430,27 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
         take_partial(a);
+        // exchange buffer, words 2048.. : the ranks' sampling pairs (16 bytes apart), words 2304.. : their "landed" words (128 apart)
+        auto sym_pair = [&](unsigned char* base, int rank) { return (int*)(base + 2048 + (size_t)rank * 16); };
+        auto sym_pair_flag = [&](unsigned char* base, int rank) { return (uint32_t*)(base + 2304 + (size_t)rank * 128); };
+        const uint32_t pick_tag = 1023;
         if (tp) { a.pair_out = rt->tp_pairs + 2 * rt->tp_size; a.row_offset = rt->tp_rank * rt->vocab_l; }
+        if (fused) {
+            a.n_peers = rt->tp_size; a.seq = rt->tp_seq; a.peer_tag = pick_tag;
+            for (int r = 0; r < rt->tp_size; r++) { a.peer_out[r] = (float*)sym_pair(rt->peer_sym[r], rt->tp_rank); a.peer_flag[r] = sym_pair_flag(rt->peer_sym[r], rt->tp_rank); }
+        }
         claim_ctr(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
-        if (tp) {
+        if (fused) {
+            // every rank's sampling kernel has written its pair into every rank's buffer: wait for the words, fold the pairs
+            CU(rt, launch_tp_pick(sym_pair(rt->sym, 0), 4, sym_pair_flag(rt->sym, 0), rt->tp_seq, pick_tag, rt->status, rt->tp_size, rt->state,
+                                  rt->tokens_out, 1, st));
+            n++;
+        } else if (tp) {
             // every rank needs every shard's best row: all-gather the pairs, then fold them the same way everywhere
             const int rc = nccl().AllGather(rt->tp_pairs + 2 * rt->tp_size, rt->tp_pairs, 2, kNcclInt32, rt->comm, st);
             if (rc) return fail(rt, LUM_E_CUDA, "ncclAllGather: %s", nccl().GetErrorString(rc));
-            CU(rt, launch_tp_pick(rt->tp_pairs, rt->tp_size, rt->state, rt->tokens_out, 1, st));
+            CU(rt, launch_tp_pick(rt->tp_pairs, 2, nullptr, nullptr, 0, rt->status, rt->tp_size, rt->state, rt->tokens_out, 1, st));
             n += 2;
         }
     }
