@@ -81,6 +81,27 @@ __device__ __forceinline__ void attn_fill_rope(const AttnArgs& a, unsigned char*
     }
 }
 
+// DPL consecutive cache elements as the bits they are stored in (bf16: 2 bytes each, else f32)
+template <bool BF16, int DPL> struct RawRow;
+template <> struct RawRow<true, 4> { using type = uint2; };
+template <> struct RawRow<true, 2> { using type = uint32_t; };
+template <> struct RawRow<false, 4> { using type = float4; };
+template <> struct RawRow<false, 2> { using type = float2; };
+template <bool BF16, int DPL>
+__device__ __forceinline__ typename RawRow<BF16, DPL>::type raw_load(const void* base, size_t elem_off) {
+    using T = typename RawRow<BF16, DPL>::type;
+    return BF16 ? *(const T*)((const uint16_t*)base + elem_off) : *(const T*)((const float*)base + elem_off);
+}
+__device__ __forceinline__ void raw_to_float_impl(uint2 r, float* out) {
+    out[0] = __uint_as_float(r.x << 16); out[1] = __uint_as_float(r.x & 0xffff0000u);
+    out[2] = __uint_as_float(r.y << 16); out[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+__device__ __forceinline__ void raw_to_float_impl(uint32_t r, float* out) { out[0] = __uint_as_float(r << 16); out[1] = __uint_as_float(r & 0xffff0000u); }
+__device__ __forceinline__ void raw_to_float_impl(float4 r, float* out) { out[0] = r.x; out[1] = r.y; out[2] = r.z; out[3] = r.w; }
+__device__ __forceinline__ void raw_to_float_impl(float2 r, float* out) { out[0] = r.x; out[1] = r.y; }
+template <bool BF16, int DPL>
+__device__ __forceinline__ void raw_to_float(typename RawRow<BF16, DPL>::type r, float* out) { raw_to_float_impl(r, out); }
+
 template <bool BF16, int DPL>
 __device__ __forceinline__ void load_dpl(const void* base, size_t elem_off, float* out) {
     if (BF16) {
@@ -201,14 +222,28 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
 #pragma unroll
         for (int i = 0; i < DPL; i++) { q[g][i] = g < G ? s_q[g][d0 + i] : 0.0f; o[g][i] = 0.0f; }
     }
-    // rows of this CTA: cached rows r0 .. r1-1, then (last split only) the step's own row from shared memory
+    // rows of this CTA: cached rows r0 .. r1-1, then (last split only) the step's own row from shared memory.  A warp takes rows
+    // warp, warp + NW, ...; the next row's K and V are requested (raw bits, converted only when used) before the current row is
+    // worked on, so a warp waits for memory once, not once per row.
+    using Raw = typename RawRow<BF16, DPL>::type;
+    Raw kn = Raw(), vn = Raw();
+    if (warp < nc) {
+        const size_t off = (size_t)(r0 + warp) * row_elems + (size_t)kvh * HD + d0;
+        kn = raw_load<BF16, DPL>(a.k_cache, off);
+        vn = raw_load<BF16, DPL>(a.v_cache, off);
+    }
 #pragma unroll 1
     for (int j = warp; j < n_rows; j += NW) {
         float kr[DPL], vr[DPL];
+        const Raw kc = kn, vc = vn;
+        if (j + NW < nc) {
+            const size_t off = (size_t)(r0 + j + NW) * row_elems + (size_t)kvh * HD + d0;
+            kn = raw_load<BF16, DPL>(a.k_cache, off);
+            vn = raw_load<BF16, DPL>(a.v_cache, off);
+        }
         if (j < nc) {
-            const size_t off = (size_t)(r0 + j) * row_elems + (size_t)kvh * HD + d0;
-            load_dpl<BF16, DPL>(a.k_cache, off, kr);
-            load_dpl<BF16, DPL>(a.v_cache, off, vr);
+            raw_to_float<BF16, DPL>(kc, kr);
+            raw_to_float<BF16, DPL>(vc, vr);
         } else {
 #pragma unroll
             for (int i = 0; i < DPL; i++) { kr[i] = s_q[G][d0 + i]; vr[i] = s_v[d0 + i]; }
