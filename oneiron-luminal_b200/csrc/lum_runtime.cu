@@ -120,7 +120,7 @@ struct lum_rt {
     float* am_val = nullptr;
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
-    bool l2_prefetch = true;          // attention warms L2 with the o projection's weights (LUM_L2_PREFETCH=0 turns it off)
+    bool l2_prefetch = false;         // LUM_L2_PREFETCH=1: attention warms L2 with the o projection's weights (measured: no gain)
     unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
     int n_splits = 1;
