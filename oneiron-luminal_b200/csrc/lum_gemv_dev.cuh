@@ -150,15 +150,16 @@ __device__ __forceinline__ float load_gain(const void* g, int kind, int i) {
     return kind == WK_BF16 ? bf16_bits_to_f32(((const uint16_t*)g)[i]) : ((const float*)g)[i];
 }
 
-// Sum over the block's `nthreads` threads (a multiple of 32, <= 512); result in all threads.
-__device__ __forceinline__ float block_sum(float v, float* scratch, int tid, int nthreads, int bar_id) {
+// Sum over the block's `nthreads` threads (a multiple of 32, <= 512); result in all threads.  `reuse`: the scratch words may be
+// written again right after the call (costs a second barrier); false when the caller passes another barrier first anyway.
+__device__ __forceinline__ float block_sum(float v, float* scratch, int tid, int nthreads, int bar_id, bool reuse = true) {
     v = warp_sum(v);
     if ((tid & 31) == 0) scratch[tid >> 5] = v;
     named_sync(bar_id, nthreads);
     float t = 0.0f;
     const int nw = nthreads >> 5;
     for (int w = 0; w < nw; w++) t += scratch[w];
-    named_sync(bar_id, nthreads);
+    if (reuse) named_sync(bar_id, nthreads);
     return t;
 }
 
@@ -397,7 +398,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             const float4 t = xv[it];
             ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
         }
-        ss = block_sum(ss, g.scratch, tid, kWorkers, 1);
+        ss = block_sum(ss, g.scratch, tid, kWorkers, 1, false);   // the prologue ends in a barrier before anything touches the scratch again
         const float mean = ss * (1.0f / (float)K);
         inv = 1.0f / sqrtf(mean + a.eps);
     }
