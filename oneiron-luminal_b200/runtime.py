@@ -90,6 +90,11 @@ CONFIGS: Dict[str, ModelDesc] = {
     # down and o projections take the plain-load kernel — the shapes an 8-way split of the Llama-3-8B model produces
     "small_q8_odd": _desc(n_layers=2, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=3584, vocab=2048, max_seq=128,
                           rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
+    # a quarter of the Llama-3-8B layer (8/2 heads, ffn 3584, vocabulary 32064) at full hidden size: split over 2 ranks, every
+    # rank holds exactly the shard shapes of the full model split over 8 (one KV head, o K = 512, down K = 1792, 16032 vocabulary rows)
+    "llama3_8b_q8_quarter": _desc(n_layers=2, hidden=4096, n_q_heads=8, n_kv_heads=2, head_dim=128, ffn=3584, vocab=32064,
+                                  max_seq=256, rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"],
+                                  kv_dtype=DTYPE["bf16"]),
     # small Q8_0 model for fast parity runs
     "small_q8": _desc(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=1536, vocab=2048, max_seq=128,
                       rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),

@@ -18,7 +18,7 @@ def _gpus():
 
 
 @pytest.mark.parametrize("fused", [1, 0])
-@pytest.mark.parametrize("world,cfg", [(2, "small_q8"), (2, "small_q8_odd"), (2, "tiny_f32"), (2, "llama3_8b_q8_2layer"),
+@pytest.mark.parametrize("world,cfg", [(2, "small_q8"), (2, "small_q8_odd"), (2, "tiny_f32"), (2, "llama3_8b_q8_2layer"), (2, "llama3_8b_q8_quarter"),
                                        (4, "llama3_8b_q8_2layer")])
 def test_tp_matches_single_gpu(world, cfg, fused):
     """fused = 1: partial sums through peer memory inside the projection kernels; 0: NCCL all-reduce between them."""
