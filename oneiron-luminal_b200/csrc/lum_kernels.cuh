@@ -32,10 +32,10 @@ struct DecodeState {
 };
 
 struct GemvSeg {
-    const void* w;      // Q8_0: quants plane (int8 [rows, K]) or the packed stage-unit stream; else the f32 / bf16 matrix [rows, K]
+    const void* w;      // Q8_0: quants plane (int8 [rows, K]) or the packed tile stream; else the f32 / bf16 matrix [rows, K]
     const __half* s;    // Q8_0 planes: scales [rows, K/32]; otherwise null
     int rows;
-    int kc;             // Q8_0: 0 = planes; > 0 = packed stage-units with this K-chunk (see lum_synth.cu)
+    int kc;             // Q8_0: 0 = planes; 512 = packed tile stream (tiles of 8 rows x 512 columns, see lum_synth.cu)
 };
 
 struct GemvArgs {
@@ -64,12 +64,12 @@ struct GemvArgs {
     int row_offset;
     uint32_t* status;
     // geometry of the streaming kernel
-    int KC;                // K-chunk per stage (power of two, divides K, 512..4096)
+    int KC;                // tile width of the packed layout (set by the launcher)
     int stages;
-    int max_units;         // most stage-units any CTA owns (sizes the reduction scratch)
+    int max_units;         // tuning override: 1 + extra jobs a CTA may claim beyond its even share (0 = default)
     int use_pdl;
     int force_direct;      // 1: never take the streaming kernel (operator tests compare the two)
-    int debug;             // tuning probes of the streaming kernel (0 in normal use)
+    int debug;             // tuning override: 1 + permille of the jobs owned statically (0 = default)
     unsigned int* job_ctr; // streaming kernel: zeroed counter the producers claim pooled jobs from (null: static split)
     unsigned int* job_ctr_zero;   // optional: a counter of a launch far enough away in stream order, zeroed by CTA 0 for its next use
     // Tensor parallel without a collective kernel.  Producing side (EPI_PEER): peer_out[r] is rank r's buffer for THIS rank's

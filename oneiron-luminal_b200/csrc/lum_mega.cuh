@@ -4,7 +4,7 @@
 
 namespace lum {
 
-// Per-layer device pointers (weights in the packed Q8_0 stage-unit layout).
+// Per-layer device pointers (weights in the packed Q8_0 tile-stream layout).
 struct MegaLayer {
     const unsigned char *wq, *wk, *wv, *wo, *wg, *wu, *wd;
     const void *attn_norm, *mlp_norm, *q_norm, *k_norm;

@@ -77,7 +77,7 @@ struct Tensor {
     void* w = nullptr;       // quants / f32 / bf16
     __half* s = nullptr;     // Q8_0 scales
     int kind = WK_F32;
-    int kc = 0;              // Q8_0: 0 = planes, > 0 = packed stage-units with this K-chunk
+    int kc = 0;              // Q8_0: 0 = planes, 512 = packed tile stream
     size_t rows = 0, cols = 0;          // this rank's shard
     size_t row0 = 0, col0 = 0;          // shard origin in the full tensor
     size_t full_rows = 0, full_cols = 0;
@@ -890,7 +890,7 @@ int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void
         // before its DMA has landed and would not be ordered against kernels on this stream
         e = cudaMemcpy2DAsync(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice, rt->stream);
         if (t->kc) {
-            // wire blocks -> temporary planes -> packed stage-units
+            // wire blocks -> temporary planes -> packed tile stream
             void* planes = nullptr;
             const size_t n = t->rows * t->cols;
             if (e == cudaSuccess) e = cudaMalloc(&planes, n + n / 16 + 64);
