@@ -89,7 +89,7 @@ __device__ __forceinline__ void argmax_finish(const GemvArgs& a, ArgBest mine, i
 // scaled by the gains).
 __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, int tid, int nthreads, float* scratch, int bar_id) {
     const int K = a.K;
-    if (a.n_parts > 0) peer_wait_parts(a.part_flags, a.n_parts, a.seq, a.parts_tag, a.status, tid, nthreads, bar_id);
+    if (a.n_parts > 0 && a.part_flags) peer_wait_parts(a.part_flags, a.n_parts, a.seq, a.parts_tag, a.status, tid, nthreads, bar_id);
     // the raw activations first (x, plus a reduced partial or the ranks' partials in rank order), then the norm over them
     float ss = 0.0f;
     for (int k = tid; k < K; k += nthreads) {
@@ -331,7 +331,8 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
         if (a.max_units == 0) a.max_units = env_slack;
         a.KC = kTileK;
         const int tpr = a.K / kTileK, gpf = tpr >= 5 ? 1 : kFillTiles / tpr;
-        const int jobs = (rows_total / kTileRows + gpf - 1) / gpf;
+        int jobs = (rows_total / kTileRows + gpf - 1) / gpf;
+        if (a.ksplit == 2 && a.epi == EPI_STORE && a.nseg == 1 && gemv_can_ksplit(a.K, a.seg[0].kc)) jobs *= 2; else a.ksplit = 0;
         int grid = sm_count < jobs ? sm_count : jobs;
         const size_t fixed = gemv_fixed_smem(a.K);
         // One CTA per SM (576 threads): the ring takes what is left of shared memory.  LUM_GEMV_STAGES overrides.
@@ -354,6 +355,7 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
         return launch_with_attrs((const void*)q8_gemv_stream, dim3(grid), dim3(kGemvThreads), smem, st, a.use_pdl != 0, a);
     }
 
+    if (a.ksplit == 2) return cudaErrorInvalidValue;     // the caller's consumer expects two partial vectors: only the streaming kernel makes them
     // direct kernel: a few CTAs per SM's worth of rows, at least 8 rows per CTA
     int grid = sm_count * 2;
     if (grid > (rows_total + 7) / 8) grid = (rows_total + 7) / 8;

@@ -77,9 +77,11 @@ constexpr int kMmaN = 48;                // accumulator columns per tile: 16 blo
 constexpr int kXqTileBytes = 1536;       // activation bytes per tile: 48 operand rows x 32
 
 // fields of meta2[stage]
-constexpr uint32_t kM2JobEnd = 1u << 16, kM2Up = 1u << 17;
-__device__ __forceinline__ uint32_t m2_pack(int ntiles, int c0, int n_rg, bool job_end, int part) {
-    return (uint32_t)ntiles | ((uint32_t)c0 << 4) | ((uint32_t)n_rg << 12) | (job_end ? kM2JobEnd : 0u) | (part ? kM2Up : 0u);
+constexpr uint32_t kM2JobEnd = 1u << 16, kM2Up = 1u << 17, kM2First = 1u << 18, kM2Half = 1u << 19;
+constexpr int kUnitHalf = 1 << 30;        // unit_of[]: the slot holds the second K half of its row group
+__device__ __forceinline__ uint32_t m2_pack(int ntiles, int c0, int n_rg, bool job_end, int part, bool first, int half) {
+    return (uint32_t)ntiles | ((uint32_t)c0 << 4) | ((uint32_t)n_rg << 12) | (job_end ? kM2JobEnd : 0u) | (part ? kM2Up : 0u) |
+           (first ? kM2First : 0u) | (half ? kM2Half : 0u);
 }
 
 // Shared-memory carve-up used by a streaming phase.
@@ -188,7 +190,11 @@ __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const flo
             if (pr >= 0) a.y[unit_of[sl] * kTileRows + r] = swiglu(vals[i], vals[pr * kTileRows + r]);
         }
     } else if (a.epi == EPI_STORE) {
-        for (int i = tid; i < n; i += nthreads) a.y[unit_of[i >> 3] * kTileRows + (i & 7)] = vals[i];
+        for (int i = tid; i < n; i += nthreads) {
+            const int u = unit_of[i >> 3];
+            float* y = (u & kUnitHalf) ? a.y + a.y_half_stride : a.y;
+            y[(u & (kUnitHalf - 1)) * kTileRows + (i & 7)] = vals[i];
+        }
     } else if (a.epi == EPI_RESID) {
         for (int i = tid; i < n; i += nthreads) { const int row = unit_of[i >> 3] * kTileRows + (i & 7); a.y[row] = a.resid[row] + vals[i]; }
     } else if (a.epi == EPI_PEER) {
@@ -357,7 +363,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         return t;
     };
-    if (xs.n_parts > 0) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
+    if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
     float4 xv[kXTrips];
 #pragma unroll
     for (int it = 0; it < kXTrips; it++) {
@@ -470,6 +476,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
 //   fill of gpf row groups; for SwiGLU the same for the gate matrix followed by the same for the up matrix.
 struct GemvPlan {
     int tpr, gpf, sub;
+    int ks;           // 2: every row group is two jobs, one per K half (long single matrices only)
     int J;            // jobs in the phase
     int js;           // jobs statically owned by every CTA: CTA c has [c*js, (c+1)*js)
     int pool0;        // first pooled job: [pool0, J) are claimed dynamically (or, without a counter, split statically)
@@ -482,13 +489,14 @@ __device__ __forceinline__ GemvPlan gemv_plan(const GemvArgs& a, int n_cta, bool
     p.tpr = a.K / kTileK;
     p.gpf = p.tpr >= 5 ? 1 : kFillTiles / p.tpr;
     p.sub = a.epi == EPI_SWIGLU ? 2 : 1;
+    p.ks = (a.ksplit == 2 && a.epi == EPI_STORE && a.nseg == 1 && gemv_can_ksplit(a.K, a.seg[0].kc)) ? 2 : 1;
     int jobs = 0, rgs = 0;
     for (int i = 0; i < 3; i++) {
         const int n = i < a.nseg ? a.seg[i].rows / kTileRows : 0;
         p.nrg[i] = n;
         p.seg_job0[i] = jobs;
         p.seg_rg0[i] = rgs;
-        if (a.epi != EPI_SWIGLU || i == 0) { jobs += (n + p.gpf - 1) / p.gpf; rgs += n; }
+        if (a.epi != EPI_SWIGLU || i == 0) { jobs += (n + p.gpf - 1) / p.gpf * p.ks; rgs += n; }
     }
     p.seg_job0[3] = jobs;
     p.seg_rg0[3] = rgs;
@@ -525,17 +533,27 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvPlan& 
         return true;
     };
     auto advance = [&]() { r.armed++; if (++r.stage == S) { r.stage = 0; r.par ^= 1u; } };
-    auto emit = [&](const unsigned char* src, int ntiles, int c0, int n_rg, int rg_global, bool job_end, int part) -> bool {
+    auto emit = [&](const unsigned char* src, int ntiles, int c0, int n_rg, int rg_global, bool job_end, int part, bool first, int half) -> bool {
         if (!next_stage()) return false;
         const uint32_t fb = g.full0 + 8u * r.stage;
         const uint32_t bytes = (uint32_t)ntiles * kTileBytes;
-        g.meta[r.stage] = make_int2(rg_global, (int)m2_pack(ntiles, c0, n_rg, job_end, part));
+        g.meta[r.stage] = make_int2(rg_global, (int)m2_pack(ntiles, c0, n_rg, job_end, part, first, half));
         mbar_arrive_expect_tx(fb, bytes);
         bulk_g2s(smem_u32(g.stage0 + (size_t)r.stage * kFillBytes), src, bytes, fb);
         advance();
         return true;
     };
     auto issue_job = [&](int j) -> bool {
+        if (p.ks == 2) {
+            // one K half of one row group: tiles [t0, t1)
+            const int rg = j >> 1, half = j & 1, t0 = half * (p.tpr >> 1), t1 = t0 + (p.tpr >> 1);
+            const unsigned char* base = (const unsigned char*)a.seg[0].w + (size_t)rg * p.tpr * kTileBytes;
+            for (int c = t0; c < t1; c += kFillTiles) {
+                const int nt = min(kFillTiles, t1 - c);
+                if (!emit(base + (size_t)c * kTileBytes, nt, c, 1, rg, c + kFillTiles >= t1, 0, c == t0, half)) return false;
+            }
+            return true;
+        }
         int sg = 0;
         if (a.epi != EPI_SWIGLU) while (sg < a.nseg - 1 && j >= p.seg_job0[sg + 1]) sg++;
         const int rg = (j - p.seg_job0[sg]) * p.gpf;                      // first row group of the job, inside its segment
@@ -544,11 +562,11 @@ __device__ __forceinline__ bool gemv_produce(const GemvArgs& a, const GemvPlan& 
             const unsigned char* base = (const unsigned char*)a.seg[sg + part].w + (size_t)rg * p.tpr * kTileBytes;
             const bool last_part = part == p.sub - 1;
             if (p.tpr <= kFillTiles) {
-                if (!emit(base, n_rg * p.tpr, 0, n_rg, p.seg_rg0[sg] + rg, last_part, part)) return false;
+                if (!emit(base, n_rg * p.tpr, 0, n_rg, p.seg_rg0[sg] + rg, last_part, part, true, 0)) return false;
             } else {
                 for (int c = 0; c < p.tpr; c += kFillTiles) {
                     const int nt = min(kFillTiles, p.tpr - c);
-                    if (!emit(base + (size_t)c * kTileBytes, nt, c, 1, p.seg_rg0[sg] + rg, last_part && c + kFillTiles >= p.tpr, part)) return false;
+                    if (!emit(base + (size_t)c * kTileBytes, nt, c, 1, p.seg_rg0[sg] + rg, last_part && c + kFillTiles >= p.tpr, part, c == 0, 0)) return false;
                 }
             }
         }
@@ -747,11 +765,12 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
             const uint32_t m2 = (uint32_t)mm.y;
             const int nt = (int)(m2 & 15u), c0 = (int)((m2 >> 4) & 255u), n_rg = (int)((m2 >> 12) & 15u);
             const unsigned char* st = g.stage0 + (size_t)cr.stage * kFillBytes;
-            if (c0 == 0) {
+            const bool first = (m2 & kM2First) != 0;       // first fill of a job part: its row groups take new slots
+            if (first) {
                 slot_base = slot;
                 slot += n_rg;
                 if (tid < n_rg) {
-                    g.unit_of[slot_base + tid] = u + tid;
+                    g.unit_of[slot_base + tid] = (u + tid) | ((m2 & kM2Half) ? kUnitHalf : 0);
                     g.pair_of[slot_base + tid] = (m2 & kM2Up) ? -1 : slot_base + n_rg + tid;
                 }
             }
@@ -799,7 +818,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
                 v += __shfl_xor_sync(0xffffffffu, v, 16);
                 if (lane < 8) {
                     float* dst = g.red + (size_t)slot_base * 64 + warp * 8 + lane;
-                    *dst = c0 == 0 ? v : *dst + v;
+                    *dst = first ? v : *dst + v;
                 }
             } else {
 #pragma unroll 1

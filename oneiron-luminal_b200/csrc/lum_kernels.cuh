@@ -72,6 +72,9 @@ struct GemvArgs {
     int debug;             // tuning override: 1 + permille of the jobs owned statically (0 = default)
     unsigned int* job_ctr; // streaming kernel: zeroed counter the producers claim pooled jobs from (null: static split)
     unsigned int* job_ctr_zero;   // optional: a counter of a launch far enough away in stream order, zeroed by CTA 0 for its next use
+    int ksplit;            // 2: EPI_STORE over one long-K matrix cut into two K halves per row group (twice the jobs, half the size);
+                           // half h's partial sums go to y + h * y_half_stride and the consumer of y adds the two vectors up
+    int y_half_stride;
     // Tensor parallel without a collective kernel.  Producing side (EPI_PEER): peer_out[r] is rank r's buffer for THIS rank's
     // partial vector (r == own rank included), peer_flag[r] the word in rank r's memory that says it is complete.
     float* peer_out[kMaxPeers];
@@ -131,6 +134,9 @@ struct EmbedArgs {
 
 // message of the last failed stand-alone operator on this thread (read back through lum_last_error(NULL))
 void set_op_error(const char* msg);
+
+// whether a [N, K] Q8_0 matrix (kc: its layout, see GemvSeg) can be run as two K halves per row group (GemvArgs::ksplit)
+__host__ __device__ inline bool gemv_can_ksplit(int K, int kc) { const int tpr = K / 512; return kc == 512 && K % 512 == 0 && tpr > 8 && (tpr & 1) == 0; }
 
 // launchers (each returns the CUDA error of the launch)
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);

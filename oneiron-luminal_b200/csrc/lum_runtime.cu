@@ -120,6 +120,7 @@ struct lum_rt {
     float* am_val = nullptr;
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
+    bool down_ksplit = true;          // LUM_DOWN_KSPLIT=0: the down projection as one job per row group
     bool l2_prefetch = false;         // LUM_L2_PREFETCH=1: attention warms L2 with the o projection's weights (measured: no gain)
     unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
@@ -334,6 +335,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
     const bool fused = tp && rt->peers_open;
     uint32_t pending_tag = 0;
     int pending_buf = 0;
+    bool pending_halves = false;
     auto sym_flag = [&](unsigned char* base, int buf, int rank) { return (uint32_t*)(base + ((size_t)buf * kMaxPeers + rank) * 128); };
     auto sym_part = [&](unsigned char* base, int buf, int rank) { return (float*)(base + 4096) + ((size_t)buf * rt->tp_size + rank) * H; };
     auto publish_to_peers = [&](GemvArgs& g, int buf, uint32_t tag) {
@@ -349,6 +351,9 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         if (fused) {
             g.parts = sym_part(rt->sym, pending_buf, 0); g.part_flags = sym_flag(rt->sym, pending_buf, 0);
             g.n_parts = rt->tp_size; g.part_stride = H; g.parts_tag = pending_tag; g.seq = rt->tp_seq;
+        } else if (pending_halves) {
+            g.parts = rt->part; g.n_parts = 2; g.part_stride = H;      // the two K halves of the down projection (same GPU: no words to wait for)
+            pending_halves = false;
         } else {
             g.x_add = rt->part;
         }
@@ -416,6 +421,12 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         dn.K = (int)w.down.cols; dn.x = rt->h;
         if (fused) publish_to_peers(dn, 1, (uint32_t)(2 * l + 2));
         else if (tp) { dn.epi = EPI_STORE; dn.y = rt->part; }
+        else if (rt->down_ksplit && gemv_can_ksplit(dn.K, w.down.kc)) {
+            // One GPU: the long-K projection as two jobs per row group (a job is then 61 KB instead of 122 KB: the kernel's
+            // tail, one job long, halves); the two partial vectors join the residual stream in the next prologue.
+            dn.epi = EPI_STORE; dn.y = rt->part; dn.ksplit = 2; dn.y_half_stride = H;
+            pending = true; pending_halves = true;
+        }
         else { dn.epi = EPI_RESID; dn.y = cur; dn.resid = cur; }
         claim_ctr(dn);
         CU(rt, launch_gemv(dn, rt->sm_count, st)); n++;
@@ -819,7 +830,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     const int G = d.n_q_heads / d.n_kv_heads;
     TRY(dev_alloc(rt, (void**)&rt->x, (size_t)H * 4));
     TRY(dev_alloc(rt, (void**)&rt->x2, (size_t)H * 4));
-    TRY(dev_alloc(rt, (void**)&rt->part, (size_t)H * 4));
+    TRY(dev_alloc(rt, (void**)&rt->part, (size_t)2 * H * 4));   // a reduced partial vector, or the two K halves of the down projection
     TRY(dev_alloc(rt, (void**)&rt->tp_pairs, (size_t)(2 * tp + 2) * 4));
     if (tp > 1) {
         rt->sym_bytes = 4096 + (size_t)2 * tp * H * 4;
@@ -863,6 +874,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     rt->has_model = true;
     rt->use_mega = rt->cfg.use_mega;
     if (const char* e = getenv("LUM_L2_PREFETCH")) rt->l2_prefetch = atoi(e) != 0;
+    if (const char* e = getenv("LUM_DOWN_KSPLIT")) rt->down_ksplit = atoi(e) != 0;
     if (int r = setup_mega(rt)) { free_model(rt); return r; }
     return 0;
 }
