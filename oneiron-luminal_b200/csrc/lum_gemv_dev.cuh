@@ -288,9 +288,9 @@ __device__ __forceinline__ ArgBest argmax_final(const float* part_val, const int
 // Tensor parallel, producing side: called by all `nthreads` threads of every CTA after the kernel's last row has been
 // stored into the ranks' buffers.  The last CTA to arrive tells every rank that this rank's partial vector is complete.
 __device__ __forceinline__ void peer_publish(const GemvArgs& a, int tid, int nthreads, int bar_id) {
-    __threadfence_system();                 // this thread's stores to the other GPUs are ordered before the arrival below
-    named_sync(bar_id, nthreads);
+    named_sync(bar_id, nthreads);           // every thread's stores to the other GPUs are issued ...
     if (tid == 0) {
+        __threadfence_system();             // ... and, through the barrier, ordered before this thread's arrival below (one fence per CTA)
         const unsigned int t = atomicAdd(a.peer_ticket, 1u);
         if (t == gridDim.x - 1) {
             *a.peer_ticket = 0u;
