@@ -20,7 +20,7 @@
 namespace lum {
 
 // One (kv head, split) per CTA.
-template <int HD, int GM, bool BF16>
+template <int HD, int GM, bool BF16, bool CL>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char attn_smem[];
     if (a.use_pdl) pdl_launch_dependents();
@@ -47,39 +47,84 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     const bool ok = p >= 0 && p < a.max_seq;
     if (ok) attn_fill_rope<HD>(a, attn_smem, p, (int)threadIdx.x);
     if (a.use_pdl) pdl_grid_wait();
-    if (!ok) {
+    if (!ok) {                                  // the same for every CTA of the grid: no cluster barrier is left half attended
         if (threadIdx.x == 0) atomicOr(a.status, LUM_ST_BAD_POS);
         return;
     }
-    attn_decode_body<HD, GM, BF16>(a, attn_smem, (int)blockIdx.x, (int)blockIdx.y, p, (int)threadIdx.x, 2, true);
+    attn_decode_body<HD, GM, BF16, CL>(a, attn_smem, (int)blockIdx.x, (int)blockIdx.y, p, (int)threadIdx.x, 2, true);
 }
 
 template <int HD, int GM>
-static const void* attn_fn(bool bf16) { return bf16 ? (const void*)attn_decode<HD, GM, true> : (const void*)attn_decode<HD, GM, false>; }
+static const void* attn_fn(bool bf16, bool cl) {
+    if (cl) return bf16 ? (const void*)attn_decode<HD, GM, true, true> : (const void*)attn_decode<HD, GM, false, true>;
+    return bf16 ? (const void*)attn_decode<HD, GM, true, false> : (const void*)attn_decode<HD, GM, false, false>;
+}
+static const void* attn_fn_for(int hd, int G, bool bf16, bool cl) {
+    if (hd == 128) return G <= 4 ? attn_fn<128, 4>(bf16, cl) : attn_fn<128, 8>(bf16, cl);
+    if (hd == 64) return G <= 4 ? attn_fn<64, 4>(bf16, cl) : attn_fn<64, 8>(bf16, cl);
+    return nullptr;
+}
+
+static void attn_fill_config(const AttnArgs& a, int G, bool cl, cudaStream_t st, cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at) {
+    *cfg = cudaLaunchConfig_t{};
+    cfg->gridDim = dim3(a.n_kv, a.n_splits);
+    cfg->blockDim = dim3(kAttnThreads);
+    cfg->dynamicSmemBytes = attn_smem_bytes(a.hd, G);
+    cfg->stream = st;
+    int n = 0;
+    if (a.use_pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cl) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = 1; at[n].val.clusterDim.y = (unsigned)a.n_splits; at[n].val.clusterDim.z = 1;
+        n++;
+    }
+    cfg->attrs = at;
+    cfg->numAttrs = n;
+}
+
+// Whether the splits of one KV head can run as one thread-block cluster on this device (asked once per shape by the runtime).
+bool attn_cluster_supported(const AttnArgs& a) {
+    const int G = a.n_kv > 0 ? a.n_q / a.n_kv : 0;
+    if (a.n_splits < 2 || a.n_splits > kMaxClusterSplits || G < 1 || G > 8) return false;
+    const void* fn = attn_fn_for(a.hd, G, a.kv_bf16 != 0, true);
+    if (!fn) return false;
+    const size_t smem = attn_smem_bytes(a.hd, G);
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (a.n_splits > 8 && cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { cudaGetLastError(); return false; }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute at[2];
+    AttnArgs b = a;
+    b.use_pdl = 0;
+    attn_fill_config(b, G, true, nullptr, &cfg, at);
+    int n_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, fn, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
+    return n_clusters >= a.n_kv;        // all KV heads' clusters resident at once, like the unclustered grid
+}
 
 cudaError_t launch_attn_decode(const AttnArgs& a_in, cudaStream_t st) {
     AttnArgs a = a_in;
     const int G = a.n_q / a.n_kv;
     if (a.n_kv <= 0 || G < 1 || G > 8 || a.n_q != G * a.n_kv || a.n_splits < 1 || a.n_splits > kMaxSplits) return cudaErrorInvalidValue;
-    const void* fn = nullptr;
-    if (a.hd == 128) fn = G <= 4 ? attn_fn<128, 4>(a.kv_bf16 != 0) : attn_fn<128, 8>(a.kv_bf16 != 0);
-    else if (a.hd == 64) fn = G <= 4 ? attn_fn<64, 4>(a.kv_bf16 != 0) : attn_fn<64, 8>(a.kv_bf16 != 0);
-    else return cudaErrorInvalidValue;
+    const bool cl = a.cluster != 0;
+    if (cl && (a.n_splits < 2 || a.n_splits > kMaxClusterSplits)) return cudaErrorInvalidValue;
+    const void* fn = attn_fn_for(a.hd, G, a.kv_bf16 != 0, cl);
+    if (!fn) return cudaErrorInvalidValue;
     const size_t smem = attn_smem_bytes(a.hd, G);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.n_kv, a.n_splits);
-    cfg.blockDim = dim3(kAttnThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = a.use_pdl ? 1 : 0;
+    if (cl && a.n_splits > 8) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute at[2];
+    attn_fill_config(a, G, cl, st, &cfg, at);
     void* params[] = {&a};
     return cudaLaunchKernelExC(&cfg, fn, params);
 }

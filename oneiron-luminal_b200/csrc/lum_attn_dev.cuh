@@ -64,6 +64,7 @@ constexpr int kAttnWarps = kAttnThreads / 32;
 
 // bytes of shared memory the body needs for G query heads per KV head
 constexpr int kMaxSplits = 32;
+constexpr int kMaxClusterSplits = 16;      // largest cluster the hardware schedules (above 8 the kernel has to opt in)
 __host__ __device__ inline size_t attn_smem_bytes(int HD, int G) {
     return (size_t)(9 * HD + HD + 2 * kAttnWarps * 8 + 4 + HD) * 4 + (size_t)kAttnWarps * G * HD * 4;
 }
@@ -127,7 +128,10 @@ __device__ __forceinline__ void load_dpl(const void* base, size_t elem_off, floa
 // Runs on exactly kAttnThreads threads (tid 0..511) that synchronise on named barrier `bar_id`.
 // p = position of the token being processed (rows [.., p) are cached, row p is this step's own).
 // smem: attn_smem_bytes(HD, G) bytes, 16-byte aligned.
-template <int HD, int GM, bool BF16>
+// CL: the CTAs of one KV head form a thread-block cluster (cluster rank = split, 2 <= n_splits <= kMaxClusterSplits); the
+// splits are then merged through distributed shared memory — every CTA finishes its own slice of the outputs — instead of
+// through global partials and an arrival ticket.
+template <int HD, int GM, bool BF16, bool CL = false>
 __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned char* smem, int kvh, int split, int p, int tid, int bar_id,
                                                  bool rope_ready = false) {
     constexpr int DPL = HD / 32;            // dims per lane
@@ -289,13 +293,65 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
             L = fmaf(s_l[w][g], c, L);
             O = fmaf(s_o[((size_t)w * G + g) * HD + e], c, O);
         }
-        if (a.n_splits == 1) {
+        if (CL) {
+            // q lives in registers by now: the staging area becomes this CTA's [G][HD + 2] result, read by the whole cluster
+            float* dst = (float*)smem + (size_t)g * (HD + 2);
+            dst[e] = O;
+            if (e == 0) { dst[HD] = M; dst[HD + 1] = L; }
+        } else if (a.n_splits == 1) {
             a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);      // no other split to merge with
         } else {
             float* dst = a.part + (((size_t)kvh * a.n_splits + split) * G + g) * (HD + 2);
             dst[e] = O;
             if (e == 0) { dst[HD] = M; dst[HD + 1] = L; }
         }
+    }
+    if (CL) {
+        // The own k row (row G of the staging area) was last read inside the row loop, before the barrier above, so the
+        // writes just made collide with nothing.  Cluster barrier: every split's result is in place.
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        const int S = a.n_splits, total = G * HD;
+        const int chunk = (total + S - 1) / S;          // outputs this CTA finishes: [split * chunk, (split + 1) * chunk)
+        float* t = s_o;                                 // [S][chunk][3] staged (max, sum, out); the per-warp states are spent
+        const uint32_t base = smem_u32(smem);
+#pragma unroll 1
+        for (int idx = tid; idx < S * chunk; idx += kAttnThreads) {
+            const int s = idx / chunk, oi = idx - s * chunk, oidx = split * chunk + oi;
+            if (oidx < total) {
+                const int g = oidx / HD, e = oidx - g * HD;
+                const uint32_t r = cluster_map(base + (uint32_t)(g * (HD + 2)) * 4u, (uint32_t)s);
+                t[idx * 3] = cluster_ld_f32(r + HD * 4u);
+                t[idx * 3 + 1] = cluster_ld_f32(r + (HD + 1) * 4u);
+                t[idx * 3 + 2] = cluster_ld_f32(r + (uint32_t)e * 4u);
+            }
+        }
+        sync();
+        cluster_arrive_release();                       // this CTA has read what it needs from the others
+        if (tid < chunk && split * chunk + tid < total) {
+            // the same folding as the ticket path below — batches of 8 splits into a running (max, sum, out) — so both paths
+            // give the same bits
+            float M = -INFINITY, L = 0.0f, O = 0.0f;
+#pragma unroll 1
+            for (int s0 = 0; s0 < S; s0 += 8) {
+                const int nb = min(8, S - s0);
+                float Mb = M;
+                for (int j = 0; j < nb; j++) Mb = fmaxf(Mb, t[((s0 + j) * chunk + tid) * 3]);
+                const float c0 = (M == -INFINITY) ? 0.0f : expf(M - Mb);
+                L *= c0; O *= c0;
+                for (int j = 0; j < nb; j++) {
+                    const float* v = t + (size_t)((s0 + j) * chunk + tid) * 3;
+                    const float c = (v[0] == -INFINITY) ? 0.0f : expf(v[0] - Mb);
+                    L = fmaf(v[1], c, L);
+                    O = fmaf(v[2], c, O);
+                }
+                M = Mb;
+            }
+            a.out[(size_t)kvh * G * HD + split * chunk + tid] = O * (1.0f / L);
+        }
+        __syncwarp();
+        cluster_wait_acquire();                         // nobody leaves while a neighbour may still read its memory
+        return;
     }
     if (a.n_splits == 1) return;
 

@@ -213,4 +213,20 @@ __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sy
 // arrive without waiting (the waiting side calls named_sync with the same id and total count)
 __device__ __forceinline__ void named_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
+// ---- thread-block cluster: the hardware barrier over all threads of all CTAs of the cluster, and loads from another CTA's
+// shared memory.  Every thread of every CTA must execute each arrive / wait pair, whole warps together.
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// address of this CTA's shared-memory location `smem_addr` as it appears in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
 }  // namespace lum

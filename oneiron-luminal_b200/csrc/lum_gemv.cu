@@ -128,6 +128,7 @@ extern "C" int lum_kstamps_read(unsigned long long* s, unsigned long long* e) {
     int r = (int)cudaMemcpyFromSymbol(s, g_kstart, sizeof(g_kstart));
     return r ? r : (int)cudaMemcpyFromSymbol(e, g_kend, sizeof(g_kend));
 }
+extern "C" int lum_kx_read(unsigned long long* x) { return (int)cudaMemcpyFromSymbol(x, g_kx, sizeof(g_kx)); }
 #endif
 
 __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs a) {
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     __shared__ int s_abort;
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
+    KSTAMP(a, 0);
     GemvSmem g;
     gemv_carve(smem, a.K, a.stages, &s_abort, &g);
     if (tid == 0) GPROBE(0);
@@ -143,6 +145,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
 #endif
     if (tid == 0 && blockIdx.x == 0 && a.job_ctr_zero) *a.job_ctr_zero = 0u;
     const uint32_t tmem = gemv_cta_begin(g, tid, &s_abort);
+    KSTAMP(a, 1);
     if (a.use_pdl) pdl_launch_dependents();
     const GemvPlan plan = gemv_plan(a, (int)gridDim.x, a.job_ctr != nullptr);
 

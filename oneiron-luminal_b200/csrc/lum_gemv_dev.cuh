@@ -45,6 +45,8 @@ static __device__ int g_pphase;
     if (threadIdx.x == 0) { if ((i) == 1) g_pphase++; g_pprobe[(g_pphase & 63) * 8 + (i)] = g_probe[i]; } } } while (0)
 // per-fill timeline of CTA 0 (SM clock): [fill][event]
 static __device__ long long g_tl[64][16];   // one copy per translation unit
+static __device__ unsigned long long g_kx[6][8 * 160];    // per-CTA stamps of the last launch of each projection kind
+#define KSTAMP(a, i) do { if (threadIdx.x == 0) g_kx[i][(((a).epi * 2 + ((a).K > 4096 ? 1 : 0)) & 7) * 160 + blockIdx.x] = globaltimer_ns(); } while (0)
 #ifndef LUM_TL_FIRST
 #define LUM_TL_FIRST 0
 #endif
@@ -52,6 +54,7 @@ static __device__ int g_tl_on = 1;         // a kernel may switch the timeline o
 #define TPROBE(f, e) do { if (blockIdx.x == 0 && g_tl_on && (f) >= LUM_TL_FIRST && (f) < LUM_TL_FIRST + 64) g_tl[(f) - LUM_TL_FIRST][e] = clock64(); } while (0)
 #else
 #define GPROBE(i) do { } while (0)
+#define KSTAMP(a, i) do { } while (0)
 #define TPROBE(f, e) do { } while (0)
 #endif
 
@@ -363,30 +366,73 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         return t;
     };
-    if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
     float4 xv[kXTrips];
+    constexpr int kSmallTrips = 2, kPartBatch = 4;
+    if (n4 <= kSmallTrips * kWorkers && (xs.n_parts > 0 || xs.x_add)) {
+        // A short vector made of several terms (residual stream + partial vectors of the ranks or of the K halves + a plain
+        // addend): few registers per term, so every term's loads are in flight together — one trip to L2 instead of one per
+        // term.  What does not depend on the other ranks is requested before their words are waited for.  The sums are formed
+        // in the same order as below: x, the parts in rank order, the addend.
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 ua[kSmallTrips];
 #pragma unroll
-    for (int it = 0; it < kXTrips; it++) {
-        const int f4 = it * kWorkers + tid;
-        xv[it] = f4 < n4 ? load4(f4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    if (xs.n_parts > 0) {
-        // written by other GPUs into this GPU's memory: read around L1; rank order, so every rank forms the same sums
+        for (int it = 0; it < kXTrips; it++) xv[it] = zero;
+#pragma unroll
+        for (int it = 0; it < kSmallTrips; it++) {
+            const int f4 = it * kWorkers + tid;
+            xv[it] = f4 < n4 ? load4(f4) : zero;
+            ua[it] = (xs.x_add && f4 < n4) ? ((const float4*)xs.x_add)[f4] : zero;
+        }
+        if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
 #pragma unroll 1
-        for (int r = 0; r < xs.n_parts; r++) {
-            const float4* pr = (const float4*)(xs.parts + (size_t)r * xs.part_stride);
+        for (int r0 = 0; r0 < xs.n_parts; r0 += kPartBatch) {
+            float4 u[kPartBatch][kSmallTrips];
 #pragma unroll
-            for (int it = 0; it < kXTrips; it++) {
-                const int f4 = it * kWorkers + tid;
-                if (f4 < n4) { const float4 u = __ldcg(pr + f4); xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+            for (int j = 0; j < kPartBatch; j++) {
+                const float4* pr = (const float4*)(xs.parts + (size_t)(r0 + j) * xs.part_stride);
+#pragma unroll
+                for (int it = 0; it < kSmallTrips; it++) {
+                    const int f4 = it * kWorkers + tid;
+                    u[j][it] = (r0 + j < xs.n_parts && f4 < n4) ? __ldcg(pr + f4) : zero;     // written by other GPUs / CTAs: read around L1
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kPartBatch; j++) {
+                if (r0 + j < xs.n_parts) {
+#pragma unroll
+                    for (int it = 0; it < kSmallTrips; it++) { xv[it].x += u[j][it].x; xv[it].y += u[j][it].y; xv[it].z += u[j][it].z; xv[it].w += u[j][it].w; }
+                }
             }
         }
-    }
-    if (xs.x_add) {
+        if (xs.x_add) {
+#pragma unroll
+            for (int it = 0; it < kSmallTrips; it++) { xv[it].x += ua[it].x; xv[it].y += ua[it].y; xv[it].z += ua[it].z; xv[it].w += ua[it].w; }
+        }
+    } else {
+        if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
 #pragma unroll
         for (int it = 0; it < kXTrips; it++) {
             const int f4 = it * kWorkers + tid;
-            if (f4 < n4) { const float4 u = ((const float4*)xs.x_add)[f4]; xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+            xv[it] = f4 < n4 ? load4(f4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (xs.n_parts > 0) {
+            // written by other GPUs into this GPU's memory: read around L1; rank order, so every rank forms the same sums
+#pragma unroll 1
+            for (int r = 0; r < xs.n_parts; r++) {
+                const float4* pr = (const float4*)(xs.parts + (size_t)r * xs.part_stride);
+#pragma unroll
+                for (int it = 0; it < kXTrips; it++) {
+                    const int f4 = it * kWorkers + tid;
+                    if (f4 < n4) { const float4 u = __ldcg(pr + f4); xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+                }
+            }
+        }
+        if (xs.x_add) {
+#pragma unroll
+            for (int it = 0; it < kXTrips; it++) {
+                const int f4 = it * kWorkers + tid;
+                if (f4 < n4) { const float4 u = ((const float4*)xs.x_add)[f4]; xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+            }
         }
     }
     if (xs.x_out && is_writer) {
@@ -709,6 +755,10 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
     GPROBE(1);
     gemv_quantize_x(a, xs, is_writer, g, tid, gr);
     GPROBE(2);
+    KSTAMP(a, 2);
+#ifdef LUM_PROBE
+    bool kx_first = true;
+#endif
     if (tid >= kConsumers) return;
     const int lane = tid & 31, warp = tid >> 5, wg = warp >> 2, q = warp & 3;
     const int S = g.stages, tpr = p.tpr;
@@ -746,6 +796,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
             if (lane == 0) mbar_arrive(g.tempty0);
 #ifdef LUM_PROBE
             if (pl) TPROBE(pf, 7 + 4 * wg);
+            if (kx_first) { KSTAMP(a, 3); kx_first = false; }
 #endif
             // The stage has landed (the tensor-core warp waited for it); observing its barrier here, complete at the first
             // attempt, makes the bulk copy's bytes and the producer's meta word visible to this thread by the book.
@@ -851,6 +902,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
         named_sync(2, kConsumers);
     }
     GPROBE(7);
+    KSTAMP(a, 4);
     // (The END marker reaches the draining warps through the tensor-core warp, so they cannot finish a phase before it has:
     // the "activations quantised" barrier of the next phase never runs more than one phase ahead of its waiter.)
 }

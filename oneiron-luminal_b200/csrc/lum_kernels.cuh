@@ -115,6 +115,7 @@ struct AttnArgs {
     int max_seq;
     uint32_t* status;
     int use_pdl;
+    int cluster;           // 1: the splits of a KV head run as one thread-block cluster and merge through its shared memory
     // Optional: bytes the NEXT kernels will stream (weights of the o projection, ...).  Attention is latency-bound and leaves
     // HBM idle, so its CTAs ask for these ranges to be brought into L2 meanwhile (a hint: nothing waits for it).
     const void* l2_pf_ptr[2];
@@ -142,6 +143,7 @@ __host__ __device__ inline bool gemv_can_ksplit(int K, int kc) { const int tpr =
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 bool gemv_stream_supported(const GemvArgs& a);
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t st);
+bool attn_cluster_supported(const AttnArgs& a);      // shape fields only: n_q, n_kv, hd, n_splits, kv_bf16
 cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
 // tensor parallel: fold the ranks' {logit bits, row} pairs into the sample (last maximum wins) and advance the state
 cudaError_t launch_tp_pick(const int* pairs, int pair_stride, const uint32_t* flags, const uint32_t* seq, uint32_t tag, uint32_t* status,

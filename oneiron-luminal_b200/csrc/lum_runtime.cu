@@ -121,6 +121,7 @@ struct lum_rt {
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
     bool down_ksplit = true;          // LUM_DOWN_KSPLIT=0: the down projection as one job per row group
+    bool attn_cluster = false;        // the splits of a KV head merge through a thread-block cluster (LUM_ATTN_CLUSTER=1; default: global partials + arrival ticket)
     bool l2_prefetch = false;         // LUM_L2_PREFETCH=1: attention warms L2 with the o projection's weights (measured: no gain)
     unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
@@ -388,6 +389,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
         t.c_inv_d = rt->c_inv_d; t.c_ln_theta = rt->c_ln_theta; t.c_log2e = rt->c_log2e; t.c_half_pi = rt->c_half_pi;
         t.theta = d.rope_theta; t.window = 0; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
+        t.cluster = rt->attn_cluster ? 1 : 0;
         if (rt->l2_prefetch && w.o.kc > 0) {
             t.l2_pf_ptr[0] = w.o.w; t.l2_pf_bytes[0] = q8_packed_bytes((int)w.o.rows, (int)w.o.cols);
         }
@@ -875,6 +877,13 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     rt->use_mega = rt->cfg.use_mega;
     if (const char* e = getenv("LUM_L2_PREFETCH")) rt->l2_prefetch = atoi(e) != 0;
     if (const char* e = getenv("LUM_DOWN_KSPLIT")) rt->down_ksplit = atoi(e) != 0;
+    {
+        bool want = false;        // measured: same tokens/s as the ticket merge, so the plainer launch stays the default
+        if (const char* e = getenv("LUM_ATTN_CLUSTER")) want = atoi(e) != 0;
+        AttnArgs t{};
+        t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits; t.kv_bf16 = d.kv_dtype == LUM_BF16;
+        rt->attn_cluster = want && attn_cluster_supported(t);
+    }
     if (int r = setup_mega(rt)) { free_model(rt); return r; }
     return 0;
 }
@@ -1129,7 +1138,9 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     if (int s = check_status(rt)) return s;
     const double us = (double)ms * 1000.0 / trials;
     if (usec) *usec = us;
-    if (display && display_len) snprintf(display, display_len, "%.3f ms/token", us / 1000.0);
+    if (display && display_len)
+        snprintf(display, display_len, "%.3f ms/token; attention: %d splits per KV head, %s merge", us / 1000.0, rt->n_splits,
+                 rt->n_splits < 2 ? "no" : rt->attn_cluster ? "cluster" : "ticket");
     return 0;
 }
 

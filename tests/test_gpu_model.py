@@ -213,6 +213,29 @@ def test_launch_modes_agree(pkg, rt, graph, pdl, mega):
         other.close()
 
 
+@pytest.mark.parametrize("splits", [2, 5, 8, 16])
+def test_attention_cluster_merge_equals_ticket_merge(pkg, rt, splits, monkeypatch):
+    """The splits of a KV head merged through a thread-block cluster's shared memory (the default wherever a cluster of
+    `splits` CTAs can be scheduled) and merged by the last CTA to arrive from partials in global memory give the same bits,
+    for cluster sizes up to the opt-in maximum of 16 and a split count that leaves the last CTAs without rows."""
+    desc = pkg.CONFIGS["small_q8"]
+    prompt = [9, 4, 511, 2, 2, 300, 41]
+    outs = []
+    for cluster in ("0", "1"):
+        monkeypatch.setenv("LUM_ATTN_CLUSTER", cluster)     # read when the model is loaded
+        other = pkg.B200Runtime.initialize(device=0, attn_splits=splits)
+        try:
+            other.load_model(desc)
+            other.synth(11)
+            toks = other.generate(prompt, 12)
+            outs.append((toks, other.get_f32().copy()))
+            assert ("cluster merge" if cluster == "1" else "ticket merge") in other.profile(2)[1]
+        finally:
+            other.close()
+    assert outs[0][0] == outs[1][0]
+    assert (outs[0][1] == outs[1][1]).all()
+
+
 def test_chunked_prompt_equals_token_by_token(pkg, rt):
     desc = pkg.CONFIGS["small_q8"]
     rt.load_model(desc)
