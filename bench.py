@@ -196,6 +196,43 @@ def kernel_roofline(pkg, torch, peaks, peak_kind):
             "traffic": 135_265_280}, launches + 4
 
 
+def kernel_rows_sweep(pkg, torch):
+    """The dominant kernel alone at K = 4096 over a range of row counts, launched back to back on distinct weights (each
+    set of buffers larger than L2).  Time per launch is close to linear in the rows: the slope is the steady-state cost of
+    one ring fill per CTA (8 tiles = 34816 bytes per SM), the intercept what every launch pays besides streaming."""
+    lib = pkg.load_library()
+    k, sms = 4096, torch.cuda.get_device_properties(0).multi_processor_count
+    x = torch.randn(k, dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rows = []
+    for n in (4096, 8192, 14336, 28672, 57344, 114688):
+        b = lib.lum_q8_0_packed_bytes(n, k)
+        nbuf = max(4, int(600e6 // b) + 1)
+        w = [torch.empty(b, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+        for i in range(nbuf):
+            assert lib.lum_op_synth_q8_0_packed(SEED, 700 + i, n, k, w[i].data_ptr(), None) == 0
+        y = torch.empty(n, dtype=torch.float32, device="cuda")
+        reps, best = 3 * nbuf, None
+        for _ in range(3):
+            for i in range(nbuf):
+                assert lib.lum_op_gemv_q8_0_packed(w[i].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st) == 0
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                lib.lum_op_gemv_q8_0_packed(w[i % nbuf].data_ptr(), n, k, x.data_ptr(), y.data_ptr(), 0, st)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            best = us if best is None else min(best, us)
+        rows.append({"rows": n, "us_per_launch": best, "fills_per_cta": n / 8 / sms, "gb_per_s": b / best / 1e3})
+        del w, y
+        torch.cuda.empty_cache()
+    a, b = rows[-2], rows[-1]
+    slope = (b["us_per_launch"] - a["us_per_launch"]) / (b["fills_per_cta"] - a["fills_per_cta"])
+    return {"kernel": "q8_gemv_stream", "k": k, "rows": rows, "us_per_fill_steady": slope,
+            "steady_gb_per_s": sms * 34816 / slope / 1e3, "fixed_us_per_launch": b["us_per_launch"] - slope * b["fills_per_cta"]}
+
+
 def run_ours(args, pkg):
     import torch
     import torch.distributed as dist
@@ -348,7 +385,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
-    ap.add_argument("--only", default="all", choices=["all", "kernel"], help="kernel: time only the dominant kernel alone (small, for ncu captures)")
+    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep"],
+                    help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
@@ -359,6 +397,11 @@ def main():
         peaks, kind = measured_peaks()
         roof, _ = kernel_roofline(pkg, torch, peaks, kind)
         print(json.dumps({"roofline": roof}))
+        return
+    if args.only == "sweep":
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps({"rows_sweep": kernel_rows_sweep(pkg, torch)}))
         return
     if args.impl == "reference":
         run_reference_arm(args, pkg)
