@@ -233,6 +233,39 @@ def kernel_rows_sweep(pkg, torch):
             "steady_gb_per_s": sms * 34816 / slope / 1e3, "fixed_us_per_launch": b["us_per_launch"] - slope * b["fills_per_cta"]}
 
 
+def launch_chain_floor(pkg, torch):
+    """The decode step of the benchmark's model with every projection shrunk to almost nothing (hidden 512, 4/1 heads of 128,
+    ffn 512, vocabulary 1024; same 32 layers, same launches, same context): what is left is the chain of dependent launches —
+    hand-over between kernels, set-up, activation prologue, first accumulator read-back, epilogue — with no weight streaming
+    to speak of.  Reported beside the full model on the same box."""
+    base = pkg.CONFIGS[WORKLOAD]
+    out = {}
+    for name, d in (("full", base), ("tiny_projections", base.copy(hidden=512, n_q_heads=4, n_kv_heads=1, ffn=512, vocab=1024))):
+        rt = pkg.B200Runtime.initialize(device=0)
+        try:
+            rt.load_model(d)
+            rt.synth(SEED)
+            rt.set_data([i % 1000 + 1 for i in range(512)])
+            rt.execute({"s": 512, "p": 0})
+            rt.decode_greedy(64)
+            rt.synchronize()
+            st = torch.cuda.ExternalStream(rt.stream())
+            best = None
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                rt.decode_greedy(64)
+                e1.record(st)
+                rt.synchronize()
+                us = e0.elapsed_time(e1) / 64 * 1e3
+                best = us if best is None else min(best, us)
+            n = rt.launches_per_step()
+            out[name] = {"us_per_token": best, "launches_per_token": n, "us_per_launch": best / n, "us_per_layer": best / d.n_layers}
+        finally:
+            rt.close()
+    return out
+
+
 def run_ours(args, pkg):
     import torch
     import torch.distributed as dist
@@ -385,8 +418,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
-    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep"],
-                    help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts")
+    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor"],
+                    help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts; floor: the decode step with all projections shrunk away")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
@@ -402,6 +435,11 @@ def main():
         import torch
         torch.cuda.set_device(0)
         print(json.dumps({"rows_sweep": kernel_rows_sweep(pkg, torch)}))
+        return
+    if args.only == "floor":
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps({"launch_chain_floor": launch_chain_floor(pkg, torch)}))
         return
     if args.impl == "reference":
         run_reference_arm(args, pkg)
