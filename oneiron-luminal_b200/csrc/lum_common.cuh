@@ -213,6 +213,34 @@ __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sy
 // arrive without waiting (the waiting side calls named_sync with the same id and total count)
 __device__ __forceinline__ void named_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
+// ---- value + completion word in one 8-byte store (the scheme of NCCL's LL protocol): an aligned 8-byte store reaches the
+// other GPU's memory whole, so a reader that finds the expected word beside a value has the value — no fence, no flag trip.
+__device__ __forceinline__ void st_ll(uint2* p, uint32_t bits, uint32_t word) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(word) : "memory");
+}
+__device__ __forceinline__ uint2 ld_ll(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// two consecutive elements (16-byte aligned): {bits0, word0, bits1, word1}
+__device__ __forceinline__ uint4 ld_ll2(const uint2* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// One element, waited for (bounded): returns false when the word never came.
+__device__ __forceinline__ bool ld_ll_wait(const uint2* p, uint32_t word, float* out) {
+    const long long t0 = clock64();
+    unsigned int spins = 0;
+    for (;;) {
+        const uint2 v = ld_ll(p);
+        if (v.y == word) { *out = __uint_as_float(v.x); return true; }
+        if ((++spins & 63u) == 0 && clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) { *out = 0.0f; return false; }
+        __nanosleep(40);
+    }
+}
+
 // ---- thread-block cluster: the hardware barrier over all threads of all CTAs of the cluster, and loads from another CTA's
 // shared memory.  Every thread of every CTA must execute each arrive / wait pair, whole warps together.
 __device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }

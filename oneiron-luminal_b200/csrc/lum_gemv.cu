@@ -95,7 +95,15 @@ __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, int ti
     for (int k = tid; k < K; k += nthreads) {
         float v = a.x[k];
         if (a.x_add) v += a.x_add[k];
-        for (int r = 0; r < a.n_parts; r++) v += __ldcg(a.parts + (size_t)r * a.part_stride + k);
+        for (int r = 0; r < a.n_parts; r++) {
+            if (a.parts_ll) {
+                float u;
+                if (!ld_ll_wait((const uint2*)a.parts + (size_t)r * a.part_stride + k, peer_word(__ldcg(a.seq), a.parts_tag), &u)) atomicOr(a.status, LUM_ST_WAIT_PEER);
+                v += u;
+            } else {
+                v += __ldcg(a.parts + (size_t)r * a.part_stride + k);
+            }
+        }
         if ((a.x_add || a.n_parts > 0) && a.x_out && blockIdx.x == 0) a.x_out[k] = v;
         xs[k] = v;
         ss = fmaf(v, v, ss);
@@ -174,13 +182,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
 #endif
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
-    xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq;
+    xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq; xs.parts_ll = a.parts_ll;
     ArgBest best{-INFINITY, -1};
     ConsumerRing cr{0, 0u, 0u, 0u, 0};
     gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
     if (tid >= kConsumers) return;
     gemv_consumers_done();
-    if (a.epi == EPI_PEER) peer_publish(a, tid, kConsumers, 2);
+    if (a.epi == EPI_PEER && !a.peer_ll) peer_publish(a, tid, kConsumers, 2);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
     GPROBE(4);
 #ifdef LUM_PROBE
@@ -279,7 +287,7 @@ __global__ void __launch_bounds__(256) gemv_direct(const GemvArgs a) {
     ArgBest best{-INFINITY, -1};
     gemv_epilogue_rows(a, vals, row0, n, tid, 256, scratch, 1, &best);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, 256, 1);
-    if (a.epi == EPI_PEER) peer_publish(a, tid, 256, 1);
+    if (a.epi == EPI_PEER && !a.peer_ll) peer_publish(a, tid, 256, 1);
 }
 
 // ------------------------------------------------------------------------------ host side

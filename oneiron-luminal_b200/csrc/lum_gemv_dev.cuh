@@ -204,9 +204,16 @@ __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const flo
         for (int i = tid; i < n; i += nthreads) {
             const int row = unit_of[i >> 3] * kTileRows + (i & 7);
             const float v = vals[i];
+            if (a.peer_ll) {
+                const uint32_t word = peer_word(__ldcg(a.seq), a.peer_tag);
 #pragma unroll
-            for (int r = 0; r < kMaxPeers; r++)
-                if (r < a.n_peers) a.peer_out[r][row] = v;
+                for (int r = 0; r < kMaxPeers; r++)
+                    if (r < a.n_peers) st_ll((uint2*)a.peer_out[r] + row, __float_as_uint(v), word);
+            } else {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; r++)
+                    if (r < a.n_peers) a.peer_out[r][row] = v;
+            }
         }
     } else {  // EPI_ARGMAX
         ArgBest b{-INFINITY, -1};
@@ -246,9 +253,16 @@ __device__ __forceinline__ void gemv_epilogue_rows(const GemvArgs& a, const floa
     } else if (a.epi == EPI_PEER) {
         for (int i = tid; i < n; i += nthreads) {
             const float v = vals[i];
+            if (a.peer_ll) {
+                const uint32_t word = peer_word(__ldcg(a.seq), a.peer_tag);
 #pragma unroll
-            for (int r = 0; r < kMaxPeers; r++)
-                if (r < a.n_peers) a.peer_out[r][row0 + i] = v;
+                for (int r = 0; r < kMaxPeers; r++)
+                    if (r < a.n_peers) st_ll((uint2*)a.peer_out[r] + row0 + i, __float_as_uint(v), word);
+            } else {
+#pragma unroll
+                for (int r = 0; r < kMaxPeers; r++)
+                    if (r < a.n_peers) a.peer_out[r][row0 + i] = v;
+            }
         }
     } else {  // EPI_ARGMAX
         ArgBest b{-INFINITY, -1};
@@ -328,7 +342,22 @@ struct XSource {
     int n_parts, part_stride;
     uint32_t parts_tag;
     const uint32_t* seq;
+    int parts_ll;          // parts are {value bits, completion word} pairs, each waited for on its own word
 };
+
+// Four consecutive elements of a partial vector stored as {bits, word} pairs: both 16-byte loads are issued at once; an element
+// whose word has not arrived yet is then waited for on its own (bounded).
+__device__ __forceinline__ float4 ll_load4(const uint2* p, uint32_t word, uint32_t* status) {
+    const uint4 a = ld_ll2(p), b = ld_ll2(p + 2);
+    float4 v = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+    bool ok = true;
+    if (a.y != word) ok &= ld_ll_wait(p, word, &v.x);
+    if (a.w != word) ok &= ld_ll_wait(p + 1, word, &v.y);
+    if (b.y != word) ok &= ld_ll_wait(p + 2, word, &v.z);
+    if (b.w != word) ok &= ld_ll_wait(p + 3, word, &v.w);
+    if (!ok) atomicOr(status, LUM_ST_WAIT_PEER);
+    return v;
+}
 
 // The RMSNorm gains do not depend on the previous operation, so a kernel can fetch them while it still waits for its
 // grid dependency: thread tid keeps the gains of the elements it will quantise (trip it: float4 number it * kWorkers + tid).
@@ -384,6 +413,41 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             ua[it] = (xs.x_add && f4 < n4) ? ((const float4*)xs.x_add)[f4] : zero;
         }
         if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
+        if (xs.parts_ll) {
+            // every element carries its own completion word: all loads of two ranks' vectors go out together, stragglers are
+            // waited for one by one
+            const uint32_t word = peer_word(__ldcg(xs.seq), xs.parts_tag);
+#pragma unroll 1
+            for (int r0 = 0; r0 < xs.n_parts; r0 += 2) {
+                uint4 raw[2][kSmallTrips][2];
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const uint2* pr = (const uint2*)xs.parts + (size_t)min(r0 + j, xs.n_parts - 1) * xs.part_stride;
+#pragma unroll
+                    for (int it = 0; it < kSmallTrips; it++) {
+                        const int f4 = min(it * kWorkers + tid, n4 - 1);
+                        raw[j][it][0] = ld_ll2(pr + 4 * f4);
+                        raw[j][it][1] = ld_ll2(pr + 4 * f4 + 2);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    if (r0 + j < xs.n_parts) {
+                        const uint2* pr = (const uint2*)xs.parts + (size_t)(r0 + j) * xs.part_stride;
+#pragma unroll
+                        for (int it = 0; it < kSmallTrips; it++) {
+                            const int f4 = it * kWorkers + tid;
+                            if (f4 < n4) {
+                                const uint4 a4 = raw[j][it][0], b4 = raw[j][it][1];
+                                float4 v = make_float4(__uint_as_float(a4.x), __uint_as_float(a4.z), __uint_as_float(b4.x), __uint_as_float(b4.z));
+                                if (a4.y != word || a4.w != word || b4.y != word || b4.w != word) v = ll_load4(pr + 4 * f4, word, a.status);
+                                xv[it].x += v.x; xv[it].y += v.y; xv[it].z += v.z; xv[it].w += v.w;
+                            }
+                        }
+                    }
+                }
+            }
+        } else {
 #pragma unroll 1
         for (int r0 = 0; r0 < xs.n_parts; r0 += kPartBatch) {
             float4 u[kPartBatch][kSmallTrips];
@@ -404,6 +468,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
                 }
             }
         }
+        }
         if (xs.x_add) {
 #pragma unroll
             for (int it = 0; it < kSmallTrips; it++) { xv[it].x += ua[it].x; xv[it].y += ua[it].y; xv[it].z += ua[it].z; xv[it].w += ua[it].w; }
@@ -423,7 +488,11 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
 #pragma unroll
                 for (int it = 0; it < kXTrips; it++) {
                     const int f4 = it * kWorkers + tid;
-                    if (f4 < n4) { const float4 u = __ldcg(pr + f4); xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
+                    if (f4 < n4) {
+                        const float4 u = xs.parts_ll ? ll_load4((const uint2*)xs.parts + (size_t)r * xs.part_stride + 4 * f4, peer_word(__ldcg(xs.seq), xs.parts_tag), a.status)
+                                                     : __ldcg(pr + f4);
+                        xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w;
+                    }
                 }
             }
         }

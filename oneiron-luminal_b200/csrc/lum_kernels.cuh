@@ -78,6 +78,8 @@ struct GemvArgs {
     // Tensor parallel without a collective kernel.  Producing side (EPI_PEER): peer_out[r] is rank r's buffer for THIS rank's
     // partial vector (r == own rank included), peer_flag[r] the word in rank r's memory that says it is complete.
     float* peer_out[kMaxPeers];
+    int peer_ll;                  // 1: peer_out[r] is an array of {value bits, completion word} pairs (8 bytes per row); nothing else is published
+    int parts_ll;                 // 1: `parts` is such an array (part_stride in elements); every element is waited for on its own word
     uint32_t* peer_flag[kMaxPeers];
     int n_peers;
     unsigned int* peer_ticket;    // local arrival counter of the producing kernel's CTAs, left at 0

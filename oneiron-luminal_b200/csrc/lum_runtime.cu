@@ -338,19 +338,20 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
     int pending_buf = 0;
     bool pending_halves = false;
     auto sym_flag = [&](unsigned char* base, int buf, int rank) { return (uint32_t*)(base + ((size_t)buf * kMaxPeers + rank) * 128); };
-    auto sym_part = [&](unsigned char* base, int buf, int rank) { return (float*)(base + 4096) + ((size_t)buf * rt->tp_size + rank) * H; };
+    // partial vectors as {value bits, completion word} pairs: 8 bytes per element
+    auto sym_part = [&](unsigned char* base, int buf, int rank) { return (float*)(base + 4096) + ((size_t)buf * rt->tp_size + rank) * H * 2; };
     auto publish_to_peers = [&](GemvArgs& g, int buf, uint32_t tag) {
         g.epi = EPI_PEER; g.y = nullptr;
         g.n_peers = rt->tp_size;
         for (int r = 0; r < rt->tp_size; r++) { g.peer_out[r] = sym_part(rt->peer_sym[r], buf, rt->tp_rank); g.peer_flag[r] = sym_flag(rt->peer_sym[r], buf, rt->tp_rank); }
-        g.peer_ticket = rt->peer_ticket; g.seq = rt->tp_seq; g.peer_tag = tag;
+        g.peer_ticket = rt->peer_ticket; g.seq = rt->tp_seq; g.peer_tag = tag; g.peer_ll = 1;
         pending = true; pending_tag = tag; pending_buf = buf;
     };
     auto take_partial = [&](GemvArgs& g) {   // the projection's prologue folds the reduced partial into the stream
         g.x = cur;
         if (!pending) return;
         if (fused) {
-            g.parts = sym_part(rt->sym, pending_buf, 0); g.part_flags = sym_flag(rt->sym, pending_buf, 0);
+            g.parts = sym_part(rt->sym, pending_buf, 0); g.part_flags = nullptr; g.parts_ll = 1;    // each element carries its own completion word
             g.n_parts = rt->tp_size; g.part_stride = H; g.parts_tag = pending_tag; g.seq = rt->tp_seq;
         } else if (pending_halves) {
             g.parts = rt->part; g.n_parts = 2; g.part_stride = H;      // the two K halves of the down projection (same GPU: no words to wait for)
@@ -835,7 +836,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     TRY(dev_alloc(rt, (void**)&rt->part, (size_t)2 * H * 4));   // a reduced partial vector, or the two K halves of the down projection
     TRY(dev_alloc(rt, (void**)&rt->tp_pairs, (size_t)(2 * tp + 2) * 4));
     if (tp > 1) {
-        rt->sym_bytes = 4096 + (size_t)2 * tp * H * 4;
+        rt->sym_bytes = 4096 + (size_t)2 * tp * H * 8;
         TRY(dev_alloc(rt, (void**)&rt->sym, rt->sym_bytes));
         TRY(dev_alloc(rt, (void**)&rt->tp_seq, 4));
         TRY(dev_alloc(rt, (void**)&rt->peer_ticket, 4));
