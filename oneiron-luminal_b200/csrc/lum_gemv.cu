@@ -139,6 +139,7 @@ extern "C" int lum_kstamps_read(unsigned long long* s, unsigned long long* e) {
 extern "C" int lum_kx_read(unsigned long long* x) { return (int)cudaMemcpyFromSymbol(x, g_kx, sizeof(g_kx)); }
 #endif
 
+template <bool PEER>
 __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_abort;
@@ -185,10 +186,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq; xs.parts_ll = a.parts_ll;
     ArgBest best{-INFINITY, -1};
     ConsumerRing cr{0, 0u, 0u, 0u, 0};
-    gemv_consume(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
+    gemv_consume<PEER>(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
     if (tid >= kConsumers) return;
     gemv_consumers_done();
-    if (a.epi == EPI_PEER && !a.peer_ll) peer_publish(a, tid, kConsumers, 2);
+    if (PEER && a.epi == EPI_PEER && !a.peer_ll) peer_publish(a, tid, kConsumers, 2);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
     GPROBE(4);
 #ifdef LUM_PROBE
@@ -358,14 +359,17 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
         if (stages < 2) stages = 2;
         a.stages = stages;
         const size_t smem = fixed + (size_t)stages * kFillBytes;
-        static size_t attr_set = 0;
-        if (smem > attr_set) {
-            cudaError_t e = cudaFuncSetAttribute(q8_gemv_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));
+        // two instantiations: with and without the tensor-parallel paths (partial vectors of other ranks in, peer stores out)
+        const bool peer = a.n_peers > 0 || a.parts_ll || a.part_flags != nullptr || a.epi == EPI_PEER;
+        const void* fn = peer ? (const void*)q8_gemv_stream<true> : (const void*)q8_gemv_stream<false>;
+        static bool attr_set[2] = {false, false};
+        if (!attr_set[peer ? 1 : 0]) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));
             if (e != cudaSuccess) return e;
-            attr_set = 226 * 1024;
+            attr_set[peer ? 1 : 0] = true;
         }
         if (smem > 226 * 1024) return cudaErrorInvalidValue;
-        return launch_with_attrs((const void*)q8_gemv_stream, dim3(grid), dim3(kGemvThreads), smem, st, a.use_pdl != 0, a);
+        return launch_with_attrs(fn, dim3(grid), dim3(kGemvThreads), smem, st, a.use_pdl != 0, a);
     }
 
     if (a.ksplit == 2) return cudaErrorInvalidValue;     // the caller's consumer expects two partial vectors: only the streaming kernel makes them

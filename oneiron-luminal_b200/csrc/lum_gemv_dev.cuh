@@ -184,6 +184,9 @@ __device__ __forceinline__ void argbest_take(ArgBest& b, float ov, int oi) {
 // sums at vals[s*8 ..].  Plain phases: row group ids count over the concatenated segments.  SwiGLU phases: gate slots carry
 // the slot of the matching up rows in pair_of[s] (up slots carry -1) and only they produce output.
 // For EPI_ARGMAX the rows are stored and thread 0 folds the chunk's best into *best.
+// PEER = false compiles the tensor-parallel paths out: the kernel's code size is latency (it has to stay well inside the
+// instruction cache: measured, 100 KB -> 135 KB of code cost 12 % tokens/s on one GPU).
+template <bool PEER = false>
 __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const float* vals, const int* unit_of, const int* pair_of, int n_slots,
                                                     int tid, int nthreads, float* scratch, int bar_id, ArgBest* best) {
     const int n = n_slots * kTileRows;
@@ -200,7 +203,7 @@ __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const flo
         }
     } else if (a.epi == EPI_RESID) {
         for (int i = tid; i < n; i += nthreads) { const int row = unit_of[i >> 3] * kTileRows + (i & 7); a.y[row] = a.resid[row] + vals[i]; }
-    } else if (a.epi == EPI_PEER) {
+    } else if (PEER && a.epi == EPI_PEER) {
         for (int i = tid; i < n; i += nthreads) {
             const int row = unit_of[i >> 3] * kTileRows + (i & 7);
             const float v = vals[i];
@@ -347,7 +350,7 @@ struct XSource {
 
 // Four consecutive elements of a partial vector stored as {bits, word} pairs: both 16-byte loads are issued at once; an element
 // whose word has not arrived yet is then waited for on its own (bounded).
-__device__ __forceinline__ float4 ll_load4(const uint2* p, uint32_t word, uint32_t* status) {
+static __device__ __noinline__ float4 ll_load4(const uint2* p, uint32_t word, uint32_t* status) {   // out of line: the kernel's code size is latency
     const uint4 a = ld_ll2(p), b = ld_ll2(p + 2);
     float4 v = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
     bool ok = true;
@@ -380,6 +383,7 @@ __device__ __forceinline__ void gemv_gain_preload(const GemvArgs& a, int tid, Ga
 // Runs on all kWorkers threads; 8 consecutive threads own one block.  Every thread first issues all of its loads (the
 // vector sits in L2, a microsecond away: one round trip, not one per trip), keeps them in registers for both passes, and
 // ends with the writes published to the tensor core (xready) and to the other workers (named barrier 1).
+template <bool PEER = false>
 __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvSmem& g, int tid, const GainRegs& gr) {
     const int K = a.K, n4 = K >> 2;
     auto load4 = [&](int f4) -> float4 {
@@ -412,8 +416,8 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             xv[it] = f4 < n4 ? load4(f4) : zero;
             ua[it] = (xs.x_add && f4 < n4) ? ((const float4*)xs.x_add)[f4] : zero;
         }
-        if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
-        if (xs.parts_ll) {
+        if (PEER && xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
+        if (PEER && xs.parts_ll) {
             // every element carries its own completion word: all loads of two ranks' vectors go out together, stragglers are
             // waited for one by one
             const uint32_t word = peer_word(__ldcg(xs.seq), xs.parts_tag);
@@ -474,7 +478,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             for (int it = 0; it < kSmallTrips; it++) { xv[it].x += ua[it].x; xv[it].y += ua[it].y; xv[it].z += ua[it].z; xv[it].w += ua[it].w; }
         }
     } else {
-        if (xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
+        if (PEER && xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
 #pragma unroll
         for (int it = 0; it < kXTrips; it++) {
             const int f4 = it * kWorkers + tid;
@@ -489,7 +493,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
                 for (int it = 0; it < kXTrips; it++) {
                     const int f4 = it * kWorkers + tid;
                     if (f4 < n4) {
-                        const float4 u = xs.parts_ll ? ll_load4((const uint2*)xs.parts + (size_t)r * xs.part_stride + 4 * f4, peer_word(__ldcg(xs.seq), xs.parts_tag), a.status)
+                        const float4 u = (PEER && xs.parts_ll) ? ll_load4((const uint2*)xs.parts + (size_t)r * xs.part_stride + 4 * f4, peer_word(__ldcg(xs.seq), xs.parts_tag), a.status)
                                                      : __ldcg(pr + f4);
                         xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w;
                     }
@@ -819,10 +823,11 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
 // products, turns them into the block's f32 contribution and adds up its tiles; per fill and row group the 4 block-lanes
 // of a warp that share a row are folded with two shuffles and the 8 warps' partials are summed in a fixed order at the
 // end of a chunk, followed by the epilogue.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
+template <bool PEER = false>
 __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvPlan& p, const GemvSmem& g,
                                              ConsumerRing& cr, int tid, uint32_t tmem, uint32_t* status, ArgBest* best, const GainRegs& gr) {
     GPROBE(1);
-    gemv_quantize_x(a, xs, is_writer, g, tid, gr);
+    gemv_quantize_x<PEER>(a, xs, is_writer, g, tid, gr);
     GPROBE(2);
     KSTAMP(a, 2);
 #ifdef LUM_PROBE
@@ -967,7 +972,7 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
             g.vals[i] = t;
         }
         named_sync(2, kConsumers);
-        if (slot > 0) gemv_epilogue_units(a, g.vals, g.unit_of, g.pair_of, slot, tid, kConsumers, g.scratch, 2, best);
+        if (slot > 0) gemv_epilogue_units<PEER>(a, g.vals, g.unit_of, g.pair_of, slot, tid, kConsumers, g.scratch, 2, best);
         named_sync(2, kConsumers);
     }
     GPROBE(7);

@@ -121,7 +121,7 @@ struct lum_rt {
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
     bool down_ksplit = true;          // LUM_DOWN_KSPLIT=0: the down projection as one job per row group
-    bool attn_cluster = false;        // the splits of a KV head merge through a thread-block cluster (LUM_ATTN_CLUSTER=1; default: global partials + arrival ticket)
+    bool attn_cluster = false;        // the splits of a KV head merge through a thread-block cluster (LUM_ATTN_CLUSTER=0: global partials + arrival ticket)
     bool l2_prefetch = false;         // LUM_L2_PREFETCH=1: attention warms L2 with the o projection's weights (measured: no gain)
     unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
@@ -820,12 +820,13 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     }
     int splits = rt->cfg.attn_splits;
     if (splits <= 0) {
-        // as many splits of the cached rows as there are SMs per KV head, at most 32 — rounded down to a multiple of 8, the
-        // number of partials the merging CTA fetches per trip (18 splits cost it a third trip for two partials; measured
-        // 16 splits: +1.3 % tokens/s over 18)
+        // as many splits of the cached rows as there are SMs per KV head, at most 16 — the largest thread-block cluster, so
+        // that the splits of a KV head can merge through the cluster's shared memory — and a multiple of 8, the number of
+        // partials folded per trip (measured, 8 KV heads: 16 splits +1.3 % tokens/s over 18; 4 KV heads per rank on two GPUs:
+        // 16 splits 500 tokens/s, 24: 496, 32: 492, 8: 489)
         splits = rt->sm_count / (rt->nkv_l > 0 ? rt->nkv_l : 1);
         if (splits < 1) splits = 1;
-        if (splits > 32) splits = 32;
+        if (splits > 16) splits = 16;
         if (splits > 8) splits &= ~7;
     }
     if (splits > 32) splits = 32;       // the merge holds one partial per split in registers
@@ -879,7 +880,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (const char* e = getenv("LUM_L2_PREFETCH")) rt->l2_prefetch = atoi(e) != 0;
     if (const char* e = getenv("LUM_DOWN_KSPLIT")) rt->down_ksplit = atoi(e) != 0;
     {
-        bool want = false;        // measured: same tokens/s as the ticket merge, so the plainer launch stays the default
+        bool want = true;         // measured: same tokens/s as the ticket merge with 8 KV heads on one GPU, +2.5 % with 4 per rank on two
         if (const char* e = getenv("LUM_ATTN_CLUSTER")) want = atoi(e) != 0;
         AttnArgs t{};
         t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits; t.kv_bf16 = d.kv_dtype == LUM_BF16;
