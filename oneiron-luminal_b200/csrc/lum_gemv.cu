@@ -139,8 +139,10 @@ extern "C" int lum_kstamps_read(unsigned long long* s, unsigned long long* e) {
 extern "C" int lum_kx_read(unsigned long long* x) { return (int)cudaMemcpyFromSymbol(x, g_kx, sizeof(g_kx)); }
 #endif
 
-template <bool PEER>
+// WIDE: K above 4096 (up to 16384): the prologue then holds up to eight float4 per thread instead of two.
+template <bool PEER, bool WIDE>
 __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs a) {
+    constexpr int TRIPS = WIDE ? kXTrips : 2;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_abort;
     const int tid = threadIdx.x;
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
         return;
     }
     GainRegs gr;
-    gemv_gain_preload(a, tid, gr);             // independent of the previous kernel: fetched while waiting for it
+    gemv_gain_preload<TRIPS>(a, tid, gr);      // independent of the previous kernel: fetched while waiting for it
     if (a.use_pdl) pdl_grid_wait();
 #ifdef LUM_PROBE
     if (tid == 0) g_kstart[(g_klaunch_of(a) & 7) * 160 + blockIdx.x] = globaltimer_ns();
@@ -186,7 +188,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq; xs.parts_ll = a.parts_ll;
     ArgBest best{-INFINITY, -1};
     ConsumerRing cr{0, 0u, 0u, 0u, 0};
-    gemv_consume<PEER>(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
+    gemv_consume<PEER, TRIPS>(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
     if (tid >= kConsumers) return;
     gemv_consumers_done();
     if (PEER && a.epi == EPI_PEER && !a.peer_ll) peer_publish(a, tid, kConsumers, 2);
@@ -361,12 +363,19 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
         const size_t smem = fixed + (size_t)stages * kFillBytes;
         // two instantiations: with and without the tensor-parallel paths (partial vectors of other ranks in, peer stores out)
         const bool peer = a.n_peers > 0 || a.parts_ll || a.part_flags != nullptr || a.epi == EPI_PEER;
-        const void* fn = peer ? (const void*)q8_gemv_stream<true> : (const void*)q8_gemv_stream<false>;
-        static bool attr_set[2] = {false, false};
-        if (!attr_set[peer ? 1 : 0]) {
+        // One instantiation serves every K: alternating between a narrow and a wide kernel costs more in instruction-cache
+        // misses than the narrow one saves (measured: 415 against 439 tokens/s); the narrow one stays for models whose
+        // every projection is short.
+        static const int env_narrow = [] { const char* e = getenv("LUM_GEMV_NARROW"); return e ? atoi(e) : 0; }();
+        const bool wide = env_narrow == 0 || a.K > 2 * kWorkers * 4;      // more than two float4 per worker thread
+        const void* fn = peer ? (wide ? (const void*)q8_gemv_stream<true, true> : (const void*)q8_gemv_stream<true, false>)
+                              : (wide ? (const void*)q8_gemv_stream<false, true> : (const void*)q8_gemv_stream<false, false>);
+        static bool attr_set[4] = {false, false, false, false};
+        const int which = (peer ? 2 : 0) + (wide ? 1 : 0);
+        if (!attr_set[which]) {
             cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));
             if (e != cudaSuccess) return e;
-            attr_set[peer ? 1 : 0] = true;
+            attr_set[which] = true;
         }
         if (smem > 226 * 1024) return cudaErrorInvalidValue;
         return launch_with_attrs(fn, dim3(grid), dim3(kGemvThreads), smem, st, a.use_pdl != 0, a);

@@ -366,12 +366,13 @@ static __device__ __noinline__ float4 ll_load4(const uint2* p, uint32_t word, ui
 // grid dependency: thread tid keeps the gains of the elements it will quantise (trip it: float4 number it * kWorkers + tid).
 constexpr int kXTrips = 8;                  // K <= 16384: at most 8 float4 per worker thread
 struct GainRegs { uint2 b[kXTrips]; bool loaded; };
+template <int TRIPS = kXTrips>
 __device__ __forceinline__ void gemv_gain_preload(const GemvArgs& a, int tid, GainRegs& gr) {
     gr.loaded = a.gain != nullptr && a.gain_kind == WK_BF16;
     if (!gr.loaded) return;
     const int n4 = a.K >> 2;
 #pragma unroll
-    for (int it = 0; it < kXTrips; it++) {
+    for (int it = 0; it < TRIPS; it++) {
         const int f4 = it * kWorkers + tid;
         gr.b[it] = f4 < n4 ? ((const uint2*)a.gain)[f4] : make_uint2(0u, 0u);
     }
@@ -383,7 +384,9 @@ __device__ __forceinline__ void gemv_gain_preload(const GemvArgs& a, int tid, Ga
 // Runs on all kWorkers threads; 8 consecutive threads own one block.  Every thread first issues all of its loads (the
 // vector sits in L2, a microsecond away: one round trip, not one per trip), keeps them in registers for both passes, and
 // ends with the writes published to the tensor core (xready) and to the other workers (named barrier 1).
-template <bool PEER = false>
+// TRIPS: float4 loads per worker thread the code is built for (K <= 2048 * TRIPS): a kernel for short vectors carries a
+// quarter of the prologue's code.
+template <bool PEER = false, int TRIPS = kXTrips>
 __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvSmem& g, int tid, const GainRegs& gr) {
     const int K = a.K, n4 = K >> 2;
     auto load4 = [&](int f4) -> float4 {
@@ -399,7 +402,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         return t;
     };
-    float4 xv[kXTrips];
+    float4 xv[TRIPS];
     constexpr int kSmallTrips = 2, kPartBatch = 4;
     if (n4 <= kSmallTrips * kWorkers && (xs.n_parts > 0 || xs.x_add)) {
         // A short vector made of several terms (residual stream + partial vectors of the ranks or of the K halves + a plain
@@ -409,7 +412,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
         float4 ua[kSmallTrips];
 #pragma unroll
-        for (int it = 0; it < kXTrips; it++) xv[it] = zero;
+        for (int it = 0; it < TRIPS; it++) xv[it] = zero;
 #pragma unroll
         for (int it = 0; it < kSmallTrips; it++) {
             const int f4 = it * kWorkers + tid;
@@ -480,7 +483,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
     } else {
         if (PEER && xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
 #pragma unroll
-        for (int it = 0; it < kXTrips; it++) {
+        for (int it = 0; it < TRIPS; it++) {
             const int f4 = it * kWorkers + tid;
             xv[it] = f4 < n4 ? load4(f4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -490,7 +493,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             for (int r = 0; r < xs.n_parts; r++) {
                 const float4* pr = (const float4*)(xs.parts + (size_t)r * xs.part_stride);
 #pragma unroll
-                for (int it = 0; it < kXTrips; it++) {
+                for (int it = 0; it < TRIPS; it++) {
                     const int f4 = it * kWorkers + tid;
                     if (f4 < n4) {
                         const float4 u = (PEER && xs.parts_ll) ? ll_load4((const uint2*)xs.parts + (size_t)r * xs.part_stride + 4 * f4, peer_word(__ldcg(xs.seq), xs.parts_tag), a.status)
@@ -502,7 +505,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         if (xs.x_add) {
 #pragma unroll
-            for (int it = 0; it < kXTrips; it++) {
+            for (int it = 0; it < TRIPS; it++) {
                 const int f4 = it * kWorkers + tid;
                 if (f4 < n4) { const float4 u = ((const float4*)xs.x_add)[f4]; xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w; }
             }
@@ -510,7 +513,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
     }
     if (xs.x_out && is_writer) {
 #pragma unroll
-        for (int it = 0; it < kXTrips; it++) {
+        for (int it = 0; it < TRIPS; it++) {
             const int f4 = it * kWorkers + tid;
             if (f4 < n4) ((float4*)xs.x_out)[f4] = xv[it];
         }
@@ -519,7 +522,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
     if (a.gain) {
         float ss = 0.0f;
 #pragma unroll
-        for (int it = 0; it < kXTrips; it++) {      // absent trips hold zeros
+        for (int it = 0; it < TRIPS; it++) {      // absent trips hold zeros
             const float4 t = xv[it];
             ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
         }
@@ -529,16 +532,25 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
     }
     // all threads run every trip so the 8-lane shuffles always have their partners (K is a multiple of 32: a block never
     // straddles the end); trips past the end of the vector are skipped as a whole warp
+    // The loop is unrolled by two only — the kernel's code size is latency (measured: the decode step of a model with tiny
+    // projections takes 961 us with this loop rolled against 1226 us with all eight trips unrolled; on the Llama-3-8B shape
+    // rolled 437.6, by two 442.2, by eight 439 tokens/s) — and picks its trip's registers with selects, so the loaded values
+    // never leave the register file.
     const int trips = (n4 + kWorkers - 1) / kWorkers;
-#pragma unroll
-    for (int it = 0; it < kXTrips; it++) {
+#pragma unroll 2
+    for (int it = 0; it < TRIPS; it++) {
         if (it < trips) {
             const int f4 = it * kWorkers + tid;
             const bool in = f4 < n4;
-            float e[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
+            float4 cur = xv[0];
+            uint2 gb = gr.b[0];
+#pragma unroll
+            for (int k = 1; k < TRIPS; k++) {
+                if (it == k) { cur = xv[k]; gb = gr.b[k]; }
+            }
+            float e[4] = {cur.x, cur.y, cur.z, cur.w};
             if (a.gain && in) {
                 if (gr.loaded) {
-                    const uint2 gb = gr.b[it];
                     e[0] = (inv * e[0]) * __uint_as_float(gb.x << 16); e[1] = (inv * e[1]) * __uint_as_float(gb.x & 0xffff0000u);
                     e[2] = (inv * e[2]) * __uint_as_float(gb.y << 16); e[3] = (inv * e[3]) * __uint_as_float(gb.y & 0xffff0000u);
                 } else {
@@ -823,11 +835,11 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
 // products, turns them into the block's f32 contribution and adds up its tiles; per fill and row group the 4 block-lanes
 // of a warp that share a row are folded with two shuffles and the 8 warps' partials are summed in a fixed order at the
 // end of a chunk, followed by the epilogue.  For EPI_ARGMAX, *best (thread 0) receives this CTA's best row.
-template <bool PEER = false>
+template <bool PEER = false, int TRIPS = kXTrips>
 __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvPlan& p, const GemvSmem& g,
                                              ConsumerRing& cr, int tid, uint32_t tmem, uint32_t* status, ArgBest* best, const GainRegs& gr) {
     GPROBE(1);
-    gemv_quantize_x<PEER>(a, xs, is_writer, g, tid, gr);
+    gemv_quantize_x<PEER, TRIPS>(a, xs, is_writer, g, tid, gr);
     GPROBE(2);
     KSTAMP(a, 2);
 #ifdef LUM_PROBE
