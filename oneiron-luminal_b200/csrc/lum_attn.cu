@@ -20,7 +20,7 @@
 namespace lum {
 
 // One (kv head, split) per CTA.
-template <int HD, int GM, bool BF16, bool CL>
+template <int HD, int GM, bool BF16, bool CL, int RS>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char attn_smem[];
     if (a.use_pdl) pdl_launch_dependents();
@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     // kernel waits for that step in full), so the rotation table can be worked out while the projections still run.
     const int p = a.state->pos;
     const bool ok = p >= 0 && p < a.max_seq;
-    if (ok) attn_fill_rope<HD>(a, attn_smem, p, (int)threadIdx.x);
+    if (ok) attn_fill_rope<HD, RS>(a, attn_smem, p, (int)threadIdx.x);
     if (a.use_pdl) pdl_grid_wait();
     if (!ok) {                                  // the same for every CTA of the grid: no cluster barrier is left half attended
         if (threadIdx.x == 0) atomicOr(a.status, LUM_ST_BAD_POS);
@@ -54,15 +54,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     attn_decode_body<HD, GM, BF16, CL>(a, attn_smem, (int)blockIdx.x, (int)blockIdx.y, p, (int)threadIdx.x, 2, true);
 }
 
-template <int HD, int GM>
+template <int HD, int GM, int RS>
 static const void* attn_fn(bool bf16, bool cl) {
-    if (cl) return bf16 ? (const void*)attn_decode<HD, GM, true, true> : (const void*)attn_decode<HD, GM, false, true>;
-    return bf16 ? (const void*)attn_decode<HD, GM, true, false> : (const void*)attn_decode<HD, GM, false, false>;
+    if (cl) return bf16 ? (const void*)attn_decode<HD, GM, true, true, RS> : (const void*)attn_decode<HD, GM, false, true, RS>;
+    return bf16 ? (const void*)attn_decode<HD, GM, true, false, RS> : (const void*)attn_decode<HD, GM, false, false, RS>;
 }
-static const void* attn_fn_for(int hd, int G, bool bf16, bool cl) {
-    if (hd == 128) return G <= 4 ? attn_fn<128, 4>(bf16, cl) : attn_fn<128, 8>(bf16, cl);
-    if (hd == 64) return G <= 4 ? attn_fn<64, 4>(bf16, cl) : attn_fn<64, 8>(bf16, cl);
+template <int RS>
+static const void* attn_fn_rs(int hd, int G, bool bf16, bool cl) {
+    if (hd == 128) return G <= 4 ? attn_fn<128, 4, RS>(bf16, cl) : attn_fn<128, 8, RS>(bf16, cl);
+    if (hd == 64) return G <= 4 ? attn_fn<64, 4, RS>(bf16, cl) : attn_fn<64, 8, RS>(bf16, cl);
     return nullptr;
+}
+static const void* attn_fn_for(int hd, int G, bool bf16, bool cl, int rope_style) {
+    return rope_style == 0 ? attn_fn_rs<0>(hd, G, bf16, cl) : attn_fn_rs<1>(hd, G, bf16, cl);
 }
 
 static void attn_fill_config(const AttnArgs& a, int G, bool cl, cudaStream_t st, cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at) {
@@ -90,7 +94,7 @@ static void attn_fill_config(const AttnArgs& a, int G, bool cl, cudaStream_t st,
 bool attn_cluster_supported(const AttnArgs& a) {
     const int G = a.n_kv > 0 ? a.n_q / a.n_kv : 0;
     if (a.n_splits < 2 || a.n_splits > kMaxClusterSplits || G < 1 || G > 8) return false;
-    const void* fn = attn_fn_for(a.hd, G, a.kv_bf16 != 0, true);
+    const void* fn = attn_fn_for(a.hd, G, a.kv_bf16 != 0, true, a.rope_style);
     if (!fn) return false;
     const size_t smem = attn_smem_bytes(a.hd, G);
     if (smem > 48 * 1024 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return false; }
@@ -111,7 +115,7 @@ cudaError_t launch_attn_decode(const AttnArgs& a_in, cudaStream_t st) {
     if (a.n_kv <= 0 || G < 1 || G > 8 || a.n_q != G * a.n_kv || a.n_splits < 1 || a.n_splits > kMaxSplits) return cudaErrorInvalidValue;
     const bool cl = a.cluster != 0;
     if (cl && (a.n_splits < 2 || a.n_splits > kMaxClusterSplits)) return cudaErrorInvalidValue;
-    const void* fn = attn_fn_for(a.hd, G, a.kv_bf16 != 0, cl);
+    const void* fn = attn_fn_for(a.hd, G, a.kv_bf16 != 0, cl, a.rope_style);
     if (!fn) return cudaErrorInvalidValue;
     const size_t smem = attn_smem_bytes(a.hd, G);
     if (smem > 48 * 1024) {

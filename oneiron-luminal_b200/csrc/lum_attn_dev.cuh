@@ -33,8 +33,11 @@ __device__ __forceinline__ float gain_at(const void* g, int kind, int i) {
 }
 
 // cos/sin of the rotation for pair index i at position pos.
+// RS: the rotation convention known at compile time (0 / 1), or -1 to decide at run time — each convention brings its own
+// precise transcendental functions, several KB of code apiece.
+template <int RS = -1>
 __device__ __forceinline__ void rope_cs(const AttnArgs& a, int i, int pos, float* cs, float* sn) {
-    if (a.rope_style == 0) {
+    if (RS == 0 || (RS < 0 && a.rope_style == 0)) {
         // the graph's chain, constant by constant: f = 2i * (1/d); inv = 1/exp2((f * ln theta) * log2 e);
         // emb = pos * inv; sin(emb); cos as sin(-emb + pi/2)
         const float f = (float)(2 * i) * a.c_inv_d;
@@ -71,12 +74,12 @@ __host__ __device__ inline size_t attn_smem_bytes(int HD, int G) {
 // where the rotation table (cos, sin per dimension pair) lives in the attention scratch
 __device__ __forceinline__ float* attn_rope_table(unsigned char* smem, int HD) { return (float*)smem + 9 * HD + HD + 2 * kAttnWarps * 8 + 4; }
 // The table depends only on the position: a kernel can fill it while it still waits for the projections (threads 0 .. HD/2-1).
-template <int HD>
+template <int HD, int RS = -1>
 __device__ __forceinline__ void attn_fill_rope(const AttnArgs& a, unsigned char* smem, int p, int tid) {
     float* tab = attn_rope_table(smem, HD);
     if (tid < HD / 2) {
         float cs, sn;
-        rope_cs(a, tid, p, &cs, &sn);
+        rope_cs<RS>(a, tid, p, &cs, &sn);
         tab[2 * tid] = cs;
         tab[2 * tid + 1] = sn;
     }
@@ -287,7 +290,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
 #pragma unroll
         for (int w = 0; w < NW; w++) M = fmaxf(M, s_m[w][g]);
         float L = 0.0f, O = 0.0f;
-#pragma unroll
+#pragma unroll 2
         for (int w = 0; w < NW; w++) {
             const float c = (s_m[w][g] == -INFINITY) ? 0.0f : expf(s_m[w][g] - M);
             L = fmaf(s_l[w][g], c, L);

@@ -145,7 +145,7 @@ __host__ __device__ inline bool gemv_can_ksplit(int K, int kc) { const int tpr =
 cudaError_t launch_gemv(const GemvArgs& a, int sm_count, cudaStream_t st);
 bool gemv_stream_supported(const GemvArgs& a);
 cudaError_t launch_attn_decode(const AttnArgs& a, cudaStream_t st);
-bool attn_cluster_supported(const AttnArgs& a);      // shape fields only: n_q, n_kv, hd, n_splits, kv_bf16
+bool attn_cluster_supported(const AttnArgs& a);      // shape fields only: n_q, n_kv, hd, n_splits, kv_bf16, rope_style
 cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
 // tensor parallel: fold the ranks' {logit bits, row} pairs into the sample (last maximum wins) and advance the state
 cudaError_t launch_tp_pick(const int* pairs, int pair_stride, const uint32_t* flags, const uint32_t* seq, uint32_t tag, uint32_t* status,

@@ -883,7 +883,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
         bool want = true;         // measured: same tokens/s as the ticket merge with 8 KV heads on one GPU, +2.5 % with 4 per rank on two
         if (const char* e = getenv("LUM_ATTN_CLUSTER")) want = atoi(e) != 0;
         AttnArgs t{};
-        t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits; t.kv_bf16 = d.kv_dtype == LUM_BF16;
+        t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits; t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
         rt->attn_cluster = want && attn_cluster_supported(t);
     }
     if (int r = setup_mega(rt)) { free_model(rt); return r; }
