@@ -192,8 +192,8 @@ def kernel_roofline(pkg, torch, peaks, peak_kind):
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
             "peak_kind": f"of {peak_kind} (burst copy)", "us_per_launch": ms * 1000.0, "bytes_per_launch": bytes_per_launch,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised in
-            # profiles/q8_gemv_stream_gateup_shape.md (124.90 MB read + 10.37 MB written)
-            "traffic": 135_265_280}, launches + 4
+            # profiles/q8_gemv_stream_gateup_shape.md (124.87 MB read + 9.17 MB written)
+            "traffic": 134_049_024}, launches + 4
 
 
 def kernel_rows_sweep(pkg, torch):
