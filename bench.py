@@ -34,6 +34,16 @@ UNIT = "tokens/s"
 WORKLOAD = "llama3_8b_q8"
 
 
+def set_workload(name: str, prompt_given: bool):
+    """Switch the benchmarked configuration (its own metric name, so lines of different workloads are never compared)."""
+    global WORKLOAD, METRIC, PROMPT_LEN
+    WORKLOAD = name
+    if name == "qwen3_4b_q8":
+        METRIC = "q8_qwen3_4b_bs1_decode_tokens_per_s"
+        if not prompt_given:
+            PROMPT_LEN = 1024
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -101,58 +111,60 @@ def physical_gpu_index(local: int) -> int:
 
 # ---------------------------------------------------------------------------------------------- CPU arm
 
-def cpu_port_tokens_per_s(pkg, steps: int, warmup: int):
-    """Times the oracle (a C++ restatement of the reference's CPU interpreter semantics, all host threads) on a
-    bounded sample: 2 of the 32 layers plus the full lm_head of the same shapes, one token at a short context,
-    and scales to the whole model: t_token = 16 x t(2 layers) + t(head)."""
+def bench_config(world: int, warmup: int, fused: bool):
+    """The `config` object of the JSON line — the same for both arms (the CPU arm runs the GPU arm's configuration)."""
+    return {"workload": WORKLOAD, "batch": 1, "prompt_len": PROMPT_LEN, "tokens_per_step": TOKENS_PER_STEP,
+            "context_at_start": PROMPT_LEN + warmup * TOKENS_PER_STEP,
+            "l2": "weights 8.0 GB >> 126 MB L2; every token re-streams them" if WORKLOAD == "llama3_8b_q8" else "weights >> 126 MB L2; every token re-streams them",
+            "parallelism": "single GPU" if world == 1 else f"tp{world}: heads/FFN/vocab sharded, " + ("partial sums exchanged through peer memory inside the projection kernels" if fused else "NCCL all-reduce per projection"),
+            "seed": SEED}
+
+
+def cpu_port_tokens_per_s(pkg, steps: int, warmup: int, context: int):
+    """Times the oracle (a C++ restatement of the reference's CPU interpreter semantics, all host threads) on a bounded
+    sample of the workload: the WHOLE model (every layer, the whole vocabulary), `warmup` + `steps` single-token forward
+    passes at positions context, context + 1, ... — the cache rows before `context` hold seeded stand-in values instead
+    of a computed prompt (computing it would take the CPU several minutes; the arithmetic per token is the same)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import numpy as np
     from oracle import OracleModel, load
     full = pkg.CONFIGS[WORKLOAD]
-    cut_layers = 2
-    d_body = full.copy(n_layers=cut_layers, vocab=32, max_seq=64)       # layers only (tiny head)
-    d_head = full.copy(n_layers=0 + 1, vocab=full.vocab, max_seq=8, ffn=32, n_q_heads=8, n_kv_heads=8)  # head dominates
+    steps, warmup = max(1, steps), max(0, warmup)
+    d = full.copy(max_seq=context + steps + warmup + 8)
     lib = load()
     threads = lib.orc_threads()
-    body = OracleModel(d_body)
-    body.synth(SEED)
-    head = OracleModel(d_head)
-    head.synth(SEED)
-    toks = [1, 2, 3, 4, 5, 6, 7, 8]
-    body.forward(toks, 0)
-    head.forward([1], 0)
-
-    def one(m, p):
-        t0 = time.perf_counter()
-        m.forward([3], p)
-        return time.perf_counter() - t0
-
-    # the head model still runs one thin layer; measure that layer alone and subtract it
-    d_thin = d_head.copy(vocab=32)
-    thin = OracleModel(d_thin)
-    thin.synth(SEED)
-    thin.forward([1], 0)
+    t_build = time.perf_counter()
+    m = OracleModel(d)
+    m.synth(SEED)
+    m.kv_fill(SEED, context)
+    t_build = time.perf_counter() - t_build
+    tok, p = 1, context
     for _ in range(warmup):
-        one(body, 8); one(head, 1); one(thin, 1)
-    t_body = min(one(body, 8 + i) for i in range(max(1, steps)))
-    t_head = min(one(head, 1 + i) for i in range(max(1, steps))) - min(one(thin, 1 + i) for i in range(max(1, steps)))
-    t_token = t_body * (full.n_layers / cut_layers) + max(t_head, 0.0)
-    sample = (f"{cut_layers} of {full.n_layers} layers (hidden {full.hidden}, ffn {full.ffn}, Q8_0) at context 8 plus the full "
-              f"{full.vocab}-row lm_head, best of {max(1, steps)}; scaled x{full.n_layers // cut_layers} + head")
-    return 1.0 / t_token, threads, sample, np.__version__
+        tok = m.argmax(m.forward([tok], p)[0]); p += 1
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = m.argmax(m.forward([tok], p)[0]); p += 1
+    dt = time.perf_counter() - t0
+    sample = (f"whole model ({full.n_layers} layers, vocabulary {full.vocab}), {steps} single-token passes at context {context}.."
+              f"{context + steps + warmup - 1} after {warmup} warm-up passes; cache rows below {context} seeded, not computed; "
+              f"model set-up {t_build:.0f} s outside the timed region")
+    return steps / dt, threads, sample, np.__version__
 
 
 def run_reference_arm(args, pkg):
+    """One "step" of this arm is one decoded token (a bounded sample of the GPU arm's 64-token step)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    v, threads, sample, _ = cpu_port_tokens_per_s(pkg, args.steps, args.warmup)
+    context = PROMPT_LEN + args.warmup * TOKENS_PER_STEP
+    v, threads, sample, _ = cpu_port_tokens_per_s(pkg, args.steps, args.warmup, min(context, 2048))
+    cfg = bench_config(max(1, args.gpus), args.warmup, os.environ.get("LUM_TP_FUSED", "1") != "0")
+    cfg["note"] = "CPU restatement of the reference's NativeRuntime semantics; the reference (Rust) cannot be built here"
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1000.0 * TOKENS_PER_STEP / v, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1000.0 / v, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch": 1, "prompt_len": PROMPT_LEN, "tokens_per_step": TOKENS_PER_STEP,
-                   "note": "CPU restatement of the reference's NativeRuntime semantics; the reference (Rust) cannot be built here"},
+        "config": cfg,
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -191,9 +203,9 @@ def kernel_roofline(pkg, torch, peaks, peak_kind):
     return {"bound": "hbm", "kernel": "q8_gemv_stream", "shape": f"N={n} K={k} (gate+up sized), alone, back to back",
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
             "peak_kind": f"of {peak_kind} (burst copy)", "us_per_launch": ms * 1000.0, "bytes_per_launch": bytes_per_launch,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape, from the ncu capture summarised in
-            # profiles/q8_gemv_stream_gateup_shape.md (124.87 MB read + 9.17 MB written)
-            "traffic": 134_049_024}, launches + 4
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape under ncu (124.87 MB read + 9.17 MB
+            # written): a figure from a profile of this kernel, not measured by this run
+            "traffic": 134_049_024, "traffic_from": "ncu capture of this kernel on this shape (profiles/), not this run"}, launches + 4
 
 
 def kernel_rows_sweep(pkg, torch):
@@ -303,6 +315,9 @@ def run_ours(args, pkg):
     rt.set_data(prompt)
     rt.execute({"s": len(prompt), "p": 0})
     rt.synchronize()
+    # for the output check below: the logits row that follows the prompt (this rank's vocabulary shard) and its greedy token
+    prompt_logits = rt.get_f32()
+    first_token = rt.get_token()
 
     ext = torch.cuda.ExternalStream(rt.stream(), device=torch.device("cuda", local))
 
@@ -338,10 +353,15 @@ def run_ours(args, pkg):
     p_mean = p_start + n_tok / 2.0
     bytes_tok = pkg.decode_bytes_per_token(pkg.CONFIGS[WORKLOAD], p_mean)
 
+    # Output check: the first 32 greedy tokens and the post-prompt logits against the committed oracle fixture of this
+    # workload (tests/golden/<workload>_full.npz: whole model, this seed, this prompt), on every rank.
+    parity = check_parity(rt, prompt, prompt_logits, first_token, n_decoded=(args.warmup + args.steps) * TOKENS_PER_STEP,
+                          world=world, rank=rank, dist=dist if world > 1 else None, torch=torch)
+
     # end-to-end through the public API, one token at a time, host <-> device every token
     tok = rt.get_token()
     p = p_start + n_tok
-    e2e_tokens = min(n_tok, 128)
+    e2e_tokens = max(1, min(n_tok, desc.max_seq - 1 - p))
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_tokens):
@@ -364,25 +384,25 @@ def run_ours(args, pkg):
         step_ach = bytes_tok * tok_s_rank / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            # one sequence, one fixed-size model whatever N: the same experiment at every N
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 accumulate over Q8_0 (int8 x f16-scale) weights", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch": 1, "prompt_len": PROMPT_LEN, "tokens_per_step": TOKENS_PER_STEP,
-                       "context_at_start": p_start, "l2": "weights 8.0 GB >> 126 MB L2; every token re-streams them",
-                       "parallelism": "single GPU" if world == 1 else f"tp{world}: heads/FFN/vocab sharded, " + ("partial sums exchanged through peer memory inside the projection kernels" if fused else "NCCL all-reduce per projection"),
-                       "seed": SEED},
+            "config": bench_config(world, args.warmup, fused),
+            "parity": parity,
             "roofline": roof,
             "step_roofline": {"bound": "hbm", "what": "whole decode step, all kernels; bytes are the whole model's, peak is per GPU x n_gpus",
                               "bytes_per_token": bytes_tok, "achieved": step_ach, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
                               "frac": step_ach / (peaks["hbm_gbs"] * world), "frac_of_8tbs_nominal": step_ach / (8000.0 * world),
                               "peak_kind": f"of {peak_kind}"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": 8 * TOKENS_PER_STEP, "d2h_bytes_per_step": 4 * TOKENS_PER_STEP,
+                    "tokens": e2e_tokens,
                     "note": "per token: token id + position host->device, sampled token device->host, synchronous"},
             "gpu_launches": launches_step * n_tok,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
             try:
-                v, threads, sample, _ = cpu_port_tokens_per_s(pkg, 2, 1)
+                v, threads, sample, _ = cpu_port_tokens_per_s(pkg, 8, 1, min(p_start, 2048))
                 line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
             except Exception as exc:  # the GPU number stands on its own
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
@@ -392,6 +412,33 @@ def run_ours(args, pkg):
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line))
+
+
+def check_parity(rt, prompt, prompt_logits, first_token, n_decoded, world, rank, dist, torch):
+    """Compares what this run produced with the oracle's committed outputs for the same workload, seed and prompt."""
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", f"{WORKLOAD}_full.npz")
+    if not os.path.exists(path):
+        return {"checked": False, "reason": f"no fixture {os.path.relpath(path, ROOT)}"}
+    fx = np.load(path)
+    if int(fx["seed"]) != SEED or list(fx["prompt"]) != list(prompt):
+        return {"checked": False, "reason": "fixture was made for another seed or prompt (this run used non-default sizes)"}
+    want = [int(t) for t in fx["tokens"]]
+    n = min(len(want), 1 + n_decoded)
+    got = [int(first_token)] + ([int(t) for t in rt.get_decoded(n - 1)] if n > 1 else [])
+    ref = fx["prompt_logits"].astype(np.float32)
+    shard = ref.size // world
+    mine = ref[rank * shard:(rank + 1) * shard]
+    err = float(np.max(np.abs(prompt_logits - mine)) / np.max(np.abs(ref)))
+    equal = got == want[:n]
+    if world > 1:
+        t = torch.tensor([err, 0.0 if equal else 1.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        err, equal = float(t[0].item()), float(t[1].item()) == 0.0
+    first_bad = next((i for i in range(n) if got[i] != want[i]), None)
+    return {"checked": True, "tokens_equal": bool(equal), "steps": n, "logits_rel_err": err, "logits_tolerance": 1e-2,
+            "first_mismatch": first_bad, "min_margin_of_fixture": float(np.min(fx["margins"][:n])),
+            "fixture": os.path.relpath(path, ROOT)}
 
 
 def _prompt_tokens(vocab: int, n: int):
@@ -418,12 +465,16 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
+    ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8"],
+                    help="llama3_8b_q8: the configuration the metric is quoted on (default); qwen3_4b_q8: the Qwen3-4B shape")
     ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor"],
                     help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts; floor: the decode step with all projections shrunk away")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
     PROMPT_LEN, TOKENS_PER_STEP = args.prompt_len, args.tokens_per_step
+    if args.workload != WORKLOAD:
+        set_workload(args.workload, prompt_given=args.prompt_len != 512)
     if args.only == "kernel":
         import torch
         torch.cuda.set_device(0)

@@ -119,12 +119,44 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
 int32_t lum_set_input(lum_rt* rt, int64_t hlir_node, const void* host, size_t bytes, uint32_t dtype);
 /* `get_f32(node_id)` for the graph's Output: the logits of the last row (n = vocab). */
 int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n);
+/* The `CudaInput::Ptr` case of `set_data` (crates/luminal_cuda/src/runtime.rs:36-39, 326-396): the input's bytes already sit
+ * in device memory the caller owns.  Weights are repacked from there (no host round trip); token / position ids, a few
+ * bytes, are read back once because the step's kernels take the token from the device-resident decode state. */
+int32_t lum_set_input_device_ptr(lum_rt* rt, int64_t hlir_node, const void* device_ptr, size_t bytes, uint32_t dtype);
+
+/* The part of `trait Runtime` that `Graph::search` drives (src/op.rs:18-29; callers src/graph.rs:293-302, 337, 351-352,
+ * 420-424, 569-570):
+ *   `allocate_dummy_input(node_index, num_elements)` -> lum_alloc_dummy_input: give an Input defined stand-in contents so that a
+ *       candidate can be timed before real data exists.  Before a graph is loaded the request is remembered and applied by
+ *       lum_load_llir; afterwards a weight Input is filled from the seeded generator (the element count must match the
+ *       tensor), the token Input gets `num_elements` zero ids (and sets 's').
+ *   `clear_intermediate_buffers()` -> lum_clear_intermediates: zero the activation buffers and the KV cache, reset the decode
+ *       state and forget pending dummy inputs; weights stay.
+ *   `profile(&LLIRGraph, &dyn_map, trials)` -> lum_profile_llir: time `trials` executions of the graph in `blob` at dynamic
+ *       dimensions s / p on a scratch runtime with seeded stand-in weights; the runtime's own model, if any, is untouched and
+ *       the context stays usable whatever happens (the search catches failing candidates, src/graph.rs:419-447).  `blob` may
+ *       be a whole decoder or a CHUNK: whole decoder layers between two GraphBreaks, whose residual stream enters as an Input
+ *       and leaves as an Output (src/graph.rs:633-808 cuts the graph there and profiles each distinct chunk once).  A chunk
+ *       cannot be loaded on its own (lum_load_llir refuses it and says so): the search loads the stitched graph. */
+int32_t lum_alloc_dummy_input(lum_rt* rt, int64_t hlir_node, size_t n_elems);
+int32_t lum_clear_intermediates(lum_rt* rt);
+int32_t lum_profile_llir(lum_rt* rt, const uint8_t* blob, size_t size, uint64_t s, uint64_t p, int32_t trials, double* usec_per_execute,
+                         char* display, size_t display_len);
+/* Host-only recognition of a chunk: hyper-parameters (vocab = 0) and the HLIR ids of the residual stream's Input and Output. */
+int32_t lum_llir_describe_chunk(const uint8_t* blob, size_t size, lum_model_desc* desc_out, int64_t* hidden_input, int64_t* hidden_output,
+                                char* err, size_t err_len);
 
 /* KV cache: owned by the runtime (the reference has caller-owned buffers whose raw addresses are
  * baked into op payloads, examples/llama/src/model.rs:194-223).  reset = `KVCache::reset`. */
 int32_t lum_kv_reset(lum_rt* rt);
 /* Copy rows [0, rows) of one layer's K (kind 0) or V (kind 1) cache to host as f32. */
 int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float* host_out);
+/* Rows [0, rows) of one layer's K or V cache in the cache's own element type (bf16 or f32; this rank's KV heads), to and
+ * from host memory: a conversation's cache can be parked and brought back (the reference's caches are caller-owned device
+ * buffers the caller can copy at will, examples/llama/src/model.rs:194-223).  `bytes` must be rows * kv_heads * head_dim *
+ * element size.  After loading, set 'p' to the number of rows before the next lum_execute. */
+int32_t lum_kv_save(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, void* host_out, size_t bytes);
+int32_t lum_kv_load(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, const void* host, size_t bytes);
 
 /* ---------------------------------------------------------------------------------------------
  * Execution, at the level of the reference's decode loop (examples/llama/src/main.rs:82-118):
@@ -163,6 +195,19 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec_per_step, char* dis
 int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n);
 /* CUDA stream the runtime launches on (a cudaStream_t), for callers that time with their own events. */
 void* lum_stream(lum_rt* rt);
+/* Counters for reports in the manner of `ExecutionStats` / `print_execution_stats` (src/op.rs:33-35;
+ * crates/luminal_cuda/src/runtime.rs:604-678) and of the bandwidth-utilisation arithmetic of
+ * crates/luminal_bench/src/metrics.rs:13-60: MBU = (weight_bytes_per_token + kv_bytes_per_position * p) / time / peak. */
+typedef struct lum_stats {
+    uint64_t tokens_executed;         /* tokens run through lum_execute / lum_decode_greedy since lum_create */
+    uint64_t kernel_launches;         /* kernels those tokens launched (graph nodes count one each) */
+    uint64_t weight_bytes_per_token;  /* lum_model_weight_bytes of the loaded model (0 without one) */
+    uint64_t kv_bytes_per_position;   /* K + V bytes one cached position holds over all layers (this rank) */
+    int32_t launches_per_step;        /* as counted when the step was last issued or captured (0 before the first step) */
+    int32_t reserved;
+    double last_profile_usec;         /* result of the last lum_profile / lum_profile_llir */
+} lum_stats;
+int32_t lum_get_stats(const lum_rt* rt, lum_stats* out);
 
 /* ---------------------------------------------------------------------------------------------
  * Tensor parallelism over the GPUs of one node: one process and one runtime per GPU (the reference is single-GPU:
@@ -219,6 +264,12 @@ int32_t lum_op_sample_q8_0(const void* packed_dev, int32_t n, int32_t k, const f
 int32_t lum_op_sample_q8_0_static(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* logits_dev,
                                   int32_t* best_dev, void* stream);
 int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev, void* stream);
+/* The stand-alone operators above run asynchronously; a bounded wait inside one of their kernels that ran out of budget leaves
+ * a status word on the device.  This call synchronises `stream`, returns LUM_E_DEVICE (message through lum_last_error(NULL))
+ * if any operator launched on the current device since the last call flagged one — the static-scratch entry included — and
+ * clears the words.  It allocates nothing.  The stand-alone operators keep their per-device state in process-wide tables that
+ * are not locked: call them from one thread per device. */
+int32_t lum_op_status(void* stream);
 /* Q8_0 wire blocks (host layout, on device) -> planes; planes -> f32. */
 int32_t lum_op_q8_0_unpack(const uint8_t* blocks_dev, size_t n_blocks, int8_t* quants_dev, void* scales_dev, void* stream);
 int32_t lum_op_q8_0_dequant(const int8_t* quants_dev, const void* scales_dev, size_t n_elems, float* out_dev, void* stream);

@@ -20,4 +20,7 @@ from .runtime import (  # noqa: F401
     library_path,
     decode_bytes_per_token,
     describe_llir,
+    describe_llir_chunk,
+    mbu,
+    Stats,
 )

@@ -127,17 +127,6 @@ __device__ __forceinline__ float dot4_s8(uint32_t w, float4 x, float acc) {
 
 // ------------------------------------------------------------------------------ streaming kernel (one op)
 
-#ifdef LUM_PROBE
-// per-CTA stamps of the last launches, keyed by the projection kind (epilogue kind * 2 + (K > 4096)): when every CTA got past the
-// grid dependency and when it finished
-__device__ unsigned long long g_kstart[8 * 160], g_kend[8 * 160];
-__device__ __forceinline__ int g_klaunch_of(const GemvArgs& a) { return a.epi * 2 + (a.K > 4096 ? 1 : 0); }
-extern "C" int lum_kstamps_read(unsigned long long* s, unsigned long long* e) {
-    int r = (int)cudaMemcpyFromSymbol(s, g_kstart, sizeof(g_kstart));
-    return r ? r : (int)cudaMemcpyFromSymbol(e, g_kend, sizeof(g_kend));
-}
-extern "C" int lum_kx_read(unsigned long long* x) { return (int)cudaMemcpyFromSymbol(x, g_kx, sizeof(g_kx)); }
-#endif
 
 // WIDE: K above 4096 (up to 16384): the prologue then holds up to eight float4 per thread instead of two.
 template <bool PEER, bool WIDE>
@@ -147,16 +136,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     __shared__ int s_abort;
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    KSTAMP(a, 0);
     GemvSmem g;
     gemv_carve(smem, a.K, a.stages, &s_abort, &g);
-    if (tid == 0) GPROBE(0);
-#if defined(LUM_PROBE) && defined(LUM_TL_EPI)
-    if (tid == 0 && blockIdx.x == 0) g_tl_on = (a.epi == LUM_TL_EPI && a.K == LUM_TL_K) ? 1 : 0;   // timeline of one kind of launch only
-#endif
     if (tid == 0 && blockIdx.x == 0 && a.job_ctr_zero) *a.job_ctr_zero = 0u;
     const uint32_t tmem = gemv_cta_begin(g, tid, &s_abort);
-    KSTAMP(a, 1);
     if (a.use_pdl) pdl_launch_dependents();
     const GemvPlan plan = gemv_plan(a, (int)gridDim.x, a.job_ctr != nullptr);
 
@@ -165,13 +148,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
         if (lane == 0) {
             ProducerRing pr{0, 0u, 0};
             if (!gemv_produce(a, plan, g, pr, (int)blockIdx.x, (int)gridDim.x, a.job_ctr, a.status)) gemv_producer_drain(g, pr, a.status);
-            GPROBE(5);
         }
         return;
     }
     if (warp == kMmaWarp) {
         if (lane == 0) {
-            MmaRing mr{0, 0u, 0u, 0u, 0u, 0};
+            MmaRing mr{0, 0u, 0u, 0u, 0u};
             gemv_mma_issue(a, plan, g, mr, tmem, a.status);
         }
         gemv_mma_end(g, tmem, lane, a.status);
@@ -180,29 +162,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) q8_gemv_stream(const GemvArgs
     GainRegs gr;
     gemv_gain_preload<TRIPS>(a, tid, gr);      // independent of the previous kernel: fetched while waiting for it
     if (a.use_pdl) pdl_grid_wait();
-#ifdef LUM_PROBE
-    if (tid == 0) g_kstart[(g_klaunch_of(a) & 7) * 160 + blockIdx.x] = globaltimer_ns();
-#endif
     XSource xs{};
     xs.x = a.x; xs.x_add = a.x_add; xs.x_out = a.x_out;
     xs.parts = a.parts; xs.part_flags = a.part_flags; xs.n_parts = a.n_parts; xs.part_stride = a.part_stride; xs.parts_tag = a.parts_tag; xs.seq = a.seq; xs.parts_ll = a.parts_ll;
     ArgBest best{-INFINITY, -1};
-    ConsumerRing cr{0, 0u, 0u, 0u, 0};
+    ConsumerRing cr{0, 0u, 0u, 0u};
     gemv_consume<PEER, TRIPS>(a, xs, blockIdx.x == 0, plan, g, cr, tid, tmem, a.status, &best, gr);
     if (tid >= kConsumers) return;
     gemv_consumers_done();
     if (PEER && a.epi == EPI_PEER && !a.peer_ll) peer_publish(a, tid, kConsumers, 2);
     if (a.epi == EPI_ARGMAX) argmax_finish(a, best, tid, kConsumers, 2);
-    GPROBE(4);
-#ifdef LUM_PROBE
-    if (tid == 0) g_kend[(g_klaunch_of(a) & 7) * 160 + blockIdx.x] = globaltimer_ns();
-#endif
 }
-#ifdef LUM_PROBE
-extern "C" int lum_probe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_probe, sizeof(g_probe)); }
-extern "C" int lum_gpprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_pprobe, sizeof(g_pprobe)); }
-extern "C" int lum_tl_read(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl)); }
-#endif
 
 // ------------------------------------------------------------------------------ direct kernel
 
@@ -411,8 +381,9 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
 // fixed array below instead of an allocated buffer.  Consequences, all part of the contract:
 //   * capacity: 256 CTAs.  The kernel runs one CTA per SM, so a device with more than 256 SMs is refused.
 //   * every GPU that loads this library carries the 4 KiB array until the process exits;
-//   * every call on a device shares it, and it keeps the previous call's contents: the entry zeroes the ticket and the
-//     status word on the caller's stream before each launch, the rest is overwritten by the kernel before it is read;
+//   * every call on a device shares it, and it keeps the previous call's contents: the entry zeroes the arrival ticket on
+//     the caller's stream before each launch, the per-CTA slots are overwritten by the kernel before it is read, and the
+//     status word keeps a pending error until lum_op_status reports and clears it;
 //   * two calls whose kernels could overlap on one GPU (different streams, no dependency) race on it — order them;
 //   * the array's name is only a host-side handle; its device address is looked up with cudaGetSymbolAddress the first
 //     time the entry is called on a device (with that device current).  That first call does this one-time set-up
@@ -420,10 +391,18 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
 static __device__ __align__(256) unsigned char g_sample_static[4096];
 constexpr int kStaticMaxCtas = 256;     // 256 floats + 256 ints + ticket + status = 2056 bytes of the 4096
 
+static unsigned char* g_static_dev_ptr[64] = {nullptr};      // device address of the array, per device ordinal (set on first use)
+// where lum_op_status finds this entry's status word on the current device (null: the entry was never used there)
+uint32_t* lum_static_sample_status() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_static_dev_ptr[dev]) return nullptr;
+    return (uint32_t*)(g_static_dev_ptr[dev] + 2052);
+}
+
 extern "C" int32_t lum_op_sample_q8_0_static(const void* packed, int32_t n, int32_t k, const float* x, float* logits,
                                             int32_t* best, void* stream) {
     using namespace lum;
-    static unsigned char* dev_ptr[64] = {nullptr};      // device address of the array, per device ordinal
+    unsigned char** dev_ptr = g_static_dev_ptr;
     const int kc = q8_pack_kc(n, k);
     if (!packed || !x || !logits || !best || !kc) {
         set_op_error("sample_q8_0_static: bad arguments or shape cannot be packed (needs K % 512 == 0, K <= 16384, N % 8 == 0)");
@@ -446,7 +425,8 @@ extern "C" int32_t lum_op_sample_q8_0_static(const void* packed, int32_t n, int3
     }
     unsigned char* base = dev_ptr[dev];
     cudaStream_t st = (cudaStream_t)stream;
-    e = cudaMemsetAsync(base + 2048, 0, 8, st);         // arrival ticket and status word start at zero
+    e = cudaMemsetAsync(base + 2048, 0, 4, st);         // the arrival ticket starts at zero (a status left by an earlier call
+                                                        // stays until lum_op_status reads it; the array is zero when the library loads)
     if (e != cudaSuccess) { set_op_error("sample_q8_0_static: clearing the ticket failed"); return -2; }
     GemvArgs a{};
     a.nseg = 1; a.seg[0] = {packed, nullptr, n, kc}; a.K = k; a.wkind = WK_Q8; a.epi = EPI_ARGMAX; a.x = x; a.y = logits;

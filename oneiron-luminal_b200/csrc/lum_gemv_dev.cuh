@@ -36,27 +36,6 @@
 
 namespace lum {
 
-#ifdef LUM_PROBE
-// Build-time probe (never in the shipped library): %globaltimer stamps of a few points in CTA 0 (one copy per translation unit).
-static __device__ unsigned long long g_probe[32];
-static __device__ unsigned long long g_pprobe[64 * 8];   // per phase (in call order, wrapping): stamps 1..4 of thread 0
-static __device__ int g_pphase;
-#define GPROBE(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || (i) == 5)) { g_probe[i] = globaltimer_ns(); \
-    if (threadIdx.x == 0) { if ((i) == 1) g_pphase++; g_pprobe[(g_pphase & 63) * 8 + (i)] = g_probe[i]; } } } while (0)
-// per-fill timeline of CTA 0 (SM clock): [fill][event]
-static __device__ long long g_tl[64][16];   // one copy per translation unit
-static __device__ unsigned long long g_kx[6][8 * 160];    // per-CTA stamps of the last launch of each projection kind
-#define KSTAMP(a, i) do { if (threadIdx.x == 0) g_kx[i][(((a).epi * 2 + ((a).K > 4096 ? 1 : 0)) & 7) * 160 + blockIdx.x] = globaltimer_ns(); } while (0)
-#ifndef LUM_TL_FIRST
-#define LUM_TL_FIRST 0
-#endif
-static __device__ int g_tl_on = 1;         // a kernel may switch the timeline off for launches it is not interested in
-#define TPROBE(f, e) do { if (blockIdx.x == 0 && g_tl_on && (f) >= LUM_TL_FIRST && (f) < LUM_TL_FIRST + 64) g_tl[(f) - LUM_TL_FIRST][e] = clock64(); } while (0)
-#else
-#define GPROBE(i) do { } while (0)
-#define KSTAMP(a, i) do { } while (0)
-#define TPROBE(f, e) do { } while (0)
-#endif
 
 constexpr int kWorkers = 512;            // 16 worker warps: activation prologue, attention (persistent kernel); warps 0-7 also drain the accumulators
 constexpr int kConsumers = 256;          // the first 8 worker warps = two warpgroups, each owning one tensor-memory slot
@@ -645,8 +624,8 @@ __device__ __forceinline__ GemvPlan gemv_plan(const GemvArgs& a, int n_cta, bool
 
 // Ring positions, carried across phases.
 struct ProducerRing { int stage; uint32_t par; long long armed; };
-struct ConsumerRing { int stage; uint32_t par; uint32_t tpar; uint32_t ppar; int pf; };          // tpar: accumulator hand-over parity; ppar: phase parity
-struct MmaRing { int stage; uint32_t par; uint32_t tpar; uint32_t busy; uint32_t xpar; int pf; };   // busy: accumulators issued and not yet known drained
+struct ConsumerRing { int stage; uint32_t par; uint32_t tpar; uint32_t ppar; };          // tpar: accumulator hand-over parity; ppar: phase parity
+struct MmaRing { int stage; uint32_t par; uint32_t tpar; uint32_t busy; uint32_t xpar; };   // busy: accumulators issued and not yet known drained
 
 // Producer side of one phase: ONE lane (lane 0 of the producer warp) walks this CTA's static jobs, then claims pooled
 // jobs with atomicAdd on *job_ctr (the next claim is always in flight while the current job is being issued), and
@@ -772,9 +751,6 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
     constexpr uint32_t idesc = umma_idesc_s8(128, kMmaN);
     const int tpr = p.tpr;
     const bool wrap = p.gpf > 1;
-#ifdef LUM_PROBE
-    int& pf = r.pf;
-#endif
     for (;;) {
         // the previous fill's accumulators must have been read back before they are overwritten; waiting for that first
         // costs nothing while the next fill is still in flight
@@ -783,9 +759,7 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
             r.tpar ^= 1u;
             r.busy = 0u;
         }
-        TPROBE(pf, 1);
         if (!mbar_wait_abortable(g.full0 + 8u * r.stage, r.par, g.abort)) return fail(LUM_ST_WAIT_FULL);
-        TPROBE(pf, 0);
         const int2 mm = g.meta[r.stage];
         const int u = mm.x;
         if (u != kMetaEnd) {
@@ -794,7 +768,6 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
             uint32_t a_lo = st_lo + (uint32_t)r.stage * (kFillBytes >> 4);
             uint32_t b_lo = xq_lo + (uint32_t)c0 * (kXqTileBytes >> 4);
             tc_fence_after_sync();
-            TPROBE(pf, 3);
             if (nt == kFillTiles && !wrap) {
                 // the common case, straight-line: the tensor pipe takes ~60 cycles per instruction and the issuing thread
                 // is held that long, so every other instruction in between adds to the burst
@@ -813,16 +786,11 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
                     if (wrap && ++t == tpr) { t = 0; b_lo = xq_lo; }
                 }
             }
-            TPROBE(pf, 4);
             umma_commit(g.tfull0);
-            TPROBE(pf, 2);
         } else {
             mbar_arrive(g.tfull0);                           // the END marker travels the same way, with nothing to read back
         }
         r.busy = 1u;                                         // every hand-over, END included, is answered on tempty
-#ifdef LUM_PROBE
-        pf++;
-#endif
         if (++r.stage == S) { r.stage = 0; r.par ^= 1u; }
         if (u == kMetaEnd) break;
     }
@@ -838,13 +806,7 @@ __device__ __forceinline__ bool gemv_mma_issue(const GemvArgs& a, const GemvPlan
 template <bool PEER = false, int TRIPS = kXTrips>
 __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& xs, bool is_writer, const GemvPlan& p, const GemvSmem& g,
                                              ConsumerRing& cr, int tid, uint32_t tmem, uint32_t* status, ArgBest* best, const GainRegs& gr) {
-    GPROBE(1);
     gemv_quantize_x<PEER, TRIPS>(a, xs, is_writer, g, tid, gr);
-    GPROBE(2);
-    KSTAMP(a, 2);
-#ifdef LUM_PROBE
-    bool kx_first = true;
-#endif
     if (tid >= kConsumers) return;
     const int lane = tid & 31, warp = tid >> 5, wg = warp >> 2, q = warp & 3;
     const int S = g.stages, tpr = p.tpr;
@@ -856,10 +818,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
     auto fail = [&](uint32_t code) { if (!*g.abort) { atomicOr(status, code); *g.abort = 1; } };
     int slot = 0, slot_base = 0;
     bool ended = false;
-#ifdef LUM_PROBE
-    int& pf = cr.pf;
-    const bool pl = lane == 0 && q == 0;
-#endif
 #pragma unroll 1
     while (!ended) {
         slot = 0;
@@ -880,10 +838,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
             tmem_ld_wait();
             __syncwarp();
             if (lane == 0) mbar_arrive(g.tempty0);
-#ifdef LUM_PROBE
-            if (pl) TPROBE(pf, 7 + 4 * wg);
-            if (kx_first) { KSTAMP(a, 3); kx_first = false; }
-#endif
             // The stage has landed (the tensor-core warp waited for it); observing its barrier here, complete at the first
             // attempt, makes the bulk copy's bytes and the producer's meta word visible to this thread by the book.
             if (!mbar_wait_abortable(g.full0 + 8u * cr.stage, cr.par, g.abort)) { fail(LUM_ST_WAIT_FULL); ended = true; break; }
@@ -893,9 +847,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
                 __syncwarp();
                 if (lane == 0) mbar_arrive(g.empty0 + 8u * cr.stage);
                 if (++cr.stage == S) { cr.stage = 0; cr.par ^= 1u; }
-#ifdef LUM_PROBE
-                pf++;
-#endif
                 ended = true;
                 break;
             }
@@ -922,9 +873,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(g.empty0 + 8u * cr.stage);
-#ifdef LUM_PROBE
-            if (pl) TPROBE(pf, 8 + 4 * wg);
-#endif
             if (++cr.stage == S) { cr.stage = 0; cr.par ^= 1u; }
             float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (4 * wg < nt) {
@@ -968,12 +916,8 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
                     if (lane < 8) g.red[(size_t)(slot_base + rgl) * 64 + warp * 8 + lane] = v;
                 }
             }
-#ifdef LUM_PROBE
-            pf++;
-#endif
             if ((m2 & kM2JobEnd) && slot + p.sub * p.gpf > kChunkRG) break;
         }
-        GPROBE(3);
         named_sync(2, kConsumers);
         // fixed-order sum of the 8 warps' partials -> vals, then the epilogue for this chunk's row groups
         for (int i = tid; i < slot * kTileRows; i += kConsumers) {
@@ -987,8 +931,6 @@ __device__ __forceinline__ void gemv_consume(const GemvArgs& a, const XSource& x
         if (slot > 0) gemv_epilogue_units<PEER>(a, g.vals, g.unit_of, g.pair_of, slot, tid, kConsumers, g.scratch, 2, best);
         named_sync(2, kConsumers);
     }
-    GPROBE(7);
-    KSTAMP(a, 4);
     // (The END marker reaches the draining warps through the tensor-core warp, so they cannot finish a phase before it has:
     // the "activations quantised" barrier of the next phase never runs more than one phase ahead of its waiter.)
 }

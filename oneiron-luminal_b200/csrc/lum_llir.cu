@@ -150,6 +150,10 @@ struct lum_llir_plan {
     lum_model_desc desc{};
     std::map<int64_t, std::pair<int, int>> weight_of;   // HLIR node id of an Input -> (slot, layer)
     int64_t token_input = -1, pos_input = -1, logits_output = -1;
+    // A layer chunk (what the reference's search profiles between two GraphBreaks, src/graph.rs:633-808): whole decoder
+    // layers whose residual stream enters as an Input and leaves as an Output, without embedding and vocabulary head.
+    bool chunk = false;
+    int64_t hidden_input = -1, hidden_output = -1;
 };
 
 static void describe(const uint8_t* blob, size_t size, lum_llir_plan& out) {
@@ -166,8 +170,23 @@ static void describe(const uint8_t* blob, size_t size, lum_llir_plan& out) {
     // RowEmbed
     uint32_t emb = UINT32_MAX;
     for (uint32_t i = 0; i < nodes.size(); i++) if (M.is(i, "RowEmbed")) { emb = i; break; }
-    if (emb == UINT32_MAX) throw std::runtime_error("not a Llama-style decoder: no RowEmbed");
-    {
+    uint32_t x = emb;
+    if (emb == UINT32_MAX) {
+        // no embedding: a chunk of layers.  Its residual stream is the Input that feeds both a RowRMSNorm (as the row) and a RowAdd.
+        for (uint32_t i = 0; i < nodes.size() && x == UINT32_MAX; i++) {
+            if (!M.is(i, "Input")) continue;
+            bool normed = false, added = false;
+            for (uint32_t u : M.users(i)) {
+                if (M.is(u, "RowRMSNorm") && M.node(u).p.size() >= 5 && M.node(u).p[1].input == i) { normed = true; d.hidden = (int)eval(M.node(u).p[3].e); }
+                if (M.is(u, "RowAdd")) added = true;
+            }
+            if (normed && added) x = i;
+        }
+        if (x == UINT32_MAX) throw std::runtime_error("not a Llama-style decoder: no RowEmbed, and no Input that is both normalised and added to (a layer chunk's residual stream)");
+        out.chunk = true;
+        out.hidden_input = input_id(x);
+        d.embed_dtype = LUM_BF16;
+    } else {
         const Node& nd = M.node(emb);
         if (nd.p.size() < 6) M.stop(emb, "malformed RowEmbed");
         d.hidden = (int)eval(nd.p[5].e);
@@ -175,9 +194,14 @@ static void describe(const uint8_t* blob, size_t size, lum_llir_plan& out) {
         bind(nd.p[3].input, LUM_S_EMBED, 0);
         d.embed_dtype = input_dt(nd.p[3].input);
     }
-    uint32_t x = emb;
     int layer = 0;
     for (;;) {
+        if (out.chunk && layer > 0) {
+            // a chunk ends where the residual stream leaves as an Output
+            bool leaves = false;
+            for (uint32_t u : M.users(x)) if (M.is(u, "Output")) { out.hidden_output = M.node(u).p.at(1).i; leaves = true; }
+            if (leaves) break;
+        }
         // every residual-stream value feeds one RMSNorm (and, inside a layer, one RowAdd)
         uint32_t n1 = UINT32_MAX;
         for (uint32_t u : M.users(x)) if (M.is(u, "RowRMSNorm") && M.node(u).p.at(1).input == x) n1 = u;
@@ -185,7 +209,7 @@ static void describe(const uint8_t* blob, size_t size, lum_llir_plan& out) {
         norm_eps(M.node(n1));
         std::vector<uint32_t> mms;
         for (uint32_t u : M.users(n1)) if (M.is_matmul(u)) mms.push_back(u);
-        if (mms.size() == 1) {
+        if (mms.size() == 1 && !out.chunk) {
             // final norm + lm_head + Output
             const MatMul lm = M.matmul(mms[0]);
             if (lm.k != d.hidden) M.stop(mms[0], "lm_head K differs from the hidden size");
@@ -292,10 +316,29 @@ int32_t lum_llir_describe(const uint8_t* blob, size_t size, lum_model_desc* desc
         if (!blob || !desc_out) throw std::runtime_error("null argument");
         lum_llir_plan plan;
         describe(blob, size, plan);
+        if (plan.chunk) throw std::runtime_error("a chunk of layers (no embedding / vocabulary head): describe it with lum_llir_describe_chunk");
         *desc_out = plan.desc;
         if (token_input) *token_input = plan.token_input;
         if (pos_input) *pos_input = plan.pos_input;
         if (logits_output) *logits_output = plan.logits_output;
+        return 0;
+    } catch (const std::exception& e) {
+        if (err && err_len) snprintf(err, err_len, "%s", e.what());
+        return LUM_E_INVALID;
+    }
+}
+
+// The same for a chunk of whole layers: hyper-parameters (vocab = 0), the HLIR ids of the residual stream's Input and Output.
+int32_t lum_llir_describe_chunk(const uint8_t* blob, size_t size, lum_model_desc* desc_out, int64_t* hidden_input, int64_t* hidden_output,
+                                char* err, size_t err_len) {
+    try {
+        if (!blob || !desc_out) throw std::runtime_error("null argument");
+        lum_llir_plan plan;
+        describe(blob, size, plan);
+        if (!plan.chunk) throw std::runtime_error("a whole decoder, not a chunk: describe it with lum_llir_describe");
+        *desc_out = plan.desc;
+        if (hidden_input) *hidden_input = plan.hidden_input;
+        if (hidden_output) *hidden_output = plan.hidden_output;
         return 0;
     } catch (const std::exception& e) {
         if (err && err_len) snprintf(err, err_len, "%s", e.what());
@@ -326,3 +369,4 @@ int lum_llir_lookup(const lum_llir_plan* p, int64_t hlir_node, int* slot, int* l
 }
 const lum_model_desc* lum_llir_desc(const lum_llir_plan* p) { return &p->desc; }
 void lum_llir_io(const lum_llir_plan* p, int64_t* tok, int64_t* pos, int64_t* out) { *tok = p->token_input; *pos = p->pos_input; *out = p->logits_output; }
+int lum_llir_is_chunk(const lum_llir_plan* p) { return p->chunk ? 1 : 0; }

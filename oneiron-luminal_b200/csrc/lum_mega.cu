@@ -27,18 +27,6 @@
 
 namespace lum {
 
-#ifdef LUM_PROBE
-// Build-time probe (never in the shipped library): %globaltimer stamps of CTA 0's phase boundaries.
-__device__ unsigned long long g_mprobe[1024];
-__device__ unsigned long long g_arrive[64 * 160];
-extern "C" int lum_arrive_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_arrive, sizeof(g_arrive)); }
-#define MPROBE(i) do { if (blockIdx.x == 0 && tid == 0 && (i) < 1024) g_mprobe[i] = globaltimer_ns(); } while (0)
-extern "C" int lum_mprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_mprobe, sizeof(g_mprobe)); }
-extern "C" int lum_pprobe_read(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_pprobe, sizeof(g_pprobe)); }
-extern "C" int lum_mtl_read(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(g_tl)); }
-#else
-#define MPROBE(i) do { } while (0)
-#endif
 
 // ---- grid-wide barrier ----------------------------------------------------------------------------
 // Arrival counter in global memory, only ever incremented; barrier number b (0-based since the counter
@@ -50,9 +38,6 @@ __device__ __forceinline__ void grid_barrier(const MegaArgs& a, unsigned long lo
     named_sync(1, kWorkers);                        // all of this CTA's writes of the phase are issued
     if (tid == 0) {
         __threadfence();
-#ifdef LUM_PROBE
-        if (seq - a.gbar_base < 64) g_arrive[(seq - a.gbar_base) * 160 + blockIdx.x] = globaltimer_ns();
-#endif
         // gbar[0] counts arrivals; gbar[16] (its own 128-byte line, so polls do not queue behind the atomics) holds the
         // number of barriers completed.  The last CTA to arrive publishes the new generation; the others poll it.
         const unsigned long long old = atomicAdd(a.gbar, 1ull);
@@ -147,8 +132,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
     const bool is_producer = warp == kProducerWarp, is_mma = warp == kMmaWarp;
     const bool is_worker = warp < kWorkers / 32;
     ProducerRing pring{0, 0u, 0};
-    ConsumerRing cring{0, 0u, 0u, 0u, 0};
-    MmaRing mring{0, 0u, 0u, 0u, 0u, 0};
+    ConsumerRing cring{0, 0u, 0u, 0u};
+    MmaRing mring{0, 0u, 0u, 0u, 0u};
     bool issuing = true;
     unsigned long long seq = a.gbar_base;             // grid barriers passed so far
     unsigned long long pseq = a.gbar_base;            // running phase number: picks the job-claim counter of each phase
@@ -187,38 +172,26 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_mega(const MegaArgs a)
             pseq++;
             if (is_producer) {
                 if (streams && lane == 0 && producing) {
-#ifdef LUM_PROBE
-                    if (t == 1 && blockIdx.x == 0) g_mprobe[512 + ph * 2] = globaltimer_ns();
-#endif
                     producing = gemv_produce(ga, plan, g, pring, cta, ncta, ctr, a.status);
-#ifdef LUM_PROBE
-                    if (t == 1 && blockIdx.x == 0) g_mprobe[512 + ph * 2 + 1] = globaltimer_ns();
-#endif
                 }
             } else if (is_mma) {
                 if (streams && lane == 0 && issuing) issuing = gemv_mma_issue(ga, plan, g, mring, tmem, a.status);
             } else if (!streams) {
                 // RoPE + cache append + attention
-                if (t == 1) MPROBE(ph * 3);
                 if (!s_abort) attn_phase<HD, GM, BF16>(a, L, (unsigned char*)g.xq, pos, tid);
-                if (t == 1) MPROBE(ph * 3 + 1);
                 grid_barrier(a, seq, &s_abort, tid);
-                if (t == 1) MPROBE(ph * 3 + 2);
             } else {
                 XSource xs{};
                 if (ph == 0) { xs.table = a.embed; xs.table_kind = a.embed_kind; xs.token = tok; xs.x_out = a.x; }   // the embedding row is x
                 else xs.x = p == 2 ? a.attn : p == 4 ? a.h : a.x;
                 ArgBest best{-INFINITY, -1};
-                if (t == 1) MPROBE(ph * 3);
                 if (!s_abort) {
                     GainRegs gr;
                     gemv_gain_preload(ga, tid, gr);
                     gemv_consume(ga, xs, cta == 0, plan, g, cring, tid, tmem, a.status, &best, gr);
                 }
-                if (t == 1) MPROBE(ph * 3 + 1);
                 if (p == 5 && tid == 0) { a.part_val[cta] = best.v; a.part_idx[cta] = best.i; }
                 grid_barrier(a, seq, &s_abort, tid);
-                if (t == 1) MPROBE(ph * 3 + 2);
                 if (p == 5) {
                     // every CTA folds the per-CTA maxima itself: all of them need the token for the next embedding row
                     if (warp == 0) {

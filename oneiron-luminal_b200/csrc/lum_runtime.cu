@@ -19,6 +19,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <dlfcn.h>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -35,6 +36,8 @@ void lum_llir_free_plan(lum_llir_plan* p);
 int lum_llir_lookup(const lum_llir_plan* p, int64_t hlir_node, int* slot, int* layer);
 const lum_model_desc* lum_llir_desc(const lum_llir_plan* p);
 void lum_llir_io(const lum_llir_plan* p, int64_t* tok, int64_t* pos, int64_t* out);
+int lum_llir_is_chunk(const lum_llir_plan* p);
+uint32_t* lum_static_sample_status();   // csrc/lum_gemv.cu
 
 namespace {
 
@@ -137,6 +140,10 @@ struct lum_rt {
     std::vector<int32_t> tokens_in;
 
     lum_llir_plan* llir = nullptr;    // set by lum_load_llir: which Input node feeds which weight slot
+    std::map<int64_t, size_t> dummy_inputs;   // lum_alloc_dummy_input calls made before a graph was loaded: node -> elements
+    bool body_only = false;           // profiling a chunk of layers: steps never run the vocabulary head
+    uint64_t n_tokens_run = 0, n_launches = 0;
+    double last_profile_usec = 0.0;
 
     // tensor parallel
     void* comm = nullptr;             // ncclComm_t
@@ -232,6 +239,8 @@ void free_model(lum_rt* rt) {
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
+    rt->launches_full = 0;
+    rt->attn_cnt = nullptr; rt->am_cnt = nullptr;
     rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr; rt->step_ctr = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
     rt->allocs.clear();
@@ -282,6 +291,11 @@ int check_status(lum_rt* rt) {
     CU(rt, cudaStreamSynchronize(rt->stream));
     if (st) {
         cudaMemsetAsync(rt->status, 0, sizeof st, rt->stream);
+        // kernels that gave up may have left their arrival tickets and job-claim counters mid-count: start them over
+        if (rt->step_ctr) cudaMemsetAsync(rt->step_ctr, 0, ((size_t)4 * rt->d.n_layers + 1) * sizeof(unsigned int), rt->stream);
+        if (rt->attn_cnt) cudaMemsetAsync(rt->attn_cnt, 0, (size_t)rt->nkv_l * 4, rt->stream);
+        if (rt->am_cnt) cudaMemsetAsync(rt->am_cnt, 0, 4, rt->stream);
+        if (rt->peer_ticket) cudaMemsetAsync(rt->peer_ticket, 0, 4, rt->stream);
         if (rt->gbar) {   // an aborted persistent launch leaves its barrier count short: start over
             cudaMemsetAsync(rt->gbar, 0, 32 * sizeof(unsigned long long), rt->stream);
             cudaMemsetAsync(rt->abort_flag, 0, sizeof(int), rt->stream);
@@ -506,7 +520,7 @@ int run_step(lum_rt* rt, bool with_head) {
         CU(rt, cudaGraphLaunch(with_head ? rt->g_full : rt->g_body, rt->stream));
         return 0;
     }
-    return issue_step(rt, with_head, rt->cfg.use_pdl != 0, &rt->launches_full);
+    return issue_step(rt, with_head, rt->cfg.use_pdl != 0, with_head ? &rt->launches_full : nullptr);
 }
 
 // n tokens in one go.  forced: host token ids (prompt processing: sample only after the last) or null (feed
@@ -527,6 +541,8 @@ int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
         a.gbar_base = rt->gbar_base;
         CU(rt, launch_mega(a, rt->sm_count, rt->stream));
         rt->gbar_base += mega_barriers(a);
+        rt->n_tokens_run += (uint64_t)n;
+        rt->n_launches += 1;
         return 0;
     }
     for (int i = 0; i < n; i++) {
@@ -534,8 +550,11 @@ int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
             set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, pos0 + i, forced[i], 0, 1, 0);
             CU(rt, cudaGetLastError());
         }
-        if (int r = run_step(rt, !forced || i + 1 == n)) return r;
+        const bool head = !rt->body_only && (!forced || i + 1 == n);
+        if (int r = run_step(rt, head)) return r;
+        rt->n_launches += (uint64_t)(rt->launches_full > 0 ? rt->launches_full - (head ? 0 : 1) : 0);
     }
+    rt->n_tokens_run += (uint64_t)n;
     return 0;
 }
 
@@ -661,6 +680,11 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
     lum_llir_plan* plan = nullptr;
     std::string err;
     if (int r = lum_llir_make_plan(blob, size, &plan, &err)) return fail(rt, r, "load_llir: %s", err.c_str());
+    if (lum_llir_is_chunk(plan)) {
+        lum_llir_free_plan(plan);
+        return fail(rt, LUM_E_INVALID, "load_llir: the graph is a chunk of layers (no embedding / vocabulary head); a chunk can be profiled "
+                    "(lum_profile_llir), the graph to load is the stitched one");
+    }
     lum_model_desc d = *lum_llir_desc(plan);
     d.max_seq = max_seq; d.kv_dtype = kv_dtype; d.max_new_tokens = max_new_tokens;
     d.tp_size = rt->tp_size; d.tp_rank = rt->tp_rank;
@@ -668,6 +692,11 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
     if (r) { lum_llir_free_plan(plan); return r; }
     if (rt->llir) lum_llir_free_plan(rt->llir);
     rt->llir = plan;
+    // dummy inputs asked for before the graph existed
+    std::map<int64_t, size_t> pending;
+    pending.swap(rt->dummy_inputs);
+    for (const auto& kv : pending)
+        if (int r2 = lum_alloc_dummy_input(rt, kv.first, kv.second)) return r2;
     return 0;
 }
 
@@ -699,6 +728,175 @@ int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n)
     lum_llir_io(rt->llir, &tok, &pos, &out);
     if (hlir_node != out) return fail(rt, LUM_E_INVALID, "get_output: node %lld is not the graph's Output", (long long)hlir_node);
     return lum_get_logits(rt, host_out, n);
+}
+
+
+// ---- the rest of the `Runtime` trait as `Graph::search` uses it -------------------------------------------------------
+
+int32_t lum_set_input_device_ptr(lum_rt* rt, int64_t hlir_node, const void* device_ptr, size_t bytes, uint32_t dtype) {
+    if (!rt || !rt->llir || !rt->has_model) return fail(rt, LUM_E_INVALID, "set_input_device_ptr: no graph loaded (lum_load_llir)");
+    if (!device_ptr) return fail(rt, LUM_E_INVALID, "set_input_device_ptr: null pointer");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    int64_t tok, pos, out;
+    lum_llir_io(rt->llir, &tok, &pos, &out);
+    if (hlir_node == tok || hlir_node == pos) {
+        // a handful of ids: bring them to the host and take the ordinary path (the step's kernels read the token from the
+        // device-resident decode state, which the host sets per token)
+        if (dtype != LUM_INT || bytes % 4) return fail(rt, LUM_E_INVALID, "set_input_device_ptr: ids must be Int");
+        std::vector<int32_t> ids(bytes / 4);
+        CU(rt, cudaStreamSynchronize(rt->stream));
+        CU(rt, cudaMemcpy(ids.data(), device_ptr, bytes, cudaMemcpyDeviceToHost));
+        return lum_set_input(rt, hlir_node, ids.data(), bytes, dtype);
+    }
+    // weights: the same repacking path, reading the wire bytes from device memory
+    return lum_set_input(rt, hlir_node, device_ptr, bytes, dtype);
+}
+
+int32_t lum_alloc_dummy_input(lum_rt* rt, int64_t hlir_node, size_t n_elems) {
+    if (!rt) return LUM_E_INVALID;
+    if (!rt->llir || !rt->has_model) { rt->dummy_inputs[hlir_node] = n_elems; return 0; }    // applied when the graph arrives
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    int64_t tok, pos, out;
+    lum_llir_io(rt->llir, &tok, &pos, &out);
+    if (hlir_node == tok) {
+        if (n_elems == 0 || n_elems > (size_t)rt->d.max_seq) return fail(rt, LUM_E_INVALID, "alloc_dummy_input: %zu token ids do not fit the cache capacity %d", n_elems, rt->d.max_seq);
+        rt->tokens_in.assign(n_elems, 0);
+        rt->dim_s = n_elems;
+        return 0;
+    }
+    if (hlir_node == pos) return 0;                       // positions follow from 'p'
+    int slot = 0, layer = 0;
+    if (!lum_llir_lookup(rt->llir, hlir_node, &slot, &layer)) return fail(rt, LUM_E_INVALID, "alloc_dummy_input: node %lld is not an Input of the loaded graph", (long long)hlir_node);
+    Tensor* t = slot_tensor(rt, slot, layer);
+    if (!t) return fail(rt, LUM_E_INVALID, "alloc_dummy_input: slot %d / layer %d does not exist in this model", slot, layer);
+    if (n_elems != t->full_rows * t->full_cols)
+        return fail(rt, LUM_E_INVALID, "alloc_dummy_input: node %lld holds %zu elements, asked for %zu", (long long)hlir_node, t->full_rows * t->full_cols, n_elems);
+    // the tensor's storage exists since load_llir; give it defined contents of the right distribution
+    const uint64_t tid = tensor_id(slot, slot_layer_for_id(rt, slot, layer));
+    cudaError_t e;
+    const bool gains = slot == LUM_S_ATTN_NORM || slot == LUM_S_MLP_NORM || slot == LUM_S_FINAL_NORM || slot == LUM_S_Q_NORM || slot == LUM_S_K_NORM;
+    if (t->kind == WK_Q8) e = launch_synth_q8(0x5eedull, tid, (int8_t*)t->w, t->s, t->rows, t->cols, t->row0, t->col0, t->full_cols, t->kc, rt->stream);
+    else e = launch_synth_normal(0x5eedull, tid, t->w, t->kind, t->rows, t->cols, t->row0, t->col0, t->full_cols, gains ? 1 : 0, rt->stream);
+    if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "alloc_dummy_input: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int32_t lum_clear_intermediates(lum_rt* rt) {
+    if (!rt) return LUM_E_INVALID;
+    rt->dummy_inputs.clear();
+    if (!rt->has_model) return 0;
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const lum_model_desc& d = rt->d;
+    const size_t qd_l = (size_t)rt->nq_l * d.head_dim, kvd_l = (size_t)rt->nkv_l * d.head_dim;
+    CU(rt, cudaMemsetAsync(rt->x, 0, (size_t)d.hidden * 4, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->x2, 0, (size_t)d.hidden * 4, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->part, 0, (size_t)2 * d.hidden * 4, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->qkv, 0, (qd_l + 2 * kvd_l) * 4, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->attn, 0, qd_l * 4, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->h, 0, (size_t)rt->ffn_l * 4, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->logits, 0, (size_t)rt->vocab_l * 4, rt->stream));
+    if (int r = lum_kv_reset(rt)) return r;
+    set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, 0, 0, 0, 1, 1);
+    CU(rt, cudaGetLastError());
+    rt->tokens_in.clear();
+    rt->dim_s = 1; rt->dim_p = 0;
+    return 0;
+}
+
+int32_t lum_profile_llir(lum_rt* rt, const uint8_t* blob, size_t size, uint64_t s_dim, uint64_t p_dim, int32_t trials, double* usec,
+                         char* display, size_t display_len) {
+    if (!rt || !blob) return fail(rt, LUM_E_INVALID, "profile_llir: null argument");
+    if (trials <= 0) trials = 1;
+    if (s_dim == 0) s_dim = 1;
+    lum_llir_plan* plan = nullptr;
+    std::string err;
+    if (int r = lum_llir_make_plan(blob, size, &plan, &err)) return fail(rt, r, "profile_llir: %s", err.c_str());
+    const bool chunk = lum_llir_is_chunk(plan) != 0;
+    lum_model_desc d = *lum_llir_desc(plan);
+    lum_llir_free_plan(plan);
+    if (p_dim + s_dim + 1 > (1u << 20)) return fail(rt, LUM_E_INVALID, "profile_llir: context too long");
+    d.max_seq = (int32_t)(p_dim + s_dim + 1);
+    d.kv_dtype = rt->has_model ? rt->d.kv_dtype : LUM_BF16;
+    d.max_new_tokens = 16;
+    d.tp_size = 1; d.tp_rank = 0;
+    if (chunk) { d.vocab = 256; d.tied_head = 0; }          // the chunk has no head: a small stand-in that never runs
+    // A scratch runtime on the same device: candidates are timed on seeded stand-in weights and never touch the loaded model.
+    lum_rt* tmp = nullptr;
+    lum_config c = rt->cfg;
+    c.use_mega = 0;
+    if (int r = lum_create(&c, &tmp)) return fail(rt, r, "profile_llir: %s", g_create_error.c_str());
+    auto bail = [&](int code) { const std::string msg = tmp->err; lum_destroy(tmp); return fail(rt, code, "profile_llir: %s", msg.c_str()); };
+    if (int r = lum_model_init(tmp, &d)) return bail(r);
+    if (int r = lum_model_synth(tmp, 0x5eedull)) return bail(r);
+    tmp->body_only = chunk;
+    std::vector<int32_t> ids((size_t)s_dim, 0);
+    cudaEvent_t e0, e1;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) { tmp->err = "cudaEventCreate failed"; return bail(LUM_E_CUDA); }
+    int r = run_tokens(tmp, (int)s_dim, ids.data(), (int)p_dim);          // warm-up; also captures the graphs
+    if (!r) {
+        cudaEventRecord(e0, tmp->stream);
+        for (int i = 0; i < trials && !r; i++) r = run_tokens(tmp, (int)s_dim, ids.data(), (int)p_dim);
+        cudaEventRecord(e1, tmp->stream);
+    }
+    cudaStreamSynchronize(tmp->stream);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (!r) r = check_status(tmp);
+    if (r) return bail(r);
+    lum_destroy(tmp);
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const double us = (double)ms * 1000.0 / trials;
+    rt->last_profile_usec = us;
+    if (usec) *usec = us;
+    if (display && display_len)
+        snprintf(display, display_len, "%.3f ms per execute (%s, %d layer%s, s=%llu p=%llu)", us / 1000.0, chunk ? "chunk" : "whole decoder", d.n_layers,
+                 d.n_layers == 1 ? "" : "s", (unsigned long long)s_dim, (unsigned long long)p_dim);
+    return 0;
+}
+
+static int kv_span(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, size_t bytes, void** dev, const char* who) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "%s: no model", who);
+    if (layer < 0 || layer >= rt->d.n_layers || rows < 0 || rows > rt->d.max_seq || (kind != 0 && kind != 1)) return fail(rt, LUM_E_INVALID, "%s: bad layer / kind / rows", who);
+    const size_t want = (size_t)rows * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+    if (bytes != want) return fail(rt, LUM_E_INVALID, "%s: %d rows are %zu bytes in the cache's own type, got %zu", who, rows, want, bytes);
+    *dev = kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc;
+    return 0;
+}
+int32_t lum_kv_save(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, void* host_out, size_t bytes) {
+    void* dev = nullptr;
+    if (int r = kv_span(rt, layer, kind, rows, bytes, &dev, "kv_save")) return r;
+    if (!host_out) return fail(rt, LUM_E_INVALID, "kv_save: null output");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    if (bytes) CU(rt, cudaMemcpyAsync(host_out, dev, bytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+int32_t lum_kv_load(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, const void* host, size_t bytes) {
+    void* dev = nullptr;
+    if (int r = kv_span(rt, layer, kind, rows, bytes, &dev, "kv_load")) return r;
+    if (!host) return fail(rt, LUM_E_INVALID, "kv_load: null input");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    if (bytes) CU(rt, cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
+int32_t lum_get_stats(const lum_rt* rt, lum_stats* out) {
+    if (!rt || !out) return LUM_E_INVALID;
+    memset(out, 0, sizeof *out);
+    out->tokens_executed = rt->n_tokens_run;
+    out->kernel_launches = rt->n_launches;
+    out->last_profile_usec = rt->last_profile_usec;
+    if (rt->has_model) {
+        uint64_t wb = 0;
+        lum_model_weight_bytes(rt, &wb);
+        out->weight_bytes_per_token = wb;
+        out->kv_bytes_per_position = (uint64_t)rt->d.n_layers * 2 * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+        out->launches_per_step = rt->launches_full;
+    }
+    return 0;
 }
 
 int32_t lum_tp_unique_id(uint8_t* out128) {
@@ -911,7 +1109,7 @@ int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void
         if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "set_weight: staging buffer: %s", cudaGetErrorString(e));
         // copies go on the runtime's own (non-blocking) stream: a legacy-stream copy from pageable memory may return
         // before its DMA has landed and would not be ordered against kernels on this stream
-        e = cudaMemcpy2DAsync(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice, rt->stream);
+        e = cudaMemcpy2DAsync(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyDefault, rt->stream);   // host or device source
         if (t->kc) {
             // wire blocks -> temporary planes -> packed tile stream
             void* planes = nullptr;
@@ -932,7 +1130,7 @@ int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void
         cudaFree(tmp);
         if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "set_weight: %s", cudaGetErrorString(e));
     } else {
-        CU(rt, cudaMemcpy2DAsync(t->w, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyHostToDevice, rt->stream));
+        CU(rt, cudaMemcpy2DAsync(t->w, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyDefault, rt->stream));
         CU(rt, cudaStreamSynchronize(rt->stream));
     }
     return 0;
@@ -1139,6 +1337,7 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     if (r) return r;
     if (int s = check_status(rt)) return s;
     const double us = (double)ms * 1000.0 / trials;
+    rt->last_profile_usec = us;
     if (usec) *usec = us;
     if (display && display_len)
         snprintf(display, display_len, "%.3f ms/token; attention: %d splits per KV head, %s merge", us / 1000.0, rt->n_splits,
@@ -1148,7 +1347,9 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
 
 int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n) {
     if (!rt || !rt->has_model || !n) return LUM_E_INVALID;
-    *n = (rt->mega_ok && rt->use_mega) ? 1 : rt->tp_size > 1 ? 1 + 5 * rt->d.n_layers + 1 + 1 /* pick */ : 1 + 5 * rt->d.n_layers + 1;
+    if (rt->mega_ok && rt->use_mega) { *n = 1; return 0; }
+    if (rt->launches_full > 0) { *n = rt->launches_full; return 0; }      // counted while the step was issued / captured
+    *n = rt->tp_size > 1 ? 1 + 5 * rt->d.n_layers + 1 + 1 /* pick */ : 1 + 5 * rt->d.n_layers + 1;
     return 0;
 }
 
@@ -1164,9 +1365,9 @@ static int cur_sm_count() {
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     return n > 0 ? n : 1;
 }
+static uint32_t* g_op_words[64] = {nullptr};      // one status word per device for the stand-alone operators
 static uint32_t* op_status_word() {
-    // one status word per device for the stand-alone operators
-    static uint32_t* words[64] = {nullptr};
+    uint32_t** words = g_op_words;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return nullptr;
@@ -1211,8 +1412,9 @@ int32_t lum_op_gemv_q8_0_packed(const void* packed, int32_t n, int32_t k, const 
 
 // per-device scratch of lum_op_sample_q8_0: per-CTA maxima, arrival ticket, status word (allocated on first use)
 struct SampleScratch { float* val; int* idx; unsigned int* counter; uint32_t* status; };
+static SampleScratch g_sample_scratch[64] = {};
 static SampleScratch* sample_scratch() {
-    static SampleScratch per_dev[64] = {};
+    SampleScratch* per_dev = g_sample_scratch;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return nullptr;
@@ -1237,6 +1439,29 @@ int32_t lum_op_sample_q8_0(const void* packed, int32_t n, int32_t k, const float
     a.part_val = sc->val; a.part_idx = sc->idx; a.counter = sc->counter; a.status = sc->status; a.pair_out = best; a.row_offset = 0;
     const cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : op_fail("sample_q8_0", e);
+}
+
+int32_t lum_op_status(void* stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { g_create_error = "op_status: cannot query the current device"; return LUM_E_CUDA; }
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return op_fail("op_status", e);
+    uint32_t* words[3] = {g_op_words[dev], g_sample_scratch[dev].status, lum_static_sample_status()};
+    uint32_t seen = 0;
+    for (uint32_t* w : words) {
+        if (!w) continue;
+        uint32_t v = 0;
+        e = cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return op_fail("op_status", e);
+        if (v) { seen |= v; cudaMemset(w, 0, 4); }
+    }
+    if (seen) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "a stand-alone operator reported device status 0x%x (a bounded wait ran out)", seen);
+        g_create_error = buf;
+        return LUM_E_DEVICE;
+    }
+    return 0;
 }
 
 int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tid, int32_t n, int32_t k, void* packed, void* stream) {

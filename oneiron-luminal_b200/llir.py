@@ -148,7 +148,25 @@ def contiguous(shape: Sequence[int]) -> List[int]:
 F32, F16, BF16, INT, BOOL, NVFP4, MXFP4, Q8_0 = range(8)
 
 
-def build_llama_llir(desc, shuffle_qkv: bool = False):
+def build_llama_chunk_llir(desc, n_layers: int = 1):
+    """A chunk of ``n_layers`` whole decoder layers as the reference's search cuts it out between two GraphBreaks
+    (src/graph.rs:633-808) and hands to ``Runtime::profile``: the residual stream enters as an Input and leaves as an
+    Output; no embedding, no final norm, no vocabulary head.  Returns ``(blob, ids)`` like ``build_llama_llir``."""
+    sub = _Shape(desc, n_layers)
+    return build_llama_llir(sub, chunk=True)
+
+
+class _Shape:
+    """A model description with another layer count (anything with the fields of ``ModelDesc``)."""
+
+    def __init__(self, desc, n_layers):
+        for f in ("hidden", "head_dim", "n_q_heads", "n_kv_heads", "ffn", "vocab", "weight_dtype", "embed_dtype", "rms_eps",
+                  "rope_theta", "rope_style", "qk_norm", "tied_head"):
+            setattr(self, f, getattr(desc, f))
+        self.n_layers = n_layers
+
+
+def build_llama_llir(desc, shuffle_qkv: bool = False, chunk: bool = False):
     """The block-level LLIR a search produces for the Llama example (examples/llama/src/model.rs:40-215 lowered
     through the block ops of crates/luminal_cuda/src/block/ops.rs), for the hyper-parameters in ``desc`` (anything
     with the fields of ``ModelDesc``).
@@ -187,10 +205,15 @@ def build_llama_llir(desc, shuffle_qkv: bool = False):
     def rope(x, n, pos):
         return b.add("RowRope", elist(["s"]), inp(x), elist([n]), expr(n), inp(pos), flt(desc.rope_theta), integer(desc.rope_style))
 
-    tok = new_input("tokens", "input", INT)
-    pos = new_input("positions", "token_ids", INT)
-    emb = new_input("embed", "model.embed_tokens.weight", edt)
-    x = b.add("RowEmbed", elist(["s"]), inp(tok), elist([1]), inp(emb), elist([H]), expr(H))
+    pos = None
+    if chunk:
+        pos = new_input("positions", "token_ids", INT)
+        x = new_input("hidden_in", "chunk.hidden_in", F32)
+    else:
+        tok = new_input("tokens", "input", INT)
+        pos = new_input("positions", "token_ids", INT)
+        emb = new_input("embed", "model.embed_tokens.weight", edt)
+        x = b.add("RowEmbed", elist(["s"]), inp(tok), elist([1]), inp(emb), elist([H]), expr(H))
     for l in range(desc.n_layers):
         pre = f"model.layers.{l}."
         g1 = new_input(("attn_norm", l), pre + "input_layernorm.weight", F32)
@@ -221,6 +244,10 @@ def build_llama_llir(desc, shuffle_qkv: bool = False):
         sw = b.add("RowSwishMul", elist(["s"]), inp(gate), elist([F]), inp(up), elist([F]), expr(F), expr(F))
         dn = matmul(sw, wd, H, F)
         x = b.add("RowAdd", elist(["s"]), inp(x1), elist([H]), inp(dn), elist([H]), elist([H]), expr(H))
+    if chunk:
+        ids["hidden_out"] = next_id[0]
+        b.output(x, ids["hidden_out"])
+        return b.blob(), ids
     gf = new_input("final_norm", "model.norm.weight", F32)
     nf = rmsnorm(x, gf)
     if desc.tied_head:

@@ -59,6 +59,14 @@ class ModelDesc(C.Structure):
         return d
 
 
+class Stats(C.Structure):
+    """Mirror of ``lum_stats`` (include/lum_b200.h)."""
+
+    _fields_ = [("tokens_executed", C.c_uint64), ("kernel_launches", C.c_uint64), ("weight_bytes_per_token", C.c_uint64),
+                ("kv_bytes_per_position", C.c_uint64), ("launches_per_step", C.c_int32), ("reserved", C.c_int32),
+                ("last_profile_usec", C.c_double)]
+
+
 def _desc(**kw) -> ModelDesc:
     d = ModelDesc()
     base = dict(max_seq=4096, rms_eps=1e-5, rope_style=0, qk_norm=0, tied_head=0, max_new_tokens=4096, tp_size=1, tp_rank=0)
@@ -81,6 +89,10 @@ CONFIGS: Dict[str, ModelDesc] = {
     "llama3_8b_q8_2layer": _desc(n_layers=2, hidden=4096, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=4096,
                                  max_seq=256, rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"],
                                  kv_dtype=DTYPE["bf16"]),
+    # Qwen3-4B shape: per-head q/k RMSNorm, split-half RoPE, theta 1e6, eps 1e-6, head tied to the bf16 embedding
+    "qwen3_4b_q8": _desc(n_layers=36, hidden=2560, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=9728, vocab=151936,
+                         max_seq=4096, rms_eps=1e-6, rope_theta=1000000.0, rope_style=1, qk_norm=1, tied_head=1,
+                         weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),
     # Qwen3-4B layer shape (per-head q/k RMSNorm, split-half RoPE, theta 1e6, eps 1e-6, head tied to the embedding) cut to
     # 2 layers and a small vocabulary: hidden 2560 = 5 tiles, ffn 9728 = 19 tiles per row group
     "qwen3_4b_q8_2layer": _desc(n_layers=2, hidden=2560, n_q_heads=32, n_kv_heads=8, head_dim=128, ffn=9728, vocab=4096,
@@ -149,6 +161,15 @@ def load_library() -> C.CDLL:
         "lum_llir_describe": (i32, [vp, sz, P(ModelDesc), P(C.c_int64), P(C.c_int64), P(C.c_int64), C.c_char_p, sz]),
         "lum_load_llir": (i32, [vp, vp, sz, i32, u32, i32]),
         "lum_set_input": (i32, [vp, C.c_int64, vp, sz, u32]),
+        "lum_set_input_device_ptr": (i32, [vp, C.c_int64, vp, sz, u32]),
+        "lum_alloc_dummy_input": (i32, [vp, C.c_int64, sz]),
+        "lum_clear_intermediates": (i32, [vp]),
+        "lum_profile_llir": (i32, [vp, vp, sz, u64, u64, i32, P(C.c_double), C.c_char_p, sz]),
+        "lum_llir_describe_chunk": (i32, [vp, sz, P(ModelDesc), P(C.c_int64), P(C.c_int64), C.c_char_p, sz]),
+        "lum_kv_save": (i32, [vp, i32, i32, i32, vp, sz]),
+        "lum_kv_load": (i32, [vp, i32, i32, i32, vp, sz]),
+        "lum_get_stats": (i32, [vp, P(Stats)]),
+        "lum_op_status": (i32, [vp]),
         "lum_get_output": (i32, [vp, C.c_int64, P(C.c_float), sz]),
         "lum_kv_reset": (i32, [vp]),
         "lum_kv_read": (i32, [vp, i32, i32, i32, P(C.c_float)]),
@@ -203,6 +224,27 @@ def describe_llir(blob: bytes):
     if rc != 0:
         raise LumError(rc, err.value.decode())
     return d, tok.value, pos.value, out.value
+
+
+def describe_llir_chunk(blob: bytes):
+    """Host-only: ``(ModelDesc, hidden_input, hidden_output)`` of a chunk of whole layers (what the reference's search
+    profiles between two GraphBreaks); raises ``LumError`` for anything else."""
+    lib = load_library()
+    d = ModelDesc()
+    hin, hout = C.c_int64(-1), C.c_int64(-1)
+    err = C.create_string_buffer(256)
+    buf = C.create_string_buffer(blob, len(blob))
+    rc = lib.lum_llir_describe_chunk(buf, len(blob), C.byref(d), C.byref(hin), C.byref(hout), err, 256)
+    if rc != 0:
+        raise LumError(rc, err.value.decode())
+    return d, hin.value, hout.value
+
+
+def mbu(stats: "Stats", usec_per_token: float, context: int, peak_gb_s: float) -> float:
+    """Memory-bandwidth utilisation of a decode step, the way the reference's bench crate states it
+    (crates/luminal_bench/src/metrics.rs:13-60): bytes the step must move / time / peak bandwidth."""
+    bytes_tok = stats.weight_bytes_per_token + stats.kv_bytes_per_position * (context + 1)
+    return bytes_tok / (usec_per_token * 1e-6) / (peak_gb_s * 1e9)
 
 
 class B200Runtime:
@@ -303,6 +345,45 @@ class B200Runtime:
     def set_input(self, hlir_node: int, data, dtype: str) -> None:
         """``set_data(node_id, data)`` (crates/luminal_cuda/src/runtime.rs:160-165) by HLIR node id of an Input."""
         self._ck(self._lib.lum_set_input(self._h, hlir_node, data.ctypes.data_as(C.c_void_p), data.nbytes, DTYPE[dtype]))
+
+    def set_input_device_ptr(self, hlir_node: int, device_ptr: int, nbytes: int, dtype: str) -> None:
+        """``set_data`` with ``CudaInput::Ptr`` (crates/luminal_cuda/src/runtime.rs:36-39): the bytes are already on the device."""
+        self._ck(self._lib.lum_set_input_device_ptr(self._h, hlir_node, C.c_void_p(device_ptr), nbytes, DTYPE[dtype]))
+
+    def allocate_dummy_input(self, hlir_node: int, n_elems: int) -> None:
+        """``Runtime::allocate_dummy_input`` (src/op.rs:24-27)."""
+        self._ck(self._lib.lum_alloc_dummy_input(self._h, hlir_node, n_elems))
+
+    def clear_intermediate_buffers(self) -> None:
+        """``Runtime::clear_intermediate_buffers`` (src/op.rs:28-29)."""
+        self._ck(self._lib.lum_clear_intermediates(self._h))
+
+    def profile_llir(self, blob: bytes, dyn_map: Optional[Dict[str, int]] = None, trials: int = 4):
+        """``Runtime::profile(&LLIRGraph, &dyn_map, trials)`` (src/op.rs:18-23): ``(usec per execute, display string)`` for a
+        whole decoder or a chunk of layers, timed on a scratch runtime with stand-in weights."""
+        dm = dyn_map or {}
+        us = C.c_double()
+        text = C.create_string_buffer(160)
+        buf = C.create_string_buffer(blob, len(blob))
+        self._ck(self._lib.lum_profile_llir(self._h, buf, len(blob), int(dm.get("s", 1)), int(dm.get("p", 0)), trials, C.byref(us), text, 160))
+        return us.value, text.value.decode()
+
+    def kv_save(self, layer: int, kind: str, rows: int):
+        """Rows [0, rows) of one layer's K or V cache as raw bytes in the cache's own element type."""
+        import numpy as np
+        d = self.desc
+        esz = 2 if d.kv_dtype == DTYPE["bf16"] else 4
+        out = np.empty(rows * (d.n_kv_heads // max(1, d.tp_size)) * d.head_dim * esz, dtype=np.uint8)
+        self._ck(self._lib.lum_kv_save(self._h, layer, 0 if kind == "k" else 1, rows, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
+    def kv_load(self, layer: int, kind: str, rows: int, data) -> None:
+        self._ck(self._lib.lum_kv_load(self._h, layer, 0 if kind == "k" else 1, rows, data.ctypes.data_as(C.c_void_p), data.nbytes))
+
+    def stats(self) -> Stats:
+        st = Stats()
+        self._ck(self._lib.lum_get_stats(self._h, C.byref(st)))
+        return st
 
     def get_output(self, hlir_node: int):
         """``get_f32(node_id)`` (crates/luminal_cuda/src/runtime.rs:168-204) for the graph's Output: last-row logits."""

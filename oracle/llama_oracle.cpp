@@ -473,6 +473,26 @@ void orc_model_kv_reset(void* h) {
     for (auto& v : m.kc) std::fill(v.begin(), v.end(), 0.0f);
     for (auto& v : m.vc) std::fill(v.begin(), v.end(), 0.0f);
 }
+// Fill cache rows [0, rows) of every layer with seeded values of the size real keys and values have (N(0,1), rounded to
+// bfloat16 when the cache is): lets a timing run start at a long context without computing the prompt first.
+int orc_model_kv_fill(void* h, uint64_t seed, int rows) {
+    Model& m = *(Model*)h;
+    if (rows < 0 || rows > m.c.max_seq) { m.err = "kv_fill: rows outside the cache"; return -1; }
+    const size_t row = (size_t)m.c.n_kv_heads * m.c.head_dim;
+    for (int l = 0; l < m.c.n_layers; l++) {
+        const uint64_t kk = orc::rng_key(seed, (1ull << 24) + 2ull * (uint64_t)l), kv = orc::rng_key(seed, (1ull << 24) + 2ull * (uint64_t)l + 1);
+        float* K = m.kc[(size_t)l].data();
+        float* V = m.vc[(size_t)l].data();
+        orc::parallel_for((long)(row * rows), 1 << 14, [&](long a, long b) {
+            for (long i = a; i < b; i++) {
+                const float k = orc::rng_weight_f32(kk, (uint64_t)i) * 50.0f, v = orc::rng_weight_f32(kv, (uint64_t)i) * 50.0f;
+                K[i] = m.c.kv_bf16 ? orc::round_bf16(k) : k;
+                V[i] = m.c.kv_bf16 ? orc::round_bf16(v) : v;
+            }
+        });
+    }
+    return 0;
+}
 // Copy one layer's cache rows [0, rows) as f32: kind 0 = K, 1 = V.
 int orc_model_kv_read(void* h, int layer, int kind, int rows, float* out) {
     Model& m = *(Model*)h;

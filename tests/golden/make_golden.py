@@ -4,10 +4,18 @@ The reference cannot run here (Rust, no toolchain) and holds no model-level gold
 these fixtures are the oracle's own outputs on seeded inputs.  They pin the oracle against silent drift and
 give the GPU tests a fixed target that does not depend on rebuilding the oracle on the GPU box.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py                 # the small cases (seconds)
+    python tests/golden/make_golden.py llama3_8b_q8    # a full-size case (tens of minutes of CPU time, ~12 GB of RAM)
+    python tests/golden/make_golden.py qwen3_4b_q8
+
+Full-size cases are the configurations the benchmark numbers are quoted on: whole model, whole vocabulary, the
+benchmark's seed and prompt.  They hold the prompt, the first 32 greedy tokens with their top-1/top-2 margins,
+the logits row that follows the prompt and the one that produced the 32nd token, and a few K/V cache rows of
+the first and the last layer.
 """
 import os
 import sys
+import time
 
 import numpy as np
 
@@ -25,9 +33,55 @@ CASES = {
     "small_q8": ("small_q8", 99, 12, 24),
 }
 
+# name: (config, seed, prompt tokens, greedy steps); the seed and prompt lengths are bench.py's
+FULL_SEED = 20240607
+FULL_CASES = {
+    "llama3_8b_q8": ("llama3_8b_q8", FULL_SEED, 512, 32),
+    "qwen3_4b_q8": ("qwen3_4b_q8", FULL_SEED, 1024, 32),
+}
+
+
+def full_case(pkg, name):
+    cfg, seed, n_prompt, n_new = FULL_CASES[name]
+    d = pkg.CONFIGS[cfg].copy(max_seq=n_prompt + n_new + 8)      # the oracle's cache is f32: keep it no larger than needed
+    t0 = time.time()
+    m = OracleModel(d)
+    m.synth(seed)
+    prompt = m.synth_tokens(seed, n_prompt)
+    print(f"{name}: model ready after {time.time() - t0:.0f} s", flush=True)
+    m.kv_reset()
+    logits = m.forward(prompt, 0)[0]
+    prompt_logits = logits.copy()
+    toks, margins = [m.argmax(logits)], [m.margin(logits)]
+    print(f"{name}: prompt done after {time.time() - t0:.0f} s", flush=True)
+    p = n_prompt
+    while len(toks) < n_new:
+        logits = m.forward([toks[-1]], p)[0]
+        p += 1
+        toks.append(m.argmax(logits))
+        margins.append(m.margin(logits))
+    rows = p                                             # cache rows written: the prompt and the first n_new - 1 tokens
+    pick = sorted({0, 1, n_prompt // 2 - 1, n_prompt - 1, n_prompt, rows - 1})
+    L = d.n_layers
+    kv = {}
+    for layer in (0, L - 1):
+        for kind in ("k", "v"):
+            kv[f"{kind}_cache_layer{layer}"] = m.kv_read(layer, kind, rows)[pick].astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, f"{name}_full.npz"), config=cfg, seed=seed, prompt=np.array(prompt, dtype=np.int32),
+                        tokens=np.array(toks, dtype=np.int32), margins=np.array(margins, dtype=np.float32),
+                        prompt_logits=prompt_logits.astype(np.float32), last_logits=logits.astype(np.float32),
+                        cache_rows=np.array(pick, dtype=np.int32), **kv)
+    print(name, "tokens", toks, "min margin", float(min(margins)), "max |logit|", float(np.max(np.abs(logits))),
+          f"({time.time() - t0:.0f} s)", flush=True)
+
 
 def main():
     pkg = load_package()
+    wanted = sys.argv[1:]
+    if wanted:
+        for name in wanted:
+            full_case(pkg, name)
+        return
     for name, (cfg, seed, n_prompt, n_new) in CASES.items():
         m = OracleModel(pkg.CONFIGS[cfg])
         m.synth(seed)

@@ -58,6 +58,7 @@ def load() -> C.CDLL:
         "orc_argmax_last": (i32, [fp, i32]),
         "orc_top2_margin": (C.c_float, [fp, i32]),
         "orc_model_kv_reset": (None, [vp]),
+        "orc_model_kv_fill": (i32, [vp, u64, i32]),
         "orc_model_kv_read": (i32, [vp, i32, i32, i32, fp]),
         "orc_rmsnorm": (None, [fp, fp, i32, C.c_float, fp]),
         "orc_matvec_f32": (None, [fp, i32, i32, fp, fp]),
@@ -124,6 +125,10 @@ class OracleModel:
 
     def kv_reset(self):
         self.lib.orc_model_kv_reset(self.h)
+
+    def kv_fill(self, seed: int, rows: int):
+        """Seeded stand-in contents for cache rows [0, rows) of every layer (timing runs at a long context)."""
+        self._ck(self.lib.orc_model_kv_fill(self.h, seed, rows))
 
     def kv_read(self, layer: int, kind: str, rows: int):
         out = np.empty((rows, self.cfg.n_kv_heads * self.cfg.head_dim), dtype=np.float32)

@@ -109,3 +109,108 @@ def test_llir_loaded_runtime_equals_model_plan(pkg, L, oracle_lib, name):
     with pytest.raises(pkg.LumError, match="position ids"):
         rt.set_input(ids["positions"], np.asarray([5, 6], dtype=np.int32), "int")
     rt.close()
+
+
+# --------------------------------------------------------------------------------------------------------- chunks
+def test_chunk_is_recognised_on_the_host(pkg, L):
+    """A chunk of layers (what the reference's search profiles, src/graph.rs:351-352) is described by its own entry and
+    refused, with a message that says why, where a whole decoder is expected."""
+    want = pkg.CONFIGS["small_q8"]
+    blob, ids = L.build_llama_chunk_llir(want, n_layers=1)
+    d, hin, hout = pkg.describe_llir_chunk(blob)
+    assert (d.n_layers, d.hidden, d.n_q_heads, d.n_kv_heads, d.head_dim, d.ffn) == (1, want.hidden, want.n_q_heads, want.n_kv_heads, want.head_dim, want.ffn)
+    assert (hin, hout) == (ids["hidden_in"], ids["hidden_out"]) and d.vocab == 0
+    blob2, _ = L.build_llama_chunk_llir(want, n_layers=2)
+    assert pkg.describe_llir_chunk(blob2)[0].n_layers == 2
+    with pytest.raises(pkg.LumError, match="chunk of layers"):
+        pkg.describe_llir(blob)
+    whole, _ = L.build_llama_llir(want)
+    with pytest.raises(pkg.LumError, match="whole decoder"):
+        pkg.describe_llir_chunk(whole)
+
+
+@pytest.mark.gpu
+def test_search_surface_dummy_profile_clear_load_execute(pkg, L, oracle_lib):
+    """The order `Graph::search` drives a runtime in (src/graph.rs:293-302, 337, 351-352, 420-424, 569-570): dummy inputs,
+    profile of a chunk and of the whole graph, clear, load the stitched graph, then real data and execute."""
+    import oracle
+    want = pkg.CONFIGS["small_q8"]
+    whole, ids = L.build_llama_llir(want)
+    chunk, _ = L.build_llama_chunk_llir(want, n_layers=1)
+    rt = pkg.B200Runtime.initialize(device=0)
+    n_embed = want.vocab * want.hidden
+    rt.allocate_dummy_input(ids["embed"], n_embed)             # before any graph: remembered
+    us_c, text_c = rt.profile_llir(chunk, {"s": 1, "p": 16}, trials=3)
+    us_w, text_w = rt.profile_llir(whole, {"s": 1, "p": 16}, trials=3)
+    assert us_c > 0 and "chunk" in text_c and us_w > us_c and "whole decoder" in text_w
+    with pytest.raises(pkg.LumError, match="chunk of layers"):
+        rt.load_llir(chunk, max_seq=want.max_seq)
+    rt.clear_intermediate_buffers()
+    rt.load_llir(whole, max_seq=want.max_seq, kv_dtype="bf16", max_new_tokens=64)
+    rt.allocate_dummy_input(ids[("q", 0)], want.n_q_heads * want.head_dim * want.hidden)
+    with pytest.raises(pkg.LumError, match="elements"):
+        rt.allocate_dummy_input(ids[("q", 0)], 17)
+    rt.allocate_dummy_input(ids["tokens"], 4)
+    rt.set_dim("p", 0)
+    rt.execute()                                               # runs on stand-in contents without error
+    rt.synchronize()
+    rt.clear_intermediate_buffers()
+    # real data, as after the search: equals the plan-loaded runtime bit for bit
+    seed, prompt = 5, [9, 8, 7, 6, 5]
+    for key, (arr, dt) in oracle.host_tensors(oracle_lib, want, seed).items():
+        rt.set_input(ids[key], arr, dt)
+    rt.set_dim("s", len(prompt)); rt.set_dim("p", 0)
+    rt.set_input(ids["tokens"], np.asarray(prompt, dtype=np.int32), "int")
+    rt.execute()
+    got = rt.get_output(ids["logits"])
+    ref = pkg.B200Runtime.initialize(device=0)
+    ref.load_model(want); ref.synth(seed)
+    ref.set_data(prompt); ref.execute({"s": len(prompt), "p": 0})
+    assert np.array_equal(got, ref.get_f32())
+    st = rt.stats()
+    assert st.tokens_executed >= 4 + len(prompt) and st.kernel_launches > 0 and st.weight_bytes_per_token == ref.weight_bytes()
+    assert st.last_profile_usec == pytest.approx(us_w)
+    assert 0 < pkg.mbu(st, us_w, 16, 6540.8) < 1.5
+    ref.close(); rt.close()
+
+
+@pytest.mark.gpu
+def test_device_pointer_inputs_and_kv_save_load(pkg, L, oracle_lib):
+    """`CudaInput::Ptr` inputs (weights already on the device) and parking / restoring the cache."""
+    import oracle
+    import torch
+    want = pkg.CONFIGS["small_q8"]
+    blob, ids = L.build_llama_llir(want)
+    seed, prompt = 21, [1, 2, 3, 4, 5, 6, 7]
+    rt = pkg.B200Runtime.initialize(device=0)
+    rt.load_llir(blob, max_seq=want.max_seq, kv_dtype="bf16", max_new_tokens=64)
+    keep = []
+    for key, (arr, dt) in oracle.host_tensors(oracle_lib, want, seed).items():
+        t = torch.from_numpy(arr).cuda()
+        keep.append(t)
+        rt.set_input_device_ptr(ids[key], t.data_ptr(), arr.nbytes, dt)
+    torch.cuda.synchronize()
+    toks = torch.tensor(prompt, dtype=torch.int32, device="cuda")
+    rt.set_dim("s", len(prompt)); rt.set_dim("p", 0)
+    rt.set_input_device_ptr(ids["tokens"], toks.data_ptr(), 4 * len(prompt), "int")
+    rt.execute()
+    first = rt.get_token()
+    ref = pkg.B200Runtime.initialize(device=0)
+    ref.load_model(want); ref.synth(seed)
+    ref.set_data(prompt); ref.execute({"s": len(prompt), "p": 0})
+    assert first == ref.get_token() and np.array_equal(rt.get_f32(), ref.get_f32())
+    # park the cache, wipe it, bring it back: decoding continues as if nothing happened
+    rows = len(prompt)
+    saved = [(l, k, rt.kv_save(l, k, rows)) for l in range(want.n_layers) for k in ("k", "v")]
+    ref.decode_greedy(6)
+    want_seq = ref.get_decoded(6)
+    rt.kv_reset()
+    for l, k, data in saved:
+        rt.kv_load(l, k, rows, data)
+    with pytest.raises(pkg.LumError, match="bytes"):
+        rt.kv_load(0, "k", rows, saved[0][2][:-2])
+    rt.set_dim("p", rows)
+    rt.decode_reset()
+    rt.decode_greedy(6)
+    assert np.array_equal(rt.get_decoded(6), want_seq)
+    ref.close(); rt.close()
