@@ -248,6 +248,14 @@ int32_t lum_op_q8_0_pack(const int8_t* quants_dev, const void* scales_dev, int32
 int32_t lum_op_gemv_q8_0_packed(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev,
                                 int32_t force_direct, void* stream);
 int32_t lum_op_synth_q8_0_packed(uint64_t seed, uint64_t tensor_id, int32_t n, int32_t k, void* packed_dev, void* stream);
+/* Y[M, N] = X[M, K] W^T for M > 1 activation rows (row-major f32, leading dimensions K and N) on packed weights: the M > 1 path
+ * of `TileMatmulFullSplit` (ops.rs:1653-1738) for a Q8_0 right-hand side, on the tensor cores (tcgen05.mma kind::i8 on
+ * three int8 levels of the activations; f32-level accuracy).  The operator needs scratch for the quantised activations and
+ * the K-split partial sums: the caller passes a device workspace of at least lum_op_gemm_q8_0_workspace(n, k, m) bytes (0 =
+ * shape not supported: needs K % 512 == 0, K <= 16384, N % 8 == 0). */
+size_t lum_op_gemm_q8_0_workspace(int32_t n, int32_t k, int32_t m);
+int32_t lum_op_gemm_q8_0_packed(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, int32_t m, float* y_dev,
+                                void* workspace_dev, size_t workspace_bytes, void* stream);
 /* Vocabulary projection + greedy sample in one launch: logits[N] = W x, best_dev[0] = bit pattern of the largest logit,
  * best_dev[1] = its row (the LAST row among equal maxima — `sample`, examples/llama/src/main.rs:137-148).  The per-CTA
  * maxima and the arrival ticket live in a small per-device scratch buffer the library allocates on first use. */

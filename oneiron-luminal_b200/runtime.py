@@ -194,6 +194,8 @@ def load_library() -> C.CDLL:
         "lum_op_q8_0_pack": (i32, [vp, vp, i32, i32, vp, vp]),
         "lum_op_gemv_q8_0_packed": (i32, [vp, i32, i32, vp, vp, i32, vp]),
         "lum_op_synth_q8_0_packed": (i32, [u64, u64, i32, i32, vp, vp]),
+        "lum_op_gemm_q8_0_workspace": (sz, [i32, i32, i32]),
+        "lum_op_gemm_q8_0_packed": (i32, [vp, i32, i32, vp, i32, vp, vp, sz, vp]),
         "lum_op_sample_q8_0": (i32, [vp, i32, i32, vp, vp, vp, vp]),
         "lum_op_sample_q8_0_static": (i32, [vp, i32, i32, vp, vp, vp, vp]),
         "lum_op_gemv_f32": (i32, [vp, i32, i32, vp, vp, vp]),

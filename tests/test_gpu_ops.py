@@ -267,3 +267,68 @@ def test_bad_arguments_return_errors(lib):
     assert lib.lum_op_q8_0_dequant(None, None, 31, None, None) < 0
     assert lib.lum_q8_0_packed_bytes(44, 1024) == 0 and lib.lum_q8_0_packed_bytes(48, 1024) == 48 * 1024 * 34 // 32
     assert lib.lum_q8_0_packed_bytes(8, 96) == 0
+
+
+# ---------------------------------------------------------------------------------------------------- M > 1: the tensor-core GEMM
+GEMM_KAT = [
+    # (n, k, m, mode)
+    (128, 512, 2, "ones"),            # one work item, one K-tile
+    (128, 512, 32, "integers"),       # a full chunk of activation rows; exact
+    (136, 1024, 3, "integers"),       # a partial last tile of weight rows (8 of 128), two K-tiles
+    (256, 4096, 33, "random"),        # two chunks, the second with one row; K split over work items
+    (1024, 4096, 32, "random"),       # the batched-decode shape class (k/v projection)
+    (4096, 4096, 40, "random"),
+    (512, 14336, 17, "random"),       # down-projection K: 28 K-tiles
+    (384, 2560, 64, "random"),        # K = 5 tiles (Qwen hidden)
+    (2048, 512, 200, "random"),       # many activation chunks per weight tile
+]
+
+
+@pytest.mark.parametrize("n,k,m,mode", GEMM_KAT)
+def test_gemm_q8_known_answers(torch_cuda, lib, n, k, m, mode):
+    """Every output row of the M > 1 product against the oracle's matrix-vector product of the same activation row, at the
+    reference's tolerance for f32 dot products; exact for integer data."""
+    torch = torch_cuda
+    rng = np.random.default_rng(n * 7 + k * 3 + m)
+    blocks = make_wire(rng, n, k, mode)
+    if mode == "ones":
+        x = np.ones((m, k), dtype=np.float32)
+    elif mode == "integers":
+        x = rng.integers(-4, 5, (m, k)).astype(np.float32)
+    else:
+        x = (rng.normal(0, 1, (m, k)) * rng.uniform(0.01, 30.0, (m, 1))).astype(np.float32)     # rows of very different size
+    q, s = upload_q8(torch, lib, blocks, n, k)
+    packed = torch.empty(lib.lum_q8_0_packed_bytes(n, k), dtype=torch.uint8, device="cuda")
+    ck(lib, lib.lum_op_q8_0_pack(q.data_ptr(), s.data_ptr(), n, k, packed.data_ptr(), None))
+    wsb = lib.lum_op_gemm_q8_0_workspace(n, k, m)
+    assert wsb > 0
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    ck(lib, lib.lum_op_gemm_q8_0_packed(packed.data_ptr(), n, k, xd.data_ptr(), m, y.data_ptr(), ws.data_ptr(), wsb, None))
+    torch.cuda.synchronize()
+    ck(lib, lib.lum_op_status(None))
+    got = y.cpu().numpy()
+    want = np.stack([oracle_matvec_q8(blocks, n, k, np.ascontiguousarray(x[i])) for i in range(m)])
+    if mode == "ones":
+        assert (got == float(k)).all()
+    elif mode == "integers":
+        # every exact answer is a multiple of 1/4; the three-level activations carry 2^-24 relative rounding, so the sums sit
+        # within a few units in the last place of it and snap onto it
+        assert (np.round(got * 4) / 4 == want).all()
+    if mode != "ones":
+        wf = np.empty(n * k, dtype=np.float32)
+        load().orc_q8_0_dequant(blocks.ctypes.data_as(C.c_void_p), n * k // 32, _fp(wf))
+        mag = np.abs(x).astype(np.float64) @ np.abs(wf.reshape(n, k)).astype(np.float64).T
+        check_close(got.astype(np.float64), want.astype(np.float64), mag, k)
+    # the M = 1 kernel on the same rows: the two paths share the arithmetic and differ only in summation order
+    y1 = torch.empty(n, dtype=torch.float32, device="cuda")
+    ck(lib, lib.lum_op_gemv_q8_0_packed(packed.data_ptr(), n, k, xd[m - 1].contiguous().data_ptr(), y1.data_ptr(), 0, None))
+    torch.cuda.synchronize()
+    ref1 = y1.cpu().numpy()
+    assert np.max(np.abs(ref1 - got[m - 1])) <= 16 * EPS * max(1.0, float(np.max(np.abs(ref1)))) * np.sqrt(k / 32)
+
+
+def test_gemm_q8_refuses_bad_arguments(torch_cuda, lib):
+    assert lib.lum_op_gemm_q8_0_workspace(100, 512, 4) == 0 and lib.lum_op_gemm_q8_0_workspace(128, 500, 4) == 0
+    assert lib.lum_op_gemm_q8_0_packed(None, 128, 512, None, 2, None, None, 0, None) != 0
