@@ -312,3 +312,54 @@ def test_profile_restores_state(pkg, rt):
     rt.decode_greedy(9)
     assert [first] + [int(t) for t in rt.get_decoded(9)] == base
     assert rt.launches_per_step() in (1, 2 + 5 * desc.n_layers)
+
+
+@pytest.mark.parametrize("name", ["llama3_8b_q8", "qwen3_4b_q8"])
+def test_full_size_configuration_matches_oracle_fixture(pkg, name):
+    """The configurations the benchmark numbers are quoted on, whole: every layer, the whole vocabulary, the benchmark's
+    seed and prompt.  Checked against the oracle's committed outputs (tests/golden/make_golden.py <name>): the first 32
+    greedy tokens identical, logits within 1e-2 max-abs relative error, K/V cache rows of the first and last layer."""
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"{name}_full.npz")
+    if not os.path.exists(path):
+        pytest.skip(f"no fixture {path}")
+    fx = np.load(path)
+    desc = pkg.CONFIGS[name]
+    prompt = [int(t) for t in fx["prompt"]]
+    want = [int(t) for t in fx["tokens"]]
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc)
+        rt.synth(int(fx["seed"]))
+        rt.kv_reset(); rt.decode_reset()
+        rt.set_data(prompt); rt.execute({"s": len(prompt), "p": 0})
+        first = rt.get_token()
+        logits0 = rt.get_f32()
+        ref0 = fx["prompt_logits"]
+        err0 = float(np.max(np.abs(logits0 - ref0)) / np.max(np.abs(ref0)))
+        rt.decode_greedy(len(want) - 1)
+        got = [first] + [int(t) for t in rt.get_decoded(len(want) - 1)]
+        logits1 = rt.get_f32()
+        ref1 = fx["last_logits"]
+        err1 = float(np.max(np.abs(logits1 - ref1)) / np.max(np.abs(ref1)))
+        margins = fx["margins"]
+        assert got == want, f"first mismatch at step {next(i for i in range(len(want)) if got[i] != want[i])}; fixture margins there {margins[:len(want)]}"
+        assert err0 <= 1e-2 and err1 <= 1e-2, (err0, err1)
+        rows = [int(r) for r in fx["cache_rows"]]
+        n_rows = max(rows) + 1
+        for layer in (0, desc.n_layers - 1):
+            for kind in ("k", "v"):
+                have = rt.kv_read(layer, kind, n_rows)[rows]
+                ref = fx[f"{kind}_cache_layer{layer}"]
+                rms = float(np.sqrt(np.mean((have - ref) ** 2)) / np.sqrt(np.mean(ref ** 2)))
+                if layer == 0:
+                    # cache values are bfloat16: equal, or one rounding step apart where the f32 value sat next to a tie
+                    assert np.max(np.abs(have - ref) / np.maximum(np.abs(ref), 1e-3)) <= 2.0 ** -7, (layer, kind)
+                    assert np.mean(have == ref) > 0.98, (layer, kind, float(np.mean(have == ref)))
+                else:
+                    # after all layers: every rounding step a cached bfloat16 value flips by (2^-8 of it) feeds the layers
+                    # above, so the last layer's rows agree to a few bfloat16 steps, not bit for bit
+                    assert rms <= 1e-2, (layer, kind, rms)
+        print(f"{name}: 32 tokens equal; logits rel err {err0:.2e} (after the prompt), {err1:.2e} (after 32 tokens); min margin {float(margins.min()):.2e}")
+    finally:
+        rt.close()
