@@ -49,6 +49,11 @@ typedef struct lum_config {
     int32_t attn_splits;  /* CTAs per KV head in decode attention; 0 = choose from the SM count */
     int32_t use_mega;     /* 1: run whole tokens in one persistent cooperative kernel when the model allows;
                              0 (default): one kernel per operation (CUDA graph / plain launches as chosen above) */
+    int32_t prefill_min_rows; /* lum_execute with at least this many tokens takes them as rows of matrix-matrix products on the
+                             tensor cores (when the model allows) instead of one decode step per token; 0 = default (4),
+                             a huge value = never */
+    int32_t wait_budget_ms;   /* how long a kernel waits for a word another CTA or GPU must write before it gives up with
+                             LUM_E_DEVICE; 0 = default (about two seconds) */
 } lum_config;
 
 void lum_config_default(lum_config* cfg);
@@ -89,6 +94,9 @@ typedef struct lum_model_desc {
     /* tensor parallel: this rank's shard.  1/0 = whole model.  Heads and FFN columns are split
      * evenly; o/down hold a K-slice and their outputs are summed over the ranks (see lum_tp_init). */
     int32_t tp_size, tp_rank;
+    /* sequences the K/V cache holds side by side (0 or 1: one).  lum_execute / lum_decode_greedy work on the sequence chosen
+     * by lum_seq_select; lum_batch_decode advances all of them together. */
+    int32_t max_batch;
 } lum_model_desc;
 
 int32_t lum_model_init(lum_rt* rt, const lum_model_desc* desc);
@@ -185,6 +193,24 @@ int32_t lum_get_decoded(lum_rt* rt, int32_t* host_out, size_t n);
 int32_t lum_decode_reset(lum_rt* rt);
 /* Block until all submitted work is done and report device-side status (LUM_E_DEVICE if a kernel flagged one). */
 int32_t lum_synchronize(lum_rt* rt);
+
+/* ---------------------------------------------------------------------------------------------
+ * Several sequences (batch > 1).  The reference's graph has one dynamic row dimension 's' and a cache per layer
+ * (examples/llama/src/model.rs:91-113, 194-223); with `max_batch` > 1 in lum_model_desc this runtime keeps that many
+ * caches per layer side by side.
+ *   lum_seq_select(seq)        which sequence lum_execute / lum_decode_greedy / lum_kv_* address (default 0);
+ *   lum_batch_begin(n, t, p)   the current token and position (= rows already cached) of sequences 0 .. n-1, typically what
+ *                              each one's prompt ended with; resets the batch log;
+ *   lum_batch_decode(steps)    `steps` greedy tokens for every sequence: one row per sequence and step through the
+ *                              tensor-core products, attention of each row over its own cache, a greedy sample per row,
+ *                              fed back on the device;
+ *   lum_batch_get_decoded      the log, [steps][n] row-major;  lum_batch_get_logits: the last step's logits of one sequence.
+ * Needs Q8_0 weights in the packed layout and one GPU (no tensor parallelism). */
+int32_t lum_seq_select(lum_rt* rt, int32_t seq);
+int32_t lum_batch_begin(lum_rt* rt, int32_t n_seq, const int32_t* tokens, const int32_t* positions);
+int32_t lum_batch_decode(lum_rt* rt, int32_t n_steps);
+int32_t lum_batch_get_decoded(lum_rt* rt, int32_t* host_out, size_t n_steps);
+int32_t lum_batch_get_logits(lum_rt* rt, int32_t seq, float* host_out, size_t n);
 
 /* `Runtime::profile` (src/op.rs:18-23): time `trials` decode steps with CUDA events on the
  * runtime's stream (state is restored afterwards); returns mean microseconds per step and a

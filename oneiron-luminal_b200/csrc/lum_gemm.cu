@@ -25,6 +25,7 @@
 #include <cstdlib>
 
 #include "lum_gemv_dev.cuh"
+#include "lum_rows.cuh"
 
 namespace lum {
 
@@ -42,36 +43,6 @@ constexpr int kGmDrainWarps = 8;
 constexpr int kGmThreads = (kGmDrainWarps + 2) * 32;   // + producer warp + tensor-core warp
 constexpr int kGmBarBytes = 256;
 constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmXStages * kGmXStage;
-
-struct GemmSeg { const unsigned char* w; int rows; int col0; };     // col0: where row 0 of this matrix lands in an output row
-
-struct GemmArgs {
-    GemmSeg seg[3];
-    int nseg;
-    int K;
-    const int8_t* xq;        // [m_chunks][K / 32][kGmXBlock]
-    const float* sx;         // [m_chunks][K / 32][kGmMB]
-    int M, m_chunks;
-    int ksplit;              // K ranges (whole K-tiles each); part i of the sums goes to y + i * part_stride
-    float* y;
-    int ldy;
-    size_t part_stride;
-    uint32_t* status;
-    int use_pdl;
-};
-
-// Rows of the next product's input.  value(m, k) = sum over parts of a[part][m][k] (+ resid[m][k]), or, with `b`, the SwiGLU
-// of the two sums: silu(sum a) * sum b.
-struct RowsArgs {
-    const float* a; const float* b;
-    int n_parts; size_t part_stride; int ld;          // a / b: [n_parts] planes, row stride ld floats
-    const float* resid; int resid_ld;
-    float* out; int out_ld;                          // optional: the formed rows (the new residual stream), before the norm
-    const void* gain; int gain_kind; float eps;      // RMSNorm gains (null: none)
-    int M, K;
-    int8_t* xq; float* sx;
-    int use_pdl;
-};
 
 __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     extern __shared__ __align__(16) float rowbuf[];          // K floats + 8 words of reduction scratch

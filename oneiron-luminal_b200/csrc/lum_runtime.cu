@@ -26,6 +26,7 @@
 #include "../../include/lum_b200.h"
 #include "lum_kernels.cuh"
 #include "lum_mega.cuh"
+#include "lum_rows.cuh"
 
 using namespace lum;
 
@@ -139,6 +140,21 @@ struct lum_rt {
     uint64_t dim_s = 1, dim_p = 0;
     std::vector<int32_t> tokens_in;
 
+    // ---- steps that carry several rows (prompt processing, batched decode): buffers of the tensor-core path, made on first use
+    struct Rows {
+        int cap = 0;                      // rows a pass can take
+        int *tok = nullptr, *pos = nullptr, *seq = nullptr;          // [cap] per-row token / position / sequence
+        float *xr = nullptr, *q_rot = nullptr, *attn = nullptr;      // residual rows [cap][H]; rotated queries and attention output [cap][qd]
+        float *qkv = nullptr, *o = nullptr, *gu = nullptr, *down = nullptr, *logits = nullptr;   // K-split partial planes of the products
+        int8_t* xq = nullptr; float* sx = nullptr;                   // quantised activation rows of the product in flight
+        std::vector<int32_t> h_tok, h_pos;
+    } rows;
+    int prefill_min_rows = 4;
+    int max_batch = 1, cur_seq = 0;
+    int batch_n = 0;                  // sequences of the running batch (lum_batch_begin)
+    int *b_step = nullptr, *b_log = nullptr;     // batched decode: step counter and token log [max_new_tokens][max_batch] on the device
+    cudaGraphExec_t g_batch = nullptr;
+    int g_batch_n = 0;
     lum_llir_plan* llir = nullptr;    // set by lum_load_llir: which Input node feeds which weight slot
     std::map<int64_t, size_t> dummy_inputs;   // lum_alloc_dummy_input calls made before a graph was loaded: node -> elements
     bool body_only = false;           // profiling a chunk of layers: steps never run the vocabulary head
@@ -240,6 +256,10 @@ void free_model(lum_rt* rt) {
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
     rt->launches_full = 0;
+    if (rt->g_batch) cudaGraphExecDestroy(rt->g_batch);
+    rt->g_batch = nullptr; rt->g_batch_n = 0; rt->batch_n = 0; rt->cur_seq = 0;
+    rt->rows = lum_rt::Rows();
+    rt->b_step = nullptr; rt->b_log = nullptr;
     rt->attn_cnt = nullptr; rt->am_cnt = nullptr;
     rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr; rt->step_ctr = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
@@ -398,7 +418,8 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
 
         AttnArgs t{};
         t.q = rt->qkv; t.k_new = rt->qkv + (size_t)rt->nq_l * hd; t.v_new = t.k_new + (size_t)rt->nkv_l * hd;
-        t.k_cache = w.kc; t.v_cache = w.vc; t.out = rt->attn; t.part = rt->attn_part; t.counters = rt->attn_cnt;
+        const size_t seq_off = (size_t)rt->cur_seq * d.max_seq * rt->nkv_l * hd * (d.kv_dtype == LUM_BF16 ? 2 : 4);
+        t.k_cache = (char*)w.kc + seq_off; t.v_cache = (char*)w.vc + seq_off; t.out = rt->attn; t.part = rt->attn_part; t.counters = rt->attn_cnt;
         t.state = rt->state; t.q_gain = d.qk_norm ? w.q_norm.w : nullptr; t.k_gain = d.qk_norm ? w.k_norm.w : nullptr;
         t.gain_kind = gk; t.qk_eps = d.rms_eps; t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits;
         t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
@@ -523,10 +544,206 @@ int run_step(lum_rt* rt, bool with_head) {
     return issue_step(rt, with_head, rt->cfg.use_pdl != 0, with_head ? &rt->launches_full : nullptr);
 }
 
+// ---- steps of several rows ----------------------------------------------------------------------------------------
+// Every linear of the model in the packed tile stream, one GPU: the tensor-core products can take the model's rows.
+bool rows_supported(const lum_rt* rt) {
+    const lum_model_desc& d = rt->d;
+    if (!rt->has_model || d.weight_dtype != LUM_Q8_0 || rt->tp_size > 1 || (d.head_dim != 64 && d.head_dim != 128)) return false;
+    if (d.n_q_heads / d.n_kv_heads > (d.head_dim == 128 ? 4 : 8)) return false;
+    for (const LayerW& w : rt->L) {
+        const Tensor* ts[] = {&w.q, &w.k, &w.v, &w.o, &w.gate, &w.up, &w.down};
+        for (const Tensor* t : ts) if (t->kc != 512) return false;
+    }
+    return true;
+}
+
+// floats the K-split partial planes of a product with n_out outputs per row can need, over every row count up to cap
+size_t rows_parts_floats(const lum_rt* rt, int n_out, int K, int cap) {
+    size_t worst = 0;
+    for (int M = 32; M <= ((cap + 31) / 32) * 32; M += 32) {
+        const int m = M < cap ? M : cap;
+        const size_t need = (size_t)gemm_pick_ksplit(n_out, m, K, rt->sm_count) * m * n_out;
+        if (need > worst) worst = need;
+    }
+    return worst;
+}
+
+int ensure_rows(lum_rt* rt, int want_rows) {
+    lum_rt::Rows& b = rt->rows;
+    if (b.cap >= want_rows) return 0;
+    if (b.cap) return fail(rt, LUM_E_INVALID, "rows: %d rows asked for, buffers hold %d", want_rows, b.cap);
+    int cap = 512;
+    if (const char* e = getenv("LUM_ROWS_CAP")) cap = atoi(e);
+    if (cap < 32) cap = 32;
+    if (cap < rt->max_batch) cap = rt->max_batch;
+    if (cap < want_rows) cap = want_rows;
+    const lum_model_desc& d = rt->d;
+    const int H = d.hidden, hd = d.head_dim, qd = rt->nq_l * hd, kvd = rt->nkv_l * hd, W = qd + 2 * kvd, F = rt->ffn_l;
+    int kmax = H > qd ? H : qd;
+    if (F > kmax) kmax = F;
+    if (int r = dev_alloc(rt, (void**)&b.tok, (size_t)cap * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.pos, (size_t)cap * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.seq, (size_t)cap * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.xr, (size_t)cap * H * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.q_rot, (size_t)cap * qd * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.attn, (size_t)cap * qd * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.qkv, rows_parts_floats(rt, W, H, cap) * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.o, rows_parts_floats(rt, H, qd, cap) * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.gu, rows_parts_floats(rt, 2 * F, H, cap) * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.down, rows_parts_floats(rt, H, F, cap) * 4)) return r;
+    if (rt->max_batch > 1 && !d.tied_head)
+        if (int r = dev_alloc(rt, (void**)&b.logits, rows_parts_floats(rt, rt->vocab_l, H, rt->max_batch) * 4)) return r;
+    if (int r = dev_alloc(rt, (void**)&b.xq, gemm_xq_bytes(cap, kmax))) return r;
+    if (int r = dev_alloc(rt, (void**)&b.sx, gemm_sx_bytes(cap, kmax))) return r;
+    std::vector<int32_t> iota((size_t)cap);
+    for (int i = 0; i < cap; i++) iota[(size_t)i] = i;
+    CU(rt, cudaMemcpyAsync(b.seq, iota.data(), (size_t)cap * 4, cudaMemcpyHostToDevice, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    b.cap = cap;
+    return 0;
+}
+
+// One pass of M rows through every layer.  d_tok / d_pos: device arrays [M]; d_seq: device array [M], or null when every row
+// belongs to sequence seq0.  head: 0 none (the rows only fill the cache), 1 vocabulary projection + greedy sample of the LAST row
+// into the decode state (the end of a prompt), 2 of every row into the batch state (batched decode).
+int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int seq0, int head) {
+    const lum_model_desc& d = rt->d;
+    lum_rt::Rows& b = rt->rows;
+    const int H = d.hidden, hd = d.head_dim, qd = rt->nq_l * hd, kvd = rt->nkv_l * hd, W = qd + 2 * kvd, F = rt->ffn_l;
+    const int gk = kind_of(d.embed_dtype), sms = rt->sm_count;
+    cudaStream_t st = rt->stream;
+    const int ks_qkv = gemm_pick_ksplit(W, M, H, sms), ks_o = gemm_pick_ksplit(H, M, qd, sms), ks_gu = gemm_pick_ksplit(2 * F, M, H, sms),
+              ks_dn = gemm_pick_ksplit(H, M, F, sms);
+    CU(rt, launch_embed_rows(rt->embed.w, rt->embed.kind, H, d.vocab, d_tok, b.xr, M, rt->status, st));
+    uint64_t launches = 1;
+    auto quant = [&](RowsArgs& r, int K) -> cudaError_t { r.M = M; r.K = K; r.xq = b.xq; r.sx = b.sx; launches++; return launch_rows_quantize(r, st); };
+    auto gemm = [&](GemmArgs& g, int K, int ks, float* y, int ldy) -> cudaError_t {
+        g.K = K; g.xq = b.xq; g.sx = b.sx; g.M = M; g.ksplit = ks; g.y = y; g.ldy = ldy; g.part_stride = (size_t)M * ldy; g.status = rt->status;
+        launches++;
+        return launch_gemm(g, sms, st);
+    };
+    for (int l = 0; l < d.n_layers; l++) {
+        LayerW& w = rt->L[(size_t)l];
+        {   // residual stream (+ the previous layer's down projection) -> RMSNorm -> operand of q | k | v
+            RowsArgs r{};
+            if (l == 0) { r.a = b.xr; r.n_parts = 1; r.ld = H; }
+            else { r.a = b.down; r.n_parts = ks_dn; r.part_stride = (size_t)M * H; r.ld = H; r.resid = b.xr; r.resid_ld = H; r.out = b.xr; r.out_ld = H; }
+            r.gain = w.attn_norm.w; r.gain_kind = gk; r.eps = rt->eps6;
+            CU(rt, quant(r, H));
+            GemmArgs g{};
+            g.nseg = 3;
+            g.seg[0] = {(const unsigned char*)w.q.w, (int)w.q.rows, 0};
+            g.seg[1] = {(const unsigned char*)w.k.w, (int)w.k.rows, qd};
+            g.seg[2] = {(const unsigned char*)w.v.w, (int)w.v.rows, qd + kvd};
+            CU(rt, gemm(g, H, ks_qkv, b.qkv, W));
+        }
+        {
+            RopeRowsArgs t{};
+            t.qkv = b.qkv; t.n_parts = ks_qkv; t.part_stride = (size_t)M * W; t.row_pos = d_pos; t.row_seq = d_seq; t.seq0 = seq0;
+            t.q_rot = b.q_rot; t.k_cache = w.kc; t.v_cache = w.vc;
+            t.q_gain = d.qk_norm ? w.q_norm.w : nullptr; t.k_gain = d.qk_norm ? w.k_norm.w : nullptr; t.gain_kind = gk; t.qk_eps = d.rms_eps;
+            t.M = M; t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
+            t.max_seq = d.max_seq; t.max_batch = rt->max_batch;
+            t.c_inv_d = rt->c_inv_d; t.c_ln_theta = rt->c_ln_theta; t.c_log2e = rt->c_log2e; t.c_half_pi = rt->c_half_pi; t.theta = d.rope_theta;
+            t.status = rt->status;
+            CU(rt, launch_rope_append_rows(t, st));
+            AttnRowsArgs a{};
+            a.q_rot = b.q_rot; a.k_cache = w.kc; a.v_cache = w.vc; a.row_pos = d_pos; a.row_seq = d_seq; a.seq0 = seq0; a.out = b.attn;
+            a.M = M; a.n_q = rt->nq_l; a.n_kv = rt->nkv_l; a.hd = hd; a.kv_bf16 = t.kv_bf16; a.window = 0; a.max_seq = d.max_seq; a.max_batch = rt->max_batch;
+            CU(rt, launch_attn_rows(a, st));
+            launches += 2;
+        }
+        {   // attention output -> operand of the o projection
+            RowsArgs r{};
+            r.a = b.attn; r.n_parts = 1; r.ld = qd;
+            CU(rt, quant(r, qd));
+            GemmArgs g{};
+            g.nseg = 1; g.seg[0] = {(const unsigned char*)w.o.w, (int)w.o.rows, 0};
+            CU(rt, gemm(g, qd, ks_o, b.o, H));
+        }
+        {   // residual add -> RMSNorm -> operand of gate | up
+            RowsArgs r{};
+            r.a = b.o; r.n_parts = ks_o; r.part_stride = (size_t)M * H; r.ld = H; r.resid = b.xr; r.resid_ld = H; r.out = b.xr; r.out_ld = H;
+            r.gain = w.mlp_norm.w; r.gain_kind = gk; r.eps = rt->eps6;
+            CU(rt, quant(r, H));
+            GemmArgs g{};
+            g.nseg = 2;
+            g.seg[0] = {(const unsigned char*)w.gate.w, (int)w.gate.rows, 0};
+            g.seg[1] = {(const unsigned char*)w.up.w, (int)w.up.rows, F};
+            CU(rt, gemm(g, H, ks_gu, b.gu, 2 * F));
+        }
+        {   // SwiGLU -> operand of the down projection
+            RowsArgs r{};
+            r.a = b.gu; r.b = b.gu + F; r.n_parts = ks_gu; r.part_stride = (size_t)M * 2 * F; r.ld = 2 * F;
+            CU(rt, quant(r, F));
+            GemmArgs g{};
+            g.nseg = 1; g.seg[0] = {(const unsigned char*)w.down.w, (int)w.down.rows, 0};
+            CU(rt, gemm(g, F, ks_dn, b.down, H));
+        }
+    }
+    if (head == 1) {
+        // the last row's residual = xr[M-1] + the partial planes of the last down projection; the single-row kernel adds them up
+        const Tensor& hw = d.tied_head ? rt->embed : rt->lm_head;
+        GemvArgs a{};
+        a.status = rt->status; a.use_pdl = 0; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = hw.kind;
+        a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows, hw.kc};
+        a.K = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
+        a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
+        a.advance = 1;
+        a.x = b.xr + (size_t)(M - 1) * H;
+        a.parts = b.down + (size_t)(M - 1) * H; a.n_parts = ks_dn; a.part_stride = M * H;
+        CU(rt, launch_gemv(a, sms, st));
+        launches++;
+    } else if (head == 2) {
+        RowsArgs r{};
+        r.a = b.down; r.n_parts = ks_dn; r.part_stride = (size_t)M * H; r.ld = H; r.resid = b.xr; r.resid_ld = H; r.out = b.xr; r.out_ld = H;
+        r.gain = rt->final_norm.w; r.gain_kind = gk; r.eps = rt->eps6;
+        CU(rt, quant(r, H));
+        const int V = rt->vocab_l, ks_v = gemm_pick_ksplit(V, M, H, sms);
+        GemmArgs g{};
+        g.nseg = 1; g.seg[0] = {(const unsigned char*)rt->lm_head.w, V, 0};
+        CU(rt, gemm(g, H, ks_v, b.logits, V));
+        ArgmaxRowsArgs x{};
+        x.logits = b.logits; x.n_parts = ks_v; x.part_stride = (size_t)M * V; x.M = M; x.vocab = V;
+        x.row_tok = d_tok; x.row_pos = d_pos; x.log = rt->b_log; x.step = rt->b_step; x.max_steps = d.max_new_tokens;
+        CU(rt, launch_argmax_rows(x, st));
+        CU(rt, launch_step_advance(rt->b_step, st));
+        launches += 2;
+    }
+    rt->n_launches += launches;
+    return 0;
+}
+
+// A prompt (n forced tokens of the selected sequence from position pos0) as rows, in passes of at most rows.cap rows; the
+// last row's logits and greedy sample end up where a single-token step leaves them.
+int run_prompt_rows(lum_rt* rt, int n, const int32_t* forced, int pos0) {
+    if (int r = ensure_rows(rt, 1)) return r;
+    lum_rt::Rows& b = rt->rows;
+    for (int c0 = 0; c0 < n; c0 += b.cap) {
+        const int M = n - c0 < b.cap ? n - c0 : b.cap;
+        const bool last = c0 + M == n;
+        b.h_tok.assign(forced + c0, forced + c0 + M);
+        b.h_pos.resize((size_t)M);
+        for (int i = 0; i < M; i++) b.h_pos[(size_t)i] = pos0 + c0 + i;
+        CU(rt, cudaMemcpyAsync(b.tok, b.h_tok.data(), (size_t)M * 4, cudaMemcpyHostToDevice, rt->stream));
+        CU(rt, cudaMemcpyAsync(b.pos, b.h_pos.data(), (size_t)M * 4, cudaMemcpyHostToDevice, rt->stream));
+        CU(rt, cudaStreamSynchronize(rt->stream));           // the host vectors are reused by the next pass
+        if (last) {
+            set_state_kernel<<<1, 1, 0, rt->stream>>>(rt->state, pos0 + n - 1, forced[n - 1], 0, 1, 0);
+            CU(rt, cudaGetLastError());
+        }
+        if (int r = run_rows(rt, M, b.tok, b.pos, nullptr, rt->cur_seq, last ? 1 : 0)) return r;
+    }
+    rt->n_tokens_run += (uint64_t)n;
+    return 0;
+}
+
 // n tokens in one go.  forced: host token ids (prompt processing: sample only after the last) or null (feed
 // every sample back in).  The persistent kernel takes them all in one launch; otherwise one step per token.
 int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
     if (n <= 0) return 0;
+    if (forced && !rt->body_only && n >= rt->prefill_min_rows && !(rt->mega_ok && rt->use_mega) && rows_supported(rt))
+        return run_prompt_rows(rt, n, forced, pos0);
     if (rt->mega_ok && rt->use_mega) {
         MegaArgs a = rt->mega;
         a.n_tokens = n;
@@ -562,7 +779,7 @@ int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
 int setup_mega(lum_rt* rt) {
     rt->mega_ok = false;
     const lum_model_desc& d = rt->d;
-    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || rt->tp_size > 1) return 0;
+    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || rt->tp_size > 1 || d.max_batch > 1) return 0;
     std::vector<MegaLayer> hl((size_t)d.n_layers);
     bool packed = rt->lm_head.kc > 0;
     for (int l = 0; l < d.n_layers && packed; l++) {
@@ -628,6 +845,10 @@ void lum_config_default(lum_config* c) {
     if (const char* e = getenv("LUM_ATTN_SPLITS")) c->attn_splits = atoi(e);
     c->use_mega = 0;
     if (const char* e = getenv("LUM_MEGA")) c->use_mega = atoi(e);
+    c->prefill_min_rows = 0;
+    if (const char* e = getenv("LUM_PREFILL_MIN_ROWS")) c->prefill_min_rows = atoi(e);
+    c->wait_budget_ms = 0;
+    if (const char* e = getenv("LUM_WAIT_BUDGET_MS")) c->wait_budget_ms = atoi(e);
 }
 
 int32_t lum_create(const lum_config* cfg, lum_rt** out) {
@@ -861,7 +1082,8 @@ static int kv_span(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, size_t
     if (layer < 0 || layer >= rt->d.n_layers || rows < 0 || rows > rt->d.max_seq || (kind != 0 && kind != 1)) return fail(rt, LUM_E_INVALID, "%s: bad layer / kind / rows", who);
     const size_t want = (size_t)rows * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
     if (bytes != want) return fail(rt, LUM_E_INVALID, "%s: %d rows are %zu bytes in the cache's own type, got %zu", who, rows, want, bytes);
-    *dev = kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc;
+    const size_t seq_off = (size_t)rt->cur_seq * rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+    *dev = (char*)(kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc) + seq_off;
     return 0;
 }
 int32_t lum_kv_save(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, void* host_out, size_t bytes) {
@@ -897,6 +1119,93 @@ int32_t lum_get_stats(const lum_rt* rt, lum_stats* out) {
         out->launches_per_step = rt->launches_full;
     }
     return 0;
+}
+
+
+// ---- several sequences ---------------------------------------------------------------------------------------------------
+
+int32_t lum_seq_select(lum_rt* rt, int32_t seq) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "seq_select: no model");
+    if (seq < 0 || seq >= rt->max_batch) return fail(rt, LUM_E_INVALID, "seq_select: sequence %d outside max_batch %d", seq, rt->max_batch);
+    if (seq != rt->cur_seq) {
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        CU(rt, cudaStreamSynchronize(rt->stream));
+        // the captured single-token graphs address the previous sequence's cache
+        if (rt->g_full) { cudaGraphExecDestroy(rt->g_full); rt->g_full = nullptr; }
+        if (rt->g_body) { cudaGraphExecDestroy(rt->g_body); rt->g_body = nullptr; }
+        rt->cur_seq = seq;
+    }
+    return 0;
+}
+
+int32_t lum_batch_begin(lum_rt* rt, int32_t n_seq, const int32_t* tokens, const int32_t* positions) {
+    if (!rt || !rt->has_model || !tokens || !positions) return fail(rt, LUM_E_INVALID, "batch_begin: no model or null argument");
+    if (n_seq < 1 || n_seq > rt->max_batch) return fail(rt, LUM_E_INVALID, "batch_begin: %d sequences, the model was loaded with max_batch %d", n_seq, rt->max_batch);
+    if (rt->max_batch < 2) return fail(rt, LUM_E_INVALID, "batch_begin: load the model with max_batch > 1");
+    if (!rows_supported(rt) || rt->d.tied_head) return fail(rt, LUM_E_UNSUPPORTED, "batch decode needs packed Q8_0 weights with a Q8_0 vocabulary projection on one GPU");
+    for (int i = 0; i < n_seq; i++) {
+        if (tokens[i] < 0 || tokens[i] >= rt->d.vocab) return fail(rt, LUM_E_INVALID, "batch_begin: token id %d outside the vocabulary", tokens[i]);
+        if (positions[i] < 0 || positions[i] >= rt->d.max_seq) return fail(rt, LUM_E_INVALID, "batch_begin: position %d outside the cache capacity %d", positions[i], rt->d.max_seq);
+    }
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    if (int r = ensure_rows(rt, n_seq)) return r;
+    CU(rt, cudaMemcpyAsync(rt->rows.tok, tokens, (size_t)n_seq * 4, cudaMemcpyHostToDevice, rt->stream));
+    CU(rt, cudaMemcpyAsync(rt->rows.pos, positions, (size_t)n_seq * 4, cudaMemcpyHostToDevice, rt->stream));
+    CU(rt, cudaMemsetAsync(rt->b_step, 0, 4, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    rt->batch_n = n_seq;
+    rt->rows.h_pos.assign(positions, positions + n_seq);        // host copy: the capacity check of lum_batch_decode
+    return 0;
+}
+
+int32_t lum_batch_decode(lum_rt* rt, int32_t n_steps) {
+    if (!rt || !rt->has_model || rt->batch_n < 1) return fail(rt, LUM_E_INVALID, "batch_decode: call lum_batch_begin first");
+    if (n_steps < 0) return fail(rt, LUM_E_INVALID, "batch_decode: negative step count");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    for (int i = 0; i < rt->batch_n; i++) {
+        if (rt->rows.h_pos[(size_t)i] + n_steps > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "batch_decode: sequence %d would pass the cache capacity %d", i, rt->d.max_seq);
+        rt->rows.h_pos[(size_t)i] += n_steps;
+    }
+    const int M = rt->batch_n;
+    if (rt->cfg.use_graph && (!rt->g_batch || rt->g_batch_n != M)) {
+        if (rt->g_batch) { cudaGraphExecDestroy(rt->g_batch); rt->g_batch = nullptr; }
+        cudaGraph_t g = nullptr;
+        CU(rt, cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeThreadLocal));
+        const uint64_t keep = rt->n_launches;
+        const int r = run_rows(rt, M, rt->rows.tok, rt->rows.pos, rt->rows.seq, 0, 2);
+        rt->n_launches = keep;
+        cudaError_t e = cudaStreamEndCapture(rt->stream, &g);
+        if (r) { if (g) cudaGraphDestroy(g); return r; }
+        if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "batch_decode: cudaStreamEndCapture: %s", cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&rt->g_batch, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) { rt->g_batch = nullptr; return fail(rt, LUM_E_CUDA, "batch_decode: cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+        rt->g_batch_n = M;
+    }
+    for (int s = 0; s < n_steps; s++) {
+        if (rt->cfg.use_graph) CU(rt, cudaGraphLaunch(rt->g_batch, rt->stream));
+        else if (int r = run_rows(rt, M, rt->rows.tok, rt->rows.pos, rt->rows.seq, 0, 2)) return r;
+    }
+    rt->n_tokens_run += (uint64_t)n_steps * M;
+    return 0;
+}
+
+int32_t lum_batch_get_decoded(lum_rt* rt, int32_t* host_out, size_t n_steps) {
+    if (!rt || !rt->has_model || !host_out || rt->batch_n < 1) return fail(rt, LUM_E_INVALID, "batch_get_decoded: no batch or null output");
+    if (n_steps > (size_t)rt->d.max_new_tokens) return fail(rt, LUM_E_INVALID, "batch_get_decoded: the log holds at most %d steps", rt->d.max_new_tokens);
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    if (n_steps) CU(rt, cudaMemcpyAsync(host_out, rt->b_log, n_steps * rt->batch_n * 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return check_status(rt);
+}
+
+int32_t lum_batch_get_logits(lum_rt* rt, int32_t seq, float* host_out, size_t n) {
+    if (!rt || !rt->has_model || !host_out || rt->batch_n < 1 || !rt->rows.logits) return fail(rt, LUM_E_INVALID, "batch_get_logits: no batch or null output");
+    if (seq < 0 || seq >= rt->batch_n || n != (size_t)rt->vocab_l) return fail(rt, LUM_E_INVALID, "batch_get_logits: sequence %d of %d, %zu elements (vocabulary %d)", seq, rt->batch_n, n, rt->vocab_l);
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    CU(rt, cudaMemcpyAsync(host_out, rt->rows.logits + (size_t)seq * rt->vocab_l, n * 4, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return check_status(rt);
 }
 
 int32_t lum_tp_unique_id(uint8_t* out128) {
@@ -966,6 +1275,9 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     free_model(rt);
     lum_model_desc d = *dp;
     if (d.tp_size <= 0) { d.tp_size = 1; d.tp_rank = 0; }
+    if (d.max_batch <= 0) d.max_batch = 1;
+    if (d.max_batch > 1024) return fail(rt, LUM_E_INVALID, "max_batch %d (at most 1024 sequences)", d.max_batch);
+    if (d.max_batch > 1 && d.tp_size > 1) return fail(rt, LUM_E_UNSUPPORTED, "several sequences under tensor parallelism");
     if (d.max_new_tokens <= 0) d.max_new_tokens = 4096;
     const int tp = d.tp_size;
     if (d.n_layers <= 0 || d.hidden <= 0 || d.n_q_heads <= 0 || d.n_kv_heads <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.max_seq <= 0)
@@ -1010,7 +1322,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
             TRY(alloc_tensor(rt, w.q_norm, ek, 1, hd, 1, hd, 0, 0));
             TRY(alloc_tensor(rt, w.k_norm, ek, 1, hd, 1, hd, 0, 0));
         }
-        const size_t cache_bytes = (size_t)d.max_seq * kvd_l * kv_elem;
+        const size_t cache_bytes = (size_t)d.max_batch * d.max_seq * kvd_l * kv_elem;
         TRY(dev_alloc(rt, &w.kc, cache_bytes));
         TRY(dev_alloc(rt, &w.vc, cache_bytes));
         cudaMemsetAsync(w.kc, 0, cache_bytes, rt->stream);
@@ -1073,6 +1385,13 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     rt->c_log2e = round6(1.0 / std::log(2.0));
     rt->c_half_pi = round6(1.5707963267948966);
     rt->dim_s = 1; rt->dim_p = 0;
+    rt->max_batch = d.max_batch; rt->cur_seq = 0; rt->batch_n = 0;
+    rt->prefill_min_rows = rt->cfg.prefill_min_rows > 0 ? rt->cfg.prefill_min_rows : 4;
+    if (d.max_batch > 1) {
+        if (int r2 = dev_alloc(rt, (void**)&rt->b_step, 4)) { free_model(rt); return r2; }
+        if (int r2 = dev_alloc(rt, (void**)&rt->b_log, (size_t)d.max_new_tokens * d.max_batch * 4)) { free_model(rt); return r2; }
+        cudaMemsetAsync(rt->b_step, 0, 4, rt->stream);
+    }
     rt->has_model = true;
     rt->use_mega = rt->cfg.use_mega;
     if (const char* e = getenv("LUM_L2_PREFETCH")) rt->l2_prefetch = atoi(e) != 0;
@@ -1200,7 +1519,7 @@ int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes) {
 int32_t lum_kv_reset(lum_rt* rt) {
     if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "kv_reset: no model");
     CU(rt, cudaSetDevice(rt->cfg.device));
-    const size_t bytes = (size_t)rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+    const size_t bytes = (size_t)rt->max_batch * rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);   // every sequence
     for (LayerW& w : rt->L) {
         CU(rt, cudaMemsetAsync(w.kc, 0, bytes, rt->stream));
         CU(rt, cudaMemsetAsync(w.vc, 0, bytes, rt->stream));
@@ -1218,7 +1537,8 @@ int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float
     float* tmp = nullptr;
     cudaError_t e = cudaMalloc((void**)&tmp, n * 4);
     if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "kv_read: %s", cudaGetErrorString(e));
-    const void* src = kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc;
+    const size_t seq_off = (size_t)rt->cur_seq * rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+    const void* src = (const char*)(kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc) + seq_off;
     e = launch_to_f32(src, rt->d.kv_dtype == LUM_BF16 ? WK_BF16 : WK_F32, tmp, n, rt->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);

@@ -36,7 +36,7 @@ SLOT = {
 
 class Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("use_graph", C.c_int32), ("use_pdl", C.c_int32), ("attn_splits", C.c_int32),
-                ("use_mega", C.c_int32)]
+                ("use_mega", C.c_int32), ("prefill_min_rows", C.c_int32), ("wait_budget_ms", C.c_int32)]
 
 
 class ModelDesc(C.Structure):
@@ -48,7 +48,7 @@ class ModelDesc(C.Structure):
         ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("rope_style", C.c_int32),
         ("weight_dtype", C.c_uint32), ("embed_dtype", C.c_uint32), ("kv_dtype", C.c_uint32),
         ("qk_norm", C.c_int32), ("tied_head", C.c_int32), ("max_new_tokens", C.c_int32),
-        ("tp_size", C.c_int32), ("tp_rank", C.c_int32),
+        ("tp_size", C.c_int32), ("tp_rank", C.c_int32), ("max_batch", C.c_int32),
     ]
 
     def copy(self, **kw) -> "ModelDesc":
@@ -69,7 +69,7 @@ class Stats(C.Structure):
 
 def _desc(**kw) -> ModelDesc:
     d = ModelDesc()
-    base = dict(max_seq=4096, rms_eps=1e-5, rope_style=0, qk_norm=0, tied_head=0, max_new_tokens=4096, tp_size=1, tp_rank=0)
+    base = dict(max_seq=4096, rms_eps=1e-5, rope_style=0, qk_norm=0, tied_head=0, max_new_tokens=4096, tp_size=1, tp_rank=0, max_batch=1)
     base.update(kw)
     for k, v in base.items():
         setattr(d, k, v)
@@ -182,6 +182,11 @@ def load_library() -> C.CDLL:
         "lum_get_decoded": (i32, [vp, P(i32), sz]),
         "lum_decode_reset": (i32, [vp]),
         "lum_synchronize": (i32, [vp]),
+        "lum_seq_select": (i32, [vp, i32]),
+        "lum_batch_begin": (i32, [vp, i32, P(i32), P(i32)]),
+        "lum_batch_decode": (i32, [vp, i32]),
+        "lum_batch_get_decoded": (i32, [vp, P(i32), sz]),
+        "lum_batch_get_logits": (i32, [vp, i32, P(C.c_float), sz]),
         "lum_profile": (i32, [vp, i32, P(C.c_double), C.c_char_p, sz]),
         "lum_launches_per_step": (i32, [vp, P(i32)]),
         "lum_stream": (vp, [vp]),
@@ -260,7 +265,8 @@ class B200Runtime:
     # ---- lifecycle -------------------------------------------------------------------------------
     @classmethod
     def initialize(cls, device: int = 0, use_graph: Optional[bool] = None, use_pdl: Optional[bool] = None,
-                   attn_splits: Optional[int] = None, use_mega: Optional[bool] = None) -> "B200Runtime":
+                   attn_splits: Optional[int] = None, use_mega: Optional[bool] = None, prefill_min_rows: Optional[int] = None,
+                   wait_budget_ms: Optional[int] = None) -> "B200Runtime":
         lib = load_library()
         cfg = Config()
         lib.lum_config_default(C.byref(cfg))
@@ -273,6 +279,10 @@ class B200Runtime:
             cfg.attn_splits = int(attn_splits)
         if use_mega is not None:
             cfg.use_mega = int(use_mega)
+        if prefill_min_rows is not None:
+            cfg.prefill_min_rows = int(prefill_min_rows)
+        if wait_budget_ms is not None:
+            cfg.wait_budget_ms = int(wait_budget_ms)
         h = C.c_void_p()
         rc = lib.lum_create(C.byref(cfg), C.byref(h))
         if rc != 0:
@@ -462,6 +472,33 @@ class B200Runtime:
 
     def synchronize(self) -> None:
         self._ck(self._lib.lum_synchronize(self._h))
+
+    # ---- several sequences ---------------------------------------------------------------------------
+    def seq_select(self, seq: int) -> None:
+        """Which of the ``max_batch`` sequences ``execute`` / ``decode_greedy`` / ``kv_*`` address."""
+        self._ck(self._lib.lum_seq_select(self._h, seq))
+
+    def batch_begin(self, tokens: Sequence[int], positions: Sequence[int]) -> None:
+        n = len(tokens)
+        t = (C.c_int32 * n)(*[int(v) for v in tokens])
+        p = (C.c_int32 * n)(*[int(v) for v in positions])
+        self._ck(self._lib.lum_batch_begin(self._h, n, t, p))
+        self._batch_n = n
+
+    def batch_decode(self, n_steps: int) -> None:
+        self._ck(self._lib.lum_batch_decode(self._h, n_steps))
+
+    def batch_get_decoded(self, n_steps: int):
+        import numpy as np
+        out = np.empty((n_steps, self._batch_n), dtype=np.int32)
+        self._ck(self._lib.lum_batch_get_decoded(self._h, out.ctypes.data_as(C.POINTER(C.c_int32)), n_steps))
+        return out
+
+    def batch_get_logits(self, seq: int):
+        import numpy as np
+        out = np.empty(self.desc.vocab, dtype=np.float32)
+        self._ck(self._lib.lum_batch_get_logits(self._h, seq, out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
 
     def profile(self, trials: int = 16):
         us = C.c_double()

@@ -23,8 +23,20 @@ def rel_err(a, b):
     return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))) / np.max(np.abs(b)))
 
 
+PER_TOKEN = 1 << 30      # prefill_min_rows that keeps every prompt on the one-decode-step-per-token path
+
+
 @pytest.fixture(scope="module")
 def rt(pkg):
+    """Prompts token by token (the executors are compared bit for bit on it); the multi-row prompt path has tests of its own."""
+    r = pkg.B200Runtime.initialize(device=0, prefill_min_rows=PER_TOKEN)
+    yield r
+    r.close()
+
+
+@pytest.fixture(scope="module")
+def rt_rows(pkg):
+    """Default configuration: prompts of 4 tokens or more run as rows of tensor-core matrix products."""
     r = pkg.B200Runtime.initialize(device=0)
     yield r
     r.close()
@@ -159,7 +171,7 @@ def test_llama_shape_two_layers_32_steps(pkg, mega):
         prompt = orc.synth_tokens(seed, 24)
         _LLAMA2L = (prompt,) + orc.generate(prompt, 33, return_last_logits=True, return_margins=True)
     prompt, want, lo, margins = _LLAMA2L
-    rt = pkg.B200Runtime.initialize(device=0, use_mega=bool(mega))
+    rt = pkg.B200Runtime.initialize(device=0, use_mega=bool(mega), prefill_min_rows=PER_TOKEN)
     try:
         rt.load_model(desc)
         rt.synth(seed)
@@ -203,7 +215,7 @@ def test_launch_modes_agree(pkg, rt, graph, pdl, mega):
     rt.synth(3)
     base = rt.generate(prompt, 12)
     lb = rt.get_f32()
-    other = pkg.B200Runtime.initialize(device=0, use_graph=bool(graph), use_pdl=bool(pdl), use_mega=bool(mega))
+    other = pkg.B200Runtime.initialize(device=0, use_graph=bool(graph), use_pdl=bool(pdl), use_mega=bool(mega), prefill_min_rows=PER_TOKEN)
     try:
         other.load_model(desc)
         other.synth(3)
@@ -361,5 +373,105 @@ def test_full_size_configuration_matches_oracle_fixture(pkg, name):
                     # above, so the last layer's rows agree to a few bfloat16 steps, not bit for bit
                     assert rms <= 1e-2, (layer, kind, rms)
         print(f"{name}: 32 tokens equal; logits rel err {err0:.2e} (after the prompt), {err1:.2e} (after 32 tokens); min margin {float(margins.min()):.2e}")
+    finally:
+        rt.close()
+
+
+# ------------------------------------------------------------------------------------------------- prompts as rows (M > 1)
+@pytest.mark.parametrize("name,n_prompt", [("small_q8", 4), ("small_q8", 33), ("small_q8", 100), ("llama3_8b_q8_2layer", 2), ("llama3_8b_q8_2layer", 32),
+                                           ("llama3_8b_q8_2layer", 128), ("llama3_8b_q8_2layer", 200), ("qwen3_4b_q8_2layer", 70)])
+def test_prompt_as_rows_matches_oracle_and_per_token_path(pkg, name, n_prompt):
+    """A prompt taken as rows of tensor-core matrix products (the reference's graph computes all s rows per execute,
+    examples/llama/src/model.rs:91-113): greedy tokens identical to the oracle's, logits within tolerance, and the K/V rows it
+    writes equal to those of the one-token-at-a-time path up to a bfloat16 rounding step."""
+    desc = pkg.CONFIGS[name]
+    desc = desc.copy(max_seq=max(desc.max_seq, n_prompt + 16))
+    seed, n_new = 77, 9
+    orc = OracleModel(desc)
+    orc.synth(seed)
+    prompt = orc.synth_tokens(seed, n_prompt)
+    want, lo, margins = orc.generate(prompt, n_new, return_last_logits=True, return_margins=True)
+    rows = pkg.B200Runtime.initialize(device=0, prefill_min_rows=2)
+    tok = pkg.B200Runtime.initialize(device=0, prefill_min_rows=PER_TOKEN)
+    try:
+        for r in (rows, tok):
+            r.load_model(desc)
+            r.synth(seed)
+            r.kv_reset(); r.decode_reset()
+            r.set_data(prompt); r.execute({"s": n_prompt, "p": 0})
+        la, lb = rows.get_f32(), tok.get_f32()
+        assert rows.get_token() == tok.get_token() == want[0]
+        assert rel_err(la, lb) <= 1e-3
+        for layer in (0, desc.n_layers - 1):
+            for kind in ("k", "v"):
+                ka, kb = rows.kv_read(layer, kind, n_prompt), tok.kv_read(layer, kind, n_prompt)
+                assert np.max(np.abs(ka - kb)) <= 2.0 ** -6 * np.max(np.abs(kb)), (layer, kind)      # a bfloat16 step of the largest values
+                assert np.mean(ka == kb) > 0.9, (layer, kind, float(np.mean(ka == kb)))
+        rows.decode_greedy(n_new - 1)
+        got = [want[0]] + [int(t) for t in rows.get_decoded(n_new - 1)]
+        assert got == want, f"min oracle top-1/top-2 margin {min(margins):.3e}"
+        assert rel_err(rows.get_f32(), lo) <= LOGIT_TOL
+        assert rows.stats().launches_per_step > 0
+    finally:
+        rows.close(); tok.close()
+
+
+def test_prompt_rows_in_chunks_and_after_a_prefix(pkg):
+    """More rows than one pass takes (LUM_ROWS_CAP) and a prompt that continues a cached prefix: same tokens as one pass."""
+    import os as _os
+    desc = pkg.CONFIGS["small_q8"]
+    prompt = [(7 * i + 3) % desc.vocab for i in range(90)]
+    one = pkg.B200Runtime.initialize(device=0, prefill_min_rows=2)
+    one.load_model(desc); one.synth(5)
+    base = one.generate(prompt, 8)
+    la = one.get_f32()
+    one.close()
+    _os.environ["LUM_ROWS_CAP"] = "32"
+    try:
+        two = pkg.B200Runtime.initialize(device=0, prefill_min_rows=2)
+        two.load_model(desc); two.synth(5)
+        assert two.generate(prompt, 8) == base and (two.get_f32() == la).all()     # passes of 32, 32, 26 rows: the same arithmetic per row
+        two.kv_reset(); two.decode_reset()
+        two.set_data(prompt[:41]); two.execute({"s": 41, "p": 0})
+        two.set_data(prompt[41:]); two.execute({"s": 49, "p": 41})
+        first = two.get_token()
+        two.decode_greedy(7)
+        assert [first] + [int(t) for t in two.get_decoded(7)] == base
+        two.close()
+    finally:
+        del _os.environ["LUM_ROWS_CAP"]
+
+
+def test_batched_decode_equals_sequences_decoded_alone(pkg):
+    """Four sequences with prompts of different lengths, decoded together one row each per step: every sequence gets the
+    tokens it gets when decoded alone."""
+    desc = pkg.CONFIGS["llama3_8b_q8_2layer"].copy(max_batch=4, max_seq=128)
+    seed, steps = 31, 10
+    prompts = [[(11 * i + 5 * s + 1) % desc.vocab for i in range(n)] for s, n in enumerate((5, 17, 40, 9))]
+    alone = []
+    solo = pkg.B200Runtime.initialize(device=0)
+    solo.load_model(desc.copy(max_batch=1)); solo.synth(seed)
+    for p in prompts:
+        alone.append(solo.generate(p, steps + 1))
+    solo.close()
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc); rt.synth(seed)
+        firsts = []
+        for s, p in enumerate(prompts):
+            rt.seq_select(s)
+            rt.set_data(p); rt.execute({"s": len(p), "p": 0})
+            firsts.append(rt.get_token())
+        assert firsts == [a[0] for a in alone]
+        rt.batch_begin(firsts, [len(p) for p in prompts])
+        rt.batch_decode(steps)
+        log = rt.batch_get_decoded(steps)
+        for s in range(len(prompts)):
+            assert [int(t) for t in log[:, s]] == alone[s][1:], f"sequence {s}"
+        assert rt.batch_get_logits(2).shape == (desc.vocab,)
+        with pytest.raises(pkg.LumError, match="capacity"):
+            rt.batch_decode(200)
+        with pytest.raises(pkg.LumError, match="max_batch"):
+            rt.seq_select(4)
     finally:
         rt.close()
