@@ -441,6 +441,104 @@ def check_parity(rt, prompt, prompt_logits, first_token, n_decoded, world, rank,
             "fixture": os.path.relpath(path, ROOT)}
 
 
+def run_tensor_core_regime(args, pkg, which: str):
+    """The Llama-3-8B-shape model in the regime where the work is a matrix-matrix product (one GPU):
+    `llama3_8b_q8_bs32`: batched decode, 32 sequences with 2048 cached tokens each, one row per sequence and step; a "step"
+    is `--tokens-per-step` tokens of every sequence.  HBM-bound: weights once + every sequence's cache per token step.
+    `llama3_8b_q8_prefill4096`: one 4096-token prompt; a "step" is the whole prompt.  Tensor-pipe-bound."""
+    import torch
+    torch.cuda.set_device(0)
+    peaks, peak_kind = measured_peaks()
+    base = pkg.CONFIGS["llama3_8b_q8"]
+    rt = pkg.B200Runtime.initialize(device=0)
+    sampler = ClockSampler(physical_gpu_index(0))
+    if which == "llama3_8b_q8_bs32":
+        B, ctx, tps = 32, 2048, max(1, min(TOKENS_PER_STEP, 16))
+        total = (args.warmup + 2 * args.steps) * tps          # warm-up, the timed steps, then the same number again end to end
+        rt.load_model(base.copy(max_batch=B, max_seq=ctx + total + 8, max_new_tokens=total + 8))
+        rt.synth(SEED)
+        firsts = []
+        for sq in range(B):                      # every sequence's context: a seeded random-id prompt, run as rows
+            rt.seq_select(sq)
+            ids = _prompt_tokens(base.vocab, ctx + sq)[sq:]
+            rt.set_data(ids); rt.execute({"s": ctx, "p": 0})
+            firsts.append(rt.get_token())
+        rt.batch_begin(firsts, [ctx] * B)
+        for _ in range(args.warmup):
+            rt.batch_decode(tps)
+        rt.synchronize()
+        ext = torch.cuda.ExternalStream(rt.stream())
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for _ in range(args.steps):
+            rt.batch_decode(tps)
+        e1.record(ext)
+        rt.synchronize()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+        n_tok = args.steps * tps * B
+        value = n_tok / (ms * 1e-3)
+        p_mean = ctx + (args.warmup + args.steps / 2.0) * tps
+        bytes_step = pkg.decode_bytes_per_token(base, 0) - 131072 + 131072.0 * (p_mean + 1) * B     # weights once, every sequence's cache
+        ach = bytes_step * (args.steps * tps) / (ms * 1e-3) / 1e9
+        # end to end: the same loop with the sampled tokens of every step read back by the host
+        t0 = time.perf_counter()
+        for _ in range(args.steps * tps):
+            rt.batch_decode(1)
+            rt.batch_get_decoded(1)
+        e2e = args.steps * tps * B / (time.perf_counter() - t0)
+        line = {"metric": "q8_llama3_8b_bs32_decode_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 x int8 -> s32 on tcgen05 (three int8 levels of the f32 activations), f32 scales and sums", "data": "synthetic",
+                "config": {"workload": which, "batch": B, "context": ctx, "tokens_per_step": tps, "seed": SEED,
+                           "l2": "weights 8.0 GB + caches 8.6 GB >> 126 MB L2"},
+                "roofline": {"bound": "hbm", "kernel": "whole batched step (q8_gemm_tc + attn_rows dominate)", "achieved": ach, "peak": peaks["hbm_gbs"],
+                             "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "bytes_per_step": bytes_step, "traffic": None},
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * B * tps,
+                        "note": "every step's sampled tokens device->host; the fed-back tokens stay on the device"},
+                "gpu_launches": int(rt.stats().kernel_launches), "clocks": clocks}
+    else:
+        n = 4096
+        rt.load_model(base.copy(max_seq=n + 8))
+        rt.synth(SEED)
+        ids = _prompt_tokens(base.vocab, n)
+        ext = torch.cuda.ExternalStream(rt.stream())
+        for _ in range(max(1, args.warmup)):
+            rt.set_data(ids); rt.execute({"s": n, "p": 0})
+        rt.synchronize()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for _ in range(args.steps):
+            rt.set_data(ids); rt.execute({"s": n, "p": 0})
+        e1.record(ext)
+        rt.synchronize()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+        value = args.steps * n / (ms * 1e-3)
+        # linear layers 2 * weights * rows (the vocabulary projection runs for the last row only) + causal attention
+        d = base
+        w_layers = d.n_layers * (2 * d.hidden * d.n_q_heads * d.head_dim + 2 * d.hidden * d.n_kv_heads * d.head_dim + 3 * d.hidden * d.ffn)
+        flops = 2.0 * w_layers * n + 2.0 * d.vocab * d.hidden + d.n_layers * 4.0 * d.n_q_heads * d.head_dim * n * (n + 1) / 2
+        ach = flops * args.steps / (ms * 1e-3) / 1e12
+        t0 = time.perf_counter()
+        rt.set_data(ids); rt.execute({"s": n, "p": 0}); rt.get_token()
+        e2e = n / (time.perf_counter() - t0)
+        line = {"metric": "q8_llama3_8b_prefill4096_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 x int8 -> s32 on tcgen05 (three int8 levels of the f32 activations), f32 scales and sums; f32 attention", "data": "synthetic",
+                "config": {"workload": which, "batch": 1, "prompt_len": n, "seed": SEED},
+                "roofline": {"bound": "tensor", "kernel": "whole prompt (q8_gemm_tc + attn_rows)", "achieved": ach, "peak": peaks.get("bf16_tflops_sustained", 1383.9),
+                             "unit": "TFLOP/s", "frac": ach / peaks.get("bf16_tflops_sustained", 1383.9), "peak_kind": f"of {peak_kind} (sustained bf16 GEMM)",
+                             "flops_per_step": flops, "traffic": None},
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4,
+                        "note": "token ids host->device, the sampled token device->host"},
+                "gpu_launches": int(rt.stats().kernel_launches), "clocks": clocks}
+    rt.close()
+    print(json.dumps(line))
+
+
 def _prompt_tokens(vocab: int, n: int):
     """The seeded prompt, generated without the oracle: SplitMix64 counter generator, tensor id 2^20."""
     mask = (1 << 64) - 1
@@ -465,14 +563,21 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
-    ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8"],
-                    help="llama3_8b_q8: the configuration the metric is quoted on (default); qwen3_4b_q8: the Qwen3-4B shape")
+    ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8", "llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096"],
+                    help="llama3_8b_q8: the configuration the metric is quoted on (default); qwen3_4b_q8: the Qwen3-4B shape; "
+                         "llama3_8b_q8_bs32 / llama3_8b_q8_prefill4096: the same model in the tensor-core regime (batched decode / one long prompt)")
     ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor"],
                     help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts; floor: the decode step with all projections shrunk away")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
     PROMPT_LEN, TOKENS_PER_STEP = args.prompt_len, args.tokens_per_step
+    if args.workload in ("llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096"):
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU arm is timed on the batch-1 decode workloads only"}))
+            return
+        run_tensor_core_regime(args, pkg, args.workload)
+        return
     if args.workload != WORKLOAD:
         set_workload(args.workload, prompt_given=args.prompt_len != 512)
     if args.only == "kernel":
