@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode(const AttnArgs a)
     const int p = a.state->pos;
     const bool ok = p >= 0 && p < a.max_seq;
     if (ok) attn_fill_rope<HD, RS>(a, attn_smem, p, (int)threadIdx.x);
+    if (ok && a.kv_prefetch) attn_prefetch_rows<HD, BF16>(a, (int)blockIdx.x, (int)blockIdx.y, p, (int)threadIdx.x);
     if (a.use_pdl) pdl_grid_wait();
     if (!ok) {                                  // the same for every CTA of the grid: no cluster barrier is left half attended
         if (threadIdx.x == 0) atomicOr(a.status, LUM_ST_BAD_POS);

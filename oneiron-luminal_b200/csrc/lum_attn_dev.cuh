@@ -128,6 +128,25 @@ __device__ __forceinline__ void load_dpl(const void* base, size_t elem_off, floa
     }
 }
 
+// The cached rows a CTA will walk do not depend on the projections of the current step (rows [.., p) were written by earlier
+// steps), so a kernel that still waits for those projections can already ask for them to be brought into L2: one request
+// per 128-byte line of every K and V row of this (KV head, split).
+template <int HD, bool BF16>
+__device__ __forceinline__ void attn_prefetch_rows(const AttnArgs& a, int kvh, int split, int p, int tid) {
+    const int lo = (a.window > 0 && p + 1 > a.window) ? p + 1 - a.window : 0;
+    const int n_cached = p - lo;
+    const int per = (n_cached + a.n_splits - 1) / a.n_splits;
+    const int r0 = lo + split * per;
+    const int nc = max(0, min(p, r0 + per) - r0);
+    constexpr int kRowBytes = HD * (BF16 ? 2 : 4), kLines = kRowBytes / 128;        // lines per K (or V) row of one head
+    const size_t row_bytes = (size_t)a.n_kv * kRowBytes;
+    for (int i = tid; i < nc * 2 * kLines; i += kAttnThreads) {
+        const int r = i / (2 * kLines), w = i - r * (2 * kLines);
+        const char* base = (const char*)(w < kLines ? a.k_cache : a.v_cache) + (size_t)(r0 + r) * row_bytes + (size_t)kvh * kRowBytes + (size_t)(w % kLines) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base));
+    }
+}
+
 // Runs on exactly kAttnThreads threads (tid 0..511) that synchronise on named barrier `bar_id`.
 // p = position of the token being processed (rows [.., p) are cached, row p is this step's own).
 // smem: attn_smem_bytes(HD, G) bytes, 16-byte aligned.

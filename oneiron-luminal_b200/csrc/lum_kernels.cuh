@@ -118,6 +118,7 @@ struct AttnArgs {
     uint32_t* status;
     int use_pdl;
     int cluster;           // 1: the splits of a KV head run as one thread-block cluster and merge through its shared memory
+    int kv_prefetch;       // 1: ask for this CTA's cached rows to be brought into L2 while still waiting for the projections
     // Optional: bytes the NEXT kernels will stream (weights of the o projection, ...).  Attention is latency-bound and leaves
     // HBM idle, so its CTAs ask for these ranges to be brought into L2 meanwhile (a hint: nothing waits for it).
     const void* l2_pf_ptr[2];

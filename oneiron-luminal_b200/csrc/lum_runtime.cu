@@ -126,7 +126,8 @@ struct lum_rt {
     unsigned int* am_cnt = nullptr;
     bool down_ksplit = true;          // LUM_DOWN_KSPLIT=0: the down projection as one job per row group
     bool attn_cluster = false;        // the splits of a KV head merge through a thread-block cluster (LUM_ATTN_CLUSTER=0: global partials + arrival ticket)
-    bool l2_prefetch = false;         // LUM_L2_PREFETCH=1: attention warms L2 with the o projection's weights (measured: no gain)
+    bool kv_prefetch = true;          // LUM_KV_PREFETCH=0: attention does not warm L2 with its cached rows before the projections finish
+    int l2_pf_mb = 0;                 // LUM_L2_PREFETCH_MB: attention's CTAs prefetch this many MB of each of the gate and up weight streams into L2
     unsigned int* step_ctr = nullptr;   // one job-claim counter per projection of a decode step (kernel-per-op executors)
     uint32_t* status = nullptr;
     int n_splits = 1;
@@ -426,8 +427,14 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         t.c_inv_d = rt->c_inv_d; t.c_ln_theta = rt->c_ln_theta; t.c_log2e = rt->c_log2e; t.c_half_pi = rt->c_half_pi;
         t.theta = d.rope_theta; t.window = 0; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
         t.cluster = rt->attn_cluster ? 1 : 0;
-        if (rt->l2_prefetch && w.o.kc > 0) {
-            t.l2_pf_ptr[0] = w.o.w; t.l2_pf_bytes[0] = q8_packed_bytes((int)w.o.rows, (int)w.o.cols);
+        t.kv_prefetch = rt->kv_prefetch ? 1 : 0;
+        if (rt->l2_pf_mb > 0 && w.gate.kc > 0 && w.up.kc > 0) {
+            // Attention leaves HBM idle (it moves a few megabytes in ~10 us): its CTAs ask for the head of the gate and up weight
+            // streams — what the kernel after next reads first — to be brought into L2 meanwhile.
+            const unsigned long long want = (unsigned long long)rt->l2_pf_mb << 20;
+            const unsigned long long gb = q8_packed_bytes((int)w.gate.rows, (int)w.gate.cols), ub = q8_packed_bytes((int)w.up.rows, (int)w.up.cols);
+            t.l2_pf_ptr[0] = w.gate.w; t.l2_pf_bytes[0] = want < gb ? want : gb;
+            t.l2_pf_ptr[1] = w.up.w; t.l2_pf_bytes[1] = want < ub ? want : ub;
         }
         CU(rt, launch_attn_decode(t, st)); n++;
 
@@ -1394,7 +1401,10 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     }
     rt->has_model = true;
     rt->use_mega = rt->cfg.use_mega;
-    if (const char* e = getenv("LUM_L2_PREFETCH")) rt->l2_prefetch = atoi(e) != 0;
+    rt->kv_prefetch = true;
+    if (const char* e = getenv("LUM_KV_PREFETCH")) rt->kv_prefetch = atoi(e) != 0;
+    rt->l2_pf_mb = 0;
+    if (const char* e = getenv("LUM_L2_PREFETCH_MB")) rt->l2_pf_mb = atoi(e);
     if (const char* e = getenv("LUM_DOWN_KSPLIT")) rt->down_ksplit = atoi(e) != 0;
     {
         bool want = true;         // measured: same tokens/s as the ticket merge with 8 KV heads on one GPU, +2.5 % with 4 per rank on two
