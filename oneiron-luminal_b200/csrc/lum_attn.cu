@@ -197,4 +197,15 @@ cudaError_t launch_tp_pick(const int* pairs, int pair_stride, const uint32_t* fl
     return cudaGetLastError();
 }
 
+// Tensor parallel: the step-boundary ordering of the fused exchange for steps that end without the vocabulary projection.
+__global__ void tp_fence(const float* parts, int part_stride_floats, int n_ranks, const uint32_t* seq, uint32_t tag, uint32_t* status) {
+    if ((int)threadIdx.x >= n_ranks) return;
+    float v;
+    if (!ld_ll_wait((const uint2*)(parts + (size_t)threadIdx.x * part_stride_floats), peer_word(__ldcg(seq), tag), &v)) atomicOr(status, LUM_ST_WAIT_PEER);
+}
+cudaError_t launch_tp_fence(const float* parts, int part_stride_floats, int n_ranks, const uint32_t* seq, uint32_t tag, uint32_t* status, cudaStream_t st) {
+    tp_fence<<<1, 32, 0, st>>>(parts, part_stride_floats, n_ranks, seq, tag, status);
+    return cudaGetLastError();
+}
+
 }  // namespace lum

@@ -222,7 +222,29 @@ __device__ __forceinline__ float row_dot(const GemvSeg& sg, int row, int K, cons
         }
     } else {
         const uint16_t* w = (const uint16_t*)sg.w + (size_t)row * K;
-        for (int i = lane; i < K; i += 32) acc = fmaf(bf16_bits_to_f32(w[i]), xs[i], acc);
+        if ((K & 7) == 0) {
+            // 16-byte loads (8 weights), two in flight per lane: a vocabulary-sized bf16 matrix (a head tied to the embedding) is
+            // hundreds of megabytes per token and must stream
+            const uint4* w8 = (const uint4*)w;
+            const int n8 = K >> 3;
+            auto dot8 = [&](uint4 a, int i, float s) {
+                const float4 x0 = *(const float4*)(xs + (size_t)i * 8), x1 = *(const float4*)(xs + (size_t)i * 8 + 4);
+                s = fmaf(__uint_as_float(a.x << 16), x0.x, s); s = fmaf(__uint_as_float(a.x & 0xffff0000u), x0.y, s);
+                s = fmaf(__uint_as_float(a.y << 16), x0.z, s); s = fmaf(__uint_as_float(a.y & 0xffff0000u), x0.w, s);
+                s = fmaf(__uint_as_float(a.z << 16), x1.x, s); s = fmaf(__uint_as_float(a.z & 0xffff0000u), x1.y, s);
+                s = fmaf(__uint_as_float(a.w << 16), x1.z, s); s = fmaf(__uint_as_float(a.w & 0xffff0000u), x1.w, s);
+                return s;
+            };
+            int i = lane;
+            for (; i + 32 < n8; i += 64) {
+                const uint4 a = __ldcs(w8 + i), b = __ldcs(w8 + i + 32);
+                acc = dot8(a, i, acc);
+                acc = dot8(b, i + 32, acc);
+            }
+            if (i < n8) acc = dot8(__ldcs(w8 + i), i, acc);
+        } else {
+            for (int i = lane; i < K; i += 32) acc = fmaf(bf16_bits_to_f32(w[i]), xs[i], acc);
+        }
     }
     return warp_sum(acc);
 }
@@ -352,8 +374,9 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
     }
 
     if (a.ksplit == 2) return cudaErrorInvalidValue;     // the caller's consumer expects two partial vectors: only the streaming kernel makes them
-    // direct kernel: a few CTAs per SM's worth of rows, at least 8 rows per CTA
-    int grid = sm_count * 2;
+    // direct kernel: a few CTAs per SM's worth of rows, at least 8 rows per CTA; a large bf16 / f32 matrix gets as many CTAs as
+    // an SM can hold, so that enough loads are in flight to keep HBM busy
+    int grid = sm_count * (a.wkind != WK_Q8 && (long long)rows_total * a.K >= (1ll << 24) ? 8 : 2);
     if (grid > (rows_total + 7) / 8) grid = (rows_total + 7) / 8;
     if (grid < 1) grid = 1;
     const int max_rows = (rows_total + grid - 1) / grid + 1;

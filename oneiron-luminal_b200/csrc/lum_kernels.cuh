@@ -152,18 +152,22 @@ cudaError_t launch_embed(const EmbedArgs& a, cudaStream_t st);
 cudaError_t launch_tp_pick(const int* pairs, int pair_stride, const uint32_t* flags, const uint32_t* seq, uint32_t tag, uint32_t* status,
                            int n_ranks, DecodeState* state, int* tokens_out, int advance, cudaStream_t st);
 
+// tensor parallel: wait (bounded) until one {value, word} element of every rank's partial vector carries `tag` of the current step
+cudaError_t launch_tp_fence(const float* parts, int part_stride_floats, int n_ranks, const uint32_t* seq, uint32_t tag, uint32_t* status, cudaStream_t st);
+
 // synthetic tensors + format conversion
+// cols: K of the device layout; valid_cols (0 = cols): the columns that exist — a packed K-shard is padded with zero columns to whole tiles
 cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,
-                            size_t full_cols, int kc, cudaStream_t st);
+                            size_t full_cols, int kc, cudaStream_t st, size_t valid_cols = 0);
 cudaError_t launch_synth_normal(uint64_t seed, uint64_t tid, void* out, int kind, size_t rows, size_t cols, size_t row0, size_t col0,
                                 size_t full_cols, int ones, cudaStream_t st);
 // Packed Q8_0 layout: the K-chunk a [rows, K] matrix packs with (0 = not packable) and its size in bytes.
 int q8_pack_kc(int rows, int K);
 size_t q8_packed_bytes(int rows, int K);
-cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st);
+cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st, int valid_cols = 0);
 cudaError_t launch_q8_unpack_wire(const uint8_t* blocks, int8_t* q, __half* s, size_t n_blocks, cudaStream_t st);
 cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size_t n_elems, cudaStream_t st);
-cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st);
+cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st, int valid_cols = 0);
 cudaError_t launch_to_f32(const void* in, int kind, float* out, size_t n, cudaStream_t st);
 
 }  // namespace lum

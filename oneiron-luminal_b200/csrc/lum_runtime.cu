@@ -83,6 +83,8 @@ struct Tensor {
     int kind = WK_F32;
     int kc = 0;              // Q8_0: 0 = planes, 512 = packed tile stream
     size_t rows = 0, cols = 0;          // this rank's shard
+    size_t kdev = 0;                    // K of the device layout: cols, or cols rounded up to whole 512-column tiles with zero columns
+                                        // (a packed Q8_0 K-shard such as 14336 / 8 = 1792 -> 2048) so that it still takes the streaming kernels
     size_t row0 = 0, col0 = 0;          // shard origin in the full tensor
     size_t full_rows = 0, full_cols = 0;
     size_t bytes() const {
@@ -224,13 +226,18 @@ int dev_alloc(lum_rt* rt, void** p, size_t bytes) {
 }
 
 int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_cols, size_t rows, size_t cols, size_t row0, size_t col0) {
-    t.kind = kind; t.rows = rows; t.cols = cols; t.row0 = row0; t.col0 = col0; t.full_rows = full_rows; t.full_cols = full_cols;
+    t.kind = kind; t.rows = rows; t.cols = cols; t.kdev = cols; t.row0 = row0; t.col0 = col0; t.full_rows = full_rows; t.full_cols = full_cols;
     const size_t n = rows * cols;
     if (kind == WK_Q8) {
         if (cols % 32 || full_cols % 32 || col0 % 32) return fail(rt, LUM_E_INVALID, "Q8_0 tensors need K %% 32 == 0 (K = %zu)", cols);
+        t.kdev = cols;
         t.kc = q8_pack_kc((int)rows, (int)cols);
+        if (!t.kc && cols > 512) {
+            const size_t up = (cols + 511) / 512 * 512;
+            if (q8_pack_kc((int)rows, (int)up)) { t.kdev = up; t.kc = q8_pack_kc((int)rows, (int)up); }
+        }
         if (t.kc) {
-            if (int r = dev_alloc(rt, &t.w, q8_packed_bytes((int)rows, (int)cols) + 64)) return r;
+            if (int r = dev_alloc(rt, &t.w, q8_packed_bytes((int)rows, (int)t.kdev) + 64)) return r;
             t.s = nullptr;
         } else {
             if (int r = dev_alloc(rt, &t.w, n + 64)) return r;
@@ -432,7 +439,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
             // Attention leaves HBM idle (it moves a few megabytes in ~10 us): its CTAs ask for the head of the gate and up weight
             // streams — what the kernel after next reads first — to be brought into L2 meanwhile.
             const unsigned long long want = (unsigned long long)rt->l2_pf_mb << 20;
-            const unsigned long long gb = q8_packed_bytes((int)w.gate.rows, (int)w.gate.cols), ub = q8_packed_bytes((int)w.up.rows, (int)w.up.cols);
+            const unsigned long long gb = q8_packed_bytes((int)w.gate.rows, (int)w.gate.kdev), ub = q8_packed_bytes((int)w.up.rows, (int)w.up.kdev);
             t.l2_pf_ptr[0] = w.gate.w; t.l2_pf_bytes[0] = want < gb ? want : gb;
             t.l2_pf_ptr[1] = w.up.w; t.l2_pf_bytes[1] = want < ub ? want : ub;
         }
@@ -442,7 +449,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         GemvArgs o{};
         o.status = rt->status; o.use_pdl = pdl; o.wkind = w.o.kind;
         o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows, w.o.kc};
-        o.K = (int)w.o.cols; o.x = rt->attn;
+        o.K = (int)w.o.kdev; o.x = rt->attn;
         if (fused) publish_to_peers(o, 0, (uint32_t)(2 * l + 1));
         else if (tp) { o.epi = EPI_STORE; o.y = rt->part; }
         else { o.epi = EPI_RESID; o.y = cur; o.resid = cur; }
@@ -463,7 +470,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         GemvArgs dn{};
         dn.status = rt->status; dn.use_pdl = pdl; dn.wkind = w.down.kind;
         dn.nseg = 1; dn.seg[0] = {w.down.w, w.down.s, (int)w.down.rows, w.down.kc};
-        dn.K = (int)w.down.cols; dn.x = rt->h;
+        dn.K = (int)w.down.kdev; dn.x = rt->h;
         if (fused) publish_to_peers(dn, 1, (uint32_t)(2 * l + 2));
         else if (tp) { dn.epi = EPI_STORE; dn.y = rt->part; }
         else if (rt->down_ksplit && gemv_can_ksplit(dn.K, w.down.kc)) {
@@ -509,6 +516,14 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
             CU(rt, launch_tp_pick(rt->tp_pairs, 2, nullptr, nullptr, 0, rt->status, rt->tp_size, rt->state, rt->tokens_out, 1, st));
             n += 2;
         }
+    }
+    if (fused && !with_head && pending) {
+        // A step without the vocabulary projection (prompt processing) reads nobody's last down projection, so nothing would order
+        // the ranks at the step boundary: a rank running ahead could overwrite buffer 0 (next step's first o projection) while
+        // another still waits for this step's words in it.  Seeing ANY word of a rank's last down projection means that rank is
+        // past its reads of buffer 0: wait (bounded) for one element per rank.
+        CU(rt, launch_tp_fence((const float*)sym_part(rt->sym, pending_buf, 0), H * 2, rt->tp_size, rt->tp_seq, pending_tag, rt->status, st));
+        n++;
     }
     if (n_launch) *n_launch = n;
     return 0;
@@ -559,7 +574,7 @@ bool rows_supported(const lum_rt* rt) {
     if (d.n_q_heads / d.n_kv_heads > (d.head_dim == 128 ? 4 : 8)) return false;
     for (const LayerW& w : rt->L) {
         const Tensor* ts[] = {&w.q, &w.k, &w.v, &w.o, &w.gate, &w.up, &w.down};
-        for (const Tensor* t : ts) if (t->kc != 512) return false;
+        for (const Tensor* t : ts) if (t->kc != 512 || t->kdev != t->cols) return false;
     }
     return true;
 }
@@ -792,7 +807,7 @@ int setup_mega(lum_rt* rt) {
     for (int l = 0; l < d.n_layers && packed; l++) {
         LayerW& w = rt->L[(size_t)l];
         const Tensor* ts[] = {&w.q, &w.k, &w.v, &w.o, &w.gate, &w.up, &w.down};
-        for (const Tensor* t : ts) packed = packed && t->kc > 0;
+        for (const Tensor* t : ts) packed = packed && t->kc > 0 && t->kdev == t->cols;
         packed = packed && w.q.kc == w.k.kc && w.q.kc == w.v.kc && w.q.kc == w.gate.kc && w.q.kc == w.up.kc && w.q.kc == rt->lm_head.kc;
         MegaLayer& m = hl[(size_t)l];
         m.wq = (const unsigned char*)w.q.w; m.wk = (const unsigned char*)w.k.w; m.wv = (const unsigned char*)w.v.w;
@@ -1003,7 +1018,7 @@ int32_t lum_alloc_dummy_input(lum_rt* rt, int64_t hlir_node, size_t n_elems) {
     const uint64_t tid = tensor_id(slot, slot_layer_for_id(rt, slot, layer));
     cudaError_t e;
     const bool gains = slot == LUM_S_ATTN_NORM || slot == LUM_S_MLP_NORM || slot == LUM_S_FINAL_NORM || slot == LUM_S_Q_NORM || slot == LUM_S_K_NORM;
-    if (t->kind == WK_Q8) e = launch_synth_q8(0x5eedull, tid, (int8_t*)t->w, t->s, t->rows, t->cols, t->row0, t->col0, t->full_cols, t->kc, rt->stream);
+    if (t->kind == WK_Q8) e = launch_synth_q8(0x5eedull, tid, (int8_t*)t->w, t->s, t->rows, t->kdev, t->row0, t->col0, t->full_cols, t->kc, rt->stream, t->cols);
     else e = launch_synth_normal(0x5eedull, tid, t->w, t->kind, t->rows, t->cols, t->row0, t->col0, t->full_cols, gains ? 1 : 0, rt->stream);
     if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "alloc_dummy_input: %s", cudaGetErrorString(e));
     return 0;
@@ -1363,8 +1378,14 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
         cudaMemsetAsync(rt->peer_ticket, 0, 4, rt->stream);
     }
     TRY(dev_alloc(rt, (void**)&rt->qkv, (qd_l + 2 * kvd_l) * 4));
-    TRY(dev_alloc(rt, (void**)&rt->attn, qd_l * 4));
-    TRY(dev_alloc(rt, (void**)&rt->h, (size_t)rt->ffn_l * 4));
+    {
+        // inputs of the K-sharded projections: as long as the (possibly zero-padded) K of the device layout, zero beyond the data
+        const size_t attn_len = rt->L[0].o.kdev > qd_l ? rt->L[0].o.kdev : qd_l, h_len = rt->L[0].down.kdev > (size_t)rt->ffn_l ? rt->L[0].down.kdev : (size_t)rt->ffn_l;
+        TRY(dev_alloc(rt, (void**)&rt->attn, attn_len * 4));
+        TRY(dev_alloc(rt, (void**)&rt->h, h_len * 4));
+        cudaMemsetAsync(rt->attn, 0, attn_len * 4, rt->stream);
+        cudaMemsetAsync(rt->h, 0, h_len * 4, rt->stream);
+    }
     TRY(dev_alloc(rt, (void**)&rt->logits, (size_t)rt->vocab_l * 4));
     TRY(dev_alloc(rt, (void**)&rt->state, sizeof(DecodeState)));
     TRY(dev_alloc(rt, (void**)&rt->tokens_out, (size_t)d.max_new_tokens * 4));
@@ -1447,7 +1468,7 @@ int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void
             if (e == cudaSuccess) {
                 __half* ps = (__half*)((char*)planes + n);
                 e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)planes, ps, n / 32, rt->stream);
-                if (e == cudaSuccess) e = launch_q8_pack_units((const int8_t*)planes, ps, (int)t->rows, (int)t->cols, t->kc, (unsigned char*)t->w, rt->stream);
+                if (e == cudaSuccess) e = launch_q8_pack_units((const int8_t*)planes, ps, (int)t->rows, (int)t->kdev, t->kc, (unsigned char*)t->w, rt->stream, (int)t->cols);
             }
             if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
             else cudaStreamSynchronize(rt->stream);
@@ -1474,7 +1495,7 @@ int32_t lum_model_synth(lum_rt* rt, uint64_t seed) {
         if (!t) return 0;
         const uint64_t tid = tensor_id(slot, slot_layer_for_id(rt, slot, layer));
         cudaError_t e;
-        if (t->kind == WK_Q8) e = launch_synth_q8(seed, tid, (int8_t*)t->w, t->s, t->rows, t->cols, t->row0, t->col0, t->full_cols, t->kc, rt->stream);
+        if (t->kind == WK_Q8) e = launch_synth_q8(seed, tid, (int8_t*)t->w, t->s, t->rows, t->kdev, t->row0, t->col0, t->full_cols, t->kc, rt->stream, t->cols);
         else e = launch_synth_normal(seed, tid, t->w, t->kind, t->rows, t->cols, t->row0, t->col0, t->full_cols, ones, rt->stream);
         if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "synth slot %d layer %d: %s", slot, layer, cudaGetErrorString(e));
         return 0;
@@ -1502,7 +1523,7 @@ int32_t lum_model_get_weight_f32(lum_rt* rt, int32_t slot, int32_t layer, size_t
     float* tmp = nullptr;
     cudaError_t e = cudaMalloc((void**)&tmp, n * 4 + 16);
     if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "get_weight: %s", cudaGetErrorString(e));
-    if (t->kind == WK_Q8) e = launch_q8_dequant_rows(t->w, t->s, (int)t->cols, t->kc, offset / t->cols, n / t->cols, tmp, rt->stream);
+    if (t->kind == WK_Q8) e = launch_q8_dequant_rows(t->w, t->s, (int)t->kdev, t->kc, offset / t->cols, n / t->cols, tmp, rt->stream, (int)t->cols);
     else e = launch_to_f32((const uint8_t*)t->w + offset * (t->kind == WK_BF16 ? 2 : 4), t->kind, tmp, n, rt->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);

@@ -40,7 +40,8 @@ __device__ __forceinline__ double rng_normal(uint64_t key, uint64_t idx) {
 // A shard [rows, cols] of a full tensor with `full_cols` columns, starting at (row0, col0): element
 // (r, c) draws with the index it has in the full tensor, so every tensor-parallel rank regenerates
 // exactly its slice.
-struct Shard { size_t rows, cols, row0, col0, full_cols; };
+struct Shard { size_t rows, cols, row0, col0, full_cols, valid; };   // cols: K of the device layout (>= valid: zero columns pad a
+                                                                              // K-shard to whole tiles); valid: columns that exist
 
 constexpr size_t kTileQ = 4096, kTileBytes = 4352, kTileK = 512, kTileRows = 8;
 
@@ -70,6 +71,7 @@ __global__ void synth_q8_quants(uint64_t key, int8_t* q, Shard sh, int kc) {
     if (kc) packed_to_rc(i, sh.cols, &r, &c, &off);
     else { r = i / sh.cols; c = i - r * sh.cols; off = i; }
     const size_t gi = (sh.row0 + r) * sh.full_cols + sh.col0 + c;
+    if (c >= sh.valid) { *(uint4*)(q + off) = make_uint4(0u, 0u, 0u, 0u); return; }
     uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
@@ -90,23 +92,27 @@ __global__ void synth_q8_scales(uint64_t skey, __half* s, unsigned char* packed,
     if (b >= sh.rows * bpr) return;
     const size_t r = b / bpr, c = (b - r * bpr) * 32;
     const size_t gb = ((sh.row0 + r) * sh.full_cols + sh.col0 + c) / 32;
-    const __half v = __float2half_rn((float)(fabs(0.02 * rng_normal(skey, gb)) / 127.0));
+    const __half v = c < sh.valid ? __float2half_rn((float)(fabs(0.02 * rng_normal(skey, gb)) / 127.0)) : __float2half_rn(0.0f);
     if (kc) *(__half*)(packed + packed_scale_off(r, c, sh.cols)) = v;
     else s[b] = v;
 }
 // planes -> packed
-__global__ void q8_pack_units(const int8_t* q, const __half* s, size_t rows, size_t cols, int kc, unsigned char* out) {
+// planes hold `valid` columns per row; the packed stream is laid out for `cols` >= valid columns, the rest zeros
+__global__ void q8_pack_units(const int8_t* q, const __half* s, size_t rows, size_t cols, size_t valid, int kc, unsigned char* out) {
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
     if (i >= rows * cols) return;
     size_t r, c, off;
     packed_to_rc(i, cols, &r, &c, &off);
-    *(uint4*)(out + off) = *(const uint4*)(q + r * cols + c);
-    if ((c & 31) == 0) *(__half*)(out + packed_scale_off(r, c, cols)) = s[r * (cols / 32) + c / 32];
+    const bool in = c < valid;
+    *(uint4*)(out + off) = in ? *(const uint4*)(q + r * valid + c) : make_uint4(0u, 0u, 0u, 0u);
+    if ((c & 31) == 0) *(__half*)(out + packed_scale_off(r, c, cols)) = in ? s[r * (valid / 32) + c / 32] : __float2half_rn(0.0f);
 }
-cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st) {
+cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st, int valid_cols) {
     if (kc != (int)kTileK || K % kTileK || rows % kTileRows) return cudaErrorInvalidValue;
+    if (valid_cols <= 0) valid_cols = K;
+    if (valid_cols > K || valid_cols % 32) return cudaErrorInvalidValue;
     const size_t t16 = (size_t)rows * K / 16;
-    q8_pack_units<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(q, s, (size_t)rows, (size_t)K, kc, out);
+    q8_pack_units<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(q, s, (size_t)rows, (size_t)K, (size_t)valid_cols, kc, out);
     return cudaGetLastError();
 }
 __global__ void synth_normal(uint64_t key, void* out, int kind, Shard sh, int ones) {
@@ -121,9 +127,10 @@ __global__ void synth_normal(uint64_t key, void* out, int kind, Shard sh, int on
 
 // kc == 0: planes (q, s).  kc > 0: packed stream written at q (s unused).
 cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, size_t rows, size_t cols, size_t row0, size_t col0,
-                            size_t full_cols, int kc, cudaStream_t st) {
+                            size_t full_cols, int kc, cudaStream_t st, size_t valid_cols) {
     if (cols % 32 || col0 % 32 || full_cols % 32) return cudaErrorInvalidValue;
-    const Shard sh{rows, cols, row0, col0, full_cols};
+    if (valid_cols == 0) valid_cols = cols;
+    const Shard sh{rows, cols, row0, col0, full_cols, valid_cols};
     const size_t t16 = rows * cols / 16;
     synth_q8_quants<<<(unsigned)((t16 + 255) / 256), 256, 0, st>>>(rng_key(seed, tid), q, sh, kc);
     const size_t nb = rows * cols / 32;
@@ -132,7 +139,7 @@ cudaError_t launch_synth_q8(uint64_t seed, uint64_t tid, int8_t* q, __half* s, s
 }
 cudaError_t launch_synth_normal(uint64_t seed, uint64_t tid, void* out, int kind, size_t rows, size_t cols, size_t row0, size_t col0,
                                 size_t full_cols, int ones, cudaStream_t st) {
-    const Shard sh{rows, cols, row0, col0, full_cols};
+    const Shard sh{rows, cols, row0, col0, full_cols, cols};
     synth_normal<<<(unsigned)((rows * cols + 255) / 256), 256, 0, st>>>(rng_key(seed, tid), out, kind, sh, ones);
     return cudaGetLastError();
 }
@@ -164,10 +171,10 @@ cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size
 }
 
 // logical rows [row0, row0 + n_rows) of a Q8_0 matrix in either layout -> f32 row-major
-__global__ void q8_dequant_rows(const void* w, const __half* s, size_t K, int kc, size_t row0, size_t n, float* out) {
+__global__ void q8_dequant_rows(const void* w, const __half* s, size_t K, size_t valid, int kc, size_t row0, size_t n, float* out) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const size_t r = row0 + i / K, c = i % K;
+    const size_t r = row0 + i / valid, c = i % valid;          // the caller sees `valid` columns per row; the layout has K
     if (kc) {
         const size_t T = (r / kTileRows) * (K / kTileK) + c / kTileK, ck = c % kTileK, j = ck & 31;
         const unsigned char* tb = (const unsigned char*)w + T * kTileBytes;
@@ -177,9 +184,10 @@ __global__ void q8_dequant_rows(const void* w, const __half* s, size_t K, int kc
         out[i] = __fmul_rn((float)((const int8_t*)w)[r * K + c], __half2float(s[(r * K + c) >> 5]));
     }
 }
-cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st) {
-    const size_t n = n_rows * (size_t)K;
-    q8_dequant_rows<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w, s, (size_t)K, kc, row0, n, out);
+cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st, int valid_cols) {
+    if (valid_cols <= 0) valid_cols = K;
+    const size_t n = n_rows * (size_t)valid_cols;
+    q8_dequant_rows<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w, s, (size_t)K, (size_t)valid_cols, kc, row0, n, out);
     return cudaGetLastError();
 }
 

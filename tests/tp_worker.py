@@ -15,6 +15,7 @@ from __graft_entry__ import load_package  # noqa: E402
 
 def main():
     cfg_name, seed, n_new = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+    n_prompt = int(sys.argv[4]) if len(sys.argv) > 4 else 12
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -30,7 +31,7 @@ def main():
         # exchange of partial sums through peer memory (no collective kernel between the projections)
         rt.tp_peer_import(T.exchange_peer_handles(dist, world, rt.tp_peer_export(), device=torch.device("cuda", local)))
     rt.synth(seed)
-    prompt = [(7 * i + 3) % desc.vocab for i in range(12)]
+    prompt = [(7 * i + 3) % desc.vocab for i in range(n_prompt)]
     toks = rt.generate(prompt, n_new)
     logits = rt.get_f32()                       # this rank's vocabulary shard
     shard = desc.vocab // world
@@ -43,7 +44,7 @@ def main():
     assert all((t == tok_t).all().item() for t in all_toks), "ranks disagree on the sampled tokens"
     rt.close()
     if rank == 0:
-        ref = pkg.B200Runtime.initialize(device=local)
+        ref = pkg.B200Runtime.initialize(device=local, prefill_min_rows=1 << 30)      # same per-token prompt path as the sharded ranks
         ref.load_model(desc)
         ref.synth(seed)
         want = ref.generate(prompt, n_new)
