@@ -76,7 +76,12 @@ int32_t lum_device_info(const lum_rt* rt, int32_t* sm_count, uint64_t* mem_bytes
  */
 typedef enum lum_slot {
     LUM_S_EMBED = 0, LUM_S_ATTN_NORM, LUM_S_Q, LUM_S_K, LUM_S_V, LUM_S_O, LUM_S_MLP_NORM,
-    LUM_S_GATE, LUM_S_UP, LUM_S_DOWN, LUM_S_FINAL_NORM, LUM_S_LM_HEAD, LUM_S_Q_NORM, LUM_S_K_NORM
+    LUM_S_GATE, LUM_S_UP, LUM_S_DOWN, LUM_S_FINAL_NORM, LUM_S_LM_HEAD, LUM_S_Q_NORM, LUM_S_K_NORM,
+    /* gpt_oss-style layers (examples/gpt_oss/src/model.rs:95-151, 319-380): "…self_attn.{q,k,v,o}_proj.bias", the per-head sink
+     * logits (`SinkBuffers`), "…mlp.router.{weight,bias}" and the experts' tensors (`ExpertWeightBuffers`): gate_up
+     * [n_experts * 2 * ffn, hidden] with row 2i = gate i and row 2i+1 = up i, down [n_experts * hidden, ffn], and their biases */
+    LUM_S_Q_BIAS, LUM_S_K_BIAS, LUM_S_V_BIAS, LUM_S_O_BIAS, LUM_S_SINKS, LUM_S_ROUTER, LUM_S_ROUTER_BIAS,
+    LUM_S_EXP_GATE_UP, LUM_S_EXP_GATE_UP_BIAS, LUM_S_EXP_DOWN, LUM_S_EXP_DOWN_BIAS
 } lum_slot;
 
 typedef struct lum_model_desc {
@@ -84,7 +89,8 @@ typedef struct lum_model_desc {
     int32_t max_seq;        /* KV-cache capacity in positions (reference: main.rs:19,48) */
     float rms_eps;          /* the graph constant, e.g. 1e-5; used after its 6-decimal text round trip */
     float rope_theta;
-    int32_t rope_style;     /* 0: adjacent pairs as the Llama graph (model.rs:146-157); 1: split halves (qwen) */
+    int32_t rope_style;     /* 0: adjacent pairs as the Llama graph (model.rs:146-157); 1: split halves (qwen); 2: split halves with the
+                               YaRN frequency table and cos/sin factor of examples/gpt_oss/src/model.rs:47-81 (yarn_* below) */
     uint32_t weight_dtype;  /* LUM_F32 or LUM_Q8_0: all linear weights */
     uint32_t embed_dtype;   /* LUM_F32 or LUM_BF16: embedding table and norm gains */
     uint32_t kv_dtype;      /* LUM_F32 (reference: model.rs:200-215) or LUM_BF16 */
@@ -97,6 +103,16 @@ typedef struct lum_model_desc {
     /* sequences the K/V cache holds side by side (0 or 1: one).  lum_execute / lum_decode_greedy work on the sequence chosen
      * by lum_seq_select; lum_batch_decode advances all of them together. */
     int32_t max_batch;
+    /* gpt_oss-style layers; all zero for the Llama / Qwen families */
+    int32_t sliding_window;      /* > 0: a row attends to the last `sliding_window` positions only (model.rs:661-664) ... */
+    int32_t window_even_layers;  /* ... 1: on the even-indexed layers (LAYER_IS_SLIDING, model.rs:84-88); 0: on every layer */
+    int32_t attn_sinks;          /* 1: a per-head logit (slot SINKS) joins the softmax denominator (model.rs:727-747) */
+    int32_t proj_bias;           /* 1: biases on the q, k, v, o projections (slots *_BIAS) */
+    float yarn_factor, yarn_beta_fast, yarn_beta_slow, yarn_orig_max_pos;    /* rope_style 2 */
+    int32_t n_experts, top_k;    /* > 0: the FFN is `MoeExperts` (model.rs:772-1118): router + top_k of n_experts experts of width ffn */
+    float swiglu_limit;          /* clamp of the experts' gate / up values (the reference: 7.0) */
+    /* expert parallel: this rank holds experts [ep_rank * n_experts / ep_size, ...); 0 / 1 = all of them (see lum_ep_*) */
+    int32_t ep_size, ep_rank;
 } lum_model_desc;
 
 int32_t lum_model_init(lum_rt* rt, const lum_model_desc* desc);

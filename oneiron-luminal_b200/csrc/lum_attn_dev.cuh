@@ -45,12 +45,30 @@ __device__ __forceinline__ void rope_cs(const AttnArgs& a, int i, int pos, float
         const float emb = (float)pos * inv;
         *sn = sinf(emb);
         *cs = sinf(emb * -1.0f + a.c_half_pi);
+    } else if (a.rope_style == 2) {
+        // YaRN table (examples/gpt_oss/src/model.rs:557-567): angle = pos * inv_freq[i], cos and sin times the attention factor
+        const float ang = (float)pos * a.inv_freq[i];
+        *sn = sinf(ang) * a.attn_factor;
+        *cs = cosf(ang) * a.attn_factor;
     } else {
         const float freq = powf(a.theta, -((float)(2 * i)) / (float)a.hd);
         const float ang = (float)pos * freq;
         *sn = sinf(ang);
         *cs = cosf(ang);
     }
+}
+
+// The last step of a head's softmax: an optional sink logit (no value row) joins the denominator
+// (examples/gpt_oss/src/model.rs:727-757), then the division.
+__device__ __forceinline__ float attn_finish(float O, float M, float L, const void* sinks, int kind, int head) {
+    if (sinks) {
+        const float s = gain_at(sinks, kind, head);
+        const float mn = fmaxf(M, s);
+        const float c = expf(M - mn);
+        L = L * c + expf(s - mn);
+        O = O * c;
+    }
+    return O * (1.0f / L);
 }
 
 // One (kv head, split) of cached rows per CTA; all G <= GM query heads that share the KV head together.
@@ -186,10 +204,17 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
     const int nheads = G + (owns_new ? 1 : 0);
     for (int idx = tid; idx < nheads * HD; idx += kAttnThreads) {
         const int h = idx / HD, e = idx - h * HD;
-        s_q[h][e] = h < G ? a.q[((size_t)kvh * G + h) * HD + e] : a.k_new[(size_t)kvh * HD + e];
+        float v = h < G ? a.q[((size_t)kvh * G + h) * HD + e] : a.k_new[(size_t)kvh * HD + e];
+        if (h < G) { if (a.q_bias) v = v + gain_at(a.q_bias, a.gain_kind, (kvh * G + h) * HD + e); }
+        else if (a.k_bias) v = v + gain_at(a.k_bias, a.gain_kind, kvh * HD + e);
+        s_q[h][e] = v;
     }
     if (owns_new)
-        for (int e = tid; e < HD; e += kAttnThreads) s_v[e] = a.v_new[(size_t)kvh * HD + e];
+        for (int e = tid; e < HD; e += kAttnThreads) {
+            float v = a.v_new[(size_t)kvh * HD + e];
+            if (a.v_bias) v = v + gain_at(a.v_bias, a.gain_kind, kvh * HD + e);
+            s_v[e] = v;
+        }
     if (!rope_ready) attn_fill_rope<HD>(a, smem, p, tid);
     sync();
     if (a.q_gain || a.k_gain) {
@@ -321,7 +346,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
             dst[e] = O;
             if (e == 0) { dst[HD] = M; dst[HD + 1] = L; }
         } else if (a.n_splits == 1) {
-            a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);      // no other split to merge with
+            a.out[((size_t)kvh * G + g) * HD + e] = attn_finish(O, M, L, a.sinks, a.gain_kind, kvh * G + g);      // no other split to merge with
         } else {
             float* dst = a.part + (((size_t)kvh * a.n_splits + split) * G + g) * (HD + 2);
             dst[e] = O;
@@ -369,7 +394,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
                 }
                 M = Mb;
             }
-            a.out[(size_t)kvh * G * HD + split * chunk + tid] = O * (1.0f / L);
+            a.out[(size_t)kvh * G * HD + split * chunk + tid] = attn_finish(O, M, L, a.sinks, a.gain_kind, kvh * G + (split * chunk + tid) / HD);
         }
         __syncwarp();
         cluster_wait_acquire();                         // nobody leaves while a neighbour may still read its memory
@@ -420,7 +445,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
             }
             M = Mb;
         }
-        a.out[((size_t)kvh * G + g) * HD + e] = O * (1.0f / L);
+        a.out[((size_t)kvh * G + g) * HD + e] = attn_finish(O, M, L, a.sinks, a.gain_kind, kvh * G + g);
     }
     if (tid == 0) a.counters[kvh] = 0u;
 }

@@ -110,7 +110,7 @@ __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, int ti
     }
     if (a.gain) {
         ss = block_sum(ss, scratch, tid, nthreads, bar_id);
-        const float mean = ss * (1.0f / (float)K);
+        const float mean = ss * (1.0f / (float)(a.k_norm > 0 ? a.k_norm : K));
         const float inv = 1.0f / sqrtf(mean + a.eps);
         for (int k = tid; k < K; k += nthreads) xs[k] = (inv * xs[k]) * load_gain(a.gain, a.gain_kind, k);
     }

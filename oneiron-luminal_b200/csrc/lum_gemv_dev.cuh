@@ -178,10 +178,15 @@ __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const flo
         for (int i = tid; i < n; i += nthreads) {
             const int u = unit_of[i >> 3];
             float* y = (u & kUnitHalf) ? a.y + a.y_half_stride : a.y;
-            y[(u & (kUnitHalf - 1)) * kTileRows + (i & 7)] = vals[i];
+            const int row = (u & (kUnitHalf - 1)) * kTileRows + (i & 7);
+            y[row] = (a.bias && !(u & kUnitHalf)) ? vals[i] + load_gain(a.bias, a.gain_kind, row) : vals[i];
         }
     } else if (a.epi == EPI_RESID) {
-        for (int i = tid; i < n; i += nthreads) { const int row = unit_of[i >> 3] * kTileRows + (i & 7); a.y[row] = a.resid[row] + vals[i]; }
+        for (int i = tid; i < n; i += nthreads) {
+            const int row = unit_of[i >> 3] * kTileRows + (i & 7);
+            const float v = a.bias ? vals[i] + load_gain(a.bias, a.gain_kind, row) : vals[i];
+            a.y[row] = a.resid[row] + v;
+        }
     } else if (PEER && a.epi == EPI_PEER) {
         for (int i = tid; i < n; i += nthreads) {
             const int row = unit_of[i >> 3] * kTileRows + (i & 7);
@@ -227,9 +232,12 @@ __device__ __forceinline__ void gemv_epilogue_units(const GemvArgs& a, const flo
 __device__ __forceinline__ void gemv_epilogue_rows(const GemvArgs& a, const float* vals, int row0, int n, int tid, int nthreads,
                                                    float* scratch, int bar_id, ArgBest* best) {
     if (a.epi == EPI_STORE) {
-        for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = vals[i];
+        for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = a.bias ? vals[i] + load_gain(a.bias, a.gain_kind, row0 + i) : vals[i];
     } else if (a.epi == EPI_RESID) {
-        for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = a.resid[row0 + i] + vals[i];
+        for (int i = tid; i < n; i += nthreads) {
+            const float v = a.bias ? vals[i] + load_gain(a.bias, a.gain_kind, row0 + i) : vals[i];
+            a.y[row0 + i] = a.resid[row0 + i] + v;
+        }
     } else if (a.epi == EPI_SWIGLU) {
         for (int i = tid; i < n; i += nthreads) a.y[row0 + i] = swiglu(vals[i], vals[n + i]);
     } else if (a.epi == EPI_PEER) {
@@ -400,14 +408,15 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         if (PEER && xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
         if (PEER && xs.parts_ll) {
-            // every element carries its own completion word: all loads of two ranks' vectors go out together, stragglers are
+            // every element carries its own completion word: all loads of four ranks' vectors go out together, stragglers are
             // waited for one by one
             const uint32_t word = peer_word(__ldcg(xs.seq), xs.parts_tag);
+            constexpr int kLLBatch = 4;      // ranks whose vectors are requested together: one trip to L2 per batch (8 ranks: two trips)
 #pragma unroll 1
-            for (int r0 = 0; r0 < xs.n_parts; r0 += 2) {
-                uint4 raw[2][kSmallTrips][2];
+            for (int r0 = 0; r0 < xs.n_parts; r0 += kLLBatch) {
+                uint4 raw[kLLBatch][kSmallTrips][2];
 #pragma unroll
-                for (int j = 0; j < 2; j++) {
+                for (int j = 0; j < kLLBatch; j++) {
                     const uint2* pr = (const uint2*)xs.parts + (size_t)min(r0 + j, xs.n_parts - 1) * xs.part_stride;
 #pragma unroll
                     for (int it = 0; it < kSmallTrips; it++) {
@@ -417,7 +426,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 2; j++) {
+                for (int j = 0; j < kLLBatch; j++) {
                     if (r0 + j < xs.n_parts) {
                         const uint2* pr = (const uint2*)xs.parts + (size_t)(r0 + j) * xs.part_stride;
 #pragma unroll
@@ -506,7 +515,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
             ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
         }
         ss = block_sum(ss, g.scratch, tid, kWorkers, 1, false);   // the prologue ends in a barrier before anything touches the scratch again
-        const float mean = ss * (1.0f / (float)K);
+        const float mean = ss * (1.0f / (float)(a.k_norm > 0 ? a.k_norm : K));
         inv = 1.0f / sqrtf(mean + a.eps);
     }
     // all threads run every trip so the 8-lane shuffles always have their partners (K is a multiple of 32: a block never

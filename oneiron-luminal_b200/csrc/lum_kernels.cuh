@@ -52,6 +52,9 @@ struct GemvArgs {
     float eps;
     float* y;
     const float* resid;
+    const void* bias;      // optional: added to every finished row sum before the epilogue (EPI_STORE / EPI_RESID); element type gain_kind
+    int k_norm;            // > 0: the number of real activations when K was padded with zero columns to whole tiles (the RMSNorm's mean
+                           // divides by it; x and the gains hold zeros beyond it)
     // greedy-sample epilogue
     float* part_val;       // [grid]
     int* part_idx;         // [grid]
@@ -118,6 +121,14 @@ struct AttnArgs {
     uint32_t* status;
     int use_pdl;
     int cluster;           // 1: the splits of a KV head run as one thread-block cluster and merge through its shared memory
+    // gpt_oss-style attention (examples/gpt_oss/src/model.rs:520-764): rope_style 2 takes its angles from a table of inverse
+    // frequencies and scales cos / sin by a factor; a per-head sink logit joins the softmax denominator; q / k / v carry biases
+    const float* inv_freq; // [hd / 2] (rope_style 2)
+    float attn_factor;
+    const void* sinks;     // [n_q] of this rank's heads, or null (element type: gain_kind)
+    const void* q_bias;    // [n_q * hd] / [n_kv * hd] of this rank's heads, or null (element type: gain_kind)
+    const void* k_bias;
+    const void* v_bias;
     int kv_prefetch;       // 1: ask for this CTA's cached rows to be brought into L2 while still waiting for the projections
     // Optional: bytes the NEXT kernels will stream (weights of the o projection, ...).  Attention is latency-bound and leaves
     // HBM idle, so its CTAs ask for these ranges to be brought into L2 meanwhile (a hint: nothing waits for it).

@@ -27,6 +27,7 @@
 #include "lum_kernels.cuh"
 #include "lum_mega.cuh"
 #include "lum_rows.cuh"
+#include "lum_moe.cuh"
 
 using namespace lum;
 
@@ -54,6 +55,10 @@ struct NcclApi {
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
+    int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
     bool ok = false;
     std::string why;
 };
@@ -69,6 +74,10 @@ NcclApi& nccl() {
         a.AllReduce = (decltype(a.AllReduce))dlsym(h, "ncclAllReduce");
         a.AllGather = (decltype(a.AllGather))dlsym(h, "ncclAllGather");
         a.GetErrorString = (decltype(a.GetErrorString))dlsym(h, "ncclGetErrorString");
+        a.Send = (decltype(a.Send))dlsym(h, "ncclSend");
+        a.Recv = (decltype(a.Recv))dlsym(h, "ncclRecv");
+        a.GroupStart = (decltype(a.GroupStart))dlsym(h, "ncclGroupStart");
+        a.GroupEnd = (decltype(a.GroupEnd))dlsym(h, "ncclGroupEnd");
         a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllReduce && a.AllGather && a.GetErrorString;
         if (!a.ok) a.why = "libnccl is missing an entry point";
         return a;
@@ -95,6 +104,8 @@ struct Tensor {
 
 struct LayerW {
     Tensor q, k, v, o, gate, up, down, attn_norm, mlp_norm, q_norm, k_norm;
+    Tensor q_b, k_b, v_b, o_b, sinks;                         // gpt_oss-style: projection biases, per-head sink logits
+    Tensor router, router_b, exp_gu, exp_gu_b, exp_dn, exp_dn_b;   // routed experts (this rank's experts only)
     void* kc = nullptr;
     void* vc = nullptr;
 };
@@ -152,6 +163,11 @@ struct lum_rt {
         int8_t* xq = nullptr; float* sx = nullptr;                   // quantised activation rows of the product in flight
         std::vector<int32_t> h_tok, h_pos;
     } rows;
+    float* yarn_inv = nullptr;        // rope_style 2: inverse-frequency table [head_dim / 2] on the device
+    float yarn_factor_cs = 1.0f;      // ... and the factor on cos / sin
+    float *moe_xf = nullptr, *moe_sw = nullptr, *moe_recv = nullptr, *moe_part = nullptr, *moe_comb = nullptr;   // MoE scratch (slots, gated activations, exchanges)
+    int moe_slot = 0;
+    int ep_size = 1, ep_rank = 0;
     int prefill_min_rows = 4;
     int max_batch = 1, cur_seq = 0;
     int batch_n = 0;                  // sequences of the running batch (lum_batch_begin)
@@ -225,14 +241,15 @@ int dev_alloc(lum_rt* rt, void** p, size_t bytes) {
     return 0;
 }
 
-int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_cols, size_t rows, size_t cols, size_t row0, size_t col0) {
+int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_cols, size_t rows, size_t cols, size_t row0, size_t col0,
+                 bool force_planes = false, size_t min_elems = 0) {
     t.kind = kind; t.rows = rows; t.cols = cols; t.kdev = cols; t.row0 = row0; t.col0 = col0; t.full_rows = full_rows; t.full_cols = full_cols;
     const size_t n = rows * cols;
     if (kind == WK_Q8) {
         if (cols % 32 || full_cols % 32 || col0 % 32) return fail(rt, LUM_E_INVALID, "Q8_0 tensors need K %% 32 == 0 (K = %zu)", cols);
         t.kdev = cols;
-        t.kc = q8_pack_kc((int)rows, (int)cols);
-        if (!t.kc && cols > 512) {
+        t.kc = force_planes ? 0 : q8_pack_kc((int)rows, (int)cols);
+        if (!t.kc && cols > 512 && !force_planes) {
             const size_t up = (cols + 511) / 512 * 512;
             if (q8_pack_kc((int)rows, (int)up)) { t.kdev = up; t.kc = q8_pack_kc((int)rows, (int)up); }
         }
@@ -244,7 +261,10 @@ int alloc_tensor(lum_rt* rt, Tensor& t, int kind, size_t full_rows, size_t full_
             if (int r = dev_alloc(rt, (void**)&t.s, n / 16 + 64)) return r;
         }
     } else {
-        if (int r = dev_alloc(rt, &t.w, n * (kind == WK_BF16 ? 2 : 4) + 64)) return r;
+        // min_elems: vectors a kernel reads up to a padded length (norm gains under a zero-padded K) are that long, zeros beyond the data
+        const size_t ne = n > min_elems ? n : min_elems;
+        if (int r = dev_alloc(rt, &t.w, ne * (kind == WK_BF16 ? 2 : 4) + 64)) return r;
+        cudaMemsetAsync(t.w, 0, ne * (kind == WK_BF16 ? 2 : 4) + 64, rt->stream);
     }
     return 0;
 }
@@ -260,6 +280,7 @@ void close_peers(lum_rt* rt) {
 void free_model(lum_rt* rt) {
     close_peers(rt);
     rt->sym = nullptr; rt->sym_bytes = 0; rt->tp_seq = nullptr; rt->peer_ticket = nullptr;
+    rt->yarn_inv = nullptr; rt->moe_xf = rt->moe_sw = rt->moe_recv = rt->moe_part = rt->moe_comb = nullptr;
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
     rt->g_full = rt->g_body = nullptr;
@@ -293,16 +314,28 @@ Tensor* slot_tensor(lum_rt* rt, int slot, int layer) {
         case LUM_S_V: return &l.v;
         case LUM_S_O: return &l.o;
         case LUM_S_MLP_NORM: return &l.mlp_norm;
-        case LUM_S_GATE: return &l.gate;
-        case LUM_S_UP: return &l.up;
-        case LUM_S_DOWN: return &l.down;
+        case LUM_S_GATE: return rt->d.n_experts > 0 ? nullptr : &l.gate;
+        case LUM_S_UP: return rt->d.n_experts > 0 ? nullptr : &l.up;
+        case LUM_S_DOWN: return rt->d.n_experts > 0 ? nullptr : &l.down;
         case LUM_S_Q_NORM: return rt->d.qk_norm ? &l.q_norm : nullptr;
         case LUM_S_K_NORM: return rt->d.qk_norm ? &l.k_norm : nullptr;
+        case LUM_S_Q_BIAS: return rt->d.proj_bias ? &l.q_b : nullptr;
+        case LUM_S_K_BIAS: return rt->d.proj_bias ? &l.k_b : nullptr;
+        case LUM_S_V_BIAS: return rt->d.proj_bias ? &l.v_b : nullptr;
+        case LUM_S_O_BIAS: return rt->d.proj_bias ? &l.o_b : nullptr;
+        case LUM_S_SINKS: return rt->d.attn_sinks ? &l.sinks : nullptr;
+        case LUM_S_ROUTER: return rt->d.n_experts > 0 ? &l.router : nullptr;
+        case LUM_S_ROUTER_BIAS: return rt->d.n_experts > 0 ? &l.router_b : nullptr;
+        case LUM_S_EXP_GATE_UP: return rt->d.n_experts > 0 ? &l.exp_gu : nullptr;
+        case LUM_S_EXP_GATE_UP_BIAS: return rt->d.n_experts > 0 ? &l.exp_gu_b : nullptr;
+        case LUM_S_EXP_DOWN: return rt->d.n_experts > 0 ? &l.exp_dn : nullptr;
+        case LUM_S_EXP_DOWN_BIAS: return rt->d.n_experts > 0 ? &l.exp_dn_b : nullptr;
         default: return nullptr;
     }
 }
 // generator id of a slot: shared with the CPU oracle's own statement of the generator
-uint64_t tensor_id(int slot, int layer) { return (uint64_t)layer * 16u + (uint64_t)slot; }
+// (slots 14 and up — the gpt_oss-style tensors — have a range of their own, so the ids of the first 14 never moved)
+uint64_t tensor_id(int slot, int layer) { return slot < 14 ? (uint64_t)layer * 16u + (uint64_t)slot : (1ull << 21) + (uint64_t)layer * 32u + (uint64_t)slot; }
 int slot_layer_for_id(const lum_rt* rt, int slot, int layer) {
     return (slot == LUM_S_EMBED || slot == LUM_S_FINAL_NORM || slot == LUM_S_LM_HEAD) ? rt->d.n_layers : layer;
 }
@@ -338,6 +371,34 @@ int check_status(lum_rt* rt) {
     return 0;
 }
 
+// ---- expert parallel exchanges (NCCL all-to-all as grouped send / receive) ------------------------------------------------
+// Every rank sends the same `n` floats (its token's slot) to every rank: slot r of `recv` is rank r's.
+int ep_all_to_all(lum_rt* rt, const float* send, float* recv, size_t n) {
+    NcclApi& nc = nccl();
+    if (!nc.GroupStart || !nc.Send || !nc.Recv) return fail(rt, LUM_E_UNSUPPORTED, "libnccl lacks ncclSend / ncclRecv");
+    int rc = nc.GroupStart();
+    for (int r = 0; r < rt->ep_size && !rc; r++) {
+        rc = nc.Send(send, n, kNcclFloat32, r, rt->comm, rt->stream);
+        if (!rc) rc = nc.Recv(recv + (size_t)r * n, n, kNcclFloat32, r, rt->comm, rt->stream);
+    }
+    const int rc2 = nc.GroupEnd();
+    if (rc || rc2) return fail(rt, LUM_E_CUDA, "expert-parallel dispatch: %s", nc.GetErrorString(rc ? rc : rc2));
+    return 0;
+}
+// Row r of `send` goes to rank r; row r of `recv` is what rank r sent for this rank's token.
+int ep_all_to_all_rows(lum_rt* rt, const float* send, float* recv, size_t n) {
+    NcclApi& nc = nccl();
+    if (!nc.GroupStart || !nc.Send || !nc.Recv) return fail(rt, LUM_E_UNSUPPORTED, "libnccl lacks ncclSend / ncclRecv");
+    int rc = nc.GroupStart();
+    for (int r = 0; r < rt->ep_size && !rc; r++) {
+        rc = nc.Send(send + (size_t)r * n, n, kNcclFloat32, r, rt->comm, rt->stream);
+        if (!rc) rc = nc.Recv(recv + (size_t)r * n, n, kNcclFloat32, r, rt->comm, rt->stream);
+    }
+    const int rc2 = nc.GroupEnd();
+    if (rc || rc2) return fail(rt, LUM_E_CUDA, "expert-parallel combine: %s", nc.GetErrorString(rc ? rc : rc2));
+    return 0;
+}
+
 // ---- the per-token schedule ---------------------------------------------------------------------
 // Issues the kernels of one token on rt->stream.  with_head: include final norm + lm_head + sampler.
 //
@@ -348,7 +409,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
     const lum_model_desc& d = rt->d;
     const int H = d.hidden, hd = d.head_dim;
     const int gk = kind_of(d.embed_dtype);
-    const bool tp = rt->tp_size > 1;
+    const bool tp = rt->d.tp_size > 1;        // (an expert-parallel group is not tensor parallelism: every rank runs whole layers)
     int n = 0;
     cudaStream_t st = rt->stream;
     float* cur = rt->x;                 // residual stream lives here ...
@@ -365,7 +426,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
     // projection half a step away in stream order — used (and quiescent) long before, next used long after — so that every
     // counter is zero again when its projection comes round in the next step.  The two maps (with and without the
     // vocabulary projection) are both bijections that zero a counter either before its use in the same step or after it.
-    const int n_proj = 4 * d.n_layers + (with_head ? 1 : 0);
+    const int n_proj = (d.n_experts > 0 ? 2 : 4) * d.n_layers + (with_head ? 1 : 0);     // streaming projections per step (routed experts have kernels of their own)
     int gi = 0;
     auto claim_ctr = [&](GemvArgs& g) {
         if (n_proj >= 8 && rt->step_ctr) { g.job_ctr = rt->step_ctr + gi; g.job_ctr_zero = rt->step_ctr + (gi + n_proj / 2) % n_proj; }
@@ -419,7 +480,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows, w.q.kc};
         a.seg[1] = {w.k.w, w.k.s, (int)w.k.rows, w.k.kc};
         a.seg[2] = {w.v.w, w.v.s, (int)w.v.rows, w.v.kc};
-        a.K = H; a.epi = EPI_STORE; a.gain = w.attn_norm.w; a.y = rt->qkv;
+        a.K = (int)w.q.kdev; a.k_norm = H; a.epi = EPI_STORE; a.gain = w.attn_norm.w; a.y = rt->qkv;
         take_partial(a);
         claim_ctr(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
@@ -432,7 +493,11 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         t.gain_kind = gk; t.qk_eps = d.rms_eps; t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits;
         t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
         t.c_inv_d = rt->c_inv_d; t.c_ln_theta = rt->c_ln_theta; t.c_log2e = rt->c_log2e; t.c_half_pi = rt->c_half_pi;
-        t.theta = d.rope_theta; t.window = 0; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
+        t.theta = d.rope_theta; t.max_seq = d.max_seq; t.status = rt->status; t.use_pdl = pdl;
+        t.window = (d.sliding_window > 0 && (!d.window_even_layers || (l % 2) == 0)) ? d.sliding_window : 0;
+        t.inv_freq = rt->yarn_inv; t.attn_factor = rt->yarn_factor_cs;
+        if (d.attn_sinks) t.sinks = w.sinks.w;
+        if (d.proj_bias) { t.q_bias = w.q_b.w; t.k_bias = w.k_b.w; t.v_bias = w.v_b.w; }
         t.cluster = rt->attn_cluster ? 1 : 0;
         t.kv_prefetch = rt->kv_prefetch ? 1 : 0;
         if (rt->l2_pf_mb > 0 && w.gate.kc > 0 && w.up.kc > 0) {
@@ -450,6 +515,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         o.status = rt->status; o.use_pdl = pdl; o.wkind = w.o.kind;
         o.nseg = 1; o.seg[0] = {w.o.w, w.o.s, (int)w.o.rows, w.o.kc};
         o.K = (int)w.o.kdev; o.x = rt->attn;
+        if (d.proj_bias) { o.bias = w.o_b.w; o.gain_kind = gk; }
         if (fused) publish_to_peers(o, 0, (uint32_t)(2 * l + 1));
         else if (tp) { o.epi = EPI_STORE; o.y = rt->part; }
         else { o.epi = EPI_RESID; o.y = cur; o.resid = cur; }
@@ -457,11 +523,38 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         CU(rt, launch_gemv(o, rt->sm_count, st)); n++;
         if (tp && !fused) { if (int r = all_reduce()) return r; pending = true; }
 
+        if (d.n_experts > 0) {
+            // Routed experts (`MoeExperts`, examples/gpt_oss/src/model.rs:263-276): RMSNorm + router + top-k, then the selected
+            // experts' gate_up / SwiGLU and down products, added to the residual stream.  Expert parallel: every rank runs its own
+            // sequence up to here; the tokens' normalised activations and routing are exchanged all-to-all, every rank computes
+            // its experts' share for all tokens, the shares return all-to-all and are summed.
+            MoeArgs m{};
+            m.x = cur; m.x_ld = H; m.gain = w.mlp_norm.w; m.gain_kind = gk; m.eps = rt->eps6;
+            m.router = w.router.w; m.router_bias = w.router_b.w; m.xf = rt->moe_xf; m.slot = rt->moe_slot;
+            m.hidden = H; m.ffn = d.ffn; m.n_experts = d.n_experts; m.top_k = d.top_k;
+            m.expert0 = rt->ep_rank * (d.n_experts / rt->ep_size); m.n_local = d.n_experts / rt->ep_size;
+            m.gu_q = (const int8_t*)w.exp_gu.w; m.gu_s = w.exp_gu.s; m.gu_bias = w.exp_gu_b.w;
+            m.dn_q = (const int8_t*)w.exp_dn.w; m.dn_s = w.exp_dn.s; m.dn_bias = w.exp_dn_b.w;
+            m.sw = rt->moe_sw; m.limit = d.swiglu_limit; m.use_pdl = pdl; m.out_ld = H;
+            CU(rt, launch_moe_route(m, 1, st)); n++;
+            if (rt->ep_size > 1) {
+                const int T = rt->ep_size;
+                if (int r2 = ep_all_to_all(rt, rt->moe_xf, rt->moe_recv, (size_t)rt->moe_slot)) return r2;      // dispatch
+                m.xf_in = rt->moe_recv; m.n_tokens = T; m.out = rt->moe_part; m.out_add = nullptr; m.use_pdl = 0;
+                CU(rt, launch_moe_experts(m, rt->sm_count, st)); n += 2;
+                if (int r2 = ep_all_to_all_rows(rt, rt->moe_part, rt->moe_comb, (size_t)H)) return r2;          // combine
+                CU(rt, launch_moe_combine(cur, rt->moe_comb, T, H, H, st)); n += 3;
+            } else {
+                m.xf_in = rt->moe_xf; m.n_tokens = 1; m.out_add = cur;
+                CU(rt, launch_moe_experts(m, rt->sm_count, st)); n += 2;
+            }
+            continue;
+        }
         // RMSNorm + gate, up + SwiGLU
         GemvArgs g{};
         g.status = rt->status; g.use_pdl = pdl; g.gain_kind = gk; g.eps = rt->eps6; g.wkind = w.gate.kind;
         g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows, w.gate.kc}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows, w.up.kc};
-        g.K = H; g.epi = EPI_SWIGLU; g.gain = w.mlp_norm.w; g.y = rt->h;
+        g.K = (int)w.gate.kdev; g.k_norm = H; g.epi = EPI_SWIGLU; g.gain = w.mlp_norm.w; g.y = rt->h;
         take_partial(g);
         claim_ctr(g);
         CU(rt, launch_gemv(g, rt->sm_count, st)); n++;
@@ -489,7 +582,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         GemvArgs a{};
         a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = hw.kind;
         a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows, hw.kc};
-        a.K = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
+        a.K = hw.kind == WK_Q8 ? (int)hw.kdev : H; a.k_norm = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
         take_partial(a);
@@ -570,7 +663,8 @@ int run_step(lum_rt* rt, bool with_head) {
 // Every linear of the model in the packed tile stream, one GPU: the tensor-core products can take the model's rows.
 bool rows_supported(const lum_rt* rt) {
     const lum_model_desc& d = rt->d;
-    if (!rt->has_model || d.weight_dtype != LUM_Q8_0 || rt->tp_size > 1 || (d.head_dim != 64 && d.head_dim != 128)) return false;
+    if (!rt->has_model || d.weight_dtype != LUM_Q8_0 || d.tp_size > 1 || (d.head_dim != 64 && d.head_dim != 128)) return false;
+    if (d.n_experts > 0 || d.proj_bias || d.attn_sinks || d.sliding_window > 0 || d.rope_style == 2) return false;     // per-token path only
     if (d.n_q_heads / d.n_kv_heads > (d.head_dim == 128 ? 4 : 8)) return false;
     for (const LayerW& w : rt->L) {
         const Tensor* ts[] = {&w.q, &w.k, &w.v, &w.o, &w.gate, &w.up, &w.down};
@@ -801,7 +895,8 @@ int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
 int setup_mega(lum_rt* rt) {
     rt->mega_ok = false;
     const lum_model_desc& d = rt->d;
-    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || rt->tp_size > 1 || d.max_batch > 1) return 0;
+    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || d.tp_size > 1 || d.max_batch > 1) return 0;
+    if (d.n_experts > 0 || d.proj_bias || d.attn_sinks || d.sliding_window > 0 || d.rope_style == 2) return 0;
     std::vector<MegaLayer> hl((size_t)d.n_layers);
     bool packed = rt->lm_head.kc > 0;
     for (int l = 0; l < d.n_layers && packed; l++) {
@@ -930,7 +1025,7 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
     }
     lum_model_desc d = *lum_llir_desc(plan);
     d.max_seq = max_seq; d.kv_dtype = kv_dtype; d.max_new_tokens = max_new_tokens;
-    d.tp_size = rt->tp_size; d.tp_rank = rt->tp_rank;
+    d.tp_size = rt->tp_size; d.tp_rank = rt->tp_rank;      // a runtime that joined a group loads the graph tensor-parallel
     const int r = lum_model_init(rt, &d);
     if (r) { lum_llir_free_plan(plan); return r; }
     if (rt->llir) lum_llir_free_plan(rt->llir);
@@ -1314,7 +1409,19 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (d.tied_head && tp > 1) return fail(rt, LUM_E_UNSUPPORTED, "tied head under tensor parallelism");
     if (tp > 1 && (!rt->comm || rt->tp_size != tp || rt->tp_rank != d.tp_rank))
         return fail(rt, LUM_E_INVALID, "tp_size %d / tp_rank %d need a matching lum_tp_init first", tp, d.tp_rank);
-    if (tp == 1 && rt->tp_size > 1) return fail(rt, LUM_E_INVALID, "this runtime joined a %d-rank group; the model must be sharded the same way", rt->tp_size);
+    if (d.ep_size <= 0) { d.ep_size = 1; d.ep_rank = 0; }
+    if (d.ep_size > 1 && (d.n_experts <= 0 || tp > 1 || d.n_experts % d.ep_size || d.ep_rank < 0 || d.ep_rank >= d.ep_size))
+        return fail(rt, LUM_E_INVALID, "expert parallelism needs a mixture-of-experts model, tp_size 1 and n_experts divisible by ep_size");
+    if (d.ep_size > 1 && (!rt->comm || rt->tp_size != d.ep_size || rt->tp_rank != d.ep_rank))
+        return fail(rt, LUM_E_INVALID, "ep_size %d / ep_rank %d need a matching lum_tp_init (the group the experts are spread over) first", d.ep_size, d.ep_rank);
+    if (tp == 1 && d.ep_size == 1 && rt->tp_size > 1) return fail(rt, LUM_E_INVALID, "this runtime joined a %d-rank group; the model must be sharded the same way", rt->tp_size);
+    if (d.n_experts > 0 && (d.top_k < 1 || d.top_k > 8 || d.top_k > d.n_experts || d.n_experts > 1024 || d.weight_dtype != LUM_Q8_0 || tp > 1 || d.hidden % 32 || d.ffn % 32))
+        return fail(rt, LUM_E_UNSUPPORTED, "mixture of experts: 1 <= top_k <= 8, Q8_0 weights, hidden and ffn multiples of 32, no tensor parallelism");
+    if ((d.proj_bias || d.attn_sinks || d.sliding_window > 0 || d.rope_style == 2) && tp > 1)
+        return fail(rt, LUM_E_UNSUPPORTED, "gpt_oss-style attention (biases, sinks, window, YaRN) under tensor parallelism");
+    if (d.rope_style < 0 || d.rope_style > 2) return fail(rt, LUM_E_INVALID, "rope_style %d", d.rope_style);
+    if (d.rope_style == 2 && (d.yarn_factor <= 0.0f || d.yarn_beta_fast <= 0.0f || d.yarn_beta_slow <= 0.0f || d.yarn_orig_max_pos <= 0.0f))
+        return fail(rt, LUM_E_INVALID, "rope_style 2 needs the yarn_* parameters");
     if (d.n_q_heads % tp || (d.n_q_heads / tp) % (d.n_kv_heads / tp)) return fail(rt, LUM_E_INVALID, "query heads must divide by tp_size");
     rt->d = d;
     rt->nq_l = d.n_q_heads / tp; rt->nkv_l = d.n_kv_heads / tp; rt->ffn_l = d.ffn / tp; rt->vocab_l = d.vocab / tp;
@@ -1324,22 +1431,45 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     const size_t qd_l = (size_t)rt->nq_l * hd, kvd_l = (size_t)rt->nkv_l * hd;
 
 #define TRY(x) do { if (int r_ = (x)) { free_model(rt); return r_; } } while (0)
+    // A hidden size that is not a whole number of 512-column tiles (2880) is zero-padded in the packed weight layout; what the
+    // projection kernels read along K — residual vectors, norm gains — is then that long too, zeros beyond the data.
+    const size_t Hpad = (wk == WK_Q8 && H % 512 && H > 512) ? ((size_t)H + 511) / 512 * 512 : (size_t)H;
+    rt->ep_size = d.ep_size; rt->ep_rank = d.ep_rank;
+    const int epr = d.n_experts > 0 ? d.n_experts / d.ep_size : 0;        // experts this rank holds
     TRY(alloc_tensor(rt, rt->embed, ek, d.vocab, H, d.vocab, H, 0, 0));
-    TRY(alloc_tensor(rt, rt->final_norm, ek, 1, H, 1, H, 0, 0));
+    TRY(alloc_tensor(rt, rt->final_norm, ek, 1, H, 1, H, 0, 0, false, Hpad));
     if (!d.tied_head) TRY(alloc_tensor(rt, rt->lm_head, wk, d.vocab, H, rt->vocab_l, H, (size_t)r * rt->vocab_l, 0));
     rt->L.resize((size_t)d.n_layers);
     const size_t kv_elem = d.kv_dtype == LUM_BF16 ? 2 : 4;
     for (int l = 0; l < d.n_layers; l++) {
         LayerW& w = rt->L[(size_t)l];
-        TRY(alloc_tensor(rt, w.attn_norm, ek, 1, H, 1, H, 0, 0));
-        TRY(alloc_tensor(rt, w.mlp_norm, ek, 1, H, 1, H, 0, 0));
+        TRY(alloc_tensor(rt, w.attn_norm, ek, 1, H, 1, H, 0, 0, false, Hpad));
+        TRY(alloc_tensor(rt, w.mlp_norm, ek, 1, H, 1, H, 0, 0, false, Hpad));
         TRY(alloc_tensor(rt, w.q, wk, qd, H, qd_l, H, r * qd_l, 0));
         TRY(alloc_tensor(rt, w.k, wk, kvd, H, kvd_l, H, r * kvd_l, 0));
         TRY(alloc_tensor(rt, w.v, wk, kvd, H, kvd_l, H, r * kvd_l, 0));
         TRY(alloc_tensor(rt, w.o, wk, H, qd, H, qd_l, 0, r * qd_l));
-        TRY(alloc_tensor(rt, w.gate, wk, d.ffn, H, rt->ffn_l, H, (size_t)r * rt->ffn_l, 0));
-        TRY(alloc_tensor(rt, w.up, wk, d.ffn, H, rt->ffn_l, H, (size_t)r * rt->ffn_l, 0));
-        TRY(alloc_tensor(rt, w.down, wk, H, d.ffn, H, rt->ffn_l, 0, (size_t)r * rt->ffn_l));
+        if (d.n_experts > 0) {
+            // router replicated; this rank's experts as Q8_0 planes (rows are contiguous runs for the row-wise expert kernels)
+            const size_t E = (size_t)d.n_experts, F = (size_t)d.ffn, e0 = (size_t)d.ep_rank * epr;
+            TRY(alloc_tensor(rt, w.router, ek, E, H, E, H, 0, 0));
+            TRY(alloc_tensor(rt, w.router_b, ek, 1, E, 1, E, 0, 0));
+            TRY(alloc_tensor(rt, w.exp_gu, wk, E * 2 * F, H, (size_t)epr * 2 * F, H, e0 * 2 * F, 0, true));
+            TRY(alloc_tensor(rt, w.exp_gu_b, ek, 1, E * 2 * F, 1, (size_t)epr * 2 * F, 0, e0 * 2 * F));
+            TRY(alloc_tensor(rt, w.exp_dn, wk, E * H, F, (size_t)epr * H, F, e0 * H, 0, true));
+            TRY(alloc_tensor(rt, w.exp_dn_b, ek, 1, E * H, 1, (size_t)epr * H, 0, e0 * H));
+        } else {
+            TRY(alloc_tensor(rt, w.gate, wk, d.ffn, H, rt->ffn_l, H, (size_t)r * rt->ffn_l, 0));
+            TRY(alloc_tensor(rt, w.up, wk, d.ffn, H, rt->ffn_l, H, (size_t)r * rt->ffn_l, 0));
+            TRY(alloc_tensor(rt, w.down, wk, H, d.ffn, H, rt->ffn_l, 0, (size_t)r * rt->ffn_l));
+        }
+        if (d.proj_bias) {
+            TRY(alloc_tensor(rt, w.q_b, ek, 1, qd, 1, qd, 0, 0));
+            TRY(alloc_tensor(rt, w.k_b, ek, 1, kvd, 1, kvd, 0, 0));
+            TRY(alloc_tensor(rt, w.v_b, ek, 1, kvd, 1, kvd, 0, 0));
+            TRY(alloc_tensor(rt, w.o_b, ek, 1, H, 1, H, 0, 0));
+        }
+        if (d.attn_sinks) TRY(alloc_tensor(rt, w.sinks, ek, 1, d.n_q_heads, 1, d.n_q_heads, 0, 0));
         if (d.qk_norm) {
             TRY(alloc_tensor(rt, w.q_norm, ek, 1, hd, 1, hd, 0, 0));
             TRY(alloc_tensor(rt, w.k_norm, ek, 1, hd, 1, hd, 0, 0));
@@ -1364,9 +1494,42 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (splits > 32) splits = 32;       // the merge holds one partial per split in registers
     rt->n_splits = splits;
     const int G = d.n_q_heads / d.n_kv_heads;
-    TRY(dev_alloc(rt, (void**)&rt->x, (size_t)H * 4));
-    TRY(dev_alloc(rt, (void**)&rt->x2, (size_t)H * 4));
-    TRY(dev_alloc(rt, (void**)&rt->part, (size_t)2 * H * 4));   // a reduced partial vector, or the two K halves of the down projection
+    TRY(dev_alloc(rt, (void**)&rt->x, Hpad * 4));
+    TRY(dev_alloc(rt, (void**)&rt->x2, Hpad * 4));
+    TRY(dev_alloc(rt, (void**)&rt->part, (size_t)2 * Hpad * 4));   // a reduced partial vector, or the two K halves of the down projection
+    cudaMemsetAsync(rt->x, 0, Hpad * 4, rt->stream);
+    cudaMemsetAsync(rt->x2, 0, Hpad * 4, rt->stream);
+    cudaMemsetAsync(rt->part, 0, (size_t)2 * Hpad * 4, rt->stream);
+    if (d.rope_style == 2) {
+        // YaRN inverse frequencies (examples/gpt_oss/src/model.rs:47-81): binary64 on the host, stored as f32
+        std::vector<float> inv((size_t)hd / 2);
+        const double base = (double)d.rope_theta, dim = (double)hd, PI = 3.14159265358979323846;
+        auto corr = [&](double rot) { return (dim * std::log((double)d.yarn_orig_max_pos / (rot * 2.0 * PI))) / (2.0 * std::log(base)); };
+        const double low = corr((double)d.yarn_beta_fast), high = corr((double)d.yarn_beta_slow);
+        for (int i = 0; i < hd / 2; i++) {
+            const double pf = std::pow(base, 2.0 * (double)i / dim);
+            const double extrap = 1.0 / pf, interp = 1.0 / ((double)d.yarn_factor * pf), diff = high - low;
+            double t = std::fabs(diff) > 1e-10 ? ((double)i - low) / diff : 0.0;
+            t = t < 0.0 ? 0.0 : t > 1.0 ? 1.0 : t;
+            const double ef = 1.0 - t;
+            inv[(size_t)i] = (float)(interp * (1.0 - ef) + extrap * ef);
+        }
+        TRY(dev_alloc(rt, (void**)&rt->yarn_inv, inv.size() * 4));
+        CU(rt, cudaMemcpyAsync(rt->yarn_inv, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice, rt->stream));
+        CU(rt, cudaStreamSynchronize(rt->stream));
+        rt->yarn_factor_cs = (float)(0.1 * std::log((double)d.yarn_factor) + 1.0);
+    }
+    if (d.n_experts > 0) {
+        const int T = d.ep_size;                                   // tokens a rank's experts see per step: its own, or one of every rank
+        rt->moe_slot = (H + 2 * d.top_k + 3) / 4 * 4;
+        TRY(dev_alloc(rt, (void**)&rt->moe_xf, (size_t)rt->moe_slot * 4));
+        TRY(dev_alloc(rt, (void**)&rt->moe_sw, (size_t)T * d.top_k * d.ffn * 4));
+        if (T > 1) {
+            TRY(dev_alloc(rt, (void**)&rt->moe_recv, (size_t)T * rt->moe_slot * 4));
+            TRY(dev_alloc(rt, (void**)&rt->moe_part, (size_t)T * H * 4));
+            TRY(dev_alloc(rt, (void**)&rt->moe_comb, (size_t)T * H * 4));
+        }
+    }
     TRY(dev_alloc(rt, (void**)&rt->tp_pairs, (size_t)(2 * tp + 2) * 4));
     if (tp > 1) {
         rt->sym_bytes = 4096 + (size_t)2 * tp * H * 8;
@@ -1504,7 +1667,8 @@ int32_t lum_model_synth(lum_rt* rt, uint64_t seed) {
     if (int r = fill(LUM_S_FINAL_NORM, 0, 1)) return r;
     if (int r = fill(LUM_S_LM_HEAD, 0, 0)) return r;
     for (int l = 0; l < d.n_layers; l++) {
-        const int lin[] = {LUM_S_Q, LUM_S_K, LUM_S_V, LUM_S_O, LUM_S_GATE, LUM_S_UP, LUM_S_DOWN};
+        const int lin[] = {LUM_S_Q, LUM_S_K, LUM_S_V, LUM_S_O, LUM_S_GATE, LUM_S_UP, LUM_S_DOWN, LUM_S_ROUTER, LUM_S_ROUTER_BIAS, LUM_S_EXP_GATE_UP,
+                           LUM_S_EXP_GATE_UP_BIAS, LUM_S_EXP_DOWN, LUM_S_EXP_DOWN_BIAS, LUM_S_Q_BIAS, LUM_S_K_BIAS, LUM_S_V_BIAS, LUM_S_O_BIAS, LUM_S_SINKS};
         for (int s : lin) if (int r = fill(s, l, 0)) return r;
         const int nrm[] = {LUM_S_ATTN_NORM, LUM_S_MLP_NORM, LUM_S_Q_NORM, LUM_S_K_NORM};
         for (int s : nrm) if (int r = fill(s, l, 1)) return r;
@@ -1539,6 +1703,12 @@ int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes) {
         b += w.q.bytes() + w.k.bytes() + w.v.bytes() + w.o.bytes() + w.gate.bytes() + w.up.bytes() + w.down.bytes();
         b += w.attn_norm.bytes() + w.mlp_norm.bytes();
         if (rt->d.qk_norm) b += w.q_norm.bytes() + w.k_norm.bytes();
+        if (rt->d.n_experts > 0) {
+            // a token reads the router and top_k experts (gate_up + down, their biases)
+            const uint64_t H = (uint64_t)rt->d.hidden, F = (uint64_t)rt->d.ffn, eb = rt->embed.kind == WK_BF16 ? 2 : 4;
+            b += w.router.bytes() + w.router_b.bytes() + (uint64_t)rt->d.top_k * ((2 * F * H + H * F) * 34 / 32 + (2 * F + H) * eb);
+        }
+        if (rt->d.proj_bias) b += w.q_b.bytes() + w.k_b.bytes() + w.v_b.bytes() + w.o_b.bytes();
     }
     b += rt->final_norm.bytes();
     b += rt->d.tied_head ? rt->embed.bytes() : rt->lm_head.bytes();
@@ -1700,7 +1870,7 @@ int32_t lum_launches_per_step(const lum_rt* rt, int32_t* n) {
     if (!rt || !rt->has_model || !n) return LUM_E_INVALID;
     if (rt->mega_ok && rt->use_mega) { *n = 1; return 0; }
     if (rt->launches_full > 0) { *n = rt->launches_full; return 0; }      // counted while the step was issued / captured
-    *n = rt->tp_size > 1 ? 1 + 5 * rt->d.n_layers + 1 + 1 /* pick */ : 1 + 5 * rt->d.n_layers + 1;
+    *n = rt->d.tp_size > 1 ? 1 + 5 * rt->d.n_layers + 1 + 1 /* pick */ : 1 + 5 * rt->d.n_layers + 1;
     return 0;
 }
 

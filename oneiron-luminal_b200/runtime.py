@@ -31,6 +31,8 @@ DTYPE = {"f32": 0, "f16": 1, "bf16": 2, "int": 3, "bool": 4, "nvfp4": 5, "mxfp4"
 SLOT = {
     "embed": 0, "attn_norm": 1, "q": 2, "k": 3, "v": 4, "o": 5, "mlp_norm": 6,
     "gate": 7, "up": 8, "down": 9, "final_norm": 10, "lm_head": 11, "q_norm": 12, "k_norm": 13,
+    "q_bias": 14, "k_bias": 15, "v_bias": 16, "o_bias": 17, "sinks": 18, "router": 19, "router_bias": 20,
+    "exp_gate_up": 21, "exp_gate_up_bias": 22, "exp_down": 23, "exp_down_bias": 24,
 }
 
 
@@ -49,6 +51,9 @@ class ModelDesc(C.Structure):
         ("weight_dtype", C.c_uint32), ("embed_dtype", C.c_uint32), ("kv_dtype", C.c_uint32),
         ("qk_norm", C.c_int32), ("tied_head", C.c_int32), ("max_new_tokens", C.c_int32),
         ("tp_size", C.c_int32), ("tp_rank", C.c_int32), ("max_batch", C.c_int32),
+        ("sliding_window", C.c_int32), ("window_even_layers", C.c_int32), ("attn_sinks", C.c_int32), ("proj_bias", C.c_int32),
+        ("yarn_factor", C.c_float), ("yarn_beta_fast", C.c_float), ("yarn_beta_slow", C.c_float), ("yarn_orig_max_pos", C.c_float),
+        ("n_experts", C.c_int32), ("top_k", C.c_int32), ("swiglu_limit", C.c_float), ("ep_size", C.c_int32), ("ep_rank", C.c_int32),
     ]
 
     def copy(self, **kw) -> "ModelDesc":
@@ -107,6 +112,22 @@ CONFIGS: Dict[str, ModelDesc] = {
     "llama3_8b_q8_quarter": _desc(n_layers=2, hidden=4096, n_q_heads=8, n_kv_heads=2, head_dim=128, ffn=3584, vocab=32064,
                                   max_seq=256, rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"],
                                   kv_dtype=DTYPE["bf16"]),
+    # gpt-oss-20B shape (examples/gpt_oss scaled to 24 layers / 32 experts): alternating 128-token sliding-window and full layers,
+    # per-head sinks, projection biases, YaRN RoPE, top-4 of 32 experts of width 2880
+    "gpt_oss_20b_q8": _desc(n_layers=24, hidden=2880, n_q_heads=64, n_kv_heads=8, head_dim=64, ffn=2880, vocab=201088, max_seq=4096,
+                            rope_theta=150000.0, rope_style=2, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"],
+                            sliding_window=128, window_even_layers=1, attn_sinks=1, proj_bias=1, yarn_factor=32.0, yarn_beta_fast=32.0,
+                            yarn_beta_slow=1.0, yarn_orig_max_pos=4096.0, n_experts=32, top_k=4, swiglu_limit=7.0),
+    # the same layer kind, small: window 8 so that a short run leaves it, 16/2 heads of 64 (8 query heads per KV head), 8 experts
+    "small_oss": _desc(n_layers=4, hidden=512, n_q_heads=16, n_kv_heads=2, head_dim=64, ffn=512, vocab=2048, max_seq=128,
+                       rope_theta=150000.0, rope_style=2, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"],
+                       sliding_window=8, window_even_layers=1, attn_sinks=1, proj_bias=1, yarn_factor=32.0, yarn_beta_fast=32.0,
+                       yarn_beta_slow=1.0, yarn_orig_max_pos=4096.0, n_experts=8, top_k=4, swiglu_limit=7.0),
+    # the attention features alone on a dense FFN (window, sinks, biases, YaRN), hidden not a multiple of the tile width
+    "small_oss_dense": _desc(n_layers=3, hidden=576, n_q_heads=16, n_kv_heads=2, head_dim=64, ffn=1152, vocab=2048, max_seq=128,
+                             rope_theta=150000.0, rope_style=2, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"],
+                             sliding_window=8, window_even_layers=1, attn_sinks=1, proj_bias=1, yarn_factor=32.0, yarn_beta_fast=32.0,
+                             yarn_beta_slow=1.0, yarn_orig_max_pos=4096.0),
     # small Q8_0 model for fast parity runs
     "small_q8": _desc(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn=1536, vocab=2048, max_seq=128,
                       rope_theta=500000.0, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"]),

@@ -55,6 +55,14 @@ struct ModelCfg {            // keep in sync with the ctypes mirror in tests/ora
     int32_t embed_bf16;      // 1: embedding table and norm gains are bfloat16 values
     int32_t qk_norm;         // 1: per-head RMSNorm on q and k before RoPE (Qwen3)
     int32_t tied_head;       // 1: lm_head = embedding table (f32 / bf16 values, never Q8_0)
+    // gpt_oss-style layers (examples/gpt_oss/src/model.rs)
+    int32_t sliding_window;      // 0: full causal attention; else a row attends to the last `sliding_window` positions (model.rs:661-664)
+    int32_t window_even_layers;  // 1: only even-indexed layers are windowed (LAYER_IS_SLIDING, model.rs:84-88); 0: every layer
+    int32_t attn_sinks;          // 1: a learnable logit per query head joins the softmax denominator (model.rs:727-747)
+    int32_t proj_bias;           // 1: biases on the q, k, v and o projections (model.rs:230-260)
+    float yarn_factor, yarn_beta_fast, yarn_beta_slow, yarn_orig_max_pos;   // rope_style 2: YaRN table (model.rs:47-81)
+    int32_t n_experts, top_k;    // > 0: the FFN is a routed mixture of experts (model.rs:263-276, 791-962); ffn = the experts' width
+    float swiglu_limit;          // clamp of the experts' gate / up values (7.0)
 };
 
 // A linear weight: either f32 [n,k] or Q8_0 planes (quants [n,k] + one binary16 scale per 32).
@@ -70,9 +78,17 @@ struct Linear {
     }
 };
 
-enum Slot { S_EMBED = 0, S_ATTN_NORM, S_Q, S_K, S_V, S_O, S_MLP_NORM, S_GATE, S_UP, S_DOWN, S_FINAL_NORM, S_LM_HEAD, S_Q_NORM, S_K_NORM, S_COUNT };
+enum Slot { S_EMBED = 0, S_ATTN_NORM, S_Q, S_K, S_V, S_O, S_MLP_NORM, S_GATE, S_UP, S_DOWN, S_FINAL_NORM, S_LM_HEAD, S_Q_NORM, S_K_NORM,
+            S_Q_BIAS, S_K_BIAS, S_V_BIAS, S_O_BIAS, S_SINKS, S_ROUTER, S_ROUTER_BIAS, S_EXP_GATE_UP, S_EXP_GATE_UP_BIAS, S_EXP_DOWN,
+            S_EXP_DOWN_BIAS, S_COUNT };
 
-struct Layer { Linear q, k, v, o, gate, up, down; std::vector<float> attn_norm, mlp_norm, q_norm, k_norm; };
+struct Layer {
+    Linear q, k, v, o, gate, up, down;
+    std::vector<float> attn_norm, mlp_norm, q_norm, k_norm;
+    std::vector<float> q_b, k_b, v_b, o_b, sinks;                       // projection biases, per-head sink logits
+    Linear router, exp_gu, exp_down;                                    // router [E, H]; experts' gate_up [E * 2F, H] (row 2i gate, 2i+1 up) and down [E * H, F]
+    std::vector<float> router_b, exp_gu_b, exp_down_b;
+};
 
 // "{:.6}" round trip of a float literal (src/hlir.rs:215-219, 238-255)
 static float round6(double v) {
@@ -157,6 +173,30 @@ struct Model {
                     p[1] = x0 * sn + x1 * cs;
                 }
             }
+        } else if (c.rope_style == 2) {
+            // YaRN: inverse frequencies blended between interpolation and extrapolation, worked out in binary64 and stored as
+            // f32; cos and sin scaled by 0.1 ln(factor) + 1 (examples/gpt_oss/src/model.rs:47-81, 557-572); split halves
+            const double base = (double)c.rope_theta, dim = (double)d, PI = 3.14159265358979323846;
+            auto corr = [&](double rot) { return (dim * std::log((double)c.yarn_orig_max_pos / (rot * 2.0 * PI))) / (2.0 * std::log(base)); };
+            const double low = corr((double)c.yarn_beta_fast), high = corr((double)c.yarn_beta_slow);
+            const float fac = (float)(0.1 * std::log((double)c.yarn_factor) + 1.0);
+            for (int i = 0; i < half; i++) {
+                const double pf = std::pow(base, 2.0 * (double)i / dim);
+                const double extrap = 1.0 / pf, interp = 1.0 / ((double)c.yarn_factor * pf);
+                const double diff = high - low;
+                double t = std::fabs(diff) > 1e-10 ? ((double)i - low) / diff : 0.0;
+                t = t < 0.0 ? 0.0 : t > 1.0 ? 1.0 : t;
+                const double ef = 1.0 - t;
+                const float inv = (float)(interp * (1.0 - ef) + extrap * ef);
+                const float ang = (float)pos * inv;
+                const float sn = sinf(ang) * fac, cs = cosf(ang) * fac;
+                for (int h = 0; h < n_heads; h++) {
+                    float* p = v + (size_t)h * d;
+                    const float x0 = p[i], x1 = p[i + half];
+                    p[i] = x0 * cs - x1 * sn;
+                    p[i + half] = x1 * cs + x0 * sn;
+                }
+            }
         } else {
             for (int i = 0; i < half; i++) {
                 const float freq = powf(c.rope_theta, -((float)(2 * i)) / (float)d);
@@ -170,6 +210,64 @@ struct Model {
                 }
             }
         }
+    }
+
+    // one row of y = W x with the matvec's arithmetic
+    static float row_dot(const Linear& W, size_t row, const float* x) {
+        float acc = 0.0f;
+        for (int j = 0; j < W.k; j++) acc = acc + W.w(row, (size_t)j) * x[j];
+        return acc;
+    }
+
+    // Routed experts (examples/gpt_oss/src/model.rs:263-276 and the two kernels at :791-962): router logits = W_r xf + b_r;
+    // top-k by repeated arg-max (the first of equal maxima wins), softmax over the selected logits; per selected expert
+    // gate / up = rows 2i / 2i+1 of its gate_up matrix (+ bias), gate <= limit, |up| <= limit, glu = gate * sigmoid(1.702 gate),
+    // s = (up + 1) * glu; out = sum over the selected experts of weight * (W_down s + b_down); x += out.
+    void moe(const Layer& L, const float* xf, float* x, float* scratch) const {
+        const int H = c.hidden, F = c.ffn, E = c.n_experts, TK = c.top_k;
+        std::vector<float> logits((size_t)E);
+        for (int e = 0; e < E; e++) logits[(size_t)e] = row_dot(L.router, (size_t)e, xf) + L.router_b[(size_t)e];
+        std::vector<int> sel((size_t)TK);
+        std::vector<float> wt((size_t)TK);
+        std::vector<float> buf = logits;
+        for (int ki = 0; ki < TK; ki++) {
+            float best = -1e30f; int bi = 0;
+            for (int e = 0; e < E; e++) if (buf[(size_t)e] > best) { best = buf[(size_t)e]; bi = e; }
+            sel[(size_t)ki] = bi; wt[(size_t)ki] = best; buf[(size_t)bi] = -1e30f;
+        }
+        float mx = wt[0];
+        for (int ki = 1; ki < TK; ki++) mx = fmaxf(mx, wt[(size_t)ki]);
+        float se = 0.0f;
+        for (int ki = 0; ki < TK; ki++) { wt[(size_t)ki] = expf(wt[(size_t)ki] - mx); se = se + wt[(size_t)ki]; }
+        const float inv = 1.0f / se;
+        for (int ki = 0; ki < TK; ki++) wt[(size_t)ki] = wt[(size_t)ki] * inv;
+        std::vector<float> sw((size_t)TK * F);
+        parallel_for((long)TK * F, 64, [&](long a, long b) {
+            for (long p = a; p < b; p++) {
+                const int el = (int)(p / F), i = (int)(p % F), e = sel[(size_t)el];
+                const size_t grow = (size_t)e * 2 * F + 2 * (size_t)i;
+                float gate = row_dot(L.exp_gu, grow, xf) + L.exp_gu_b[grow];
+                float up = row_dot(L.exp_gu, grow + 1, xf) + L.exp_gu_b[grow + 1];
+                gate = fminf(gate, c.swiglu_limit);
+                up = fmaxf(fminf(up, c.swiglu_limit), -c.swiglu_limit);
+                const float glu = gate * (1.0f / (1.0f + expf(-gate * 1.702f)));
+                sw[(size_t)p] = (up + 1.0f) * glu;
+            }
+        });
+        (void)scratch;
+        std::vector<float> out((size_t)H);
+        parallel_for(H, 32, [&](long a, long b) {
+            for (long col = a; col < b; col++) {
+                float ov = 0.0f;
+                for (int el = 0; el < TK; el++) {
+                    const size_t drow = (size_t)sel[(size_t)el] * H + (size_t)col;
+                    const float acc = row_dot(L.exp_down, drow, &sw[(size_t)el * F]) + L.exp_down_b[drow];
+                    ov = ov + wt[(size_t)el] * acc;
+                }
+                out[(size_t)col] = ov;
+            }
+        });
+        for (int j = 0; j < H; j++) x[j] = x[j] + out[(size_t)j];
     }
 
     // One token at absolute position `pos`; x is the residual stream (in/out). Cache rows < pos must be filled.
@@ -193,6 +291,10 @@ struct Model {
         matvec(L.q, n1, q);
         matvec(L.k, n1, k);
         matvec(L.v, n1, v);
+        if (c.proj_bias) {
+            for (int j = 0; j < qd; j++) q[j] = q[j] + L.q_b[(size_t)j];
+            for (int j = 0; j < kvd; j++) { k[j] = k[j] + L.k_b[(size_t)j]; v[j] = v[j] + L.v_b[(size_t)j]; }
+        }
         if (c.qk_norm) {
             const float eps_qk = c.rms_eps;   // Qwen's fused kernel uses the literal, not a graph constant
             for (int h = 0; h < nq; h++) rmsnorm(q + (size_t)h * d, L.q_norm.data(), d, eps_qk, q + (size_t)h * d);
@@ -209,6 +311,40 @@ struct Model {
         const float scale = 1.0f / sqrtf((float)d);
         const float* KC = kc[(size_t)l].data();
         const float* VC = vc[(size_t)l].data();
+        const int win = (c.sliding_window > 0 && (!c.window_even_layers || (l % 2) == 0)) ? c.sliding_window : 0;
+        if (win > 0 || c.attn_sinks) {
+            // the gpt_oss kernel's form (examples/gpt_oss/src/model.rs:641-757): one pass with a running maximum over rows
+            // start .. pos, then the head's sink logit joins the denominator (it has no value row), then the division
+            const int start = (win > 0 && pos >= win) ? pos - win + 1 : 0;
+            for (int h = 0; h < nq; h++) {
+                const int kvh = h / grp;
+                const float* qh = q + (size_t)h * d;
+                float* oh = att + (size_t)h * d;
+                for (int e = 0; e < d; e++) oh[e] = 0.0f;
+                float am = -INFINITY, ad = 0.0f;
+                for (int r = start; r <= pos; r++) {
+                    const float* kr = KC + (size_t)r * kvd + (size_t)kvh * d;
+                    const float* vr = VC + (size_t)r * kvd + (size_t)kvh * d;
+                    float dot = 0.0f;
+                    for (int e = 0; e < d; e++) dot = dot + qh[e] * kr[e];
+                    const float logit = dot * scale;
+                    const float mn = fmaxf(am, logit);
+                    const float corr = expf(am - mn), w = expf(logit - mn);
+                    ad = ad * corr + w;
+                    am = mn;
+                    for (int e = 0; e < d; e++) oh[e] = oh[e] * corr + w * vr[e];
+                }
+                if (c.attn_sinks) {
+                    const float sink = L.sinks[(size_t)h];
+                    const float mn = fmaxf(am, sink);
+                    const float corr = expf(am - mn);
+                    ad = ad * corr + expf(sink - mn);
+                    for (int e = 0; e < d; e++) oh[e] = oh[e] * corr;
+                }
+                const float inv = 1.0f / ad;
+                for (int e = 0; e < d; e++) oh[e] = oh[e] * inv;
+            }
+        } else
         parallel_for(nq, pos >= 256 ? 1 : nq, [&](long h0, long h1) {
         for (long h = h0; h < h1; h++) {
             const int kvh = (int)h / grp;
@@ -237,9 +373,11 @@ struct Model {
         }
         });
         matvec(L.o, att, o);
+        if (c.proj_bias) for (int j = 0; j < H; j++) o[j] = o[j] + L.o_b[(size_t)j];
         for (int j = 0; j < H; j++) x[j] = x[j] + o[j];
 
         rmsnorm(x, L.mlp_norm.data(), H, eps6, n1);
+        if (c.n_experts > 0) { moe(L, n1, x, g); return; }
         matvec(L.gate, n1, g);
         matvec(L.up, n1, u);
         const float c_l2e = round6(1.0 / std::log(2.0));
@@ -292,7 +430,9 @@ static Linear* slot_linear(Model& m, int slot, int layer) {
     if (layer < 0 || layer >= m.c.n_layers) return nullptr;
     Layer& L = m.layers[(size_t)layer];
     switch (slot) { case S_Q: return &L.q; case S_K: return &L.k; case S_V: return &L.v; case S_O: return &L.o;
-                    case S_GATE: return &L.gate; case S_UP: return &L.up; case S_DOWN: return &L.down; default: return nullptr; }
+                    case S_GATE: return &L.gate; case S_UP: return &L.up; case S_DOWN: return &L.down;
+                    case S_ROUTER: return &L.router; case S_EXP_GATE_UP: return &L.exp_gu; case S_EXP_DOWN: return &L.exp_down;
+                    default: return nullptr; }
 }
 static std::vector<float>* slot_vector(Model& m, int slot, int layer) {
     if (slot == S_EMBED) return &m.embed;
@@ -300,7 +440,10 @@ static std::vector<float>* slot_vector(Model& m, int slot, int layer) {
     if (layer < 0 || layer >= m.c.n_layers) return nullptr;
     Layer& L = m.layers[(size_t)layer];
     switch (slot) { case S_ATTN_NORM: return &L.attn_norm; case S_MLP_NORM: return &L.mlp_norm;
-                    case S_Q_NORM: return &L.q_norm; case S_K_NORM: return &L.k_norm; default: return nullptr; }
+                    case S_Q_NORM: return &L.q_norm; case S_K_NORM: return &L.k_norm;
+                    case S_Q_BIAS: return &L.q_b; case S_K_BIAS: return &L.k_b; case S_V_BIAS: return &L.v_b; case S_O_BIAS: return &L.o_b;
+                    case S_SINKS: return &L.sinks; case S_ROUTER_BIAS: return &L.router_b; case S_EXP_GATE_UP_BIAS: return &L.exp_gu_b;
+                    case S_EXP_DOWN_BIAS: return &L.exp_down_b; default: return nullptr; }
 }
 static void slot_dims(const ModelCfg& c, int slot, int* n, int* k) {
     const int qd = c.n_q_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
@@ -312,12 +455,26 @@ static void slot_dims(const ModelCfg& c, int slot, int* n, int* k) {
         case S_DOWN: *n = c.hidden; *k = c.ffn; break;
         case S_LM_HEAD: case S_EMBED: *n = c.vocab; *k = c.hidden; break;
         case S_Q_NORM: case S_K_NORM: *n = 1; *k = c.head_dim; break;
+        case S_Q_BIAS: *n = 1; *k = qd; break;
+        case S_K_BIAS: case S_V_BIAS: *n = 1; *k = kvd; break;
+        case S_O_BIAS: *n = 1; *k = c.hidden; break;
+        case S_SINKS: *n = 1; *k = c.n_q_heads; break;
+        case S_ROUTER: *n = c.n_experts; *k = c.hidden; break;
+        case S_ROUTER_BIAS: *n = 1; *k = c.n_experts; break;
+        case S_EXP_GATE_UP: *n = c.n_experts * 2 * c.ffn; *k = c.hidden; break;
+        case S_EXP_GATE_UP_BIAS: *n = 1; *k = c.n_experts * 2 * c.ffn; break;
+        case S_EXP_DOWN: *n = c.n_experts * c.hidden; *k = c.ffn; break;
+        case S_EXP_DOWN_BIAS: *n = 1; *k = c.n_experts * c.hidden; break;
         default: *n = 1; *k = c.hidden; break;
     }
 }
 
 // Tensor id used to key the generator: one id per (layer, slot).
-static inline uint64_t tensor_id(int slot, int layer) { return (uint64_t)(layer < 0 ? 0 : layer) * 16u + (uint64_t)slot; }
+// (the slots added for gpt_oss-style layers, 14 and up, have a range of their own so that the ids of the first 14 never moved)
+static inline uint64_t tensor_id(int slot, int layer) {
+    const uint64_t l = (uint64_t)(layer < 0 ? 0 : layer);
+    return slot < 14 ? l * 16u + (uint64_t)slot : (1ull << 21) + l * 32u + (uint64_t)slot;
+}
 static const uint64_t kScaleStream = 4096;   // scales draw from key(seed, tid + 4096)
 
 }  // namespace orc
@@ -441,10 +598,20 @@ int orc_model_synth(void* h, uint64_t seed) {
     if (fill(orc::S_FINAL_NORM, c.n_layers, edt, 1)) return -1;
     if (!c.tied_head && fill(orc::S_LM_HEAD, c.n_layers, wdt, 0)) return -1;
     for (int l = 0; l < c.n_layers; l++) {
-        const int lin[] = {orc::S_Q, orc::S_K, orc::S_V, orc::S_O, orc::S_GATE, orc::S_UP, orc::S_DOWN};
-        for (int s : lin) if (fill(s, l, wdt, 0)) return -1;
+        const int att[] = {orc::S_Q, orc::S_K, orc::S_V, orc::S_O};
+        for (int s : att) if (fill(s, l, wdt, 0)) return -1;
+        if (c.n_experts > 0) {
+            if (fill(orc::S_ROUTER, l, edt, 0) || fill(orc::S_ROUTER_BIAS, l, edt, 0)) return -1;
+            if (fill(orc::S_EXP_GATE_UP, l, wdt, 0) || fill(orc::S_EXP_DOWN, l, wdt, 0)) return -1;
+            if (fill(orc::S_EXP_GATE_UP_BIAS, l, edt, 0) || fill(orc::S_EXP_DOWN_BIAS, l, edt, 0)) return -1;
+        } else {
+            const int mlp[] = {orc::S_GATE, orc::S_UP, orc::S_DOWN};
+            for (int s : mlp) if (fill(s, l, wdt, 0)) return -1;
+        }
         if (fill(orc::S_ATTN_NORM, l, edt, 1) || fill(orc::S_MLP_NORM, l, edt, 1)) return -1;
         if (c.qk_norm && (fill(orc::S_Q_NORM, l, edt, 1) || fill(orc::S_K_NORM, l, edt, 1))) return -1;
+        if (c.proj_bias) { const int bs[] = {orc::S_Q_BIAS, orc::S_K_BIAS, orc::S_V_BIAS, orc::S_O_BIAS}; for (int s : bs) if (fill(s, l, edt, 0)) return -1; }
+        if (c.attn_sinks && fill(orc::S_SINKS, l, edt, 0)) return -1;
     }
     return 0;
 }

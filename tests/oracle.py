@@ -21,6 +21,9 @@ class OrcCfg(C.Structure):
         ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32), ("max_seq", C.c_int32),
         ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("rope_style", C.c_int32), ("weight_q8", C.c_int32),
         ("kv_bf16", C.c_int32), ("embed_bf16", C.c_int32), ("qk_norm", C.c_int32), ("tied_head", C.c_int32),
+        ("sliding_window", C.c_int32), ("window_even_layers", C.c_int32), ("attn_sinks", C.c_int32), ("proj_bias", C.c_int32),
+        ("yarn_factor", C.c_float), ("yarn_beta_fast", C.c_float), ("yarn_beta_slow", C.c_float), ("yarn_orig_max_pos", C.c_float),
+        ("n_experts", C.c_int32), ("top_k", C.c_int32), ("swiglu_limit", C.c_float),
     ]
 
 
@@ -91,6 +94,9 @@ def cfg_from_desc(d) -> OrcCfg:
     for f in ("n_layers", "hidden", "n_q_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "max_seq", "rms_eps",
               "rope_theta", "rope_style", "qk_norm", "tied_head"):
         setattr(c, f, getattr(d, f))
+    for f in ("sliding_window", "window_even_layers", "attn_sinks", "proj_bias", "yarn_factor", "yarn_beta_fast", "yarn_beta_slow",
+              "yarn_orig_max_pos", "n_experts", "top_k", "swiglu_limit"):
+        setattr(c, f, getattr(d, f, 0))
     c.weight_q8 = 1 if d.weight_dtype == 7 else 0
     c.kv_bf16 = 1 if d.kv_dtype == 2 else 0
     c.embed_bf16 = 1 if d.embed_dtype == 2 else 0

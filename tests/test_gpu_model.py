@@ -475,3 +475,31 @@ def test_batched_decode_equals_sequences_decoded_alone(pkg):
             rt.seq_select(4)
     finally:
         rt.close()
+
+
+# ------------------------------------------------------------------------------------------------- gpt_oss-style layers
+@pytest.mark.parametrize("name", ["small_oss_dense", "small_oss"])
+def test_gpt_oss_style_layers_match_oracle(pkg, name):
+    """Sliding window on the even layers (8 positions, so a 30-token run leaves it), per-head sink logits, biases on q/k/v/o,
+    YaRN rotation — and, for `small_oss`, the routed experts (top-4 of 8, gate_up interleaved, clamp, weighted sum) — against
+    the oracle's restatement of examples/gpt_oss/src/model.rs:520-764 and :791-962: greedy tokens identical, logits within
+    tolerance, cache rows.  `small_oss_dense` has a hidden size (576) that is not a whole number of weight tiles."""
+    desc = pkg.CONFIGS[name]
+    seed, n_prompt, n_new = 13, 18, 14
+    orc = OracleModel(desc)
+    orc.synth(seed)
+    prompt = orc.synth_tokens(seed, n_prompt)
+    want, lo, margins = orc.generate(prompt, n_new, return_last_logits=True, return_margins=True)
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc)
+        rt.synth(seed)
+        got = rt.generate(prompt, n_new)
+        lg = rt.get_f32()
+        k0 = rt.kv_read(desc.n_layers - 1, "k", n_prompt + n_new - 1)
+    finally:
+        rt.close()
+    assert got == want, f"min oracle top-1/top-2 margin {min(margins):.3e}"
+    assert rel_err(lg, lo) <= LOGIT_TOL
+    kr = orc.kv_read(desc.n_layers - 1, "k", n_prompt + n_new - 1)
+    assert np.max(np.abs(k0 - kr)) <= 2.0 ** -6 * np.max(np.abs(kr))
