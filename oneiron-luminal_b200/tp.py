@@ -50,6 +50,23 @@ def validate(desc, tp_size: int) -> None:
                 raise ValueError(f"{slot}: a K-shard must hold whole 32-element Q8_0 blocks")
 
 
+def validate_ep(desc, ep_size: int) -> None:
+    """Raise if the model's experts cannot be spread over `ep_size` ranks (a mixture-of-experts model, whole experts per rank)."""
+    if getattr(desc, "n_experts", 0) <= 0:
+        raise ValueError("expert parallelism needs a mixture-of-experts model")
+    if ep_size < 1 or desc.n_experts % ep_size:
+        raise ValueError(f"{desc.n_experts} experts do not divide over {ep_size} ranks")
+
+
+def local_experts(desc, ep_size: int, ep_rank: int) -> range:
+    """The experts rank `ep_rank` holds: a contiguous block, as lum_model_desc.ep_size / ep_rank lay them out."""
+    validate_ep(desc, ep_size)
+    if not 0 <= ep_rank < ep_size:
+        raise ValueError("bad expert-parallel rank")
+    per = desc.n_experts // ep_size
+    return range(ep_rank * per, (ep_rank + 1) * per)
+
+
 def exchange_unique_id(dist, rank: int, make_id: Callable[[], bytes], device=None) -> bytes:
     """Rank 0 makes the 128-byte communicator id; everybody gets it through `torch.distributed` (any backend)."""
     import torch

@@ -77,3 +77,52 @@ def test_unique_id_exchange_two_gloo_ranks(tmp_path):
                        stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env, timeout=240)
     assert r.returncode == 0, r.stdout[-3000:]
     assert r.stdout.count("ok") == 2
+
+
+def test_expert_parallel_host_helpers(pkg):
+    """Which experts a rank holds, and which models / group sizes are refused (no GPU needed)."""
+    from oneiron_luminal_b200 import tp as T
+    d = pkg.CONFIGS["gpt_oss_20b_q8"]
+    assert list(T.local_experts(d, 8, 3)) == [12, 13, 14, 15]
+    assert list(T.local_experts(d, 1, 0)) == list(range(32))
+    with pytest.raises(ValueError):
+        T.validate_ep(d, 5)                                  # 32 experts over 5 ranks
+    with pytest.raises(ValueError):
+        T.validate_ep(pkg.CONFIGS["llama3_8b_q8"], 2)        # no experts
+    with pytest.raises(ValueError):
+        T.local_experts(d, 4, 4)
+
+
+def test_expert_parallel_group_two_gloo_ranks(tmp_path):
+    """The group handshake an expert-parallel run makes (communicator id to every rank, every rank its own block of experts),
+    as two gloo ranks on CPU."""
+    script = tmp_path / "ep_worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import os, sys
+        sys.path.insert(0, {ROOT!r})
+        import torch.distributed as dist
+        from __graft_entry__ import load_package
+        pkg = load_package()
+        from oneiron_luminal_b200 import tp as T
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        d = pkg.CONFIGS["small_oss"]
+        T.validate_ep(d, world)
+        uid = T.exchange_unique_id(dist, rank, lambda: bytes(range(128)))
+        assert uid == bytes(range(128))
+        mine = list(T.local_experts(d, world, rank))
+        got = [None] * world
+        dist.all_gather_object(got, mine)
+        assert sorted(sum(got, [])) == list(range(d.n_experts))            # every expert on exactly one rank
+        shard = d.copy(ep_size=world, ep_rank=rank)
+        assert (shard.ep_size, shard.ep_rank, shard.tp_size) == (world, rank, 1)
+        dist.barrier()
+        dist.destroy_process_group()
+        print("rank", rank, "ok")
+    """))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29619")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29619", str(script)],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env, timeout=240)
+    assert r.returncode == 0, r.stdout[-3000:]
+    assert r.stdout.count("ok") == 2
