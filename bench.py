@@ -539,6 +539,91 @@ def run_tensor_core_regime(args, pkg, which: str):
     print(json.dumps(line))
 
 
+def run_moe(args, pkg):
+    """gpt-oss-20B-shape mixture of experts: every rank decodes its own sequence (batch = number of GPUs), the experts are spread
+    over the ranks and every layer's tokens travel to them and back all-to-all (NCCL).  On one GPU: batch 1, all experts local.
+    A "step" is `--tokens-per-step` tokens of every sequence; `value` is the tokens/s of all sequences together (weak scaling)."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks, peak_kind = measured_peaks()
+    base = pkg.CONFIGS["gpt_oss_20b_q8"]
+    n_prompt = PROMPT_LEN if PROMPT_LEN != 512 else 2048
+    tps = TOKENS_PER_STEP
+    total = (args.warmup + args.steps) * tps
+    desc = base.copy(max_seq=n_prompt + total + 8, max_new_tokens=total + 8)
+    rt = pkg.B200Runtime.initialize(device=local)
+    if world > 1:
+        from oneiron_luminal_b200 import tp as T
+        T.validate_ep(desc, world)
+        uid = T.exchange_unique_id(dist, rank, pkg.B200Runtime.tp_unique_id, device=torch.device("cuda", local))
+        rt.tp_init(uid, world, rank)
+        desc = desc.copy(ep_size=world, ep_rank=rank)
+    rt.load_model(desc)
+    rt.synth(SEED)
+    prompt = _prompt_tokens(base.vocab, n_prompt + rank)[rank:]
+    rt.kv_reset(); rt.decode_reset()
+    rt.set_data(prompt); rt.execute({"s": n_prompt, "p": 0})
+    rt.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        rt.decode_greedy(tps)
+    ext = torch.cuda.ExternalStream(rt.stream(), device=torch.device("cuda", local))
+    sampler = ClockSampler(physical_gpu_index(local))
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ext)
+    for _ in range(args.steps):
+        rt.decode_greedy(tps)
+    e1.record(ext)
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    n_tok = args.steps * tps
+    value = world * n_tok / (ms * 1e-3)
+    st = rt.stats()
+    p_mean = n_prompt + (args.warmup + args.steps / 2.0) * tps
+    # a token reads the attention weights, the router, top-4 experts and the vocabulary projection; K/V rows of the full layers up to
+    # its position and at most 128 on the windowed layers
+    kv_row = st.kv_bytes_per_position / base.n_layers
+    kv_bytes = kv_row * (base.n_layers / 2 * (p_mean + 1) + base.n_layers / 2 * min(p_mean + 1, base.sliding_window))
+    bytes_tok = st.weight_bytes_per_token + kv_bytes
+    ach = bytes_tok * (value / world) / 1e9
+    line = None
+    if rank == 0:
+        line = {"metric": "q8_gpt_oss_20b_decode_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32 accumulate over Q8_0 weights", "data": "synthetic",
+                "config": {"workload": "gpt_oss_20b_q8", "batch": world, "prompt_len": n_prompt, "tokens_per_step": tps, "seed": SEED,
+                           "parallelism": "single GPU, all experts local" if world == 1 else f"ep{world}: one sequence per GPU, {base.n_experts // world} experts per GPU, all-to-all dispatch and combine per layer (NCCL)"},
+                "roofline": {"bound": "hbm", "kernel": "whole decode step of one rank", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "bytes_per_token": bytes_tok, "traffic": None},
+                "e2e": {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "not measured for this workload"},
+                "gpu_launches": int(st.kernel_launches), "clocks": clocks}
+    rt.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line))
+
+
 def _prompt_tokens(vocab: int, n: int):
     """The seeded prompt, generated without the oracle: SplitMix64 counter generator, tensor id 2^20."""
     mask = (1 << 64) - 1
@@ -563,7 +648,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
-    ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8", "llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096"],
+    ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8", "llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096", "gpt_oss_20b_q8"],
                     help="llama3_8b_q8: the configuration the metric is quoted on (default); qwen3_4b_q8: the Qwen3-4B shape; "
                          "llama3_8b_q8_bs32 / llama3_8b_q8_prefill4096: the same model in the tensor-core regime (batched decode / one long prompt)")
     ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor"],
@@ -572,6 +657,12 @@ def main():
     from __graft_entry__ import load_package
     pkg = load_package()
     PROMPT_LEN, TOKENS_PER_STEP = args.prompt_len, args.tokens_per_step
+    if args.workload == "gpt_oss_20b_q8":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU arm is timed on the batch-1 dense decode workloads only"}))
+            return
+        run_moe(args, pkg)
+        return
     if args.workload in ("llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the CPU arm is timed on the batch-1 decode workloads only"}))

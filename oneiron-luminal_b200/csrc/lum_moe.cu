@@ -43,6 +43,49 @@ __device__ __forceinline__ float q8_row_dot(const int8_t* q, const __half* sc, i
     return warp_sum(acc);
 }
 
+// N rows at once (N <= 4): every trip's loads of all rows are issued before any is used, so a warp keeps N x 1 KiB in flight
+// instead of one — the expert kernels are bound by how many bytes are on their way from HBM.  Same arithmetic per row as
+// q8_row_dot.  Rows whose pointer is null are skipped (result 0).
+template <int N>
+__device__ __forceinline__ void q8_rows_dot(const int8_t* const (&q)[N], const __half* const (&sc)[N], int K, const float* const (&x)[N], int lane,
+                                            float (&out)[N]) {
+    float acc[N];
+#pragma unroll
+    for (int r = 0; r < N; r++) acc[r] = 0.0f;
+    auto dot4 = [](uint32_t w, float4 v, float a) {
+        a = fmaf((float)(int)(int8_t)(w & 0xffu), v.x, a);
+        a = fmaf((float)(int)(int8_t)((w >> 8) & 0xffu), v.y, a);
+        a = fmaf((float)(int)(int8_t)((w >> 16) & 0xffu), v.z, a);
+        a = fmaf((float)((int)w >> 24), v.w, a);
+        return a;
+    };
+    for (int b = lane; b < (K >> 5); b += 32) {
+        uint4 w0[N], w1[N];
+        float d[N];
+#pragma unroll
+        for (int r = 0; r < N; r++) {
+            if (q[r]) {
+                const uint4* p = (const uint4*)(q[r] + (size_t)b * 32);
+                w0[r] = __ldcs(p); w1[r] = __ldcs(p + 1);
+                d[r] = __half2float(sc[r][b]);
+            } else { w0[r] = w1[r] = make_uint4(0u, 0u, 0u, 0u); d[r] = 0.0f; }
+        }
+#pragma unroll
+        for (int r = 0; r < N; r++) {
+            if (q[r]) {
+                const float4* x4 = (const float4*)(x[r] + (size_t)b * 32);
+                float p0 = dot4(w0[r].x, x4[0], 0.0f), p1 = dot4(w0[r].y, x4[1], 0.0f);
+                p0 = dot4(w0[r].z, x4[2], p0); p1 = dot4(w0[r].w, x4[3], p1);
+                p0 = dot4(w1[r].x, x4[4], p0); p1 = dot4(w1[r].y, x4[5], p1);
+                p0 = dot4(w1[r].z, x4[6], p0); p1 = dot4(w1[r].w, x4[7], p1);
+                acc[r] = fmaf(p0 + p1, d[r], acc[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < N; r++) out[r] = warp_sum(acc[r]);
+}
+
 __global__ void __launch_bounds__(256) moe_route(const MoeArgs a) {
     extern __shared__ __align__(16) float mr_smem[];          // xf [H], logits [E], 8 words of scratch
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -64,7 +107,17 @@ __global__ void __launch_bounds__(256) moe_route(const MoeArgs a) {
     __syncthreads();
     for (int e = warp; e < E; e += 8) {
         float acc = 0.0f;
-        if (a.gain_kind == WK_BF16) {
+        if (a.gain_kind == WK_BF16 && (H & 7) == 0) {
+            const uint4* w8 = (const uint4*)((const uint16_t*)a.router + (size_t)e * H);      // 8 weights per 16-byte load
+            for (int i = lane; i < (H >> 3); i += 32) {
+                const uint4 w = w8[i];
+                const float4 x0 = *(const float4*)(xf + (size_t)i * 8), x1 = *(const float4*)(xf + (size_t)i * 8 + 4);
+                acc = fmaf(__uint_as_float(w.x << 16), x0.x, acc); acc = fmaf(__uint_as_float(w.x & 0xffff0000u), x0.y, acc);
+                acc = fmaf(__uint_as_float(w.y << 16), x0.z, acc); acc = fmaf(__uint_as_float(w.y & 0xffff0000u), x0.w, acc);
+                acc = fmaf(__uint_as_float(w.z << 16), x1.x, acc); acc = fmaf(__uint_as_float(w.z & 0xffff0000u), x1.y, acc);
+                acc = fmaf(__uint_as_float(w.w << 16), x1.z, acc); acc = fmaf(__uint_as_float(w.w & 0xffff0000u), x1.w, acc);
+            }
+        } else if (a.gain_kind == WK_BF16) {
             const uint16_t* w = (const uint16_t*)a.router + (size_t)e * H;
             for (int i = lane; i < H; i += 32) acc = fmaf(bf16_bits_to_f32(w[i]), xf[i], acc);
         } else {
@@ -108,8 +161,12 @@ __global__ void __launch_bounds__(256) moe_gate_up(const MoeArgs a) {
         if (le < 0 || le >= a.n_local) continue;                      // another rank holds this expert
         const size_t row = (size_t)le * 2 * F + 2 * (size_t)i;
         const int nb = H >> 5;
-        float gate = q8_row_dot(a.gu_q + row * H, a.gu_s + row * nb, H, xf, lane);
-        float up = q8_row_dot(a.gu_q + (row + 1) * H, a.gu_s + (row + 1) * nb, H, xf, lane);
+        const int8_t* const qs[2] = {a.gu_q + row * H, a.gu_q + (row + 1) * H};
+        const __half* const ss[2] = {a.gu_s + row * nb, a.gu_s + (row + 1) * nb};
+        const float* const xs[2] = {xf, xf};
+        float gu[2];
+        q8_rows_dot<2>(qs, ss, H, xs, lane, gu);
+        float gate = gu[0], up = gu[1];
         if (lane == 0) {
             gate += load_gain(a.gu_bias, a.gain_kind, (int)row);
             up += load_gain(a.gu_bias, a.gain_kind, (int)row + 1);
@@ -132,13 +189,25 @@ __global__ void __launch_bounds__(256) moe_down(const MoeArgs a) {
         const int* sel = (const int*)(xf + H);
         const float* wt = xf + H + a.top_k;
         float ov = 0.0f;
-        for (int el = 0; el < a.top_k; el++) {
-            const int le = sel[el] - a.expert0;
-            if (le < 0 || le >= a.n_local) continue;
-            const size_t row = (size_t)le * H + col;
-            float acc = q8_row_dot(a.dn_q + row * F, a.dn_s + row * (F >> 5), F, a.sw + ((size_t)t * a.top_k + el) * F, lane);
-            acc += load_gain(a.dn_bias, a.gain_kind, (int)row);
-            ov = fmaf(wt[el], acc, ov);
+        for (int e0 = 0; e0 < a.top_k; e0 += 4) {          // the token's selected experts, four at a time
+            const int8_t* qs[4]; const __half* ss[4]; const float* xs[4];
+            size_t rows[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int el = e0 + j;
+                const int le = el < a.top_k ? sel[el] - a.expert0 : -1;
+                const bool mine = le >= 0 && le < a.n_local;
+                rows[j] = mine ? (size_t)le * H + col : 0;
+                qs[j] = mine ? a.dn_q + rows[j] * F : nullptr;
+                ss[j] = mine ? a.dn_s + rows[j] * (F >> 5) : nullptr;
+                xs[j] = a.sw + ((size_t)t * a.top_k + (el < a.top_k ? el : 0)) * F;
+            }
+            const int8_t* const (&qc)[4] = qs; const __half* const (&sc4)[4] = ss; const float* const (&xc)[4] = xs;
+            float accs[4];
+            q8_rows_dot<4>(qc, sc4, F, xc, lane, accs);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (qs[j]) ov = fmaf(wt[e0 + j], accs[j] + load_gain(a.dn_bias, a.gain_kind, (int)rows[j]), ov);
         }
         if (lane == 0) {
             if (a.out_add) a.out_add[(size_t)t * a.out_ld + col] += ov;     // one GPU: straight into the residual stream
