@@ -250,6 +250,11 @@ typedef struct lum_stats {
     double last_profile_usec;         /* result of the last lum_profile / lum_profile_llir */
 } lum_stats;
 int32_t lum_get_stats(const lum_rt* rt, lum_stats* out);
+/* Test hook (no reference counterpart): makes one bounded wait run out on purpose, on the host's terms — it runs the first
+ * layer's q | k | v projection expecting one more partial vector than anybody writes, so the kernel waits lum_config.wait_budget_ms
+ * for completion words that never come, gives up and returns.  Expected result: LUM_E_DEVICE (status 0x80), with the runtime
+ * fully usable afterwards.  Nothing faults, traps or hangs; set wait_budget_ms to a few milliseconds first. */
+int32_t lum_debug_wait_timeout(lum_rt* rt);
 
 /* ---------------------------------------------------------------------------------------------
  * Tensor parallelism over the GPUs of one node: one process and one runtime per GPU (the reference is single-GPU:

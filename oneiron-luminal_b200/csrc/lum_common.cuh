@@ -229,14 +229,18 @@ __device__ __forceinline__ uint4 ld_ll2(const uint2* p) {
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-// One element, waited for (bounded): returns false when the word never came.
-__device__ __forceinline__ bool ld_ll_wait(const uint2* p, uint32_t word, float* out) {
+// One element, waited for (bounded): returns false when the word never came within `budget` SM clocks (0: LUM_WAIT_BUDGET_CYCLES),
+// or at once when `status` already says that a wait of this kind ran out (one budget per kernel, not one per element).
+__device__ __forceinline__ bool ld_ll_wait(const uint2* p, uint32_t word, float* out, long long budget = 0, const uint32_t* status = nullptr) {
+    if (budget <= 0) budget = LUM_WAIT_BUDGET_CYCLES;
     const long long t0 = clock64();
     unsigned int spins = 0;
     for (;;) {
         const uint2 v = ld_ll(p);
         if (v.y == word) { *out = __uint_as_float(v.x); return true; }
-        if ((++spins & 63u) == 0 && clock64() - t0 > LUM_WAIT_BUDGET_CYCLES) { *out = 0.0f; return false; }
+        if ((++spins & 63u) == 0) {
+            if (clock64() - t0 > budget || (status && (*(volatile const uint32_t*)status & LUM_ST_WAIT_PEER))) { *out = 0.0f; return false; }
+        }
         __nanosleep(40);
     }
 }

@@ -98,7 +98,7 @@ __device__ __forceinline__ void gemv_load_x(const GemvArgs& a, float* xs, int ti
         for (int r = 0; r < a.n_parts; r++) {
             if (a.parts_ll) {
                 float u;
-                if (!ld_ll_wait((const uint2*)a.parts + (size_t)r * a.part_stride + k, peer_word(__ldcg(a.seq), a.parts_tag), &u)) atomicOr(a.status, LUM_ST_WAIT_PEER);
+                if (!ld_ll_wait((const uint2*)a.parts + (size_t)r * a.part_stride + k, peer_word(__ldcg(a.seq), a.parts_tag), &u, a.wait_cycles, a.status)) atomicOr(a.status, LUM_ST_WAIT_PEER);
                 v += u;
             } else {
                 v += __ldcg(a.parts + (size_t)r * a.part_stride + k);

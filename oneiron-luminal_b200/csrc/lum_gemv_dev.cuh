@@ -337,14 +337,14 @@ struct XSource {
 
 // Four consecutive elements of a partial vector stored as {bits, word} pairs: both 16-byte loads are issued at once; an element
 // whose word has not arrived yet is then waited for on its own (bounded).
-static __device__ __noinline__ float4 ll_load4(const uint2* p, uint32_t word, uint32_t* status) {   // out of line: the kernel's code size is latency
+static __device__ __noinline__ float4 ll_load4(const uint2* p, uint32_t word, uint32_t* status, long long budget) {   // out of line: the kernel's code size is latency
     const uint4 a = ld_ll2(p), b = ld_ll2(p + 2);
     float4 v = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
     bool ok = true;
-    if (a.y != word) ok &= ld_ll_wait(p, word, &v.x);
-    if (a.w != word) ok &= ld_ll_wait(p + 1, word, &v.y);
-    if (b.y != word) ok &= ld_ll_wait(p + 2, word, &v.z);
-    if (b.w != word) ok &= ld_ll_wait(p + 3, word, &v.w);
+    if (a.y != word) ok &= ld_ll_wait(p, word, &v.x, budget, status);
+    if (a.w != word) ok &= ld_ll_wait(p + 1, word, &v.y, budget, status);
+    if (b.y != word) ok &= ld_ll_wait(p + 2, word, &v.z, budget, status);
+    if (b.w != word) ok &= ld_ll_wait(p + 3, word, &v.w, budget, status);
     if (!ok) atomicOr(status, LUM_ST_WAIT_PEER);
     return v;
 }
@@ -435,7 +435,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
                             if (f4 < n4) {
                                 const uint4 a4 = raw[j][it][0], b4 = raw[j][it][1];
                                 float4 v = make_float4(__uint_as_float(a4.x), __uint_as_float(a4.z), __uint_as_float(b4.x), __uint_as_float(b4.z));
-                                if (a4.y != word || a4.w != word || b4.y != word || b4.w != word) v = ll_load4(pr + 4 * f4, word, a.status);
+                                if (a4.y != word || a4.w != word || b4.y != word || b4.w != word) v = ll_load4(pr + 4 * f4, word, a.status, a.wait_cycles);
                                 xv[it].x += v.x; xv[it].y += v.y; xv[it].z += v.z; xv[it].w += v.w;
                             }
                         }
@@ -484,7 +484,7 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
                 for (int it = 0; it < TRIPS; it++) {
                     const int f4 = it * kWorkers + tid;
                     if (f4 < n4) {
-                        const float4 u = (PEER && xs.parts_ll) ? ll_load4((const uint2*)xs.parts + (size_t)r * xs.part_stride + 4 * f4, peer_word(__ldcg(xs.seq), xs.parts_tag), a.status)
+                        const float4 u = (PEER && xs.parts_ll) ? ll_load4((const uint2*)xs.parts + (size_t)r * xs.part_stride + 4 * f4, peer_word(__ldcg(xs.seq), xs.parts_tag), a.status, a.wait_cycles)
                                                      : __ldcg(pr + f4);
                         xv[it].x += u.x; xv[it].y += u.y; xv[it].z += u.z; xv[it].w += u.w;
                     }

@@ -95,6 +95,7 @@ struct GemvArgs {
     int n_parts;
     int part_stride;
     uint32_t parts_tag;
+    long long wait_cycles;        // budget of a wait on a word another GPU must write, in SM clocks (0: LUM_WAIT_BUDGET_CYCLES, about 2 s)
 };
 
 struct AttnArgs {

@@ -169,6 +169,7 @@ struct lum_rt {
     int moe_slot = 0;
     int ep_size = 1, ep_rank = 0;
     int prefill_min_rows = 4;
+    long long wait_cycles = 0;        // lum_config.wait_budget_ms in SM clocks (0: the library default)
     int max_batch = 1, cur_seq = 0;
     int batch_n = 0;                  // sequences of the running batch (lum_batch_begin)
     int *b_step = nullptr, *b_log = nullptr;     // batched decode: step counter and token log [max_new_tokens][max_batch] on the device
@@ -367,6 +368,7 @@ int check_status(lum_rt* rt) {
                     (st & LUM_ST_WAIT_FULL) ? "stage wait timed out; " : "",
                     (st & LUM_ST_WAIT_EMPTY) ? "producer wait timed out; " : "", (st & LUM_ST_WAIT_DRAIN) ? "drain wait timed out; " : "",
                     (st & LUM_ST_BAD_TOKEN) ? "token id out of range; " : "", (st & LUM_ST_BAD_POS) ? "position out of range; " : "");
+        // (0x40 tensor-memory hand-over and 0x80 a word from another GPU that never came show in the hexadecimal value)
     }
     return 0;
 }
@@ -475,6 +477,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         LayerW& w = rt->L[(size_t)l];
         GemvArgs a{};
         a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = w.q.kind;
+        a.wait_cycles = rt->wait_cycles;
         // RMSNorm + q,k,v
         a.nseg = 3;
         a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows, w.q.kc};
@@ -553,6 +556,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         // RMSNorm + gate, up + SwiGLU
         GemvArgs g{};
         g.status = rt->status; g.use_pdl = pdl; g.gain_kind = gk; g.eps = rt->eps6; g.wkind = w.gate.kind;
+        g.wait_cycles = rt->wait_cycles;
         g.nseg = 2; g.seg[0] = {w.gate.w, w.gate.s, (int)w.gate.rows, w.gate.kc}; g.seg[1] = {w.up.w, w.up.s, (int)w.up.rows, w.up.kc};
         g.K = (int)w.gate.kdev; g.k_norm = H; g.epi = EPI_SWIGLU; g.gain = w.mlp_norm.w; g.y = rt->h;
         take_partial(g);
@@ -581,6 +585,7 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         const Tensor& hw = d.tied_head ? rt->embed : rt->lm_head;
         GemvArgs a{};
         a.status = rt->status; a.use_pdl = pdl; a.gain_kind = gk; a.eps = rt->eps6; a.wkind = hw.kind;
+        a.wait_cycles = rt->wait_cycles;
         a.nseg = 1; a.seg[0] = {hw.w, hw.s, (int)hw.rows, hw.kc};
         a.K = hw.kind == WK_Q8 ? (int)hw.kdev : H; a.k_norm = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
@@ -984,6 +989,12 @@ int32_t lum_create(const lum_config* cfg, lum_rt** out) {
     if (p.major < 10) return fail(nullptr, LUM_E_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only", p.major, p.minor);
     lum_rt* rt = new lum_rt();
     rt->cfg = c; rt->sm_count = p.multiProcessorCount; rt->cc = p.major * 10 + p.minor; rt->mem_bytes = p.totalGlobalMem;
+    {
+        int khz = 0;
+        cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c.device);
+        if (khz <= 0) khz = 1900000;
+        rt->wait_cycles = c.wait_budget_ms > 0 ? (long long)c.wait_budget_ms * khz : 0;
+    }
     e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete rt; return fail(nullptr, LUM_E_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     *out = rt;
@@ -1322,6 +1333,35 @@ int32_t lum_batch_get_logits(lum_rt* rt, int32_t seq, float* host_out, size_t n)
     CU(rt, cudaSetDevice(rt->cfg.device));
     CU(rt, cudaMemcpyAsync(host_out, rt->rows.logits + (size_t)seq * rt->vocab_l, n * 4, cudaMemcpyDeviceToHost, rt->stream));
     CU(rt, cudaStreamSynchronize(rt->stream));
+    return check_status(rt);
+}
+
+// Test hook: makes a bounded wait run out.  Runs layer 0's q | k | v projection with one extra partial vector that never
+// arrives (a zeroed {value, completion word} array nothing writes): the kernel's prologue waits the configured budget for the
+// words, gives up, flags the status word and still finishes (ring drained, tensor memory released).
+int32_t lum_debug_wait_timeout(lum_rt* rt) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "debug_wait_timeout: no model");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const int H = rt->d.hidden;
+    LayerW& w = rt->L[0];
+    void* ll = nullptr;
+    uint32_t* seq = nullptr;
+    cudaError_t e = cudaMalloc(&ll, (size_t)H * 8);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&seq, 4);
+    if (e != cudaSuccess) { if (ll) cudaFree(ll); return fail(rt, LUM_E_NOMEM, "debug_wait_timeout: %s", cudaGetErrorString(e)); }
+    cudaMemsetAsync(ll, 0, (size_t)H * 8, rt->stream);
+    cudaMemsetAsync(seq, 0, 4, rt->stream);
+    GemvArgs a{};
+    a.status = rt->status; a.use_pdl = 0; a.gain_kind = kind_of(rt->d.embed_dtype); a.eps = rt->eps6; a.wkind = w.q.kind;
+    a.wait_cycles = rt->wait_cycles;
+    a.nseg = 1; a.seg[0] = {w.q.w, w.q.s, (int)w.q.rows, w.q.kc};
+    a.K = (int)w.q.kdev; a.k_norm = H; a.epi = EPI_STORE; a.gain = w.attn_norm.w; a.y = rt->qkv; a.x = rt->x;
+    a.parts = (const float*)ll; a.parts_ll = 1; a.n_parts = 1; a.part_stride = H; a.parts_tag = 7; a.seq = seq;
+    e = launch_gemv(a, rt->sm_count, rt->stream);
+    cudaStreamSynchronize(rt->stream);
+    cudaFree(ll);
+    cudaFree(seq);
+    if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "debug_wait_timeout: %s", cudaGetErrorString(e));
     return check_status(rt);
 }
 

@@ -190,6 +190,7 @@ def load_library() -> C.CDLL:
         "lum_kv_save": (i32, [vp, i32, i32, i32, vp, sz]),
         "lum_kv_load": (i32, [vp, i32, i32, i32, vp, sz]),
         "lum_get_stats": (i32, [vp, P(Stats)]),
+        "lum_debug_wait_timeout": (i32, [vp]),
         "lum_op_status": (i32, [vp]),
         "lum_get_output": (i32, [vp, C.c_int64, P(C.c_float), sz]),
         "lum_kv_reset": (i32, [vp]),
@@ -412,6 +413,10 @@ class B200Runtime:
 
     def kv_load(self, layer: int, kind: str, rows: int, data) -> None:
         self._ck(self._lib.lum_kv_load(self._h, layer, 0 if kind == "k" else 1, rows, data.ctypes.data_as(C.c_void_p), data.nbytes))
+
+    def debug_wait_timeout(self) -> None:
+        """Test hook: one bounded wait runs out (raises LumError with code LUM_E_DEVICE); the runtime stays usable."""
+        self._ck(self._lib.lum_debug_wait_timeout(self._h))
 
     def stats(self) -> Stats:
         st = Stats()

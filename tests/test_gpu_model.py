@@ -503,3 +503,27 @@ def test_gpt_oss_style_layers_match_oracle(pkg, name):
     assert rel_err(lg, lo) <= LOGIT_TOL
     kr = orc.kv_read(desc.n_layers - 1, "k", n_prompt + n_new - 1)
     assert np.max(np.abs(k0 - kr)) <= 2.0 ** -6 * np.max(np.abs(kr))
+
+
+def test_bounded_wait_runs_out_and_runtime_recovers(pkg):
+    """A wait on a word nobody writes gives up after the configured budget: the kernel returns (ring drained, tensor memory
+    released), the host reports LUM_E_DEVICE, and the same runtime then decodes exactly as before.  Nothing faults or hangs: the
+    failure is an absent writer, arranged by the host."""
+    import time
+    desc = pkg.CONFIGS["llama3_8b_q8_2layer"]
+    rt = pkg.B200Runtime.initialize(device=0, wait_budget_ms=5)
+    try:
+        rt.load_model(desc); rt.synth(8)
+        prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+        base = rt.generate(prompt, 10)
+        t0 = time.time()
+        with pytest.raises(pkg.LumError) as ei:
+            rt.debug_wait_timeout()
+        assert ei.value.code == -4 and "0x80" in str(ei.value)          # LUM_E_DEVICE, "a word from another GPU never came"
+        assert time.time() - t0 < 5.0                                    # one budget, not one per element
+        assert rt.generate(prompt, 10) == base                           # status cleared, counters reset, context intact
+        with pytest.raises(pkg.LumError):
+            rt.debug_wait_timeout()
+        assert rt.generate(prompt, 10) == base
+    finally:
+        rt.close()
