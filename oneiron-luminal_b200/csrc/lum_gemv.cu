@@ -378,6 +378,7 @@ cudaError_t launch_gemv(const GemvArgs& a_in, int sm_count, cudaStream_t st) {
     // an SM can hold, so that enough loads are in flight to keep HBM busy
     int grid = sm_count * (a.wkind != WK_Q8 && (long long)rows_total * a.K >= (1ll << 24) ? 8 : 2);
     if (grid > (rows_total + 7) / 8) grid = (rows_total + 7) / 8;
+    if (a.epi == EPI_ARGMAX && grid > kArgmaxSlots) grid = kArgmaxSlots;       // one best-logit slot per CTA
     if (grid < 1) grid = 1;
     const int max_rows = (rows_total + grid - 1) / grid + 1;
     const size_t smem = 256 + (size_t)((a.K + 3) & ~3) * 4 + (size_t)max_rows * 2 * 4;
@@ -429,6 +430,10 @@ extern "C" int32_t lum_op_sample_q8_0_static(const void* packed, int32_t n, int3
     const int kc = q8_pack_kc(n, k);
     if (!packed || !x || !logits || !best || !kc) {
         set_op_error("sample_q8_0_static: bad arguments or shape cannot be packed (needs K % 512 == 0, K <= 16384, N % 8 == 0)");
+        return -1;
+    }
+    if ((uintptr_t)x & 15) {       // the streaming kernel copies x with 16-byte loads; no other kernel reads the packed layout
+        set_op_error("sample_q8_0_static: x must be 16-byte aligned");
         return -1;
     }
     int dev = 0, sms = 0;

@@ -16,6 +16,7 @@ enum : int {
     EPI_PEER = 4,     // tensor parallel: acc is this rank's partial of row; stored into every rank's copy of this rank's partial vector
 };
 constexpr int kMaxPeers = 8;
+constexpr int kArgmaxSlots = 2048;      // capacity of GemvArgs::part_val / part_idx: the most CTAs a greedy-sampling launch may have
 // word (seq, tag) a rank publishes when its partial vector of one projection is complete everywhere
 __host__ __device__ inline uint32_t peer_word(uint32_t seq, uint32_t tag) { return seq * 1024u + tag; }
 

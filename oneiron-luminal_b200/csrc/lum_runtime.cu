@@ -1594,8 +1594,8 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     TRY(dev_alloc(rt, (void**)&rt->tokens_out, (size_t)d.max_new_tokens * 4));
     TRY(dev_alloc(rt, (void**)&rt->attn_part, (size_t)rt->nkv_l * splits * G * (hd + 2) * 4));
     TRY(dev_alloc(rt, (void**)&rt->attn_cnt, (size_t)rt->nkv_l * 4));
-    TRY(dev_alloc(rt, (void**)&rt->am_val, 1024 * 4));
-    TRY(dev_alloc(rt, (void**)&rt->am_idx, 1024 * 4));
+    TRY(dev_alloc(rt, (void**)&rt->am_val, kArgmaxSlots * 4));
+    TRY(dev_alloc(rt, (void**)&rt->am_idx, kArgmaxSlots * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_cnt, 4));
     TRY(dev_alloc(rt, (void**)&rt->step_ctr, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int)));
     cudaMemsetAsync(rt->step_ctr, 0, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int), rt->stream);
@@ -1992,6 +1992,7 @@ static SampleScratch* sample_scratch() {
 int32_t lum_op_sample_q8_0(const void* packed, int32_t n, int32_t k, const float* x, float* logits, int32_t* best, void* stream) {
     const int kc = q8_pack_kc(n, k);
     if (!packed || !x || !logits || !best || !kc) { g_create_error = "sample_q8_0: bad arguments or shape cannot be packed"; return LUM_E_INVALID; }
+    if ((uintptr_t)x & 15) { g_create_error = "sample_q8_0: x must be 16-byte aligned"; return LUM_E_INVALID; }
     SampleScratch* sc = sample_scratch();
     if (!sc) return op_fail("sample_q8_0 scratch", cudaErrorMemoryAllocation);
     if (cur_sm_count() > 256) { g_create_error = "sample_q8_0: more than 256 SMs"; return LUM_E_UNSUPPORTED; }

@@ -365,9 +365,13 @@ def test_full_size_configuration_matches_oracle_fixture(pkg, name):
                 ref = fx[f"{kind}_cache_layer{layer}"]
                 rms = float(np.sqrt(np.mean((have - ref) ** 2)) / np.sqrt(np.mean(ref ** 2)))
                 if layer == 0:
-                    # cache values are bfloat16: equal, or one rounding step apart where the f32 value sat next to a tie
-                    assert np.max(np.abs(have - ref) / np.maximum(np.abs(ref), 1e-3)) <= 2.0 ** -7, (layer, kind)
+                    # cache values are bfloat16: equal, or one rounding step apart where the f32 value sat next to a tie.  An
+                    # element that the rotation left small by cancellation carries the f32 error of its two large terms
+                    # (the angle position x frequency is rounded differently by the two libms), hence the absolute term.
+                    tol = 2.0 ** -7 * np.abs(ref) + 2.0 ** -14 * np.max(np.abs(ref))
+                    assert np.all(np.abs(have - ref) <= tol), (layer, kind, float(np.max(np.abs(have - ref) - tol)))
                     assert np.mean(have == ref) > 0.98, (layer, kind, float(np.mean(have == ref)))
+                    assert rms <= 1e-3, (layer, kind, rms)
                 else:
                     # after all layers: every rounding step a cached bfloat16 value flips by (2^-8 of it) feeds the layers
                     # above, so the last layer's rows agree to a few bfloat16 steps, not bit for bit
