@@ -116,10 +116,24 @@ typedef struct lum_model_desc {
 } lum_model_desc;
 
 int32_t lum_model_init(lum_rt* rt, const lum_model_desc* desc);
-/* Replaces `set_data(id, data)` / `load_safetensors` for weight tensors
- * (crates/luminal_cuda/src/runtime.rs:133-165).  `dtype` = LUM_F32, LUM_BF16 or LUM_Q8_0 (wire
- * blocks of lum_llir.h); `bytes` must match the slot's full (unsharded) shape. */
-int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void* host, size_t bytes, uint32_t dtype);
+/* Replaces `set_data(id, data)` for weight tensors (crates/luminal_cuda/src/runtime.rs:160-165).  `data` (host or device memory) holds
+ * the FULL (unsharded) tensor, `bytes` must match it; under tensor / expert parallelism this rank's part is cut out of it.
+ * `dtype` = LUM_F32, LUM_F16, LUM_BF16, or LUM_Q8_0 (wire blocks of lum_llir.h, only for slots the plan holds quantised).  A float
+ * source is converted on the device to what the slot holds: f32, bf16, or Q8_0 through the quantiser of lum_op_q8_0_quantize. */
+int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void* data, size_t bytes, uint32_t dtype);
+/* The same, for data that already is this rank's shard (what lum_save_safetensors wrote). */
+int32_t lum_model_set_weight_shard(lum_rt* rt, int32_t slot, int32_t layer, const void* data, size_t bytes, uint32_t dtype);
+/* Replaces `CudaRuntime::load_safetensors(cx, path)` (crates/luminal_cuda/src/runtime.rs:133-158): every tensor of the file whose name
+ * is the label of a slot this model has (the labels listed above) is stored with lum_model_set_weight; other tensors are skipped,
+ * as the reference skips labels the graph does not have.  F32, F16 and BF16 tensors are taken as values (the reference: F32 only);
+ * U8 tensors are taken as raw bytes, as in the reference — here Q8_0 wire blocks.  A file written by lum_save_safetensors is
+ * recognised by its metadata and must come from the same rank of the same group; its tensors are stored as shards.
+ * n_loaded / n_ignored (either may be NULL) count the tensors stored / skipped. */
+int32_t lum_load_safetensors(lum_rt* rt, const char* path, int32_t* n_loaded, int32_t* n_ignored);
+/* Shard writer (no reference counterpart): writes what this rank holds, in the layout lum_model_set_weight_shard takes (Q8_0 slots
+ * as U8 tensors [rows, cols / 32 * 34] of wire blocks), with metadata naming the rank's place in its tensor- / expert-parallel
+ * group.  Loading such a file needs neither the full checkpoint nor the quantiser. */
+int32_t lum_save_safetensors(lum_rt* rt, const char* path);
 /* Fill every tensor from the counter-based generator (documented in csrc/lum_synth.cu). */
 int32_t lum_model_synth(lum_rt* rt, uint64_t seed);
 /* Read `n` elements of a (possibly quantised) tensor back as f32, starting at element `offset`
@@ -325,6 +339,28 @@ int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x
  * clears the words.  It allocates nothing.  The stand-alone operators keep their per-device state in process-wide tables that
  * are not locked: call them from one thread per device. */
 int32_t lum_op_status(void* stream);
+/* Q8_0 quantiser on the device (no reference counterpart; ggml's reference quantiser restated): per block of 32 values
+ * d = max|x| / 127, q = roundf(x * (1 / d)), scale stored as binary16(d).  `dtype` of the source: LUM_F32, LUM_F16 or LUM_BF16.
+ * Output: quant and scale planes as lum_op_gemv_q8_0 reads them. */
+int32_t lum_op_q8_0_quantize(const void* src_dev, uint32_t dtype, size_t n_elems, int8_t* quants_dev, void* scales_dev, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * safetensors container, host side (the file format `load_safetensors` reads, runtime.rs:133-137).  Errors of these entries
+ * are reported by lum_st_last_error() (per thread).  Tensor dtypes use lum_dtype plus the two codes below. */
+#define LUM_ST_U8 100u     /* raw bytes */
+#define LUM_ST_OTHER 255u  /* a dtype this library does not read (I64, F64, ...) */
+typedef struct lum_st lum_st;
+const char* lum_st_last_error(void);
+int32_t lum_st_open(const char* path, lum_st** out);              /* maps the file and parses its header */
+void lum_st_close(lum_st* st);
+int32_t lum_st_count(const lum_st* st);
+/* name / data point into the mapping and stay valid until lum_st_close; shape8 receives up to 8 dimensions */
+int32_t lum_st_tensor(const lum_st* st, int32_t i, const char** name, uint32_t* dtype, int32_t* ndim, int64_t* shape8, const void** data,
+                      size_t* bytes);
+const char* lum_st_metadata(const lum_st* st, const char* key);   /* NULL when absent */
+/* shapes8: n x 8 dimensions (the first ndims[i] of each row are used) */
+int32_t lum_st_write(const char* path, int32_t n, const char* const* names, const uint32_t* dtypes, const int32_t* ndims, const int64_t* shapes8,
+                     const void* const* datas, int32_t n_meta, const char* const* meta_keys, const char* const* meta_vals);
 /* Q8_0 wire blocks (host layout, on device) -> planes; planes -> f32. */
 int32_t lum_op_q8_0_unpack(const uint8_t* blocks_dev, size_t n_blocks, int8_t* quants_dev, void* scales_dev, void* stream);
 int32_t lum_op_q8_0_dequant(const int8_t* quants_dev, const void* scales_dev, size_t n_elems, float* out_dev, void* stream);

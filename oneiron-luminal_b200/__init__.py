@@ -23,4 +23,6 @@ from .runtime import (  # noqa: F401
     describe_llir_chunk,
     mbu,
     Stats,
+    safetensors_read,
+    safetensors_write,
 )

@@ -179,8 +179,24 @@ int q8_pack_kc(int rows, int K);
 size_t q8_packed_bytes(int rows, int K);
 cudaError_t launch_q8_pack_units(const int8_t* q, const __half* s, int rows, int K, int kc, unsigned char* out, cudaStream_t st, int valid_cols = 0);
 cudaError_t launch_q8_unpack_wire(const uint8_t* blocks, int8_t* q, __half* s, size_t n_blocks, cudaStream_t st);
+cudaError_t launch_q8_quantize(const void* src, uint32_t dtype, size_t n_blocks, int8_t* q, __half* s, cudaStream_t st);   // f32 / f16 / bf16 -> planes
+
+// What the weight-ingest code needs to know about one tensor slot of a loaded model (this rank's shard).
+struct WeightView {
+    void* w; __half* s;                  // device storage: quants / values, Q8_0 plane scales (null when packed)
+    int kind, kc;                        // WK_*; Q8_0: 0 = planes, 512 = packed tile stream
+    size_t rows, cols, kdev;             // the shard; kdev = columns of the device layout (>= cols, zero columns beyond)
+    size_t row0, col0, full_rows, full_cols;
+    int device; cudaStream_t stream;
+};
 cudaError_t launch_q8_dequant(const int8_t* q, const __half* s, float* out, size_t n_elems, cudaStream_t st);
 cudaError_t launch_q8_dequant_rows(const void* w, const __half* s, int K, int kc, size_t row0, size_t n_rows, float* out, cudaStream_t st, int valid_cols = 0);
 cudaError_t launch_to_f32(const void* in, int kind, float* out, size_t n, cudaStream_t st);
 
 }  // namespace lum
+
+// Internal hand-over between the runtime (which owns the model) and the weight-ingest code; not part of the C ABI.
+struct lum_rt;
+int lum_internal_weight_view(lum_rt* rt, int slot, int layer, lum::WeightView* out);     // 0 = filled; 1 = no model / no such slot
+int lum_internal_fail(lum_rt* rt, int code, const char* msg);                            // records the message, returns the code
+int lum_internal_parallel(lum_rt* rt, int* tp_size, int* tp_rank, int* ep_size, int* ep_rank);   // returns the number of layers

@@ -955,6 +955,22 @@ int setup_mega(lum_rt* rt) {
 
 }  // namespace
 
+// ---- hand-over to the weight-ingest code (lum_ingest.cu)
+int lum_internal_weight_view(lum_rt* rt, int slot, int layer, lum::WeightView* out) {
+    if (!rt || !rt->has_model) return 1;
+    Tensor* t = slot_tensor(rt, slot, layer);
+    if (!t || !t->w) return 1;
+    *out = {t->w, t->s, t->kind, t->kc, t->rows, t->cols, t->kdev, t->row0, t->col0, t->full_rows, t->full_cols, rt->cfg.device, rt->stream};
+    return 0;
+}
+int lum_internal_fail(lum_rt* rt, int code, const char* msg) { return fail(rt, code, "%s", msg); }
+int lum_internal_parallel(lum_rt* rt, int* tp_size, int* tp_rank, int* ep_size, int* ep_rank) {
+    const lum_model_desc& d = rt->d;
+    *tp_size = d.tp_size > 1 ? d.tp_size : 1; *tp_rank = d.tp_size > 1 ? d.tp_rank : 0;
+    *ep_size = d.ep_size > 1 ? d.ep_size : 1; *ep_rank = d.ep_size > 1 ? d.ep_rank : 0;
+    return d.n_layers;
+}
+
 // =================================================================================== C ABI
 
 extern "C" {
@@ -1638,54 +1654,6 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
         rt->attn_cluster = want && attn_cluster_supported(t);
     }
     if (int r = setup_mega(rt)) { free_model(rt); return r; }
-    return 0;
-}
-
-int32_t lum_model_set_weight(lum_rt* rt, int32_t slot, int32_t layer, const void* host, size_t bytes, uint32_t dtype) {
-    if (!rt || !rt->has_model || !host) return fail(rt, LUM_E_INVALID, "set_weight: no model or null data");
-    CU(rt, cudaSetDevice(rt->cfg.device));
-    Tensor* t = slot_tensor(rt, slot, layer);
-    if (!t) return fail(rt, LUM_E_INVALID, "set_weight: slot %d / layer %d does not exist in this model", slot, layer);
-    if (kind_of(dtype) != t->kind || (dtype != LUM_F32 && dtype != LUM_BF16 && dtype != LUM_Q8_0))
-        return fail(rt, LUM_E_INVALID, "set_weight: slot %d expects dtype kind %d, got %u", slot, t->kind, dtype);
-    const size_t full = t->full_rows * t->full_cols;
-    const size_t want = dtype == LUM_Q8_0 ? full / 32 * 34 : full * (dtype == LUM_BF16 ? 2 : 4);
-    if (bytes != want) return fail(rt, LUM_E_INVALID, "set_weight: slot %d needs %zu bytes, got %zu", slot, want, bytes);
-    CU(rt, cudaStreamSynchronize(rt->stream));
-    // bytes per element-run in the wire format, so a shard is a 2-D slice of the host tensor
-    const size_t esz_num = dtype == LUM_Q8_0 ? 34 : (dtype == LUM_BF16 ? 2 : 4), esz_den = dtype == LUM_Q8_0 ? 32 : 1;
-    const size_t src_pitch = t->full_cols * esz_num / esz_den, row_bytes = t->cols * esz_num / esz_den;
-    const uint8_t* src = (const uint8_t*)host + t->row0 * src_pitch + t->col0 * esz_num / esz_den;
-    if (dtype == LUM_Q8_0) {
-        void* tmp = nullptr;
-        cudaError_t e = cudaMalloc(&tmp, t->rows * row_bytes);
-        if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "set_weight: staging buffer: %s", cudaGetErrorString(e));
-        // copies go on the runtime's own (non-blocking) stream: a legacy-stream copy from pageable memory may return
-        // before its DMA has landed and would not be ordered against kernels on this stream
-        e = cudaMemcpy2DAsync(tmp, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyDefault, rt->stream);   // host or device source
-        if (t->kc) {
-            // wire blocks -> temporary planes -> packed tile stream
-            void* planes = nullptr;
-            const size_t n = t->rows * t->cols;
-            if (e == cudaSuccess) e = cudaMalloc(&planes, n + n / 16 + 64);
-            if (e == cudaSuccess) {
-                __half* ps = (__half*)((char*)planes + n);
-                e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)planes, ps, n / 32, rt->stream);
-                if (e == cudaSuccess) e = launch_q8_pack_units((const int8_t*)planes, ps, (int)t->rows, (int)t->kdev, t->kc, (unsigned char*)t->w, rt->stream, (int)t->cols);
-            }
-            if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
-            else cudaStreamSynchronize(rt->stream);
-            if (planes) cudaFree(planes);
-        } else {
-            if (e == cudaSuccess) e = launch_q8_unpack_wire((const uint8_t*)tmp, (int8_t*)t->w, t->s, t->rows * t->cols / 32, rt->stream);
-            if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
-        }
-        cudaFree(tmp);
-        if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "set_weight: %s", cudaGetErrorString(e));
-    } else {
-        CU(rt, cudaMemcpy2DAsync(t->w, row_bytes, src, src_pitch, row_bytes, t->rows, cudaMemcpyDefault, rt->stream));
-        CU(rt, cudaStreamSynchronize(rt->stream));
-    }
     return 0;
 }
 

@@ -176,6 +176,17 @@ def load_library() -> C.CDLL:
         "lum_device_info": (i32, [vp, P(i32), P(u64), P(i32)]),
         "lum_model_init": (i32, [vp, P(ModelDesc)]),
         "lum_model_set_weight": (i32, [vp, i32, i32, vp, sz, u32]),
+        "lum_model_set_weight_shard": (i32, [vp, i32, i32, vp, sz, u32]),
+        "lum_load_safetensors": (i32, [vp, C.c_char_p, P(i32), P(i32)]),
+        "lum_save_safetensors": (i32, [vp, C.c_char_p]),
+        "lum_op_q8_0_quantize": (i32, [vp, u32, sz, vp, vp, vp]),
+        "lum_st_last_error": (C.c_char_p, []),
+        "lum_st_open": (i32, [C.c_char_p, P(vp)]),
+        "lum_st_close": (None, [vp]),
+        "lum_st_count": (i32, [vp]),
+        "lum_st_tensor": (i32, [vp, i32, P(C.c_char_p), P(u32), P(i32), P(C.c_int64), P(vp), P(sz)]),
+        "lum_st_metadata": (C.c_char_p, [vp, C.c_char_p]),
+        "lum_st_write": (i32, [C.c_char_p, i32, P(C.c_char_p), P(u32), P(i32), P(C.c_int64), P(vp), i32, P(C.c_char_p), P(C.c_char_p)]),
         "lum_model_synth": (i32, [vp, u64]),
         "lum_model_get_weight_f32": (i32, [vp, i32, i32, sz, sz, P(C.c_float)]),
         "lum_model_weight_bytes": (i32, [vp, P(u64)]),
@@ -239,6 +250,67 @@ def load_library() -> C.CDLL:
 
 
 EXPORTED_SYMBOLS = None  # filled lazily by tests from include/lum_b200.h
+
+
+_ST_NP = {0: "float32", 1: "float16", 2: "uint16", 3: "int32", 4: "bool", 100: "uint8"}      # bf16 values travel as their bit patterns
+
+
+def safetensors_read(path: str):
+    """Host-only: ``(tensors, metadata)`` of a safetensors file through the library's own reader.  ``tensors`` maps a name to
+    ``(dtype_name, numpy array)``; bf16 tensors come back as uint16 bit patterns (dtype_name "bf16"); dtypes the library does
+    not read come back as ``("other", raw uint8 bytes)``."""
+    import numpy as np
+    lib = load_library()
+    h = C.c_void_p()
+    if lib.lum_st_open(path.encode(), C.byref(h)):
+        raise LumError(-1, lib.lum_st_last_error().decode())
+    try:
+        out = {}
+        for i in range(lib.lum_st_count(h)):
+            name, dt, nd, n = C.c_char_p(), C.c_uint32(), C.c_int32(), C.c_size_t()
+            shape = (C.c_int64 * 8)()
+            data = C.c_void_p()
+            if lib.lum_st_tensor(h, i, C.byref(name), C.byref(dt), C.byref(nd), shape, C.byref(data), C.byref(n)):
+                raise LumError(-1, lib.lum_st_last_error().decode())
+            raw = np.frombuffer(C.string_at(data, n.value), dtype=np.uint8) if n.value else np.zeros(0, np.uint8)
+            dims = tuple(int(shape[k]) for k in range(nd.value))
+            if dt.value in _ST_NP:
+                arr = raw.view(_ST_NP[dt.value]).reshape(dims)
+                out[name.value.decode()] = ({0: "f32", 1: "f16", 2: "bf16", 3: "i32", 4: "bool", 100: "u8"}[dt.value], arr)
+            else:
+                out[name.value.decode()] = ("other", raw)
+        meta = {}
+        for k in ("lum.shard", "lum.tp_size", "lum.tp_rank", "lum.ep_size", "lum.ep_rank", "lum.q8_0", "format"):
+            v = lib.lum_st_metadata(h, k.encode())
+            if v is not None:
+                meta[k] = v.decode()
+        return out, meta
+    finally:
+        lib.lum_st_close(h)
+
+
+def safetensors_write(path: str, tensors, metadata=None) -> None:
+    """Host-only: write ``{name: (dtype_name, numpy array)}`` (dtype names as safetensors_read returns them) with the library's
+    own writer; tensors are stored in the order given."""
+    import numpy as np
+    lib = load_library()
+    code = {"f32": 0, "f16": 1, "bf16": 2, "i32": 3, "bool": 4, "u8": 100}
+    names = list(tensors)
+    n = len(names)
+    arrs = [np.require(tensors[k][1], requirements="C") for k in names]        # (ascontiguousarray would turn a scalar into [1])
+    c_names = (C.c_char_p * n)(*[k.encode() for k in names])
+    c_dt = (C.c_uint32 * n)(*[code[tensors[k][0]] for k in names])
+    c_nd = (C.c_int32 * n)(*[a.ndim for a in arrs])
+    c_sh = (C.c_int64 * (8 * n))()
+    for i, a in enumerate(arrs):
+        for k, d in enumerate(a.shape):
+            c_sh[8 * i + k] = d
+    c_data = (C.c_void_p * n)(*[a.ctypes.data for a in arrs])
+    md = dict(metadata or {})
+    mk = (C.c_char_p * max(1, len(md)))(*[k.encode() for k in md])
+    mv = (C.c_char_p * max(1, len(md)))(*[str(v).encode() for v in md.values()])
+    if lib.lum_st_write(path.encode(), n, c_names, c_dt, c_nd, c_sh, c_data, len(md), mk, mv):
+        raise LumError(-1, lib.lum_st_last_error().decode())
 
 
 def describe_llir(blob: bytes):
@@ -433,6 +505,20 @@ class B200Runtime:
     def set_weight(self, slot: str, layer: int, data, dtype: str) -> None:
         """``data``: a C-contiguous numpy array holding f32 values, bf16 bit patterns (uint16) or Q8_0 wire blocks (uint8)."""
         self._ck(self._lib.lum_model_set_weight(self._h, SLOT[slot], layer, data.ctypes.data_as(C.c_void_p), data.nbytes, DTYPE[dtype]))
+
+    def set_weight_shard(self, slot: str, layer: int, data, dtype: str) -> None:
+        """As set_weight, for data that already is this rank's shard."""
+        self._ck(self._lib.lum_model_set_weight_shard(self._h, SLOT[slot], layer, data.ctypes.data_as(C.c_void_p), data.nbytes, DTYPE[dtype]))
+
+    def load_safetensors(self, path: str):
+        """``load_safetensors(cx, path)`` (crates/luminal_cuda/src/runtime.rs:133-158); returns (tensors stored, tensors skipped)."""
+        a, b = C.c_int32(), C.c_int32()
+        self._ck(self._lib.lum_load_safetensors(self._h, path.encode(), C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def save_safetensors(self, path: str) -> None:
+        """Write this rank's shard of the weights (Q8_0 as wire blocks) to a safetensors file load_safetensors takes back."""
+        self._ck(self._lib.lum_save_safetensors(self._h, path.encode()))
 
     def synth(self, seed: int) -> None:
         self._ck(self._lib.lum_model_synth(self._h, C.c_uint64(seed)))

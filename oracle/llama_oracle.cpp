@@ -500,6 +500,26 @@ void orc_q8_0_dequant(const uint8_t* blocks, size_t n_blocks, float* out) {
 
 // Synthetic tensor in wire form.  dtype: LUM_F32=0 -> f32 N(0,0.02); 2 -> bfloat16 bits of N(0,0.02);
 // 7 -> Q8_0 wire blocks.  `ones` fills norm gains with 1.0.
+// Q8_0 quantiser.  The reference has no Q8_0 code; the block format and this quantiser are ggml's (`quantize_row_q8_0_ref`,
+// ggml-quants.c — a dependency that is not in the reference tree), restated from its published algorithm:
+//     d = max|x| / 127,  id = d ? 1 / d : 0,  q_i = roundf(x_i * id),  stored scale = binary16(d).
+// Parity of this function is unpinned by reference vectors (there are none); the tests pin it with hand-worked blocks.
+// Output: wire blocks {binary16 scale (little-endian), 32 int8 quants}, 34 bytes each.
+void orc_q8_0_quantize(const float* x, size_t n_blocks, uint8_t* blocks) {
+    for (size_t b = 0; b < n_blocks; b++) {
+        const float* v = x + b * 32;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; j++) { const float a = std::fabs(v[j]); if (a > amax) amax = a; }
+        const float d = amax / 127.0f;
+        const float id = d != 0.0f ? 1.0f / d : 0.0f;
+        uint8_t* o = blocks + b * 34;
+        const uint16_t h = orc::f32_to_f16(d);
+        o[0] = (uint8_t)(h & 0xff);
+        o[1] = (uint8_t)(h >> 8);
+        for (int j = 0; j < 32; j++) o[2 + j] = (uint8_t)(int8_t)std::roundf(v[j] * id);
+    }
+}
+
 int orc_synth(uint64_t seed, uint64_t tid, uint32_t dtype, size_t n_elems, int ones, void* out) {
     const uint64_t key = orc::rng_key(seed, tid), skey = orc::rng_key(seed, tid + orc::kScaleStream);
     if (dtype == 0) {

@@ -52,6 +52,7 @@ def load() -> C.CDLL:
         "orc_model_destroy": (None, [vp]),
         "orc_model_error": (C.c_char_p, [vp]),
         "orc_q8_0_dequant": (None, [vp, sz, fp]),
+        "orc_q8_0_quantize": (None, [fp, sz, vp]),
         "orc_synth": (i32, [u64, u64, u32, sz, i32, vp]),
         "orc_synth_range": (i32, [u64, u64, u32, sz, sz, vp]),
         "orc_synth_tokens": (None, [u64, u64, u32, sz, ip]),
@@ -83,6 +84,22 @@ def load() -> C.CDLL:
 
 def _fp(a):
     return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def q8_0_quantize(x: np.ndarray) -> np.ndarray:
+    """f32 values (a multiple of 32 of them) -> Q8_0 wire blocks [n / 32, 34] uint8, by the oracle's quantiser."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    assert x.size % 32 == 0
+    out = np.empty((x.size // 32, 34), dtype=np.uint8)
+    load().orc_q8_0_quantize(_fp(x), x.size // 32, out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def q8_0_dequant(blocks: np.ndarray) -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 34)
+    out = np.empty(blocks.shape[0] * 32, dtype=np.float32)
+    load().orc_q8_0_dequant(blocks.ctypes.data_as(C.c_void_p), blocks.shape[0], _fp(out))
+    return out
 
 
 TOKENS_TID = 1 << 20  # generator id of prompt token streams
