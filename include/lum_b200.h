@@ -146,8 +146,14 @@ int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes);
  * include/lum_llir.h describes.  The block ops are matched against the Llama-style decoder schedule this runtime
  * implements (csrc/lum_llir.cu lists the pattern); the hyper-parameters and the Input-node -> weight-slot map come out
  * of the graph, while cache capacity and cache dtype — caller-owned buffers in the reference (main.rs:19,48) — are
- * arguments.  A graph of another shape is refused (LUM_E_INVALID, message names the node); there is no fallback.
- * lum_llir_describe does the recognition alone and needs no GPU. */
+ * arguments.  lum_llir_describe does the recognition alone and needs no GPU.
+ * A graph made only of the HLIR primitives (Constant, Iota, Cast, Exp2, Log2, Sin, Recip, Sqrt, Add, Mul, Mod, LessThan, Gather,
+ * Sum, Max between Inputs and Outputs — the set the reference keeps fallback kernels for, crates/luminal_cuda/src/kernel/hlir.rs:53-69;
+ * the `Kernel*` spellings of the same terms are accepted too) is not matched against anything: it is executed node by node
+ * (csrc/lum_generic.cu) with the CPU interpreter's semantics; max_seq / kv_dtype / max_new_tokens are ignored for it.  Inputs of any
+ * element type go in through lum_set_input, dynamic dimensions by any letter through lum_set_dim, results come back through
+ * lum_get_output (as f32) or lum_get_output_raw.  Any other graph — block ops that do not form the decoder schedule, or a mix of
+ * block ops and primitives outside it — is refused (LUM_E_INVALID, message names the node). */
 int32_t lum_llir_describe(const uint8_t* blob, size_t size, lum_model_desc* desc_out, int64_t* token_input, int64_t* pos_input,
                           int64_t* logits_output, char* err, size_t err_len);
 int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_seq, uint32_t kv_dtype, int32_t max_new_tokens);
@@ -157,6 +163,10 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
 int32_t lum_set_input(lum_rt* rt, int64_t hlir_node, const void* host, size_t bytes, uint32_t dtype);
 /* `get_f32(node_id)` for the graph's Output: the logits of the last row (n = vocab). */
 int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n);
+/* `get_i32` / `get_bool` / `get_f16` / `get_bf16` (crates/luminal_cuda/src/runtime.rs:206-236) for a graph of primitive ops: the
+ * result in its own element type.  dtype / n_elems (either may be NULL) receive the type and the element count; with host_out NULL
+ * nothing is copied (a size query). */
+int32_t lum_get_output_raw(lum_rt* rt, int64_t hlir_node, void* host_out, size_t capacity_bytes, uint32_t* dtype, size_t* n_elems);
 /* The `CudaInput::Ptr` case of `set_data` (crates/luminal_cuda/src/runtime.rs:36-39, 326-396): the input's bytes already sit
  * in device memory the caller owns.  Weights are repacked from there (no host round trip); token / position ids, a few
  * bytes, are read back once because the step's kernels take the token from the device-resident decode state. */

@@ -39,6 +39,19 @@ int lum_llir_lookup(const lum_llir_plan* p, int64_t hlir_node, int* slot, int* l
 const lum_model_desc* lum_llir_desc(const lum_llir_plan* p);
 void lum_llir_io(const lum_llir_plan* p, int64_t* tok, int64_t* pos, int64_t* out);
 int lum_llir_is_chunk(const lum_llir_plan* p);
+// the executor of primitive graphs (lum_generic.cu)
+struct lum_generic_plan;
+int lum_generic_accepts(const uint8_t* blob, size_t size);
+int lum_generic_make(const uint8_t* blob, size_t size, lum_generic_plan** out, std::string* err);
+void lum_generic_free(lum_generic_plan* p);
+int lum_generic_set_input(lum_generic_plan* p, int64_t hlir, const void* data, size_t bytes, uint32_t dtype, int device_ptr, cudaStream_t st, std::string* err);
+int lum_generic_alloc_input(lum_generic_plan* p, int64_t hlir, size_t n, cudaStream_t st, std::string* err);
+void lum_generic_clear(lum_generic_plan* p);
+int lum_generic_execute(lum_generic_plan* p, const std::map<char, int64_t>& dyn, cudaStream_t st, std::string* err);
+int lum_generic_output(lum_generic_plan* p, int64_t hlir, uint32_t* dtype, size_t* n, const void** dev, std::string* err);
+size_t lum_generic_launches(const lum_generic_plan* p);
+size_t lum_generic_nodes(const lum_generic_plan* p);
+cudaError_t lum_generic_to_f32(const void* src, uint32_t dtype, size_t n, float* dst, cudaStream_t st);
 uint32_t* lum_static_sample_status();   // csrc/lum_gemv.cu
 
 namespace {
@@ -176,6 +189,8 @@ struct lum_rt {
     cudaGraphExec_t g_batch = nullptr;
     int g_batch_n = 0;
     lum_llir_plan* llir = nullptr;    // set by lum_load_llir: which Input node feeds which weight slot
+    lum_generic_plan* generic = nullptr;      // set by lum_load_llir for a graph of primitive ops: it runs node by node, no decoder plan
+    std::map<char, int64_t> dyn;              // dynamic dimensions by letter (the decoder plan reads 's' and 'p' only)
     std::map<int64_t, size_t> dummy_inputs;   // lum_alloc_dummy_input calls made before a graph was loaded: node -> elements
     bool body_only = false;           // profiling a chunk of layers: steps never run the vocabulary head
     uint64_t n_tokens_run = 0, n_launches = 0;
@@ -1024,6 +1039,7 @@ void lum_destroy(lum_rt* rt) {
     free_model(rt);
     if (rt->comm) nccl().CommDestroy(rt->comm);
     if (rt->llir) lum_llir_free_plan(rt->llir);
+    if (rt->generic) lum_generic_free(rt->generic);
     cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -1044,6 +1060,20 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
     if (!rt || !blob) return fail(rt, LUM_E_INVALID, "load_llir: null argument");
     lum_llir_plan* plan = nullptr;
     std::string err;
+    if (lum_generic_accepts(blob, size)) {
+        // only primitive ops: no decoder to recognise, the graph runs node by node
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        lum_generic_plan* g = nullptr;
+        if (int r = lum_generic_make(blob, size, &g, &err)) return fail(rt, r, "load_llir: %s", err.c_str());
+        if (rt->generic) lum_generic_free(rt->generic);
+        rt->generic = g;
+        std::map<int64_t, size_t> pending;
+        pending.swap(rt->dummy_inputs);
+        for (const auto& kv : pending)
+            if (int r2 = lum_generic_alloc_input(g, kv.first, kv.second, rt->stream, &err)) return fail(rt, r2, "load_llir: %s", err.c_str());
+        return 0;
+    }
+    if (rt->generic) { lum_generic_free(rt->generic); rt->generic = nullptr; }
     if (int r = lum_llir_make_plan(blob, size, &plan, &err)) return fail(rt, r, "load_llir: %s", err.c_str());
     if (lum_llir_is_chunk(plan)) {
         lum_llir_free_plan(plan);
@@ -1066,6 +1096,13 @@ int32_t lum_load_llir(lum_rt* rt, const uint8_t* blob, size_t size, int32_t max_
 }
 
 int32_t lum_set_input(lum_rt* rt, int64_t hlir_node, const void* host, size_t bytes, uint32_t dtype) {
+    if (rt && rt->generic) {
+        if (!host && bytes) return fail(rt, LUM_E_INVALID, "set_input: null data");
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        std::string err;
+        if (int r = lum_generic_set_input(rt->generic, hlir_node, host, bytes, dtype, 0, rt->stream, &err)) return fail(rt, r, "set_input: %s", err.c_str());
+        return 0;
+    }
     if (!rt || !rt->llir || !rt->has_model) return fail(rt, LUM_E_INVALID, "set_input: no graph loaded (lum_load_llir)");
     if (!host) return fail(rt, LUM_E_INVALID, "set_input: null data");
     int64_t tok, pos, out;
@@ -1087,7 +1124,44 @@ int32_t lum_set_input(lum_rt* rt, int64_t hlir_node, const void* host, size_t by
     return lum_model_set_weight(rt, slot, layer, host, bytes, dtype);
 }
 
+int32_t lum_get_output_raw(lum_rt* rt, int64_t hlir_node, void* host_out, size_t capacity_bytes, uint32_t* dtype, size_t* n_elems) {
+    if (!rt || !rt->generic) return fail(rt, LUM_E_INVALID, "get_output_raw: no graph of primitive ops loaded (a decoder's output is read with lum_get_output / lum_get_logits)");
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    std::string err;
+    uint32_t dt = 0; size_t n = 0; const void* dev = nullptr;
+    if (int r = lum_generic_output(rt->generic, hlir_node, &dt, &n, &dev, &err)) return fail(rt, r, "get_output_raw: %s", err.c_str());
+    if (dtype) *dtype = dt;
+    if (n_elems) *n_elems = n;
+    if (!host_out) return 0;
+    const size_t bytes = n * (dt == LUM_F32 || dt == LUM_INT ? 4 : (dt == LUM_F16 || dt == LUM_BF16) ? 2 : 1);
+    if (bytes > capacity_bytes) return fail(rt, LUM_E_INVALID, "get_output_raw: the result holds %zu bytes, the buffer %zu", bytes, capacity_bytes);
+    if (bytes) CU(rt, cudaMemcpyAsync(host_out, dev, bytes, cudaMemcpyDeviceToHost, rt->stream));
+    CU(rt, cudaStreamSynchronize(rt->stream));
+    return 0;
+}
+
 int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n) {
+    if (rt && rt->generic) {
+        if (!host_out) return fail(rt, LUM_E_INVALID, "get_output: null output");
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        std::string err;
+        uint32_t dt = 0; size_t have = 0; const void* dev = nullptr;
+        if (int r = lum_generic_output(rt->generic, hlir_node, &dt, &have, &dev, &err)) return fail(rt, r, "get_output: %s", err.c_str());
+        if (have != n) return fail(rt, LUM_E_INVALID, "get_output: the result holds %zu elements, asked for %zu", have, n);
+        if (n == 0) return 0;
+        if (dt == LUM_F32) { CU(rt, cudaMemcpyAsync(host_out, dev, n * 4, cudaMemcpyDeviceToHost, rt->stream)); }
+        else {      // `get_f32` of a non-f32 result: converted on the device, as Cast would
+            float* tmp = nullptr;
+            CU(rt, cudaMalloc((void**)&tmp, n * 4));
+            cudaError_t e = lum_generic_to_f32(dev, dt, n, tmp, rt->stream);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
+            cudaStreamSynchronize(rt->stream);
+            cudaFree(tmp);
+            if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "get_output: %s", cudaGetErrorString(e));
+        }
+        CU(rt, cudaStreamSynchronize(rt->stream));
+        return 0;
+    }
     if (!rt || !rt->llir) return fail(rt, LUM_E_INVALID, "get_output: no graph loaded (lum_load_llir)");
     int64_t tok, pos, out;
     lum_llir_io(rt->llir, &tok, &pos, &out);
@@ -1099,6 +1173,12 @@ int32_t lum_get_output(lum_rt* rt, int64_t hlir_node, float* host_out, size_t n)
 // ---- the rest of the `Runtime` trait as `Graph::search` uses it -------------------------------------------------------
 
 int32_t lum_set_input_device_ptr(lum_rt* rt, int64_t hlir_node, const void* device_ptr, size_t bytes, uint32_t dtype) {
+    if (rt && rt->generic) {
+        if (!device_ptr) return fail(rt, LUM_E_INVALID, "set_input_device_ptr: null pointer");
+        std::string err;
+        if (int r = lum_generic_set_input(rt->generic, hlir_node, device_ptr, bytes, dtype, 1, rt->stream, &err)) return fail(rt, r, "set_input_device_ptr: %s", err.c_str());
+        return 0;
+    }
     if (!rt || !rt->llir || !rt->has_model) return fail(rt, LUM_E_INVALID, "set_input_device_ptr: no graph loaded (lum_load_llir)");
     if (!device_ptr) return fail(rt, LUM_E_INVALID, "set_input_device_ptr: null pointer");
     CU(rt, cudaSetDevice(rt->cfg.device));
@@ -1119,6 +1199,15 @@ int32_t lum_set_input_device_ptr(lum_rt* rt, int64_t hlir_node, const void* devi
 
 int32_t lum_alloc_dummy_input(lum_rt* rt, int64_t hlir_node, size_t n_elems) {
     if (!rt) return LUM_E_INVALID;
+    if (rt->generic) {
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        std::string err;
+        if (int r = lum_generic_alloc_input(rt->generic, hlir_node, n_elems, rt->stream, &err)) {
+            rt->dummy_inputs[hlir_node] = n_elems;        // not an Input of the loaded graph: kept for the next graph (a chunk being profiled)
+            return 0;
+        }
+        return 0;
+    }
     if (!rt->llir || !rt->has_model) { rt->dummy_inputs[hlir_node] = n_elems; return 0; }    // applied when the graph arrives
     CU(rt, cudaSetDevice(rt->cfg.device));
     int64_t tok, pos, out;
@@ -1149,6 +1238,7 @@ int32_t lum_alloc_dummy_input(lum_rt* rt, int64_t hlir_node, size_t n_elems) {
 int32_t lum_clear_intermediates(lum_rt* rt) {
     if (!rt) return LUM_E_INVALID;
     rt->dummy_inputs.clear();
+    if (rt->generic) { CU(rt, cudaSetDevice(rt->cfg.device)); CU(rt, cudaStreamSynchronize(rt->stream)); lum_generic_clear(rt->generic); }
     if (!rt->has_model) return 0;
     CU(rt, cudaSetDevice(rt->cfg.device));
     const lum_model_desc& d = rt->d;
@@ -1172,9 +1262,37 @@ int32_t lum_profile_llir(lum_rt* rt, const uint8_t* blob, size_t size, uint64_t 
                          char* display, size_t display_len) {
     if (!rt || !blob) return fail(rt, LUM_E_INVALID, "profile_llir: null argument");
     if (trials <= 0) trials = 1;
+    std::string err;
+    if (lum_generic_accepts(blob, size)) {
+        // a candidate made of primitive ops: run it node by node on stand-in inputs (the dummy inputs asked for so far, ones elsewhere
+        // would need shapes this call does not know: every Input must have been given by lum_alloc_dummy_input or be set on the loaded graph)
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        lum_generic_plan* g = nullptr;
+        if (int r = lum_generic_make(blob, size, &g, &err)) return fail(rt, r, "profile_llir: %s", err.c_str());
+        for (const auto& kv : rt->dummy_inputs) { std::string ignore; lum_generic_alloc_input(g, kv.first, kv.second, rt->stream, &ignore); }
+        std::map<char, int64_t> dyn = rt->dyn;
+        dyn['s'] = (int64_t)s_dim; dyn['p'] = (int64_t)p_dim;
+        cudaEvent_t e0, e1;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) { lum_generic_free(g); return fail(rt, LUM_E_CUDA, "profile_llir: cudaEventCreate failed"); }
+        int r = lum_generic_execute(g, dyn, rt->stream, &err);
+        cudaEventRecord(e0, rt->stream);
+        for (int i = 0; i < trials && !r; i++) r = lum_generic_execute(g, dyn, rt->stream, &err);
+        cudaEventRecord(e1, rt->stream);
+        cudaStreamSynchronize(rt->stream);
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        cudaEventDestroy(e0); cudaEventDestroy(e1);
+        const size_t n_nodes = lum_generic_nodes(g);
+        lum_generic_free(g);
+        if (r) return fail(rt, r, "profile_llir: %s", err.c_str());
+        const double us = (double)ms * 1000.0 / trials;
+        rt->last_profile_usec = us;
+        if (usec) *usec = us;
+        if (display && display_len) snprintf(display, display_len, "%.3f ms per execute (%zu primitive nodes, one launch each)", us / 1000.0, n_nodes);
+        return 0;
+    }
     if (s_dim == 0) s_dim = 1;
     lum_llir_plan* plan = nullptr;
-    std::string err;
     if (int r = lum_llir_make_plan(blob, size, &plan, &err)) return fail(rt, r, "profile_llir: %s", err.c_str());
     const bool chunk = lum_llir_is_chunk(plan) != 0;
     lum_model_desc d = *lum_llir_desc(plan);
@@ -1446,6 +1564,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     CU(rt, cudaSetDevice(rt->cfg.device));
     cudaStreamSynchronize(rt->stream);
     free_model(rt);
+    if (rt->generic) { lum_generic_free(rt->generic); rt->generic = nullptr; }      // a decoder replaces a loaded graph of primitive ops
     lum_model_desc d = *dp;
     if (d.tp_size <= 0) { d.tp_size = 1; d.tp_rank = 0; }
     if (d.max_batch <= 0) d.max_batch = 1;
@@ -1758,9 +1877,11 @@ int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float
 
 int32_t lum_set_dim(lum_rt* rt, char dim, uint64_t value) {
     if (!rt) return LUM_E_INVALID;
+    const bool letter = (dim >= 'a' && dim <= 'z') || (dim >= 'A' && dim <= 'Z');
     if (dim == 's') rt->dim_s = value;
     else if (dim == 'p') rt->dim_p = value;
-    else return fail(rt, LUM_E_INVALID, "set_dim: unknown dynamic dimension '%c' (this plan has 's' and 'p')", dim);
+    else if (!rt->generic || !letter) return fail(rt, LUM_E_INVALID, "set_dim: unknown dynamic dimension '%c' (a decoder plan has 's' and 'p')", dim);
+    rt->dyn[dim] = (int64_t)value;
     return 0;
 }
 
@@ -1771,6 +1892,14 @@ int32_t lum_set_tokens(lum_rt* rt, const int32_t* ids, size_t n) {
 }
 
 int32_t lum_execute(lum_rt* rt) {
+    if (rt && rt->generic) {
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        std::string err;
+        const size_t before = lum_generic_launches(rt->generic);
+        const int r = lum_generic_execute(rt->generic, rt->dyn, rt->stream, &err);
+        rt->n_launches += lum_generic_launches(rt->generic) - before;
+        return r ? fail(rt, r, "execute: %s", err.c_str()) : 0;
+    }
     if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "execute: no model loaded");
     CU(rt, cudaSetDevice(rt->cfg.device));
     const uint64_t s = rt->dim_s, p = rt->dim_p;

@@ -204,6 +204,7 @@ def load_library() -> C.CDLL:
         "lum_debug_wait_timeout": (i32, [vp]),
         "lum_op_status": (i32, [vp]),
         "lum_get_output": (i32, [vp, C.c_int64, P(C.c_float), sz]),
+        "lum_get_output_raw": (i32, [vp, C.c_int64, vp, sz, P(u32), P(sz)]),
         "lum_kv_reset": (i32, [vp]),
         "lum_kv_read": (i32, [vp, i32, i32, i32, P(C.c_float)]),
         "lum_set_dim": (i32, [vp, C.c_char, u64]),
@@ -442,8 +443,14 @@ class B200Runtime:
 
     def load_llir(self, blob: bytes, max_seq: int = 4096, kv_dtype: str = "bf16", max_new_tokens: int = 4096) -> None:
         """``Runtime::load_llir`` (src/op.rs:16): recognise the decoder a serialised graph describes and set it up."""
-        d, tok, pos, out = describe_llir(blob)
         buf = C.create_string_buffer(blob, len(blob))
+        try:
+            d, tok, pos, out = describe_llir(blob)
+        except LumError:
+            # not a decoder: a graph of primitive ops runs node by node (anything else is refused by the library, with the reason)
+            self._ck(self._lib.lum_load_llir(self._h, buf, len(blob), max_seq, DTYPE[kv_dtype], max_new_tokens))
+            self.desc = None
+            return
         self._ck(self._lib.lum_load_llir(self._h, buf, len(blob), max_seq, DTYPE[kv_dtype], max_new_tokens))
         self.desc = d.copy(max_seq=max_seq, kv_dtype=DTYPE[kv_dtype], max_new_tokens=max_new_tokens)
         self.token_input, self.pos_input, self.logits_output = tok, pos, out
@@ -498,9 +505,25 @@ class B200Runtime:
     def get_output(self, hlir_node: int):
         """``get_f32(node_id)`` (crates/luminal_cuda/src/runtime.rs:168-204) for the graph's Output: last-row logits."""
         import numpy as np
-        out = np.empty(self.desc.vocab, dtype=np.float32)
+        if self.desc is None:       # a graph of primitive ops: whatever the Output holds, as f32
+            n = C.c_size_t()
+            self._ck(self._lib.lum_get_output_raw(self._h, hlir_node, None, 0, None, C.byref(n)))
+            out = np.empty(n.value, dtype=np.float32)
+        else:
+            out = np.empty(self.desc.vocab, dtype=np.float32)
         self._ck(self._lib.lum_get_output(self._h, hlir_node, out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
         return out
+
+    def get_output_raw(self, hlir_node: int):
+        """The result an Output of a primitive graph names, in its own element type: float32 / int32 / uint8 (Bool) arrays, and
+        uint16 bit patterns for f16 / bf16.  Returns ``(dtype_name, array)``."""
+        import numpy as np
+        dt, n = C.c_uint32(), C.c_size_t()
+        self._ck(self._lib.lum_get_output_raw(self._h, hlir_node, None, 0, C.byref(dt), C.byref(n)))
+        name = {v: k for k, v in DTYPE.items()}[dt.value]
+        out = np.empty(n.value, dtype={"f32": np.float32, "int": np.int32, "bool": np.uint8, "f16": np.uint16, "bf16": np.uint16}[name])
+        self._ck(self._lib.lum_get_output_raw(self._h, hlir_node, out.ctypes.data_as(C.c_void_p), out.nbytes, None, None))
+        return name, out
 
     def set_weight(self, slot: str, layer: int, data, dtype: str) -> None:
         """``data``: a C-contiguous numpy array holding f32 values, bf16 bit patterns (uint16) or Q8_0 wire blocks (uint8)."""
