@@ -13,6 +13,7 @@ from .runtime import (  # noqa: F401
     B200Runtime,
     LumError,
     ModelDesc,
+    Config,
     CONFIGS,
     DTYPE,
     SLOT,

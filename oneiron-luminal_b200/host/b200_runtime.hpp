@@ -95,10 +95,31 @@ public:
         ck(lum_profile(h_, trials, &us, buf, sizeof buf));
         return {us, buf};
     }
-    // allocate_dummy_input / clear_intermediate_buffers (src/op.rs:24-29) have nothing to do here:
-    // the plan owns fixed activation buffers and no intermediate is ever re-zeroed.
-    void allocate_dummy_input(size_t, size_t) {}
-    void clear_intermediate_buffers() {}
+    // The part of the trait `Graph::search` drives (src/op.rs:18-29; src/graph.rs:293-302, 337, 351-352)
+    void allocate_dummy_input(int64_t node_index, size_t num_elements) { ck(lum_alloc_dummy_input(h_, node_index, num_elements)); }
+    void clear_intermediate_buffers() { ck(lum_clear_intermediates(h_)); }
+    std::pair<ProfileMetric, std::string> profile(const std::vector<uint8_t>& blob, const std::map<char, size_t>& dyn_map, int trials) {
+        double us = 0; char buf[160] = {0};
+        auto dim = [&](char c, size_t dflt) { auto it = dyn_map.find(c); return it == dyn_map.end() ? dflt : it->second; };
+        ck(lum_profile_llir(h_, blob.data(), blob.size(), dim('s', 1), dim('p', 0), trials, &us, buf, sizeof buf));
+        return {us, buf};
+    }
+    // `load_safetensors(cx, path)` (crates/luminal_cuda/src/runtime.rs:133-158): returns {tensors stored, tensors skipped}
+    std::pair<int, int> load_safetensors(const std::string& path) {
+        int32_t a = 0, b = 0;
+        ck(lum_load_safetensors(h_, path.c_str(), &a, &b));
+        return {a, b};
+    }
+    void save_safetensors(const std::string& path) { ck(lum_save_safetensors(h_, path.c_str())); }
+    // a graph of primitive ops: any Output, converted to f32
+    std::vector<float> get_f32(int64_t node) {
+        size_t n = 0;
+        ck(lum_get_output_raw(h_, node, nullptr, 0, nullptr, &n));
+        std::vector<float> out(n);
+        ck(lum_get_output(h_, node, out.data(), n));
+        return out;
+    }
+    lum_stats stats() const { lum_stats s; lum_get_stats(h_, &s); return s; }
 
     lum_rt* raw() const { return h_; }
 
