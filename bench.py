@@ -400,6 +400,15 @@ def run_ours(args, pkg):
             "gpu_launches": launches_step * n_tok,
             "clocks": clocks,
         }
+        # the reference bench crate's derived figures (crates/luminal_bench/src/metrics.rs:13-60) for this step
+        from oneiron_luminal_b200.metrics import BenchMetricsMap, HardwareSpec, decode_step_metrics
+        mm = BenchMetricsMap(HardwareSpec("NVIDIA B200", 180.0, peaks["hbm_gbs"] * world, peaks["bf16_tflops"] * world))
+        name = f"decode/{WORKLOAD}/p{p_start}"
+        mm.add(name, decode_step_metrics(desc, p_start + n_tok // 2))
+        line["mbu_mfu"] = dict(mm.summary(name, 1e6 / value), benchmark=name, peaks=f"of {peak_kind}")
+        if args.report:
+            with open(args.report, "w") as fh:
+                fh.write(mm.to_json())
         if world == 1 and not args.no_cpu:
             try:
                 v, threads, sample, _ = cpu_port_tokens_per_s(pkg, 8, 1, min(p_start, 2048))
@@ -646,6 +655,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--report", default=None, help="also write the byte / flop counts of the timed step as a metrics JSON in the reference bench crate's format")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt tokens before the timed decode (profiling runs use a short one)")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP)
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8", "llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096", "gpt_oss_20b_q8"],
