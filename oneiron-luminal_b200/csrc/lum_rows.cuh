@@ -56,6 +56,7 @@ struct AttnRowsArgs {
     const int* row_pos; const int* row_seq; int seq0;
     float* out;                // [M][n_q * hd]
     int M, n_q, n_kv, hd, kv_bf16, window, max_seq, max_batch;
+    uint32_t* status;
 };
 struct ArgmaxRowsArgs {
     float* logits;             // [n_parts][M][vocab]; the sums end up in plane 0
@@ -75,6 +76,8 @@ cudaError_t launch_gemm(const GemmArgs& a, int sm_count, cudaStream_t st);
 cudaError_t launch_embed_rows(const void* table, int kind, int H, int vocab, const int* row_tok, float* x, int M, uint32_t* status, cudaStream_t st);
 cudaError_t launch_rope_append_rows(const RopeRowsArgs& a, cudaStream_t st);
 cudaError_t launch_attn_rows(const AttnRowsArgs& a, cudaStream_t st);
+bool attn_prompt_tc_supported(const AttnRowsArgs& a);            // lum_attn_tc.cu: rows of one sequence, bf16 cache, head dimension 128
+cudaError_t launch_attn_prompt_tc(const AttnRowsArgs& a, cudaStream_t st);
 cudaError_t launch_argmax_rows(const ArgmaxRowsArgs& a, cudaStream_t st);
 cudaError_t launch_step_advance(int* step, cudaStream_t st);
 

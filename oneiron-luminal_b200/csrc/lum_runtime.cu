@@ -786,7 +786,11 @@ int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int se
             AttnRowsArgs a{};
             a.q_rot = b.q_rot; a.k_cache = w.kc; a.v_cache = w.vc; a.row_pos = d_pos; a.row_seq = d_seq; a.seq0 = seq0; a.out = b.attn;
             a.M = M; a.n_q = rt->nq_l; a.n_kv = rt->nkv_l; a.hd = hd; a.kv_bf16 = t.kv_bf16; a.window = 0; a.max_seq = d.max_seq; a.max_batch = rt->max_batch;
-            CU(rt, launch_attn_rows(a, st));
+            a.status = rt->status;
+            // many rows of one sequence (a prompt): the tensor-core kernel; few rows, or rows of different sequences: one CTA per row
+            static const int env_tc = [] { const char* e = getenv("LUM_ATTN_TC"); return e ? atoi(e) : 1; }();
+            if (env_tc && M >= 16 && attn_prompt_tc_supported(a)) CU(rt, launch_attn_prompt_tc(a, st));
+            else CU(rt, launch_attn_rows(a, st));
             launches += 2;
         }
         {   // attention output -> operand of the o projection
