@@ -5,24 +5,33 @@
 // on the 5th-generation tensor cores.
 //
 // Arithmetic.  The CPU restatement multiplies f32 activations by exactly dequantised weights, and greedy decoding over a
-// large vocabulary only stays token-exact at f32-level accuracy, so the activations are NOT rounded to a 8- or 16-bit
-// type.  As in the GEMV, every 32-block of an activation row is written as three int8 levels,
-//     x ~= s * (a1 + a2/254 + a3/254^2),   |error| <= max|x| * 2^-24,
-// the tensor core forms the three exact integer dot products of a weight block with them (tcgen05.mma kind::i8, s32
-// accumulators in tensor memory), and the block scales (f16 of the weights, f32 of the activations) are applied in f32
-// when the accumulators are read back.  Q8_0 has one scale per 32 weights ALONG K, so an accumulator can only hold one
-// K-block: one instruction (M = 128 weight rows, N = 96 = 32 activation rows x 3 levels, K = 32) per K-block, five
-// accumulators rotating through tensor memory, and 8 draining warps that turn each into f32 partial sums held in registers.
+// large vocabulary only stays token-exact at f32-level accuracy, so neither operand may simply be rounded to 16 bits.
+// Both are written as short sums of binary16 terms instead, and the tensor core (tcgen05.mma kind::f16, f32 accumulators in
+// tensor memory) adds up the products of the terms:
+//   * a weight w = q * d (q int8, d binary16) has at most 18 significant bits.  1024 w = hi + lo EXACTLY, with
+//     hi = f16(q * 1024 d) and lo = q * 1024 d - hi (one fused multiply-add); the factor 1024 keeps lo out of the binary16
+//     subnormals whatever d is.  Two instructions per pair of weights, on the packed-half units.
+//   * an activation row is scaled by a power of two that puts its largest magnitude in [2^13, 2^14) and split into three
+//     terms x1 + x2 + x3 (successive binary16 roundings of the residual): 33 bits, so the only loss is below 2^-24 of the
+//     element or 2^-38 of the row's maximum.
+//   * five products are accumulated: hi x1, hi x2, hi x3, lo x1, lo x2 (lo x3 is below 2^-33 of the result).
+// Q8_0's per-32 scales therefore never leave the operand: ONE accumulator per output tile runs over the whole K range and is
+// read back once, instead of once per 32-block (which is what binds an integer formulation: the read-back, not the tensor core).
+// The power-of-two factors (1024 and the row's) are undone exactly when the accumulator is stored.
 //
 // Two kernels:
 //  * rows_quantize — one CTA per activation row.  Forms the row (sum of the previous product's K-split partials, residual
 //    add, SwiGLU), optionally RMS-normalises it (`RowRMSNorm`, ops.rs:519-566; `RowSwishMul`, ops.rs:303-325; `RowAdd`,
-//    ops.rs:135-146 are fused here), writes the three levels in tensor-core operand order and the block scales.
-//  * q8_gemm_tc — persistent CTAs over work items (128 weight rows, one chunk of 32 activation rows, one K range).  A
-//    producer warp fills two shared-memory rings with bulk copies (weights: whole K-tiles of 16 row groups, 68 KiB;
-//    activations: half K-tiles, 24 KiB + scales), one thread issues the tensor-core instructions, 8 warps drain.
+//    ops.rs:135-146 are fused here), writes the three terms in tensor-core operand order and the row's output factor.
+//  * q8_gemm_tc — persistent CTAs over work items (128 weight rows, one chunk of up to 128 activation rows, one K range).
+//    A producer warp fills two shared-memory rings with bulk copies (weights: whole K-tiles of 16 row groups, 68 KiB;
+//    activations: 32-column slices of the three terms), 8 warps turn each 32-column slice of the int8 tile stream into the
+//    hi / lo operands, one thread issues the tensor-core instructions (10 per slice), and the same 8 warps store the
+//    accumulator when an item's K range is done (two accumulators alternate, so the next item's products run meanwhile).
 //    Outputs are plain f32 stores of K-split partial planes; whoever consumes them (the next rows_quantize) adds them up.
 #include <cstdlib>
+
+#include <cuda_fp16.h>
 
 #include "lum_gemv_dev.cuh"
 #include "lum_rows.cuh"
@@ -31,35 +40,50 @@ namespace lum {
 
 constexpr int kGmRows = 128;                        // weight rows per work item: 16 row groups
 constexpr int kGmRG = kGmRows / kTileRows;
-constexpr int kGmMB = 32;                           // activation rows per chunk
-constexpr int kGmCols = 3 * kGmMB;                  // accumulator columns per K-block
-constexpr int kGmXBlock = kGmCols * 32;             // bytes of the activation operand of one K-block: 96 operand rows x 32
-constexpr int kGmWStage = kGmRG * kTileBytes;       // 69632
-constexpr int kGmXHalf = 8 * kGmXBlock;             // 24576: the 8 K-blocks of half a K-tile
-constexpr int kGmSxHalf = 8 * kGmMB * 4;            // their f32 block scales
-constexpr int kGmXStage = kGmXHalf + kGmSxHalf;
-constexpr int kGmWStages = 2, kGmXStages = 3, kGmAcc = 5;
-constexpr int kGmDrainWarps = 8;
-constexpr int kGmThreads = (kGmDrainWarps + 2) * 32;   // + producer warp + tensor-core warp
+constexpr int kGmMaxChunk = 128;                    // activation rows per chunk: 32, 64 or 128 (gemm_chunk_rows)
+constexpr int kGmWStage = kGmRG * kTileBytes;       // 69632: one K-tile of 128 weight rows, as streamed
+constexpr int kGmCvtBytes = 2 * kGmRows * 32 * 2;   // 16384: hi and lo operands of one 32-column slice
+constexpr int kGmXStageMax = 3 * kGmMaxChunk * 32 * 2;   // 24576: the three activation terms of one slice
+constexpr int kGmWStages = 2, kGmCvtBufs = 2, kGmXStages = 2;
+constexpr int kGmCvtWarps = 8;
+constexpr int kGmThreads = (kGmCvtWarps + 2) * 32;   // + producer warp + tensor-core warp
 constexpr int kGmBarBytes = 256;
-constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmXStages * kGmXStage;
+constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmCvtBufs * kGmCvtBytes + (size_t)kGmXStages * kGmXStageMax;
+constexpr int kGmWExp = 10;                         // weights enter as 2^10 w
+constexpr uint32_t kGmTmemCols = 256;               // two accumulators of up to 128 columns
 
+// activation rows per chunk for a product of M rows
+__host__ __device__ inline int gemm_chunk_rows(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+__device__ __forceinline__ float block_max(float v, float* scratch, int tid, int nthreads, int bar_id) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    named_sync(bar_id, nthreads);
+    if ((tid & 31) == 0) scratch[tid >> 5] = v;
+    named_sync(bar_id, nthreads);
+    float t = 0.0f;
+    for (int w = 0; w < (nthreads >> 5); w++) t = fmaxf(t, scratch[w]);
+    return t;
+}
+
+// activation operand: [chunk][K / 32 slices][3 terms][4 groups of 8 columns][chunk rows][16 bytes]
 __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     extern __shared__ __align__(16) float rowbuf[];          // K floats + 8 words of reduction scratch
     const int m = blockIdx.x, tid = threadIdx.x;
     const int K = a.K, nb = K >> 5;
     float* scratch = rowbuf + K;
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
-    int8_t* xq_chunk = a.xq + (size_t)(m / kGmMB) * nb * kGmXBlock;
-    float* sx_chunk = a.sx + (size_t)(m / kGmMB) * nb * kGmMB;
-    const int ml = m % kGmMB;
+    const int nc = gemm_chunk_rows(a.M);
+    const size_t slice_bytes = (size_t)3 * 4 * nc * 16;
+    unsigned char* xq_chunk = (unsigned char*)a.xq + (size_t)(m / nc) * nb * slice_bytes;
+    const int ml = m % nc;
     if (m >= a.M) {
-        // padding row of the last chunk: zeros (scale 0 makes its products vanish whatever the quants are)
-        for (int i = tid; i < nb * 24; i += 256) {             // 96 bytes per block = 24 words
-            const int b = i / 24, w = i - b * 24, level = w >> 3, j0 = (w & 7) << 2, row = ml * 3 + level;
-            *(uint32_t*)(xq_chunk + (size_t)b * kGmXBlock + ((row >> 3) << 8) + ((j0 >> 4) << 7) + ((row & 7) << 4) + (j0 & 15)) = 0u;
+        // padding row of the last chunk: zeros
+        for (int ch = tid; ch < nb * 12; ch += 256) {
+            const int s = ch / 12, tc = ch - s * 12;           // (term, column group) of slice s
+            *(uint4*)(xq_chunk + (size_t)s * slice_bytes + (size_t)tc * nc * 16 + ml * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
-        for (int b = tid; b < nb; b += 256) sx_chunk[(size_t)b * kGmMB + ml] = 0.0f;
+        if (tid == 0) a.sx[m] = 0.0f;
         return;
     }
     float ss = 0.0f;
@@ -89,46 +113,51 @@ __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     } else {
         __syncthreads();
     }
-    // 8 consecutive threads own one 32-block; same three-level rounding as the GEMV prologue (lum_gemv_dev.cuh)
-    for (int f4 = tid; f4 < ((K >> 2) + 255) / 256 * 256; f4 += 256) {
-        const bool in = f4 < (K >> 2);
-        float4 cur = in ? ((const float4*)rowbuf)[f4] : make_float4(0.f, 0.f, 0.f, 0.f);
-        float e[4] = {cur.x, cur.y, cur.z, cur.w};
-        if (a.gain && in) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) e[j] = (inv * e[j]) * load_gain(a.gain, a.gain_kind, f4 * 4 + j);
+    // the normalised row, and its largest magnitude
+    float amax = 0.0f;
+    for (int f4 = tid; f4 < (K >> 2); f4 += 256) {          // each thread revisits the elements it wrote
+        float4 v = ((const float4*)rowbuf)[f4];
+        if (a.gain) {
+            v.x = (inv * v.x) * load_gain(a.gain, a.gain_kind, f4 * 4);
+            v.y = (inv * v.y) * load_gain(a.gain, a.gain_kind, f4 * 4 + 1);
+            v.z = (inv * v.z) * load_gain(a.gain, a.gain_kind, f4 * 4 + 2);
+            v.w = (inv * v.w) * load_gain(a.gain, a.gain_kind, f4 * 4 + 3);
+            ((float4*)rowbuf)[f4] = v;
         }
-        float amax = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const float s1 = amax * (1.0f / 127.0f);
-        const float i1 = amax > 0.0f ? 127.0f / amax : 0.0f;
-        const float s2 = s1 * (1.0f / 254.0f), i2 = i1 * 254.0f;
-        const float i3 = i1 * 64516.0f;
-        constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: the sum's low mantissa byte is the rounded integer
-        uint32_t p1 = 0, p2 = 0, p3 = 0;
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    amax = block_max(amax, scratch, tid, 256, 1);           // (its barriers also publish the row to the other threads)
+    // power of two that puts the maximum in [2^13, 2^14); a zero (or non-finite) row keeps factor 1
+    int ex = 0;
+    if (amax > 0.0f && amax < INFINITY) frexpf(amax, &ex);
+    else ex = 14;
+    const float up = ldexpf(1.0f, 14 - ex);
+    if (tid == 0) a.sx[m] = ldexpf(1.0f, ex - 14 - kGmWExp);       // undoes this factor and the weights' 2^10
+    for (int c8 = tid; c8 < (K >> 3); c8 += 256) {
+        const float4 v0 = ((const float4*)rowbuf)[2 * c8], v1 = ((const float4*)rowbuf)[2 * c8 + 1];
+        const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        uint32_t t1[4], t2[4], t3[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float t1 = fmaf(e[j], i1, kMagic);
-            const float r1 = fmaf(-s1, t1 - kMagic, e[j]);
-            const float t2 = fmaf(r1, i2, kMagic);
-            const float r2 = fmaf(-s2, t2 - kMagic, r1);
-            const float t3 = fmaf(r2, i3, kMagic);
-            p1 |= (__float_as_uint(t1) & 0xffu) << (8 * j);
-            p2 |= (__float_as_uint(t2) & 0xffu) << (8 * j);
-            p3 |= (__float_as_uint(t3) & 0xffu) << (8 * j);
+            __half h[2][3];
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const float x = e[2 * j + q] * up;                       // exact: a power of two
+                h[q][0] = __float2half_rn(x);
+                const float r1 = x - __half2float(h[q][0]);              // exact in f32
+                h[q][1] = __float2half_rn(r1);
+                const float r2 = r1 - __half2float(h[q][1]);
+                h[q][2] = __float2half_rn(r2);
+            }
+            t1[j] = (uint32_t)__half_as_ushort(h[0][0]) | ((uint32_t)__half_as_ushort(h[1][0]) << 16);
+            t2[j] = (uint32_t)__half_as_ushort(h[0][1]) | ((uint32_t)__half_as_ushort(h[1][1]) << 16);
+            t3[j] = (uint32_t)__half_as_ushort(h[0][2]) | ((uint32_t)__half_as_ushort(h[1][2]) << 16);
         }
-        if (in) {
-            const int blk = f4 >> 3, j0 = (f4 & 7) << 2;
-            const int inner = ((j0 >> 4) << 7) + (j0 & 15);
-            int8_t* dst = xq_chunk + (size_t)blk * kGmXBlock;
-            const int n1 = ml * 3, n2 = n1 + 1, n3 = n1 + 2;          // operand rows of this activation row's three levels
-            *(uint32_t*)(dst + ((n1 >> 3) << 8) + ((n1 & 7) << 4) + inner) = p1;
-            *(uint32_t*)(dst + ((n2 >> 3) << 8) + ((n2 & 7) << 4) + inner) = p2;
-            *(uint32_t*)(dst + ((n3 >> 3) << 8) + ((n3 & 7) << 4) + inner) = p3;
-            if ((tid & 7) == 0) sx_chunk[(size_t)blk * kGmMB + ml] = s1;
-        }
+        const int s = c8 >> 2, cg = c8 & 3;
+        unsigned char* dst = xq_chunk + (size_t)s * slice_bytes + (size_t)cg * nc * 16 + ml * 16;
+        *(uint4*)(dst) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
+        *(uint4*)(dst + (size_t)4 * nc * 16) = make_uint4(t2[0], t2[1], t2[2], t2[3]);
+        *(uint4*)(dst + (size_t)8 * nc * 16) = make_uint4(t3[0], t3[1], t3[2], t3[3]);
     }
 }
 
@@ -151,25 +180,44 @@ __device__ __forceinline__ GemmItem gemm_item(const GemmArgs& a, int item, int t
     return it;
 }
 
+// packed binary16 arithmetic on plain 32-bit registers
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) { uint32_t d; asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) { uint32_t d; asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) { uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
+
+// kind::f16 with binary16 operands, f32 accumulators, both operands K-major, shape M x N (K = 16)
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N) { return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24); }
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bars = smem_u32(smem);
-    const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 56, tfull = bars + 80, tempty = bars + 120,
-                   fin = bars + 160, tmem_slot = bars + 168;
+    const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 48, cfull = bars + 64, cempty = bars + 80,
+                   afull = bars + 96, aempty = bars + 112, fin = bars + 128, tmem_slot = bars + 136;
     unsigned char* wst = (unsigned char*)(((uintptr_t)smem + kGmBarBytes + 127) & ~(uintptr_t)127);
-    unsigned char* xst = wst + (size_t)kGmWStages * kGmWStage;
+    unsigned char* cst = wst + (size_t)kGmWStages * kGmWStage;
+    unsigned char* xst = cst + (size_t)kGmCvtBufs * kGmCvtBytes;
     volatile int* abort = &s_abort;
     if (tid == 0) {
         s_abort = 0;
-        for (int i = 0; i < kGmWStages; i++) { mbar_init(wfull + 8u * i, 1); mbar_init(wempty + 8u * i, kGmDrainWarps + 1); }
-        for (int i = 0; i < kGmXStages; i++) { mbar_init(xfull + 8u * i, 1); mbar_init(xempty + 8u * i, kGmDrainWarps + 1); }
-        for (int i = 0; i < kGmAcc; i++) { mbar_init(tfull + 8u * i, 1); mbar_init(tempty + 8u * i, kGmDrainWarps); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(wfull + 8u * i, 1); mbar_init(wempty + 8u * i, kGmCvtWarps);
+            mbar_init(xfull + 8u * i, 1); mbar_init(xempty + 8u * i, 1);
+            mbar_init(cfull + 8u * i, kGmCvtWarps); mbar_init(cempty + 8u * i, 1);
+            mbar_init(afull + 8u * i, 1); mbar_init(aempty + 8u * i, kGmCvtWarps);
+        }
         mbar_init(fin, 1);
         mbar_fence_init();
     }
-    if (warp == kGmDrainWarps + 1) tmem_alloc(tmem_slot, 512);
+    if (warp == kGmCvtWarps + 1) tmem_alloc(tmem_slot, kGmTmemCols);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -178,12 +226,15 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }     // the activation operand comes from the previous kernel
 
     const int tpr = a.K / kTileK, nb = a.K >> 5;
+    const int nc = a.nc;                                   // activation rows per chunk
+    const uint32_t x_term = (uint32_t)nc * 64u;            // bytes of one term of one slice: 4 column groups x nc rows x 16
+    const uint32_t x_slice = 3u * x_term;
     int tiles = 0;
     for (int s = 0; s < a.nseg; s++) tiles += (a.seg[s].rows + kGmRows - 1) / kGmRows;
     const int n_items = tiles * a.ksplit * a.m_chunks;
     auto fail = [&](uint32_t code) { if (!*abort) { atomicOr(a.status, code); *abort = 1; } };
 
-    if (warp == kGmDrainWarps) {
+    if (warp == kGmCvtWarps) {
         // ---------------------------------------------------------------- producer: one lane
         if (lane == 0) {
             uint32_t wi = 0, xi = 0;
@@ -192,165 +243,167 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                 const GemmItem it = gemm_item(a, item, tpr);
                 const unsigned char* wseg = a.seg[it.seg].w;
                 for (int t = it.t0; t < it.t1 && ok; t++) {
-                    const uint32_t ws = wi % kGmWStages;
-                    if (!mbar_wait_abortable(wempty + 8u * ws, ((wi / kGmWStages) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                    const uint32_t ws = wi & 1u;
+                    if (!mbar_wait_abortable(wempty + 8u * ws, ((wi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
                     mbar_arrive_expect_tx(wfull + 8u * ws, (uint32_t)it.n_rg * kTileBytes);
                     for (int j = 0; j < it.n_rg; j++)
                         bulk_g2s(smem_u32(wst + (size_t)ws * kGmWStage + (size_t)j * kTileBytes),
                                  wseg + ((size_t)(it.rg0 + j) * tpr + t) * kTileBytes, kTileBytes, wfull + 8u * ws);
                     wi++;
-                    for (int h = 0; h < 2 && ok; h++) {
-                        const uint32_t xs = xi % kGmXStages;
-                        if (!mbar_wait_abortable(xempty + 8u * xs, ((xi / kGmXStages) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
-                        const size_t blk = (size_t)it.mc * nb + (size_t)t * 16 + (size_t)h * 8;
-                        mbar_arrive_expect_tx(xfull + 8u * xs, kGmXStage);
-                        bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStage), a.xq + blk * kGmXBlock, kGmXHalf, xfull + 8u * xs);
-                        bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStage + kGmXHalf), a.sx + blk * kGmMB, kGmSxHalf, xfull + 8u * xs);
+                    for (int s = 0; s < 16 && ok; s++) {
+                        const uint32_t xs = xi & 1u;
+                        if (!mbar_wait_abortable(xempty + 8u * xs, ((xi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                        mbar_arrive_expect_tx(xfull + 8u * xs, x_slice);
+                        bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStageMax), (const unsigned char*)a.xq + ((size_t)it.mc * nb + (size_t)t * 16 + s) * x_slice,
+                                 x_slice, xfull + 8u * xs);
                         xi++;
                     }
                 }
             }
             if (!ok) {
                 // never leave while a copy into this CTA's shared memory may be in flight: wait (bounded) for what was armed
-                for (uint32_t k = 0; k < kGmWStages && k < wi; k++) { const uint32_t i = wi - 1 - k; mbar_wait(wfull + 8u * (i % kGmWStages), (i / kGmWStages) & 1u); }
-                for (uint32_t k = 0; k < kGmXStages && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i % kGmXStages), (i / kGmXStages) & 1u); }
+                for (uint32_t k = 0; k < 2 && k < wi; k++) { const uint32_t i = wi - 1 - k; mbar_wait(wfull + 8u * (i & 1u), (i >> 1) & 1u); }
+                for (uint32_t k = 0; k < 2 && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i & 1u), (i >> 1) & 1u); }
             }
         }
         return;
     }
-    if (warp == kGmDrainWarps + 1) {
+    if (warp == kGmCvtWarps + 1) {
         // ---------------------------------------------------------------- tensor-core warp: one lane issues
         if (lane == 0) {
-            uint32_t wi = 0, xi = 0, ai = 0;
+            uint32_t xi = 0, ci = 0, ic = 0;
             bool ok = true;
-            constexpr uint32_t idesc = umma_idesc_s8(kGmRows, kGmCols);
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const uint32_t idesc = umma_idesc_f16(kGmRows, nc);
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ic++) {
                 const GemmItem it = gemm_item(a, item, tpr);
+                const uint32_t ab = ic & 1u;
+                if (!mbar_wait_abortable(aempty + 8u * ab, ((ic >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_TMEM); break; }
+                tc_fence_after_sync();
+                const uint32_t acc = tmem + ab * (uint32_t)kGmMaxChunk;
+                uint32_t started = 0;
                 for (int t = it.t0; t < it.t1 && ok; t++) {
-                    const uint32_t ws = wi % kGmWStages;
-                    if (!mbar_wait_abortable(wfull + 8u * ws, (wi / kGmWStages) & 1u, abort)) { fail(LUM_ST_WAIT_FULL); ok = false; break; }
-                    const uint32_t wbase = smem_u32(wst + (size_t)ws * kGmWStage);
-                    for (int h = 0; h < 2 && ok; h++) {
-                        const uint32_t xs = xi % kGmXStages;
-                        if (!mbar_wait_abortable(xfull + 8u * xs, (xi / kGmXStages) & 1u, abort)) { fail(LUM_ST_WAIT_FULL); ok = false; break; }
-                        const uint32_t xbase = smem_u32(xst + (size_t)xs * kGmXStage);
-                        tc_fence_after_sync();
-                        for (int bb = 0; bb < 8; bb++) {
-                            const uint32_t buf = ai % kGmAcc;
-                            if (!mbar_wait_abortable(tempty + 8u * buf, ((ai / kGmAcc) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_TMEM); ok = false; break; }
-                            tc_fence_after_sync();
-                            // A: the 128 weight rows' quants of K-block h*8+bb: 8-row groups 4352 bytes apart (one tile per row
-                            // group), the two 16-byte K halves 128 bytes apart.  B: 96 activation operand rows, groups 256 apart.
-                            const uint64_t da = umma_smem_desc(wbase + (uint32_t)(h * 8 + bb) * 256u, 128u, (uint32_t)kTileBytes);
-                            const uint64_t db = umma_smem_desc(xbase + (uint32_t)bb * kGmXBlock, 128u, 256u);
-                            umma_s8_ss(tmem + buf * kGmCols, da, db, idesc);
-                            umma_commit(tfull + 8u * buf);
-                            ai++;
+                    for (int s = 0; s < 16; s++) {
+                        const uint32_t cb = ci & 1u, xs = xi & 1u;
+                        if (!mbar_wait_abortable(cfull + 8u * cb, (ci >> 1) & 1u, abort) || !mbar_wait_abortable(xfull + 8u * xs, (xi >> 1) & 1u, abort)) {
+                            fail(LUM_ST_WAIT_FULL); ok = false; break;
                         }
-                        umma_commit(xempty + 8u * xs);        // arrives when the instructions that read this activation stage have retired
-                        xi++;
+                        tc_fence_after_sync();
+                        const uint32_t wb = smem_u32(cst + (size_t)cb * kGmCvtBytes), xb = smem_u32(xst + (size_t)xs * kGmXStageMax);
+#pragma unroll
+                        for (int k2 = 0; k2 < 2; k2++) {          // two instructions' worth of K (16 columns each) per slice
+                            // operands: [column group of 8][row][16 bytes]; a K = 16 instruction reads two adjacent column groups
+                            const uint64_t hi = umma_smem_desc(wb + (uint32_t)k2 * 4096u, 2048u, 128u), lo = umma_smem_desc(wb + 8192u + (uint32_t)k2 * 4096u, 2048u, 128u);
+                            const uint32_t xo = xb + (uint32_t)k2 * 2u * (uint32_t)nc * 16u;
+                            const uint64_t x1 = umma_smem_desc(xo, (uint32_t)nc * 16u, 128u), x2 = umma_smem_desc(xo + x_term, (uint32_t)nc * 16u, 128u),
+                                           x3 = umma_smem_desc(xo + 2u * x_term, (uint32_t)nc * 16u, 128u);
+                            umma_f16_ss(acc, hi, x1, idesc, started);
+                            started = 1u;
+                            umma_f16_ss(acc, hi, x2, idesc, 1u);
+                            umma_f16_ss(acc, hi, x3, idesc, 1u);
+                            umma_f16_ss(acc, lo, x1, idesc, 1u);
+                            umma_f16_ss(acc, lo, x2, idesc, 1u);
+                        }
+                        umma_commit(cempty + 8u * cb);        // arrive when the instructions that read these operands have retired
+                        umma_commit(xempty + 8u * xs);
+                        ci++; xi++;
                     }
-                    umma_commit(wempty + 8u * ws);
-                    wi++;
                 }
+                if (ok) umma_commit(afull + 8u * ab);
             }
             umma_commit(fin);
             if (!mbar_wait(fin, 0u)) atomicOr(a.status, LUM_ST_WAIT_TMEM);
         }
         __syncwarp();
-        named_sync(4, kGmDrainWarps * 32 + 32);
+        named_sync(4, kGmCvtWarps * 32 + 32);
         tc_fence_after_sync();
-        tmem_dealloc(tmem, 512);
+        tmem_dealloc(tmem, kGmTmemCols);
         return;
     }
 
-    // -------------------------------------------------------------------- draining warps
+    // -------------------------------------------------------------------- converting / storing warps
     {
-        const int q = warp & 3, hf = warp >> 2;                 // tensor-memory lane quarter; which 16 of the chunk's 32 activation rows
-        const int n = (q << 5) + lane;                          // this thread's weight row inside the item
-        const uint32_t tl = tmem + ((uint32_t)(q << 5) << 16) + (uint32_t)(hf * 48);
-        uint32_t wi = 0, xi = 0, ai = 0;
+        const int g = tid >> 4, h = (tid >> 3) & 1, r = tid & 7;     // row group, which 16 of a block's 32 columns, row of the group
+        const int n = g * 8 + r;                                     // weight row inside the item (operand row)
+        const int q = warp & 3, ch = warp >> 2;                      // for the store: tensor-memory lane quarter, which half of the chunk's rows
+        const int n_st = (q << 5) + lane;
+        uint32_t wi = 0, ci = 0, ic = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ic++) {
             const GemmItem it = gemm_item(a, item, tpr);
-            float acc[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) acc[i] = 0.0f;
             for (int t = it.t0; t < it.t1 && ok; t++) {
-                const uint32_t ws = wi % kGmWStages;
-                if (!mbar_wait_abortable(wfull + 8u * ws, (wi / kGmWStages) & 1u, abort)) { fail(LUM_ST_WAIT_FULL); ok = false; break; }
-                const __half* wsc = (const __half*)(wst + (size_t)ws * kGmWStage + (size_t)(n >> 3) * kTileBytes + kTileQ) + (n & 7);
-                for (int h = 0; h < 2 && ok; h++) {
-                    const uint32_t xs = xi % kGmXStages;
-                    if (!mbar_wait_abortable(xfull + 8u * xs, (xi / kGmXStages) & 1u, abort)) { fail(LUM_ST_WAIT_FULL); ok = false; break; }
-                    const float* sxp = (const float*)(xst + (size_t)xs * kGmXStage + kGmXHalf) + hf * 16;
+                const uint32_t ws = wi & 1u;
+                if (!mbar_wait_abortable(wfull + 8u * ws, (wi >> 1) & 1u, abort)) { fail(LUM_ST_WAIT_FULL); ok = false; break; }
+                const unsigned char* tile = wst + (size_t)ws * kGmWStage + (size_t)g * kTileBytes;
+                const bool live = g < it.n_rg;                       // row groups past the matrix's end contribute zeros
 #pragma unroll 1
-                    for (int bb = 0; bb < 8; bb++) {
-                        const uint32_t buf = ai % kGmAcc;
-                        if (!mbar_wait_abortable(tfull + 8u * buf, (ai / kGmAcc) & 1u, abort)) { fail(LUM_ST_WAIT_TMEM); ok = false; break; }
-                        tc_fence_after_sync();
-                        uint32_t v0[16], v1[16], v2[16];
-                        tmem_ld16(tl + buf * kGmCols, v0);
-                        tmem_ld16(tl + buf * kGmCols + 16u, v1);
-                        tmem_ld16(tl + buf * kGmCols + 32u, v2);
-                        tmem_ld_wait();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(tempty + 8u * buf);
-                        ai++;
-                        const float dw = (n >> 3) < it.n_rg ? __half2float(wsc[(h * 8 + bb) * 8]) : 0.0f;
-                        const float4* s4 = (const float4*)(sxp + bb * kGmMB);
-                        const float4 sa = s4[0], sb = s4[1], sc = s4[2], sd = s4[3];
-                        const float sxs[16] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w, sc.x, sc.y, sc.z, sc.w, sd.x, sd.y, sd.z, sd.w};
-                        // activation row i of this half: columns 3i, 3i+1, 3i+2 of the 48 = the three levels' dot products
-#define LUM_GM_ROW(i, A, o)                                                                                                  \
-    {                                                                                                                        \
-        const float tt = fmaf((float)(int)A[(o) + 2], 1.0f / 64516.0f, (float)((int)A[o] * 254 + (int)A[(o) + 1]) * (1.0f / 254.0f)); \
-        acc[i] = __fadd_rn(acc[i], __fmul_rn(tt, sxs[i] * dw));   /* product rounded on its own, as the GEMV does */            \
-    }
-                        LUM_GM_ROW(0, v0, 0) LUM_GM_ROW(1, v0, 3) LUM_GM_ROW(2, v0, 6) LUM_GM_ROW(3, v0, 9) LUM_GM_ROW(4, v0, 12)
-                        {   // row 5 straddles the first two loads: columns 15, 16, 17
-                            const float tt = fmaf((float)(int)v1[1], 1.0f / 64516.0f, (float)((int)v0[15] * 254 + (int)v1[0]) * (1.0f / 254.0f));
-                            acc[5] = __fadd_rn(acc[5], __fmul_rn(tt, sxs[5] * dw));
-                        }
-                        LUM_GM_ROW(6, v1, 2) LUM_GM_ROW(7, v1, 5) LUM_GM_ROW(8, v1, 8) LUM_GM_ROW(9, v1, 11)
-                        {   // row 10: columns 30, 31, 32
-                            const float tt = fmaf((float)(int)v2[0], 1.0f / 64516.0f, (float)((int)v1[14] * 254 + (int)v1[15]) * (1.0f / 254.0f));
-                            acc[10] = __fadd_rn(acc[10], __fmul_rn(tt, sxs[10] * dw));
-                        }
-                        LUM_GM_ROW(11, v2, 1) LUM_GM_ROW(12, v2, 4) LUM_GM_ROW(13, v2, 7) LUM_GM_ROW(14, v2, 10) LUM_GM_ROW(15, v2, 13)
-#undef LUM_GM_ROW
+                for (int s = 0; s < 16; s++) {
+                    const uint32_t cb = ci & 1u;
+                    if (!mbar_wait_abortable(cempty + 8u * cb, ((ci >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                    const uint4 raw = *(const uint4*)(tile + s * 256 + h * 128 + r * 16);
+                    const uint32_t d16 = live ? (uint32_t)*(const unsigned short*)(tile + kTileQ + (s * 8 + r) * 2) : 0u;
+                    const uint32_t dd = h2_mul(d16 | (d16 << 16), 0x64006400u);            // 1024 d, exact
+                    const uint32_t w4[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // bytes (q + 128) into the mantissas of 1024 + (q + 128), two at a time; minus 1152 leaves q, exactly
+                        const uint32_t q0 = h2_sub(__byte_perm(w4[j], 0x64646464u, 0x4140), 0x64806480u);
+                        const uint32_t q1 = h2_sub(__byte_perm(w4[j], 0x64646464u, 0x4342), 0x64806480u);
+                        hi[2 * j] = h2_mul(q0, dd); hi[2 * j + 1] = h2_mul(q1, dd);
+                        lo[2 * j] = h2_fma(q0, dd, hi[2 * j] ^ 0x80008000u);             // q d' - hi: the rounding error of hi, exactly
+                        lo[2 * j + 1] = h2_fma(q1, dd, hi[2 * j + 1] ^ 0x80008000u);
                     }
+                    unsigned char* dst = cst + (size_t)cb * kGmCvtBytes + (size_t)(h * 2) * 2048 + n * 16;
+                    *(uint4*)(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *(uint4*)(dst + 2048) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                    *(uint4*)(dst + 8192) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *(uint4*)(dst + 8192 + 2048) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                    fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(xempty + 8u * xs);
-                    xi++;
+                    if (lane == 0) mbar_arrive(cfull + 8u * cb);
+                    ci++;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(wempty + 8u * ws);
                 wi++;
             }
-            if (ok && (n >> 3) < it.n_rg) {
-                const GemmSeg& sg = a.seg[it.seg];
-                float* yp = a.y + (size_t)it.ks * a.part_stride + sg.col0 + it.rg0 * kTileRows + n;
+            if (!ok) break;
+            // ---- the item's K range is done: store the accumulator (lane = weight row, columns = activation rows)
+            const uint32_t ab = ic & 1u;
+            if (!mbar_wait_abortable(afull + 8u * ab, (ic >> 1) & 1u, abort)) { fail(LUM_ST_WAIT_TMEM); ok = false; break; }
+            tc_fence_after_sync();
+            const bool row_live = (n_st >> 3) < it.n_rg;
+            const GemmSeg& sg = a.seg[it.seg];
+            float* yp = a.y + (size_t)it.ks * a.part_stride + sg.col0 + it.rg0 * kTileRows + n_st;
+            const int half_rows = nc >> 1;
+            for (int c0 = 0; c0 < half_rows; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem + ((uint32_t)(q << 5) << 16) + ab * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0), v);
+                tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int m = it.mc * kGmMB + hf * 16 + i;
-                    if (m < a.M) yp[(size_t)m * a.ldy] = acc[i];
+                    const int m = it.mc * nc + ch * half_rows + c0 + i;
+                    if (row_live && m < a.M) yp[(size_t)m * a.ldy] = __uint_as_float(v[i]) * __ldg(a.sx + m);
                 }
             }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(aempty + 8u * ab);
         }
         tc_fence_before_sync();
-        named_arrive(4, kGmDrainWarps * 32 + 32);
+        named_arrive(4, kGmCvtWarps * 32 + 32);
     }
 }
 
 // ---------------------------------------------------------------------------------------------------------- host side
 
-size_t gemm_xq_bytes(int M, int K) { return (size_t)((M + kGmMB - 1) / kGmMB) * (K / 32) * kGmXBlock; }
-size_t gemm_sx_bytes(int M, int K) { return (size_t)((M + kGmMB - 1) / kGmMB) * (K / 32) * kGmMB * 4; }
+size_t gemm_xq_bytes(int M, int K) { const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * K * 6; }
+size_t gemm_sx_bytes(int M, int K) { (void)K; const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * 4; }
 
 // K ranges per product: enough work items to occupy every SM a couple of times over, each range at least one K-tile
 int gemm_pick_ksplit(int n_rows_total, int M, int K, int sm_count) {
-    const int tiles = (n_rows_total + kGmRows - 1) / kGmRows, mc = (M + kGmMB - 1) / kGmMB, tpr = K / kTileK;
+    const int nc = gemm_chunk_rows(M);
+    const int tiles = (n_rows_total + kGmRows - 1) / kGmRows, mc = (M + nc - 1) / nc, tpr = K / kTileK;
     int ks = (2 * sm_count + tiles * mc - 1) / (tiles * mc);
     if (ks > tpr) ks = tpr;
     if (ks > 8) ks = 8;
@@ -371,8 +424,9 @@ cudaError_t launch_rows_quantize(const RowsArgs& a_in, cudaStream_t st) {
         }
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
     }
+    const int nc = gemm_chunk_rows(a.M);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((a.M + kGmMB - 1) / kGmMB * kGmMB);      // padding rows of the last chunk are zeroed by their own CTAs
+    cfg.gridDim = dim3((a.M + nc - 1) / nc * nc);      // padding rows of the last chunk are zeroed by their own CTAs
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -394,7 +448,8 @@ bool gemm_supported(const GemmArgs& a) {
 
 cudaError_t launch_gemm(const GemmArgs& a_in, int sm_count, cudaStream_t st) {
     GemmArgs a = a_in;
-    a.m_chunks = (a.M + kGmMB - 1) / kGmMB;
+    a.nc = gemm_chunk_rows(a.M);
+    a.m_chunks = (a.M + a.nc - 1) / a.nc;
     if (!gemm_supported(a)) return cudaErrorInvalidValue;
     static bool set = false;
     if (!set) {

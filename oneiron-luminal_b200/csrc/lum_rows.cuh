@@ -11,9 +11,9 @@ struct GemmArgs {
     GemmSeg seg[3];
     int nseg;
     int K;
-    const int8_t* xq;        // [m_chunks][K / 32][kGmXBlock]
-    const float* sx;         // [m_chunks][K / 32][kGmMB]
-    int M, m_chunks;
+    const int8_t* xq;        // activation operand as rows_quantize writes it: three binary16 terms per element, tensor-core order
+    const float* sx;         // [rows]: the power-of-two factor that turns a row's accumulators into its outputs
+    int M, m_chunks, nc;     // nc: activation rows per chunk (set by the launcher)
     int ksplit;              // K ranges (whole K-tiles each); part i of the sums goes to y + i * part_stride
     float* y;
     int ldy;
