@@ -26,7 +26,8 @@
 //  * q8_gemm_tc — persistent CTAs over work items (128 weight rows, one chunk of up to 128 activation rows, one K range).
 //    A producer warp fills two shared-memory rings with bulk copies (weights: whole K-tiles of 16 row groups, 68 KiB;
 //    activations: 32-column slices of the three terms), 8 warps turn each 32-column slice of the int8 tile stream into the
-//    hi / lo operands, one thread issues the tensor-core instructions (10 per slice), and the same 8 warps store the
+//    hi / lo operands and store them to tensor memory (the A operand is read from there, which leaves shared-memory bandwidth
+//    to the activation operand), one thread issues the tensor-core instructions (10 per slice), and the same 8 warps store the
 //    accumulator when an item's K range is done (two accumulators alternate, so the next item's products run meanwhile).
 //    Outputs are plain f32 stores of K-split partial planes; whoever consumes them (the next rows_quantize) adds them up.
 #include <cstdlib>
@@ -42,15 +43,16 @@ constexpr int kGmRows = 128;                        // weight rows per work item
 constexpr int kGmRG = kGmRows / kTileRows;
 constexpr int kGmMaxChunk = 128;                    // activation rows per chunk: 32, 64 or 128 (gemm_chunk_rows)
 constexpr int kGmWStage = kGmRG * kTileBytes;       // 69632: one K-tile of 128 weight rows, as streamed
-constexpr int kGmCvtBytes = 2 * kGmRows * 32 * 2;   // 16384: hi and lo operands of one 32-column slice
 constexpr int kGmXStageMax = 3 * kGmMaxChunk * 32 * 2;   // 24576: the three activation terms of one slice
-constexpr int kGmWStages = 2, kGmCvtBufs = 2, kGmXStages = 2;
+constexpr int kGmWStages = 2, kGmCvtBufs = 4, kGmXStages = 3;
+constexpr uint32_t kGmCvtCols = 32;                 // tensor-memory columns of one converted slice: hi (16: 32 binary16 per row) | lo (16)
 constexpr int kGmCvtWarps = 8;
 constexpr int kGmThreads = (kGmCvtWarps + 2) * 32;   // + producer warp + tensor-core warp
 constexpr int kGmBarBytes = 256;
-constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmCvtBufs * kGmCvtBytes + (size_t)kGmXStages * kGmXStageMax;
+constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmXStages * kGmXStageMax;
 constexpr int kGmWExp = 10;                         // weights enter as 2^10 w
-constexpr uint32_t kGmTmemCols = 256;               // two accumulators of up to 128 columns
+constexpr uint32_t kGmTmemCols = 512;               // two accumulators of up to 128 columns, then the two converted-weight buffers
+constexpr uint32_t kGmCvtCol0 = 256;
 
 // activation rows per chunk for a product of M rows
 __host__ __device__ inline int gemm_chunk_rows(int M) { return M <= 32 ? 32 : M <= 64 ? 64 : 128; }
@@ -195,25 +197,40 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t da, uint64
         : "memory");
 }
 
+// the same with the A operand in tensor memory: lane = row, 32-bit column j = elements 2j, 2j + 1 of the row
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// whole warp: 8 consecutive 32-bit columns of this thread's lane
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+                 "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bars = smem_u32(smem);
-    const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 48, cfull = bars + 64, cempty = bars + 80,
-                   afull = bars + 96, aempty = bars + 112, fin = bars + 128, tmem_slot = bars + 136;
+    const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 64, cfull = bars + 96, cempty = bars + 128,
+                   afull = bars + 160, aempty = bars + 176, fin = bars + 192, tmem_slot = bars + 200;
     unsigned char* wst = (unsigned char*)(((uintptr_t)smem + kGmBarBytes + 127) & ~(uintptr_t)127);
-    unsigned char* cst = wst + (size_t)kGmWStages * kGmWStage;
-    unsigned char* xst = cst + (size_t)kGmCvtBufs * kGmCvtBytes;
+    unsigned char* xst = wst + (size_t)kGmWStages * kGmWStage;
     volatile int* abort = &s_abort;
     if (tid == 0) {
         s_abort = 0;
         for (int i = 0; i < 2; i++) {
             mbar_init(wfull + 8u * i, 1); mbar_init(wempty + 8u * i, kGmCvtWarps);
-            mbar_init(xfull + 8u * i, 1); mbar_init(xempty + 8u * i, 1);
-            mbar_init(cfull + 8u * i, kGmCvtWarps); mbar_init(cempty + 8u * i, 1);
             mbar_init(afull + 8u * i, 1); mbar_init(aempty + 8u * i, kGmCvtWarps);
         }
+        for (int i = 0; i < kGmCvtBufs; i++) { mbar_init(cfull + 8u * i, kGmCvtWarps); mbar_init(cempty + 8u * i, 1); }
+        for (int i = 0; i < kGmXStages; i++) { mbar_init(xfull + 8u * i, 1); mbar_init(xempty + 8u * i, 1); }
         mbar_init(fin, 1);
         mbar_fence_init();
     }
@@ -251,8 +268,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                                  wseg + ((size_t)(it.rg0 + j) * tpr + t) * kTileBytes, kTileBytes, wfull + 8u * ws);
                     wi++;
                     for (int s = 0; s < 16 && ok; s++) {
-                        const uint32_t xs = xi & 1u;
-                        if (!mbar_wait_abortable(xempty + 8u * xs, ((xi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                        const uint32_t xs = xi % kGmXStages;
+                        if (!mbar_wait_abortable(xempty + 8u * xs, ((xi / kGmXStages) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
                         mbar_arrive_expect_tx(xfull + 8u * xs, x_slice);
                         bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStageMax), (const unsigned char*)a.xq + ((size_t)it.mc * nb + (size_t)t * 16 + s) * x_slice,
                                  x_slice, xfull + 8u * xs);
@@ -263,7 +280,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
             if (!ok) {
                 // never leave while a copy into this CTA's shared memory may be in flight: wait (bounded) for what was armed
                 for (uint32_t k = 0; k < 2 && k < wi; k++) { const uint32_t i = wi - 1 - k; mbar_wait(wfull + 8u * (i & 1u), (i >> 1) & 1u); }
-                for (uint32_t k = 0; k < 2 && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i & 1u), (i >> 1) & 1u); }
+                for (uint32_t k = 0; k < kGmXStages && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i % kGmXStages), (i / kGmXStages) & 1u); }
             }
         }
         return;
@@ -283,25 +300,26 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                 uint32_t started = 0;
                 for (int t = it.t0; t < it.t1 && ok; t++) {
                     for (int s = 0; s < 16; s++) {
-                        const uint32_t cb = ci & 1u, xs = xi & 1u;
-                        if (!mbar_wait_abortable(cfull + 8u * cb, (ci >> 1) & 1u, abort) || !mbar_wait_abortable(xfull + 8u * xs, (xi >> 1) & 1u, abort)) {
+                        const uint32_t cb = ci % kGmCvtBufs, xs = xi % kGmXStages;
+                        if (!mbar_wait_abortable(cfull + 8u * cb, (ci / kGmCvtBufs) & 1u, abort) || !mbar_wait_abortable(xfull + 8u * xs, (xi / kGmXStages) & 1u, abort)) {
                             fail(LUM_ST_WAIT_FULL); ok = false; break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t wb = smem_u32(cst + (size_t)cb * kGmCvtBytes), xb = smem_u32(xst + (size_t)xs * kGmXStageMax);
+                        const uint32_t wt = tmem + kGmCvtCol0 + cb * kGmCvtCols, xb = smem_u32(xst + (size_t)xs * kGmXStageMax);
 #pragma unroll
                         for (int k2 = 0; k2 < 2; k2++) {          // two instructions' worth of K (16 columns each) per slice
-                            // operands: [column group of 8][row][16 bytes]; a K = 16 instruction reads two adjacent column groups
-                            const uint64_t hi = umma_smem_desc(wb + (uint32_t)k2 * 4096u, 2048u, 128u), lo = umma_smem_desc(wb + 8192u + (uint32_t)k2 * 4096u, 2048u, 128u);
+                            // weights: tensor memory, 8 columns (16 binary16) per instruction; activations: shared memory,
+                            // [column group of 8][row][16 bytes], an instruction reads two adjacent column groups
+                            const uint32_t hi = wt + (uint32_t)k2 * 8u, lo = wt + 16u + (uint32_t)k2 * 8u;
                             const uint32_t xo = xb + (uint32_t)k2 * 2u * (uint32_t)nc * 16u;
                             const uint64_t x1 = umma_smem_desc(xo, (uint32_t)nc * 16u, 128u), x2 = umma_smem_desc(xo + x_term, (uint32_t)nc * 16u, 128u),
                                            x3 = umma_smem_desc(xo + 2u * x_term, (uint32_t)nc * 16u, 128u);
-                            umma_f16_ss(acc, hi, x1, idesc, started);
+                            umma_f16_ts(acc, hi, x1, idesc, started);
                             started = 1u;
-                            umma_f16_ss(acc, hi, x2, idesc, 1u);
-                            umma_f16_ss(acc, hi, x3, idesc, 1u);
-                            umma_f16_ss(acc, lo, x1, idesc, 1u);
-                            umma_f16_ss(acc, lo, x2, idesc, 1u);
+                            umma_f16_ts(acc, hi, x2, idesc, 1u);
+                            umma_f16_ts(acc, hi, x3, idesc, 1u);
+                            umma_f16_ts(acc, lo, x1, idesc, 1u);
+                            umma_f16_ts(acc, lo, x2, idesc, 1u);
                         }
                         umma_commit(cempty + 8u * cb);        // arrive when the instructions that read these operands have retired
                         umma_commit(xempty + 8u * xs);
@@ -322,10 +340,11 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
 
     // -------------------------------------------------------------------- converting / storing warps
     {
-        const int g = tid >> 4, h = (tid >> 3) & 1, r = tid & 7;     // row group, which 16 of a block's 32 columns, row of the group
-        const int n = g * 8 + r;                                     // weight row inside the item (operand row)
-        const int q = warp & 3, ch = warp >> 2;                      // for the store: tensor-memory lane quarter, which half of the chunk's rows
-        const int n_st = (q << 5) + lane;
+        // a warp reaches the 32 tensor-memory lanes of its quarter: thread = weight row of the item (lane of tensor memory); warps
+        // 0-3 take columns 0-15 of every 32-block, warps 4-7 columns 16-31 (and, for the store, the two halves of the chunk's rows)
+        const int q = warp & 3, h = warp >> 2, ch = h;
+        const int n = (q << 5) + lane, g = n >> 3, r = n & 7, n_st = n;
+        const uint32_t lane_addr = (uint32_t)(q << 5) << 16;
         uint32_t wi = 0, ci = 0, ic = 0;
         bool ok = true;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ic++) {
@@ -337,8 +356,9 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                 const bool live = g < it.n_rg;                       // row groups past the matrix's end contribute zeros
 #pragma unroll 1
                 for (int s = 0; s < 16; s++) {
-                    const uint32_t cb = ci & 1u;
-                    if (!mbar_wait_abortable(cempty + 8u * cb, ((ci >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                    const uint32_t cb = ci % kGmCvtBufs;
+                    if (!mbar_wait_abortable(cempty + 8u * cb, ((ci / kGmCvtBufs) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                    tc_fence_after_sync();
                     const uint4 raw = *(const uint4*)(tile + s * 256 + h * 128 + r * 16);
                     const uint32_t d16 = live ? (uint32_t)*(const unsigned short*)(tile + kTileQ + (s * 8 + r) * 2) : 0u;
                     const uint32_t dd = h2_mul(d16 | (d16 << 16), 0x64006400u);            // 1024 d, exact
@@ -353,12 +373,11 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                         lo[2 * j] = h2_fma(q0, dd, hi[2 * j] ^ 0x80008000u);             // q d' - hi: the rounding error of hi, exactly
                         lo[2 * j + 1] = h2_fma(q1, dd, hi[2 * j + 1] ^ 0x80008000u);
                     }
-                    unsigned char* dst = cst + (size_t)cb * kGmCvtBytes + (size_t)(h * 2) * 2048 + n * 16;
-                    *(uint4*)(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *(uint4*)(dst + 2048) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                    *(uint4*)(dst + 8192) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                    *(uint4*)(dst + 8192 + 2048) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                    fence_proxy_async_smem();
+                    const uint32_t wt = tmem + lane_addr + kGmCvtCol0 + cb * kGmCvtCols + (uint32_t)h * 8u;
+                    tmem_st8(wt, hi);
+                    tmem_st8(wt + 16u, lo);
+                    tmem_st_wait();
+                    tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(cfull + 8u * cb);
                     ci++;
@@ -378,7 +397,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
             const int half_rows = nc >> 1;
             for (int c0 = 0; c0 < half_rows; c0 += 16) {
                 uint32_t v[16];
-                tmem_ld16(tmem + ((uint32_t)(q << 5) << 16) + ab * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0), v);
+                tmem_ld16(tmem + lane_addr + ab * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0), v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
