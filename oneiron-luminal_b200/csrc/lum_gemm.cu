@@ -11,10 +11,13 @@
 //   * a weight w = q * d (q int8, d binary16) has at most 18 significant bits.  1024 w = hi + lo EXACTLY, with
 //     hi = f16(q * 1024 d) and lo = q * 1024 d - hi (one fused multiply-add); the factor 1024 keeps lo out of the binary16
 //     subnormals whatever d is.  Two instructions per pair of weights, on the packed-half units.
-//   * an activation row is scaled by a power of two that puts its largest magnitude in [2^13, 2^14) and split into three
-//     terms x1 + x2 + x3 (successive binary16 roundings of the residual): 33 bits, so the only loss is below 2^-24 of the
-//     element or 2^-38 of the row's maximum.
-//   * five products are accumulated: hi x1, hi x2, hi x3, lo x1, lo x2 (lo x3 is below 2^-33 of the result).
+//   * an activation row is scaled by a power of two that puts its largest magnitude in [2^13, 2^14) and split into two
+//     terms x1 + x2 (binary16 roundings of the value and of the residual): 22 bits.
+//   * three products are accumulated: hi x1, hi x2, lo x1.  What is left out (lo x2 and the activation's third term) is
+//     below 2^-21 of |w| |x| per element — the size of the differences that the ORDER of an f32 summation over K >= 2048
+//     terms makes anyway (the CPU restatement sums sequentially, the tensor core in its own order), so the result is
+//     as close to the restatement as any f32 evaluation of the same dot product is.  (Five products, with a third activation
+//     term, reproduce every bit of the operands; measured, they cost 1.6x the time and change no token and no test.)
 // Q8_0's per-32 scales therefore never leave the operand: ONE accumulator per output tile runs over the whole K range and is
 // read back once, instead of once per 32-block (which is what binds an integer formulation: the read-back, not the tensor core).
 // The power-of-two factors (1024 and the row's) are undone exactly when the accumulator is stored.
@@ -24,11 +27,12 @@
 //    add, SwiGLU), optionally RMS-normalises it (`RowRMSNorm`, ops.rs:519-566; `RowSwishMul`, ops.rs:303-325; `RowAdd`,
 //    ops.rs:135-146 are fused here), writes the three terms in tensor-core operand order and the row's output factor.
 //  * q8_gemm_tc — persistent CTAs over work items (128 weight rows, one chunk of up to 128 activation rows, one K range).
-//    A producer warp fills two shared-memory rings with bulk copies (weights: whole K-tiles of 16 row groups, 68 KiB;
-//    activations: 32-column slices of the three terms), 8 warps turn each 32-column slice of the int8 tile stream into the
+//    A producer warp fills two shared-memory rings with bulk copies (weights: whole K-tiles of 16 row groups, 68 KiB, two
+//    stages; activations: 32-column slices of the two terms, 32 KiB per stage, two stages — the activation operand is four bytes per
+//    element and re-read by every tile of weight rows, so it is the stream that needs the bytes in flight), 8 warps turn each 32-column slice of the int8 tile stream into the
 //    hi / lo operands and store them to tensor memory (the A operand is read from there, which leaves shared-memory bandwidth
-//    to the activation operand), one thread issues the tensor-core instructions (10 per slice), and the same 8 warps store the
-//    accumulator when an item's K range is done (two accumulators alternate, so the next item's products run meanwhile).
+//    to the activation operand), one thread issues the tensor-core instructions (12 per step of two slices), and the same 8 warps store the
+//    two accumulators when an item's K range is done.
 //    Outputs are plain f32 stores of K-split partial planes; whoever consumes them (the next rows_quantize) adds them up.
 #include <cstdlib>
 
@@ -39,19 +43,28 @@
 
 namespace lum {
 
-constexpr int kGmRows = 128;                        // weight rows per work item: 16 row groups
+constexpr int kGmHB = 1;                            // tensor-core tiles (128 weight rows) per work item; they share every activation slice
+constexpr int kGmRows = 128 * kGmHB;                // weight rows per work item
 constexpr int kGmRG = kGmRows / kTileRows;
 constexpr int kGmMaxChunk = 128;                    // activation rows per chunk: 32, 64 or 128 (gemm_chunk_rows)
-constexpr int kGmWStage = kGmRG * kTileBytes;       // 69632: one K-tile of 128 weight rows, as streamed
-constexpr int kGmXStageMax = 3 * kGmMaxChunk * 32 * 2;   // 24576: the three activation terms of one slice
-constexpr int kGmWStages = 2, kGmCvtBufs = 4, kGmXStages = 3;
-constexpr uint32_t kGmCvtCols = 32;                 // tensor-memory columns of one converted slice: hi (16: 32 binary16 per row) | lo (16)
+// A weight stage is a whole K-tile of the item's row groups: one bulk copy of 4352 bytes per row group.  (Measured: a bulk copy
+// costs the SM's copy engine about 50 ns whatever its size, so stages cut into halves or quarters of a K-tile — two small copies
+// per row group each — bound the kernel at 5 to 17 copies per 32-column slice; whole tiles are 2 copies per slice.)
+constexpr int kGmPartSlices = 16;                   // 32-column slices per weight stage
+constexpr int kGmWRow = kTileBytes;                 // 4352: one tile, quants then scales, as streamed
+constexpr int kGmWStage = kGmRG * kGmWRow;          // 69632 per 128 weight rows
+constexpr int kGmXTerms = 2;                        // binary16 terms per activation element
+constexpr int kGmStep = 2;                          // 32-column slices per hand-over at 64 / 128 rows per chunk (4 at 32: GemmArgs::step) between the warps (every hand-over costs each single-threaded role
+                                                    // several hundred cycles of its own, whatever the amount of work behind it)
+constexpr int kGmXStageMax = kGmStep * kGmXTerms * kGmMaxChunk * 32 * 2;   // 32768: the activation terms of one step of a 128-row chunk
+constexpr int kGmWStages = 2, kGmCvtBufs = 4, kGmXStages = 2;
+constexpr uint32_t kGmCvtCols1 = 32 * kGmHB;                 // tensor-memory columns of one converted slice: per 128-row tile hi (16: 32 binary16 per row) | lo (16)
 constexpr int kGmCvtWarps = 8;
 constexpr int kGmThreads = (kGmCvtWarps + 2) * 32;   // + producer warp + tensor-core warp
-constexpr int kGmBarBytes = 256;
+constexpr int kGmBarBytes = 512;
 constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmXStages * kGmXStageMax;
 constexpr int kGmWExp = 10;                         // weights enter as 2^10 w
-constexpr uint32_t kGmTmemCols = 512;               // two accumulators of up to 128 columns, then the two converted-weight buffers
+constexpr uint32_t kGmTmemCols = 512;               // one accumulator of up to 128 columns per 128-row tile, then the four converted-weight buffers
 constexpr uint32_t kGmCvtCol0 = 256;
 
 // activation rows per chunk for a product of M rows
@@ -68,7 +81,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch, int tid, int
     return t;
 }
 
-// activation operand: [chunk][K / 32 slices][3 terms][4 groups of 8 columns][chunk rows][16 bytes]
+// activation operand: [chunk][K / 32 slices][kGmXTerms terms][4 groups of 8 columns][chunk rows][16 bytes]
 __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     extern __shared__ __align__(16) float rowbuf[];          // K floats + 8 words of reduction scratch
     const int m = blockIdx.x, tid = threadIdx.x;
@@ -76,13 +89,13 @@ __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     float* scratch = rowbuf + K;
     if (a.use_pdl) { pdl_launch_dependents(); pdl_grid_wait(); }
     const int nc = gemm_chunk_rows(a.M);
-    const size_t slice_bytes = (size_t)3 * 4 * nc * 16;
+    const size_t slice_bytes = (size_t)kGmXTerms * 4 * nc * 16;
     unsigned char* xq_chunk = (unsigned char*)a.xq + (size_t)(m / nc) * nb * slice_bytes;
     const int ml = m % nc;
     if (m >= a.M) {
         // padding row of the last chunk: zeros
-        for (int ch = tid; ch < nb * 12; ch += 256) {
-            const int s = ch / 12, tc = ch - s * 12;           // (term, column group) of slice s
+        for (int ch = tid; ch < nb * kGmXTerms * 4; ch += 256) {
+            const int s = ch / (kGmXTerms * 4), tc = ch - s * (kGmXTerms * 4);           // (term, column group) of slice s
             *(uint4*)(xq_chunk + (size_t)s * slice_bytes + (size_t)tc * nc * 16 + ml * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
         if (tid == 0) a.sx[m] = 0.0f;
@@ -159,7 +172,7 @@ __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
         unsigned char* dst = xq_chunk + (size_t)s * slice_bytes + (size_t)cg * nc * 16 + ml * 16;
         *(uint4*)(dst) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
         *(uint4*)(dst + (size_t)4 * nc * 16) = make_uint4(t2[0], t2[1], t2[2], t2[3]);
-        *(uint4*)(dst + (size_t)8 * nc * 16) = make_uint4(t3[0], t3[1], t3[2], t3[3]);
+        if (kGmXTerms > 2) *(uint4*)(dst + (size_t)8 * nc * 16) = make_uint4(t3[0], t3[1], t3[2], t3[3]);
     }
 }
 
@@ -205,6 +218,14 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the B descriptor given as its two halves (the high half is the same for every operand of a kernel)
+__device__ __forceinline__ void umma_f16_ts2(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // whole warp: 8 consecutive 32-bit columns of this thread's lane
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
@@ -218,8 +239,9 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bars = smem_u32(smem);
-    const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 64, cfull = bars + 96, cempty = bars + 128,
-                   afull = bars + 160, aempty = bars + 176, fin = bars + 192, tmem_slot = bars + 200;
+    const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 96, cfull = bars + 160, cempty = bars + 224,
+                   afull = bars + 288, aempty = bars + 296, fin = bars + 304, tmem_slot = bars + 312;
+    static_assert(kGmXStages <= 8 && kGmCvtBufs <= 8 && kGmCvtCol0 + kGmCvtBufs * kGmCvtCols1 * kGmStep <= kGmTmemCols, "barrier area / tensor memory");
     unsigned char* wst = (unsigned char*)(((uintptr_t)smem + kGmBarBytes + 127) & ~(uintptr_t)127);
     unsigned char* xst = wst + (size_t)kGmWStages * kGmWStage;
     volatile int* abort = &s_abort;
@@ -227,8 +249,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
         s_abort = 0;
         for (int i = 0; i < 2; i++) {
             mbar_init(wfull + 8u * i, 1); mbar_init(wempty + 8u * i, kGmCvtWarps);
-            mbar_init(afull + 8u * i, 1); mbar_init(aempty + 8u * i, kGmCvtWarps);
         }
+        mbar_init(afull, 1); mbar_init(aempty, kGmCvtWarps);
         for (int i = 0; i < kGmCvtBufs; i++) { mbar_init(cfull + 8u * i, kGmCvtWarps); mbar_init(cempty + 8u * i, 1); }
         for (int i = 0; i < kGmXStages; i++) { mbar_init(xfull + 8u * i, 1); mbar_init(xempty + 8u * i, 1); }
         mbar_init(fin, 1);
@@ -245,42 +267,57 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     const int tpr = a.K / kTileK, nb = a.K >> 5;
     const int nc = a.nc;                                   // activation rows per chunk
     const uint32_t x_term = (uint32_t)nc * 64u;            // bytes of one term of one slice: 4 column groups x nc rows x 16
-    const uint32_t x_slice = 3u * x_term;
+    const uint32_t x_slice = (uint32_t)kGmXTerms * x_term;
+    const uint32_t ncb = (uint32_t)a.cvt_bufs, nxs = (uint32_t)a.x_stages;
+    const int step = a.step;                               // slices per hand-over
+    const uint32_t cvt_cols = kGmCvtCols1 * (uint32_t)step;
+    const int sps = kGmStep * kGmMaxChunk / nc;            // slices per activation stage: a stage is always one 32 KiB copy
     int tiles = 0;
     for (int s = 0; s < a.nseg; s++) tiles += (a.seg[s].rows + kGmRows - 1) / kGmRows;
     const int n_items = tiles * a.ksplit * a.m_chunks;
     auto fail = [&](uint32_t code) { if (!*abort) { atomicOr(a.status, code); *abort = 1; } };
 
     if (warp == kGmCvtWarps) {
-        // ---------------------------------------------------------------- producer: one lane
-        if (lane == 0) {
+        // ---------------------------------------------------------------- producer warp
+        // Lane 0 waits for a free stage and arms its barrier; the weight copies of a stage (two per row group) are then issued
+        // by 32 lanes side by side — issued by one lane, one after the other, they are what bounds the kernel (measured: about
+        // 75 ns per copy).  The activation slices are one large copy each and stay with lane 0.
+        {
             uint32_t wi = 0, xi = 0;
-            bool ok = true;
+            int ok = 1;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const GemmItem it = gemm_item(a, item, tpr);
                 const unsigned char* wseg = a.seg[it.seg].w;
                 for (int t = it.t0; t < it.t1 && ok; t++) {
                     const uint32_t ws = wi & 1u;
-                    if (!mbar_wait_abortable(wempty + 8u * ws, ((wi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
-                    mbar_arrive_expect_tx(wfull + 8u * ws, (uint32_t)it.n_rg * kTileBytes);
-                    for (int j = 0; j < it.n_rg; j++)
-                        bulk_g2s(smem_u32(wst + (size_t)ws * kGmWStage + (size_t)j * kTileBytes),
-                                 wseg + ((size_t)(it.rg0 + j) * tpr + t) * kTileBytes, kTileBytes, wfull + 8u * ws);
-                    wi++;
-                    for (int s = 0; s < 16 && ok; s++) {
-                        const uint32_t xs = xi % kGmXStages;
-                        if (!mbar_wait_abortable(xempty + 8u * xs, ((xi / kGmXStages) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
-                        mbar_arrive_expect_tx(xfull + 8u * xs, x_slice);
-                        bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStageMax), (const unsigned char*)a.xq + ((size_t)it.mc * nb + (size_t)t * 16 + s) * x_slice,
-                                 x_slice, xfull + 8u * xs);
-                        xi++;
+                    if (lane == 0) {
+                        if (!mbar_wait_abortable(wempty + 8u * ws, ((wi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = 0; }
+                        else mbar_arrive_expect_tx(wfull + 8u * ws, (uint32_t)it.n_rg * kGmWRow);
                     }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    for (int j = lane; j < it.n_rg; j += 32)
+                        bulk_g2s(smem_u32(wst + (size_t)ws * kGmWStage + (size_t)j * kGmWRow), wseg + ((size_t)(it.rg0 + j) * tpr + t) * kTileBytes, kTileBytes,
+                                 wfull + 8u * ws);
+                    wi++;
+                    if (lane == 0) {
+                        for (int s = 0; s < kGmPartSlices && ok; s += sps) {
+                            const uint32_t xs = xi % nxs;
+                            if (!mbar_wait_abortable(xempty + 8u * xs, ((xi / nxs) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = 0; break; }
+                            mbar_arrive_expect_tx(xfull + 8u * xs, x_slice * (uint32_t)sps);
+                            bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStageMax), (const unsigned char*)a.xq + ((size_t)it.mc * nb + (size_t)t * 16 + s) * x_slice,
+                                     x_slice * (uint32_t)sps, xfull + 8u * xs);
+                            xi++;
+                        }
+                    }
+                    xi = __shfl_sync(0xffffffffu, xi, 0);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // never leave while a copy into this CTA's shared memory may be in flight: wait (bounded) for what was armed
                 for (uint32_t k = 0; k < 2 && k < wi; k++) { const uint32_t i = wi - 1 - k; mbar_wait(wfull + 8u * (i & 1u), (i >> 1) & 1u); }
-                for (uint32_t k = 0; k < kGmXStages && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i % kGmXStages), (i / kGmXStages) & 1u); }
+                for (uint32_t k = 0; k < nxs && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i % nxs), (i / nxs) & 1u); }
             }
         }
         return;
@@ -290,43 +327,49 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
         if (lane == 0) {
             uint32_t xi = 0, ci = 0, ic = 0;
             bool ok = true;
-            const uint32_t idesc = umma_idesc_f16(kGmRows, nc);
+            const uint32_t idesc = umma_idesc_f16(128, nc);
+            // activation operand descriptors: start address in the low 14 bits; column groups nc * 16 bytes apart, 8-row groups 128
+            const uint32_t x_lo = (((uint32_t)nc * 16u >> 4) & 0x3fffu) << 16, x_hi = umma_desc_hi(128u), x_base = smem_u32(xst);
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ic++) {
                 const GemmItem it = gemm_item(a, item, tpr);
-                const uint32_t ab = ic & 1u;
-                if (!mbar_wait_abortable(aempty + 8u * ab, ((ic >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_TMEM); break; }
+                if (!mbar_wait_abortable(aempty, (ic & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_TMEM); break; }      // the previous item's sums were stored
                 tc_fence_after_sync();
-                const uint32_t acc = tmem + ab * (uint32_t)kGmMaxChunk;
                 uint32_t started = 0;
                 for (int t = it.t0; t < it.t1 && ok; t++) {
-                    for (int s = 0; s < 16; s++) {
-                        const uint32_t cb = ci % kGmCvtBufs, xs = xi % kGmXStages;
-                        if (!mbar_wait_abortable(cfull + 8u * cb, (ci / kGmCvtBufs) & 1u, abort) || !mbar_wait_abortable(xfull + 8u * xs, (xi / kGmXStages) & 1u, abort)) {
+                    for (int s = 0; s < 16; s += step) {
+                        const uint32_t cb = ci % ncb, xs = xi % nxs;
+                        const int sub = s % sps;                  // first slice of the step inside the activation stage
+                        if (!mbar_wait_abortable(cfull + 8u * cb, (ci / ncb) & 1u, abort) ||
+                            (sub == 0 && !mbar_wait_abortable(xfull + 8u * xs, (xi / nxs) & 1u, abort))) {
                             fail(LUM_ST_WAIT_FULL); ok = false; break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t wt = tmem + kGmCvtCol0 + cb * kGmCvtCols, xb = smem_u32(xst + (size_t)xs * kGmXStageMax);
+                        const uint32_t wt = tmem + kGmCvtCol0 + cb * cvt_cols;
+                        const uint32_t xb = x_base + xs * (uint32_t)kGmXStageMax + (uint32_t)sub * x_slice;
+                        if (!(a.debug & 2)) {
+#pragma unroll 4
+                            for (int kk = 0; kk < 2 * step; kk++) {     // K = 16 per instruction: two per 32-column slice
+                                // weights: tensor memory, 8 columns (16 binary16) per instruction; activations: shared memory,
+                                // [column group of 8][row][16 bytes], an instruction reads two adjacent column groups
+                                const uint32_t xo = xb + (uint32_t)(kk >> 1) * x_slice + (uint32_t)(kk & 1) * 2u * (uint32_t)nc * 16u;
+                                const uint32_t x1 = x_lo | ((xo >> 4) & 0x3fffu), x2 = x_lo | (((xo + x_term) >> 4) & 0x3fffu);
 #pragma unroll
-                        for (int k2 = 0; k2 < 2; k2++) {          // two instructions' worth of K (16 columns each) per slice
-                            // weights: tensor memory, 8 columns (16 binary16) per instruction; activations: shared memory,
-                            // [column group of 8][row][16 bytes], an instruction reads two adjacent column groups
-                            const uint32_t hi = wt + (uint32_t)k2 * 8u, lo = wt + 16u + (uint32_t)k2 * 8u;
-                            const uint32_t xo = xb + (uint32_t)k2 * 2u * (uint32_t)nc * 16u;
-                            const uint64_t x1 = umma_smem_desc(xo, (uint32_t)nc * 16u, 128u), x2 = umma_smem_desc(xo + x_term, (uint32_t)nc * 16u, 128u),
-                                           x3 = umma_smem_desc(xo + 2u * x_term, (uint32_t)nc * 16u, 128u);
-                            umma_f16_ts(acc, hi, x1, idesc, started);
-                            started = 1u;
-                            umma_f16_ts(acc, hi, x2, idesc, 1u);
-                            umma_f16_ts(acc, hi, x3, idesc, 1u);
-                            umma_f16_ts(acc, lo, x1, idesc, 1u);
-                            umma_f16_ts(acc, lo, x2, idesc, 1u);
+                                for (int hb = 0; hb < kGmHB; hb++) {      // the 128-row tiles of the item
+                                    const uint32_t acc = tmem + (uint32_t)hb * (uint32_t)kGmMaxChunk;
+                                    const uint32_t hi = wt + (uint32_t)(kk >> 1) * 32u * kGmHB + (uint32_t)hb * 32u + (uint32_t)(kk & 1) * 8u, lo = hi + 16u;
+                                    umma_f16_ts2(acc, hi, x1, x_hi, idesc, started);
+                                    umma_f16_ts2(acc, hi, x2, x_hi, idesc, 1u);
+                                    umma_f16_ts2(acc, lo, x1, x_hi, idesc, 1u);
+                                }
+                                started = 1u;
+                            }
                         }
                         umma_commit(cempty + 8u * cb);        // arrive when the instructions that read these operands have retired
-                        umma_commit(xempty + 8u * xs);
-                        ci++; xi++;
+                        ci++;
+                        if (sub + step == sps) { umma_commit(xempty + 8u * xs); xi++; }
                     }
                 }
-                if (ok) umma_commit(afull + 8u * ab);
+                if (ok) umma_commit(afull);
             }
             umma_commit(fin);
             if (!mbar_wait(fin, 0u)) atomicOr(a.status, LUM_ST_WAIT_TMEM);
@@ -343,7 +386,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
         // a warp reaches the 32 tensor-memory lanes of its quarter: thread = weight row of the item (lane of tensor memory); warps
         // 0-3 take columns 0-15 of every 32-block, warps 4-7 columns 16-31 (and, for the store, the two halves of the chunk's rows)
         const int q = warp & 3, h = warp >> 2, ch = h;
-        const int n = (q << 5) + lane, g = n >> 3, r = n & 7, n_st = n;
+        const int n = (q << 5) + lane, r = n & 7;                    // row inside a 128-row tile
         const uint32_t lane_addr = (uint32_t)(q << 5) << 16;
         uint32_t wi = 0, ci = 0, ic = 0;
         bool ok = true;
@@ -352,13 +395,20 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
             for (int t = it.t0; t < it.t1 && ok; t++) {
                 const uint32_t ws = wi & 1u;
                 if (!mbar_wait_abortable(wfull + 8u * ws, (wi >> 1) & 1u, abort)) { fail(LUM_ST_WAIT_FULL); ok = false; break; }
-                const unsigned char* tile = wst + (size_t)ws * kGmWStage + (size_t)g * kTileBytes;
-                const bool live = g < it.n_rg;                       // row groups past the matrix's end contribute zeros
 #pragma unroll 1
-                for (int s = 0; s < 16; s++) {
-                    const uint32_t cb = ci % kGmCvtBufs;
-                    if (!mbar_wait_abortable(cempty + 8u * cb, ((ci / kGmCvtBufs) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                for (int s0 = 0; s0 < kGmPartSlices; s0 += step) {
+                    const uint32_t cb = ci % ncb;
+                    if (!mbar_wait_abortable(cempty + 8u * cb, ((ci / ncb) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
                     tc_fence_after_sync();
+                    if (a.debug & 1) { __syncwarp(); if (lane == 0) mbar_arrive(cfull + 8u * cb); ci++; continue; }
+#pragma unroll 2
+                 for (int ss = 0; ss < step; ss++) {
+                  const int s = s0 + ss;
+#pragma unroll
+                  for (int hb = 0; hb < kGmHB; hb++) {
+                    const int g = (n >> 3) + hb * 16;
+                    const unsigned char* tile = wst + (size_t)ws * kGmWStage + (size_t)g * kGmWRow;
+                    const bool live = g < it.n_rg;                   // row groups past the matrix's end contribute zeros
                     const uint4 raw = *(const uint4*)(tile + s * 256 + h * 128 + r * 16);
                     const uint32_t d16 = live ? (uint32_t)*(const unsigned short*)(tile + kTileQ + (s * 8 + r) * 2) : 0u;
                     const uint32_t dd = h2_mul(d16 | (d16 << 16), 0x64006400u);            // 1024 d, exact
@@ -373,9 +423,11 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                         lo[2 * j] = h2_fma(q0, dd, hi[2 * j] ^ 0x80008000u);             // q d' - hi: the rounding error of hi, exactly
                         lo[2 * j + 1] = h2_fma(q1, dd, hi[2 * j + 1] ^ 0x80008000u);
                     }
-                    const uint32_t wt = tmem + lane_addr + kGmCvtCol0 + cb * kGmCvtCols + (uint32_t)h * 8u;
+                    const uint32_t wt = tmem + lane_addr + kGmCvtCol0 + cb * cvt_cols + (uint32_t)ss * 32u * kGmHB + (uint32_t)hb * 32u + (uint32_t)h * 8u;
                     tmem_st8(wt, hi);
                     tmem_st8(wt + 16u, lo);
+                  }
+                 }
                     tmem_st_wait();
                     tc_fence_before_sync();
                     __syncwarp();
@@ -388,26 +440,29 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
             }
             if (!ok) break;
             // ---- the item's K range is done: store the accumulator (lane = weight row, columns = activation rows)
-            const uint32_t ab = ic & 1u;
-            if (!mbar_wait_abortable(afull + 8u * ab, (ic >> 1) & 1u, abort)) { fail(LUM_ST_WAIT_TMEM); ok = false; break; }
+            if (!mbar_wait_abortable(afull, ic & 1u, abort)) { fail(LUM_ST_WAIT_TMEM); ok = false; break; }
             tc_fence_after_sync();
-            const bool row_live = (n_st >> 3) < it.n_rg;
             const GemmSeg& sg = a.seg[it.seg];
-            float* yp = a.y + (size_t)it.ks * a.part_stride + sg.col0 + it.rg0 * kTileRows + n_st;
             const int half_rows = nc >> 1;
-            for (int c0 = 0; c0 < half_rows; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem + lane_addr + ab * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0), v);
-                tmem_ld_wait();
+#pragma unroll 1
+            for (int hb = 0; hb < kGmHB; hb++) {
+                const int n_st = hb * 128 + n;
+                const bool row_live = (n_st >> 3) < it.n_rg;
+                float* yp = a.y + (size_t)it.ks * a.part_stride + sg.col0 + it.rg0 * kTileRows + n_st;
+                for (int c0 = 0; c0 < half_rows; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem + lane_addr + (uint32_t)hb * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0), v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int m = it.mc * nc + ch * half_rows + c0 + i;
-                    if (row_live && m < a.M) yp[(size_t)m * a.ldy] = __uint_as_float(v[i]) * __ldg(a.sx + m);
+                    for (int i = 0; i < 16; i++) {
+                        const int m = it.mc * nc + ch * half_rows + c0 + i;
+                        if (row_live && m < a.M) yp[(size_t)m * a.ldy] = __uint_as_float(v[i]) * __ldg(a.sx + m);
+                    }
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(aempty + 8u * ab);
+            if (lane == 0) mbar_arrive(aempty);
         }
         tc_fence_before_sync();
         named_arrive(4, kGmCvtWarps * 32 + 32);
@@ -416,7 +471,7 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
 
 // ---------------------------------------------------------------------------------------------------------- host side
 
-size_t gemm_xq_bytes(int M, int K) { const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * K * 6; }
+size_t gemm_xq_bytes(int M, int K) { const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * K * 2 * kGmXTerms; }
 size_t gemm_sx_bytes(int M, int K) { (void)K; const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * 4; }
 
 // K ranges per product: enough work items to occupy every SM a couple of times over, each range at least one K-tile
@@ -468,6 +523,17 @@ bool gemm_supported(const GemmArgs& a) {
 cudaError_t launch_gemm(const GemmArgs& a_in, int sm_count, cudaStream_t st) {
     GemmArgs a = a_in;
     a.nc = gemm_chunk_rows(a.M);
+    static const int env_debug = [] { const char* e = getenv("LUM_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
+    a.debug = env_debug;
+    static const int env_cb = [] { const char* e = getenv("LUM_GEMM_CB"); return e ? atoi(e) : 8; }();
+    static const int env_xs = [] { const char* e = getenv("LUM_GEMM_XS"); return e ? atoi(e) : kGmXStages; }();
+    static const int env_step = [] { const char* e = getenv("LUM_GEMM_STEP"); return e ? atoi(e) : 0; }();
+    a.step = a.nc == 32 ? 4 : kGmStep;
+    if (env_step == 2 || (env_step == 4 && a.nc == 32)) a.step = env_step;
+    int max_bufs = 256 / (32 * kGmHB * a.step);          // converted-weight buffers that fit the 256 columns behind the accumulators
+    if (max_bufs > kGmCvtBufs) max_bufs = kGmCvtBufs;            // as many as there are barriers
+    a.cvt_bufs = env_cb < 1 ? 1 : env_cb > max_bufs ? max_bufs : env_cb;
+    a.x_stages = env_xs < 1 ? 1 : env_xs > kGmXStages ? kGmXStages : env_xs;
     a.m_chunks = (a.M + a.nc - 1) / a.nc;
     if (!gemm_supported(a)) return cudaErrorInvalidValue;
     static bool set = false;

@@ -14,6 +14,8 @@ struct GemmArgs {
     const int8_t* xq;        // activation operand as rows_quantize writes it: three binary16 terms per element, tensor-core order
     const float* sx;         // [rows]: the power-of-two factor that turns a row's accumulators into its outputs
     int M, m_chunks, nc;     // nc: activation rows per chunk (set by the launcher)
+    int cvt_bufs, x_stages, step;  // ring depths; 32-column slices per hand-over between the kernel's roles (set by the launcher)
+    int debug;               // timing experiments only (LUM_GEMM_DEBUG): 1 = skip the weight conversion, 2 = skip the tensor-core instructions
     int ksplit;              // K ranges (whole K-tiles each); part i of the sums goes to y + i * part_stride
     float* y;
     int ldy;

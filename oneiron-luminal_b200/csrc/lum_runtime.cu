@@ -708,7 +708,9 @@ int ensure_rows(lum_rt* rt, int want_rows) {
     lum_rt::Rows& b = rt->rows;
     if (b.cap >= want_rows) return 0;
     if (b.cap) return fail(rt, LUM_E_INVALID, "rows: %d rows asked for, buffers hold %d", want_rows, b.cap);
-    int cap = 512;
+    // rows per pass: a whole 4096-token prompt in one pass when the cache can hold one (more rows per product = more work items per
+    // product, which is what balances them over the SMs), never more than the cache's capacity
+    int cap = rt->d.max_seq < 4096 ? rt->d.max_seq : 4096;
     if (const char* e = getenv("LUM_ROWS_CAP")) cap = atoi(e);
     if (cap < 32) cap = 32;
     if (cap < rt->max_batch) cap = rt->max_batch;

@@ -409,8 +409,16 @@ def test_prompt_as_rows_matches_oracle_and_per_token_path(pkg, name, n_prompt):
         for layer in (0, desc.n_layers - 1):
             for kind in ("k", "v"):
                 ka, kb = rows.kv_read(layer, kind, n_prompt), tok.kv_read(layer, kind, n_prompt)
+                ko = orc.kv_read(layer, kind, n_prompt)
                 assert np.max(np.abs(ka - kb)) <= 2.0 ** -6 * np.max(np.abs(kb)), (layer, kind)      # a bfloat16 step of the largest values
-                assert np.mean(ka == kb) > 0.9, (layer, kind, float(np.mean(ka == kb)))
+                # The two paths sum in different orders (the tensor core accumulates K = 16 at a time in its own arithmetic, the
+                # single-row kernel per 32-block in f32), so a cached bfloat16 value whose f32 value sits next to a rounding
+                # boundary may land on either side: in the first layer that is rare; every such step then shifts the layers above.
+                # What counts is the distance to the oracle's rows, which is the same for both paths.
+                assert np.mean(ka == kb) > (0.9 if layer == 0 else 0.6), (layer, kind, float(np.mean(ka == kb)))
+                for k_gpu in (ka, kb):
+                    rms = float(np.sqrt(np.mean((k_gpu - ko) ** 2)) / np.sqrt(np.mean(ko ** 2)))
+                    assert rms <= 1e-2, (layer, kind, rms)
         rows.decode_greedy(n_new - 1)
         got = [want[0]] + [int(t) for t in rows.get_decoded(n_new - 1)]
         assert got == want, f"min oracle top-1/top-2 margin {min(margins):.3e}"
