@@ -245,6 +245,52 @@ def kernel_rows_sweep(pkg, torch):
             "steady_gb_per_s": sms * 34816 / slope / 1e3, "fixed_us_per_launch": b["us_per_launch"] - slope * b["fills_per_cta"]}
 
 
+def gemm_shapes(pkg, torch, shapes=None):
+    """The tensor-core GEMM alone (row quantiser + q8_gemm_tc [+ the K-split sum]) through lum_op_gemm_q8_0_packed on the
+    Llama-3-8B layer's shapes, 512 rows (one pass of a prompt) and 32 rows (batched decode): µs per call and useful TFLOP/s
+    (2 N K M: the redundant products of the operand split are not counted)."""
+    lib = pkg.load_library()
+    out = []
+    for n, k, m in (shapes or [(28672, 4096, 512), (6144, 4096, 512), (4096, 4096, 512), (4096, 14336, 512),
+                               (28672, 4096, 32), (6144, 4096, 32), (4096, 14336, 32), (128256, 4096, 32)]):
+        packed = torch.empty(lib.lum_q8_0_packed_bytes(n, k), dtype=torch.uint8, device="cuda")
+        assert lib.lum_op_synth_q8_0_packed(SEED, 900, n, k, packed.data_ptr(), None) == 0
+        x = torch.randn(m, k, device="cuda")
+        y = torch.empty(m, n, device="cuda")
+        ws_bytes = lib.lum_op_gemm_q8_0_workspace(n, k, m)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        best = None
+        for _ in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); e0.record()
+            assert lib.lum_op_gemm_q8_0_packed(packed.data_ptr(), n, k, x.data_ptr(), m, y.data_ptr(), ws.data_ptr(), ws_bytes, None) == 0
+            e1.record(); torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3
+            best = us if best is None else min(best, us)
+        assert lib.lum_op_status(None) == 0
+        out.append({"n": n, "k": k, "m": m, "us": best, "tflops": 2.0 * n * k * m / best / 1e6, "weight_gb_per_s": n * k * 34 / 32 / best / 1e3})
+        del packed, x, y, ws
+        torch.cuda.empty_cache()
+    return {"kernel": "rows_quantize + q8_gemm_tc", "shapes": out}
+
+
+def prompt_two_layers(pkg, torch, n=4096):
+    """A 4096-token prompt through a 2-layer cut of the Llama-3-8B shape (vocabulary 4096): the same kernels and shapes as the
+    full model's prompt pass, a few hundred MB on the device — the case the profiler captures of the prompt kernels use."""
+    desc = pkg.CONFIGS["llama3_8b_q8_2layer"].copy(max_seq=n + 64)
+    rt = pkg.B200Runtime.initialize(device=0)
+    rt.load_model(desc); rt.synth(SEED)
+    ids = _prompt_tokens(desc.vocab, n)
+    ms = []
+    for _ in range(3):
+        rt.kv_reset(); rt.decode_reset(); rt.synchronize()
+        t0 = time.perf_counter()
+        rt.set_data(ids); rt.execute({"s": n, "p": 0}); rt.synchronize()
+        ms.append((time.perf_counter() - t0) * 1e3)
+    rt.close()
+    return {"config": "llama3_8b_q8_2layer", "prompt_len": n, "ms_two_layers_and_head": min(ms), "ms_per_32_layers": min(ms) / 2 * 32}
+
+
 def launch_chain_floor(pkg, torch):
     """The decode step of the benchmark's model with every projection shrunk to almost nothing (hidden 512, 4/1 heads of 128,
     ffn 512, vocabulary 1024; same 32 layers, same launches, same context): what is left is the chain of dependent launches —
@@ -499,7 +545,7 @@ def run_tensor_core_regime(args, pkg, which: str):
         e2e = args.steps * tps * B / (time.perf_counter() - t0)
         line = {"metric": "q8_llama3_8b_bs32_decode_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "int8 x int8 -> s32 on tcgen05 (three int8 levels of the f32 activations), f32 scales and sums", "data": "synthetic",
+                "dtype": "f16 x f16 -> f32 on tcgen05 (weights as two exact binary16 terms, activations as two), f32 sums", "data": "synthetic",
                 "config": {"workload": which, "batch": B, "context": ctx, "tokens_per_step": tps, "seed": SEED,
                            "l2": "weights 8.0 GB + caches 8.6 GB >> 126 MB L2"},
                 "roofline": {"bound": "hbm", "kernel": "whole batched step (q8_gemm_tc + attn_rows dominate)", "achieved": ach, "peak": peaks["hbm_gbs"],
@@ -536,9 +582,9 @@ def run_tensor_core_regime(args, pkg, which: str):
         e2e = n / (time.perf_counter() - t0)
         line = {"metric": "q8_llama3_8b_prefill4096_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "int8 x int8 -> s32 on tcgen05 (three int8 levels of the f32 activations), f32 scales and sums; f32 attention", "data": "synthetic",
+                "dtype": "f16 x f16 -> f32 on tcgen05 (weights as two exact binary16 terms, activations as two); attention bf16 x bf16 -> f32 on tcgen05 (two-term queries and weights)", "data": "synthetic",
                 "config": {"workload": which, "batch": 1, "prompt_len": n, "seed": SEED},
-                "roofline": {"bound": "tensor", "kernel": "whole prompt (q8_gemm_tc + attn_rows)", "achieved": ach, "peak": peaks.get("bf16_tflops_sustained", 1383.9),
+                "roofline": {"bound": "tensor", "kernel": "whole prompt (q8_gemm_tc 85 %, attn_prompt_tc 11 % of the time)", "achieved": ach, "peak": peaks.get("bf16_tflops_sustained", 1383.9),
                              "unit": "TFLOP/s", "frac": ach / peaks.get("bf16_tflops_sustained", 1383.9), "peak_kind": f"of {peak_kind} (sustained bf16 GEMM)",
                              "flops_per_step": flops, "traffic": None},
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4,
@@ -661,8 +707,10 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8", "llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096", "gpt_oss_20b_q8"],
                     help="llama3_8b_q8: the configuration the metric is quoted on (default); qwen3_4b_q8: the Qwen3-4B shape; "
                          "llama3_8b_q8_bs32 / llama3_8b_q8_prefill4096: the same model in the tensor-core regime (batched decode / one long prompt)")
-    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor"],
-                    help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts; floor: the decode step with all projections shrunk away")
+    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor", "gemm", "gemm512", "gemm32", "prompt2"],
+                    help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts; "
+                         "floor: the decode step with all projections shrunk away; gemm: the tensor-core GEMM alone on the layer's shapes "
+                         "(gemm512 / gemm32: the gate+up shape only, 512 / 32 rows, for ncu captures); prompt2: a 4096-token prompt through a 2-layer cut")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
@@ -692,6 +740,17 @@ def main():
         import torch
         torch.cuda.set_device(0)
         print(json.dumps({"rows_sweep": kernel_rows_sweep(pkg, torch)}))
+        return
+    if args.only in ("gemm", "gemm512", "gemm32"):
+        import torch
+        torch.cuda.set_device(0)
+        shapes = {"gemm": None, "gemm512": [(28672, 4096, 512)], "gemm32": [(28672, 4096, 32)]}[args.only]
+        print(json.dumps({"gemm_shapes": gemm_shapes(pkg, torch, shapes)}))
+        return
+    if args.only == "prompt2":
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps({"prompt_two_layers": prompt_two_layers(pkg, torch)}))
         return
     if args.only == "floor":
         import torch
