@@ -408,10 +408,15 @@ __device__ __forceinline__ void gemv_quantize_x(const GemvArgs& a, const XSource
         }
         if (PEER && xs.n_parts > 0 && xs.part_flags) peer_wait_parts(xs.part_flags, xs.n_parts, xs.seq, xs.parts_tag, a.status, tid, kWorkers, 1);
         if (PEER && xs.parts_ll) {
-            // every element carries its own completion word: all loads of four ranks' vectors go out together, stragglers are
+            // every element carries its own completion word: all loads of two ranks' vectors go out together, stragglers are
             // waited for one by one
             const uint32_t word = peer_word(__ldcg(xs.seq), xs.parts_tag);
-            constexpr int kLLBatch = 4;      // ranks whose vectors are requested together: one trip to L2 per batch (8 ranks: two trips)
+#ifndef LUM_LL_BATCH
+#define LUM_LL_BATCH 2
+#endif
+            // ranks whose vectors are requested together.  Measured on 2 GPUs, same call: 1 -> 558.7, 2 -> 553.6, 4 -> 495.2 tokens/s
+            // (four ranks' loads in flight cost registers: the kernel spills); 2 is what the 4- and 8-GPU numbers were measured with
+            constexpr int kLLBatch = LUM_LL_BATCH;
 #pragma unroll 1
             for (int r0 = 0; r0 < xs.n_parts; r0 += kLLBatch) {
                 uint4 raw[kLLBatch][kSmallTrips][2];
