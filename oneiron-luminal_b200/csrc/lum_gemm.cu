@@ -31,7 +31,7 @@
 //    stages; activations: 32-column slices of the two terms, 32 KiB per stage, two stages — the activation operand is four bytes per
 //    element and re-read by every tile of weight rows, so it is the stream that needs the bytes in flight), 8 warps turn each 32-column slice of the int8 tile stream into the
 //    hi / lo operands and store them to tensor memory (the A operand is read from there, which leaves shared-memory bandwidth
-//    to the activation operand), one thread issues the tensor-core instructions (12 per step of two slices), and the same 8 warps store the
+//    to the activation operand), one thread issues the tensor-core instructions (8 per step of two 32-column slices, 16 per step of four at 32 rows), and the same 8 warps store the
 //    two accumulators when an item's K range is done.
 //    Outputs are plain f32 stores of K-split partial planes; whoever consumes them (the next rows_quantize) adds them up.
 #include <cstdlib>
@@ -53,14 +53,14 @@ constexpr int kGmMaxChunk = 128;                    // activation rows per chunk
 constexpr int kGmPartSlices = 16;                   // 32-column slices per weight stage
 constexpr int kGmWRow = kTileBytes;                 // 4352: one tile, quants then scales, as streamed
 constexpr int kGmWStage = kGmRG * kGmWRow;          // 69632 per 128 weight rows
-constexpr int kGmXTerms = 2;                        // binary16 terms per activation element
+constexpr int kGmXTerms = 2;                        // binary16 terms per activation element (the kernel's two-instruction scheme assumes 2)
 constexpr int kGmStep = 2;                          // 32-column slices per hand-over at 64 / 128 rows per chunk (4 at 32: GemmArgs::step) between the warps (every hand-over costs each single-threaded role
                                                     // several hundred cycles of its own, whatever the amount of work behind it)
 constexpr int kGmXStageMax = kGmStep * kGmXTerms * kGmMaxChunk * 32 * 2;   // 32768: the activation terms of one step of a 128-row chunk
 constexpr int kGmWStages = 2, kGmCvtBufs = 4, kGmXStages = 2;
 constexpr uint32_t kGmCvtCols1 = 32 * kGmHB;                 // tensor-memory columns of one converted slice: per 128-row tile hi (16: 32 binary16 per row) | lo (16)
 constexpr int kGmCvtWarps = 8;
-constexpr int kGmThreads = (kGmCvtWarps + 2) * 32;   // + producer warp + tensor-core warp
+constexpr int kGmThreads = (kGmCvtWarps + 3) * 32;   // + activation producer warp + tensor-core warp + weight producer warp
 constexpr int kGmBarBytes = 512;
 constexpr size_t kGmSmem = kGmBarBytes + 128 + (size_t)kGmWStages * kGmWStage + (size_t)kGmXStages * kGmXStageMax;
 constexpr int kGmWExp = 10;                         // weights enter as 2^10 w
@@ -81,7 +81,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch, int tid, int
     return t;
 }
 
-// activation operand: [chunk][K / 32 slices][kGmXTerms terms][4 groups of 8 columns][chunk rows][16 bytes]
+// activation operand: [chunk][K / 32 slices][4 groups of 8 columns][kGmXTerms terms][chunk rows][16 bytes]: within a column group the
+// rows of the first term are followed by the rows of the second, so ONE operand descriptor of 2 x chunk rows covers both terms
 __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     extern __shared__ __align__(16) float rowbuf[];          // K floats + 8 words of reduction scratch
     const int m = blockIdx.x, tid = threadIdx.x;
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
     if (m >= a.M) {
         // padding row of the last chunk: zeros
         for (int ch = tid; ch < nb * kGmXTerms * 4; ch += 256) {
-            const int s = ch / (kGmXTerms * 4), tc = ch - s * (kGmXTerms * 4);           // (term, column group) of slice s
+            const int s = ch / (kGmXTerms * 4), tc = ch - s * (kGmXTerms * 4);           // (column group, term) of slice s
             *(uint4*)(xq_chunk + (size_t)s * slice_bytes + (size_t)tc * nc * 16 + ml * 16) = make_uint4(0u, 0u, 0u, 0u);
         }
         if (tid == 0) a.sx[m] = 0.0f;
@@ -169,10 +170,10 @@ __global__ void __launch_bounds__(256) rows_quantize(const RowsArgs a) {
             t3[j] = (uint32_t)__half_as_ushort(h[0][2]) | ((uint32_t)__half_as_ushort(h[1][2]) << 16);
         }
         const int s = c8 >> 2, cg = c8 & 3;
-        unsigned char* dst = xq_chunk + (size_t)s * slice_bytes + (size_t)cg * nc * 16 + ml * 16;
+        unsigned char* dst = xq_chunk + (size_t)s * slice_bytes + (size_t)cg * kGmXTerms * nc * 16 + ml * 16;
         *(uint4*)(dst) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
-        *(uint4*)(dst + (size_t)4 * nc * 16) = make_uint4(t2[0], t2[1], t2[2], t2[3]);
-        if (kGmXTerms > 2) *(uint4*)(dst + (size_t)8 * nc * 16) = make_uint4(t3[0], t3[1], t3[2], t3[3]);
+        *(uint4*)(dst + (size_t)nc * 16) = make_uint4(t2[0], t2[1], t2[2], t2[3]);
+        if (kGmXTerms > 2) *(uint4*)(dst + (size_t)2 * nc * 16) = make_uint4(t3[0], t3[1], t3[2], t3[3]);
     }
 }
 
@@ -241,7 +242,8 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     const uint32_t bars = smem_u32(smem);
     const uint32_t wfull = bars, wempty = bars + 16, xfull = bars + 32, xempty = bars + 96, cfull = bars + 160, cempty = bars + 224,
                    afull = bars + 288, aempty = bars + 296, fin = bars + 304, tmem_slot = bars + 312;
-    static_assert(kGmXStages <= 8 && kGmCvtBufs <= 8 && kGmCvtCol0 + kGmCvtBufs * kGmCvtCols1 * kGmStep <= kGmTmemCols, "barrier area / tensor memory");
+    static_assert(kGmXStages <= 8 && kGmCvtBufs <= 8 && kGmCvtCol0 + kGmCvtBufs * kGmCvtCols1 * kGmStep <= kGmTmemCols && kGmXTerms == 2 &&
+                  kGmHB * 2 * kGmMaxChunk <= (int)kGmCvtCol0, "barrier area / tensor memory");
     unsigned char* wst = (unsigned char*)(((uintptr_t)smem + kGmBarBytes + 127) & ~(uintptr_t)127);
     unsigned char* xst = wst + (size_t)kGmWStages * kGmWStage;
     volatile int* abort = &s_abort;
@@ -277,48 +279,56 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
     const int n_items = tiles * a.ksplit * a.m_chunks;
     auto fail = [&](uint32_t code) { if (!*abort) { atomicOr(a.status, code); *abort = 1; } };
 
+    if (warp == kGmCvtWarps + 2) {
+        // ---------------------------------------------------------------- weight producer warp
+        // Lane 0 waits for a free stage and arms its barrier; the 16 tile copies of a stage are then issued by 16 lanes side by side
+        // (a bulk copy costs the copy engine about 50 ns whatever its size; one lane issuing them one after the other is slower
+        // still).  A warp of its own: in one warp with the activation copies, the next weight stage was only asked for after the
+        // current K-tile's last activation stage had found a free slot — a third of the converters' time went into waiting for it.
+        uint32_t wi = 0;
+        int ok = 1;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const GemmItem it = gemm_item(a, item, tpr);
+            const unsigned char* wseg = a.seg[it.seg].w;
+            for (int t = it.t0; t < it.t1 && ok; t++) {
+                const uint32_t ws = wi & 1u;
+                if (lane == 0) {
+                    if (!mbar_wait_abortable(wempty + 8u * ws, ((wi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = 0; }
+                    else mbar_arrive_expect_tx(wfull + 8u * ws, (uint32_t)it.n_rg * kGmWRow);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                for (int j = lane; j < it.n_rg; j += 32)
+                    bulk_g2s(smem_u32(wst + (size_t)ws * kGmWStage + (size_t)j * kGmWRow), wseg + ((size_t)(it.rg0 + j) * tpr + t) * kTileBytes, kTileBytes,
+                             wfull + 8u * ws);
+                wi++;
+            }
+        }
+        // never leave while a copy into this CTA's shared memory may be in flight: wait (bounded) for what was armed
+        if (!ok && lane == 0)
+            for (uint32_t k = 0; k < 2 && k < wi; k++) { const uint32_t i = wi - 1 - k; mbar_wait(wfull + 8u * (i & 1u), (i >> 1) & 1u); }
+        return;
+    }
     if (warp == kGmCvtWarps) {
-        // ---------------------------------------------------------------- producer warp
-        // Lane 0 waits for a free stage and arms its barrier; the weight copies of a stage (two per row group) are then issued
-        // by 32 lanes side by side — issued by one lane, one after the other, they are what bounds the kernel (measured: about
-        // 75 ns per copy).  The activation slices are one large copy each and stay with lane 0.
-        {
-            uint32_t wi = 0, xi = 0;
-            int ok = 1;
+        // ---------------------------------------------------------------- activation producer: one lane, one 32 KiB copy per stage
+        if (lane == 0) {
+            uint32_t xi = 0;
+            bool ok = true;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 const GemmItem it = gemm_item(a, item, tpr);
-                const unsigned char* wseg = a.seg[it.seg].w;
                 for (int t = it.t0; t < it.t1 && ok; t++) {
-                    const uint32_t ws = wi & 1u;
-                    if (lane == 0) {
-                        if (!mbar_wait_abortable(wempty + 8u * ws, ((wi >> 1) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = 0; }
-                        else mbar_arrive_expect_tx(wfull + 8u * ws, (uint32_t)it.n_rg * kGmWRow);
+                    for (int s = 0; s < kGmPartSlices; s += sps) {
+                        const uint32_t xs = xi % nxs;
+                        if (!mbar_wait_abortable(xempty + 8u * xs, ((xi / nxs) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = false; break; }
+                        mbar_arrive_expect_tx(xfull + 8u * xs, x_slice * (uint32_t)sps);
+                        bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStageMax), (const unsigned char*)a.xq + ((size_t)it.mc * nb + (size_t)t * 16 + s) * x_slice,
+                                 x_slice * (uint32_t)sps, xfull + 8u * xs);
+                        xi++;
                     }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) break;
-                    for (int j = lane; j < it.n_rg; j += 32)
-                        bulk_g2s(smem_u32(wst + (size_t)ws * kGmWStage + (size_t)j * kGmWRow), wseg + ((size_t)(it.rg0 + j) * tpr + t) * kTileBytes, kTileBytes,
-                                 wfull + 8u * ws);
-                    wi++;
-                    if (lane == 0) {
-                        for (int s = 0; s < kGmPartSlices && ok; s += sps) {
-                            const uint32_t xs = xi % nxs;
-                            if (!mbar_wait_abortable(xempty + 8u * xs, ((xi / nxs) & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_EMPTY); ok = 0; break; }
-                            mbar_arrive_expect_tx(xfull + 8u * xs, x_slice * (uint32_t)sps);
-                            bulk_g2s(smem_u32(xst + (size_t)xs * kGmXStageMax), (const unsigned char*)a.xq + ((size_t)it.mc * nb + (size_t)t * 16 + s) * x_slice,
-                                     x_slice * (uint32_t)sps, xfull + 8u * xs);
-                            xi++;
-                        }
-                    }
-                    xi = __shfl_sync(0xffffffffu, xi, 0);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
                 }
             }
-            if (!ok && lane == 0) {
-                // never leave while a copy into this CTA's shared memory may be in flight: wait (bounded) for what was armed
-                for (uint32_t k = 0; k < 2 && k < wi; k++) { const uint32_t i = wi - 1 - k; mbar_wait(wfull + 8u * (i & 1u), (i >> 1) & 1u); }
+            if (!ok)
                 for (uint32_t k = 0; k < nxs && k < xi; k++) { const uint32_t i = xi - 1 - k; mbar_wait(xfull + 8u * (i % nxs), (i / nxs) & 1u); }
-            }
         }
         return;
     }
@@ -327,9 +337,13 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
         if (lane == 0) {
             uint32_t xi = 0, ci = 0, ic = 0;
             bool ok = true;
-            const uint32_t idesc = umma_idesc_f16(128, nc);
-            // activation operand descriptors: start address in the low 14 bits; column groups nc * 16 bytes apart, 8-row groups 128
-            const uint32_t x_lo = (((uint32_t)nc * 16u >> 4) & 0x3fffu) << 16, x_hi = umma_desc_hi(128u), x_base = smem_u32(xst);
+            // hi x [x1 | x2] is ONE instruction of N = 2 nc (its two halves of the accumulator are added when it is stored), lo x x1
+            // one of N = nc into the first half: two instructions per 16 columns of K instead of three (an instruction costs its
+            // issuing thread about 80 cycles whatever its N: at nc = 32 that, not the tensor core, bounds the kernel)
+            const uint32_t idesc2 = umma_idesc_f16(128, 2 * nc), idesc1 = umma_idesc_f16(128, nc);
+            // activation operand descriptors: start address in the low 14 bits; column groups 2 nc * 16 bytes apart, 8-row groups 128
+            const uint32_t x_cg = (uint32_t)kGmXTerms * (uint32_t)nc * 16u;
+            const uint32_t x_lo = ((x_cg >> 4) & 0x3fffu) << 16, x_hi = umma_desc_hi(128u), x_base = smem_u32(xst);
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ic++) {
                 const GemmItem it = gemm_item(a, item, tpr);
                 if (!mbar_wait_abortable(aempty, (ic & 1u) ^ 1u, abort)) { fail(LUM_ST_WAIT_TMEM); break; }      // the previous item's sums were stored
@@ -351,15 +365,14 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                             for (int kk = 0; kk < 2 * step; kk++) {     // K = 16 per instruction: two per 32-column slice
                                 // weights: tensor memory, 8 columns (16 binary16) per instruction; activations: shared memory,
                                 // [column group of 8][row][16 bytes], an instruction reads two adjacent column groups
-                                const uint32_t xo = xb + (uint32_t)(kk >> 1) * x_slice + (uint32_t)(kk & 1) * 2u * (uint32_t)nc * 16u;
-                                const uint32_t x1 = x_lo | ((xo >> 4) & 0x3fffu), x2 = x_lo | (((xo + x_term) >> 4) & 0x3fffu);
+                                const uint32_t xo = xb + (uint32_t)(kk >> 1) * x_slice + (uint32_t)(kk & 1) * 2u * x_cg;
+                                const uint32_t x12 = x_lo | ((xo >> 4) & 0x3fffu);
 #pragma unroll
                                 for (int hb = 0; hb < kGmHB; hb++) {      // the 128-row tiles of the item
-                                    const uint32_t acc = tmem + (uint32_t)hb * (uint32_t)kGmMaxChunk;
+                                    const uint32_t acc = tmem + (uint32_t)hb * 2u * (uint32_t)kGmMaxChunk;
                                     const uint32_t hi = wt + (uint32_t)(kk >> 1) * 32u * kGmHB + (uint32_t)hb * 32u + (uint32_t)(kk & 1) * 8u, lo = hi + 16u;
-                                    umma_f16_ts2(acc, hi, x1, x_hi, idesc, started);
-                                    umma_f16_ts2(acc, hi, x2, x_hi, idesc, 1u);
-                                    umma_f16_ts2(acc, lo, x1, x_hi, idesc, 1u);
+                                    umma_f16_ts2(acc, hi, x12, x_hi, idesc2, started);
+                                    umma_f16_ts2(acc, lo, x12, x_hi, idesc1, 1u);
                                 }
                                 started = 1u;
                             }
@@ -450,13 +463,15 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
                 const bool row_live = (n_st >> 3) < it.n_rg;
                 float* yp = a.y + (size_t)it.ks * a.part_stride + sg.col0 + it.rg0 * kTileRows + n_st;
                 for (int c0 = 0; c0 < half_rows; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem + lane_addr + (uint32_t)hb * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0), v);
+                    uint32_t v[16], v2[16];
+                    const uint32_t col = tmem + lane_addr + (uint32_t)hb * 2u * (uint32_t)kGmMaxChunk + (uint32_t)(ch * half_rows + c0);
+                    tmem_ld16(col, v);
+                    tmem_ld16(col + (uint32_t)nc, v2);              // the x2 half of the accumulator
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         const int m = it.mc * nc + ch * half_rows + c0 + i;
-                        if (row_live && m < a.M) yp[(size_t)m * a.ldy] = __uint_as_float(v[i]) * __ldg(a.sx + m);
+                        if (row_live && m < a.M) yp[(size_t)m * a.ldy] = (__uint_as_float(v[i]) + __uint_as_float(v2[i])) * __ldg(a.sx + m);
                     }
                 }
             }
@@ -474,15 +489,26 @@ __global__ void __launch_bounds__(kGmThreads, 1) q8_gemm_tc(const GemmArgs a) {
 size_t gemm_xq_bytes(int M, int K) { const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * K * 2 * kGmXTerms; }
 size_t gemm_sx_bytes(int M, int K) { (void)K; const int nc = gemm_chunk_rows(M); return (size_t)((M + nc - 1) / nc) * nc * 4; }
 
-// K ranges per product: enough work items to occupy every SM a couple of times over, each range at least one K-tile
+// K ranges per product.  Work items are equal, so a product takes ceil(items / SMs) rounds of one item each: with few items per SM
+// the last, partly filled round is a large share of the time (224 tiles over 148 SMs: 2 rounds for 1.5 rounds of work).  Cutting K
+// makes the rounds shorter and the loss smaller, but every item pays its own pipeline fill and store, and every extra range
+// writes (and the consumer reads) another plane of partial sums.  The estimate below weighs the three; its constants are
+// measured orders of magnitude (a K-tile of one item: 4 us at 32 rows per chunk, 9.5 us at 128; an item's own cost: a third of a
+// tile; plane traffic at the HBM copy rate), not a fit.
 int gemm_pick_ksplit(int n_rows_total, int M, int K, int sm_count) {
     const int nc = gemm_chunk_rows(M);
     const int tiles = (n_rows_total + kGmRows - 1) / kGmRows, mc = (M + nc - 1) / nc, tpr = K / kTileK;
-    int ks = (2 * sm_count + tiles * mc - 1) / (tiles * mc);
-    if (ks > tpr) ks = tpr;
-    if (ks > 8) ks = 8;
-    if (ks < 1) ks = 1;
-    return ks;
+    const double t_tile = 16.0 * (0.16 + 0.43 * nc / 128.0);                     // us per K-tile of one item
+    const double plane_us = (double)M * n_rows_total * 8.0 / 6.5e6;               // write + read of one plane of partial sums
+    int best = 1;
+    double best_t = 1e30;
+    for (int ks = 1; ks <= 8 && ks <= tpr; ks++) {
+        const long long items = (long long)tiles * mc * ks;
+        const long long rounds = (items + sm_count - 1) / sm_count;
+        const double t = (double)rounds * ((double)tpr / ks + 0.33) * t_tile + (ks - 1) * plane_us;
+        if (t < best_t * 0.97) { best_t = t; best = ks; }                         // a larger split has to pay for itself
+    }
+    return best;
 }
 
 cudaError_t launch_rows_quantize(const RowsArgs& a_in, cudaStream_t st) {
