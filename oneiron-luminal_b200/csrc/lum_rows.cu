@@ -15,6 +15,8 @@
 // written here equals the row the single-token path writes for the same inputs.
 #include "lum_attn_dev.cuh"
 #include "lum_gemv_dev.cuh"
+#include <cstdlib>
+
 #include "lum_rows.cuh"
 
 namespace lum {
@@ -203,6 +205,169 @@ __global__ void __launch_bounds__(256) attn_rows(const AttnRowsArgs a) {
     }
 }
 
+// The same attention for rows of a bfloat16 cache, reorganised so that no dot product needs a shuffle: used for batched decode
+// (every row its own sequence with a long context), where the kernel above — one warp per key, five shuffles per key and query head
+// — runs at a fifth of the memory rate.  One CTA per (KV head, row, split of the cached positions), 4 warps; a warp takes 32 keys at
+// a time:
+//   scores  : lane = key.  The lane reads its key's row (16-byte loads) and multiplies it with the group's queries from shared
+//             memory (the same address in every lane: a broadcast).
+//   softmax : per warp and query head, one max-reduction per 32 keys; the weights go to shared memory.
+//   values  : lane = HD / 32 head dimensions.  The 32 value rows are read coalesced, each weighted by its key's weight from shared
+//             memory (a broadcast again).
+// The warps' (max, sum, output) triples are merged in shared memory; with more than one split the CTA writes its triple to global
+// memory and attn_rows_merge folds the splits.
+template <int HD, int GM>
+__global__ void __launch_bounds__(128) attn_rows_split(const AttnRowsArgs a, int n_splits) {
+    constexpr int DPL = HD / 32, NW = 4;
+    __shared__ __align__(16) float s_q[GM][HD];
+    __shared__ float s_p[NW][GM][32];
+    __shared__ float s_m[NW][GM], s_l[NW][GM];
+    __shared__ float s_o[NW][GM][HD];
+    const int kvh = blockIdx.x, m = blockIdx.y, sp = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = a.n_q / a.n_kv;
+    const int pos = a.row_pos[m];
+    const int seq = a.row_seq ? a.row_seq[m] : a.seq0;
+    if (pos < 0 || pos >= a.max_seq || seq < 0 || seq >= a.max_batch) return;       // flagged by the append kernel
+    const int n_keys = pos + 1;
+    const int per = ((n_keys + n_splits - 1) / n_splits + 31) & ~31;                // keys per split, whole 32-key tiles
+    const int k0 = sp * per, k1 = min(n_keys, k0 + per);
+    const size_t row_elems = (size_t)a.n_kv * HD;
+    const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache + (size_t)seq * a.max_seq * row_elems + (size_t)kvh * HD;
+    const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache + (size_t)seq * a.max_seq * row_elems + (size_t)kvh * HD;
+    const float scale = 1.0f / sqrtf((float)HD);
+    for (int i = tid; i < GM * HD; i += 128) {
+        const int g = i / HD, e = i - g * HD;
+        s_q[g][e] = g < G ? a.q_rot[(size_t)m * a.n_q * HD + ((size_t)kvh * G + g) * HD + e] : 0.0f;
+    }
+    __syncthreads();
+    float o[GM][DPL], mx[GM], l[GM];
+#pragma unroll
+    for (int g = 0; g < GM; g++) {
+        mx[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) o[g][i] = 0.0f;
+    }
+#pragma unroll 1
+    for (int j0 = k0 + warp * 32; j0 < k1; j0 += NW * 32) {
+        const int j = j0 + lane;
+        const bool live = j < k1;
+        // ---- scores of this lane's key
+        float sc[GM];
+#pragma unroll
+        for (int g = 0; g < GM; g++) sc[g] = 0.0f;
+        const uint4* krow = (const uint4*)(kc + (size_t)(live ? j : k0) * row_elems);
+#pragma unroll 4
+        for (int c = 0; c < HD / 8; c++) {
+            const uint4 raw = krow[c];
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            float kf[8];
+#pragma unroll
+            for (int t = 0; t < 4; t++) { kf[2 * t] = __uint_as_float(w[t] << 16); kf[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u); }
+#pragma unroll
+            for (int g = 0; g < GM; g++) {
+                const float4 q0 = *(const float4*)&s_q[g][c * 8], q1 = *(const float4*)&s_q[g][c * 8 + 4];
+                sc[g] = fmaf(q0.x, kf[0], sc[g]); sc[g] = fmaf(q0.y, kf[1], sc[g]); sc[g] = fmaf(q0.z, kf[2], sc[g]); sc[g] = fmaf(q0.w, kf[3], sc[g]);
+                sc[g] = fmaf(q1.x, kf[4], sc[g]); sc[g] = fmaf(q1.y, kf[5], sc[g]); sc[g] = fmaf(q1.z, kf[6], sc[g]); sc[g] = fmaf(q1.w, kf[7], sc[g]);
+            }
+        }
+        // ---- softmax bookkeeping per query head; weights to shared memory
+        float corr[GM];
+#pragma unroll
+        for (int g = 0; g < GM; g++) {
+            const float logit = live ? sc[g] * scale : -INFINITY;
+            float tm = logit;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, of));
+            const float mn = fmaxf(mx[g], tm);                       // finite: a tile always holds at least one live key
+            corr[g] = (mx[g] == -INFINITY) ? 0.0f : expf(mx[g] - mn);
+            const float p = live ? expf(logit - mn) : 0.0f;
+            l[g] = l[g] * corr[g] + p;                               // per-lane partial sums, folded at the end
+            mx[g] = mn;
+            s_p[warp][g][lane] = p;
+        }
+        __syncwarp();
+        // ---- weighted values: lane = DPL head dimensions
+#pragma unroll
+        for (int g = 0; g < GM; g++)
+#pragma unroll
+            for (int i = 0; i < DPL; i++) o[g][i] *= corr[g];
+        const int nk = min(32, k1 - j0);
+#pragma unroll 4
+        for (int t = 0; t < nk; t++) {
+            const __nv_bfloat16* vrow = vc + (size_t)(j0 + t) * row_elems + lane * DPL;
+            float vf[DPL];
+            if (DPL == 4) {
+                const uint2 raw = *(const uint2*)vrow;
+                vf[0] = __uint_as_float(raw.x << 16); vf[1] = __uint_as_float(raw.x & 0xffff0000u);
+                vf[2 % DPL] = __uint_as_float(raw.y << 16); vf[3 % DPL] = __uint_as_float(raw.y & 0xffff0000u);
+            } else {
+                const uint32_t raw = *(const uint32_t*)vrow;
+                vf[0] = __uint_as_float(raw << 16); vf[1] = __uint_as_float(raw & 0xffff0000u);
+            }
+#pragma unroll
+            for (int g = 0; g < GM; g++) {
+                const float p = s_p[warp][g][t];
+#pragma unroll
+                for (int i = 0; i < DPL; i++) o[g][i] = fmaf(p, vf[i], o[g][i]);
+            }
+        }
+        __syncwarp();
+    }
+    // ---- fold the lanes' sums, then the warps
+#pragma unroll
+    for (int g = 0; g < GM; g++) {
+        float lt = l[g];
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, of);
+        if (lane == 0) { s_m[warp][g] = mx[g]; s_l[warp][g] = lt; }
+#pragma unroll
+        for (int i = 0; i < DPL; i++) s_o[warp][g][lane * DPL + i] = o[g][i];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += 128) {
+        const int g = idx / HD, e = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; w++) M = fmaxf(M, s_m[w][g]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) {
+            const float c = (s_m[w][g] == -INFINITY) ? 0.0f : expf(s_m[w][g] - M);
+            L = fmaf(s_l[w][g], c, L);
+            O = fmaf(s_o[w][g][e], c, O);
+        }
+        const size_t head = (size_t)m * a.n_q + (size_t)kvh * G + g;
+        if (n_splits == 1) {
+            a.out[head * HD + e] = O * (1.0f / L);
+        } else {
+            float* pp = a.part + (head * n_splits + sp) * (HD + 2);
+            pp[e] = O;
+            if (e == 0) { pp[HD] = M; pp[HD + 1] = L; }                // a split without keys leaves M = -inf, L = 0
+        }
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD) attn_rows_merge(const AttnRowsArgs a, int n_splits) {
+    const int head = blockIdx.x, m = blockIdx.y, e = threadIdx.x;
+    const int pos = a.row_pos[m];
+    const int seq = a.row_seq ? a.row_seq[m] : a.seq0;
+    if (pos < 0 || pos >= a.max_seq || seq < 0 || seq >= a.max_batch) return;
+    const float* pp = a.part + (((size_t)m * a.n_q + head) * n_splits) * (HD + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, pp[(size_t)s * (HD + 2) + HD]);
+    float L = 0.0f, O = 0.0f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ms = pp[(size_t)s * (HD + 2) + HD];
+        const float c = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+        L = fmaf(pp[(size_t)s * (HD + 2) + HD + 1], c, L);
+        O = fmaf(pp[(size_t)s * (HD + 2) + e], c, O);
+    }
+    a.out[((size_t)m * a.n_q + head) * HD + e] = O * (1.0f / L);
+}
+
+size_t attn_rows_part_floats(int rows, int n_q, int hd) { return (size_t)rows * n_q * kAttnRowsMaxSplits * (hd + 2); }
+
 // ---------------------------------------------------------------------------------------------------- greedy sample per row
 // One CTA per row: logits[m][:] = sum of the vocabulary projection's partial planes (written back to plane 0), the greedy
 // sample (last maximum wins), and the bookkeeping of a batched decode step: the sample becomes the row's next token, its
@@ -265,6 +430,25 @@ cudaError_t launch_rope_append_rows(const RopeRowsArgs& a, cudaStream_t st) {
 
 cudaError_t launch_attn_rows(const AttnRowsArgs& a, cudaStream_t st) {
     const int G = a.n_kv > 0 ? a.n_q / a.n_kv : 0;
+    static const int env_split = [] { const char* e = getenv("LUM_ATTN_ROWS_SPLIT"); return e ? atoi(e) : 1; }();
+    if (env_split && a.kv_bf16 && a.window == 0 && (a.hd == 128 || a.hd == 64) && G >= 1 && G <= 8 && (((uintptr_t)a.k_cache | (uintptr_t)a.v_cache) & 15) == 0 &&
+        ((size_t)a.n_kv * a.hd * 2) % 16 == 0) {
+        // enough CTAs for a few waves over the SMs; a split is at least 64 keys long only when the context is (the kernel handles empty splits)
+        int splits = 1;
+        if (a.part && a.M <= a.part_rows) {
+            splits = (4 * 148 + a.n_kv * a.M - 1) / (a.n_kv * a.M);
+            if (splits > kAttnRowsMaxSplits) splits = kAttnRowsMaxSplits;
+            if (splits < 1) splits = 1;
+        }
+        AttnRowsArgs b = a;
+        void* params[] = {&b, &splits};
+        const void* fn = a.hd == 128 ? (G <= 4 ? (const void*)attn_rows_split<128, 4> : (const void*)attn_rows_split<128, 8>)
+                                     : (G <= 4 ? (const void*)attn_rows_split<64, 4> : (const void*)attn_rows_split<64, 8>);
+        cudaError_t e = cudaLaunchKernel(fn, dim3(a.n_kv, a.M, splits), dim3(128), params, 0, st);
+        if (e != cudaSuccess || splits == 1) return e;
+        const void* fm = a.hd == 128 ? (const void*)attn_rows_merge<128> : (const void*)attn_rows_merge<64>;
+        return cudaLaunchKernel(fm, dim3(a.n_q, a.M), dim3(a.hd), params, 0, st);
+    }
     const void* fn = nullptr;
     const bool bf = a.kv_bf16 != 0;
     if (a.hd == 128 && G >= 1 && G <= 4) fn = bf ? (const void*)attn_rows<128, 4, true> : (const void*)attn_rows<128, 4, false>;

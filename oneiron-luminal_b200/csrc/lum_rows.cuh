@@ -59,6 +59,7 @@ struct AttnRowsArgs {
     float* out;                // [M][n_q * hd]
     int M, n_q, n_kv, hd, kv_bf16, window, max_seq, max_batch;
     uint32_t* status;
+    float* part; int part_rows;     // attn_rows_split: partial results [row][query head][split][head dim + 2], room for part_rows rows
 };
 struct ArgmaxRowsArgs {
     float* logits;             // [n_parts][M][vocab]; the sums end up in plane 0
@@ -78,6 +79,8 @@ cudaError_t launch_gemm(const GemmArgs& a, int sm_count, cudaStream_t st);
 cudaError_t launch_embed_rows(const void* table, int kind, int H, int vocab, const int* row_tok, float* x, int M, uint32_t* status, cudaStream_t st);
 cudaError_t launch_rope_append_rows(const RopeRowsArgs& a, cudaStream_t st);
 cudaError_t launch_attn_rows(const AttnRowsArgs& a, cudaStream_t st);
+constexpr int kAttnRowsMaxSplits = 8;
+size_t attn_rows_part_floats(int rows, int n_q, int hd);
 bool attn_prompt_tc_supported(const AttnRowsArgs& a);            // lum_attn_tc.cu: rows of one sequence, bf16 cache, head dimension 128
 cudaError_t launch_attn_prompt_tc(const AttnRowsArgs& a, cudaStream_t st);
 cudaError_t launch_argmax_rows(const ArgmaxRowsArgs& a, cudaStream_t st);

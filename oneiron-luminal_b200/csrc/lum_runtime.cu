@@ -172,6 +172,7 @@ struct lum_rt {
         int cap = 0;                      // rows a pass can take
         int *tok = nullptr, *pos = nullptr, *seq = nullptr;          // [cap] per-row token / position / sequence
         float *xr = nullptr, *q_rot = nullptr, *attn = nullptr;      // residual rows [cap][H]; rotated queries and attention output [cap][qd]
+        float* attn_part = nullptr; int attn_part_rows = 0;          // split partials of the few-rows attention kernel
         float *qkv = nullptr, *o = nullptr, *gu = nullptr, *down = nullptr, *logits = nullptr;   // K-split partial planes of the products
         int8_t* xq = nullptr; float* sx = nullptr;                   // quantised activation rows of the product in flight
         std::vector<int32_t> h_tok, h_pos;
@@ -725,6 +726,8 @@ int ensure_rows(lum_rt* rt, int want_rows) {
     if (int r = dev_alloc(rt, (void**)&b.xr, (size_t)cap * H * 4)) return r;
     if (int r = dev_alloc(rt, (void**)&b.q_rot, (size_t)cap * qd * 4)) return r;
     if (int r = dev_alloc(rt, (void**)&b.attn, (size_t)cap * qd * 4)) return r;
+    b.attn_part_rows = cap < 256 ? cap : 256;
+    if (int r = dev_alloc(rt, (void**)&b.attn_part, attn_rows_part_floats(b.attn_part_rows, rt->nq_l, hd) * 4)) return r;
     if (int r = dev_alloc(rt, (void**)&b.qkv, rows_parts_floats(rt, W, H, cap) * 4)) return r;
     if (int r = dev_alloc(rt, (void**)&b.o, rows_parts_floats(rt, H, qd, cap) * 4)) return r;
     if (int r = dev_alloc(rt, (void**)&b.gu, rows_parts_floats(rt, 2 * F, H, cap) * 4)) return r;
@@ -788,7 +791,7 @@ int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int se
             AttnRowsArgs a{};
             a.q_rot = b.q_rot; a.k_cache = w.kc; a.v_cache = w.vc; a.row_pos = d_pos; a.row_seq = d_seq; a.seq0 = seq0; a.out = b.attn;
             a.M = M; a.n_q = rt->nq_l; a.n_kv = rt->nkv_l; a.hd = hd; a.kv_bf16 = t.kv_bf16; a.window = 0; a.max_seq = d.max_seq; a.max_batch = rt->max_batch;
-            a.status = rt->status;
+            a.status = rt->status; a.part = b.attn_part; a.part_rows = b.attn_part_rows;
             // many rows of one sequence (a prompt): the tensor-core kernel; few rows, or rows of different sequences: one CTA per row
             static const int env_tc = [] { const char* e = getenv("LUM_ATTN_TC"); return e ? atoi(e) : 1; }();
             if (env_tc && M >= 16 && attn_prompt_tc_supported(a)) CU(rt, launch_attn_prompt_tc(a, st));
