@@ -123,6 +123,12 @@ CONFIGS: Dict[str, ModelDesc] = {
                        rope_theta=150000.0, rope_style=2, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"],
                        sliding_window=8, window_even_layers=1, attn_sinks=1, proj_bias=1, yarn_factor=32.0, yarn_beta_fast=32.0,
                        yarn_beta_slow=1.0, yarn_orig_max_pos=4096.0, n_experts=8, top_k=4, swiglu_limit=7.0),
+    # the gpt-oss-20B layer's own awkward sizes, small: hidden 576 and expert width 352 are whole 32-blocks but not whole tiles, and the
+    # per-expert activation block of the down kernel (3 * 352 + 44 = 1100 bytes) is not a multiple of 16 (2880: 9000 bytes, the same class)
+    "small_oss_352": _desc(n_layers=2, hidden=576, n_q_heads=16, n_kv_heads=2, head_dim=64, ffn=352, vocab=2048, max_seq=128,
+                           rope_theta=150000.0, rope_style=2, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"],
+                           sliding_window=8, window_even_layers=1, attn_sinks=1, proj_bias=1, yarn_factor=32.0, yarn_beta_fast=32.0,
+                           yarn_beta_slow=1.0, yarn_orig_max_pos=4096.0, n_experts=8, top_k=4, swiglu_limit=7.0),
     # the attention features alone on a dense FFN (window, sinks, biases, YaRN), hidden not a multiple of the tile width
     "small_oss_dense": _desc(n_layers=3, hidden=576, n_q_heads=16, n_kv_heads=2, head_dim=64, ffn=1152, vocab=2048, max_seq=128,
                              rope_theta=150000.0, rope_style=2, weight_dtype=DTYPE["q8_0"], embed_dtype=DTYPE["bf16"], kv_dtype=DTYPE["bf16"],

@@ -490,7 +490,7 @@ def test_batched_decode_equals_sequences_decoded_alone(pkg):
 
 
 # ------------------------------------------------------------------------------------------------- gpt_oss-style layers
-@pytest.mark.parametrize("name", ["small_oss_dense", "small_oss"])
+@pytest.mark.parametrize("name", ["small_oss_dense", "small_oss", "small_oss_352"])
 def test_gpt_oss_style_layers_match_oracle(pkg, name):
     """Sliding window on the even layers (8 positions, so a 30-token run leaves it), per-head sink logits, biases on q/k/v/o,
     YaRN rotation — and, for `small_oss`, the routed experts (top-4 of 8, gate_up interleaved, clamp, weighted sum) — against
