@@ -442,7 +442,9 @@ def test_prompt_rows_in_chunks_and_after_a_prefix(pkg):
     try:
         two = pkg.B200Runtime.initialize(device=0, prefill_min_rows=2)
         two.load_model(desc); two.synth(5)
-        assert two.generate(prompt, 8) == base and (two.get_f32() == la).all()     # passes of 32, 32, 26 rows: the same arithmetic per row
+        # passes of 32, 32, 26 rows: the same tokens; the logits agree to accumulation order (a pass of at most 64 rows adds the two
+        # activation terms' products up separately and joins them at the end, a pass of more rows interleaves them)
+        assert two.generate(prompt, 8) == base and rel_err(two.get_f32(), la) <= 1e-4
         two.kv_reset(); two.decode_reset()
         two.set_data(prompt[:41]); two.execute({"s": 41, "p": 0})
         two.set_data(prompt[41:]); two.execute({"s": 49, "p": 41})
