@@ -205,6 +205,10 @@ int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float
  * element size.  After loading, set 'p' to the number of rows before the next lum_execute. */
 int32_t lum_kv_save(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, void* host_out, size_t bytes);
 int32_t lum_kv_load(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, const void* host, size_t bytes);
+/* Rows [0, rows) of every layer's K and V cache of sequence `src_seq` copied to sequence `dst_seq` on the device (both
+ * < max_batch): a prompt prefix computed once and shared by several sequences.  Asynchronous on the runtime's stream.  (The
+ * reference's caller would copy its own cache buffers, examples/llama/src/model.rs:194-223.) */
+int32_t lum_kv_copy(lum_rt* rt, int32_t src_seq, int32_t dst_seq, int32_t rows);
 
 /* ---------------------------------------------------------------------------------------------
  * Execution, at the level of the reference's decode loop (examples/llama/src/main.rs:82-118):
@@ -234,6 +238,25 @@ int32_t lum_decode_reset(lum_rt* rt);
 /* Block until all submitted work is done and report device-side status (LUM_E_DEVICE if a kernel flagged one). */
 int32_t lum_synchronize(lum_rt* rt);
 
+/* The sampler that follows the vocabulary projection.  The reference's loop only has the greedy `sample`
+ * (examples/llama/src/main.rs:137-148), which is this runtime's default; this entry replaces it, for lum_execute,
+ * lum_decode_greedy and lum_batch_decode alike, by a draw made on the device (no counterpart in the reference):
+ *   candidates = the top_k logits ordered by (value descending, index ascending), NaN counting as -inf (top_k 0 = 256, the most);
+ *   w_j = expf((l_j - l_0) / temperature); running f32 sums S_j; top_p < 1 (0 = 1) keeps the shortest prefix with
+ *   S_j >= top_p * S_last; u = 24 bits of a SplitMix64 finaliser of (seed, sequence, position of the drawn token) * 2^-24;
+ *   the draw is the first j with S_j > u * S_kept.
+ * A draw therefore depends only on (logits, parameters, seed, sequence index, position): replaying a sequence replays its
+ * draws.  `s` null, temperature <= 0 or top_k == 1 switch back to the greedy sample.  One GPU only (the logits of a
+ * tensor-parallel group are sharded by vocabulary), not with the persistent kernel. */
+typedef struct lum_sampling {
+    float temperature;
+    float top_p;
+    int32_t top_k;
+    int32_t reserved;
+    uint64_t seed;
+} lum_sampling;
+int32_t lum_set_sampling(lum_rt* rt, const lum_sampling* s);
+
 /* ---------------------------------------------------------------------------------------------
  * Several sequences (batch > 1).  The reference's graph has one dynamic row dimension 's' and a cache per layer
  * (examples/llama/src/model.rs:91-113, 194-223); with `max_batch` > 1 in lum_model_desc this runtime keeps that many
@@ -244,10 +267,16 @@ int32_t lum_synchronize(lum_rt* rt);
  *   lum_batch_decode(steps)    `steps` greedy tokens for every sequence: one row per sequence and step through the
  *                              tensor-core products, attention of each row over its own cache, a greedy sample per row,
  *                              fed back on the device;
- *   lum_batch_get_decoded      the log, [steps][n] row-major;  lum_batch_get_logits: the last step's logits of one sequence.
+ *   lum_batch_get_decoded      the log, [steps][n] row-major;  lum_batch_get_logits: the last step's logits of one row.
+ *   lum_batch_begin_slots      the same as lum_batch_begin for sequences in ANY cache slots: row i of the batch works on cache
+ *                              slot slots[i] (distinct, < max_batch).  A serving loop admits a request by filling a free slot
+ *                              (lum_seq_select + lum_execute, lum_kv_load or lum_kv_copy), retires one by leaving its slot out,
+ *                              and calls this between groups of steps with the slots that are live (continuous batching;
+ *                              oneiron-luminal_b200/serving.py is such a loop).
  * Needs Q8_0 weights in the packed layout and one GPU (no tensor parallelism). */
 int32_t lum_seq_select(lum_rt* rt, int32_t seq);
 int32_t lum_batch_begin(lum_rt* rt, int32_t n_seq, const int32_t* tokens, const int32_t* positions);
+int32_t lum_batch_begin_slots(lum_rt* rt, int32_t n_seq, const int32_t* slots, const int32_t* tokens, const int32_t* positions);
 int32_t lum_batch_decode(lum_rt* rt, int32_t n_steps);
 int32_t lum_batch_get_decoded(lum_rt* rt, int32_t* host_out, size_t n_steps);
 int32_t lum_batch_get_logits(lum_rt* rt, int32_t seq, float* host_out, size_t n);
@@ -343,6 +372,11 @@ int32_t lum_op_sample_q8_0(const void* packed_dev, int32_t n, int32_t k, const f
 int32_t lum_op_sample_q8_0_static(const void* packed_dev, int32_t n, int32_t k, const float* x_dev, float* logits_dev,
                                   int32_t* best_dev, void* stream);
 int32_t lum_op_gemv_f32(const float* w_dev, int32_t n, int32_t k, const float* x_dev, float* y_dev, void* stream);
+/* The sampler of lum_set_sampling as a stand-alone operator: one draw per row of logits_dev [n_rows][vocab]; row m belongs to
+ * sequence seq0 + m and draws for position positions_dev[m]; tokens_dev [n_rows] receives the draws.  The parameters travel
+ * through one small per-device buffer: one call at a time per device. */
+int32_t lum_op_sample_topk(const float* logits_dev, int32_t n_rows, int32_t vocab, const lum_sampling* s, int32_t seq0,
+                           const int32_t* positions_dev, int32_t* tokens_dev, void* stream);
 /* The stand-alone operators above run asynchronously; a bounded wait inside one of their kernels that ran out of budget leaves
  * a status word on the device.  This call synchronises `stream`, returns LUM_E_DEVICE (message through lum_last_error(NULL))
  * if any operator launched on the current device since the last call flagged one — the static-scratch entry included — and

@@ -8,7 +8,7 @@ reference's runtime interface (``luminal::op::Runtime``, src/op.rs:10-30, and th
 There is no CPU path: importing works anywhere, but creating a runtime without the built
 library or without a CUDA device raises.
 """
-from . import llir, tp  # noqa: F401
+from . import llir, serving, tp  # noqa: F401
 from .runtime import (  # noqa: F401
     B200Runtime,
     LumError,
@@ -24,6 +24,7 @@ from .runtime import (  # noqa: F401
     describe_llir_chunk,
     mbu,
     Stats,
+    Sampling,
     safetensors_read,
     safetensors_write,
 )

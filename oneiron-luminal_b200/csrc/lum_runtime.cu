@@ -28,6 +28,7 @@
 #include "lum_mega.cuh"
 #include "lum_rows.cuh"
 #include "lum_moe.cuh"
+#include "lum_sample.cuh"
 
 using namespace lum;
 
@@ -150,6 +151,9 @@ struct lum_rt {
     float* am_val = nullptr;
     int* am_idx = nullptr;
     unsigned int* am_cnt = nullptr;
+    SampleParams* d_sample = nullptr;   // device copy of `samp` (read by sample_rows: captured graphs stay valid when values change)
+    SampleParams samp{1.0f, 1.0f, 1, 0, 0ull};
+    bool sampling = false;              // false: the greedy sample of the head kernel / argmax_rows stands
     bool down_ksplit = true;          // LUM_DOWN_KSPLIT=0: the down projection as one job per row group
     bool attn_cluster = false;        // the splits of a KV head merge through a thread-block cluster (LUM_ATTN_CLUSTER=0: global partials + arrival ticket)
     bool kv_prefetch = true;          // LUM_KV_PREFETCH=0: attention does not warm L2 with its cached rows before the projections finish
@@ -306,7 +310,7 @@ void free_model(lum_rt* rt) {
     rt->g_batch = nullptr; rt->g_batch_n = 0; rt->batch_n = 0; rt->cur_seq = 0;
     rt->rows = lum_rt::Rows();
     rt->b_step = nullptr; rt->b_log = nullptr;
-    rt->attn_cnt = nullptr; rt->am_cnt = nullptr;
+    rt->attn_cnt = nullptr; rt->am_cnt = nullptr; rt->d_sample = nullptr;
     rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr; rt->step_ctr = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
     rt->allocs.clear();
@@ -606,6 +610,9 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.K = hw.kind == WK_Q8 ? (int)hw.kdev : H; a.k_norm = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
+        if (rt->sampling && tp) return fail(rt, LUM_E_UNSUPPORTED, "the sampler reads a whole row of logits on one GPU: not under tensor parallelism");
+        const bool draw = rt->sampling;
+        if (draw) { a.advance = 0; a.tokens_out = nullptr; }      // sample_rows below does the bookkeeping with its own draw
         take_partial(a);
         // exchange buffer, words 2048.. : the ranks' sampling pairs (16 bytes apart), words 2304.. : their "landed" words (128 apart)
         auto sym_pair = [&](unsigned char* base, int rank) { return (int*)(base + 2048 + (size_t)rank * 16); };
@@ -618,6 +625,12 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         }
         claim_ctr(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
+        if (draw) {
+            SampleArgs sa{};
+            sa.logits = rt->logits; sa.row_stride = (size_t)rt->vocab_l; sa.M = 1; sa.vocab = rt->vocab_l; sa.params = rt->d_sample;
+            sa.seq0 = rt->cur_seq; sa.state = rt->state; sa.tokens_out = rt->tokens_out;
+            CU(rt, launch_sample_rows(sa, st)); n++;
+        }
         if (fused) {
             // every rank's sampling kernel has written its pair into every rank's buffer: wait for the words, fold the pairs
             CU(rt, launch_tp_pick(sym_pair(rt->sym, 0), 4, sym_pair_flag(rt->sym, 0), rt->tp_seq, pick_tag, rt->status, rt->tp_size, rt->state,
@@ -835,10 +848,18 @@ int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int se
         a.K = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
+        if (rt->sampling) { a.advance = 0; a.tokens_out = nullptr; }
         a.x = b.xr + (size_t)(M - 1) * H;
         a.parts = b.down + (size_t)(M - 1) * H; a.n_parts = ks_dn; a.part_stride = M * H;
         CU(rt, launch_gemv(a, sms, st));
         launches++;
+        if (rt->sampling) {
+            SampleArgs sa{};
+            sa.logits = rt->logits; sa.row_stride = (size_t)rt->vocab_l; sa.M = 1; sa.vocab = rt->vocab_l; sa.params = rt->d_sample;
+            sa.seq0 = rt->cur_seq; sa.state = rt->state; sa.tokens_out = rt->tokens_out;
+            CU(rt, launch_sample_rows(sa, st));
+            launches++;
+        }
     } else if (head == 2) {
         RowsArgs r{};
         r.a = b.down; r.n_parts = ks_dn; r.part_stride = (size_t)M * H; r.ld = H; r.resid = b.xr; r.resid_ld = H; r.out = b.xr; r.out_ld = H;
@@ -850,8 +871,15 @@ int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int se
         CU(rt, gemm(g, H, ks_v, b.logits, V));
         ArgmaxRowsArgs x{};
         x.logits = b.logits; x.n_parts = ks_v; x.part_stride = (size_t)M * V; x.M = M; x.vocab = V;
-        x.row_tok = d_tok; x.row_pos = d_pos; x.log = rt->b_log; x.step = rt->b_step; x.max_steps = d.max_new_tokens;
-        CU(rt, launch_argmax_rows(x, st));
+        if (!rt->sampling) { x.row_tok = d_tok; x.row_pos = d_pos; x.log = rt->b_log; x.step = rt->b_step; x.max_steps = d.max_new_tokens; }
+        CU(rt, launch_argmax_rows(x, st));          // with a sampler set it only adds up the partial planes
+        if (rt->sampling) {
+            SampleArgs sa{};
+            sa.logits = b.logits; sa.row_stride = (size_t)V; sa.M = M; sa.vocab = V; sa.params = rt->d_sample;
+            sa.row_seq = d_seq; sa.row_tok = d_tok; sa.row_pos = d_pos; sa.log = rt->b_log; sa.step = rt->b_step; sa.max_steps = d.max_new_tokens;
+            CU(rt, launch_sample_rows(sa, st));
+            launches++;
+        }
         CU(rt, launch_step_advance(rt->b_step, st));
         launches += 2;
     }
@@ -1376,6 +1404,46 @@ int32_t lum_kv_load(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, const
     return 0;
 }
 
+int32_t lum_kv_copy(lum_rt* rt, int32_t src_seq, int32_t dst_seq, int32_t rows) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "kv_copy: no model");
+    if (src_seq < 0 || src_seq >= rt->max_batch || dst_seq < 0 || dst_seq >= rt->max_batch || rows < 0 || rows > rt->d.max_seq)
+        return fail(rt, LUM_E_INVALID, "kv_copy: sequences %d -> %d of %d, %d rows of %d", src_seq, dst_seq, rt->max_batch, rows, rt->d.max_seq);
+    if (src_seq == dst_seq || rows == 0) return 0;
+    CU(rt, cudaSetDevice(rt->cfg.device));
+    const size_t row_bytes = (size_t)rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4), seq_bytes = (size_t)rt->d.max_seq * row_bytes;
+    for (const LayerW& w : rt->L) {
+        CU(rt, cudaMemcpyAsync((char*)w.kc + dst_seq * seq_bytes, (const char*)w.kc + src_seq * seq_bytes, rows * row_bytes, cudaMemcpyDeviceToDevice, rt->stream));
+        CU(rt, cudaMemcpyAsync((char*)w.vc + dst_seq * seq_bytes, (const char*)w.vc + src_seq * seq_bytes, rows * row_bytes, cudaMemcpyDeviceToDevice, rt->stream));
+    }
+    return 0;
+}
+
+int32_t lum_set_sampling(lum_rt* rt, const lum_sampling* s) {
+    if (!rt) return LUM_E_INVALID;
+    bool on = s && s->temperature > 0.0f && s->top_k != 1;
+    SampleParams p{1.0f, 1.0f, 1, 0, 0ull};
+    if (on) {
+        if (!(s->temperature < INFINITY) || s->top_k < 0 || s->top_k > kSampleMaxK || !(s->top_p >= 0.0f) || s->top_p > 1.0f)
+            return fail(rt, LUM_E_INVALID, "set_sampling: temperature %g, top_k %d (0 .. %d), top_p %g (0 .. 1)", (double)s->temperature, s->top_k, kSampleMaxK, (double)s->top_p);
+        if (rt->tp_size > 1 || (rt->has_model && rt->mega_ok && rt->use_mega))
+            return fail(rt, LUM_E_UNSUPPORTED, "set_sampling: the sampler reads a whole row of logits on one GPU (no tensor parallelism, not the persistent kernel)");
+        p.temperature = s->temperature; p.top_k = s->top_k == 0 ? kSampleMaxK : s->top_k; p.top_p = s->top_p == 0.0f ? 1.0f : s->top_p; p.seed = s->seed;
+    }
+    if (rt->has_model) {
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        CU(rt, cudaStreamSynchronize(rt->stream));
+        CU(rt, cudaMemcpy(rt->d_sample, &p, sizeof p, cudaMemcpyHostToDevice));
+        if (on != rt->sampling) {          // the captured steps hold one kernel more or less
+            if (rt->g_full) { cudaGraphExecDestroy(rt->g_full); rt->g_full = nullptr; }
+            if (rt->g_body) { cudaGraphExecDestroy(rt->g_body); rt->g_body = nullptr; }
+            if (rt->g_batch) { cudaGraphExecDestroy(rt->g_batch); rt->g_batch = nullptr; }
+        }
+    }
+    rt->samp = p;
+    rt->sampling = on;
+    return 0;
+}
+
 int32_t lum_get_stats(const lum_rt* rt, lum_stats* out) {
     if (!rt || !out) return LUM_E_INVALID;
     memset(out, 0, sizeof *out);
@@ -1410,6 +1478,10 @@ int32_t lum_seq_select(lum_rt* rt, int32_t seq) {
 }
 
 int32_t lum_batch_begin(lum_rt* rt, int32_t n_seq, const int32_t* tokens, const int32_t* positions) {
+    return lum_batch_begin_slots(rt, n_seq, nullptr, tokens, positions);
+}
+
+int32_t lum_batch_begin_slots(lum_rt* rt, int32_t n_seq, const int32_t* slots, const int32_t* tokens, const int32_t* positions) {
     if (!rt || !rt->has_model || !tokens || !positions) return fail(rt, LUM_E_INVALID, "batch_begin: no model or null argument");
     if (n_seq < 1 || n_seq > rt->max_batch) return fail(rt, LUM_E_INVALID, "batch_begin: %d sequences, the model was loaded with max_batch %d", n_seq, rt->max_batch);
     if (rt->max_batch < 2) return fail(rt, LUM_E_INVALID, "batch_begin: load the model with max_batch > 1");
@@ -1418,8 +1490,18 @@ int32_t lum_batch_begin(lum_rt* rt, int32_t n_seq, const int32_t* tokens, const 
         if (tokens[i] < 0 || tokens[i] >= rt->d.vocab) return fail(rt, LUM_E_INVALID, "batch_begin: token id %d outside the vocabulary", tokens[i]);
         if (positions[i] < 0 || positions[i] >= rt->d.max_seq) return fail(rt, LUM_E_INVALID, "batch_begin: position %d outside the cache capacity %d", positions[i], rt->d.max_seq);
     }
+    std::vector<int32_t> row_slot((size_t)n_seq);
+    std::vector<char> taken((size_t)rt->max_batch, 0);
+    for (int i = 0; i < n_seq; i++) {
+        const int sl = slots ? slots[i] : i;
+        if (sl < 0 || sl >= rt->max_batch) return fail(rt, LUM_E_INVALID, "batch_begin: cache slot %d outside max_batch %d", sl, rt->max_batch);
+        if (taken[(size_t)sl]) return fail(rt, LUM_E_INVALID, "batch_begin: cache slot %d named twice", sl);
+        taken[(size_t)sl] = 1;
+        row_slot[(size_t)i] = sl;
+    }
     CU(rt, cudaSetDevice(rt->cfg.device));
     if (int r = ensure_rows(rt, n_seq)) return r;
+    CU(rt, cudaMemcpyAsync(rt->rows.seq, row_slot.data(), (size_t)n_seq * 4, cudaMemcpyHostToDevice, rt->stream));
     CU(rt, cudaMemcpyAsync(rt->rows.tok, tokens, (size_t)n_seq * 4, cudaMemcpyHostToDevice, rt->stream));
     CU(rt, cudaMemcpyAsync(rt->rows.pos, positions, (size_t)n_seq * 4, cudaMemcpyHostToDevice, rt->stream));
     CU(rt, cudaMemsetAsync(rt->b_step, 0, 4, rt->stream));
@@ -1741,6 +1823,8 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     TRY(dev_alloc(rt, (void**)&rt->am_val, kArgmaxSlots * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_idx, kArgmaxSlots * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_cnt, 4));
+    TRY(dev_alloc(rt, (void**)&rt->d_sample, sizeof(SampleParams)));
+    cudaMemcpyAsync(rt->d_sample, &rt->samp, sizeof(SampleParams), cudaMemcpyHostToDevice, rt->stream);
     TRY(dev_alloc(rt, (void**)&rt->step_ctr, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int)));
     cudaMemsetAsync(rt->step_ctr, 0, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int), rt->stream);
     TRY(dev_alloc(rt, (void**)&rt->status, 4));
@@ -2107,6 +2191,30 @@ int32_t lum_op_sample_q8_0(const void* packed, int32_t n, int32_t k, const float
     a.part_val = sc->val; a.part_idx = sc->idx; a.counter = sc->counter; a.status = sc->status; a.pair_out = best; a.row_offset = 0;
     const cudaError_t e = launch_gemv(a, cur_sm_count(), (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : op_fail("sample_q8_0", e);
+}
+
+int32_t lum_op_sample_topk(const float* logits_dev, int32_t n_rows, int32_t vocab, const lum_sampling* s, int32_t seq0, const int32_t* positions_dev,
+                           int32_t* tokens_dev, void* stream) {
+    if (!logits_dev || !s || !tokens_dev || !positions_dev || n_rows < 1 || vocab < 1) { g_create_error = "sample_topk: null argument or empty shape"; return LUM_E_INVALID; }
+    if (!(s->temperature > 0.0f) || !(s->temperature < INFINITY) || s->top_k < 0 || s->top_k > kSampleMaxK || !(s->top_p >= 0.0f) || s->top_p > 1.0f) {
+        g_create_error = "sample_topk: temperature must be positive and finite, top_k 0 .. 256, top_p 0 .. 1";
+        return LUM_E_INVALID;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { g_create_error = "sample_topk: cannot query the current device"; return LUM_E_CUDA; }
+    static SampleParams* g_params[64] = {};     // one slot per device; the call copies its parameters in on the caller's stream
+    if (!g_params[dev]) {
+        cudaError_t e = cudaMalloc((void**)&g_params[dev], sizeof(SampleParams));
+        if (e != cudaSuccess) return op_fail("sample_topk", e);
+    }
+    SampleParams p{s->temperature, s->top_p == 0.0f ? 1.0f : s->top_p, s->top_k == 0 ? kSampleMaxK : s->top_k, 0, s->seed};
+    cudaError_t e = cudaMemcpyAsync(g_params[dev], &p, sizeof p, cudaMemcpyHostToDevice, (cudaStream_t)stream);   // pageable source: staged before the call returns
+    if (e != cudaSuccess) return op_fail("sample_topk", e);
+    SampleArgs a{};
+    a.logits = logits_dev; a.row_stride = (size_t)vocab; a.M = n_rows; a.vocab = vocab; a.params = g_params[dev]; a.seq0 = seq0; a.draw_pos = positions_dev;
+    a.out = tokens_dev;
+    e = launch_sample_rows(a, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : op_fail("sample_topk", e);
 }
 
 int32_t lum_op_status(void* stream) {

@@ -43,7 +43,7 @@ public:
     }
     B200Runtime(B200Runtime&& o) noexcept : h_(o.h_), desc_(o.desc_) { o.h_ = nullptr; }
     B200Runtime& operator=(B200Runtime&& o) noexcept {
-        if (this != &o) { if (h_) lum_destroy(h_); h_ = o.h_; desc_ = o.desc_; o.h_ = nullptr; }
+        if (this != &o) { if (h_) lum_destroy(h_); h_ = o.h_; desc_ = o.desc_; batch_n_ = o.batch_n_; o.h_ = nullptr; }
         return *this;
     }
     B200Runtime(const B200Runtime&) = delete;
@@ -90,6 +90,26 @@ public:
     std::vector<int32_t> get_decoded(size_t n) { std::vector<int32_t> v(n); ck(lum_get_decoded(h_, v.data(), n)); return v; }
     void decode_reset() { ck(lum_decode_reset(h_)); }
     void synchronize() { ck(lum_synchronize(h_)); }
+    // The sampler after the vocabulary projection: temperature <= 0 = the reference's greedy `sample` (main.rs:137-148)
+    void set_sampling(float temperature, int top_k = 0, float top_p = 1.0f, uint64_t seed = 0) {
+        if (temperature <= 0.0f) { ck(lum_set_sampling(h_, nullptr)); return; }
+        lum_sampling s{temperature, top_p, top_k, 0, seed};
+        ck(lum_set_sampling(h_, &s));
+    }
+    // Several sequences: cache slots, batched steps (row i of the batch works on slot slots[i])
+    void seq_select(int seq) { ck(lum_seq_select(h_, seq)); }
+    void kv_copy(int src_seq, int dst_seq, int rows) { ck(lum_kv_copy(h_, src_seq, dst_seq, rows)); }
+    void batch_begin_slots(const std::vector<int32_t>& slots, const std::vector<int32_t>& tokens, const std::vector<int32_t>& positions) {
+        if (slots.size() != tokens.size() || positions.size() != tokens.size()) throw Error(LUM_E_INVALID, "batch_begin_slots: one entry per row in each list");
+        ck(lum_batch_begin_slots(h_, (int32_t)tokens.size(), slots.data(), tokens.data(), positions.data()));
+        batch_n_ = tokens.size();
+    }
+    void batch_decode(int n_steps) { ck(lum_batch_decode(h_, n_steps)); }
+    std::vector<int32_t> batch_get_decoded(size_t n_steps) {      // [n_steps][rows]
+        std::vector<int32_t> v(n_steps * batch_n_);
+        ck(lum_batch_get_decoded(h_, v.data(), n_steps));
+        return v;
+    }
     std::pair<ProfileMetric, std::string> profile(int trials) {
         double us = 0; char buf[128] = {0};
         ck(lum_profile(h_, trials, &us, buf, sizeof buf));
@@ -127,6 +147,7 @@ private:
     void ck(int rc) { if (rc) throw Error(rc, lum_last_error(h_)); }
     lum_rt* h_ = nullptr;
     lum_model_desc desc_{};
+    size_t batch_n_ = 0;
 };
 
 }  // namespace lum

@@ -115,6 +115,16 @@ pub struct lum_model_desc {
 
 #[repr(C)]
 #[derive(Clone, Copy, Debug, Default)]
+pub struct lum_sampling {
+    pub temperature: f32,
+    pub top_p: f32,
+    pub top_k: i32,
+    pub reserved: i32,
+    pub seed: u64,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default)]
 pub struct lum_stats {
     pub tokens_executed: u64,
     pub kernel_launches: u64,
@@ -157,6 +167,7 @@ unsafe extern "C" {
     pub fn lum_kv_read(rt: *mut lum_rt, layer: i32, kind: i32, rows: i32, host_out: *mut f32) -> i32;
     pub fn lum_kv_save(rt: *mut lum_rt, layer: i32, kind: i32, rows: i32, host_out: *mut c_void, bytes: usize) -> i32;
     pub fn lum_kv_load(rt: *mut lum_rt, layer: i32, kind: i32, rows: i32, host: *const c_void, bytes: usize) -> i32;
+    pub fn lum_kv_copy(rt: *mut lum_rt, src_seq: i32, dst_seq: i32, rows: i32) -> i32;
 
     pub fn lum_set_dim(rt: *mut lum_rt, dim: c_char, value: u64) -> i32;
     pub fn lum_set_tokens(rt: *mut lum_rt, ids: *const i32, n: usize) -> i32;
@@ -167,9 +178,11 @@ unsafe extern "C" {
     pub fn lum_get_decoded(rt: *mut lum_rt, host_out: *mut i32, n: usize) -> i32;
     pub fn lum_decode_reset(rt: *mut lum_rt) -> i32;
     pub fn lum_synchronize(rt: *mut lum_rt) -> i32;
+    pub fn lum_set_sampling(rt: *mut lum_rt, s: *const lum_sampling) -> i32;
 
     pub fn lum_seq_select(rt: *mut lum_rt, seq: i32) -> i32;
     pub fn lum_batch_begin(rt: *mut lum_rt, n_seq: i32, tokens: *const i32, positions: *const i32) -> i32;
+    pub fn lum_batch_begin_slots(rt: *mut lum_rt, n_seq: i32, slots: *const i32, tokens: *const i32, positions: *const i32) -> i32;
     pub fn lum_batch_decode(rt: *mut lum_rt, n_steps: i32) -> i32;
     pub fn lum_batch_get_decoded(rt: *mut lum_rt, host_out: *mut i32, n_steps: usize) -> i32;
     pub fn lum_batch_get_logits(rt: *mut lum_rt, seq: i32, host_out: *mut f32, n: usize) -> i32;
@@ -195,6 +208,7 @@ unsafe extern "C" {
     pub fn lum_op_sample_q8_0(packed_dev: *const c_void, n: i32, k: i32, x_dev: *const f32, logits_dev: *mut f32, best_dev: *mut i32, stream: *mut c_void) -> i32;
     pub fn lum_op_sample_q8_0_static(packed_dev: *const c_void, n: i32, k: i32, x_dev: *const f32, logits_dev: *mut f32, best_dev: *mut i32, stream: *mut c_void) -> i32;
     pub fn lum_op_gemv_f32(w_dev: *const f32, n: i32, k: i32, x_dev: *const f32, y_dev: *mut f32, stream: *mut c_void) -> i32;
+    pub fn lum_op_sample_topk(logits_dev: *const f32, n_rows: i32, vocab: i32, s: *const lum_sampling, seq0: i32, positions_dev: *const i32, tokens_dev: *mut i32, stream: *mut c_void) -> i32;
     pub fn lum_op_status(stream: *mut c_void) -> i32;
     pub fn lum_op_q8_0_quantize(src_dev: *const c_void, dtype: u32, n_elems: usize, quants_dev: *mut i8, scales_dev: *mut c_void, stream: *mut c_void) -> i32;
 

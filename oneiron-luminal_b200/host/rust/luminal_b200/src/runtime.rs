@@ -175,6 +175,25 @@ impl B200Runtime {
         out
     }
     pub fn kv_reset(&mut self) { self.check(unsafe { lum_kv_reset(self.h) }) }
+    /// The sampler after the vocabulary projection; `None` = the greedy `sample` of examples/llama/src/main.rs:137-148.
+    pub fn set_sampling(&mut self, s: Option<lum_sampling>) {
+        let p = s.as_ref().map_or(std::ptr::null(), |v| v as *const lum_sampling);
+        self.check(unsafe { lum_set_sampling(self.h, p) })
+    }
+    /// Several sequences side by side (`max_batch` cache slots): which slot `execute` addresses, a prefix copied between
+    /// slots on the device, and batched steps over any set of live slots (row i works on `slots[i]`).
+    pub fn seq_select(&mut self, seq: usize) { self.check(unsafe { lum_seq_select(self.h, seq as i32) }) }
+    pub fn kv_copy(&mut self, src_seq: usize, dst_seq: usize, rows: usize) {
+        self.check(unsafe { lum_kv_copy(self.h, src_seq as i32, dst_seq as i32, rows as i32) })
+    }
+    pub fn batch_decode(&mut self, slots: &[i32], tokens: &[i32], positions: &[i32], n_steps: usize) -> Vec<i32> {
+        assert!(slots.len() == tokens.len() && positions.len() == tokens.len(), "one entry per row in each list");
+        self.check(unsafe { lum_batch_begin_slots(self.h, tokens.len() as i32, slots.as_ptr(), tokens.as_ptr(), positions.as_ptr()) });
+        self.check(unsafe { lum_batch_decode(self.h, n_steps as i32) });
+        let mut out = vec![0i32; n_steps * tokens.len()];
+        self.check(unsafe { lum_batch_get_decoded(self.h, out.as_mut_ptr(), n_steps) });
+        out
+    }
     pub fn stats(&self) -> lum_stats {
         let mut s = lum_stats::default();
         self.check(unsafe { lum_get_stats(self.h, &mut s) });

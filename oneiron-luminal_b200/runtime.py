@@ -72,6 +72,12 @@ class Stats(C.Structure):
                 ("last_profile_usec", C.c_double)]
 
 
+class Sampling(C.Structure):
+    """Mirror of ``lum_sampling`` (include/lum_b200.h): temperature / top-p / top-k / seed of the on-device sampler."""
+
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_int32), ("reserved", C.c_int32), ("seed", C.c_uint64)]
+
+
 def _desc(**kw) -> ModelDesc:
     d = ModelDesc()
     base = dict(max_seq=4096, rms_eps=1e-5, rope_style=0, qk_norm=0, tied_head=0, max_new_tokens=4096, tp_size=1, tp_rank=0, max_batch=1)
@@ -206,6 +212,9 @@ def load_library() -> C.CDLL:
         "lum_llir_describe_chunk": (i32, [vp, sz, P(ModelDesc), P(C.c_int64), P(C.c_int64), C.c_char_p, sz]),
         "lum_kv_save": (i32, [vp, i32, i32, i32, vp, sz]),
         "lum_kv_load": (i32, [vp, i32, i32, i32, vp, sz]),
+        "lum_kv_copy": (i32, [vp, i32, i32, i32]),
+        "lum_set_sampling": (i32, [vp, P(Sampling)]),
+        "lum_op_sample_topk": (i32, [vp, i32, i32, P(Sampling), i32, vp, vp, vp]),
         "lum_get_stats": (i32, [vp, P(Stats)]),
         "lum_debug_wait_timeout": (i32, [vp]),
         "lum_op_status": (i32, [vp]),
@@ -224,6 +233,7 @@ def load_library() -> C.CDLL:
         "lum_synchronize": (i32, [vp]),
         "lum_seq_select": (i32, [vp, i32]),
         "lum_batch_begin": (i32, [vp, i32, P(i32), P(i32)]),
+        "lum_batch_begin_slots": (i32, [vp, i32, P(i32), P(i32), P(i32)]),
         "lum_batch_decode": (i32, [vp, i32]),
         "lum_batch_get_decoded": (i32, [vp, P(i32), sz]),
         "lum_batch_get_logits": (i32, [vp, i32, P(C.c_float), sz]),
@@ -625,6 +635,30 @@ class B200Runtime:
         p = (C.c_int32 * n)(*[int(v) for v in positions])
         self._ck(self._lib.lum_batch_begin(self._h, n, t, p))
         self._batch_n = n
+
+    def batch_begin_slots(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> None:
+        """Row i of the batch works on cache slot ``slots[i]`` (distinct): the hook of a continuous-batching loop."""
+        n = len(tokens)
+        if len(slots) != n or len(positions) != n:
+            raise ValueError("slots, tokens and positions must have one entry per row")
+        sl = (C.c_int32 * n)(*[int(v) for v in slots])
+        t = (C.c_int32 * n)(*[int(v) for v in tokens])
+        p = (C.c_int32 * n)(*[int(v) for v in positions])
+        self._ck(self._lib.lum_batch_begin_slots(self._h, n, sl, t, p))
+        self._batch_n = n
+
+    def kv_copy(self, src_seq: int, dst_seq: int, rows: int) -> None:
+        """The first ``rows`` cache rows of every layer copied from one sequence's slot to another's (a shared prompt prefix)."""
+        self._ck(self._lib.lum_kv_copy(self._h, src_seq, dst_seq, rows))
+
+    def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
+        """The sampler after the vocabulary projection: temperature 0 (or top_k 1) = the reference's greedy ``sample``;
+        otherwise a temperature / top-k / top-p draw made on the device, a function of (logits, seed, sequence, position)."""
+        if temperature <= 0.0:
+            self._ck(self._lib.lum_set_sampling(self._h, None))
+        else:
+            s = Sampling(temperature=temperature, top_p=top_p, top_k=top_k, reserved=0, seed=seed)
+            self._ck(self._lib.lum_set_sampling(self._h, C.byref(s)))
 
     def batch_decode(self, n_steps: int) -> None:
         self._ck(self._lib.lum_batch_decode(self._h, n_steps))

@@ -520,6 +520,70 @@ void orc_q8_0_quantize(const float* x, size_t n_blocks, uint8_t* blocks) {
     }
 }
 
+// Temperature / top-k / top-p draw from one row of logits: the CPU statement of the device sampler's definition (the reference
+// has no stochastic sampler: examples/llama/src/main.rs:137-148 is the arg-max; parity of this function is unpinned by reference
+// vectors and rests on hand-worked cases in the tests).
+//   candidates: the top_k logits by (value descending, index ascending), NaN counting as -inf;
+//   w_j = expf((l_j - l_0) * (1 / temperature)); running f32 sums; top_p < 1 keeps the shortest prefix with S_j >= top_p * S_last;
+//   u = (SplitMix64 finaliser of (seed, seq, pos) >> 40) * 2^-24; the draw is the first j with S_j > u * S_kept.
+// Returns the token; *margin (optional) = distance of u * S_kept from the nearest boundary it could cross (a running sum that
+// decides the pick, or the top_p cut), relative to S_kept: draws with a tiny margin may legitimately differ between two
+// implementations whose expf differ in the last bit.
+int orc_sample_topk(const float* logits, int vocab, float temperature, int top_k, float top_p, uint64_t seed, int seq, int pos, float* margin) {
+    if (vocab < 1) return 0;
+    int k = top_k < 1 ? 1 : top_k;
+    if (k > 256) k = 256;
+    if (k > vocab) k = vocab;
+    auto val = [&](int i) { const float v = logits[i]; return v != v ? -INFINITY : v; };
+    std::vector<int> idx((size_t)vocab);
+    for (int i = 0; i < vocab; i++) idx[(size_t)i] = i;
+    std::partial_sort(idx.begin(), idx.begin() + k, idx.end(), [&](int a, int b) {
+        const float va = val(a), vb = val(b);
+        return va > vb || (va == vb && a < b);
+    });
+    std::vector<float> w((size_t)k);
+    const float l0 = val(idx[0]), inv_t = 1.0f / temperature;
+    for (int j = 0; j < k; j++) {
+        const float d = val(idx[(size_t)j]) - l0;
+        w[(size_t)j] = d != d ? 1.0f : expf(d * inv_t);
+    }
+    float total = 0.0f;
+    for (int j = 0; j < k; j++) total += w[(size_t)j];
+    int keep = k;
+    float cut_gap = INFINITY;
+    if (top_p < 1.0f) {
+        const float cut = top_p * total;
+        float s = 0.0f;
+        for (int j = 0; j < k; j++) {
+            s += w[(size_t)j];
+            const float g = std::fabs(s - cut);
+            if (g < cut_gap) cut_gap = g;
+            if (s >= cut) { keep = j + 1; break; }
+        }
+    }
+    float kept = 0.0f;
+    for (int j = 0; j < keep; j++) kept += w[(size_t)j];
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull * (uint64_t)(pos + 1) + 0xD1B54A32D192ED03ull * (uint64_t)(seq + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    const float u = (float)(z >> 40) * (1.0f / 16777216.0f);
+    const float target = u * kept;
+    int pick = keep - 1;
+    float s = 0.0f, gap = INFINITY;
+    for (int j = 0; j < keep; j++) {
+        s += w[(size_t)j];
+        const float g = std::fabs(s - target);
+        if (g < gap) gap = g;
+        if (s > target) { pick = j; break; }
+    }
+    if (margin) {
+        float m = gap < cut_gap ? gap : cut_gap;
+        *margin = kept > 0.0f ? m / kept : 0.0f;
+    }
+    return idx[(size_t)pick];
+}
+
 int orc_synth(uint64_t seed, uint64_t tid, uint32_t dtype, size_t n_elems, int ones, void* out) {
     const uint64_t key = orc::rng_key(seed, tid), skey = orc::rng_key(seed, tid + orc::kScaleStream);
     if (dtype == 0) {

@@ -53,6 +53,7 @@ def load() -> C.CDLL:
         "orc_model_error": (C.c_char_p, [vp]),
         "orc_q8_0_dequant": (None, [vp, sz, fp]),
         "orc_q8_0_quantize": (None, [fp, sz, vp]),
+        "orc_sample_topk": (i32, [fp, i32, C.c_float, i32, C.c_float, u64, i32, i32, fp]),
         "orc_synth": (i32, [u64, u64, u32, sz, i32, vp]),
         "orc_synth_range": (i32, [u64, u64, u32, sz, sz, vp]),
         "orc_synth_tokens": (None, [u64, u64, u32, sz, ip]),
@@ -93,6 +94,14 @@ def q8_0_quantize(x: np.ndarray) -> np.ndarray:
     out = np.empty((x.size // 32, 34), dtype=np.uint8)
     load().orc_q8_0_quantize(_fp(x), x.size // 32, out.ctypes.data_as(C.c_void_p))
     return out
+
+
+def sample_topk(logits: np.ndarray, temperature: float, top_k: int, top_p: float, seed: int, seq: int, pos: int):
+    """One draw from a row of logits by the oracle's sampler: (token, margin) — see orc_sample_topk for the margin."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32).reshape(-1)
+    m = C.c_float(0.0)
+    tok = load().orc_sample_topk(_fp(logits), logits.size, temperature, top_k, top_p, seed, seq, pos, C.byref(m))
+    return int(tok), float(m.value)
 
 
 def q8_0_dequant(blocks: np.ndarray) -> np.ndarray:

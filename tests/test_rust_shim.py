@@ -13,7 +13,7 @@ CRATE = os.path.join(ROOT, "oneiron-luminal_b200", "host", "rust", "luminal_b200
 
 SCALAR = {"int32_t": "i32", "uint32_t": "u32", "int64_t": "i64", "uint64_t": "u64", "size_t": "usize", "float": "f32", "double": "f64",
           "char": "c_char", "int8_t": "i8", "uint8_t": "u8", "void": "c_void", "lum_rt": "lum_rt", "lum_st": "lum_st", "lum_config": "lum_config",
-          "lum_model_desc": "lum_model_desc", "lum_stats": "lum_stats"}
+          "lum_model_desc": "lum_model_desc", "lum_stats": "lum_stats", "lum_sampling": "lum_sampling"}
 
 
 def strip_comments(text):
@@ -98,7 +98,7 @@ def rust_struct_fields(name):
     return [(m.group(1), m.group(2)) for m in re.finditer(r"pub (\w+): (\w+),", body)]
 
 
-@pytest.mark.parametrize("name, mirror", [("lum_config", "Config"), ("lum_model_desc", "ModelDesc"), ("lum_stats", "Stats")])
+@pytest.mark.parametrize("name, mirror", [("lum_config", "Config"), ("lum_model_desc", "ModelDesc"), ("lum_stats", "Stats"), ("lum_sampling", "Sampling")])
 def test_repr_c_structs_match_the_header_and_the_ctypes_mirror(pkg, name, mirror):
     import ctypes as C
     c, r = c_struct_fields(name), rust_struct_fields(name)
