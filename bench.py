@@ -537,12 +537,18 @@ def run_tensor_core_regime(args, pkg, which: str):
         p_mean = ctx + (args.warmup + args.steps / 2.0) * tps
         bytes_step = pkg.decode_bytes_per_token(base, 0) - 131072 + 131072.0 * (p_mean + 1) * B     # weights once, every sequence's cache
         ach = bytes_step * (args.steps * tps) / (ms * 1e-3) / 1e9
+        n_run = (args.warmup + args.steps) * tps
+        launches = int(rt.stats().kernel_launches)
+        batch_log = rt.batch_get_decoded(n_run)
+        batch_logits = {sq: rt.batch_get_logits(sq) for sq in (0, B - 1)}
         # end to end: the same loop with the sampled tokens of every step read back by the host
         t0 = time.perf_counter()
         for _ in range(args.steps * tps):
             rt.batch_decode(1)
             rt.batch_get_decoded(1)
         e2e = args.steps * tps * B / (time.perf_counter() - t0)
+        rt.close()
+        parity = _batch_parity(pkg, base, ctx, n_run, firsts, batch_log, batch_logits, B)
         line = {"metric": "q8_llama3_8b_bs32_decode_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16 x f16 -> f32 on tcgen05 (weights as two exact binary16 terms, activations as two), f32 sums", "data": "synthetic",
@@ -552,7 +558,7 @@ def run_tensor_core_regime(args, pkg, which: str):
                              "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "bytes_per_step": bytes_step, "traffic": None},
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * B * tps,
                         "note": "every step's sampled tokens device->host; the fed-back tokens stay on the device"},
-                "gpu_launches": int(rt.stats().kernel_launches), "clocks": clocks}
+                "parity": parity, "gpu_launches": launches, "clocks": clocks}
     else:
         n = 4096
         rt.load_model(base.copy(max_seq=n + 8))
@@ -578,8 +584,12 @@ def run_tensor_core_regime(args, pkg, which: str):
         flops = 2.0 * w_layers * n + 2.0 * d.vocab * d.hidden + d.n_layers * 4.0 * d.n_q_heads * d.head_dim * n * (n + 1) / 2
         ach = flops * args.steps / (ms * 1e-3) / 1e12
         t0 = time.perf_counter()
-        rt.set_data(ids); rt.execute({"s": n, "p": 0}); rt.get_token()
+        rt.set_data(ids); rt.execute({"s": n, "p": 0}); rows_token = rt.get_token()
         e2e = n / (time.perf_counter() - t0)
+        rows_logits = rt.get_f32()
+        launches = int(rt.stats().kernel_launches)
+        rt.close()
+        parity = _prefill_parity(pkg, base, ids, rows_token, rows_logits)
         line = {"metric": "q8_llama3_8b_prefill4096_tokens_per_s", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16 x f16 -> f32 on tcgen05 (weights as two exact binary16 terms, activations as two); attention bf16 x bf16 -> f32 on tcgen05 (two-term queries and weights)", "data": "synthetic",
@@ -589,9 +599,57 @@ def run_tensor_core_regime(args, pkg, which: str):
                              "flops_per_step": flops, "traffic": None},
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4,
                         "note": "token ids host->device, the sampled token device->host"},
-                "gpu_launches": int(rt.stats().kernel_launches), "clocks": clocks}
-    rt.close()
+                "parity": parity, "gpu_launches": launches, "clocks": clocks}
     print(json.dumps(line))
+
+
+def _prefill_parity(pkg, base, ids, rows_token, rows_logits):
+    """The prompt once more, one decode step per token (the path the default workload checks against the oracle's fixture):
+    the logits after the last prompt token and the greedy sample must agree with the rows pass."""
+    import numpy as np
+    solo = pkg.B200Runtime.initialize(device=0, prefill_min_rows=1 << 30)
+    try:
+        solo.load_model(base.copy(max_seq=len(ids) + 8))
+        solo.synth(SEED)
+        solo.set_data(ids); solo.execute({"s": len(ids), "p": 0})
+        tok, ref = solo.get_token(), solo.get_f32()
+    finally:
+        solo.close()
+    err = float(np.max(np.abs(rows_logits - ref)) / np.max(np.abs(ref)))
+    top2 = np.partition(ref, -2)[-2:]
+    return {"checked": True, "against": "the same prompt run one decode step per token on the GPU (that path is checked against the oracle's "
+            "full-size fixture by the default workload; the oracle itself would need hours for 4096 rows)",
+            "tokens_equal": bool(tok == rows_token), "steps": 1, "logits_rel_err": err, "logits_tolerance": 1e-2,
+            "top1_top2_margin": float(top2[1] - top2[0])}
+
+
+def _batch_parity(pkg, base, ctx, n_run, firsts, batch_log, batch_logits, B):
+    """The first and the last sequence of the batch decoded alone, one decode step per token: same tokens for the first 32
+    steps; if a sequence agrees to the end of the run, the final logits are compared too."""
+    import numpy as np
+    n_cmp = min(32, n_run)
+    out = {"checked": True, "against": "sequences 0 and %d decoded alone, one decode step per token, on the GPU (that path is checked against the "
+           "oracle's full-size fixture by the default workload)" % (B - 1), "steps": n_cmp, "tokens_equal": True, "first_mismatch": None,
+           "logits_rel_err": None, "logits_tolerance": 1e-2}
+    solo = pkg.B200Runtime.initialize(device=0)
+    try:
+        solo.load_model(base.copy(max_seq=ctx + n_run + 8, max_new_tokens=n_run + 8))
+        solo.synth(SEED)
+        for sq in (0, B - 1):
+            ids = _prompt_tokens(base.vocab, ctx + sq)[sq:]
+            got = [int(firsts[sq])] + [int(t) for t in batch_log[:, sq]]
+            want = solo.generate(ids, n_run + 1)
+            bad = next((i for i in range(n_cmp) if got[i] != want[i]), None)
+            if bad is not None:
+                out["tokens_equal"] = False
+                out["first_mismatch"] = {"sequence": sq, "step": bad}
+            elif got == want:
+                ref = solo.get_f32()
+                err = float(np.max(np.abs(batch_logits[sq] - ref)) / np.max(np.abs(ref)))
+                out["logits_rel_err"] = err if out["logits_rel_err"] is None else max(err, out["logits_rel_err"])
+    finally:
+        solo.close()
+    return out
 
 
 def run_moe(args, pkg):
@@ -653,6 +711,7 @@ def run_moe(args, pkg):
     n_tok = args.steps * tps
     value = world * n_tok / (ms * 1e-3)
     st = rt.stats()
+    parity = _moe_parity(rt, world, dist, torch)
     p_mean = n_prompt + (args.warmup + args.steps / 2.0) * tps
     # a token reads the attention weights, the router, top-4 experts and the vocabulary projection; K/V rows of the full layers up to
     # its position and at most 128 on the windowed layers
@@ -670,13 +729,43 @@ def run_moe(args, pkg):
                 "roofline": {"bound": "hbm", "kernel": "whole decode step of one rank", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": ach / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}", "bytes_per_token": bytes_tok, "traffic": None},
                 "e2e": {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "not measured for this workload"},
-                "gpu_launches": int(st.kernel_launches), "clocks": clocks}
+                "parity": parity, "gpu_launches": int(st.kernel_launches), "clocks": clocks}
     rt.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line))
+
+
+def _moe_parity(rt, world, dist, torch):
+    """The oracle's committed full-size fixture for this model: its 256-token prompt and 32 greedy tokens, run by every rank
+    (under expert parallelism all ranks step together, so all decode the fixture's sequence)."""
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "gpt_oss_20b_q8_full.npz")
+    if not os.path.exists(path):
+        return {"checked": False, "reason": f"no fixture {os.path.relpath(path, ROOT)}"}
+    fx = np.load(path)
+    if int(fx["seed"]) != SEED:
+        return {"checked": False, "reason": "fixture was made for another seed"}
+    prompt, want = [int(t) for t in fx["prompt"]], [int(t) for t in fx["tokens"]]
+    if len(prompt) + len(want) + 1 > rt.desc.max_seq or len(want) > rt.desc.max_new_tokens:
+        return {"checked": False, "reason": "this run's cache or token log is smaller than the fixture's sequence"}
+    rt.kv_reset(); rt.decode_reset()
+    rt.set_data(prompt); rt.execute({"s": len(prompt), "p": 0})
+    first, logits = rt.get_token(), rt.get_f32()
+    rt.decode_greedy(len(want) - 1)
+    got = [int(first)] + [int(t) for t in rt.get_decoded(len(want) - 1)]
+    ref = fx["prompt_logits"].astype(np.float32)
+    err = float(np.max(np.abs(logits - ref)) / np.max(np.abs(ref)))
+    equal = got == want
+    if world > 1:
+        t = torch.tensor([err, 0.0 if equal else 1.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        err, equal = float(t[0].item()), float(t[1].item()) == 0.0
+    return {"checked": True, "tokens_equal": bool(equal), "steps": len(want), "logits_rel_err": err, "logits_tolerance": 1e-2,
+            "first_mismatch": next((i for i in range(len(want)) if got[i] != want[i]), None),
+            "min_margin_of_fixture": float(np.min(fx["margins"])), "fixture": os.path.relpath(path, ROOT)}
 
 
 def _prompt_tokens(vocab: int, n: int):

@@ -246,8 +246,9 @@ int32_t lum_synchronize(lum_rt* rt);
  *   S_j >= top_p * S_last; u = 24 bits of a SplitMix64 finaliser of (seed, sequence, position of the drawn token) * 2^-24;
  *   the draw is the first j with S_j > u * S_kept.
  * A draw therefore depends only on (logits, parameters, seed, sequence index, position): replaying a sequence replays its
- * draws.  `s` null, temperature <= 0 or top_k == 1 switch back to the greedy sample.  One GPU only (the logits of a
- * tensor-parallel group are sharded by vocabulary), not with the persistent kernel. */
+ * draws.  `s` null, temperature <= 0 or top_k == 1 switch back to the greedy sample.  In a tensor-parallel group (logits
+ * sharded by vocabulary) every rank gathers the row with one all-gather and makes the same draw: set the same sampler on
+ * every rank.  Not with the persistent-kernel executor. */
 typedef struct lum_sampling {
     float temperature;
     float top_p;

@@ -207,6 +207,7 @@ struct lum_rt {
     float* x2 = nullptr;              // second residual buffer (the stream alternates between x and x2)
     float* part = nullptr;            // this rank's partial o / down projection, all-reduced in place
     int* tp_pairs = nullptr;          // [tp_size][2] sampling candidates after the all-gather; this rank's own pair at [tp_size]
+    float* logits_full = nullptr;     // tensor parallel with a sampler set: every rank's vocabulary shard, gathered
     // Exchange of partial sums through peer memory instead of all-reduce kernels.  `sym` is this rank's buffer:
     // 4 KiB of flag words ([2 buffers][rank], 128 bytes apart), then [2 buffers][rank][hidden] floats; the other
     // ranks map it through a CUDA IPC handle and write their partial vectors and "complete" words straight into it.
@@ -300,7 +301,7 @@ void close_peers(lum_rt* rt) {
 
 void free_model(lum_rt* rt) {
     close_peers(rt);
-    rt->sym = nullptr; rt->sym_bytes = 0; rt->tp_seq = nullptr; rt->peer_ticket = nullptr;
+    rt->sym = nullptr; rt->sym_bytes = 0; rt->tp_seq = nullptr; rt->peer_ticket = nullptr; rt->logits_full = nullptr;
     rt->yarn_inv = nullptr; rt->moe_xf = rt->moe_sw = rt->moe_recv = rt->moe_part = rt->moe_comb = nullptr;
     if (rt->g_full) cudaGraphExecDestroy(rt->g_full);
     if (rt->g_body) cudaGraphExecDestroy(rt->g_body);
@@ -610,7 +611,6 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         a.K = hw.kind == WK_Q8 ? (int)hw.kdev : H; a.k_norm = H; a.epi = EPI_ARGMAX; a.gain = rt->final_norm.w; a.y = rt->logits;
         a.part_val = rt->am_val; a.part_idx = rt->am_idx; a.counter = rt->am_cnt; a.state = rt->state; a.tokens_out = rt->tokens_out;
         a.advance = 1;
-        if (rt->sampling && tp) return fail(rt, LUM_E_UNSUPPORTED, "the sampler reads a whole row of logits on one GPU: not under tensor parallelism");
         const bool draw = rt->sampling;
         if (draw) { a.advance = 0; a.tokens_out = nullptr; }      // sample_rows below does the bookkeeping with its own draw
         take_partial(a);
@@ -619,19 +619,27 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         auto sym_pair_flag = [&](unsigned char* base, int rank) { return (uint32_t*)(base + 2304 + (size_t)rank * 128); };
         const uint32_t pick_tag = 1023;
         if (tp) { a.pair_out = rt->tp_pairs + 2 * rt->tp_size; a.row_offset = rt->tp_rank * rt->vocab_l; }
-        if (fused) {
+        if (fused && !draw) {
             a.n_peers = rt->tp_size; a.seq = rt->tp_seq; a.peer_tag = pick_tag;
             for (int r = 0; r < rt->tp_size; r++) { a.peer_out[r] = (float*)sym_pair(rt->peer_sym[r], rt->tp_rank); a.peer_flag[r] = sym_pair_flag(rt->peer_sym[r], rt->tp_rank); }
         }
         claim_ctr(a);
         CU(rt, launch_gemv(a, rt->sm_count, st)); n++;
         if (draw) {
+            // Tensor parallel: the logits are sharded by vocabulary rows, rank by rank; every rank gathers the whole row and makes the
+            // same draw from it (the kernel is deterministic), so no token has to travel.
+            int V = rt->vocab_l;
+            const float* row = rt->logits;
+            if (tp) {
+                const int rc = nccl().AllGather(rt->logits, rt->logits_full, (size_t)rt->vocab_l, kNcclFloat32, rt->comm, st);
+                if (rc) return fail(rt, LUM_E_CUDA, "ncclAllGather: %s", nccl().GetErrorString(rc));
+                row = rt->logits_full; V = rt->vocab_l * rt->tp_size; n++;
+            }
             SampleArgs sa{};
-            sa.logits = rt->logits; sa.row_stride = (size_t)rt->vocab_l; sa.M = 1; sa.vocab = rt->vocab_l; sa.params = rt->d_sample;
+            sa.logits = row; sa.row_stride = (size_t)V; sa.M = 1; sa.vocab = V; sa.params = rt->d_sample;
             sa.seq0 = rt->cur_seq; sa.state = rt->state; sa.tokens_out = rt->tokens_out;
             CU(rt, launch_sample_rows(sa, st)); n++;
-        }
-        if (fused) {
+        } else if (fused) {
             // every rank's sampling kernel has written its pair into every rank's buffer: wait for the words, fold the pairs
             CU(rt, launch_tp_pick(sym_pair(rt->sym, 0), 4, sym_pair_flag(rt->sym, 0), rt->tp_seq, pick_tag, rt->status, rt->tp_size, rt->state,
                                   rt->tokens_out, 1, st));
@@ -1425,8 +1433,8 @@ int32_t lum_set_sampling(lum_rt* rt, const lum_sampling* s) {
     if (on) {
         if (!(s->temperature < INFINITY) || s->top_k < 0 || s->top_k > kSampleMaxK || !(s->top_p >= 0.0f) || s->top_p > 1.0f)
             return fail(rt, LUM_E_INVALID, "set_sampling: temperature %g, top_k %d (0 .. %d), top_p %g (0 .. 1)", (double)s->temperature, s->top_k, kSampleMaxK, (double)s->top_p);
-        if (rt->tp_size > 1 || (rt->has_model && rt->mega_ok && rt->use_mega))
-            return fail(rt, LUM_E_UNSUPPORTED, "set_sampling: the sampler reads a whole row of logits on one GPU (no tensor parallelism, not the persistent kernel)");
+        if (rt->has_model && rt->mega_ok && rt->use_mega)
+            return fail(rt, LUM_E_UNSUPPORTED, "set_sampling: the persistent-kernel executor only has the greedy sample");
         p.temperature = s->temperature; p.top_k = s->top_k == 0 ? kSampleMaxK : s->top_k; p.top_p = s->top_p == 0.0f ? 1.0f : s->top_p; p.seed = s->seed;
     }
     if (rt->has_model) {
@@ -1802,6 +1810,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
         TRY(dev_alloc(rt, (void**)&rt->sym, rt->sym_bytes));
         TRY(dev_alloc(rt, (void**)&rt->tp_seq, 4));
         TRY(dev_alloc(rt, (void**)&rt->peer_ticket, 4));
+        TRY(dev_alloc(rt, (void**)&rt->logits_full, (size_t)tp * rt->vocab_l * 4));
         cudaMemsetAsync(rt->sym, 0, rt->sym_bytes, rt->stream);
         cudaMemsetAsync(rt->tp_seq, 0, 4, rt->stream);
         cudaMemsetAsync(rt->peer_ticket, 0, 4, rt->stream);

@@ -7,6 +7,7 @@ give the GPU tests a fixed target that does not depend on rebuilding the oracle 
     python tests/golden/make_golden.py                 # the small cases (seconds)
     python tests/golden/make_golden.py llama3_8b_q8    # a full-size case (tens of minutes of CPU time, ~12 GB of RAM)
     python tests/golden/make_golden.py qwen3_4b_q8
+    python tests/golden/make_golden.py gpt_oss_20b_q8  # ~23 GB of RAM
 
 Full-size cases are the configurations the benchmark numbers are quoted on: whole model, whole vocabulary, the
 benchmark's seed and prompt.  They hold the prompt, the first 32 greedy tokens with their top-1/top-2 margins,
@@ -38,6 +39,8 @@ FULL_SEED = 20240607
 FULL_CASES = {
     "llama3_8b_q8": ("llama3_8b_q8", FULL_SEED, 512, 32),
     "qwen3_4b_q8": ("qwen3_4b_q8", FULL_SEED, 1024, 32),
+    # routed experts, sliding-window / full layers alternating, sinks, YaRN: 256 tokens take the window (128) out of reach of the start
+    "gpt_oss_20b_q8": ("gpt_oss_20b_q8", FULL_SEED, 256, 32),
 }
 
 

@@ -36,3 +36,17 @@ def test_tp_matches_single_gpu(world, cfg, n_prompt, fused):
                         cfg, "77", "20", str(n_prompt)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-4000:]
     assert f"TP{world} OK" in r.stdout
+
+
+@pytest.mark.parametrize("fused", [1, 0])
+def test_tp_sampler_draws_equal_the_oracle(fused):
+    """Temperature / top-k / top-p sampling under tensor parallelism: every rank gathers the logits row and makes the same draw;
+    each draw equals the oracle's draw from the gathered logits."""
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", LUM_TP_FUSED=str(fused), LUM_TP_SAMPLE="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29634", os.path.join(ROOT, "tests", "tp_worker.py"),
+                        "small_q8", "77", "16", "12"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-4000:]
+    assert "TP2 OK sampled" in r.stdout
