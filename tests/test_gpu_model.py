@@ -326,7 +326,7 @@ def test_profile_restores_state(pkg, rt):
     assert rt.launches_per_step() in (1, 2 + 5 * desc.n_layers)
 
 
-@pytest.mark.parametrize("name", ["llama3_8b_q8", "qwen3_4b_q8"])
+@pytest.mark.parametrize("name", ["llama3_8b_q8", "qwen3_4b_q8", "gpt_oss_20b_q8"])
 def test_full_size_configuration_matches_oracle_fixture(pkg, name):
     """The configurations the benchmark numbers are quoted on, whole: every layer, the whole vocabulary, the benchmark's
     seed and prompt.  Checked against the oracle's committed outputs (tests/golden/make_golden.py <name>): the first 32
