@@ -113,6 +113,13 @@ typedef struct lum_model_desc {
     float swiglu_limit;          /* clamp of the experts' gate / up values (the reference: 7.0) */
     /* expert parallel: this rank holds experts [ep_rank * n_experts / ep_size, ...); 0 / 1 = all of them (see lum_ep_*) */
     int32_t ep_size, ep_rank;
+    /* Paged K/V cache (no counterpart in the reference, whose caches are one buffer per layer, model.rs:194-223).  0: every
+     * sequence owns max_seq contiguous rows.  > 0 (a power of two >= 64 that divides max_seq): the cache of a layer is a pool of
+     * pages of this many rows; a sequence holds only the pages its rows have reached, sequences that share a prefix
+     * (lum_kv_copy) share its whole pages until one of them writes there, and lum_kv_release returns a sequence's pages.
+     * kv_pool_pages: pages in the pool (0: max_batch * max_seq / kv_page_rows, enough for every sequence at full length;
+     * fewer = more sequences than the memory could hold at full length each).  Not with the persistent-kernel executor. */
+    int32_t kv_page_rows, kv_pool_pages;
 } lum_model_desc;
 
 int32_t lum_model_init(lum_rt* rt, const lum_model_desc* desc);
@@ -207,8 +214,15 @@ int32_t lum_kv_save(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, void*
 int32_t lum_kv_load(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, const void* host, size_t bytes);
 /* Rows [0, rows) of every layer's K and V cache of sequence `src_seq` copied to sequence `dst_seq` on the device (both
  * < max_batch): a prompt prefix computed once and shared by several sequences.  Asynchronous on the runtime's stream.  (The
- * reference's caller would copy its own cache buffers, examples/llama/src/model.rs:194-223.) */
+ * reference's caller would copy its own cache buffers, examples/llama/src/model.rs:194-223.)  With a paged cache the
+ * whole pages of the prefix are shared, not copied (copy on write), and only the rows of the last, partial page move.
+ * What `dst_seq` held before is dropped. */
 int32_t lum_kv_copy(lum_rt* rt, int32_t src_seq, int32_t dst_seq, int32_t rows);
+/* Paged cache: give the pages of sequence `seq` back to the pool (a request that ended).  A contiguous cache has nothing to
+ * give back: the call succeeds and does nothing.  lum_kv_pool reports the pool: pages in all, pages free, rows per page
+ * (all zero for a contiguous cache). */
+int32_t lum_kv_release(lum_rt* rt, int32_t seq);
+int32_t lum_kv_pool(const lum_rt* rt, int32_t* pages_total, int32_t* pages_free, int32_t* page_rows);
 
 /* ---------------------------------------------------------------------------------------------
  * Execution, at the level of the reference's decode loop (examples/llama/src/main.rs:82-118):

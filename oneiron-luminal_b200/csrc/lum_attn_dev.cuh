@@ -160,7 +160,7 @@ __device__ __forceinline__ void attn_prefetch_rows(const AttnArgs& a, int kvh, i
     const size_t row_bytes = (size_t)a.n_kv * kRowBytes;
     for (int i = tid; i < nc * 2 * kLines; i += kAttnThreads) {
         const int r = i / (2 * kLines), w = i - r * (2 * kLines);
-        const char* base = (const char*)(w < kLines ? a.k_cache : a.v_cache) + (size_t)(r0 + r) * row_bytes + (size_t)kvh * kRowBytes + (size_t)(w % kLines) * 128;
+        const char* base = (const char*)(w < kLines ? a.k_cache : a.v_cache) + kv_phys_row(a.pg, 0, 0, r0 + r) * row_bytes + (size_t)kvh * kRowBytes + (size_t)(w % kLines) * 128;
         asm volatile("prefetch.global.L2 [%0];" ::"l"(base));
     }
 }
@@ -249,7 +249,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
     sync();
     if (owns_new) {
         // append this step's row to the cache; keep the rounded values for our own use
-        const size_t off = (size_t)p * row_elems + (size_t)kvh * HD;
+        const size_t off = kv_phys_row(a.pg, 0, 0, p) * row_elems + (size_t)kvh * HD;
         for (int e = tid; e < HD; e += kAttnThreads) {
             if (BF16) {
                 const __nv_bfloat16 kb = __float2bfloat16_rn(s_q[G][e]), vb = __float2bfloat16_rn(s_v[e]);
@@ -279,7 +279,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
     using Raw = typename RawRow<BF16, DPL>::type;
     Raw kn = Raw(), vn = Raw();
     if (warp < nc) {
-        const size_t off = (size_t)(r0 + warp) * row_elems + (size_t)kvh * HD + d0;
+        const size_t off = kv_phys_row(a.pg, 0, 0, r0 + warp) * row_elems + (size_t)kvh * HD + d0;
         kn = raw_load<BF16, DPL>(a.k_cache, off);
         vn = raw_load<BF16, DPL>(a.v_cache, off);
     }
@@ -288,7 +288,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnArgs& a, unsigned cha
         float kr[DPL], vr[DPL];
         const Raw kc = kn, vc = vn;
         if (j + NW < nc) {
-            const size_t off = (size_t)(r0 + j + NW) * row_elems + (size_t)kvh * HD + d0;
+            const size_t off = kv_phys_row(a.pg, 0, 0, r0 + j + NW) * row_elems + (size_t)kvh * HD + d0;
             kn = raw_load<BF16, DPL>(a.k_cache, off);
             vn = raw_load<BF16, DPL>(a.v_cache, off);
         }

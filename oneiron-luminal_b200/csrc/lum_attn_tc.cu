@@ -115,11 +115,14 @@ __global__ void __launch_bounds__(kAtThreads, 1) attn_prompt_tc(const AttnRowsAr
     const int n_tiles = pos_max >= 0 ? pos_max / kAtKT + 1 : 0;
 
     const size_t row_elems = (size_t)a.n_kv * kAtHD;
-    const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache + (size_t)a.seq0 * a.max_seq * row_elems + (size_t)kvh * kAtHD;
-    const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache + (size_t)a.seq0 * a.max_seq * row_elems + (size_t)kvh * kAtHD;
+    const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache + (size_t)kvh * kAtHD;
+    const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache + (size_t)kvh * kAtHD;
     // one K and one V tile: 64 positions x 16 column groups = 1024 16-byte chunks each; a warp takes 8 positions x 4 groups
     auto load_tile = [&](int t, int buf) {
         const uint32_t kdst = s_base + kAtOffK + buf * kAtKVBytes, vdst = s_base + kAtOffV + buf * kAtKVBytes;
+        // the tile's 64 positions start on a multiple of 64: one sequence slot or one page (of at least 64 rows) holds them all;
+        // its first position is at most pos_max, so it is mapped
+        const size_t tile_row = kv_phys_row(a.pg, a.seq0, a.max_seq, t * kAtKT);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int ch = tid + i * kAtThreads;
@@ -127,7 +130,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attn_prompt_tc(const AttnRowsAr
             const int key = (w >> 2) * 8 + (l >> 2), c = (w & 3) * 4 + (l & 3);
             const int j = t * kAtKT + key;
             const bool in = j <= pos_max;                      // rows never written (or beyond the capacity) read as zeros
-            const size_t off = (size_t)(in ? j : 0) * row_elems + c * 8;
+            const size_t off = (tile_row + (size_t)(in ? key : 0)) * row_elems + c * 8;
             cp_async16(kdst + c * 1024 + key * 16, kc + off, in ? 16u : 0u);
             cp_async16(vdst + c * 1024 + key * 16, vc + off, in ? 16u : 0u);
         }

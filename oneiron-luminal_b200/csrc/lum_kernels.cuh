@@ -99,12 +99,22 @@ struct GemvArgs {
     long long wait_cycles;        // budget of a wait on a word another GPU must write, in SM clocks (0: LUM_WAIT_BUDGET_CYCLES, about 2 s)
 };
 
+// Logical cache rows -> physical rows.  table == nullptr: sequence `seq` owns the rows [seq * max_seq, (seq + 1) * max_seq) of the
+// cache (contiguous slots).  Otherwise the cache is a pool of pages of 2^lg rows, and table[seq * pages_per_seq + (row >> lg)] names the
+// page that holds the row.  The table is written by the host between launches only.
+struct KvPages { const int* table; int lg; int pages_per_seq; };
+__device__ __forceinline__ size_t kv_phys_row(const KvPages& pg, int seq, int max_seq, int row) {
+    if (!pg.table) return (size_t)seq * max_seq + row;
+    return ((size_t)__ldg(pg.table + (size_t)seq * pg.pages_per_seq + (row >> pg.lg)) << pg.lg) + (size_t)(row & ((1 << pg.lg) - 1));
+}
+
 struct AttnArgs {
     const float* q;        // [n_q * hd] this step's queries (before RoPE)
     const float* k_new;    // [n_kv * hd] this step's keys (before RoPE)
     const float* v_new;    // [n_kv * hd]
-    void* k_cache;         // [max_seq, n_kv * hd] bf16 or f32
+    void* k_cache;         // [max_seq, n_kv * hd] bf16 or f32: this sequence's slot — or, with pages, the whole pool
     void* v_cache;
+    KvPages pg;            // pages: table points at this sequence's entries (use kv_phys_row(pg, 0, 0, row)); table null: contiguous
     float* out;            // [n_q * hd]
     float* part;           // [n_kv, n_splits, G, hd + 2] scratch: unnormalised partial outputs + (max, sum)
     unsigned int* counters;// [n_kv] arrival tickets, left at 0

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(256) rope_append_rows(const RopeRowsArgs a) {
     }
     __syncthreads();
     for (int i = tid; i < qd; i += 256) a.q_rot[(size_t)m * qd + i] = row[i];
-    const size_t off = ((size_t)seq * a.max_seq + pos) * kvd;
+    const size_t off = kv_phys_row(a.pg, seq, a.max_seq, pos) * kvd;
     for (int i = tid; i < kvd; i += 256) {
         const float k = row[qd + i], v = row[qd + kvd + i];
         if (a.kv_bf16) {
@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(256) attn_rows(const AttnRowsArgs a) {
     if (pos < 0 || pos >= a.max_seq || seq < 0 || seq >= a.max_batch) return;       // flagged by the append kernel
     const int lo = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
     const size_t row_elems = (size_t)a.n_kv * HD;
-    const size_t base = (size_t)seq * a.max_seq * row_elems + (size_t)kvh * HD + lane * DPL;
+    const size_t base = (size_t)kvh * HD + lane * DPL;
+    auto row_off = [&](int r) { return base + kv_phys_row(a.pg, seq, a.max_seq, r) * row_elems; };
     const float scale = 1.0f / sqrtf((float)HD);
     float q[GM][DPL], o[GM][DPL], mx[GM], l[GM];
 #pragma unroll
@@ -149,16 +150,16 @@ __global__ void __launch_bounds__(256) attn_rows(const AttnRowsArgs a) {
     Raw kn = Raw(), vn = Raw();
     int j = lo + warp;
     if (j <= pos) {
-        kn = raw_load<BF16, DPL>(a.k_cache, base + (size_t)j * row_elems);
-        vn = raw_load<BF16, DPL>(a.v_cache, base + (size_t)j * row_elems);
+        kn = raw_load<BF16, DPL>(a.k_cache, row_off(j));
+        vn = raw_load<BF16, DPL>(a.v_cache, row_off(j));
     }
 #pragma unroll 1
     for (; j <= pos; j += NW) {
         float kr[DPL], vr[DPL];
         const Raw kc = kn, vc = vn;
         if (j + NW <= pos) {
-            kn = raw_load<BF16, DPL>(a.k_cache, base + (size_t)(j + NW) * row_elems);
-            vn = raw_load<BF16, DPL>(a.v_cache, base + (size_t)(j + NW) * row_elems);
+            kn = raw_load<BF16, DPL>(a.k_cache, row_off(j + NW));
+            vn = raw_load<BF16, DPL>(a.v_cache, row_off(j + NW));
         }
         raw_to_float<BF16, DPL>(kc, kr);
         raw_to_float<BF16, DPL>(vc, vr);
@@ -232,8 +233,8 @@ __global__ void __launch_bounds__(128) attn_rows_split(const AttnRowsArgs a, int
     const int per = ((n_keys + n_splits - 1) / n_splits + 31) & ~31;                // keys per split, whole 32-key tiles
     const int k0 = sp * per, k1 = min(n_keys, k0 + per);
     const size_t row_elems = (size_t)a.n_kv * HD;
-    const __nv_bfloat16* kc = (const __nv_bfloat16*)a.k_cache + (size_t)seq * a.max_seq * row_elems + (size_t)kvh * HD;
-    const __nv_bfloat16* vc = (const __nv_bfloat16*)a.v_cache + (size_t)seq * a.max_seq * row_elems + (size_t)kvh * HD;
+    const __nv_bfloat16* kc0 = (const __nv_bfloat16*)a.k_cache + (size_t)kvh * HD;
+    const __nv_bfloat16* vc0 = (const __nv_bfloat16*)a.v_cache + (size_t)kvh * HD;
     const float scale = 1.0f / sqrtf((float)HD);
     for (int i = tid; i < GM * HD; i += 128) {
         const int g = i / HD, e = i - g * HD;
@@ -251,6 +252,10 @@ __global__ void __launch_bounds__(128) attn_rows_split(const AttnRowsArgs a, int
     for (int j0 = k0 + warp * 32; j0 < k1; j0 += NW * 32) {
         const int j = j0 + lane;
         const bool live = j < k1;
+        // the tile's 32 keys start on a multiple of 32: one sequence slot or one page holds them all
+        const size_t tile_off = (kv_phys_row(a.pg, seq, a.max_seq, j0) - (size_t)j0) * row_elems;
+        const __nv_bfloat16* kc = kc0 + tile_off;
+        const __nv_bfloat16* vc = vc0 + tile_off;
         // ---- scores of this lane's key
         float sc[GM];
 #pragma unroll

@@ -46,7 +46,8 @@ struct RopeRowsArgs {
     const int* row_seq;        // [M] or null: every row belongs to sequence seq0
     int seq0;
     float* q_rot;              // [M][n_q * hd]: rotated queries
-    void* k_cache; void* v_cache;   // [max_batch][max_seq][n_kv * hd]
+    void* k_cache; void* v_cache;   // [max_batch][max_seq][n_kv * hd], or a pool of pages (pg)
+    KvPages pg;
     const void* q_gain; const void* k_gain; int gain_kind; float qk_eps;
     int M, n_q, n_kv, hd, kv_bf16, rope_style, max_seq, max_batch;
     float c_inv_d, c_ln_theta, c_log2e, c_half_pi, theta;
@@ -55,6 +56,7 @@ struct RopeRowsArgs {
 struct AttnRowsArgs {
     const float* q_rot;        // [M][n_q * hd]
     const void* k_cache; const void* v_cache;
+    KvPages pg;                // pages of at least 64 rows: a tile of 32 or 64 keys that starts on a multiple of its size lies in one page
     const int* row_pos; const int* row_seq; int seq0;
     float* out;                // [M][n_q * hd]
     int M, n_q, n_kv, hd, kv_bf16, window, max_seq, max_batch;

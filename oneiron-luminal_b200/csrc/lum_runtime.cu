@@ -179,7 +179,7 @@ struct lum_rt {
         float* attn_part = nullptr; int attn_part_rows = 0;          // split partials of the few-rows attention kernel
         float *qkv = nullptr, *o = nullptr, *gu = nullptr, *down = nullptr, *logits = nullptr;   // K-split partial planes of the products
         int8_t* xq = nullptr; float* sx = nullptr;                   // quantised activation rows of the product in flight
-        std::vector<int32_t> h_tok, h_pos;
+        std::vector<int32_t> h_tok, h_pos, h_slot;
     } rows;
     float* yarn_inv = nullptr;        // rope_style 2: inverse-frequency table [head_dim / 2] on the device
     float yarn_factor_cs = 1.0f;      // ... and the factor on cos / sin
@@ -189,6 +189,13 @@ struct lum_rt {
     int prefill_min_rows = 4;
     long long wait_cycles = 0;        // lum_config.wait_budget_ms in SM clocks (0: the library default)
     int max_batch = 1, cur_seq = 0;
+    // Paged K/V cache (lum_model_desc::kv_page_rows > 0): one pool of pages per layer and kind, the same page ids in all of them.
+    int page_rows = 0, page_lg = 0, pages_per_seq = 0, pool_pages = 0;
+    int* d_page_table = nullptr;          // [max_batch][pages_per_seq] physical page of each logical page (0 where unmapped)
+    std::vector<int> h_page_table;        // host mirror, -1 = unmapped
+    std::vector<int> page_ref;            // references per physical page (a prefix shared by several sequences counts once per sequence)
+    std::vector<int> page_free;           // stack of free pages
+    int h_next_pos = 0;                   // host mirror of the decode state's position (the next row a step without a forced position writes)
     int batch_n = 0;                  // sequences of the running batch (lum_batch_begin)
     int *b_step = nullptr, *b_log = nullptr;     // batched decode: step counter and token log [max_new_tokens][max_batch] on the device
     cudaGraphExec_t g_batch = nullptr;
@@ -312,6 +319,7 @@ void free_model(lum_rt* rt) {
     rt->rows = lum_rt::Rows();
     rt->b_step = nullptr; rt->b_log = nullptr;
     rt->attn_cnt = nullptr; rt->am_cnt = nullptr; rt->d_sample = nullptr;
+    rt->d_page_table = nullptr; rt->page_rows = 0; rt->h_page_table.clear(); rt->page_ref.clear(); rt->page_free.clear();
     rt->mega_ok = false; rt->mega_layers = nullptr; rt->forced_dev = nullptr; rt->gbar = nullptr; rt->abort_flag = nullptr; rt->job_ctr = nullptr; rt->step_ctr = nullptr;
     for (void* p : rt->allocs) cudaFree(p);
     rt->allocs.clear();
@@ -513,6 +521,10 @@ int issue_step(lum_rt* rt, bool with_head, bool pdl, int* n_launch) {
         t.q = rt->qkv; t.k_new = rt->qkv + (size_t)rt->nq_l * hd; t.v_new = t.k_new + (size_t)rt->nkv_l * hd;
         const size_t seq_off = (size_t)rt->cur_seq * d.max_seq * rt->nkv_l * hd * (d.kv_dtype == LUM_BF16 ? 2 : 4);
         t.k_cache = (char*)w.kc + seq_off; t.v_cache = (char*)w.vc + seq_off; t.out = rt->attn; t.part = rt->attn_part; t.counters = rt->attn_cnt;
+        if (rt->page_rows) {     // the pool, and this sequence's entries of the page table
+            t.k_cache = w.kc; t.v_cache = w.vc;
+            t.pg = KvPages{rt->d_page_table + (size_t)rt->cur_seq * rt->pages_per_seq, rt->page_lg, rt->pages_per_seq};
+        }
         t.state = rt->state; t.q_gain = d.qk_norm ? w.q_norm.w : nullptr; t.k_gain = d.qk_norm ? w.k_norm.w : nullptr;
         t.gain_kind = gk; t.qk_eps = d.rms_eps; t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.n_splits = rt->n_splits;
         t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
@@ -701,6 +713,71 @@ int run_step(lum_rt* rt, bool with_head) {
     return issue_step(rt, with_head, rt->cfg.use_pdl != 0, with_head ? &rt->launches_full : nullptr);
 }
 
+// ---- paged K/V cache ------------------------------------------------------------------------------------------------
+KvPages kv_pages(const lum_rt* rt) { return rt->page_rows ? KvPages{rt->d_page_table, rt->page_lg, rt->pages_per_seq} : KvPages{nullptr, 0, 0}; }
+size_t kv_row_bytes(const lum_rt* rt) { return (size_t)rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4); }
+
+int kv_page_upload(lum_rt* rt, int seq, int lp) {
+    const size_t i = (size_t)seq * rt->pages_per_seq + lp;
+    const int v = rt->h_page_table[i] < 0 ? 0 : rt->h_page_table[i];
+    CU(rt, cudaMemcpyAsync(rt->d_page_table + i, &v, 4, cudaMemcpyHostToDevice, rt->stream));     // pageable source: staged before the call returns
+    return 0;
+}
+void kv_page_unref(lum_rt* rt, int page) {
+    if (page >= 0 && --rt->page_ref[(size_t)page] == 0) rt->page_free.push_back(page);
+}
+int kv_page_take(lum_rt* rt, int* page) {
+    if (rt->page_free.empty()) return fail(rt, LUM_E_NOMEM, "the K/V page pool is exhausted (%d pages of %d rows): release a sequence (lum_kv_release) or load the model with more kv_pool_pages",
+                                           rt->pool_pages, rt->page_rows);
+    *page = rt->page_free.back();
+    rt->page_free.pop_back();
+    rt->page_ref[(size_t)*page] = 1;
+    return 0;
+}
+// Rows [from, to) of sequence `seq` are about to be written: map the pages that hold them, and give the sequence a copy of its own of
+// any page it shares with another sequence (a shared prefix is read-only).  Contiguous caches: nothing to do.
+int kv_ensure(lum_rt* rt, int seq, int from, int to) {
+    if (!rt->page_rows || to <= from) return 0;
+    const size_t page_bytes = (size_t)rt->page_rows * kv_row_bytes(rt);
+    for (int lp = from >> rt->page_lg; lp <= (to - 1) >> rt->page_lg; lp++) {
+        int& e = rt->h_page_table[(size_t)seq * rt->pages_per_seq + lp];
+        if (e >= 0 && rt->page_ref[(size_t)e] == 1) continue;
+        int fresh = -1;
+        if (int r = kv_page_take(rt, &fresh)) return r;
+        if (e >= 0) {      // shared: copy what it holds, then let go of it
+            for (const LayerW& w : rt->L) {
+                CU(rt, cudaMemcpyAsync((char*)w.kc + fresh * page_bytes, (const char*)w.kc + e * page_bytes, page_bytes, cudaMemcpyDeviceToDevice, rt->stream));
+                CU(rt, cudaMemcpyAsync((char*)w.vc + fresh * page_bytes, (const char*)w.vc + e * page_bytes, page_bytes, cudaMemcpyDeviceToDevice, rt->stream));
+            }
+            kv_page_unref(rt, e);
+        }
+        e = fresh;
+        if (int r = kv_page_upload(rt, seq, lp)) return r;
+    }
+    return 0;
+}
+void kv_release_seq(lum_rt* rt, int seq) {
+    for (int lp = 0; lp < rt->pages_per_seq; lp++) {
+        int& e = rt->h_page_table[(size_t)seq * rt->pages_per_seq + lp];
+        kv_page_unref(rt, e);
+        e = -1;
+    }
+}
+// Rows [0, rows) of one layer's K or V cache of sequence `seq`, page by page: fn(device pointer, first row, row count).
+template <typename F>
+int kv_for_spans(lum_rt* rt, int seq, int layer, int kind, int rows, const char* who, F fn) {
+    char* base = (char*)(kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc);
+    const size_t rb = kv_row_bytes(rt);
+    if (!rt->page_rows) return fn(base + (size_t)seq * rt->d.max_seq * rb, 0, rows);
+    for (int r0 = 0; r0 < rows; r0 += rt->page_rows) {
+        const int e = rt->h_page_table[(size_t)seq * rt->pages_per_seq + (r0 >> rt->page_lg)];
+        if (e < 0) return fail(rt, LUM_E_INVALID, "%s: rows from %d on of sequence %d were never written", who, r0, seq);
+        const int n = rows - r0 < rt->page_rows ? rows - r0 : rt->page_rows;
+        if (int r = fn(base + (size_t)e * rt->page_rows * rb, r0, n)) return r;
+    }
+    return 0;
+}
+
 // ---- steps of several rows ----------------------------------------------------------------------------------------
 // Every linear of the model in the packed tile stream, one GPU: the tensor-core products can take the model's rows.
 bool rows_supported(const lum_rt* rt) {
@@ -802,7 +879,7 @@ int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int se
         {
             RopeRowsArgs t{};
             t.qkv = b.qkv; t.n_parts = ks_qkv; t.part_stride = (size_t)M * W; t.row_pos = d_pos; t.row_seq = d_seq; t.seq0 = seq0;
-            t.q_rot = b.q_rot; t.k_cache = w.kc; t.v_cache = w.vc;
+            t.q_rot = b.q_rot; t.k_cache = w.kc; t.v_cache = w.vc; t.pg = kv_pages(rt);
             t.q_gain = d.qk_norm ? w.q_norm.w : nullptr; t.k_gain = d.qk_norm ? w.k_norm.w : nullptr; t.gain_kind = gk; t.qk_eps = d.rms_eps;
             t.M = M; t.n_q = rt->nq_l; t.n_kv = rt->nkv_l; t.hd = hd; t.kv_bf16 = d.kv_dtype == LUM_BF16; t.rope_style = d.rope_style;
             t.max_seq = d.max_seq; t.max_batch = rt->max_batch;
@@ -810,7 +887,7 @@ int run_rows(lum_rt* rt, int M, int* d_tok, int* d_pos, const int* d_seq, int se
             t.status = rt->status;
             CU(rt, launch_rope_append_rows(t, st));
             AttnRowsArgs a{};
-            a.q_rot = b.q_rot; a.k_cache = w.kc; a.v_cache = w.vc; a.row_pos = d_pos; a.row_seq = d_seq; a.seq0 = seq0; a.out = b.attn;
+            a.q_rot = b.q_rot; a.k_cache = w.kc; a.v_cache = w.vc; a.pg = kv_pages(rt); a.row_pos = d_pos; a.row_seq = d_seq; a.seq0 = seq0; a.out = b.attn;
             a.M = M; a.n_q = rt->nq_l; a.n_kv = rt->nkv_l; a.hd = hd; a.kv_bf16 = t.kv_bf16; a.window = 0; a.max_seq = d.max_seq; a.max_batch = rt->max_batch;
             a.status = rt->status; a.part = b.attn_part; a.part_rows = b.attn_part_rows;
             // many rows of one sequence (a prompt): the tensor-core kernel; few rows, or rows of different sequences: one CTA per row
@@ -923,6 +1000,15 @@ int run_prompt_rows(lum_rt* rt, int n, const int32_t* forced, int pos0) {
 // every sample back in).  The persistent kernel takes them all in one launch; otherwise one step per token.
 int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
     if (n <= 0) return 0;
+    {   // where this sequence's rows go: the prompt's positions, or the next n after what the last call left
+        int& len = rt->h_next_pos;
+        const int from = forced ? pos0 : len;
+        if (rt->page_rows) {      // (a contiguous cache lets the kernels flag a position beyond the capacity)
+            if (from + n > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "%d tokens from position %d pass the cache capacity %d", n, from, rt->d.max_seq);
+            if (int r = kv_ensure(rt, rt->cur_seq, from, from + n)) return r;
+        }
+        len = from + n;
+    }
     if (forced && !rt->body_only && n >= rt->prefill_min_rows && !(rt->mega_ok && rt->use_mega) && rows_supported(rt))
         return run_prompt_rows(rt, n, forced, pos0);
     if (rt->mega_ok && rt->use_mega) {
@@ -960,7 +1046,7 @@ int run_tokens(lum_rt* rt, int n, const int32_t* forced, int pos0) {
 int setup_mega(lum_rt* rt) {
     rt->mega_ok = false;
     const lum_model_desc& d = rt->d;
-    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || d.tp_size > 1 || d.max_batch > 1) return 0;
+    if (d.weight_dtype != LUM_Q8_0 || d.tied_head || d.tp_size > 1 || d.max_batch > 1 || d.kv_page_rows > 0) return 0;
     if (d.n_experts > 0 || d.proj_bias || d.attn_sinks || d.sliding_window > 0 || d.rope_style == 2) return 0;
     std::vector<MegaLayer> hl((size_t)d.n_layers);
     bool packed = rt->lm_head.kc > 0;
@@ -1384,30 +1470,35 @@ int32_t lum_profile_llir(lum_rt* rt, const uint8_t* blob, size_t size, uint64_t 
     return 0;
 }
 
-static int kv_span(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, size_t bytes, void** dev, const char* who) {
+static int kv_check(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, size_t bytes, const char* who) {
     if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "%s: no model", who);
     if (layer < 0 || layer >= rt->d.n_layers || rows < 0 || rows > rt->d.max_seq || (kind != 0 && kind != 1)) return fail(rt, LUM_E_INVALID, "%s: bad layer / kind / rows", who);
-    const size_t want = (size_t)rows * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
+    const size_t want = (size_t)rows * kv_row_bytes(rt);
     if (bytes != want) return fail(rt, LUM_E_INVALID, "%s: %d rows are %zu bytes in the cache's own type, got %zu", who, rows, want, bytes);
-    const size_t seq_off = (size_t)rt->cur_seq * rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
-    *dev = (char*)(kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc) + seq_off;
     return 0;
 }
 int32_t lum_kv_save(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, void* host_out, size_t bytes) {
-    void* dev = nullptr;
-    if (int r = kv_span(rt, layer, kind, rows, bytes, &dev, "kv_save")) return r;
+    if (int r = kv_check(rt, layer, kind, rows, bytes, "kv_save")) return r;
     if (!host_out) return fail(rt, LUM_E_INVALID, "kv_save: null output");
     CU(rt, cudaSetDevice(rt->cfg.device));
-    if (bytes) CU(rt, cudaMemcpyAsync(host_out, dev, bytes, cudaMemcpyDeviceToHost, rt->stream));
+    const size_t rb = kv_row_bytes(rt);
+    if (int r = kv_for_spans(rt, rt->cur_seq, layer, kind, rows, "kv_save", [&](char* dev, int r0, int n) -> int {
+            CU(rt, cudaMemcpyAsync((char*)host_out + (size_t)r0 * rb, dev, (size_t)n * rb, cudaMemcpyDeviceToHost, rt->stream));
+            return 0;
+        })) return r;
     CU(rt, cudaStreamSynchronize(rt->stream));
     return 0;
 }
 int32_t lum_kv_load(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, const void* host, size_t bytes) {
-    void* dev = nullptr;
-    if (int r = kv_span(rt, layer, kind, rows, bytes, &dev, "kv_load")) return r;
+    if (int r = kv_check(rt, layer, kind, rows, bytes, "kv_load")) return r;
     if (!host) return fail(rt, LUM_E_INVALID, "kv_load: null input");
     CU(rt, cudaSetDevice(rt->cfg.device));
-    if (bytes) CU(rt, cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, rt->stream));
+    if (int r = kv_ensure(rt, rt->cur_seq, 0, rows)) return r;
+    const size_t rb = kv_row_bytes(rt);
+    if (int r = kv_for_spans(rt, rt->cur_seq, layer, kind, rows, "kv_load", [&](char* dev, int r0, int n) -> int {
+            CU(rt, cudaMemcpyAsync(dev, (const char*)host + (size_t)r0 * rb, (size_t)n * rb, cudaMemcpyHostToDevice, rt->stream));
+            return 0;
+        })) return r;
     CU(rt, cudaStreamSynchronize(rt->stream));
     return 0;
 }
@@ -1418,11 +1509,50 @@ int32_t lum_kv_copy(lum_rt* rt, int32_t src_seq, int32_t dst_seq, int32_t rows) 
         return fail(rt, LUM_E_INVALID, "kv_copy: sequences %d -> %d of %d, %d rows of %d", src_seq, dst_seq, rt->max_batch, rows, rt->d.max_seq);
     if (src_seq == dst_seq || rows == 0) return 0;
     CU(rt, cudaSetDevice(rt->cfg.device));
+    if (rt->page_rows) {
+        // whole pages of the prefix are shared (whoever writes into one first gets a copy of its own, see kv_ensure); the rows of the
+        // last, partial page are copied into a page of dst's own
+        const int full = rows >> rt->page_lg, rest = rows & (rt->page_rows - 1);
+        for (int lp = 0; lp < full + (rest ? 1 : 0); lp++)
+            if (rt->h_page_table[(size_t)src_seq * rt->pages_per_seq + lp] < 0) return fail(rt, LUM_E_INVALID, "kv_copy: sequence %d has no rows from %d on", src_seq, lp * rt->page_rows);
+        kv_release_seq(rt, dst_seq);
+        for (int lp = 0; lp < full; lp++) {
+            const int e = rt->h_page_table[(size_t)src_seq * rt->pages_per_seq + lp];
+            rt->page_ref[(size_t)e]++;
+            rt->h_page_table[(size_t)dst_seq * rt->pages_per_seq + lp] = e;
+            if (int r = kv_page_upload(rt, dst_seq, lp)) return r;
+        }
+        if (rest) {
+            if (int r = kv_ensure(rt, dst_seq, full * rt->page_rows, rows)) return r;
+            const int se = rt->h_page_table[(size_t)src_seq * rt->pages_per_seq + full], de = rt->h_page_table[(size_t)dst_seq * rt->pages_per_seq + full];
+            const size_t rb = kv_row_bytes(rt), pb = (size_t)rt->page_rows * rb;
+            for (const LayerW& w : rt->L) {
+                CU(rt, cudaMemcpyAsync((char*)w.kc + de * pb, (const char*)w.kc + se * pb, rest * rb, cudaMemcpyDeviceToDevice, rt->stream));
+                CU(rt, cudaMemcpyAsync((char*)w.vc + de * pb, (const char*)w.vc + se * pb, rest * rb, cudaMemcpyDeviceToDevice, rt->stream));
+            }
+        }
+        return 0;
+    }
     const size_t row_bytes = (size_t)rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4), seq_bytes = (size_t)rt->d.max_seq * row_bytes;
     for (const LayerW& w : rt->L) {
         CU(rt, cudaMemcpyAsync((char*)w.kc + dst_seq * seq_bytes, (const char*)w.kc + src_seq * seq_bytes, rows * row_bytes, cudaMemcpyDeviceToDevice, rt->stream));
         CU(rt, cudaMemcpyAsync((char*)w.vc + dst_seq * seq_bytes, (const char*)w.vc + src_seq * seq_bytes, rows * row_bytes, cudaMemcpyDeviceToDevice, rt->stream));
     }
+    return 0;
+}
+
+int32_t lum_kv_release(lum_rt* rt, int32_t seq) {
+    if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "kv_release: no model");
+    if (seq < 0 || seq >= rt->max_batch) return fail(rt, LUM_E_INVALID, "kv_release: sequence %d outside max_batch %d", seq, rt->max_batch);
+    if (rt->page_rows) kv_release_seq(rt, seq);      // the device table keeps stale entries: nothing reads rows of a sequence that has none
+    return 0;
+}
+
+int32_t lum_kv_pool(const lum_rt* rt, int32_t* pages_total, int32_t* pages_free, int32_t* page_rows) {
+    if (!rt || !rt->has_model) return LUM_E_INVALID;
+    if (pages_total) *pages_total = rt->pool_pages;
+    if (pages_free) *pages_free = (int32_t)rt->page_free.size();
+    if (page_rows) *page_rows = rt->page_rows;
     return 0;
 }
 
@@ -1516,6 +1646,7 @@ int32_t lum_batch_begin_slots(lum_rt* rt, int32_t n_seq, const int32_t* slots, c
     CU(rt, cudaStreamSynchronize(rt->stream));
     rt->batch_n = n_seq;
     rt->rows.h_pos.assign(positions, positions + n_seq);        // host copy: the capacity check of lum_batch_decode
+    rt->rows.h_slot = row_slot;
     return 0;
 }
 
@@ -1525,6 +1656,9 @@ int32_t lum_batch_decode(lum_rt* rt, int32_t n_steps) {
     CU(rt, cudaSetDevice(rt->cfg.device));
     for (int i = 0; i < rt->batch_n; i++) {
         if (rt->rows.h_pos[(size_t)i] + n_steps > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "batch_decode: sequence %d would pass the cache capacity %d", i, rt->d.max_seq);
+    }
+    for (int i = 0; i < rt->batch_n; i++) {
+        if (int r = kv_ensure(rt, rt->rows.h_slot[(size_t)i], rt->rows.h_pos[(size_t)i], rt->rows.h_pos[(size_t)i] + n_steps)) return r;
         rt->rows.h_pos[(size_t)i] += n_steps;
     }
     const int M = rt->batch_n;
@@ -1697,7 +1831,24 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     if (d.rope_style == 2 && (d.yarn_factor <= 0.0f || d.yarn_beta_fast <= 0.0f || d.yarn_beta_slow <= 0.0f || d.yarn_orig_max_pos <= 0.0f))
         return fail(rt, LUM_E_INVALID, "rope_style 2 needs the yarn_* parameters");
     if (d.n_q_heads % tp || (d.n_q_heads / tp) % (d.n_kv_heads / tp)) return fail(rt, LUM_E_INVALID, "query heads must divide by tp_size");
+    if (d.kv_page_rows < 0 || d.kv_pool_pages < 0 || (d.kv_page_rows == 0 && d.kv_pool_pages != 0)) return fail(rt, LUM_E_INVALID, "kv_page_rows / kv_pool_pages must not be negative; a pool needs a page size");
+    if (d.kv_page_rows > 0) {
+        if (d.kv_page_rows < 64 || (d.kv_page_rows & (d.kv_page_rows - 1)) || d.max_seq % d.kv_page_rows)
+            return fail(rt, LUM_E_INVALID, "kv_page_rows %d must be a power of two >= 64 that divides max_seq %d", d.kv_page_rows, d.max_seq);
+        if (rt->cfg.use_mega) return fail(rt, LUM_E_UNSUPPORTED, "the persistent-kernel executor reads contiguous caches only");
+    }
     rt->d = d;
+    rt->page_rows = d.kv_page_rows; rt->page_lg = 0; rt->pages_per_seq = 0; rt->pool_pages = 0;
+    if (rt->page_rows) {
+        while ((1 << rt->page_lg) < rt->page_rows) rt->page_lg++;
+        rt->pages_per_seq = d.max_seq / rt->page_rows;
+        rt->pool_pages = d.kv_pool_pages > 0 ? d.kv_pool_pages : d.max_batch * rt->pages_per_seq;
+        rt->h_page_table.assign((size_t)d.max_batch * rt->pages_per_seq, -1);
+        rt->page_ref.assign((size_t)rt->pool_pages, 0);
+        rt->page_free.clear();
+        for (int i = rt->pool_pages - 1; i >= 0; i--) rt->page_free.push_back(i);      // page 0 is handed out first
+    }
+    rt->h_next_pos = 0;
     rt->nq_l = d.n_q_heads / tp; rt->nkv_l = d.n_kv_heads / tp; rt->ffn_l = d.ffn / tp; rt->vocab_l = d.vocab / tp;
     const int H = d.hidden, hd = d.head_dim, r = d.tp_rank;
     const int wk = kind_of(d.weight_dtype), ek = kind_of(d.embed_dtype);
@@ -1748,7 +1899,7 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
             TRY(alloc_tensor(rt, w.q_norm, ek, 1, hd, 1, hd, 0, 0));
             TRY(alloc_tensor(rt, w.k_norm, ek, 1, hd, 1, hd, 0, 0));
         }
-        const size_t cache_bytes = (size_t)d.max_batch * d.max_seq * kvd_l * kv_elem;
+        const size_t cache_bytes = rt->page_rows ? (size_t)rt->pool_pages * rt->page_rows * kvd_l * kv_elem : (size_t)d.max_batch * d.max_seq * kvd_l * kv_elem;
         TRY(dev_alloc(rt, &w.kc, cache_bytes));
         TRY(dev_alloc(rt, &w.vc, cache_bytes));
         cudaMemsetAsync(w.kc, 0, cache_bytes, rt->stream);
@@ -1832,6 +1983,10 @@ int32_t lum_model_init(lum_rt* rt, const lum_model_desc* dp) {
     TRY(dev_alloc(rt, (void**)&rt->am_val, kArgmaxSlots * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_idx, kArgmaxSlots * 4));
     TRY(dev_alloc(rt, (void**)&rt->am_cnt, 4));
+    if (rt->page_rows) {
+        TRY(dev_alloc(rt, (void**)&rt->d_page_table, rt->h_page_table.size() * 4));
+        cudaMemsetAsync(rt->d_page_table, 0, rt->h_page_table.size() * 4, rt->stream);
+    }
     TRY(dev_alloc(rt, (void**)&rt->d_sample, sizeof(SampleParams)));
     cudaMemcpyAsync(rt->d_sample, &rt->samp, sizeof(SampleParams), cudaMemcpyHostToDevice, rt->stream);
     TRY(dev_alloc(rt, (void**)&rt->step_ctr, ((size_t)4 * d.n_layers + 1) * sizeof(unsigned int)));
@@ -1949,7 +2104,12 @@ int32_t lum_model_weight_bytes(const lum_rt* rt, uint64_t* bytes) {
 int32_t lum_kv_reset(lum_rt* rt) {
     if (!rt || !rt->has_model) return fail(rt, LUM_E_INVALID, "kv_reset: no model");
     CU(rt, cudaSetDevice(rt->cfg.device));
-    const size_t bytes = (size_t)rt->max_batch * rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);   // every sequence
+    size_t bytes = (size_t)rt->max_batch * rt->d.max_seq * kv_row_bytes(rt);   // every sequence
+    if (rt->page_rows) {
+        bytes = (size_t)rt->pool_pages * rt->page_rows * kv_row_bytes(rt);
+        for (int sq = 0; sq < rt->max_batch; sq++) kv_release_seq(rt, sq);
+    }
+    rt->h_next_pos = 0;
     for (LayerW& w : rt->L) {
         CU(rt, cudaMemsetAsync(w.kc, 0, bytes, rt->stream));
         CU(rt, cudaMemsetAsync(w.vc, 0, bytes, rt->stream));
@@ -1967,10 +2127,13 @@ int32_t lum_kv_read(lum_rt* rt, int32_t layer, int32_t kind, int32_t rows, float
     float* tmp = nullptr;
     cudaError_t e = cudaMalloc((void**)&tmp, n * 4);
     if (e != cudaSuccess) return fail(rt, LUM_E_NOMEM, "kv_read: %s", cudaGetErrorString(e));
-    const size_t seq_off = (size_t)rt->cur_seq * rt->d.max_seq * rt->nkv_l * rt->d.head_dim * (rt->d.kv_dtype == LUM_BF16 ? 2 : 4);
-    const void* src = (const char*)(kind ? rt->L[(size_t)layer].vc : rt->L[(size_t)layer].kc) + seq_off;
-    e = launch_to_f32(src, rt->d.kv_dtype == LUM_BF16 ? WK_BF16 : WK_F32, tmp, n, rt->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
+    const size_t row_elems = (size_t)rt->nkv_l * rt->d.head_dim;
+    const int rc = kv_for_spans(rt, rt->cur_seq, layer, kind, rows, "kv_read", [&](char* dev, int r0, int nr) -> int {
+        const cudaError_t e2 = launch_to_f32(dev, rt->d.kv_dtype == LUM_BF16 ? WK_BF16 : WK_F32, tmp + (size_t)r0 * row_elems, (size_t)nr * row_elems, rt->stream);
+        return e2 == cudaSuccess ? 0 : fail(rt, LUM_E_CUDA, "kv_read: %s", cudaGetErrorString(e2));
+    });
+    if (rc) { cudaFree(tmp); return rc; }
+    e = cudaMemcpyAsync(host_out, tmp, n * 4, cudaMemcpyDeviceToHost, rt->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
     cudaFree(tmp);
     if (e != cudaSuccess) return fail(rt, LUM_E_CUDA, "kv_read: %s", cudaGetErrorString(e));
@@ -2077,6 +2240,7 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     CU(rt, cudaMemcpyAsync(&saved, rt->state, sizeof saved, cudaMemcpyDeviceToHost, rt->stream));
     CU(rt, cudaStreamSynchronize(rt->stream));
     if (saved.pos + trials + 1 > rt->d.max_seq) return fail(rt, LUM_E_INVALID, "profile: not enough cache capacity left for %d trial steps", trials);
+    rt->h_next_pos = saved.pos;
     cudaEvent_t e0, e1;
     CU(rt, cudaEventCreate(&e0));
     CU(rt, cudaEventCreate(&e1));
@@ -2092,6 +2256,7 @@ int32_t lum_profile(lum_rt* rt, int32_t trials, double* usec, char* display, siz
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     saved.log = 0;
+    rt->h_next_pos = saved.pos;
     cudaMemcpyAsync(rt->state, &saved, sizeof saved, cudaMemcpyHostToDevice, rt->stream);
     cudaStreamSynchronize(rt->stream);
     if (r) return r;

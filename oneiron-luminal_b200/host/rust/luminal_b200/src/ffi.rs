@@ -111,6 +111,8 @@ pub struct lum_model_desc {
     pub swiglu_limit: f32,
     pub ep_size: i32,
     pub ep_rank: i32,
+    pub kv_page_rows: i32,
+    pub kv_pool_pages: i32,
 }
 
 #[repr(C)]
@@ -168,6 +170,8 @@ unsafe extern "C" {
     pub fn lum_kv_save(rt: *mut lum_rt, layer: i32, kind: i32, rows: i32, host_out: *mut c_void, bytes: usize) -> i32;
     pub fn lum_kv_load(rt: *mut lum_rt, layer: i32, kind: i32, rows: i32, host: *const c_void, bytes: usize) -> i32;
     pub fn lum_kv_copy(rt: *mut lum_rt, src_seq: i32, dst_seq: i32, rows: i32) -> i32;
+    pub fn lum_kv_release(rt: *mut lum_rt, seq: i32) -> i32;
+    pub fn lum_kv_pool(rt: *const lum_rt, pages_total: *mut i32, pages_free: *mut i32, page_rows: *mut i32) -> i32;
 
     pub fn lum_set_dim(rt: *mut lum_rt, dim: c_char, value: u64) -> i32;
     pub fn lum_set_tokens(rt: *mut lum_rt, ids: *const i32, n: usize) -> i32;

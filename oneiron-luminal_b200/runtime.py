@@ -54,6 +54,7 @@ class ModelDesc(C.Structure):
         ("sliding_window", C.c_int32), ("window_even_layers", C.c_int32), ("attn_sinks", C.c_int32), ("proj_bias", C.c_int32),
         ("yarn_factor", C.c_float), ("yarn_beta_fast", C.c_float), ("yarn_beta_slow", C.c_float), ("yarn_orig_max_pos", C.c_float),
         ("n_experts", C.c_int32), ("top_k", C.c_int32), ("swiglu_limit", C.c_float), ("ep_size", C.c_int32), ("ep_rank", C.c_int32),
+        ("kv_page_rows", C.c_int32), ("kv_pool_pages", C.c_int32),
     ]
 
     def copy(self, **kw) -> "ModelDesc":
@@ -213,6 +214,8 @@ def load_library() -> C.CDLL:
         "lum_kv_save": (i32, [vp, i32, i32, i32, vp, sz]),
         "lum_kv_load": (i32, [vp, i32, i32, i32, vp, sz]),
         "lum_kv_copy": (i32, [vp, i32, i32, i32]),
+        "lum_kv_release": (i32, [vp, i32]),
+        "lum_kv_pool": (i32, [vp, P(i32), P(i32), P(i32)]),
         "lum_set_sampling": (i32, [vp, P(Sampling)]),
         "lum_op_sample_topk": (i32, [vp, i32, i32, P(Sampling), i32, vp, vp, vp]),
         "lum_get_stats": (i32, [vp, P(Stats)]),
@@ -650,6 +653,16 @@ class B200Runtime:
     def kv_copy(self, src_seq: int, dst_seq: int, rows: int) -> None:
         """The first ``rows`` cache rows of every layer copied from one sequence's slot to another's (a shared prompt prefix)."""
         self._ck(self._lib.lum_kv_copy(self._h, src_seq, dst_seq, rows))
+
+    def kv_release(self, seq: int) -> None:
+        """Paged cache: the pages of sequence ``seq`` go back to the pool (nothing to do for a contiguous cache)."""
+        self._ck(self._lib.lum_kv_release(self._h, seq))
+
+    def kv_pool(self):
+        """(pages in the pool, pages free, rows per page); zeros for a contiguous cache."""
+        a, b, c = C.c_int32(), C.c_int32(), C.c_int32()
+        self._ck(self._lib.lum_kv_pool(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
 
     def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
         """The sampler after the vocabulary projection: temperature 0 (or top_k 1) = the reference's greedy ``sample``;

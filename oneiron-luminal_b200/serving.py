@@ -109,6 +109,9 @@ class ContinuousBatcher:
         if len(r.tokens) >= r.max_new or (r.tokens and r.tokens[-1] in r.eos):
             r.done = True
             del self.live[r.slot]
+            release = getattr(self.rt, "kv_release", None)
+            if release is not None:
+                release(r.slot)                          # a paged cache gets the sequence's pages back
             self.free.append(r.slot)
             self.finished[r.rid] = r
 
