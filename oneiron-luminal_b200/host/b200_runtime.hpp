@@ -99,6 +99,9 @@ public:
     // Several sequences: cache slots, batched steps (row i of the batch works on slot slots[i])
     void seq_select(int seq) { ck(lum_seq_select(h_, seq)); }
     void kv_copy(int src_seq, int dst_seq, int rows) { ck(lum_kv_copy(h_, src_seq, dst_seq, rows)); }
+    void kv_release(int seq) { ck(lum_kv_release(h_, seq)); }                       // paged cache: pages back to the pool
+    struct KvPool { int32_t pages_total, pages_free, page_rows; };
+    KvPool kv_pool() const { KvPool p{0, 0, 0}; lum_kv_pool(h_, &p.pages_total, &p.pages_free, &p.page_rows); return p; }
     void batch_begin_slots(const std::vector<int32_t>& slots, const std::vector<int32_t>& tokens, const std::vector<int32_t>& positions) {
         if (slots.size() != tokens.size() || positions.size() != tokens.size()) throw Error(LUM_E_INVALID, "batch_begin_slots: one entry per row in each list");
         ck(lum_batch_begin_slots(h_, (int32_t)tokens.size(), slots.data(), tokens.data(), positions.data()));

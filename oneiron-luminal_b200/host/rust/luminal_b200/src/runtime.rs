@@ -186,6 +186,13 @@ impl B200Runtime {
     pub fn kv_copy(&mut self, src_seq: usize, dst_seq: usize, rows: usize) {
         self.check(unsafe { lum_kv_copy(self.h, src_seq as i32, dst_seq as i32, rows as i32) })
     }
+    /// Paged cache (`kv_page_rows` > 0): a finished sequence's pages go back to the pool; (pages, free pages, rows per page).
+    pub fn kv_release(&mut self, seq: usize) { self.check(unsafe { lum_kv_release(self.h, seq as i32) }) }
+    pub fn kv_pool(&self) -> (i32, i32, i32) {
+        let (mut a, mut b, mut c) = (0i32, 0i32, 0i32);
+        self.check(unsafe { lum_kv_pool(self.h, &mut a, &mut b, &mut c) });
+        (a, b, c)
+    }
     pub fn batch_decode(&mut self, slots: &[i32], tokens: &[i32], positions: &[i32], n_steps: usize) -> Vec<i32> {
         assert!(slots.len() == tokens.len() && positions.len() == tokens.len(), "one entry per row in each list");
         self.check(unsafe { lum_batch_begin_slots(self.h, tokens.len() as i32, slots.as_ptr(), tokens.as_ptr(), positions.as_ptr()) });
