@@ -19,11 +19,18 @@
 // Sums run in the interpreter's order (one thread per output element), so f32 sums are bit-identical to it; exp2 / log2 / sin
 // come from the CUDA math library (documented error <= 2 ulp) and may differ from a CPU libm in the last bits.
 //
+// Chains of float element-wise nodes are fused: a node whose only consumer is another float element-wise node that reads it element
+// for element (same length, row-major) is not launched; its consumer's kernel (gen_fused, a small postfix evaluator) computes it in
+// registers, rounding to the node's element type exactly where the separate kernels would have stored and reloaded it, so fused and
+// unfused execution give the same bits (LUM_GENERIC_FUSE=0 switches fusion off; the tests compare both).  Reductions, Gather, Iota,
+// integer and Bool nodes, and any edge read through a broadcast or permuted view end a chain.
+//
 // Nothing here reads memory it was not given: before a node is launched the host checks that the largest index its shapes,
 // strides and iteration counts can form lies inside the operand; Gather's data-dependent index is checked on the device.  What
 // the interpreter reports as an error (index out of range, integer modulo by zero, division by zero inside an Iota expression)
 // sets a status bit instead, the offending element becomes 0, and lum_execute returns LUM_E_DEVICE.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -146,6 +153,55 @@ __global__ void __launch_bounds__(256) gen_binary(int op, int adt, int bdt, cons
     }
 }
 
+// ---- fused chains: postfix program over up to kFuseLeaves strided operands, evaluated per output element
+constexpr int kFuseOps = 24, kFuseLeaves = 6, kFuseStack = 8;
+enum { F_LOAD = 0, F_UNARY, F_BINARY, F_CAST, F_CONST };
+struct FusedProg {
+    int n_ops, n_leaves;
+    uint8_t op[kFuseOps];       // F_*
+    uint8_t arg[kFuseOps];      // F_LOAD: leaf; F_UNARY: U_*; F_BINARY: B_*
+    uint8_t dt[kFuseOps];       // element type the node's result is rounded to
+    float imm[kFuseOps];        // F_CONST: the value
+    const void* leaf[kFuseLeaves];
+    int leaf_dt[kFuseLeaves];
+    GView view[kFuseLeaves];
+};
+__global__ void __launch_bounds__(256) gen_fused(FusedProg p, void* out, int out_dt, long long total) {
+    GRID_STRIDE(q, total) {
+        float st[kFuseStack];
+        int sp = 0;
+#pragma unroll 1
+        for (int k = 0; k < p.n_ops; k++) {
+            const int dt = p.dt[k];
+            switch (p.op[k]) {
+                case F_LOAD: { const int l = p.arg[k]; st[sp++] = ld_f32(p.leaf[l], p.leaf_dt[l], gidx(p.view[l], q)); break; }
+                case F_CONST: st[sp++] = p.imm[k]; break;
+                case F_UNARY: {
+                    const float x = st[sp - 1];
+                    float y;
+                    switch (p.arg[k]) {
+                        case U_EXP2: y = exp2f(x); break;
+                        case U_LOG2: y = log2f(x); break;
+                        case U_SIN: y = sinf(x); break;
+                        case U_RECIP: y = __fdiv_rn(1.0f, x); break;
+                        default: y = __fsqrt_rn(x); break;
+                    }
+                    st[sp - 1] = round_through(dt, y);
+                    break;
+                }
+                case F_BINARY: {
+                    const float y = round_through(dt, st[--sp]), x = st[sp - 1];
+                    const float r = p.arg[k] == B_ADD ? __fadd_rn(x, y) : p.arg[k] == B_MUL ? __fmul_rn(x, y) : fmodf(x, y);
+                    st[sp - 1] = round_through(dt, r);
+                    break;
+                }
+                default: st[sp - 1] = round_through(dt, st[sp - 1]); break;      // F_CAST between float types
+            }
+        }
+        st_float(out, out_dt, q, st[0]);
+    }
+}
+
 __global__ void __launch_bounds__(256) gen_less(int adt, int bdt, const void* a, const void* b, uint8_t* out, GView va, GView vb) {
     GRID_STRIDE(q, va.total) out[q] = ld_f32(a, adt, gidx(va, q)) < ld_f32(b, bdt, gidx(vb, q)) ? 1 : 0;
 }
@@ -255,11 +311,23 @@ bool is_primitive(const std::string& op) {
 
 }  // namespace
 
+// a float element-wise node that was not launched: its consumer computes it (or it is launched after all, if the consumer cannot)
+struct GDeferred {
+    bool on = false;
+    int kind = 0, op = 0, dt = LUM_F32;      // F_UNARY / F_BINARY / F_CAST / F_CONST, U_* / B_*, result type
+    float cval = 0.0f;                       // F_CONST
+    long long total = 0;
+    GView va{}, vb{};
+    size_t ia = 0, ib = 0;                   // operand nodes
+};
 struct lum_generic_plan {
     std::vector<Node> nodes;
     std::vector<GBuf> buf;
+    std::vector<GDeferred> def;
+    std::vector<int> n_consumers;
+    bool fuse = true;
     uint32_t* status = nullptr;
-    size_t launches = 0;
+    size_t launches = 0, fused = 0;          // kernels launched; nodes computed inside another node's kernel
 };
 
 namespace {
@@ -325,21 +393,150 @@ unsigned grid_for(long long n) {
     return (unsigned)g;
 }
 
+// ---- fusion of float element-wise chains
+bool is_float_dt(int dt) { return dt == LUM_F32 || dt == LUM_F16 || dt == LUM_BF16; }
+bool fusable_kind(const Node& n) {
+    const std::string c = canonical(n.op);
+    if (c == "Exp2" || c == "Log2" || c == "Sin" || c == "Recip" || c == "Sqrt" || c == "Add" || c == "Mul" || c == "Mod") return true;
+    return c == "Cast" && n.p.size() >= 3 && is_float_dt((int)n.p[2].dt);
+}
+GView flat_view(long long n) {
+    GView v{};
+    v.rank = 1; v.dim[0] = n; v.stride[0] = 1; v.total = n;
+    return v;
+}
+// does the view read a vector of `total` elements element for element, in order?
+bool identity_view(const GView& v, long long total) {
+    if (v.total != total) return false;
+    long long expect = 1;
+    for (int d = v.rank - 1; d >= 0; d--) {
+        if (v.dim[d] != 1 && v.stride[d] != expect) return false;
+        expect *= v.dim[d];
+    }
+    return true;
+}
+void check_launch(lum_generic_plan* P, const std::string& at) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw Fail{LUM_E_CUDA, at + ": " + cudaGetErrorString(e)};
+    P->launches++;
+}
+void launch_expr(lum_generic_plan* P, size_t k, const GDeferred& d, cudaStream_t st);
+
+// a deferred node is needed as a vector after all: launch it now
+void materialise(lum_generic_plan* P, size_t k, cudaStream_t st) {
+    if (!P->def[k].on) return;
+    const GDeferred d = P->def[k];
+    P->def[k].on = false;
+    launch_expr(P, k, d, st);
+}
+// Appends the evaluation of the node described by `d` to `g` (one value more on the evaluator's stack, which holds `depth` values
+// before).  Operands that are deferred and read element for element are inlined if the program still has room; `inlined` collects
+// them.  false: out of room (g and inlined are then garbage: the caller restores its copies).
+bool emit_expr(lum_generic_plan* P, const GDeferred& d, FusedProg& g, int depth, std::vector<size_t>& inlined, cudaStream_t st) {
+    auto operand = [&](size_t node, const GView& v, int at_depth) -> bool {
+        if (at_depth + 1 > kFuseStack) return false;
+        const GDeferred& od = P->def[node];
+        if (od.on && od.kind == F_CONST) {       // a one-element vector: whatever the view, every element reads the value
+            if (g.n_ops == kFuseOps) return false;
+            g.op[g.n_ops] = F_CONST; g.imm[g.n_ops] = od.cval; g.dt[g.n_ops] = LUM_F32; g.arg[g.n_ops] = 0;
+            g.n_ops++;
+            inlined.push_back(node);
+            return true;
+        }
+        if (od.on && identity_view(v, od.total)) {
+            const FusedProg keep = g;
+            const size_t keep_n = inlined.size();
+            if (emit_expr(P, od, g, at_depth, inlined, st)) { inlined.push_back(node); return true; }
+            g = keep;
+            inlined.resize(keep_n);
+        }
+        materialise(P, node, st);
+        const GBuf& b = P->buf[node];
+        if (!b.filled) throw Fail{LUM_E_INVALID, "node " + std::to_string(node) + ": no data for a consumer"};
+        if (g.n_leaves == kFuseLeaves || g.n_ops == kFuseOps) return false;
+        g.leaf[g.n_leaves] = b.p; g.leaf_dt[g.n_leaves] = b.dt; g.view[g.n_leaves] = v;
+        g.op[g.n_ops] = F_LOAD; g.arg[g.n_ops] = (uint8_t)g.n_leaves; g.dt[g.n_ops] = (uint8_t)b.dt;
+        g.n_leaves++; g.n_ops++;
+        return true;
+    };
+    if (!operand(d.ia, d.va, depth)) return false;
+    if (d.kind == F_BINARY && !operand(d.ib, d.vb, depth + 1)) return false;
+    if (g.n_ops == kFuseOps) return false;
+    g.op[g.n_ops] = (uint8_t)d.kind; g.arg[g.n_ops] = (uint8_t)d.op; g.dt[g.n_ops] = (uint8_t)d.dt;
+    g.n_ops++;
+    return true;
+}
+// one kernel for node k: alone (the single-node kernels) or together with the deferred producers it can take in
+void launch_expr(lum_generic_plan* P, size_t k, const GDeferred& d, cudaStream_t st) {
+    const std::string at = "node " + std::to_string(k) + " (" + P->nodes[k].op + ")";
+    if (d.kind == F_CONST) {
+        ensure(P->buf[k], 1, LUM_F32);
+        gen_fill_f32<<<1, 1, 0, st>>>((float*)P->buf[k].p, d.cval);
+        check_launch(P, at);
+        return;
+    }
+    FusedProg g{};
+    std::vector<size_t> inlined;
+    const bool fits = emit_expr(P, d, g, 0, inlined, st);
+    GBuf& out = P->buf[k];
+    if (fits && !inlined.empty()) {
+        for (size_t n : inlined) P->def[n].on = false;
+        P->fused += inlined.size();
+        ensure(out, (size_t)d.total, d.dt);
+        if (d.total) { gen_fused<<<grid_for(d.total), 256, 0, st>>>(g, out.p, d.dt, d.total); check_launch(P, at); }
+        return;
+    }
+    // nothing to take in (or no room, which two operands cannot cause): the node's own kernel; its operands are vectors by now
+    materialise(P, d.ia, st);
+    if (d.kind == F_BINARY) materialise(P, d.ib, st);
+    const GBuf& a = P->buf[d.ia];
+    ensure(out, (size_t)d.total, d.dt);
+    if (!d.total) return;
+    if (d.kind == F_UNARY) gen_unary<<<grid_for(d.total), 256, 0, st>>>(d.op, a.dt, a.p, out.p, d.va);
+    else if (d.kind == F_BINARY) gen_binary<<<grid_for(d.total), 256, 0, st>>>(d.op, a.dt, P->buf[d.ib].dt, a.p, P->buf[d.ib].p, out.p, d.va, d.vb, P->status);
+    else gen_cast<<<grid_for(d.total), 256, 0, st>>>(a.dt, d.dt, a.p, out.p, d.total);
+    check_launch(P, at);
+}
+
 void run_node(lum_generic_plan* P, size_t k, const std::map<char, int64_t>& dyn, cudaStream_t st) {
     const Node& nd = P->nodes[k];
     const std::string op = canonical(nd.op);
     GBuf& out = P->buf[k];
     auto in = [&](size_t i) -> const GBuf& {
+        if (i < nd.inputs.size()) materialise(P, nd.inputs[i], st);
         if (i >= nd.inputs.size() || !P->buf[nd.inputs[i]].filled) throw Fail{LUM_E_INVALID, "node " + std::to_string(k) + " (" + nd.op + "): an input has no data"};
         return P->buf[nd.inputs[i]];
+    };
+    // element type and length of an operand, whether it is a vector already or a deferred node
+    struct Peek { int dt; size_t n; };
+    auto peek = [&](size_t i) -> Peek {
+        if (i >= nd.inputs.size()) throw Fail{LUM_E_INVALID, "node " + std::to_string(k) + " (" + nd.op + "): an input is missing"};
+        const size_t n = nd.inputs[i];
+        if (P->def[n].on) return Peek{P->def[n].dt, (size_t)P->def[n].total};
+        if (!P->buf[n].filled) throw Fail{LUM_E_INVALID, "node " + std::to_string(k) + " (" + nd.op + "): an input has no data"};
+        return Peek{P->buf[n].dt, P->buf[n].n};
+    };
+    // a float element-wise node: left to its only consumer if that is one too, else launched (taking in what was left to it)
+    auto elementwise = [&](const GDeferred& d) {
+        bool defer = P->fuse && P->n_consumers[k] == 1;
+        if (defer) {
+            defer = false;
+            for (size_t c = k + 1; c < P->nodes.size() && !defer; c++)
+                for (size_t in_c : P->nodes[c].inputs)
+                    if (in_c == k) { defer = fusable_kind(P->nodes[c]); break; }
+        }
+        if (defer) { P->def[k] = d; P->def[k].on = true; P->buf[k].filled = false; }
+        else launch_expr(P, k, d, st);
     };
     auto need = [&](size_t n_params) { if (nd.p.size() < n_params) throw Fail{LUM_E_INVALID, "node " + std::to_string(k) + " (" + nd.op + "): too few parameters"}; };
     const std::string at = "node " + std::to_string(k) + " (" + nd.op + ")";
     if (op == "Input" || op == "Output") return;
     if (op == "Constant") {
         need(1);
-        ensure(out, 1, LUM_F32);
-        gen_fill_f32<<<1, 1, 0, st>>>((float*)out.p, (float)nd.p[0].f);
+        GDeferred d{};
+        d.kind = F_CONST; d.dt = LUM_F32; d.total = 1; d.cval = (float)nd.p[0].f;
+        elementwise(d);
+        return;
     } else if (op == "Iota") {
         need(2);
         const int64_t len = ev(nd.p[1].e, dyn);
@@ -360,21 +557,42 @@ void run_node(lum_generic_plan* P, size_t k, const std::map<char, int64_t>& dyn,
         if (len) gen_iota<<<grid_for(len), 256, 0, st>>>(t, (int32_t*)out.p, len, P->status);
     } else if (op == "Cast") {
         need(3);
-        const GBuf& a = in(0);
         const uint32_t to = nd.p[2].dt;
         if (to > LUM_BOOL) throw Fail{LUM_E_UNSUPPORTED, at + ": target type not supported"};
+        const Peek pa = peek(0);
+        if (is_float_dt((int)to) && is_float_dt(pa.dt)) {
+            GDeferred d{};
+            d.kind = F_CAST; d.dt = (int)to; d.total = (long long)pa.n; d.va = flat_view((long long)pa.n); d.ia = nd.inputs[0];
+            elementwise(d);
+            return;
+        }
+        const GBuf& a = in(0);
         ensure(out, a.n, (int)to);
         if (a.n) gen_cast<<<grid_for((long long)a.n), 256, 0, st>>>(a.dt, (int)to, a.p, out.p, (long long)a.n);
     } else if (op == "Exp2" || op == "Log2" || op == "Sin" || op == "Recip" || op == "Sqrt") {
         need(3);
-        const GBuf& a = in(0);
-        if (a.dt == LUM_INT || a.dt == LUM_BOOL) throw Fail{LUM_E_INVALID, at + ": not implemented for Int / Bool"};
-        const GView v = make_view(nd.p[0].el, nd.p[2].el, dyn, a.n, at.c_str());
-        ensure(out, (size_t)v.total, a.dt);
-        const int u = op == "Exp2" ? U_EXP2 : op == "Log2" ? U_LOG2 : op == "Sin" ? U_SIN : op == "Recip" ? U_RECIP : U_SQRT;
-        if (v.total) gen_unary<<<grid_for(v.total), 256, 0, st>>>(u, a.dt, a.p, out.p, v);
+        const Peek pa = peek(0);
+        if (pa.dt == LUM_INT || pa.dt == LUM_BOOL) throw Fail{LUM_E_INVALID, at + ": not implemented for Int / Bool"};
+        GDeferred d{};
+        d.kind = F_UNARY; d.dt = pa.dt; d.ia = nd.inputs[0];
+        d.op = op == "Exp2" ? U_EXP2 : op == "Log2" ? U_LOG2 : op == "Sin" ? U_SIN : op == "Recip" ? U_RECIP : U_SQRT;
+        d.va = make_view(nd.p[0].el, nd.p[2].el, dyn, pa.n, at.c_str());
+        d.total = d.va.total;
+        elementwise(d);
+        return;
     } else if (op == "Add" || op == "Mul" || op == "Mod" || op == "LessThan") {
         need(5);
+        const Peek pa = peek(0), pb = peek(1);
+        if (op != "LessThan" && is_float_dt(pa.dt)) {
+            GDeferred d{};
+            d.kind = F_BINARY; d.dt = pa.dt; d.ia = nd.inputs[0]; d.ib = nd.inputs[1];
+            d.op = op == "Add" ? B_ADD : op == "Mul" ? B_MUL : B_MOD;
+            d.va = make_view(nd.p[0].el, nd.p[2].el, dyn, pa.n, at.c_str());
+            d.vb = make_view(nd.p[0].el, nd.p[4].el, dyn, pb.n, at.c_str());
+            d.total = d.va.total;
+            elementwise(d);
+            return;
+        }
         const GBuf &a = in(0), &b = in(1);
         const GView va = make_view(nd.p[0].el, nd.p[2].el, dyn, a.n, at.c_str());
         const GView vb = make_view(nd.p[0].el, nd.p[4].el, dyn, b.n, at.c_str());
@@ -448,6 +666,14 @@ int lum_generic_make(const uint8_t* blob, size_t size, lum_generic_plan** out, s
         lum_generic_plan* P = new lum_generic_plan();
         P->nodes = parse(blob, size);
         P->buf.resize(P->nodes.size());
+        P->def.resize(P->nodes.size());
+        P->n_consumers.assign(P->nodes.size(), 0);
+        for (const Node& n : P->nodes)
+            for (size_t i : n.inputs) {
+                if (i >= P->nodes.size()) { delete P; *err = "a node names an input that does not exist"; return LUM_E_INVALID; }
+                P->n_consumers[i]++;
+            }
+        if (const char* e = getenv("LUM_GENERIC_FUSE")) P->fuse = atoi(e) != 0;
         if (cudaMalloc((void**)&P->status, 4) != cudaSuccess || cudaMemset(P->status, 0, 4) != cudaSuccess) { delete P; *err = "out of device memory"; return LUM_E_NOMEM; }
         *out = P;
         return 0;
@@ -492,6 +718,7 @@ int lum_generic_alloc_input(lum_generic_plan* P, int64_t hlir, size_t n, cudaStr
 }
 
 void lum_generic_clear(lum_generic_plan* P) {
+    for (GDeferred& d : P->def) d.on = false;
     for (size_t k = 0; k < P->nodes.size(); k++) {
         GBuf& b = P->buf[k];
         if (P->nodes[k].op == "Input") continue;
@@ -502,7 +729,9 @@ void lum_generic_clear(lum_generic_plan* P) {
 
 int lum_generic_execute(lum_generic_plan* P, const std::map<char, int64_t>& dyn, cudaStream_t st, std::string* err) {
     try {
+        for (GDeferred& d : P->def) d.on = false;
         for (size_t k = 0; k < P->nodes.size(); k++) run_node(P, k, dyn, st);
+        for (size_t k = 0; k < P->nodes.size(); k++) materialise(P, k, st);        // (a node left to a consumer is always taken by it; belt and braces)
     } catch (const Fail& f) {
         cudaStreamSynchronize(st);
         *err = f.msg;
@@ -532,6 +761,7 @@ int lum_generic_output(lum_generic_plan* P, int64_t hlir, uint32_t* dtype, size_
 }
 
 size_t lum_generic_launches(const lum_generic_plan* P) { return P->launches; }
+size_t lum_generic_fused(const lum_generic_plan* P) { return P->fused; }
 size_t lum_generic_nodes(const lum_generic_plan* P) { return P->nodes.size(); }
 
 // f32 view of any result (for lum_get_output): converts on the device into `dst`

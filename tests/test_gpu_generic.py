@@ -419,4 +419,67 @@ def test_search_surface_on_a_primitive_graph(pkg, rt, L):
     with pytest.raises(pkg.LumError):
         rt.get_output(2)
     st = rt.stats()
-    assert st.kernel_launches >= 6
+    assert st.kernel_launches >= 2          # two executes; the three element-wise nodes of each run as one kernel
+
+
+@pytest.mark.parametrize("dt", [F32, F16, BF16])
+def test_fused_chains_equal_unfused_and_launch_fewer_kernels(pkg, L, dt):
+    """Chains of float element-wise nodes are computed inside their consumer's kernel: same bits as one kernel per node (also
+    for half types, which are rounded after every node either way), fewer launches.  A long chain is cut where the evaluator's
+    program is full; an edge read through a broadcast view, a reduction or an integer node ends a chain."""
+    import os
+    rng = np.random.default_rng(31 + dt)
+    n, rows = 4096, 4
+
+    def enc(x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        return x if dt == F32 else x.astype(np.float16).view(np.uint16) if dt == F16 else bf16_bits(x)
+
+    b = L.LLIRBuilder()
+    gn = b.input(0, "g", dt)
+    un = b.input(1, "u", dt)
+    # swish(g) * u: seven element-wise nodes in a row -> one kernel
+    sc = b.binary("Mul", [n], b.binary("Mul", [n], gn, [1], b.constant(-1.0), [0]), [1], b.constant(1.0 / np.log(2.0)), [0])
+    sig = b.unary("Recip", [n], b.binary("Add", [n], b.unary("Exp2", [n], sc, [1]), [1], b.constant(1.0), [0]), [1])
+    sw = b.binary("Mul", [n], b.binary("Mul", [n], gn, [1], sig, [1]), [1], un, [1])
+    b.output(sw, 10)
+    # a chain longer than the evaluator's program: 40 x (+c), then a square root of the square
+    t = un
+    for i in range(40):
+        t = b.binary("Add", [n], t, [1], b.constant(0.03125 * (i % 5 - 2)), [0])
+    b.output(b.unary("Sqrt", [n], b.binary("Mul", [n], t, [1], t, [1]), [1]), 11)        # t has two readers here: it stays a vector
+    # row sums of an element-wise product, scaled by a broadcast reciprocal, cast to f32 and back into a product
+    g2 = b.binary("Mul", [rows, n // rows], gn, [n // rows, 1], un, [n // rows, 1])
+    ss = b.reduce("Sum", [rows], n // rows, g2, [n // rows], 1)
+    rc = b.unary("Recip", [rows], b.binary("Add", [rows], ss, [1], b.constant(3.0), [0]), [1])
+    sc2 = b.binary("Mul", [rows, n // rows], g2, [n // rows, 1], rc, [1, 0])             # g2 read again (two readers), rc broadcast
+    b.output(b.binary("Mul", [n], b.cast(b.cast(sc2, n, F32), n, dt), [1], un, [1]), 12)
+    blob = b.blob()
+    g = enc(rng.normal(0, 2, n)); u = enc(rng.normal(0, 1, n))
+    got = {}
+    for fuse in ("0", "1"):
+        os.environ["LUM_GENERIC_FUSE"] = fuse
+        try:
+            rt = pkg.B200Runtime.initialize(device=0)
+            try:
+                rt.load_llir(blob)
+                rt.set_input(0, g, DT_NAME[dt]); rt.set_input(1, u, DT_NAME[dt])
+                before = rt.stats().kernel_launches
+                rt.execute()
+                raws = [rt.get_output_raw(o)[1].copy() for o in (10, 11, 12)]
+                got[fuse] = (raws, rt.stats().kernel_launches - before)
+            finally:
+                rt.close()
+        finally:
+            del os.environ["LUM_GENERIC_FUSE"]
+    for a, c in zip(got["0"][0], got["1"][0]):
+        assert a.dtype == c.dtype and np.array_equal(a.view(np.uint8), c.view(np.uint8))
+    assert got["1"][1] < got["0"][1] / 2, (got["0"][1], got["1"][1])
+    # and against the interpreter, like every other graph here
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        r = run_both(rt, blob, {0: (g, dt), 1: (u, dt)}, [11, 12])
+        for o in (11, 12):
+            assert same(r[o][0], r[o][1]), o
+    finally:
+        rt.close()
