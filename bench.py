@@ -274,6 +274,48 @@ def gemm_shapes(pkg, torch, shapes=None):
     return {"kernel": "rows_quantize + q8_gemm_tc", "shapes": out}
 
 
+def sampler_times(pkg, torch):
+    """The temperature / top-k / top-p sampler alone (lum_op_sample_topk) on rows of random logits of the two vocabularies, and what
+    it costs inside the decode loop: the 2-layer cut of the Llama-3-8B shape with the full vocabulary, greedy against sampled."""
+    import ctypes as C
+    lib = pkg.load_library()
+    out = {"kernel": "sample_rows", "alone": []}
+    s = pkg.Sampling(temperature=0.8, top_p=0.95, top_k=50, reserved=0, seed=1)
+    for rows, vocab in ((1, 128256), (32, 128256), (1, 201088)):
+        logits = torch.randn(rows, vocab, device="cuda") * 3.0
+        pos = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        tok = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        best = None
+        for _ in range(6):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); e0.record()
+            assert lib.lum_op_sample_topk(logits.data_ptr(), rows, vocab, C.byref(s), 0, pos.data_ptr(), tok.data_ptr(), None) == 0
+            e1.record(); torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3
+            best = us if best is None else min(best, us)
+        out["alone"].append({"rows": rows, "vocab": vocab, "us": best, "row_bytes": vocab * 4})
+    desc = pkg.CONFIGS["llama3_8b_q8_2layer"].copy(vocab=128256, max_seq=1024, max_new_tokens=512)
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc); rt.synth(SEED)
+        ext = torch.cuda.ExternalStream(rt.stream())
+        res = {}
+        for name, temp in (("greedy", 0.0), ("sampled", 0.8)):
+            rt.set_sampling(temp, 50, 0.95, 1)
+            rt.generate([1, 2, 3, 4, 5, 6, 7, 8], 64)            # warm-up, captures the graph
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ext)
+            rt.decode_greedy(256)
+            e1.record(ext)
+            rt.synchronize()
+            res[name] = e0.elapsed_time(e1) * 1e3 / 256
+        out["decode_step_us_2layer_full_vocab"] = res
+        out["sampler_cost_per_token_us"] = res["sampled"] - res["greedy"]
+    finally:
+        rt.close()
+    return out
+
+
 def prompt_two_layers(pkg, torch, n=4096):
     """A 4096-token prompt through a 2-layer cut of the Llama-3-8B shape (vocabulary 4096): the same kernels and shapes as the
     full model's prompt pass, a few hundred MB on the device — the case the profiler captures of the prompt kernels use."""
@@ -796,10 +838,11 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama3_8b_q8", "qwen3_4b_q8", "llama3_8b_q8_bs32", "llama3_8b_q8_prefill4096", "gpt_oss_20b_q8"],
                     help="llama3_8b_q8: the configuration the metric is quoted on (default); qwen3_4b_q8: the Qwen3-4B shape; "
                          "llama3_8b_q8_bs32 / llama3_8b_q8_prefill4096: the same model in the tensor-core regime (batched decode / one long prompt)")
-    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor", "gemm", "gemm512", "gemm32", "prompt2"],
+    ap.add_argument("--only", default="all", choices=["all", "kernel", "sweep", "floor", "gemm", "gemm512", "gemm32", "prompt2", "sampler"],
                     help="kernel: time only the dominant kernel alone (small, for ncu captures); sweep: the kernel alone over a range of row counts; "
                          "floor: the decode step with all projections shrunk away; gemm: the tensor-core GEMM alone on the layer's shapes "
-                         "(gemm512 / gemm32: the gate+up shape only, 512 / 32 rows, for ncu captures); prompt2: a 4096-token prompt through a 2-layer cut")
+                         "(gemm512 / gemm32: the gate+up shape only, 512 / 32 rows, for ncu captures); prompt2: a 4096-token prompt through a 2-layer cut; "
+                         "sampler: the top-k / top-p sampler alone and its cost inside the decode loop")
     args = ap.parse_args()
     from __graft_entry__ import load_package
     pkg = load_package()
@@ -840,6 +883,11 @@ def main():
         import torch
         torch.cuda.set_device(0)
         print(json.dumps({"prompt_two_layers": prompt_two_layers(pkg, torch)}))
+        return
+    if args.only == "sampler":
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps({"sampler": sampler_times(pkg, torch)}))
         return
     if args.only == "floor":
         import torch

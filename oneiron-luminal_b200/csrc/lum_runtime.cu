@@ -1567,6 +1567,10 @@ int32_t lum_set_sampling(lum_rt* rt, const lum_sampling* s) {
             return fail(rt, LUM_E_UNSUPPORTED, "set_sampling: the persistent-kernel executor only has the greedy sample");
         p.temperature = s->temperature; p.top_k = s->top_k == 0 ? kSampleMaxK : s->top_k; p.top_p = s->top_p == 0.0f ? 1.0f : s->top_p; p.seed = s->seed;
     }
+    if (on) {
+        CU(rt, cudaSetDevice(rt->cfg.device));
+        CU(rt, sample_rows_prepare());
+    }
     if (rt->has_model) {
         CU(rt, cudaSetDevice(rt->cfg.device));
         CU(rt, cudaStreamSynchronize(rt->stream));
@@ -2379,6 +2383,7 @@ int32_t lum_op_sample_topk(const float* logits_dev, int32_t n_rows, int32_t voca
     static SampleParams* g_params[64] = {};     // one slot per device; the call copies its parameters in on the caller's stream
     if (!g_params[dev]) {
         cudaError_t e = cudaMalloc((void**)&g_params[dev], sizeof(SampleParams));
+        if (e == cudaSuccess) e = sample_rows_prepare();
         if (e != cudaSuccess) return op_fail("sample_topk", e);
     }
     SampleParams p{s->temperature, s->top_p == 0.0f ? 1.0f : s->top_p, s->top_k == 0 ? kSampleMaxK : s->top_k, 0, s->seed};

@@ -31,6 +31,7 @@ struct SampleArgs {
     int* row_tok; int* row_pos; int* log; const int* step; int max_steps;
 };
 
+cudaError_t sample_rows_prepare();      // once per device before the first launch, outside stream capture
 cudaError_t launch_sample_rows(const SampleArgs& a, cudaStream_t st);
 
 }  // namespace lum
