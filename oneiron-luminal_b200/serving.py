@@ -5,7 +5,9 @@ The reference's example loop serves one sequence: prompt, then one ``execute`` p
 free cache slot (its prompt runs as rows on the tensor cores), all live slots then advance together — one row per sequence
 and step, samples fed back on the device — and a request that ends (token budget or an end-of-sequence id) frees its slot for
 the next one in the queue between two groups of steps.  Prompt prefixes computed once can be parked in a slot and copied into
-a new request's slot on the device instead of being recomputed.
+a new request's slot on the device instead of being recomputed.  With a paged cache the loop admits a request only when
+the pool can hold its whole life (prompt and every token it may generate) next to what is already promised, and gives a
+finished request's pages back.
 
 Everything here is host-side bookkeeping over four calls of the runtime: ``seq_select`` + ``execute`` (admission),
 ``kv_copy`` (prefix reuse), ``batch_begin_slots`` + ``batch_decode`` (the steps).  The runtime object only needs those methods
@@ -31,6 +33,7 @@ class Request:
     pos: int = 0                                      # rows of this sequence in its cache slot
     done: bool = False
     reused_rows: int = 0                              # prompt rows taken from a parked prefix instead of being computed
+    pages: int = 0                                    # paged cache: pages set aside for this request's whole life
 
     @property
     def cur(self) -> int:
@@ -51,6 +54,16 @@ class ContinuousBatcher:
         self.finished: Dict[int, Request] = {}
         self.prefixes: List[Tuple[Tuple[int, ...], int]] = []            # (tokens, slot), longest first
         self._next_id = 0
+        # Paged cache: a request is admitted only when the pool can hold its prompt AND every token it may still generate, next to
+        # what the live requests and the parked prefixes were promised — so no step ever finds the pool empty.  (Pages a request
+        # shares with a parked prefix are counted for the request too: it may write into them, which gives it copies of its own.)
+        pool = getattr(rt, "kv_pool", None)
+        self.page_rows = 0
+        self.pool_pages = 0
+        if pool is not None:
+            total, _free, rows = pool()
+            self.page_rows, self.pool_pages = rows, total
+        self.promised = 0           # pages promised to live requests and parked prefixes
         self.rounds = 0
         self.steps_run = 0          # batched steps issued
         self.rows_run = 0           # rows those steps carried (sum of live sequences per step)
@@ -64,10 +77,15 @@ class ContinuousBatcher:
             raise ValueError("max_new must be at least 1")
         if len(prompt) + max_new > self.rt.desc.max_seq:
             raise ValueError(f"prompt of {len(prompt)} tokens + {max_new} new ones pass the cache capacity {self.rt.desc.max_seq}")
+        if self.page_rows and self._pages_for(len(prompt) + max_new) > self.pool_pages:
+            raise ValueError(f"{len(prompt) + max_new} rows need more pages than the pool has ({self.pool_pages} of {self.page_rows} rows)")
         r = Request(self._next_id, prompt, max_new, set(int(e) for e in (eos or ())))
         self._next_id += 1
         self.queue.append(r)
         return r.rid
+
+    def _pages_for(self, rows: int) -> int:
+        return -(-rows // self.page_rows) if self.page_rows else 0
 
     def park_prefix(self, tokens: Sequence[int]) -> int:
         """Compute a prompt prefix once into a slot of its own; later requests that start with it copy its rows on the device.
@@ -77,6 +95,9 @@ class ContinuousBatcher:
             raise ValueError("empty prefix")
         if len(self.free) < 2:
             raise RuntimeError("parking a prefix would leave no slot for requests")
+        if self.page_rows and self.promised + self._pages_for(len(tokens)) > self.pool_pages:
+            raise RuntimeError("the page pool cannot hold this prefix next to what is already promised")
+        self.promised += self._pages_for(len(tokens))
         slot = self.free.pop()
         self.rt.seq_select(slot)
         self.rt.set_data(list(tokens))
@@ -100,6 +121,8 @@ class ContinuousBatcher:
         rt.execute({"s": len(r.prompt) - start, "p": start})
         r.tokens = [int(rt.get_token())]
         r.slot, r.pos, r.reused_rows = slot, len(r.prompt), start
+        r.pages = self._pages_for(len(r.prompt) + r.max_new)
+        self.promised += r.pages
         self.live[slot] = r
         self._check_done(r)
 
@@ -108,6 +131,7 @@ class ContinuousBatcher:
             return
         if len(r.tokens) >= r.max_new or (r.tokens and r.tokens[-1] in r.eos):
             r.done = True
+            self.promised -= r.pages
             del self.live[r.slot]
             release = getattr(self.rt, "kv_release", None)
             if release is not None:
@@ -119,6 +143,9 @@ class ContinuousBatcher:
         """Admit what fits, run one group of steps for every live sequence, retire what ended.  Returns the requests that ended."""
         before = set(self.finished)
         while self.queue and self.free:
+            nxt = self.queue[0]
+            if self.page_rows and self.promised + self._pages_for(len(nxt.prompt) + nxt.max_new) > self.pool_pages:
+                break                                    # first come, first served: it waits for pages, nobody overtakes it
             self._admit(self.queue.popleft(), self.free.pop())
         if self.live:
             slots = sorted(self.live)

@@ -89,6 +89,59 @@ class FakeRuntime:
         return out
 
 
+class FakePagedRuntime(FakeRuntime):
+    """The stand-in with a page pool: rows written cost pages, a release gives them back, running out raises."""
+
+    def __init__(self, pool_pages, page_rows=8, **kw):
+        super().__init__(**kw)
+        self.pool_pages, self.page_rows = pool_pages, page_rows
+        self.low_water = pool_pages
+
+    def _used(self):
+        return sum(-(-sum(r is not None for r in c) // self.page_rows) for c in self.cache)
+
+    def _check(self):
+        free = self.pool_pages - self._used()
+        assert free >= 0, "the pool ran out: a request was admitted that it could not hold"
+        self.low_water = min(self.low_water, free)
+
+    def kv_pool(self):
+        return self.pool_pages, self.pool_pages - self._used(), self.page_rows
+
+    def kv_release(self, slot):
+        self.cache[slot] = [None] * self.desc.max_seq
+        self.calls.append(("release", slot))
+
+    def execute(self, dims):
+        super().execute(dims)
+        self._check()
+
+    def batch_decode(self, n):
+        super().batch_decode(n)
+        self._check()
+
+
+def test_admission_waits_for_pages_and_the_pool_never_runs_out():
+    sv = _serving()
+    # 4 slots of up to 64 rows = 32 pages at full length; the pool has 10
+    rt = FakePagedRuntime(pool_pages=10, page_rows=8, max_batch=4, max_seq=64, max_new_tokens=16)
+    b = sv.ContinuousBatcher(rt, steps_per_round=3)
+    rng = np.random.default_rng(5)
+    reqs = [([int(t) for t in rng.integers(0, FakeRuntime.VOCAB, int(rng.integers(1, 30)))], int(rng.integers(1, 30))) for _ in range(25)]
+    ids = [b.submit(p, n) for p, n in reqs]
+    out = b.run()
+    for rid, (p, n) in zip(ids, reqs):
+        assert out[rid] == rt.alone(p, n), rid
+    assert b.promised == 0 and rt.kv_pool()[1] == 10        # everything was given back
+    assert rt.low_water < 10                                # and the pool was really used
+    assert sum(1 for c in rt.calls if c[0] == "release") == 25
+    with pytest.raises(ValueError):
+        b.submit([1] * 60, 30)                              # could never fit: 90 rows pass the cache ... 
+    big = sv.ContinuousBatcher(FakePagedRuntime(pool_pages=3, page_rows=8, max_batch=2, max_seq=64), steps_per_round=2)
+    with pytest.raises(ValueError):
+        big.submit([1] * 20, 10)                            # 30 rows = 4 pages, the pool has 3
+
+
 def _requests(n, seed=0):
     rng = np.random.default_rng(seed)
     return [([int(t) for t in rng.integers(0, FakeRuntime.VOCAB, int(rng.integers(1, 20)))], int(rng.integers(1, 24))) for _ in range(n)]
