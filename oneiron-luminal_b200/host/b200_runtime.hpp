@@ -145,6 +145,7 @@ public:
     lum_stats stats() const { lum_stats s; lum_get_stats(h_, &s); return s; }
 
     lum_rt* raw() const { return h_; }
+    const lum_model_desc& desc() const { return desc_; }
 
 private:
     void ck(int rc) { if (rc) throw Error(rc, lum_last_error(h_)); }

@@ -2,6 +2,7 @@
 //
 //   drive abi  <graph blob> <out.safetensors>      no GPU: header-only host compiles and links; host-only entries work
 //   drive decode <desc bytes> <seed> <n new> <prompt ids...>    on a GPU: prints the greedy tokens, one line
+//   drive serve <desc bytes> <seed> <len:max_new>...             on a GPU: the continuous-batching loop, one line of tokens per request
 //   drive graph  <graph blob> <n>                  on a GPU: runs a primitive graph with Input 0 = 0..n-1, prints Output 2
 //
 // <desc bytes> is a file holding the bytes of a lum_model_desc as the Python mirror lays it out: decoding the same tokens
@@ -13,6 +14,7 @@
 #include <iterator>
 
 #include "../../oneiron-luminal_b200/host/b200_runtime.hpp"
+#include "../../oneiron-luminal_b200/host/serving.hpp"
 
 static std::vector<uint8_t> slurp(const char* path) {
     std::ifstream f(path, std::ios::binary);
@@ -83,6 +85,35 @@ int main(int argc, char** argv) {
             printf("logits %zu launches_per_step %d\n", logits.size(), rt.stats().launches_per_step);
             // errors surface as exceptions and leave the runtime usable
             try { rt.set_dim('q', 1); printf("no exception\n"); } catch (const lum::Error& e) { printf("caught %d\n", e.code); }
+            return 0;
+        }
+        if (mode == "serve" && argc >= 4) {
+            // the C++ continuous-batching loop over the real runtime: requests "len:max_new" with seeded prompts; one line per request
+            const std::vector<uint8_t> raw = slurp(argv[2]);
+            if (raw.size() != sizeof(lum_model_desc)) { fprintf(stderr, "desc file holds %zu bytes, lum_model_desc has %zu\n", raw.size(), sizeof(lum_model_desc)); return 3; }
+            lum_model_desc d;
+            memcpy(&d, raw.data(), sizeof d);
+            const uint64_t seed = strtoull(argv[3], nullptr, 10);
+            lum::B200Runtime rt = lum::B200Runtime::initialize(0);
+            rt.load_model(d);
+            rt.synth(seed);
+            lum::ContinuousBatcher<lum::B200Runtime> b(rt, 4);
+            std::vector<int> ids;
+            for (int i = 4; i < argc; i++) {
+                int len = 0, max_new = 0;
+                if (sscanf(argv[i], "%d:%d", &len, &max_new) != 2) return 2;
+                std::vector<int32_t> p((size_t)len);
+                for (int k = 0; k < len; k++) p[(size_t)k] = (int32_t)((11 * k + 5 * (i - 4) + 1) % d.vocab);
+                ids.push_back(b.submit(p, max_new));
+            }
+            const auto out = b.run();
+            for (int id : ids) {
+                printf("request %d:", id);
+                for (int32_t t : out.at(id)) printf(" %d", t);
+                printf("\n");
+            }
+            const auto pool = rt.kv_pool();
+            printf("pool %d %d %d rows_per_step %.2f\n", pool.pages_total, pool.pages_free, pool.page_rows, (double)b.rows_run / (double)b.steps_run);
             return 0;
         }
         if (mode == "graph" && argc >= 4) {

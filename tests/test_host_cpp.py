@@ -70,3 +70,35 @@ def test_cpp_host_runs_a_primitive_graph(pkg, drive, tmp_path):
     r = subprocess.run([drive, "graph", str(g), str(n)], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.split() == ["out"] + [str(i) for i in range(n)]
+
+
+def test_cpp_serving_loop_on_a_stand_in_runtime(tmp_path):
+    """oneiron-luminal_b200/host/serving.hpp (the continuous-batching loop in C++) against a stand-in runtime: results equal
+    each request alone, end-of-sequence ids, parked prefixes, page-aware admission, refusals."""
+    out = str(tmp_path / "serving_test")
+    r = subprocess.run(["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror", os.path.join(ROOT, "tests", "host_cpp", "serving_test.cpp"), "-o", out],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([out], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip() == "ok 5", r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_cpp_serving_loop_equals_requests_alone(pkg, drive, tmp_path):
+    """The C++ loop over the real runtime with a paged cache: five requests through three slots get the tokens they get alone."""
+    desc = pkg.CONFIGS["llama3_8b_q8_2layer"].copy(max_batch=3, max_seq=256, max_new_tokens=64, kv_page_rows=64, kv_pool_pages=7)
+    spec = [(5, 9), (70, 30), (40, 13), (9, 1), (100, 20)]
+    solo = pkg.B200Runtime.initialize(device=0)
+    try:
+        solo.load_model(desc.copy(max_batch=1, kv_page_rows=0, kv_pool_pages=0)); solo.synth(77)
+        alone = [solo.generate([(11 * k + 5 * i + 1) % desc.vocab for k in range(n)], m) for i, (n, m) in enumerate(spec)]
+    finally:
+        solo.close()
+    d = tmp_path / "desc.bin"
+    d.write_bytes(bytes(desc))
+    r = subprocess.run([drive, "serve", str(d), "77"] + [f"{n}:{m}" for n, m in spec], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = r.stdout.splitlines()
+    for i, want in enumerate(alone):
+        assert lines[i] == f"request {i}: " + " ".join(str(t) for t in want), i
+    assert lines[len(spec)].startswith("pool 7 7 64 rows_per_step ")
