@@ -242,9 +242,11 @@ int32_t lum_get_logits(lum_rt* rt, float* host_out, size_t n);
 /* The greedy sample of the last executed row — `sample()` of main.rs:137-148 (last maximum wins). */
 int32_t lum_get_token(lum_rt* rt, int32_t* token);
 
-/* Device-resident greedy loop: feeds each sampled token back as the next input, `n_steps` times,
+/* Device-resident loop: feeds each sampled token back as the next input, `n_steps` times,
  * starting from the token/position state the last lum_execute (or lum_decode_greedy) left.
- * No host transfer or synchronisation happens inside.  Tokens accumulate in a device log. */
+ * No host transfer or synchronisation happens inside.  Tokens accumulate in a device log.
+ * The sample is the greedy one unless lum_set_sampling has set a sampler (the name is from
+ * before that entry existed). */
 int32_t lum_decode_greedy(lum_rt* rt, int32_t n_steps);
 /* Copy the first `n` tokens of the log written since the last lum_decode_reset. Synchronises. */
 int32_t lum_get_decoded(lum_rt* rt, int32_t* host_out, size_t n);
@@ -279,9 +281,9 @@ int32_t lum_set_sampling(lum_rt* rt, const lum_sampling* s);
  *   lum_seq_select(seq)        which sequence lum_execute / lum_decode_greedy / lum_kv_* address (default 0);
  *   lum_batch_begin(n, t, p)   the current token and position (= rows already cached) of sequences 0 .. n-1, typically what
  *                              each one's prompt ended with; resets the batch log;
- *   lum_batch_decode(steps)    `steps` greedy tokens for every sequence: one row per sequence and step through the
- *                              tensor-core products, attention of each row over its own cache, a greedy sample per row,
- *                              fed back on the device;
+ *   lum_batch_decode(steps)    `steps` tokens for every sequence: one row per sequence and step through the
+ *                              tensor-core products, attention of each row over its own cache, a sample per row (greedy,
+ *                              or the sampler of lum_set_sampling), fed back on the device;
  *   lum_batch_get_decoded      the log, [steps][n] row-major;  lum_batch_get_logits: the last step's logits of one row.
  *   lum_batch_begin_slots      the same as lum_batch_begin for sequences in ANY cache slots: row i of the batch works on cache
  *                              slot slots[i] (distinct, < max_batch).  A serving loop admits a request by filling a free slot
