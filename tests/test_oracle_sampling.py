@@ -69,3 +69,52 @@ def test_frequencies_follow_the_softmax():
     c = np.bincount([oracle.sample_topk(l, 1.0, 3, 1.0, 9, 0, p)[0] for p in range(n)], minlength=3) / n
     p = np.exp(l.astype(np.float64)); p /= p.sum()
     assert np.max(np.abs(c - p)) < 0.01
+
+
+def numpy_draw(l, temperature, top_k, top_p, seed, seq, pos):
+    """A second, independent statement of the definition in numpy (stable sort for the order, float32 running sums)."""
+    v = np.where(np.isnan(l), -np.inf, l).astype(np.float32)
+    k = max(1, min(top_k, 256, v.size))
+    order = np.argsort(-v, kind="stable")[:k]            # value descending; equal values keep index order
+    d = (v[order] - v[order[0]]).astype(np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        w = np.where(np.isnan(d), np.float32(1.0), np.exp((d * np.float32(1.0 / np.float32(temperature))).astype(np.float32))).astype(np.float32)
+    run = np.zeros(k, dtype=np.float32)
+    s = np.float32(0.0)
+    for j in range(k):
+        s = np.float32(s + w[j])
+        run[j] = s
+    keep = k
+    if top_p < 1.0:
+        cut = np.float32(np.float32(top_p) * run[-1])
+        hit = np.flatnonzero(run >= cut)
+        keep = int(hit[0]) + 1 if hit.size else k
+    target = np.float32(np.float32(u_of(seed, seq, pos)) * run[keep - 1])
+    hit = np.flatnonzero(run[:keep] > target)
+    return int(order[int(hit[0]) if hit.size else keep - 1])
+
+
+def test_oracle_equals_an_independent_numpy_statement():
+    rng = np.random.default_rng(12)
+    checked = 0
+    for trial in range(400):
+        v = int(rng.integers(1, 3000))
+        kind = trial % 4
+        if kind == 0:
+            l = (rng.standard_normal(v) * 3).astype(np.float32)
+        elif kind == 1:
+            l = np.round(rng.standard_normal(v) * 2).astype(np.float32)            # many ties
+        elif kind == 2:
+            l = np.where(rng.random(v) < 0.1, np.nan, rng.standard_normal(v)).astype(np.float32)
+        else:
+            l = (rng.standard_normal(v) * 20).astype(np.float32)                     # sharp
+        t = float(rng.choice([0.3, 0.8, 1.0, 2.5]))
+        k = int(rng.choice([1, 2, 8, 50, 256]))
+        p = float(rng.choice([0.2, 0.9, 1.0]))
+        seed, seq, pos = int(rng.integers(0, 2 ** 40)), int(rng.integers(0, 64)), int(rng.integers(0, 4096))
+        tok, margin = oracle.sample_topk(l, t, k, p, seed, seq, pos)
+        if margin < 1e-5:
+            continue                                    # numpy's exp and libm's expf may differ in the last bit
+        assert tok == numpy_draw(l, t, k, p, seed, seq, pos), (trial, v, t, k, p)
+        checked += 1
+    assert checked > 350
