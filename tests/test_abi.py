@@ -33,6 +33,18 @@ def test_header_declares_expected_surface():
     for must in ["lum_create", "lum_destroy", "lum_model_init", "lum_set_dim", "lum_set_tokens", "lum_execute",
                  "lum_get_logits", "lum_profile", "lum_kv_reset", "lum_decode_greedy", "lum_op_gemv_q8_0"]:
         assert must in syms
+    # the boundary a `Runtime` implementation over this library binds (src/op.rs:10-30 and the inherent methods of
+    # crates/luminal_cuda/src/runtime.rs:133-236): graph in, inputs by node id (host data or a caller's device pointer), dynamic
+    # dimensions, the search's dummy inputs / clear / profile of a graph, outputs in f32 or their own type, the sampled token,
+    # cache handling, errors and counters
+    for must in ["lum_load_llir", "lum_llir_describe", "lum_set_input", "lum_set_input_device_ptr", "lum_alloc_dummy_input",
+                 "lum_clear_intermediates", "lum_profile_llir", "lum_get_output", "lum_get_output_raw", "lum_get_token", "lum_kv_read",
+                 "lum_kv_save", "lum_kv_load", "lum_kv_copy", "lum_kv_release", "lum_kv_pool", "lum_last_error", "lum_get_stats",
+                 "lum_load_safetensors", "lum_save_safetensors", "lum_model_set_weight", "lum_model_set_weight_shard",
+                 "lum_seq_select", "lum_batch_begin", "lum_batch_begin_slots", "lum_batch_decode", "lum_batch_get_decoded",
+                 "lum_set_sampling", "lum_op_sample_topk", "lum_op_sample_q8_0_static", "lum_op_status",
+                 "lum_tp_unique_id", "lum_tp_init", "lum_tp_peer_export", "lum_tp_peer_import", "lum_synchronize"]:
+        assert must in syms, must
 
 
 def test_library_exports_every_declared_symbol(lib):
