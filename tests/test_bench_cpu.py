@@ -1,11 +1,11 @@
-"""Host-side checks of bench.py that need no GPU: the CPU arm with the driver's own arguments, the seeded prompt."""
+"""Host-side checks of bench.py that need no GPU: the CPU arm with many steps, the seeded prompt."""
 import json
 
 import numpy as np
 
 
-def test_reference_arm_with_driver_arguments(pkg, monkeypatch, capsys):
-    """`bench.py --impl reference --steps 20 --warmup 5` (the round-end command line) on a small stand-in workload:
+def test_reference_arm_with_many_steps(pkg, monkeypatch, capsys):
+    """`bench.py --impl reference --steps 20 --warmup 5` on a small stand-in workload:
     25 single-token passes must fit the oracle's cache and print one well-formed JSON line."""
     import bench
     monkeypatch.setattr(bench, "WORKLOAD", "small_q8")
