@@ -646,9 +646,19 @@ def run_tensor_core_regime(args, pkg, which: str):
 
 
 def _prefill_parity(pkg, base, ids, rows_token, rows_logits):
-    """The prompt once more, one decode step per token (the path the default workload checks against the oracle's fixture):
-    the logits after the last prompt token and the greedy sample must agree with the rows pass."""
+    """Against the oracle's committed fixture for this very prompt (tests/golden/llama3_8b_q8_prefill4096_full.npz: whole model, 4096
+    rows, the logits after the last prompt token and the greedy sample) when it is there; otherwise the prompt once more, one
+    decode step per token (the path the default workload checks against the oracle's fixture): logits and sample must agree with
+    the rows pass."""
     import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "llama3_8b_q8_prefill4096_full.npz")
+    if os.path.exists(path):
+        fx = np.load(path)
+        if int(fx["seed"]) == SEED and list(fx["prompt"]) == list(ids):
+            ref = fx["prompt_logits"].astype(np.float32)
+            err = float(np.max(np.abs(rows_logits - ref)) / np.max(np.abs(ref)))
+            return {"checked": True, "tokens_equal": bool(int(fx["tokens"][0]) == int(rows_token)), "steps": 1, "logits_rel_err": err,
+                    "logits_tolerance": 1e-2, "min_margin_of_fixture": float(fx["margins"][0]), "fixture": os.path.relpath(path, ROOT)}
     solo = pkg.B200Runtime.initialize(device=0, prefill_min_rows=1 << 30)
     try:
         solo.load_model(base.copy(max_seq=len(ids) + 8))

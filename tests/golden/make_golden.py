@@ -8,6 +8,7 @@ give the GPU tests a fixed target that does not depend on rebuilding the oracle 
     python tests/golden/make_golden.py llama3_8b_q8    # a full-size case (tens of minutes of CPU time, ~12 GB of RAM)
     python tests/golden/make_golden.py qwen3_4b_q8
     python tests/golden/make_golden.py gpt_oss_20b_q8  # ~23 GB of RAM
+    python tests/golden/make_golden.py llama3_8b_q8_prefill4096   # a 4096-token prompt: about three and a half hours on 8 cores
 
 Full-size cases are the configurations the benchmark numbers are quoted on: whole model, whole vocabulary, the
 benchmark's seed and prompt.  They hold the prompt, the first 32 greedy tokens with their top-1/top-2 margins,
@@ -41,6 +42,8 @@ FULL_CASES = {
     "qwen3_4b_q8": ("qwen3_4b_q8", FULL_SEED, 1024, 32),
     # routed experts, sliding-window / full layers alternating, sinks, YaRN: 256 tokens take the window (128) out of reach of the start
     "gpt_oss_20b_q8": ("gpt_oss_20b_q8", FULL_SEED, 256, 32),
+    # the tensor-core prompt workload's own size: 4096 rows in one pass, the sample that follows (hours of CPU time)
+    "llama3_8b_q8_prefill4096": ("llama3_8b_q8", FULL_SEED, 4096, 1),
 }
 
 
@@ -64,7 +67,7 @@ def full_case(pkg, name):
         toks.append(m.argmax(logits))
         margins.append(m.margin(logits))
     rows = p                                             # cache rows written: the prompt and the first n_new - 1 tokens
-    pick = sorted({0, 1, n_prompt // 2 - 1, n_prompt - 1, n_prompt, rows - 1})
+    pick = sorted(i for i in {0, 1, n_prompt // 2 - 1, n_prompt - 1, n_prompt, rows - 1} if i < rows)
     L = d.n_layers
     kv = {}
     for layer in (0, L - 1):

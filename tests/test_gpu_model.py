@@ -381,6 +381,39 @@ def test_full_size_configuration_matches_oracle_fixture(pkg, name):
         rt.close()
 
 
+def test_full_size_4096_token_prompt_matches_oracle_fixture(pkg):
+    """The tensor-core prompt workload at its own size: the whole Llama-3-8B-shape model, a 4096-token prompt in one pass of rows
+    (Q8_0 GEMM and prompt attention on the tensor cores), against the oracle's committed outputs: the sample that follows the
+    prompt, its logits within 1e-2, K/V rows of the first and last layer."""
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama3_8b_q8_prefill4096_full.npz")
+    if not os.path.exists(path):
+        pytest.skip(f"no fixture {path}")
+    fx = np.load(path)
+    prompt = [int(t) for t in fx["prompt"]]
+    desc = pkg.CONFIGS["llama3_8b_q8"].copy(max_seq=len(prompt) + 8)
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc)
+        rt.synth(int(fx["seed"]))
+        rt.set_data(prompt); rt.execute({"s": len(prompt), "p": 0})
+        tok, logits = rt.get_token(), rt.get_f32()
+        ref = fx["prompt_logits"]
+        err = float(np.max(np.abs(logits - ref)) / np.max(np.abs(ref)))
+        assert tok == int(fx["tokens"][0]), (tok, int(fx["tokens"][0]), float(fx["margins"][0]))
+        assert err <= 1e-2, err
+        rows = [int(r) for r in fx["cache_rows"]]
+        for layer in (0, desc.n_layers - 1):
+            for kind in ("k", "v"):
+                have = rt.kv_read(layer, kind, max(rows) + 1)[rows]
+                want = fx[f"{kind}_cache_layer{layer}"]
+                rms = float(np.sqrt(np.mean((have - want) ** 2)) / np.sqrt(np.mean(want ** 2)))
+                assert rms <= (1e-3 if layer == 0 else 1e-2), (layer, kind, rms)
+        print(f"4096-token prompt: sample equal; logits rel err {err:.2e}; margin {float(fx['margins'][0]):.2e}")
+    finally:
+        rt.close()
+
+
 # ------------------------------------------------------------------------------------------------- prompts as rows (M > 1)
 @pytest.mark.parametrize("name,n_prompt", [("small_q8", 4), ("small_q8", 33), ("small_q8", 100), ("llama3_8b_q8_2layer", 2), ("llama3_8b_q8_2layer", 32),
                                            ("llama3_8b_q8_2layer", 128), ("llama3_8b_q8_2layer", 200), ("qwen3_4b_q8_2layer", 70)])
