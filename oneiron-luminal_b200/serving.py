@@ -166,6 +166,13 @@ class ContinuousBatcher:
         self.rounds += 1
         return [self.finished[i] for i in sorted(set(self.finished) - before)]
 
+    def stats(self) -> Dict[str, float]:
+        """Counters of the loop so far: how full the batched steps were is what decides the tokens/s of a server."""
+        return {"rounds": self.rounds, "steps": self.steps_run, "rows": self.rows_run,
+                "rows_per_step": self.rows_run / self.steps_run if self.steps_run else 0.0,
+                "live": len(self.live), "queued": len(self.queue), "finished": len(self.finished),
+                "pages_promised": self.promised, "pages_in_pool": self.pool_pages}
+
     def run(self) -> Dict[int, List[int]]:
         """Until the queue and the live set are empty.  Returns request id -> generated tokens."""
         while self.queue or self.live:

@@ -162,6 +162,8 @@ def test_every_request_gets_what_it_gets_alone():
     begins = [c[1] for c in rt.calls if c[0] == "begin"]
     assert max(len(s) for s in begins) == 4
     assert b.rows_run > b.steps_run           # more than one sequence per step on average
+    st = b.stats()
+    assert st["finished"] == 13 and st["live"] == 0 and st["queued"] == 0 and 1.0 < st["rows_per_step"] <= 4.0
 
 
 def test_end_of_sequence_id_ends_a_request_and_frees_its_slot():
