@@ -8,7 +8,8 @@ give the GPU tests a fixed target that does not depend on rebuilding the oracle 
     python tests/golden/make_golden.py llama3_8b_q8    # a full-size case (tens of minutes of CPU time, ~12 GB of RAM)
     python tests/golden/make_golden.py qwen3_4b_q8
     python tests/golden/make_golden.py gpt_oss_20b_q8  # ~23 GB of RAM
-    python tests/golden/make_golden.py llama3_8b_q8_prefill4096   # a 4096-token prompt: about three and a half hours on 8 cores
+    python tests/golden/make_golden.py llama3_8b_q8_prefill4096   # a 4096-token prompt: about two and a half hours on 8 cores
+    python tests/golden/make_golden.py llama3_8b_q8_batch4        # four sequences for batched decode: about 40 minutes
 
 Full-size cases are the configurations the benchmark numbers are quoted on: whole model, whole vocabulary, the
 benchmark's seed and prompt.  They hold the prompt, the first 32 greedy tokens with their top-1/top-2 margins,
@@ -81,12 +82,41 @@ def full_case(pkg, name):
           f"({time.time() - t0:.0f} s)", flush=True)
 
 
+# batched decode on the whole Llama-3-8B-shape model: sequences of different lengths decoded side by side, one row each per step.
+# The oracle runs them one after the other (they do not interact).  name: (config, seed, first prompt length, sequences, steps)
+BATCH_CASES = {
+    "llama3_8b_q8_batch4": ("llama3_8b_q8", FULL_SEED, 256, 4, 16),
+}
+
+
+def batch_case(pkg, name):
+    cfg, seed, n_prompt, n_seq, n_new = BATCH_CASES[name]
+    d = pkg.CONFIGS[cfg].copy(max_seq=n_prompt + n_seq + n_new + 8)
+    t0 = time.time()
+    m = OracleModel(d)
+    m.synth(seed)
+    base = m.synth_tokens(seed, n_prompt + n_seq)
+    prompts, toks, margins, last = [], [], [], []
+    for sq in range(n_seq):
+        prompt = base[sq:sq + n_prompt + sq // 2]             # different lengths: 256, 256, 257, 257 tokens, shifted starts
+        t, logits, mg = m.generate(prompt, n_new + 1, return_last_logits=True, return_margins=True)
+        prompts.append(np.array(prompt, dtype=np.int32)); toks.append(t); margins.append(mg); last.append(logits.astype(np.float32))
+        print(f"{name}: sequence {sq} done after {time.time() - t0:.0f} s, min margin {min(mg):.3e}", flush=True)
+    np.savez_compressed(os.path.join(HERE, f"{name}_full.npz"), config=cfg, seed=seed, n_seq=n_seq,
+                        prompt_lens=np.array([len(p) for p in prompts], dtype=np.int32), prompts=np.concatenate(prompts),
+                        tokens=np.array(toks, dtype=np.int32), margins=np.array(margins, dtype=np.float32), last_logits=np.stack(last))
+    print(name, "tokens", toks, f"({time.time() - t0:.0f} s)", flush=True)
+
+
 def main():
     pkg = load_package()
     wanted = sys.argv[1:]
     if wanted:
         for name in wanted:
-            full_case(pkg, name)
+            if name in BATCH_CASES:
+                batch_case(pkg, name)
+            else:
+                full_case(pkg, name)
         return
     for name, (cfg, seed, n_prompt, n_new) in CASES.items():
         m = OracleModel(pkg.CONFIGS[cfg])

@@ -414,6 +414,46 @@ def test_full_size_4096_token_prompt_matches_oracle_fixture(pkg):
         rt.close()
 
 
+def test_full_size_batched_decode_matches_oracle_fixture(pkg):
+    """Batched decode on the whole Llama-3-8B-shape model against the oracle: four sequences with prompts of different lengths
+    (each taken as rows), then 16 steps of all four together, one row per sequence and step through the tensor-core GEMM and
+    the split rows attention.  Every sequence's tokens equal the oracle's, the last step's logits within 1e-2."""
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama3_8b_q8_batch4_full.npz")
+    if not os.path.exists(path):
+        pytest.skip(f"no fixture {path}")
+    fx = np.load(path)
+    n_seq, lens = int(fx["n_seq"]), [int(v) for v in fx["prompt_lens"]]
+    flat = [int(t) for t in fx["prompts"]]
+    prompts, at = [], 0
+    for n in lens:
+        prompts.append(flat[at:at + n]); at += n
+    want = fx["tokens"]                                   # [n_seq][steps + 1]
+    steps = want.shape[1] - 1
+    desc = pkg.CONFIGS["llama3_8b_q8"].copy(max_batch=n_seq, max_seq=max(lens) + steps + 8, max_new_tokens=steps + 8)
+    rt = pkg.B200Runtime.initialize(device=0)
+    try:
+        rt.load_model(desc)
+        rt.synth(int(fx["seed"]))
+        firsts = []
+        for sq, p in enumerate(prompts):
+            rt.seq_select(sq)
+            rt.set_data(p); rt.execute({"s": len(p), "p": 0})
+            firsts.append(rt.get_token())
+        assert firsts == [int(t) for t in want[:, 0]]
+        rt.batch_begin(firsts, lens)
+        rt.batch_decode(steps)
+        log = rt.batch_get_decoded(steps)
+        for sq in range(n_seq):
+            assert [int(t) for t in log[:, sq]] == [int(t) for t in want[sq, 1:]], (sq, fx["margins"][sq])
+            ref = fx["last_logits"][sq]
+            err = float(np.max(np.abs(rt.batch_get_logits(sq) - ref)) / np.max(np.abs(ref)))
+            assert err <= 1e-2, (sq, err)
+        print(f"batched decode, {n_seq} sequences x {steps} steps: tokens equal; min margin {float(fx['margins'].min()):.2e}")
+    finally:
+        rt.close()
+
+
 # ------------------------------------------------------------------------------------------------- prompts as rows (M > 1)
 @pytest.mark.parametrize("name,n_prompt", [("small_q8", 4), ("small_q8", 33), ("small_q8", 100), ("llama3_8b_q8_2layer", 2), ("llama3_8b_q8_2layer", 32),
                                            ("llama3_8b_q8_2layer", 128), ("llama3_8b_q8_2layer", 200), ("qwen3_4b_q8_2layer", 70)])
